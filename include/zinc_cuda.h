@@ -1,0 +1,308 @@
+/*
+ * zinc_cuda.h - C ABI of the B200 (sm_100a) quantized-matmul library for the
+ * ZINC inference engine's compute-op interface.
+ *
+ * The library replaces the engine's DMMV dispatch layer and the kernels
+ * behind it: the decode dequant-matvec over GGUF blocks, the batched-prefill
+ * dequant-GEMM, the MoE expert matmuls and the routing / activation / combine
+ * steps either side of them. Every entry point below names the reference
+ * interface it stands in for, as <path in the reference project>:<lines>.
+ *
+ * Conventions (shared by all entry points)
+ *  - Every pointer named A, x, y, X, Y, routing, ... is a DEVICE pointer owned
+ *    by the caller; the library borrows it for the call and never frees it.
+ *    `*_size` is the byte size of the caller's buffer behind that pointer and
+ *    is used for bounds validation only (the role of the descriptor range in
+ *    the reference).
+ *  - Offsets keep the reference's units: a_offset / x_offset / y_offset and
+ *    expert_stride are BYTES, x_expert_stride and token strides are ELEMENTS
+ *    (src/compute/dmmv.zig:21-62, 801-803). They are widened to 64 bit.
+ *  - Weight layout is the raw GGUF block stream, row-major by output row,
+ *    K/block_size blocks per row (src/model/gguf.zig:75-122).
+ *  - Work is enqueued on the context's CUDA stream in call order, so a later
+ *    call sees the results of an earlier one; nothing is guaranteed complete
+ *    until zc_submit_and_wait returns (record / submit model of
+ *    src/vulkan/command.zig:222-320, 477).
+ *  - Every function returns a zc_status. No exception crosses the ABI. A
+ *    context is thread-compatible, not thread-safe (one recording thread, as
+ *    in the reference).
+ *  - There is no CPU fallback: a call on a machine without a usable CUDA
+ *    device fails with ZC_ERR_CUDA.
+ */
+#ifndef ZINC_CUDA_H
+#define ZINC_CUDA_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Error model. Mirrors the Zig error set of the dispatch layer:
+ * error.UnsupportedQuantType (src/compute/dmmv.zig:722, 822, 899-901),
+ * error.PipelineNotLoaded (766, 943, 1000, 1064), error.InvalidArgument
+ * (767, 944, 1001-1006, 1065-1066). */
+typedef enum zc_status {
+    ZC_OK = 0,
+    ZC_ERR_UNSUPPORTED_TYPE = 1,
+    ZC_ERR_NOT_LOADED = 2,
+    ZC_ERR_INVALID_ARG = 3,
+    ZC_ERR_OOM = 4,
+    ZC_ERR_CUDA = 5,
+    ZC_ERR_TIMEOUT = 6
+} zc_status;
+
+/* GGML tensor type ids (src/model/gguf.zig:38-69). */
+typedef enum zc_type {
+    ZC_F32 = 0,
+    ZC_F16 = 1,
+    ZC_Q5_0 = 6,
+    ZC_Q5_1 = 7,
+    ZC_Q8_0 = 8,
+    ZC_Q4_K = 12,
+    ZC_Q5_K = 13,
+    ZC_Q6_K = 14,
+    ZC_BF16 = 30,
+    ZC_MXFP4 = 39
+} zc_type;
+
+/* MoE routing rules (src/compute/forward.zig:496-571). Both select the k
+ * largest logits (ties to the lowest index) and give softmax weights over the
+ * selected set; they differ only in rounding order. */
+typedef enum zc_routing_rule {
+    ZC_ROUTE_SOFTMAX_ALL_RENORM = 0, /* topKSoftmax: softmax over all, pick, renormalise */
+    ZC_ROUTE_TOPK_THEN_SOFTMAX = 1   /* topKSoftmaxWeight / softmax_topk.comp */
+} zc_routing_rule;
+
+typedef struct zc_ctx zc_ctx;
+
+/* ---- context ------------------------------------------------------------
+ * Replaces Instance.init + DmmvDispatch.init / deinit
+ * (src/compute/dmmv.zig:305-671, 1098-1129). */
+int32_t zc_init(int32_t device, zc_ctx** out_ctx);
+int32_t zc_destroy(zc_ctx* ctx);
+/* Use a caller-owned cudaStream_t (e.g. the framework's current stream).
+ * NULL restores the context's own stream. */
+int32_t zc_set_stream(zc_ctx* ctx, void* cuda_stream);
+void* zc_get_stream(zc_ctx* ctx);
+/* Text of the last error recorded on this context (never NULL). */
+const char* zc_last_error(zc_ctx* ctx);
+const char* zc_status_string(int32_t status);
+/* Number of kernels this context has launched so far. */
+uint64_t zc_launch_count(zc_ctx* ctx);
+
+/* ---- buffers --------------------------------------------------------------
+ * Replaces Buffer.initDeviceLocal / initStaging / upload
+ * (src/vulkan/buffer.zig:102-149). Optional: any device pointer works. */
+int32_t zc_alloc(zc_ctx* ctx, uint64_t bytes, void** out_dptr);
+int32_t zc_free(zc_ctx* ctx, void* dptr);
+int32_t zc_upload(zc_ctx* ctx, void* dst, uint64_t dst_offset, const void* host_src, uint64_t bytes);
+int32_t zc_download(zc_ctx* ctx, void* host_dst, const void* src, uint64_t src_offset, uint64_t bytes);
+int32_t zc_memset(zc_ctx* ctx, void* dst, uint64_t dst_offset, int32_t byte_value, uint64_t bytes);
+
+/* ---- ordering ---------------------------------------------------------------
+ * zc_barrier replaces computeBarrier / computeBufferBarrier
+ * (src/vulkan/command.zig:345-425): a CUDA stream is already ordered, so it
+ * only exists to let call sites port one to one. zc_submit_and_wait replaces
+ * submitAndWait (src/vulkan/command.zig:477): it blocks until the stream is
+ * idle and returns the first deferred device-side error, if any. */
+int32_t zc_barrier(zc_ctx* ctx);
+int32_t zc_submit_and_wait(zc_ctx* ctx);
+
+/* ---- pre-recorded op sequences ----------------------------------------------
+ * The reference records a token's dispatches into a command buffer and
+ * submits it once (src/vulkan/command.zig:222-320, 477). The counterpart here
+ * is a CUDA graph: calls made between zc_begin_record and zc_end_record are
+ * captured instead of executed; zc_replay enqueues the whole sequence with one
+ * launch. Buffers, sizes and offsets are baked in at record time. Host copies
+ * recorded this way must use page-locked host memory. */
+int32_t zc_begin_record(zc_ctx* ctx);
+int32_t zc_end_record(zc_ctx* ctx, void** out_recording);
+int32_t zc_replay(zc_ctx* ctx, void* recording);
+int32_t zc_free_recording(zc_ctx* ctx, void* recording);
+
+/* ---- layout helpers ---------------------------------------------------------
+ * GGMLType.blockSize / bytesPerBlock (src/model/gguf.zig:75-122),
+ * TensorInfo.sizeBytes (src/model/gguf.zig:222-229),
+ * expertSliceBytes (src/compute/forward.zig:650-656). */
+uint32_t zc_block_size(uint32_t type);
+uint32_t zc_bytes_per_block(uint32_t type);
+uint64_t zc_tensor_size_bytes(uint32_t type, uint64_t n_elements);
+uint64_t zc_expert_slice_bytes(uint32_t type, uint32_t rows, uint32_t cols);
+/* 1 if the type has a DMMV kernel: pipelineForType (src/compute/dmmv.zig:678-691). */
+int32_t zc_dmmv_supported(uint32_t type);
+/* 1 if the type has a MoE DMMV kernel: moePipelineForType (src/compute/dmmv.zig:694-703). */
+int32_t zc_moe_dmmv_supported(uint32_t type);
+
+/* ---- decode matvec ------------------------------------------------------------
+ * y[M] (+)= W[M x K] . x[K].  acc_mode 0: y = result, 1: y += result.
+ * Replaces DmmvDispatch.recordDispatch (src/compute/dmmv.zig:806-874) together
+ * with the variant policy of dispatchDmmvInner (src/compute/forward.zig:8414-8540):
+ * the tall-M and batch-shader special cases there are an internal choice here.
+ * Types: q4_k, q5_k, q6_k, q8_0, mxfp4, q5_0, q5_1, f16, f32; any other type
+ * returns ZC_ERR_UNSUPPORTED_TYPE. K must be a multiple of the block size;
+ * x + x_offset must be 16-byte aligned (src/shaders/dmmv_q6k.comp:24-27). */
+int32_t zc_dmmv(zc_ctx* ctx, uint32_t type,
+                const void* A, uint64_t a_size, const void* x, uint64_t x_size,
+                void* y, uint64_t y_size,
+                uint32_t M, uint32_t K,
+                uint64_t a_offset, uint64_t x_offset, uint64_t y_offset, uint32_t acc_mode);
+
+/* out[r] = silu(Wg[r].x) * (Wu[r].x), one pass over both weight streams.
+ * Replaces dispatchDmmvFusedGateUpSwiglu and its Q8_0 sibling
+ * (src/compute/forward.zig:8237-8313; src/shaders/dmmv_q4k_fused_gate_up_swiglu.comp:195-218).
+ * Gate and up must share `type`. The reference has q4_k and q8_0 only; every
+ * DMMV type is accepted here. */
+int32_t zc_dmmv_fused_gate_up_swiglu(zc_ctx* ctx, uint32_t type,
+                                     const void* Wg, uint64_t wg_size, const void* Wu, uint64_t wu_size,
+                                     const void* x, uint64_t x_size, void* out, uint64_t out_size,
+                                     uint32_t M, uint32_t K,
+                                     uint64_t gate_offset, uint64_t up_offset,
+                                     uint64_t x_offset, uint64_t out_offset);
+
+/* y[r] += sigmoid(gate[gate_index]) * (W[r].x).  Replaces dispatchDmmvQ8_0SigmoidAcc
+ * (src/compute/forward.zig:8321-8359; src/compute/dmmv.zig:101-108;
+ * src/shaders/dmmv_q8_0_sigmoid_acc.comp:95-132). `gate_index` counts f32
+ * elements. The reference has q8_0 only; every DMMV type is accepted. */
+int32_t zc_dmmv_sigmoid_acc(zc_ctx* ctx, uint32_t type,
+                            const void* A, uint64_t a_size, const void* x, uint64_t x_size,
+                            void* y, uint64_t y_size, const void* gate, uint64_t gate_size,
+                            uint32_t M, uint32_t K,
+                            uint64_t a_offset, uint64_t x_offset, uint64_t y_offset, uint32_t gate_index);
+
+/* ---- batched prefill -------------------------------------------------------------
+ * Y[c][M] = W . X[c][K] for c < num_cols; X is [num_cols][K] f32, Y is
+ * [num_cols][M] f32 (src/compute/forward.zig:8141-8146). Replaces
+ * recordBatchDispatchPush (src/compute/dmmv.zig:880-926) and the 40-column
+ * chunk loop of dispatchProjectionBatched (src/compute/forward.zig:8147-8216):
+ * num_cols is unbounded and chunking is internal. The reference supports q4_k
+ * and q6_k; every K-quant and 32-block type is accepted. */
+int32_t zc_dmmv_batch(zc_ctx* ctx, uint32_t type,
+                      const void* A, uint64_t a_size, const void* X, uint64_t x_size,
+                      void* Y, uint64_t y_size,
+                      uint32_t M, uint32_t K,
+                      uint64_t a_offset, uint64_t x_offset, uint64_t y_offset, uint32_t num_cols);
+
+/* Tiled dequant-GEMM on the tensor cores: D[col][row] = sum_k A[row][k] B[col][k].
+ * Replaces recordMulMmQ4K (src/compute/dmmv.zig:1045-1094; src/shaders/mul_mm_q4k.comp:74-243)
+ * and the Metal tiled GEMMs (src/shaders/metal/gemm_q4k.metal:54-225, gemm_q6k.metal:38-68).
+ * B and D are column-major with element strides stride_b / stride_d; b_offset
+ * and d_offset count ELEMENTS, a_offset BYTES (src/compute/dmmv.zig:139-145).
+ * act_type selects B's element type: ZC_F32 (rounded to bf16 on load) or
+ * ZC_BF16. D is f32. Weights are dequantised to bf16 tiles and multiplied with
+ * f32 accumulation. K must be a multiple of 256 for K-quants (InvalidArgument
+ * otherwise, as the reference). */
+int32_t zc_mul_mm(zc_ctx* ctx, uint32_t type,
+                  const void* A, uint64_t a_size, const void* B, uint64_t b_size,
+                  void* D, uint64_t d_size,
+                  uint32_t M, uint32_t N, uint32_t K,
+                  uint32_t stride_b, uint32_t stride_d,
+                  uint64_t a_offset, uint64_t b_offset, uint64_t d_offset, uint32_t act_type);
+
+/* ---- MoE expert matvecs ---------------------------------------------------------------
+ * For slot s < n_used: e = routing[s]; Y[s][M] = W[e] . X[s*x_expert_stride .. +K].
+ * x_expert_stride 0 = all slots share x. routing holds u32 expert ids first
+ * (src/shaders/softmax_topk.comp:19-22). Replaces recordMoeDispatch
+ * (src/compute/dmmv.zig:709-739) and the per-type MoE shaders
+ * (src/shaders/dmmv_q4k_moe_kpar.comp:56-175 and siblings). */
+int32_t zc_moe_dmmv(zc_ctx* ctx, uint32_t type,
+                    const void* A, uint64_t a_size, const void* x, uint64_t x_size,
+                    void* y, uint64_t y_size, const void* routing, uint64_t routing_size,
+                    uint32_t M, uint32_t K,
+                    uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride,
+                    uint64_t x_offset, uint64_t y_offset);
+
+/* Gate and up for the same slots in one pass: Yg[s] = Wg[e].x, Yu[s] = Wu[e].x.
+ * Replaces the fused gate+up MoE dispatch
+ * (src/shaders/dmmv_q4k_fused_gate_up_moe.comp:77-217; src/compute/forward.zig:6206-6222). */
+int32_t zc_moe_fused_gate_up(zc_ctx* ctx, uint32_t type,
+                             const void* Wg, uint64_t wg_size, const void* Wu, uint64_t wu_size,
+                             const void* x, uint64_t x_size,
+                             void* y_gate, uint64_t yg_size, void* y_up, uint64_t yu_size,
+                             const void* routing, uint64_t routing_size,
+                             uint32_t M, uint32_t K,
+                             uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride,
+                             uint64_t x_offset, uint64_t y_offset);
+
+/* hidden[r] += sum_{s<n_used} w_s * (W[id_s][r] . X[s*x_expert_stride ..]);
+ * routing = [n_used ids u32][n_used weights f32 bits]. Replaces the fused
+ * down + weighted-accumulate dispatch (src/compute/dmmv.zig:68-76;
+ * src/shaders/dmmv_q4k_moe_fused_down_acc.comp:74-177). */
+int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type,
+                              const void* A, uint64_t a_size, const void* x, uint64_t x_size,
+                              void* y, uint64_t y_size, const void* routing, uint64_t routing_size,
+                              uint32_t M, uint32_t K,
+                              uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride,
+                              uint64_t x_offset, uint64_t y_offset);
+
+/* Cross-token MoE matvec: Y[t][s][M] = W[routing[t*n_experts_used + s]] . X[t][K];
+ * routing is the flattened [n_tokens][n_experts_used] id table; strides in
+ * elements. K % 256 != 0 returns ZC_ERR_INVALID_ARG for K-quants. Replaces
+ * recordMoeBatchedDispatch (src/compute/dmmv.zig:746-792;
+ * src/shaders/dmmv_q4k_moe_batched.comp:70-164). Tokens that share an expert
+ * are grouped so each expert's weights are read once. */
+int32_t zc_moe_dmmv_batched(zc_ctx* ctx, uint32_t type,
+                            const void* A, uint64_t a_size, const void* X, uint64_t x_size,
+                            void* Y, uint64_t y_size, const void* routing, uint64_t routing_size,
+                            uint32_t M, uint32_t K, uint64_t expert_stride,
+                            uint32_t n_experts, uint32_t n_experts_used, uint32_t n_tokens,
+                            uint32_t x_token_stride, uint32_t y_token_stride);
+
+/* ---- routing, combine, activation -----------------------------------------------------------
+ * zc_softmax_topk: per token t, out[t*out_stride ..] = [k ids u32][k weights f32 bits].
+ * Replaces dispatchSoftmaxTopk (src/compute/forward.zig:4135-4210;
+ * src/shaders/softmax_topk.comp:35-103) and the CPU routers
+ * (src/compute/forward.zig:496-571). `bias` may be NULL; otherwise bias[e] is
+ * added to logit e first (src/compute/forward.zig:6752-6754). n_experts is not
+ * limited to 256 and k not to 16. */
+int32_t zc_softmax_topk(zc_ctx* ctx, const void* logits, uint64_t logits_size,
+                        const void* bias, void* out, uint64_t out_size,
+                        uint32_t n_experts, uint32_t k, uint32_t rule,
+                        uint32_t n_tokens, uint32_t logits_stride, uint32_t out_stride);
+
+/* a[i] += sum_j w_j * b[j*src_stride + i]; w_j = f32 bits at routing[n_used + j].
+ * Replaces dispatchMoeWeightedAcc (src/shaders/moe_weighted_acc.comp:23-33). */
+int32_t zc_moe_weighted_acc(zc_ctx* ctx, void* a, uint64_t a_size, const void* b, uint64_t b_size,
+                            const void* routing, uint64_t routing_size,
+                            uint32_t n, uint32_t n_used, uint32_t src_stride);
+
+/* y = silu(gate) * up (src/shaders/swiglu.comp:25-33) and the GPT-OSS variant
+ * (src/shaders/swiglu_oai.comp:24-34; src/compute/forward.zig:607-616). */
+int32_t zc_swiglu(zc_ctx* ctx, const void* gate, const void* up, void* y, uint32_t n);
+int32_t zc_swiglu_oai(zc_ctx* ctx, const void* gate, const void* up, void* y, uint32_t n);
+
+/* counts[e] = number of cells equal to e in the routing capture buffer of one
+ * layer. Replaces recordCountExperts (src/compute/dmmv.zig:981-1028;
+ * src/shaders/count_experts.comp:58-83). d_offset_bytes as there. */
+int32_t zc_count_experts(zc_ctx* ctx, const void* routing, uint64_t routing_size,
+                         void* counts, uint64_t counts_size,
+                         uint32_t n_tokens, uint32_t n_layers, uint32_t layer,
+                         uint32_t n_experts_used, uint32_t n_experts, uint64_t d_offset_bytes);
+
+/* Grouped-by-expert prefill path (the reference's Metal path):
+ * zc_moe_route_pack: per expert the list of route ids (token*k + slot) in
+ * token order and their count (src/shaders/metal/moe_route_pack.metal:13-36).
+ * zc_moe_route_scatter: dst[t][d] += sum_slot w * src[t*k + slot][d]
+ * (src/shaders/metal/moe_route_scatter.metal:20-96). */
+int32_t zc_moe_route_pack(zc_ctx* ctx, const void* routing, uint64_t routing_size,
+                          void* counts, uint64_t counts_size, void* ids, uint64_t ids_size,
+                          uint32_t n_tokens, uint32_t n_experts, uint32_t k,
+                          uint32_t routing_stride, uint32_t ids_stride);
+int32_t zc_moe_route_scatter(zc_ctx* ctx, const void* routing, uint64_t routing_size,
+                             const void* src, uint64_t src_size, void* dst, uint64_t dst_size,
+                             uint32_t n_tokens, uint32_t hidden_dim, uint32_t k, uint32_t routing_stride);
+
+/* ---- parity / embedding rows ---------------------------------------------------------------------
+ * out[r][0..K) = dequantised row (first_row + r) of A, bit-identical to the
+ * reference's CPU dequantRow (src/compute/forward.zig:242-465; Q5_1 from
+ * src/compute/forward_metal.zig:6704-6729): products and differences are
+ * rounded separately, never fused. Also serves the embedding-row lookup the
+ * reference does on the CPU (src/compute/forward.zig:9391-9398). */
+int32_t zc_dequant_rows(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size,
+                        void* out, uint64_t out_size,
+                        uint64_t first_row, uint32_t n_rows, uint32_t K, uint64_t a_offset);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ZINC_CUDA_H */

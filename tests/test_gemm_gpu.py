@@ -1,0 +1,87 @@
+"""GPU parity of the batched-prefill paths (zc_dmmv_batch, zc_mul_mm) against the f64 oracle.
+
+Bars: f32-activation paths relative L2 <= 1e-4 when they keep f32 precision; the bf16
+tensor-core path <= 5e-3 against the exact product and <= 1e-4 against the oracle evaluated
+on bf16-rounded operands (the arithmetic that path actually computes).
+"""
+import numpy as np
+import pytest
+
+import zinc_b200 as zb
+from zinc_b200 import synth
+from helpers import canary_intact, dev, out_with_canary, rel_l2
+
+pytestmark = pytest.mark.gpu
+TOL_F32, TOL_BF16 = 1e-4, 5e-3
+
+
+@pytest.mark.parametrize("t", [zb.Q4_K, zb.Q6_K, zb.Q5_K, zb.Q8_0, zb.MXFP4],
+                         ids=["q4_k", "q6_k", "q5_k", "q8_0", "mxfp4"])
+@pytest.mark.parametrize("cols", [1, 5, 40, 129])
+def test_dmmv_batch(gpu, oracle, t, cols):
+    # Y[c][M] = W X[c][K]  (src/compute/dmmv.zig:880-926; layouts src/compute/forward.zig:8141-8146)
+    torch, ctx, dd = gpu
+    M = 96 + 7
+    K = 512 if zb.block_size(t) == 256 else 160
+    g = synth.rng(300, t * 1000 + cols)
+    w = synth.quant_matrix(g, t, M, K)
+    X = synth.activations(g, cols, K)
+    Y = out_with_canary(torch, cols * M)
+    dd.recordBatchDispatchPush(t, dev(torch, w), dev(torch, X), Y, M, K, 0, 0, 0, cols)
+    ctx.submit_and_wait()
+    got = Y[:cols * M].cpu().numpy().reshape(cols, M)
+    exact = oracle.gemm_f64(w, t, M, K, X)
+    assert canary_intact(Y, cols * M)
+    e = rel_l2(got, exact)
+    if e > TOL_F32:  # tensor-core path: compare with the bf16-operand product
+        assert e <= TOL_BF16
+        assert rel_l2(got, oracle.gemm_f64(w, t, M, K, X, round_bf16=True)) <= TOL_F32
+
+
+@pytest.mark.parametrize("t", [zb.Q4_K, zb.Q6_K], ids=["q4_k", "q6_k"])
+@pytest.mark.parametrize("act", ["f32", "bf16"])
+@pytest.mark.parametrize("M,N,K", [(64, 16, 256), (300, 77, 1024), (1024, 256, 2048)])
+def test_mul_mm(gpu, oracle, t, act, M, N, K):
+    # D[col][row] = sum_k A[row][k] B[col][k], strided column-major B and D (src/compute/dmmv.zig:1045-1094)
+    torch, ctx, dd = gpu
+    g = synth.rng(301, t * 100 + M)
+    w = synth.quant_matrix(g, t, M, K)
+    Bm = synth.activations(g, N, K)
+    stride_b, stride_d, b_off, d_off = K + 8, M + 4, 16, 8
+    Bpad = np.zeros(b_off + N * stride_b, np.float32)
+    for c in range(N):
+        Bpad[b_off + c * stride_b: b_off + c * stride_b + K] = Bm[c]
+    if act == "bf16":
+        bits = synth.to_bf16_bits(Bpad)
+        Bd = dev(torch, bits.view(np.int16))
+        Bexact = synth.bf16_bits_to_f32(synth.to_bf16_bits(Bm))
+    else:
+        Bd = dev(torch, Bpad)
+        Bexact = Bm
+    D = out_with_canary(torch, d_off + N * stride_d)
+    dd.recordMulMm(t, dev(torch, w), Bd, D, M, N, K, stride_b, stride_d, 0, b_off, d_off,
+                   zb.BF16 if act == "bf16" else zb.F32)
+    ctx.submit_and_wait()
+    got = D[d_off:d_off + N * stride_d].cpu().numpy().reshape(N, stride_d)
+    assert canary_intact(D, d_off + N * stride_d)
+    assert np.all(got[:, M:] == 0.0), "padding between columns must stay untouched"
+    exact = oracle.gemm_f64(w, t, M, K, Bexact)
+    e = rel_l2(got[:, :M], exact)
+    assert e <= TOL_BF16
+    if e > TOL_F32:
+        assert rel_l2(got[:, :M], oracle.gemm_f64(w, t, M, K, Bexact, round_bf16=True)) <= TOL_F32
+
+
+def test_mul_mm_errors(gpu):
+    torch, ctx, dd = gpu
+    w = torch.zeros(144 * 8, dtype=torch.uint8, device="cuda")
+    b = torch.zeros(4 * 256, device="cuda")
+    d = torch.zeros(4 * 8, device="cuda")
+    with pytest.raises(zb.InvalidArgument):  # K misaligned (src/compute/dmmv.zig:1065)
+        dd.recordMulMmQ4K(w, b, d, 8, 4, 200, 256, 8)
+    with pytest.raises(zb.InvalidArgument):  # N == 0 (src/compute/dmmv.zig:1066)
+        dd.recordMulMmQ4K(w, b, d, 8, 0, 256, 256, 8)
+    with pytest.raises(zb.UnsupportedQuantType):
+        dd.recordMulMm(11, w, b, d, 8, 4, 256, 256, 8)
+    dd.recordMulMmQ4K(w, b, d, 8, 4, 256, 256, 8)
+    ctx.submit_and_wait()

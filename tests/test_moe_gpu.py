@@ -1,0 +1,231 @@
+"""GPU parity of the MoE expert matvecs and of the routing / activation / combine steps around them."""
+import numpy as np
+import pytest
+
+import zinc_b200 as zb
+from zinc_b200 import synth
+from helpers import canary_intact, dev, out_with_canary, rel_l2
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-4
+MOE_TYPES = [zb.Q4_K, zb.Q5_K, zb.Q6_K, zb.MXFP4, zb.Q5_1, zb.Q8_0]
+IDS = [zb.TYPE_NAMES[t] for t in MOE_TYPES]
+
+
+def stacked(g, t, E, M, K):
+    w = synth.quant_matrix(g, t, E * M, K)
+    return w, zb.expert_slice_bytes(t, M, K)
+
+
+def routing_buf(ids, weights=None):
+    ids = np.asarray(ids, np.uint32)
+    if weights is None:
+        weights = np.full(ids.size, 1.0 / ids.size, np.float32)
+    return np.concatenate([ids, np.asarray(weights, np.float32).view(np.uint32)])
+
+
+@pytest.mark.parametrize("t", MOE_TYPES, ids=IDS)
+@pytest.mark.parametrize("shared_x", [False, True])
+def test_moe_dmmv(gpu, oracle, t, shared_x):
+    # recordMoeDispatch (src/compute/dmmv.zig:709-739): Y[s] = W[routing[s]] X[s*x_expert_stride..]
+    torch, ctx, dd = gpu
+    E, M, n_used = 5, 45, 3
+    K = 512 if zb.block_size(t) == 256 else 96
+    g = synth.rng(200, t)
+    w, stride = stacked(g, t, E, M, K)
+    ids = np.array([4, 0, 2], np.uint32)
+    x = synth.activations(g, 1 if shared_x else n_used, K)
+    y = out_with_canary(torch, n_used * M)
+    dd.recordMoeDispatch(t, dev(torch, w), dev(torch, x), y, dev(torch, routing_buf(ids)), M, K, stride, n_used,
+                         0 if shared_x else K)
+    ctx.submit_and_wait()
+    xs = np.repeat(x, n_used, axis=0) if shared_x else x
+    want = oracle.moe_dmmv_f64(w, t, M, K, stride, ids, K, xs)
+    assert canary_intact(y, n_used * M)
+    assert rel_l2(y[:n_used * M].cpu().numpy(), want) <= TOL
+
+
+def test_reference_fixture_q4k_moe(gpu, oracle):
+    # src/compute/forward_metal.zig:11582-11681: M=65, K=512, experts {2, 0}, abs tol 0.05
+    torch, ctx, dd = gpu
+    w, x, ids = synth.pattern_q4k_moe()
+    M, K, n_used = 65, 512, 2
+    stride = zb.expert_slice_bytes(zb.Q4_K, M, K)
+    y = out_with_canary(torch, n_used * M)
+    dd.recordMoeDispatch(zb.Q4_K, dev(torch, w), dev(torch, x), y, dev(torch, routing_buf(ids)), M, K, stride,
+                         n_used, K)
+    ctx.submit_and_wait()
+    got = y[:n_used * M].cpu().numpy().reshape(n_used, M)
+    for s in range(n_used):
+        want = oracle.dmmv_f32seq(w[int(ids[s]) * stride:(int(ids[s]) + 1) * stride], zb.Q4_K, M, K, x[s])
+        assert np.max(np.abs(got[s] - want)) <= 0.05
+
+
+@pytest.mark.parametrize("t", [zb.Q4_K, zb.MXFP4], ids=["q4_k", "mxfp4"])
+def test_moe_fused_gate_up(gpu, oracle, t):
+    torch, ctx, dd = gpu
+    E, M, n_used = 4, 33, 2
+    K = 512 if t == zb.Q4_K else 2880
+    g = synth.rng(201, t)
+    wg, stride = stacked(g, t, E, M, K)
+    wu, _ = stacked(g, t, E, M, K)
+    ids = np.array([3, 1], np.uint32)
+    x = synth.activations(g, 1, K)
+    yg, yu = out_with_canary(torch, n_used * M), out_with_canary(torch, n_used * M)
+    dd.dispatchMoeFusedGateUp(t, dev(torch, wg), dev(torch, wu), dev(torch, x), yg, yu,
+                              dev(torch, routing_buf(ids)), M, K, stride, n_used, 0)
+    ctx.submit_and_wait()
+    xs = np.repeat(x, n_used, axis=0)
+    assert rel_l2(yg[:n_used * M].cpu().numpy(), oracle.moe_dmmv_f64(wg, t, M, K, stride, ids, K, xs)) <= TOL
+    assert rel_l2(yu[:n_used * M].cpu().numpy(), oracle.moe_dmmv_f64(wu, t, M, K, stride, ids, K, xs)) <= TOL
+    assert canary_intact(yg, n_used * M) and canary_intact(yu, n_used * M)
+
+
+@pytest.mark.parametrize("t", [zb.Q4_K, zb.Q5_K, zb.Q6_K], ids=["q4_k", "q5_k", "q6_k"])
+def test_moe_fused_down_acc(gpu, oracle, t):
+    # hidden[r] += sum_s w_s * (W[id_s][r] . X[s])  (src/shaders/dmmv_q4k_moe_fused_down_acc.comp:74-177)
+    torch, ctx, dd = gpu
+    E, M, K, n_used = 6, 203, 512, 4
+    g = synth.rng(202, t)
+    w, stride = stacked(g, t, E, M, K)
+    ids = np.array([5, 0, 3, 1], np.uint32)
+    wts = np.array([0.4, 0.3, 0.2, 0.1], np.float32)
+    x = synth.activations(g, n_used, K)
+    h0 = synth.activations(g, M)
+    y = out_with_canary(torch, M)
+    y[:M] = dev(torch, h0)
+    dd.dispatchMoeFusedDownAcc(t, dev(torch, w), dev(torch, x), y, dev(torch, routing_buf(ids, wts)), M, K, stride,
+                               n_used, K)
+    ctx.submit_and_wait()
+    per = oracle.moe_dmmv_f64(w, t, M, K, stride, ids, K, x)
+    want = h0 + (wts.astype(np.float64)[:, None] * per).sum(0)
+    assert canary_intact(y, M)
+    assert rel_l2(y[:M].cpu().numpy(), want) <= TOL
+
+
+def test_moe_dmmv_batched(gpu, oracle):
+    # Y[t][s][M] = W[routing[t*k+s]] X[t]  (src/compute/dmmv.zig:746-792)
+    torch, ctx, dd = gpu
+    t = zb.Q4_K
+    E, M, K, k, T = 7, 24, 512, 2, 9
+    g = synth.rng(203, 0)
+    w, stride = stacked(g, t, E, M, K)
+    ids = g.integers(0, E, size=(T, k)).astype(np.uint32)
+    X = synth.activations(g, T, K)
+    Y = out_with_canary(torch, T * k * M)
+    dd.recordMoeBatchedDispatch(t, dev(torch, w), dev(torch, X), Y, dev(torch, ids), M, K, stride, E, k, T, K, k * M)
+    ctx.submit_and_wait()
+    got = Y[:T * k * M].cpu().numpy().reshape(T, k, M)
+    for tok in range(T):
+        want = oracle.moe_dmmv_f64(w, t, M, K, stride, ids[tok], K, np.repeat(X[tok:tok + 1], k, axis=0))
+        assert rel_l2(got[tok], want) <= TOL
+    assert canary_intact(Y, T * k * M)
+    with pytest.raises(zb.InvalidArgument):  # K % 256 != 0 (src/compute/dmmv.zig:767)
+        dd.recordMoeBatchedDispatch(t, dev(torch, w), dev(torch, X), Y, dev(torch, ids), M, 200, stride, E, k, T, K,
+                                    k * M)
+
+
+@pytest.mark.parametrize("rule", [zb.ROUTE_SOFTMAX_ALL_RENORM, zb.ROUTE_TOPK_THEN_SOFTMAX])
+@pytest.mark.parametrize("n,k,T", [(8, 3, 1), (256, 8, 64), (32, 4, 17), (1000, 20, 3)])
+def test_softmax_topk(gpu, oracle, rule, n, k, T):
+    torch, ctx, dd = gpu
+    g = synth.rng(204, n * 10 + rule)
+    logits = synth.activations(g, T, n)
+    out = torch.zeros(T * 2 * k, dtype=torch.int32, device="cuda")
+    dd.dispatchSoftmaxTopk(dev(torch, logits), out, n, k, rule, T)
+    ctx.submit_and_wait()
+    got = out.cpu().numpy().view(np.uint32).reshape(T, 2 * k)
+    fn = oracle.topk_softmax if rule == zb.ROUTE_SOFTMAX_ALL_RENORM else oracle.topk_softmax_weight
+    for tok in range(T):
+        ids, w = fn(logits[tok], k)
+        assert np.array_equal(got[tok, :k], ids)
+        assert np.max(np.abs(got[tok, k:].view(np.float32) - w)) <= 1e-6
+
+
+def test_softmax_topk_reference_cases_and_bias(gpu, oracle):
+    # src/compute/forward.zig:11392-11407, 11620-11710; bias add: forward.zig:6752-6754
+    torch, ctx, dd = gpu
+
+    def run(lg, k, rule, bias=None):
+        out = torch.zeros(2 * k, dtype=torch.int32, device="cuda")
+        dd.dispatchSoftmaxTopk(dev(torch, np.asarray(lg, np.float32)), out, len(lg), k, rule, 1,
+                               bias=None if bias is None else dev(torch, np.asarray(bias, np.float32)))
+        ctx.submit_and_wait()
+        o = out.cpu().numpy().view(np.uint32)
+        return o[:k], o[k:].view(np.float32)
+
+    ids, w = run([1.0, 3.0, 0.5, 2.0, 4.0, 1.5, 0.1, 0.2], 3, 0)
+    assert list(ids) == [4, 1, 3] and abs(w.sum() - 1) < 1e-5 and w[0] > w[1] > w[2]
+    ids, w = run([1.0, 1.0, 1.0, 1.0], 2, 0)
+    assert list(ids) == [0, 1] and np.allclose(w, 0.5, atol=1e-6)  # ties go to the lowest index
+    ids, w = run([1.0, 1.0, 1.0, 1.0], 2, 1)
+    assert list(ids) == [0, 1] and np.allclose(w, 0.5, atol=1e-6)
+    ids, w = run([100.0, 0.0, -100.0], 2, 0)
+    assert list(ids) == [0, 1] and w[0] > 0.99
+    ids, w = run([-9.0, -2.0, -5.0], 1, 1)
+    assert ids[0] == 1 and abs(w[0] - 1) < 1e-6
+    lg, bias = [0.0, 0.1, 0.2, 0.3], [1.0, 0.0, 0.0, -1.0]
+    ids, w = run(lg, 2, 1, bias)
+    want_ids, want_w = oracle.topk_softmax_weight(np.add(lg, bias, dtype=np.float32), 2)
+    assert np.array_equal(ids, want_ids) and np.allclose(w, want_w, atol=1e-6)
+
+
+def test_weighted_acc_swiglu_count_pack_scatter(gpu, oracle):
+    torch, ctx, dd = gpu
+    g = synth.rng(205, 0)
+    # moe_weighted_acc: a[i] += sum_j w_j b[j*stride+i]
+    n, n_used, stride = 2048 + 3, 8, 2100
+    a0 = synth.activations(g, n)
+    b = synth.activations(g, n_used * stride)
+    r = routing_buf(np.arange(n_used), g.uniform(0, 1, n_used).astype(np.float32))
+    a = out_with_canary(torch, n)
+    a[:n] = dev(torch, a0)
+    dd.dispatchMoeWeightedAcc(a, dev(torch, b), dev(torch, r), n, n_used, stride)
+    ctx.submit_and_wait()
+    assert canary_intact(a, n)
+    assert rel_l2(a[:n].cpu().numpy(), oracle.moe_weighted_acc(a0, b, r, n, n_used, stride)) <= 1e-6
+    # swiglu / swiglu_oai
+    gate, up = synth.activations(g, 4099) * 4, synth.activations(g, 4099) * 4
+    for oai in (False, True):
+        y = out_with_canary(torch, 4099)
+        dd.dispatchSwiglu(dev(torch, gate), dev(torch, up), y, 4099, oai=oai)
+        ctx.submit_and_wait()
+        assert canary_intact(y, 4099)
+        assert rel_l2(y[:4099].cpu().numpy(), oracle.swiglu(gate, up, oai=oai)) <= 1e-6
+    # count_experts over a [tokens][layers][2k] capture buffer
+    T, L, k, E, layer = 37, 3, 4, 11, 1
+    cap = g.integers(0, E, size=(T, L, 2 * k)).astype(np.uint32)
+    counts = torch.full((E + 4,), -1, dtype=torch.int32, device="cuda")
+    dd.recordCountExperts(dev(torch, cap), counts, T, L, layer, k, E, d_offset_bytes=8)
+    ctx.submit_and_wait()
+    want = oracle.count_experts(cap, E, k, T, 1, 2 * k * L, layer * 2 * k)
+    got = counts.cpu().numpy()
+    assert np.array_equal(got[2:2 + E].astype(np.uint32), want) and got[0] == -1 and got[-1] == -1
+    assert want.sum() == T * k
+    with pytest.raises(zb.InvalidArgument):
+        dd.recordCountExperts(dev(torch, cap), counts, T, L, L, k, E)  # layer out of range
+    # route pack + scatter
+    T, k, E, H = 50, 4, 16, 96
+    stride = 2 * k + 2
+    routing = np.zeros((T, stride), np.uint32)
+    for tok in range(T):
+        routing[tok, :k] = g.choice(E, size=k, replace=False)
+        routing[tok, k:2 * k] = g.uniform(0, 1, k).astype(np.float32).view(np.uint32)
+    cnt = torch.zeros(E, dtype=torch.int32, device="cuda")
+    ids = torch.full((E * T,), -1, dtype=torch.int32, device="cuda")
+    dd.dispatchMoeRoutePack(dev(torch, routing), cnt, ids, T, E, k, stride, T)
+    ctx.submit_and_wait()
+    wc, wi = oracle.moe_route_pack(routing, T, E, k, stride, T)
+    assert np.array_equal(cnt.cpu().numpy().astype(np.uint32), wc)
+    gi = ids.cpu().numpy().astype(np.uint32).reshape(E, T)
+    for e in range(E):
+        assert np.array_equal(gi[e, :wc[e]], wi[e, :wc[e]])
+    src = synth.activations(g, T * k, H)
+    dst0 = synth.activations(g, T, H)
+    dst = out_with_canary(torch, T * H)
+    dst[:T * H] = dev(torch, dst0.reshape(-1))
+    dd.dispatchMoeRouteScatter(dev(torch, routing), dev(torch, src), dst, T, H, k, stride)
+    ctx.submit_and_wait()
+    want = oracle.moe_route_scatter(routing, src, dst0, T, H, k, stride)
+    assert canary_intact(dst, T * H)
+    assert rel_l2(dst[:T * H].cpu().numpy(), want) <= 1e-6

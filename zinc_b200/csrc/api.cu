@@ -1,0 +1,635 @@
+// C ABI of the library: context, argument validation, dispatch to the kernels.
+// Nothing here computes on the CPU; a call either enqueues CUDA work on the
+// context's stream or returns an error status.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "../../include/zinc_cuda.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace zc {
+cudaError_t launch_mul_mm_simple(uint32_t type, const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N,
+                                 uint32_t K, uint32_t stride_b, uint32_t stride_d, bool act_bf16, cudaStream_t s,
+                                 uint64_t* launches);
+}
+
+struct zc_ctx {
+    int device = 0;
+    cudaStream_t own_stream = nullptr;
+    cudaStream_t stream = nullptr;
+    uint64_t launches = 0;
+    uint32_t* status_host = nullptr;  // pinned, mapped: deferred device-side status words
+    uint32_t* status_dev = nullptr;
+    char err[512] = {0};
+};
+
+namespace {
+
+using namespace zc;
+
+int32_t fail(zc_ctx* ctx, int32_t code, const char* fmt, ...) {
+    if (ctx) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(ctx->err, sizeof(ctx->err), fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+int32_t cuda_fail(zc_ctx* ctx, cudaError_t e, const char* what) {
+    if (e == cudaErrorNotSupported) return fail(ctx, ZC_ERR_UNSUPPORTED_TYPE, "%s: unsupported quant type", what);
+    if (e == cudaErrorMemoryAllocation) return fail(ctx, ZC_ERR_OOM, "%s: %s", what, cudaGetErrorString(e));
+    return fail(ctx, ZC_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+
+bool dmmv_type_ok(uint32_t t) {
+    switch (t) {
+        case T_Q4_K: case T_MXFP4: case T_Q5_0: case T_Q5_1: case T_Q5_K:
+        case T_Q6_K: case T_Q8_0: case T_F16: case T_F32: return true;
+        default: return false;
+    }
+}
+
+inline uint64_t row_bytes_of(uint32_t type, uint32_t K) {
+    return (uint64_t)(K / block_size(type)) * bytes_per_block(type);
+}
+
+inline bool range_ok(uint64_t offset, uint64_t need, uint64_t size) {
+    return offset <= size && need <= size - offset;
+}
+
+inline bool aligned(const void* p, uint64_t off, uint64_t a) {
+    return ((reinterpret_cast<uintptr_t>(p) + off) % a) == 0;
+}
+
+#define ZC_ENTER(ctx)                                                              \
+    do {                                                                           \
+        if (!(ctx)) return ZC_ERR_INVALID_ARG;                                     \
+        cudaError_t e_ = cudaSetDevice((ctx)->device);                             \
+        if (e_ != cudaSuccess) return cuda_fail((ctx), e_, "cudaSetDevice");       \
+    } while (0)
+
+// Common checks of one matvec-shaped call.
+int32_t check_mat(zc_ctx* ctx, const char* fn, uint32_t type, const void* A, uint64_t a_size, uint64_t a_offset,
+                  uint64_t a_bytes, uint32_t M, uint32_t K) {
+    if (!dmmv_type_ok(type)) return fail(ctx, ZC_ERR_UNSUPPORTED_TYPE, "%s: unsupported quant type %u", fn, type);
+    if (!A) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: null weight pointer", fn);
+    if (M == 0 || K == 0) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: M and K must be non-zero", fn);
+    if (K % block_size(type) != 0)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: K=%u is not a multiple of the block size %u", fn, K, block_size(type));
+    if (!range_ok(a_offset, a_bytes, a_size))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: weights need %llu bytes at offset %llu, buffer has %llu", fn,
+                    (unsigned long long)a_bytes, (unsigned long long)a_offset, (unsigned long long)a_size);
+    const uint64_t al = (type == T_F32) ? 4 : (type == T_F16 || type == T_Q6_K || type == T_Q8_0 || type == T_Q5_0) ? 2
+                        : (type == T_MXFP4) ? 1 : 4;
+    if (!aligned(A, a_offset, al))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: weight address must be %llu-byte aligned", fn, (unsigned long long)al);
+    return ZC_OK;
+}
+
+int32_t check_vec(zc_ctx* ctx, const char* fn, const char* name, const void* p, uint64_t size, uint64_t offset,
+                  uint64_t need, uint64_t align) {
+    if (!p) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: null %s pointer", fn, name);
+    if (!range_ok(offset, need, size))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: %s needs %llu bytes at offset %llu, buffer has %llu", fn, name,
+                    (unsigned long long)need, (unsigned long long)offset, (unsigned long long)size);
+    if (!aligned(p, offset, align))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: %s address must be %llu-byte aligned", fn, name,
+                    (unsigned long long)align);
+    return ZC_OK;
+}
+
+#define ZC_TRY(expr)                   \
+    do {                               \
+        const int32_t rc_ = (expr);    \
+        if (rc_ != ZC_OK) return rc_;  \
+    } while (0)
+
+inline const uint8_t* u8(const void* p, uint64_t off) { return static_cast<const uint8_t*>(p) + off; }
+inline const float* f32p(const void* p, uint64_t off) {
+    return reinterpret_cast<const float*>(static_cast<const uint8_t*>(p) + off);
+}
+inline float* f32m(void* p, uint64_t off) { return reinterpret_cast<float*>(static_cast<uint8_t*>(p) + off); }
+
+}  // namespace
+
+extern "C" {
+
+int32_t zc_init(int32_t device, zc_ctx** out_ctx) {
+    if (!out_ctx) return ZC_ERR_INVALID_ARG;
+    *out_ctx = nullptr;
+    int n = 0;
+    cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0 || device < 0 || device >= n) return ZC_ERR_CUDA;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return ZC_ERR_CUDA;
+    if (prop.major != 10) return ZC_ERR_NOT_LOADED;  // kernels are built for sm_100a only
+    if (cudaSetDevice(device) != cudaSuccess) return ZC_ERR_CUDA;
+    zc_ctx* ctx = new (std::nothrow) zc_ctx();
+    if (!ctx) return ZC_ERR_OOM;
+    ctx->device = device;
+    if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess) {
+        delete ctx;
+        return ZC_ERR_CUDA;
+    }
+    ctx->stream = ctx->own_stream;
+    if (cudaHostAlloc(reinterpret_cast<void**>(&ctx->status_host), 256, cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->status_dev), ctx->status_host, 0) != cudaSuccess) {
+        cudaStreamDestroy(ctx->own_stream);
+        delete ctx;
+        return ZC_ERR_OOM;
+    }
+    memset(ctx->status_host, 0, 256);
+    *out_ctx = ctx;
+    return ZC_OK;
+}
+
+int32_t zc_destroy(zc_ctx* ctx) {
+    if (!ctx) return ZC_ERR_INVALID_ARG;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
+    delete ctx;
+    return ZC_OK;
+}
+
+int32_t zc_set_stream(zc_ctx* ctx, void* cuda_stream) {
+    if (!ctx) return ZC_ERR_INVALID_ARG;
+    ctx->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;
+    return ZC_OK;
+}
+
+void* zc_get_stream(zc_ctx* ctx) { return ctx ? static_cast<void*>(ctx->stream) : nullptr; }
+
+const char* zc_last_error(zc_ctx* ctx) { return ctx ? ctx->err : "null context"; }
+
+const char* zc_status_string(int32_t s) {
+    switch (s) {
+        case ZC_OK: return "ok";
+        case ZC_ERR_UNSUPPORTED_TYPE: return "unsupported quant type";
+        case ZC_ERR_NOT_LOADED: return "kernel not loaded (device is not sm_100)";
+        case ZC_ERR_INVALID_ARG: return "invalid argument";
+        case ZC_ERR_OOM: return "out of memory";
+        case ZC_ERR_CUDA: return "CUDA error";
+        case ZC_ERR_TIMEOUT: return "device-side wait timed out";
+        default: return "unknown status";
+    }
+}
+
+uint64_t zc_launch_count(zc_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int32_t zc_alloc(zc_ctx* ctx, uint64_t bytes, void** out_dptr) {
+    ZC_ENTER(ctx);
+    if (!out_dptr || bytes == 0) return fail(ctx, ZC_ERR_INVALID_ARG, "zc_alloc: bad arguments");
+    cudaError_t e = cudaMalloc(out_dptr, bytes);
+    if (e != cudaSuccess) {
+        *out_dptr = nullptr;
+        return cuda_fail(ctx, e, "zc_alloc");
+    }
+    return ZC_OK;
+}
+
+int32_t zc_free(zc_ctx* ctx, void* dptr) {
+    ZC_ENTER(ctx);
+    if (!dptr) return ZC_OK;
+    cudaError_t e = cudaFree(dptr);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_free");
+}
+
+int32_t zc_upload(zc_ctx* ctx, void* dst, uint64_t dst_offset, const void* host_src, uint64_t bytes) {
+    ZC_ENTER(ctx);
+    if (!dst || (!host_src && bytes)) return fail(ctx, ZC_ERR_INVALID_ARG, "zc_upload: null pointer");
+    if (bytes == 0) return ZC_OK;
+    cudaError_t e = cudaMemcpyAsync(static_cast<uint8_t*>(dst) + dst_offset, host_src, bytes, cudaMemcpyHostToDevice,
+                                    ctx->stream);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_upload");
+}
+
+int32_t zc_download(zc_ctx* ctx, void* host_dst, const void* src, uint64_t src_offset, uint64_t bytes) {
+    ZC_ENTER(ctx);
+    if (!src || (!host_dst && bytes)) return fail(ctx, ZC_ERR_INVALID_ARG, "zc_download: null pointer");
+    if (bytes == 0) return ZC_OK;
+    cudaError_t e = cudaMemcpyAsync(host_dst, static_cast<const uint8_t*>(src) + src_offset, bytes,
+                                    cudaMemcpyDeviceToHost, ctx->stream);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_download");
+}
+
+int32_t zc_memset(zc_ctx* ctx, void* dst, uint64_t dst_offset, int32_t byte_value, uint64_t bytes) {
+    ZC_ENTER(ctx);
+    if (!dst) return fail(ctx, ZC_ERR_INVALID_ARG, "zc_memset: null pointer");
+    if (bytes == 0) return ZC_OK;
+    cudaError_t e = cudaMemsetAsync(static_cast<uint8_t*>(dst) + dst_offset, byte_value, bytes, ctx->stream);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_memset");
+}
+
+int32_t zc_barrier(zc_ctx* ctx) { return ctx ? ZC_OK : ZC_ERR_INVALID_ARG; }
+
+int32_t zc_submit_and_wait(zc_ctx* ctx) {
+    ZC_ENTER(ctx);
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "zc_submit_and_wait");
+    if (ctx->status_host[0] != 0) {
+        const uint32_t code = ctx->status_host[0], where = ctx->status_host[1];
+        ctx->status_host[0] = 0;
+        ctx->status_host[1] = 0;
+        return fail(ctx, ZC_ERR_TIMEOUT, "device-side wait gave up (code %u, site %u)", code, where);
+    }
+    return ZC_OK;
+}
+
+// ---- pre-recorded op sequences ------------------------------------------------------------
+int32_t zc_begin_record(zc_ctx* ctx) {
+    ZC_ENTER(ctx);
+    cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_begin_record");
+}
+
+int32_t zc_end_record(zc_ctx* ctx, void** out_recording) {
+    ZC_ENTER(ctx);
+    if (!out_recording) return fail(ctx, ZC_ERR_INVALID_ARG, "zc_end_record: null output");
+    *out_recording = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "zc_end_record");
+    cudaGraphExec_t exec = nullptr;
+    e = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "zc_end_record (instantiate)");
+    *out_recording = exec;
+    return ZC_OK;
+}
+
+int32_t zc_replay(zc_ctx* ctx, void* recording) {
+    ZC_ENTER(ctx);
+    if (!recording) return fail(ctx, ZC_ERR_INVALID_ARG, "zc_replay: null recording");
+    cudaError_t e = cudaGraphLaunch(static_cast<cudaGraphExec_t>(recording), ctx->stream);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_replay");
+}
+
+int32_t zc_free_recording(zc_ctx* ctx, void* recording) {
+    ZC_ENTER(ctx);
+    if (!recording) return ZC_OK;
+    cudaError_t e = cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(recording));
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_free_recording");
+}
+
+uint32_t zc_block_size(uint32_t type) { return block_size(type); }
+uint32_t zc_bytes_per_block(uint32_t type) { return bytes_per_block(type); }
+uint64_t zc_tensor_size_bytes(uint32_t type, uint64_t n) {
+    const uint64_t bs = block_size(type), bpb = bytes_per_block(type);
+    return ((n + bs - 1) / bs) * bpb;
+}
+uint64_t zc_expert_slice_bytes(uint32_t type, uint32_t rows, uint32_t cols) {
+    const uint64_t bs = block_size(type), bpb = bytes_per_block(type);
+    if (bpb == 0) return (uint64_t)rows * cols * 4;
+    return (uint64_t)rows * (cols / bs) * bpb;
+}
+int32_t zc_dmmv_supported(uint32_t type) { return dmmv_type_ok(type) ? 1 : 0; }
+int32_t zc_moe_dmmv_supported(uint32_t type) { return dmmv_type_ok(type) ? 1 : 0; }
+
+int32_t zc_dmmv(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* x, uint64_t x_size, void* y,
+                uint64_t y_size, uint32_t M, uint32_t K, uint64_t a_offset, uint64_t x_offset, uint64_t y_offset,
+                uint32_t acc_mode) {
+    ZC_ENTER(ctx);
+    ZC_TRY(check_mat(ctx, "zc_dmmv", type, A, a_size, a_offset, (uint64_t)M * row_bytes_of(type, K), M, K));
+    ZC_TRY(check_vec(ctx, "zc_dmmv", "x", x, x_size, x_offset, (uint64_t)K * 4, 16));
+    ZC_TRY(check_vec(ctx, "zc_dmmv", "y", y, y_size, y_offset, (uint64_t)M * 4, 4));
+    DmmvArgs a;
+    a.A = u8(A, a_offset);
+    a.x = f32p(x, x_offset);
+    a.y = f32m(y, y_offset);
+    a.M = M;
+    a.K = K;
+    a.acc_mode = acc_mode;
+    cudaError_t e = launch_dmmv(type, MODE_PLAIN, a, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_dmmv");
+}
+
+int32_t zc_dmmv_fused_gate_up_swiglu(zc_ctx* ctx, uint32_t type, const void* Wg, uint64_t wg_size, const void* Wu,
+                                     uint64_t wu_size, const void* x, uint64_t x_size, void* out, uint64_t out_size,
+                                     uint32_t M, uint32_t K, uint64_t gate_offset, uint64_t up_offset,
+                                     uint64_t x_offset, uint64_t out_offset) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_dmmv_fused_gate_up_swiglu";
+    ZC_TRY(check_mat(ctx, fn, type, Wg, wg_size, gate_offset, (uint64_t)M * row_bytes_of(type, K), M, K));
+    ZC_TRY(check_mat(ctx, fn, type, Wu, wu_size, up_offset, (uint64_t)M * row_bytes_of(type, K), M, K));
+    ZC_TRY(check_vec(ctx, fn, "x", x, x_size, x_offset, (uint64_t)K * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "out", out, out_size, out_offset, (uint64_t)M * 4, 4));
+    DmmvArgs a;
+    a.A = u8(Wg, gate_offset);
+    a.A2 = u8(Wu, up_offset);
+    a.x = f32p(x, x_offset);
+    a.y = f32m(out, out_offset);
+    a.M = M;
+    a.K = K;
+    cudaError_t e = launch_dmmv(type, MODE_GATE_UP_SWIGLU, a, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_dmmv_sigmoid_acc(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* x,
+                            uint64_t x_size, void* y, uint64_t y_size, const void* gate, uint64_t gate_size,
+                            uint32_t M, uint32_t K, uint64_t a_offset, uint64_t x_offset, uint64_t y_offset,
+                            uint32_t gate_index) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_dmmv_sigmoid_acc";
+    ZC_TRY(check_mat(ctx, fn, type, A, a_size, a_offset, (uint64_t)M * row_bytes_of(type, K), M, K));
+    ZC_TRY(check_vec(ctx, fn, "x", x, x_size, x_offset, (uint64_t)K * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "y", y, y_size, y_offset, (uint64_t)M * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "gate", gate, gate_size, (uint64_t)gate_index * 4, 4, 4));
+    DmmvArgs a;
+    a.A = u8(A, a_offset);
+    a.x = f32p(x, x_offset);
+    a.y = f32m(y, y_offset);
+    a.gate = f32p(gate, (uint64_t)gate_index * 4);
+    a.M = M;
+    a.K = K;
+    cudaError_t e = launch_dmmv(type, MODE_SIGMOID_ACC, a, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_dmmv_batch(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* X, uint64_t x_size,
+                      void* Y, uint64_t y_size, uint32_t M, uint32_t K, uint64_t a_offset, uint64_t x_offset,
+                      uint64_t y_offset, uint32_t num_cols) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_dmmv_batch";
+    ZC_TRY(check_mat(ctx, fn, type, A, a_size, a_offset, (uint64_t)M * row_bytes_of(type, K), M, K));
+    if (num_cols == 0) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: num_cols must be non-zero", fn);
+    ZC_TRY(check_vec(ctx, fn, "X", X, x_size, x_offset, (uint64_t)num_cols * K * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "Y", Y, y_size, y_offset, (uint64_t)num_cols * M * 4, 4));
+    cudaError_t e;
+    // Enough columns to amortise tile dequantisation: tensor-core GEMM
+    // (Y[c][M] is D column-major with stride M, X[c][K] is B with stride K).
+    if (num_cols >= 16)
+        e = launch_mul_mm(type, u8(A, a_offset), f32p(X, x_offset), f32m(Y, y_offset), M, num_cols, K, K, M, false,
+                          ctx->stream, &ctx->launches);
+    else
+        e = cudaErrorNotSupported;
+    if (e == cudaErrorNotSupported)
+        e = launch_dmmv_batch(type, u8(A, a_offset), f32p(X, x_offset), f32m(Y, y_offset), M, K, num_cols,
+                              ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_mul_mm(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* B, uint64_t b_size,
+                  void* D, uint64_t d_size, uint32_t M, uint32_t N, uint32_t K, uint32_t stride_b, uint32_t stride_d,
+                  uint64_t a_offset, uint64_t b_offset, uint64_t d_offset, uint32_t act_type) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_mul_mm";
+    if (act_type != ZC_F32 && act_type != ZC_BF16)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: activations must be f32 or bf16", fn);
+    if (N == 0) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: N must be non-zero", fn);
+    ZC_TRY(check_mat(ctx, fn, type, A, a_size, a_offset, (uint64_t)M * row_bytes_of(type, K), M, K));
+    if (stride_b < K || stride_d < M) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: stride smaller than extent", fn);
+    const uint64_t esz = act_type == ZC_BF16 ? 2 : 4;
+    ZC_TRY(check_vec(ctx, fn, "B", B, b_size, b_offset * esz, ((uint64_t)(N - 1) * stride_b + K) * esz, esz));
+    ZC_TRY(check_vec(ctx, fn, "D", D, d_size, d_offset * 4, ((uint64_t)(N - 1) * stride_d + M) * 4, 4));
+    const void* Bp = static_cast<const uint8_t*>(B) + b_offset * esz;
+    cudaError_t e = launch_mul_mm(type, u8(A, a_offset), Bp, f32m(D, d_offset * 4), M, N, K, stride_b, stride_d,
+                                  act_type == ZC_BF16, ctx->stream, &ctx->launches);
+    if (e == cudaErrorNotSupported)
+        e = launch_mul_mm_simple(type, u8(A, a_offset), Bp, f32m(D, d_offset * 4), M, N, K, stride_b, stride_d,
+                                 act_type == ZC_BF16, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+// Shared checks of the per-slot MoE calls.
+static int32_t check_moe(zc_ctx* ctx, const char* fn, uint32_t type, const void* A, uint64_t a_size,
+                         const void* x, uint64_t x_size, const void* routing, uint64_t routing_size, uint32_t M,
+                         uint32_t K, uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride,
+                         uint64_t x_offset, uint32_t routing_words) {
+    // Expert ids live on the device, so only the first expert's extent can be
+    // bounds-checked here; the stride must cover one expert.
+    ZC_TRY(check_mat(ctx, fn, type, A, a_size, 0, (uint64_t)M * row_bytes_of(type, K), M, K));
+    if (n_used == 0) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: n_used must be non-zero", fn);
+    if (expert_stride < (uint64_t)M * row_bytes_of(type, K))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: expert_stride smaller than one expert", fn);
+    if (x_expert_stride % 4 != 0)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: x_expert_stride must be a multiple of 4 elements", fn);
+    ZC_TRY(check_vec(ctx, fn, "x", x, x_size, x_offset, ((uint64_t)(n_used - 1) * x_expert_stride + K) * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0, (uint64_t)routing_words * 4, 4));
+    return ZC_OK;
+}
+
+int32_t zc_moe_dmmv(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* x, uint64_t x_size,
+                    void* y, uint64_t y_size, const void* routing, uint64_t routing_size, uint32_t M, uint32_t K,
+                    uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride, uint64_t x_offset,
+                    uint64_t y_offset) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_dmmv";
+    ZC_TRY(check_moe(ctx, fn, type, A, a_size, x, x_size, routing, routing_size, M, K, expert_stride, n_used,
+                     x_expert_stride, x_offset, n_used));
+    ZC_TRY(check_vec(ctx, fn, "y", y, y_size, y_offset, (uint64_t)n_used * M * 4, 4));
+    DmmvArgs a;
+    a.A = u8(A, 0);
+    a.x = f32p(x, x_offset);
+    a.y = f32m(y, y_offset);
+    a.routing = static_cast<const uint32_t*>(routing);
+    a.M = M;
+    a.K = K;
+    a.expert_stride = expert_stride;
+    a.n_used = n_used;
+    a.x_expert_stride = x_expert_stride;
+    cudaError_t e = launch_dmmv(type, MODE_MOE, a, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_moe_fused_gate_up(zc_ctx* ctx, uint32_t type, const void* Wg, uint64_t wg_size, const void* Wu,
+                             uint64_t wu_size, const void* x, uint64_t x_size, void* y_gate, uint64_t yg_size,
+                             void* y_up, uint64_t yu_size, const void* routing, uint64_t routing_size, uint32_t M,
+                             uint32_t K, uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride,
+                             uint64_t x_offset, uint64_t y_offset) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_fused_gate_up";
+    ZC_TRY(check_moe(ctx, fn, type, Wg, wg_size, x, x_size, routing, routing_size, M, K, expert_stride, n_used,
+                     x_expert_stride, x_offset, n_used));
+    ZC_TRY(check_mat(ctx, fn, type, Wu, wu_size, 0, (uint64_t)M * row_bytes_of(type, K), M, K));
+    ZC_TRY(check_vec(ctx, fn, "y_gate", y_gate, yg_size, y_offset, (uint64_t)n_used * M * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "y_up", y_up, yu_size, y_offset, (uint64_t)n_used * M * 4, 4));
+    DmmvArgs a;
+    a.A = u8(Wg, 0);
+    a.A2 = u8(Wu, 0);
+    a.x = f32p(x, x_offset);
+    a.y = f32m(y_gate, y_offset);
+    a.y2 = f32m(y_up, y_offset);
+    a.routing = static_cast<const uint32_t*>(routing);
+    a.M = M;
+    a.K = K;
+    a.expert_stride = expert_stride;
+    a.n_used = n_used;
+    a.x_expert_stride = x_expert_stride;
+    cudaError_t e = launch_dmmv(type, MODE_MOE_GATE_UP, a, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* x,
+                              uint64_t x_size, void* y, uint64_t y_size, const void* routing, uint64_t routing_size,
+                              uint32_t M, uint32_t K, uint64_t expert_stride, uint32_t n_used,
+                              uint32_t x_expert_stride, uint64_t x_offset, uint64_t y_offset) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_fused_down_acc";
+    ZC_TRY(check_moe(ctx, fn, type, A, a_size, x, x_size, routing, routing_size, M, K, expert_stride, n_used,
+                     x_expert_stride, x_offset, 2 * n_used));
+    ZC_TRY(check_vec(ctx, fn, "y", y, y_size, y_offset, (uint64_t)M * 4, 4));
+    DmmvArgs a;
+    a.A = u8(A, 0);
+    a.x = f32p(x, x_offset);
+    a.y = f32m(y, y_offset);
+    a.routing = static_cast<const uint32_t*>(routing);
+    a.M = M;
+    a.K = K;
+    a.expert_stride = expert_stride;
+    a.n_used = n_used;
+    a.x_expert_stride = x_expert_stride;
+    cudaError_t e = launch_dmmv(type, MODE_MOE_DOWN_ACC, a, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_moe_dmmv_batched(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* X,
+                            uint64_t x_size, void* Y, uint64_t y_size, const void* routing, uint64_t routing_size,
+                            uint32_t M, uint32_t K, uint64_t expert_stride, uint32_t n_experts,
+                            uint32_t n_experts_used, uint32_t n_tokens, uint32_t x_token_stride,
+                            uint32_t y_token_stride) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_dmmv_batched";
+    if (n_tokens == 0 || n_experts_used == 0 || n_experts == 0)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: zero token, expert or slot count", fn);
+    ZC_TRY(check_mat(ctx, fn, type, A, a_size, 0, (uint64_t)n_experts * expert_stride, M, K));
+    if (expert_stride < (uint64_t)M * row_bytes_of(type, K))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: expert_stride smaller than one expert", fn);
+    if (x_token_stride < K || x_token_stride % 4 != 0 || y_token_stride < (uint64_t)n_experts_used * M)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: token stride too small or x stride not a multiple of 4", fn);
+    ZC_TRY(check_vec(ctx, fn, "X", X, x_size, 0, ((uint64_t)(n_tokens - 1) * x_token_stride + K) * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "Y", Y, y_size, 0,
+                     ((uint64_t)(n_tokens - 1) * y_token_stride + (uint64_t)n_experts_used * M) * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0, (uint64_t)n_tokens * n_experts_used * 4, 4));
+    cudaError_t e = launch_moe_dmmv_batched(type, u8(A, 0), f32p(X, 0), f32m(Y, 0),
+                                            static_cast<const uint32_t*>(routing), M, K, expert_stride,
+                                            n_experts_used, n_tokens, x_token_stride, y_token_stride, ctx->stream,
+                                            &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_softmax_topk(zc_ctx* ctx, const void* logits, uint64_t logits_size, const void* bias, void* out,
+                        uint64_t out_size, uint32_t n_experts, uint32_t k, uint32_t rule, uint32_t n_tokens,
+                        uint32_t logits_stride, uint32_t out_stride) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_softmax_topk";
+    if (n_experts == 0 || k == 0 || k > n_experts || n_tokens == 0 || rule > 1)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: need 0 < k <= n_experts, n_tokens > 0, rule in {0,1}", fn);
+    if (logits_stride < n_experts || out_stride < 2 * k)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: stride smaller than row", fn);
+    if ((uint64_t)n_experts * 4 > 200 * 1024) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: n_experts too large", fn);
+    ZC_TRY(check_vec(ctx, fn, "logits", logits, logits_size, 0,
+                     ((uint64_t)(n_tokens - 1) * logits_stride + n_experts) * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "out", out, out_size, 0, ((uint64_t)(n_tokens - 1) * out_stride + 2 * k) * 4, 4));
+    cudaError_t e = launch_softmax_topk(static_cast<const float*>(logits), static_cast<const float*>(bias),
+                                        static_cast<uint32_t*>(out), n_experts, k, rule, n_tokens, logits_stride,
+                                        out_stride, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_moe_weighted_acc(zc_ctx* ctx, void* a, uint64_t a_size, const void* b, uint64_t b_size,
+                            const void* routing, uint64_t routing_size, uint32_t n, uint32_t n_used,
+                            uint32_t src_stride) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_weighted_acc";
+    if (n == 0 || n_used == 0) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: n and n_used must be non-zero", fn);
+    ZC_TRY(check_vec(ctx, fn, "a", a, a_size, 0, (uint64_t)n * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "b", b, b_size, 0, ((uint64_t)(n_used - 1) * src_stride + n) * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0, (uint64_t)2 * n_used * 4, 4));
+    cudaError_t e = launch_moe_weighted_acc(static_cast<float*>(a), static_cast<const float*>(b),
+                                            static_cast<const uint32_t*>(routing), n, n_used, src_stride,
+                                            ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+static int32_t swiglu_common(zc_ctx* ctx, const void* gate, const void* up, void* y, uint32_t n, bool oai) {
+    ZC_ENTER(ctx);
+    if (!gate || !up || !y || n == 0) return fail(ctx, ZC_ERR_INVALID_ARG, "zc_swiglu: bad arguments");
+    cudaError_t e = launch_swiglu(static_cast<const float*>(gate), static_cast<const float*>(up),
+                                  static_cast<float*>(y), n, oai, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_swiglu");
+}
+int32_t zc_swiglu(zc_ctx* ctx, const void* gate, const void* up, void* y, uint32_t n) {
+    return swiglu_common(ctx, gate, up, y, n, false);
+}
+int32_t zc_swiglu_oai(zc_ctx* ctx, const void* gate, const void* up, void* y, uint32_t n) {
+    return swiglu_common(ctx, gate, up, y, n, true);
+}
+
+int32_t zc_count_experts(zc_ctx* ctx, const void* routing, uint64_t routing_size, void* counts,
+                         uint64_t counts_size, uint32_t n_tokens, uint32_t n_layers, uint32_t layer,
+                         uint32_t n_experts_used, uint32_t n_experts, uint64_t d_offset_bytes) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_count_experts";
+    if (n_tokens == 0 || n_experts == 0 || n_experts_used == 0 || n_layers == 0 || layer >= n_layers)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: zero count or layer out of range", fn);
+    const uint32_t slot = 2 * n_experts_used;
+    ZC_TRY(check_vec(ctx, fn, "counts", counts, counts_size, d_offset_bytes, (uint64_t)n_experts * 4, 4));
+    const uint64_t need = ((uint64_t)(n_tokens - 1) * slot * n_layers + (uint64_t)layer * slot + n_experts_used) * 4;
+    ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0, need, 4));
+    cudaError_t e = launch_count_experts(
+        static_cast<const uint32_t*>(routing),
+        reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(counts) + d_offset_bytes), n_experts, n_experts_used,
+        n_tokens, 1, slot * n_layers, layer * slot, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_moe_route_pack(zc_ctx* ctx, const void* routing, uint64_t routing_size, void* counts,
+                          uint64_t counts_size, void* ids, uint64_t ids_size, uint32_t n_tokens, uint32_t n_experts,
+                          uint32_t k, uint32_t routing_stride, uint32_t ids_stride) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_route_pack";
+    if (n_tokens == 0 || n_experts == 0 || k == 0 || routing_stride < k)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: zero count or routing_stride < k", fn);
+    if ((uint64_t)ids_stride < (uint64_t)n_tokens)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: ids_stride must hold one route per token", fn);
+    ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0,
+                     ((uint64_t)(n_tokens - 1) * routing_stride + k) * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "counts", counts, counts_size, 0, (uint64_t)n_experts * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "ids", ids, ids_size, 0, (uint64_t)n_experts * ids_stride * 4, 4));
+    cudaError_t e = launch_moe_route_pack(static_cast<const uint32_t*>(routing), static_cast<uint32_t*>(counts),
+                                          static_cast<uint32_t*>(ids), n_tokens, n_experts, k, routing_stride,
+                                          ids_stride, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_moe_route_scatter(zc_ctx* ctx, const void* routing, uint64_t routing_size, const void* src,
+                             uint64_t src_size, void* dst, uint64_t dst_size, uint32_t n_tokens,
+                             uint32_t hidden_dim, uint32_t k, uint32_t routing_stride) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_route_scatter";
+    if (n_tokens == 0 || hidden_dim == 0 || k == 0 || routing_stride < 2 * k)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: zero count or routing_stride < 2k", fn);
+    ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0,
+                     ((uint64_t)(n_tokens - 1) * routing_stride + 2 * k) * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "src", src, src_size, 0, (uint64_t)n_tokens * k * hidden_dim * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "dst", dst, dst_size, 0, (uint64_t)n_tokens * hidden_dim * 4, 4));
+    cudaError_t e = launch_moe_route_scatter(static_cast<const uint32_t*>(routing), static_cast<const float*>(src),
+                                             static_cast<float*>(dst), n_tokens, hidden_dim, k, routing_stride,
+                                             ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_dequant_rows(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, void* out, uint64_t out_size,
+                        uint64_t first_row, uint32_t n_rows, uint32_t K, uint64_t a_offset) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_dequant_rows";
+    if (!dmmv_type_ok(type)) return fail(ctx, ZC_ERR_UNSUPPORTED_TYPE, "%s: unsupported quant type %u", fn, type);
+    if (n_rows == 0 || K == 0 || K % block_size(type) != 0)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: n_rows and K must be non-zero, K a multiple of the block size", fn);
+    ZC_TRY(check_vec(ctx, fn, "A", A, a_size, a_offset, (first_row + n_rows) * row_bytes_of(type, K), 1));
+    ZC_TRY(check_vec(ctx, fn, "out", out, out_size, 0, (uint64_t)n_rows * K * 4, 4));
+    cudaError_t e = launch_dequant_rows(type, u8(A, a_offset), static_cast<float*>(out), first_row, n_rows, K,
+                                        ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+}  // extern "C"

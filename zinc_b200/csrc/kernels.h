@@ -1,0 +1,80 @@
+// Internal launch interface between the C ABI (api.cu) and the kernel files.
+// All pointers are device pointers already offset and validated by the caller.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace zc {
+
+// Epilogue / addressing modes of the decode matvec kernel family.
+enum DmmvMode : int {
+    MODE_PLAIN = 0,          // y (+)= W x
+    MODE_GATE_UP_SWIGLU = 1, // out = silu(Wg x) * (Wu x)
+    MODE_SIGMOID_ACC = 2,    // y += sigmoid(gate) * (W x)
+    MODE_MOE = 3,            // per slot: Y[s] = W[routing[s]] X[s]
+    MODE_MOE_GATE_UP = 4,    // per slot: Yg[s], Yu[s]
+    MODE_MOE_DOWN_ACC = 5,   // y += sum_s w_s * W[id_s] X[s]
+    MODE_BATCH = 6,          // per column c: Y[c] = W X[c]   (n_used = columns, x_expert_stride = K)
+    MODE_MOE_BATCHED = 7,    // per (token t, slot s): Y[t][s] = W[routing[t*n_used+s]] X[t]
+};
+
+struct DmmvArgs {
+    const uint8_t* A = nullptr;   // weights (gate weights for the gate/up modes)
+    const uint8_t* A2 = nullptr;  // up weights for the gate/up modes
+    const float* x = nullptr;
+    float* y = nullptr;
+    float* y2 = nullptr;          // second output (MoE gate/up)
+    const float* gate = nullptr;  // sigmoid gate scalar
+    const uint32_t* routing = nullptr;
+    uint32_t M = 0, K = 0;
+    uint32_t acc_mode = 0;
+    uint32_t n_used = 1;
+    uint32_t x_expert_stride = 0;
+    uint64_t expert_stride = 0;
+    uint32_t n_tokens = 1;        // MODE_MOE_BATCHED
+    uint32_t x_token_stride = 0;  // MODE_MOE_BATCHED, elements
+    uint32_t y_token_stride = 0;  // MODE_MOE_BATCHED, elements
+};
+
+// Returns cudaSuccess or the launch error; *launches is incremented per kernel.
+cudaError_t launch_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
+
+// Y[c][M] = W X[c][K], X/Y f32 row per column.
+cudaError_t launch_dmmv_batch(uint32_t type, const uint8_t* A, const float* X, float* Y, uint32_t M, uint32_t K,
+                              uint32_t num_cols, cudaStream_t s, uint64_t* launches);
+
+// Cross-token MoE: Y[t][s][M] = W[routing[t*k+s]] X[t].
+cudaError_t launch_moe_dmmv_batched(uint32_t type, const uint8_t* A, const float* X, float* Y,
+                                    const uint32_t* routing, uint32_t M, uint32_t K, uint64_t expert_stride,
+                                    uint32_t n_experts_used, uint32_t n_tokens, uint32_t x_token_stride,
+                                    uint32_t y_token_stride, cudaStream_t s, uint64_t* launches);
+
+cudaError_t launch_dequant_rows(uint32_t type, const uint8_t* A, float* out, uint64_t first_row, uint32_t n_rows,
+                                uint32_t K, cudaStream_t s, uint64_t* launches);
+
+cudaError_t launch_softmax_topk(const float* logits, const float* bias, uint32_t* out, uint32_t n_experts,
+                                uint32_t k, uint32_t rule, uint32_t n_tokens, uint32_t logits_stride,
+                                uint32_t out_stride, cudaStream_t s, uint64_t* launches);
+cudaError_t launch_moe_weighted_acc(float* a, const float* b, const uint32_t* routing, uint32_t n, uint32_t n_used,
+                                    uint32_t src_stride, cudaStream_t s, uint64_t* launches);
+cudaError_t launch_swiglu(const float* gate, const float* up, float* y, uint32_t n, bool oai, cudaStream_t s,
+                          uint64_t* launches);
+cudaError_t launch_count_experts(const uint32_t* a, uint32_t* counts, uint32_t n_experts, uint32_t ne00,
+                                 uint32_t ne01, uint32_t nb00, uint32_t nb01, uint32_t a_offset, cudaStream_t s,
+                                 uint64_t* launches);
+cudaError_t launch_moe_route_pack(const uint32_t* routing, uint32_t* counts, uint32_t* ids, uint32_t n_tokens,
+                                  uint32_t n_experts, uint32_t k, uint32_t routing_stride, uint32_t ids_stride,
+                                  cudaStream_t s, uint64_t* launches);
+cudaError_t launch_moe_route_scatter(const uint32_t* routing, const float* src, float* dst, uint32_t n_tokens,
+                                     uint32_t hidden, uint32_t k, uint32_t routing_stride, cudaStream_t s,
+                                     uint64_t* launches);
+
+// Tensor-core dequant-GEMM: D[col][row] = sum_k A[row][k] B[col][k].
+// act_bf16: B holds bf16 (else f32). Returns cudaErrorNotSupported for types
+// without a tile dequantiser.
+cudaError_t launch_mul_mm(uint32_t type, const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N,
+                          uint32_t K, uint32_t stride_b, uint32_t stride_d, bool act_bf16, cudaStream_t s,
+                          uint64_t* launches);
+
+}  // namespace zc

@@ -1,0 +1,310 @@
+// Routing, activation, combine and parity kernels around the expert matmuls.
+#include <float.h>
+
+#include "dequant.cuh"
+#include "kernels.h"
+
+namespace zc {
+
+namespace {
+
+// ---- dequant rows -------------------------------------------------------------
+template <uint32_t TYPE>
+__global__ void dequant_rows_kernel(const uint8_t* __restrict__ A, float* __restrict__ out, uint64_t first_row,
+                                    uint32_t K, uint64_t total) {
+    const uint64_t row_bytes = (uint64_t)(K / block_size(TYPE)) * bytes_per_block(TYPE);
+    for (uint64_t idx = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t r = idx / K;
+        const uint32_t i = (uint32_t)(idx - r * K);
+        out[idx] = dequant_elem<TYPE>(A + (first_row + r) * row_bytes, i);
+    }
+}
+
+// ---- top-k routing ---------------------------------------------------------------
+// One CTA per token. Values live in dynamic shared memory; k rounds of a
+// block-wide arg-max with ties to the lowest index, as the strict '>' ascending
+// scans of the reference do (src/compute/forward.zig:516-529, 544-556;
+// src/shaders/softmax_topk.comp:49-81).
+struct ValIdx {
+    float v;
+    uint32_t i;
+};
+__device__ __forceinline__ ValIdx better(ValIdx a, ValIdx b) {
+    return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
+}
+
+constexpr int kTopkThreads = 256;
+
+__global__ void __launch_bounds__(kTopkThreads) softmax_topk_kernel(
+    const float* __restrict__ logits, const float* __restrict__ bias, uint32_t* __restrict__ out,
+    uint32_t n, uint32_t k, uint32_t rule, uint32_t logits_stride, uint32_t out_stride) {
+    extern __shared__ float vals[];  // n values the selection runs on
+    __shared__ ValIdx red[kTopkThreads / 32];
+    __shared__ float red_f[kTopkThreads / 32];
+    __shared__ float bcast;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* lg = logits + (size_t)blockIdx.x * logits_stride;
+    uint32_t* o = out + (size_t)blockIdx.x * out_stride;
+    const float floor_v = rule == 0u ? -1.0f : -INFINITY;
+
+    float lmax = -INFINITY;
+    for (uint32_t i = tid; i < n; i += kTopkThreads) {
+        const float v = lg[i] + (bias ? bias[i] : 0.0f);
+        vals[i] = v;
+        lmax = fmaxf(lmax, v);
+    }
+    if (rule == 0u) {
+        // softmax over all experts first
+        for (int o2 = 16; o2 > 0; o2 >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xFFFFFFFFu, lmax, o2));
+        if (lane == 0) red_f[warp] = lmax;
+        __syncthreads();
+        if (tid == 0) {
+            float m = red_f[0];
+            for (int w = 1; w < kTopkThreads / 32; ++w) m = fmaxf(m, red_f[w]);
+            bcast = m;
+        }
+        __syncthreads();
+        const float mx = bcast;
+        float lsum = 0.f;
+        for (uint32_t i = tid; i < n; i += kTopkThreads) {
+            const float p = expf(vals[i] - mx);
+            vals[i] = p;
+            lsum += p;
+        }
+        lsum = warp_sum(lsum);
+        __syncthreads();
+        if (lane == 0) red_f[warp] = lsum;
+        __syncthreads();
+        if (tid == 0) {
+            float s = 0.f;
+            for (int w = 0; w < kTopkThreads / 32; ++w) s += red_f[w];
+            bcast = s;
+        }
+        __syncthreads();
+        const float sum = bcast;
+        if (sum > 0.f)
+            for (uint32_t i = tid; i < n; i += kTopkThreads) vals[i] = vals[i] / sum;
+    }
+    __syncthreads();
+
+    for (uint32_t ki = 0; ki < k; ++ki) {
+        ValIdx best{floor_v, 0u};
+        for (uint32_t i = tid; i < n; i += kTopkThreads) {
+            const float v = vals[i];
+            if (v > best.v) best = ValIdx{v, i};
+        }
+        for (int o2 = 16; o2 > 0; o2 >>= 1) {
+            ValIdx other{__shfl_xor_sync(0xFFFFFFFFu, best.v, o2), __shfl_xor_sync(0xFFFFFFFFu, best.i, o2)};
+            best = better(best, other);
+        }
+        if (lane == 0) red[warp] = best;
+        __syncthreads();
+        if (tid == 0) {
+            ValIdx b = red[0];
+            for (int w = 1; w < kTopkThreads / 32; ++w) b = better(b, red[w]);
+            // nothing above the floor: the reference's scans leave index 0
+            if (!(b.v > floor_v)) b = ValIdx{rule == 0u ? floor_v : vals[0], 0u};
+            o[ki] = b.i;
+            o[k + ki] = __float_as_uint(b.v);
+            vals[b.i] = rule == 0u ? -2.0f : -INFINITY;  // never selected again
+        }
+        __syncthreads();
+    }
+
+    if (tid == 0) {
+        if (rule == 0u) {
+            float ws = 0.f;
+            for (uint32_t i = 0; i < k; ++i) ws += __uint_as_float(o[k + i]);
+            if (ws > 0.f)
+                for (uint32_t i = 0; i < k; ++i) o[k + i] = __float_as_uint(__uint_as_float(o[k + i]) / ws);
+        } else {
+            float mx = -INFINITY;
+            for (uint32_t i = 0; i < k; ++i) mx = fmaxf(mx, __uint_as_float(o[k + i]));
+            float sum = 0.f;
+            for (uint32_t i = 0; i < k; ++i) {
+                const float w = expf(__uint_as_float(o[k + i]) - mx);
+                o[k + i] = __float_as_uint(w);
+                sum += w;
+            }
+            if (sum > 0.f)
+                for (uint32_t i = 0; i < k; ++i) o[k + i] = __float_as_uint(__uint_as_float(o[k + i]) / sum);
+        }
+    }
+}
+
+// ---- combine / activation ------------------------------------------------------------
+// src/shaders/moe_weighted_acc.comp:23-33
+__global__ void moe_weighted_acc_kernel(float* __restrict__ a, const float* __restrict__ b,
+                                        const uint32_t* __restrict__ routing, uint32_t n, uint32_t n_used,
+                                        uint32_t src_stride) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float sum = 0.f;
+    for (uint32_t j = 0; j < n_used; ++j)
+        sum = fmaf(__uint_as_float(__ldg(routing + n_used + j)), b[(size_t)j * src_stride + i], sum);
+    a[i] += sum;
+}
+
+// src/shaders/swiglu.comp:25-33, src/shaders/swiglu_oai.comp:24-34
+template <bool OAI>
+__global__ void swiglu_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ y,
+                              uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (OAI) {
+        const float g = fminf(gate[i], 7.0f);
+        const float u = fmaxf(-7.0f, fminf(up[i], 7.0f));
+        y[i] = (g / (1.0f + expf(1.702f * (-g)))) * (u + 1.0f);
+    } else {
+        const float g = gate[i];
+        y[i] = (g / (1.0f + expf(-g))) * up[i];
+    }
+}
+
+// src/shaders/count_experts.comp:58-83: one CTA per expert.
+__global__ void __launch_bounds__(256) count_experts_kernel(const uint32_t* __restrict__ a,
+                                                            uint32_t* __restrict__ counts, uint32_t ne00,
+                                                            uint32_t ne01, uint32_t nb00, uint32_t nb01,
+                                                            uint32_t a_offset) {
+    __shared__ uint32_t red[8];
+    const uint32_t e = blockIdx.x;
+    const uint32_t total = ne00 * ne01;
+    uint32_t c = 0;
+    for (uint32_t idx = threadIdx.x; idx < total; idx += 256) {
+        const uint32_t i01 = idx / ne00, i00 = idx - i01 * ne00;
+        c += __ldg(a + a_offset + (size_t)i01 * nb01 + (size_t)i00 * nb00) == e;
+    }
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = c;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t s = 0;
+        for (int w = 0; w < 8; ++w) s += red[w];
+        counts[e] = s;
+    }
+}
+
+// src/shaders/metal/moe_route_pack.metal:13-36. One warp per expert; the route
+// list keeps token order through a ballot prefix.
+__global__ void moe_route_pack_kernel(const uint32_t* __restrict__ routing, uint32_t* __restrict__ counts,
+                                      uint32_t* __restrict__ ids, uint32_t n_tokens, uint32_t n_experts, uint32_t k,
+                                      uint32_t routing_stride, uint32_t ids_stride) {
+    const uint32_t e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (e >= n_experts) return;
+    const uint32_t total = n_tokens * k;
+    uint32_t n = 0;
+    for (uint32_t base = 0; base < total; base += 32) {
+        const uint32_t idx = base + lane;
+        bool hit = false;
+        if (idx < total) {
+            const uint32_t t = idx / k, s = idx - t * k;
+            hit = __ldg(routing + (size_t)t * routing_stride + s) == e;
+        }
+        const uint32_t mask = __ballot_sync(0xFFFFFFFFu, hit);
+        if (hit) ids[(size_t)e * ids_stride + n + __popc(mask & ((1u << lane) - 1u))] = idx;
+        n += __popc(mask);
+    }
+    if (lane == 0) counts[e] = n;
+}
+
+// src/shaders/metal/moe_route_scatter.metal:20-96
+__global__ void moe_route_scatter_kernel(const uint32_t* __restrict__ routing, const float* __restrict__ src,
+                                         float* __restrict__ dst, uint32_t n_tokens, uint32_t hidden, uint32_t k,
+                                         uint32_t routing_stride) {
+    const uint64_t id = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (id >= (uint64_t)n_tokens * hidden) return;
+    const uint32_t t = (uint32_t)(id / hidden), d = (uint32_t)(id - (uint64_t)t * hidden);
+    const uint32_t* row = routing + (size_t)t * routing_stride;
+    float sum = 0.f;
+    for (uint32_t s = 0; s < k; ++s)
+        sum = fmaf(__uint_as_float(__ldg(row + k + s)), src[((size_t)t * k + s) * hidden + d], sum);
+    dst[id] += sum;
+}
+
+}  // namespace
+
+cudaError_t launch_dequant_rows(uint32_t type, const uint8_t* A, float* out, uint64_t first_row, uint32_t n_rows,
+                                uint32_t K, cudaStream_t s, uint64_t* launches) {
+    const uint64_t total = (uint64_t)n_rows * K;
+    if (total == 0) return cudaSuccess;
+    const int threads = 256;
+    const uint32_t blocks = (uint32_t)((total + threads - 1) / threads < 148u * 64u ? (total + threads - 1) / threads
+                                                                                    : 148u * 64u);
+#define ZC_DQ(T) \
+    case T: dequant_rows_kernel<T><<<blocks, threads, 0, s>>>(A, out, first_row, K, total); break;
+    switch (type) {
+        ZC_DQ(T_F32) ZC_DQ(T_F16) ZC_DQ(T_Q8_0) ZC_DQ(T_Q4_K) ZC_DQ(T_Q5_K) ZC_DQ(T_Q6_K)
+        ZC_DQ(T_Q5_0) ZC_DQ(T_Q5_1) ZC_DQ(T_MXFP4)
+        default: return cudaErrorNotSupported;
+    }
+#undef ZC_DQ
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_softmax_topk(const float* logits, const float* bias, uint32_t* out, uint32_t n_experts,
+                                uint32_t k, uint32_t rule, uint32_t n_tokens, uint32_t logits_stride,
+                                uint32_t out_stride, cudaStream_t s, uint64_t* launches) {
+    if (n_tokens == 0) return cudaSuccess;
+    const size_t smem = (size_t)n_experts * sizeof(float);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(softmax_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return e;
+    }
+    softmax_topk_kernel<<<n_tokens, kTopkThreads, smem, s>>>(logits, bias, out, n_experts, k, rule, logits_stride,
+                                                             out_stride);
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_weighted_acc(float* a, const float* b, const uint32_t* routing, uint32_t n, uint32_t n_used,
+                                    uint32_t src_stride, cudaStream_t s, uint64_t* launches) {
+    if (n == 0) return cudaSuccess;
+    moe_weighted_acc_kernel<<<(n + 255) / 256, 256, 0, s>>>(a, b, routing, n, n_used, src_stride);
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu(const float* gate, const float* up, float* y, uint32_t n, bool oai, cudaStream_t s,
+                          uint64_t* launches) {
+    if (n == 0) return cudaSuccess;
+    if (oai) swiglu_kernel<true><<<(n + 255) / 256, 256, 0, s>>>(gate, up, y, n);
+    else swiglu_kernel<false><<<(n + 255) / 256, 256, 0, s>>>(gate, up, y, n);
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_count_experts(const uint32_t* a, uint32_t* counts, uint32_t n_experts, uint32_t ne00,
+                                 uint32_t ne01, uint32_t nb00, uint32_t nb01, uint32_t a_offset, cudaStream_t s,
+                                 uint64_t* launches) {
+    count_experts_kernel<<<n_experts, 256, 0, s>>>(a, counts, ne00, ne01, nb00, nb01, a_offset);
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_route_pack(const uint32_t* routing, uint32_t* counts, uint32_t* ids, uint32_t n_tokens,
+                                  uint32_t n_experts, uint32_t k, uint32_t routing_stride, uint32_t ids_stride,
+                                  cudaStream_t s, uint64_t* launches) {
+    const int warps = 4;
+    moe_route_pack_kernel<<<(n_experts + warps - 1) / warps, warps * 32, 0, s>>>(routing, counts, ids, n_tokens,
+                                                                                n_experts, k, routing_stride,
+                                                                                ids_stride);
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_route_scatter(const uint32_t* routing, const float* src, float* dst, uint32_t n_tokens,
+                                     uint32_t hidden, uint32_t k, uint32_t routing_stride, cudaStream_t s,
+                                     uint64_t* launches) {
+    const uint64_t total = (uint64_t)n_tokens * hidden;
+    if (total == 0) return cudaSuccess;
+    moe_route_scatter_kernel<<<(uint32_t)((total + 255) / 256), 256, 0, s>>>(routing, src, dst, n_tokens, hidden, k,
+                                                                             routing_stride);
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+}  // namespace zc

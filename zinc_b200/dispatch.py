@@ -1,0 +1,326 @@
+"""Host-side mirror of the reference's DMMV dispatch layer over the C ABI.
+
+`DmmvDispatch` keeps the method names, argument order, units and error
+behaviour of `DmmvDispatch` in the reference (src/compute/dmmv.zig:161-1094)
+and of the engine-side wrappers that call it (src/compute/forward.zig:
+8147-8540, 4135-4210), so a call site of the reference translates line by
+line. Where the reference binds buffers through a descriptor set, the methods
+here take `Buffer` objects (device pointer + byte size) in binding order.
+
+Everything computes on the GPU through libzinc_b200.so; nothing here touches
+tensor data on the host.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Any, Optional
+
+from . import _lib
+from ._lib import (BF16, F16, F32, MXFP4, Q4_K, Q5_0, Q5_1, Q5_K, Q6_K, Q8_0,  # noqa: F401 (re-exported)
+                   ROUTE_SOFTMAX_ALL_RENORM, ROUTE_TOPK_THEN_SOFTMAX)
+
+
+class ZincError(RuntimeError):
+    status = -1
+
+
+class UnsupportedQuantType(ZincError):  # error.UnsupportedQuantType
+    status = _lib.ERR_UNSUPPORTED_TYPE
+
+
+class PipelineNotLoaded(ZincError):  # error.PipelineNotLoaded
+    status = _lib.ERR_NOT_LOADED
+
+
+class InvalidArgument(ZincError):  # error.InvalidArgument
+    status = _lib.ERR_INVALID_ARG
+
+
+class OutOfMemory(ZincError):
+    status = _lib.ERR_OOM
+
+
+class CudaError(ZincError):
+    status = _lib.ERR_CUDA
+
+
+class DeviceTimeout(ZincError):
+    status = _lib.ERR_TIMEOUT
+
+
+_ERRORS = {c.status: c for c in (UnsupportedQuantType, PipelineNotLoaded, InvalidArgument, OutOfMemory,
+                                 CudaError, DeviceTimeout)}
+
+
+@dataclass
+class Buffer:
+    """A borrowed device allocation: pointer + byte size (the reference's Buffer.handle/size)."""
+    ptr: int
+    size: int
+    owner: Any = None  # keeps the backing object (torch tensor / context allocation) alive
+
+    @staticmethod
+    def from_torch(t) -> "Buffer":
+        if not t.is_cuda:
+            raise InvalidArgument("Buffer.from_torch needs a CUDA tensor")
+        if not t.is_contiguous():
+            raise InvalidArgument("Buffer.from_torch needs a contiguous tensor")
+        return Buffer(t.data_ptr(), t.numel() * t.element_size(), t)
+
+
+def _buf(b) -> Buffer:
+    if isinstance(b, Buffer):
+        return b
+    if hasattr(b, "data_ptr"):
+        return Buffer.from_torch(b)
+    raise InvalidArgument(f"expected a Buffer or CUDA tensor, got {type(b).__name__}")
+
+
+class Context:
+    """One device + one stream: the unit the reference calls an engine's command buffer."""
+
+    def __init__(self, device: int = 0, stream: Optional[int] = None):
+        self._lib = _lib.lib()
+        h = C.c_void_p()
+        rc = self._lib.zc_init(device, C.byref(h))
+        if rc != _lib.OK:
+            raise _ERRORS.get(rc, ZincError)(
+                f"zc_init(device={device}) failed: {self._lib.zc_status_string(rc).decode()}")
+        self._h = h
+        self.device = device
+        if stream is not None:
+            self.set_stream(stream)
+
+    # -- plumbing --------------------------------------------------------------------------
+    def call(self, name: str, *args) -> None:
+        rc = getattr(self._lib, name)(self._h, *args)
+        if rc != _lib.OK:
+            msg = self._lib.zc_last_error(self._h).decode()
+            raise _ERRORS.get(rc, ZincError)(f"{name}: {msg}")
+
+    def set_stream(self, stream: Optional[int]) -> None:
+        self.call("zc_set_stream", C.c_void_p(stream or 0))
+
+    @property
+    def stream(self) -> int:
+        return self._lib.zc_get_stream(self._h) or 0
+
+    @property
+    def launch_count(self) -> int:
+        return int(self._lib.zc_launch_count(self._h))
+
+    def alloc(self, nbytes: int) -> Buffer:
+        p = C.c_void_p()
+        self.call("zc_alloc", nbytes, C.byref(p))
+        return Buffer(p.value, nbytes, self)
+
+    def free(self, b: Buffer) -> None:
+        self.call("zc_free", C.c_void_p(b.ptr))
+        b.ptr, b.size = 0, 0
+
+    def upload(self, dst: Buffer, host, dst_offset: int = 0) -> None:
+        """host: any object with the buffer protocol (numpy array, bytes)."""
+        mv = memoryview(host).cast("B")
+        src = (C.c_uint8 * len(mv)).from_buffer_copy(mv) if mv.readonly else (C.c_uint8 * len(mv)).from_buffer(mv)
+        self.call("zc_upload", C.c_void_p(dst.ptr), dst_offset, C.cast(src, C.c_void_p), len(mv))
+        self.submit_and_wait()
+
+    def download(self, src: Buffer, nbytes: int, src_offset: int = 0) -> bytes:
+        out = (C.c_uint8 * nbytes)()
+        self.call("zc_download", C.cast(out, C.c_void_p), C.c_void_p(src.ptr), src_offset, nbytes)
+        self.submit_and_wait()
+        return bytes(out)
+
+    def upload_from_ptr(self, dst: Buffer, host_ptr: int, nbytes: int, dst_offset: int = 0) -> None:
+        """Asynchronous copy from (pinned) host memory; ordered on the context's stream."""
+        self.call("zc_upload", C.c_void_p(dst.ptr), dst_offset, C.c_void_p(host_ptr), nbytes)
+
+    def download_to_ptr(self, host_ptr: int, src: Buffer, nbytes: int, src_offset: int = 0) -> None:
+        """Asynchronous copy to (pinned) host memory; complete after submit_and_wait()."""
+        self.call("zc_download", C.c_void_p(host_ptr), C.c_void_p(src.ptr), src_offset, nbytes)
+
+    def memset(self, dst: Buffer, value: int, nbytes: Optional[int] = None, dst_offset: int = 0) -> None:
+        self.call("zc_memset", C.c_void_p(dst.ptr), dst_offset, value, dst.size - dst_offset if nbytes is None else nbytes)
+
+    def barrier(self) -> None:  # computeBarrier (src/vulkan/command.zig:345-425): stream order already holds
+        self.call("zc_barrier")
+
+    def submit_and_wait(self) -> None:  # submitAndWait (src/vulkan/command.zig:477)
+        self.call("zc_submit_and_wait")
+
+    # -- pre-recorded sequences (a command buffer recorded once and submitted per token) ------
+    def begin_record(self) -> None:
+        self.call("zc_begin_record")
+
+    def end_record(self) -> int:
+        h = C.c_void_p()
+        self.call("zc_end_record", C.byref(h))
+        return h.value
+
+    def replay(self, recording: int) -> None:
+        self.call("zc_replay", C.c_void_p(recording))
+
+    def free_recording(self, recording: int) -> None:
+        self.call("zc_free_recording", C.c_void_p(recording))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.zc_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ---- layout helpers (src/model/gguf.zig:75-122, 222-229; src/compute/forward.zig:650-656) ----
+def block_size(t: int) -> int:
+    return _lib.lib().zc_block_size(t)
+
+
+def bytes_per_block(t: int) -> int:
+    return _lib.lib().zc_bytes_per_block(t)
+
+
+def tensor_size_bytes(t: int, n_elements: int) -> int:
+    return _lib.lib().zc_tensor_size_bytes(t, n_elements)
+
+
+def expert_slice_bytes(t: int, rows: int, cols: int) -> int:
+    return _lib.lib().zc_expert_slice_bytes(t, rows, cols)
+
+
+def row_bytes(t: int, K: int) -> int:
+    return (K // block_size(t)) * bytes_per_block(t)
+
+
+class DmmvDispatch:
+    """Mirror of DmmvDispatch (src/compute/dmmv.zig:161-297): one object per context."""
+
+    def __init__(self, ctx: Context):
+        self.ctx = ctx
+
+    # pipelineForType / moePipelineForType (src/compute/dmmv.zig:678-703)
+    def pipelineForType(self, quant_type: int) -> bool:
+        return bool(_lib.lib().zc_dmmv_supported(quant_type))
+
+    def moePipelineForType(self, quant_type: int) -> bool:
+        return bool(_lib.lib().zc_moe_dmmv_supported(quant_type))
+
+    # recordDispatch (src/compute/dmmv.zig:806-874); buffers in binding order A, x, y
+    def recordDispatch(self, quant_type, A, x, y, M, K, a_offset=0, x_offset=0, y_offset=0, acc_mode=0):
+        A, x, y = _buf(A), _buf(x), _buf(y)
+        self.ctx.call("zc_dmmv", quant_type, A.ptr, A.size, x.ptr, x.size, y.ptr, y.size, M, K,
+                      a_offset, x_offset, y_offset, acc_mode)
+
+    # recordBatchDispatchPush (src/compute/dmmv.zig:880-926) + dispatchProjectionBatched chunk loop
+    def recordBatchDispatchPush(self, quant_type, A, X, Y, M, K, a_offset, x_offset, y_offset, num_cols):
+        A, X, Y = _buf(A), _buf(X), _buf(Y)
+        self.ctx.call("zc_dmmv_batch", quant_type, A.ptr, A.size, X.ptr, X.size, Y.ptr, Y.size, M, K,
+                      a_offset, x_offset, y_offset, num_cols)
+
+    # recordMoeDispatch (src/compute/dmmv.zig:709-739); bindings A, x, y, routing
+    def recordMoeDispatch(self, quant_type, A, x, y, routing, M, K, expert_stride, n_experts_y,
+                          x_expert_stride, x_offset=0, y_offset=0):
+        A, x, y, routing = _buf(A), _buf(x), _buf(y), _buf(routing)
+        self.ctx.call("zc_moe_dmmv", quant_type, A.ptr, A.size, x.ptr, x.size, y.ptr, y.size,
+                      routing.ptr, routing.size, M, K, expert_stride, n_experts_y, x_expert_stride,
+                      x_offset, y_offset)
+
+    # recordMoeBatchedDispatch (src/compute/dmmv.zig:746-792)
+    def recordMoeBatchedDispatch(self, quant_type, A, X, Y, routing, M, K, expert_stride, n_experts,
+                                 n_experts_used, n_tokens, x_token_stride, y_token_stride):
+        A, X, Y, routing = _buf(A), _buf(X), _buf(Y), _buf(routing)
+        self.ctx.call("zc_moe_dmmv_batched", quant_type, A.ptr, A.size, X.ptr, X.size, Y.ptr, Y.size,
+                      routing.ptr, routing.size, M, K, expert_stride, n_experts, n_experts_used, n_tokens,
+                      x_token_stride, y_token_stride)
+
+    # recordCountExperts (src/compute/dmmv.zig:981-1028)
+    def recordCountExperts(self, routing, counts, n_tokens, n_layers, layer, n_experts_used, n_experts,
+                           d_offset_bytes=0):
+        routing, counts = _buf(routing), _buf(counts)
+        self.ctx.call("zc_count_experts", routing.ptr, routing.size, counts.ptr, counts.size, n_tokens, n_layers,
+                      layer, n_experts_used, n_experts, d_offset_bytes)
+
+    # recordMulMmQ4K (src/compute/dmmv.zig:1045-1094), widened to every type and to bf16 activations
+    def recordMulMm(self, quant_type, A, B, D, M, N, K, stride_b, stride_d, a_offset=0, b_offset=0, d_offset=0,
+                    act_type=F32):
+        A, B, D = _buf(A), _buf(B), _buf(D)
+        self.ctx.call("zc_mul_mm", quant_type, A.ptr, A.size, B.ptr, B.size, D.ptr, D.size, M, N, K,
+                      stride_b, stride_d, a_offset, b_offset, d_offset, act_type)
+
+    def recordMulMmQ4K(self, A, B, D, M, N, K, stride_b, stride_d, a_offset=0, b_offset=0, d_offset=0):
+        self.recordMulMm(Q4_K, A, B, D, M, N, K, stride_b, stride_d, a_offset, b_offset, d_offset, F32)
+
+    # ---- engine-side wrappers (src/compute/forward.zig) ---------------------------------------
+    # dispatchDmmvFusedGateUpSwiglu (forward.zig:8237-8313)
+    def dispatchDmmvFusedGateUpSwiglu(self, quant_type, Wg, Wu, x, out, M, K, gate_offset=0, up_offset=0,
+                                      x_offset=0, out_offset=0):
+        Wg, Wu, x, out = _buf(Wg), _buf(Wu), _buf(x), _buf(out)
+        self.ctx.call("zc_dmmv_fused_gate_up_swiglu", quant_type, Wg.ptr, Wg.size, Wu.ptr, Wu.size, x.ptr, x.size,
+                      out.ptr, out.size, M, K, gate_offset, up_offset, x_offset, out_offset)
+
+    # dispatchDmmvQ8_0SigmoidAcc (forward.zig:8321-8359)
+    def dispatchDmmvSigmoidAcc(self, quant_type, A, x, y, gate, M, K, a_offset=0, x_offset=0, y_offset=0,
+                               gate_index=0):
+        A, x, y, gate = _buf(A), _buf(x), _buf(y), _buf(gate)
+        self.ctx.call("zc_dmmv_sigmoid_acc", quant_type, A.ptr, A.size, x.ptr, x.size, y.ptr, y.size,
+                      gate.ptr, gate.size, M, K, a_offset, x_offset, y_offset, gate_index)
+
+    # fused gate+up MoE dispatch (forward.zig:6206-6222)
+    def dispatchMoeFusedGateUp(self, quant_type, Wg, Wu, x, y_gate, y_up, routing, M, K, expert_stride, n_used,
+                               x_expert_stride, x_offset=0, y_offset=0):
+        Wg, Wu, x, y_gate, y_up, routing = map(_buf, (Wg, Wu, x, y_gate, y_up, routing))
+        self.ctx.call("zc_moe_fused_gate_up", quant_type, Wg.ptr, Wg.size, Wu.ptr, Wu.size, x.ptr, x.size,
+                      y_gate.ptr, y_gate.size, y_up.ptr, y_up.size, routing.ptr, routing.size, M, K,
+                      expert_stride, n_used, x_expert_stride, x_offset, y_offset)
+
+    # fused down + weighted accumulate (forward.zig:6362-6389)
+    def dispatchMoeFusedDownAcc(self, quant_type, A, x, y, routing, M, K, expert_stride, n_used, x_expert_stride,
+                                x_offset=0, y_offset=0):
+        A, x, y, routing = map(_buf, (A, x, y, routing))
+        self.ctx.call("zc_moe_fused_down_acc", quant_type, A.ptr, A.size, x.ptr, x.size, y.ptr, y.size,
+                      routing.ptr, routing.size, M, K, expert_stride, n_used, x_expert_stride, x_offset, y_offset)
+
+    # dispatchSoftmaxTopk (forward.zig:4135-4210) and the CPU routers (forward.zig:496-571)
+    def dispatchSoftmaxTopk(self, logits, out, n_experts, k, rule=ROUTE_TOPK_THEN_SOFTMAX, n_tokens=1,
+                            logits_stride=None, out_stride=None, bias=None):
+        logits, out = _buf(logits), _buf(out)
+        bias_ptr = _buf(bias).ptr if bias is not None else None
+        self.ctx.call("zc_softmax_topk", logits.ptr, logits.size, bias_ptr, out.ptr, out.size, n_experts, k, rule,
+                      n_tokens, n_experts if logits_stride is None else logits_stride,
+                      2 * k if out_stride is None else out_stride)
+
+    # dispatchMoeWeightedAcc (src/shaders/moe_weighted_acc.comp:23-33)
+    def dispatchMoeWeightedAcc(self, a, b, routing, n, n_used, src_stride):
+        a, b, routing = map(_buf, (a, b, routing))
+        self.ctx.call("zc_moe_weighted_acc", a.ptr, a.size, b.ptr, b.size, routing.ptr, routing.size, n, n_used,
+                      src_stride)
+
+    # dispatchFfnActivation (forward.zig:3620-3727): swiglu / swiglu_oai
+    def dispatchSwiglu(self, gate, up, y, n, oai=False):
+        gate, up, y = map(_buf, (gate, up, y))
+        need = n * 4
+        if gate.size < need or up.size < need or y.size < need:
+            raise InvalidArgument("dispatchSwiglu: buffer smaller than n floats")
+        self.ctx.call("zc_swiglu_oai" if oai else "zc_swiglu", gate.ptr, up.ptr, y.ptr, n)
+
+    # grouped-by-expert prefill helpers (src/shaders/metal/moe_route_pack.metal, moe_route_scatter.metal)
+    def dispatchMoeRoutePack(self, routing, counts, ids, n_tokens, n_experts, k, routing_stride, ids_stride):
+        routing, counts, ids = map(_buf, (routing, counts, ids))
+        self.ctx.call("zc_moe_route_pack", routing.ptr, routing.size, counts.ptr, counts.size, ids.ptr, ids.size,
+                      n_tokens, n_experts, k, routing_stride, ids_stride)
+
+    def dispatchMoeRouteScatter(self, routing, src, dst, n_tokens, hidden_dim, k, routing_stride):
+        routing, src, dst = map(_buf, (routing, src, dst))
+        self.ctx.call("zc_moe_route_scatter", routing.ptr, routing.size, src.ptr, src.size, dst.ptr, dst.size,
+                      n_tokens, hidden_dim, k, routing_stride)
+
+    # dequantRow on the device (forward.zig:242-465), bit-exact
+    def dequantRows(self, quant_type, A, out, first_row, n_rows, K, a_offset=0):
+        A, out = _buf(A), _buf(out)
+        self.ctx.call("zc_dequant_rows", quant_type, A.ptr, A.size, out.ptr, out.size, first_row, n_rows, K,
+                      a_offset)
