@@ -25,6 +25,9 @@ struct zc_ctx {
     uint64_t launches = 0;
     uint32_t* status_host = nullptr;  // pinned, mapped: deferred device-side status words
     uint32_t* status_dev = nullptr;
+    float* scratch_partial = nullptr;     // split-K partial sums of the streaming matvec
+    uint32_t* scratch_counters = nullptr; // per-tile arrival counters (zero between launches)
+    int sm_count = 0;
     char err[512] = {0};
 };
 
@@ -117,6 +120,13 @@ inline const float* f32p(const void* p, uint64_t off) {
 }
 inline float* f32m(void* p, uint64_t off) { return reinterpret_cast<float*>(static_cast<uint8_t*>(p) + off); }
 
+inline void attach_scratch(zc_ctx* ctx, DmmvArgs& a) {
+    a.scratch_partial = ctx->scratch_partial;
+    a.scratch_counters = ctx->scratch_counters;
+    a.status = ctx->status_dev;
+    a.sm_count = ctx->sm_count;
+}
+
 }  // namespace
 
 extern "C" {
@@ -146,6 +156,17 @@ int32_t zc_init(int32_t device, zc_ctx** out_ctx) {
         return ZC_ERR_OOM;
     }
     memset(ctx->status_host, 0, 256);
+    ctx->sm_count = prop.multiProcessorCount;
+    if (cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_partial), kStreamPartialBytes) != cudaSuccess ||
+        cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_counters), kStreamCounterBytes) != cudaSuccess ||
+        cudaMemset(ctx->scratch_counters, 0, kStreamCounterBytes) != cudaSuccess) {
+        if (ctx->scratch_partial) cudaFree(ctx->scratch_partial);
+        if (ctx->scratch_counters) cudaFree(ctx->scratch_counters);
+        cudaFreeHost(ctx->status_host);
+        cudaStreamDestroy(ctx->own_stream);
+        delete ctx;
+        return ZC_ERR_OOM;
+    }
     *out_ctx = ctx;
     return ZC_OK;
 }
@@ -155,6 +176,8 @@ int32_t zc_destroy(zc_ctx* ctx) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    if (ctx->scratch_partial) cudaFree(ctx->scratch_partial);
+    if (ctx->scratch_counters) cudaFree(ctx->scratch_counters);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
     return ZC_OK;
@@ -308,6 +331,7 @@ int32_t zc_dmmv(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, cons
     a.M = M;
     a.K = K;
     a.acc_mode = acc_mode;
+    attach_scratch(ctx, a);
     cudaError_t e = launch_dmmv(type, MODE_PLAIN, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_dmmv");
 }
@@ -329,6 +353,7 @@ int32_t zc_dmmv_fused_gate_up_swiglu(zc_ctx* ctx, uint32_t type, const void* Wg,
     a.y = f32m(out, out_offset);
     a.M = M;
     a.K = K;
+    attach_scratch(ctx, a);
     cudaError_t e = launch_dmmv(type, MODE_GATE_UP_SWIGLU, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
@@ -350,6 +375,7 @@ int32_t zc_dmmv_sigmoid_acc(zc_ctx* ctx, uint32_t type, const void* A, uint64_t 
     a.gate = f32p(gate, (uint64_t)gate_index * 4);
     a.M = M;
     a.K = K;
+    attach_scratch(ctx, a);
     cudaError_t e = launch_dmmv(type, MODE_SIGMOID_ACC, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }

@@ -35,7 +35,22 @@ struct DmmvArgs {
     uint32_t n_tokens = 1;        // MODE_MOE_BATCHED
     uint32_t x_token_stride = 0;  // MODE_MOE_BATCHED, elements
     uint32_t y_token_stride = 0;  // MODE_MOE_BATCHED, elements
+    // context scratch for the split-K streaming kernels (may be null: streaming path not used)
+    float* scratch_partial = nullptr;
+    uint32_t* scratch_counters = nullptr;
+    uint32_t* status = nullptr;
+    int sm_count = 0;
 };
+
+// Capacity of the split-K scratch a context owns.
+constexpr uint32_t kStreamMaxGrid = 148 * 4;     // CTAs that may publish partial tiles
+constexpr uint32_t kStreamMaxTiles = 1u << 16;   // 16-row tiles with an arrival counter
+constexpr size_t kStreamPartialBytes = (size_t)kStreamMaxGrid * 2 * 32 * sizeof(float);
+constexpr size_t kStreamCounterBytes = (size_t)kStreamMaxTiles * sizeof(uint32_t);
+
+// Streaming (bulk-copy + tensor-core) matvec: eligibility and launch.
+bool stream_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a);
+cudaError_t launch_stream_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
 
 // Returns cudaSuccess or the launch error; *launches is incremented per kernel.
 cudaError_t launch_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
