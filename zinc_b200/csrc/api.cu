@@ -26,7 +26,7 @@ struct zc_ctx {
     uint32_t* status_host = nullptr;  // pinned, mapped: deferred device-side status words
     uint32_t* status_dev = nullptr;
     float* scratch_partial = nullptr;     // split-K partial sums of the streaming matvec
-    uint32_t* scratch_counters = nullptr; // per-tile arrival counters (zero between launches)
+    uint32_t* scratch_flags = nullptr; // publication flags (zero between launches)
     int sm_count = 0;
     char err[512] = {0};
 };
@@ -122,7 +122,7 @@ inline float* f32m(void* p, uint64_t off) { return reinterpret_cast<float*>(stat
 
 inline void attach_scratch(zc_ctx* ctx, DmmvArgs& a) {
     a.scratch_partial = ctx->scratch_partial;
-    a.scratch_counters = ctx->scratch_counters;
+    a.scratch_flags = ctx->scratch_flags;
     a.status = ctx->status_dev;
     a.sm_count = ctx->sm_count;
 }
@@ -158,10 +158,10 @@ int32_t zc_init(int32_t device, zc_ctx** out_ctx) {
     memset(ctx->status_host, 0, 256);
     ctx->sm_count = prop.multiProcessorCount;
     if (cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_partial), kStreamPartialBytes) != cudaSuccess ||
-        cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_counters), kStreamCounterBytes) != cudaSuccess ||
-        cudaMemset(ctx->scratch_counters, 0, kStreamCounterBytes) != cudaSuccess) {
+        cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_flags), kStreamFlagBytes) != cudaSuccess ||
+        cudaMemset(ctx->scratch_flags, 0, kStreamFlagBytes) != cudaSuccess) {
         if (ctx->scratch_partial) cudaFree(ctx->scratch_partial);
-        if (ctx->scratch_counters) cudaFree(ctx->scratch_counters);
+        if (ctx->scratch_flags) cudaFree(ctx->scratch_flags);
         cudaFreeHost(ctx->status_host);
         cudaStreamDestroy(ctx->own_stream);
         delete ctx;
@@ -177,7 +177,7 @@ int32_t zc_destroy(zc_ctx* ctx) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->scratch_partial) cudaFree(ctx->scratch_partial);
-    if (ctx->scratch_counters) cudaFree(ctx->scratch_counters);
+    if (ctx->scratch_flags) cudaFree(ctx->scratch_flags);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
     return ZC_OK;

@@ -35,22 +35,21 @@ struct DmmvArgs {
     uint32_t n_tokens = 1;        // MODE_MOE_BATCHED
     uint32_t x_token_stride = 0;  // MODE_MOE_BATCHED, elements
     uint32_t y_token_stride = 0;  // MODE_MOE_BATCHED, elements
-    // context scratch for the split-K streaming kernels (may be null: streaming path not used)
-    float* scratch_partial = nullptr;
-    uint32_t* scratch_counters = nullptr;
+    // context scratch of the split-K streaming kernels (null: streaming path not used)
+    float* scratch_partial = nullptr;   // [kStreamMaxWorkers][32] partial sums published across CTAs
+    uint32_t* scratch_flags = nullptr;  // [kStreamMaxWorkers] publication flags, zero between launches
     uint32_t* status = nullptr;
     int sm_count = 0;
 };
 
 // Capacity of the split-K scratch a context owns.
-constexpr uint32_t kStreamMaxGrid = 148 * 4;     // CTAs that may publish partial tiles
-constexpr uint32_t kStreamMaxTiles = 1u << 16;   // 16-row tiles with an arrival counter
-constexpr size_t kStreamPartialBytes = (size_t)kStreamMaxGrid * 2 * 32 * sizeof(float);
-constexpr size_t kStreamCounterBytes = (size_t)kStreamMaxTiles * sizeof(uint32_t);
+constexpr uint32_t kStreamMaxWorkers = 4096;  // warps that may publish a partial tile
+constexpr size_t kStreamPartialBytes = (size_t)kStreamMaxWorkers * 32 * sizeof(float);
+constexpr size_t kStreamFlagBytes = (size_t)kStreamMaxWorkers * sizeof(uint32_t);
 
-// Streaming (bulk-copy + tensor-core) matvec: eligibility and launch.
-bool stream_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a);
-cudaError_t launch_stream_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
+// Warp-autonomous streaming (cp.async + tensor-core) matvec: eligibility and launch.
+bool warp_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a);
+cudaError_t launch_warp_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
 
 // Returns cudaSuccess or the launch error; *launches is incremented per kernel.
 cudaError_t launch_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
