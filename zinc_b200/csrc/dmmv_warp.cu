@@ -1,30 +1,33 @@
-// Warp-autonomous streaming decode matvec for B200 (Q4_K).
+// Warp-autonomous streaming decode matvec for B200 (Q4_K), integer tensor-core dot engine.
 //
-// Every warp is an independent worker: it owns a contiguous range of work units
-// (16 rows x one 256-weight super-block), prefetches them with 16-byte asynchronous copies
-// (cp.async, lane-private shared-memory slots, depth kDepth), turns nibbles into exact small
-// f16 integers with one logic op each and uses the tensor cores as a 16-row dot-product
-// engine with f32 accumulation. There is no block-wide synchronisation after the activation
-// vector has been converted. K is split across workers so that all SMs stream the same number
-// of bytes; a tile that spans several workers is finished by the worker that owns its first
-// unit, which adds the partial sums the later workers have published (shared memory inside a
-// CTA, global memory across CTAs) in worker order, so results do not depend on timing.
+// Every warp is an independent worker: it owns a contiguous range of work units (16 rows x
+// kCB 256-weight super-blocks), prefetches them with bulk asynchronous copies (1-D TMA, one copy
+// per row segment, completion on the warp's own mbarriers, depth kDepth: the copies cost no
+// load/store-unit bandwidth), masks the 4-bit quants into int8 lanes (one logic op per four
+// weights) and feeds them to the int8 tensor cores as a 16-row dot-product engine with exact
+// s32 accumulation. There is no block-wide synchronisation after the activation vector has
+// been converted. K is split across workers so that all SMs stream the same number of bytes;
+// a tile that spans several workers is finished by the worker that owns its first unit, which
+// adds the partial sums the later workers have published (shared memory inside a CTA, global
+// memory across CTAs) in worker order, so results do not depend on timing.
 //
 // Stands in for the reference's K-parallel decode shaders and their fused epilogues
 // (src/shaders/dmmv_q4k.comp:59-240, dmmv_q4k_wide.comp, dmmv_q4k_fused_gate_up_swiglu.comp:195-218,
 // dmmv_q8_0_sigmoid_acc.comp:95-132) for the Q4_K layout of src/compute/forward.zig:370-409.
 //
 // Arithmetic per super-block of a row, sub-blocks s = 0..7 of 32 weights:
-//   y += 2^e * sum_s ( d*sc_s * D_s - (64*d*sc_s + dmin*m_s) * SX_s ),   D_s = sum_i (64+q_i) * x'_i
-// x' = x * 2^-e is the block of x scaled into (-1024, 1024) and split into two f16 terms
-// (x' = h1 + h2, 22 bits), SX_s = sum_i x'_i in f32. 64+q_i is exact in f16, products are exact
-// in f32, D_s is accumulated in f32 by the tensor core. Weights are never rounded.
+//   y += 2^-f * ( d * sum_s sc_s * P_s  -  dmin * sum_s m_s * SX_s ),   P_s = sum_i q_i * X_i
+// X_i = round(x_i * 2^f) is the block of x in 21-bit fixed point (f chosen per 256-element block
+// from its largest magnitude), split into three 7-bit digits X = b0*2^14 + b1*2^7 + b2 that fit
+// int8. The tensor core computes sum_i q_i * b_j,i exactly in s32 for each digit; P_s is
+// reassembled in integer arithmetic, SX_s = sum_i X_i is exact too. Weights are never rounded;
+// the only rounding before the final f32 scaling is that of x to 21 bits.
 //
-// Tensor-core mapping (mma.sync m16n8k16, f16 in, f32 out): the 16 A rows are 16 weight rows;
+// Tensor-core mapping (mma.sync m16n8k32, s8 in, s32 out): the 16 A rows are 16 weight rows;
 // lane (g = lane/4, t = lane%4) owns the 32-byte qs group t of rows g and g+8, i.e. sub-blocks
-// 2t (low nibbles) and 2t+1 (high nibbles). B is block-diagonal: column 2t+term is non-zero
-// only in lane t's k slots, so D column 2t+term holds sub-block dot products of group t alone
-// and lands in lane t's own accumulator registers. Scales are applied per lane afterwards.
+// 2t (low nibbles) and 2t+1 (high nibbles). B is block-diagonal: columns 2t and 2t+1 are
+// non-zero only in lane t's k slots, so those D columns hold dot products of group t alone and
+// land in lane t's own accumulator registers. Scales are applied per lane afterwards.
 #include "kernels.h"
 #include "common.cuh"
 #include "stream_common.cuh"
@@ -35,10 +38,13 @@ namespace {
 
 constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
-constexpr int kDepth = 3;                  // prefetched units per warp
-constexpr int kSlotBytes = 6 * 512;        // 6 pieces of 16 B per lane
+constexpr int kDepth = 2;                  // units in flight per warp
+constexpr int kCB = 2;                     // super-blocks per row segment
+constexpr int kRowSeg = kCB * 144 + 16;    // 304: rows land 16 B apart mod 32 B -> conflict-free 128-bit reads
+constexpr int kSlotBytes = 16 * kRowSeg;
 constexpr int kWarpRing = kDepth * kSlotBytes;
-constexpr int kZeroUnits = 64;             // 1 KB of zeros: B operand of the lanes whose column is dead
+constexpr int kZeroUnits = 72;             // zeros: B operand of the lanes whose columns are dead
+constexpr int kFracBits = 20;              // |X| <= 2^20
 
 struct WarpArgs {
     const uint8_t* A[2];
@@ -52,11 +58,12 @@ struct WarpArgs {
 };
 
 struct Smem {
-    uint4* xf;       // x in B-operand order: unit ((blk*8 + wi)*2 + term)*4 + t = 8 halves
+    uint4* xf;       // x digits in B-operand order: unit ((blk*8 + s*4 + j)*2 + p)*4 + t
     uint4* zeros;    // kZeroUnits zero units
-    float* sx;       // per 32-element sub-block sum of x'
-    float* xs;       // per super-block 2^e
-    uint8_t* ring;   // [kWarps][kDepth][6][32] 16-byte pieces
+    float* sx;       // per 32-element sub-block sum of X
+    float* xs;       // per super-block 2^-f
+    uint8_t* ring;   // [kWarps][kDepth] stages of 16 padded row segments
+    uint64_t* full;  // [kWarps][kDepth] "stage landed" barriers
     float* spartial; // [kWarps][32] partial sums published inside the CTA
     volatile uint32_t* sflags;  // [kWarps]
 };
@@ -66,7 +73,7 @@ __host__ __device__ inline size_t smem_bytes(uint32_t K) {
     n += (size_t)(K / 32) * 4 + (size_t)(K / 256) * 4;
     n = (n + 127) & ~size_t(127);
     n += (size_t)kWarps * kWarpRing;
-    n += (size_t)kWarps * 32 * 4 + (size_t)kWarps * 4;
+    n += (size_t)kWarps * 32 * 4 + (size_t)kWarps * 4 + (size_t)kWarps * kDepth * 8 + 16;
     return n + 128;
 }
 
@@ -84,70 +91,64 @@ __device__ inline Smem carve(uint8_t* base, uint32_t K) {
     p = (p + 127) & ~uintptr_t(127);
     s.ring = reinterpret_cast<uint8_t*>(p);
     p += (size_t)kWarps * kWarpRing;
+    s.full = reinterpret_cast<uint64_t*>(p);
+    p += (size_t)kWarps * kDepth * 8;
     s.spartial = reinterpret_cast<float*>(p);
     p += (size_t)kWarps * 32 * 4;
     s.sflags = reinterpret_cast<volatile uint32_t*>(p);
     return s;
 }
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
 __device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 
-__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
-    uint32_t r;
-    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
-__device__ __forceinline__ float2 unpack_h2(uint32_t v) {
-    return __half22float2(*reinterpret_cast<const __half2*>(&v));
+// D(16x8,s32) += A(16x32,s8,row) * B(32x8,s8,col)
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Convert x into the tensor-core operand layout. One warp per super-block; lane = wi*4 + t
-// handles elements 64t + 4wi + {0..3} (low-nibble sub-block 2t) and +32 (high-nibble 2t+1).
-// A unit holds (e0, e2, e1, e3) of the low-nibble elements, then the same of the high ones:
-// the order in which and_or() leaves the nibbles of one 32-bit word in A registers.
+// Convert x into int8 digits in tensor-core operand order. One warp per super-block;
+// lane = j*8 + s*4 + t handles the 8 consecutive elements 64t + 32s + 8j .. +7 (bytes 8j..8j+7
+// of qs group t; s = 0 low nibbles, 1 high nibbles). Unit p = 0 holds (digit 0 | digit 2) of
+// those 8 elements, unit p = 1 (digit 1 | zeros): the two B register pairs of the lanes that
+// feed columns 2t and 2t+1.
 __device__ inline void prep_x(const Smem& s, const float* __restrict__ x, uint32_t K, int warp, int lane) {
-    const int wi = lane >> 2, t = lane & 3;
+    const int j = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
     for (uint32_t blk = warp; blk < (K >> 8); blk += kWarps) {
-        const float* xp = x + (size_t)blk * 256 + 64 * t + 4 * wi;
+        const float* xp = x + (size_t)blk * 256 + 64 * t + 32 * sh + 8 * j;
         const float4 lo = __ldg(reinterpret_cast<const float4*>(xp));
-        const float4 hi = __ldg(reinterpret_cast<const float4*>(xp + 32));
-        float mx = fmaxf(fmaxf(fmaxf(fabsf(lo.x), fabsf(lo.y)), fmaxf(fabsf(lo.z), fabsf(lo.w))),
-                         fmaxf(fmaxf(fabsf(hi.x), fabsf(hi.y)), fmaxf(fabsf(hi.z), fabsf(hi.w))));
+        const float4 hi = __ldg(reinterpret_cast<const float4*>(xp) + 1);
+        const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        float mx = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(v[i]));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
-        // |x'| < 1024: x' = x * 2^(136 - E), E the biased exponent of the block maximum
+        // |x| < 2^(E-126)  ->  |x * 2^f| < 2^20 with f = 146 - E (E = biased exponent of the block maximum)
         uint32_t E = (__float_as_uint(mx) >> 23) & 0xFFu;
         E = E < 32u ? 32u : E;
-        const float scale = __uint_as_float((263u - E) << 23);
-        const float v0 = lo.x * scale, v1 = lo.y * scale, v2 = lo.z * scale, v3 = lo.w * scale;
-        const float v4 = hi.x * scale, v5 = hi.y * scale, v6 = hi.z * scale, v7 = hi.w * scale;
-        uint4 a, b;
-        a.x = pack_h2(v0, v2); a.y = pack_h2(v1, v3); a.z = pack_h2(v4, v6); a.w = pack_h2(v5, v7);
-        const float2 f02 = unpack_h2(a.x), f13 = unpack_h2(a.y), f46 = unpack_h2(a.z), f57 = unpack_h2(a.w);
-        b.x = pack_h2(v0 - f02.x, v2 - f02.y); b.y = pack_h2(v1 - f13.x, v3 - f13.y);
-        b.z = pack_h2(v4 - f46.x, v6 - f46.y); b.w = pack_h2(v5 - f57.x, v7 - f57.y);
-        const float2 r02 = unpack_h2(b.x), r13 = unpack_h2(b.y), r46 = unpack_h2(b.z), r57 = unpack_h2(b.w);
-        s.xf[((blk * 8 + wi) * 2 + 0) * 4 + t] = a;
-        s.xf[((blk * 8 + wi) * 2 + 1) * 4 + t] = b;
-        // sub-block sums of exactly the values the tensor core multiplies (h1 + h2 is exact in f32)
-        float slo = ((f02.x + r02.x) + (f02.y + r02.y)) + ((f13.x + r13.x) + (f13.y + r13.y));
-        float shi = ((f46.x + r46.x) + (f46.y + r46.y)) + ((f57.x + r57.x) + (f57.y + r57.y));
+        const float scale = __uint_as_float((127u + 126u + kFracBits - E) << 23);
+        uint32_t d0[2] = {0, 0}, d1[2] = {0, 0}, d2[2] = {0, 0};
+        int sum = 0;
 #pragma unroll
-        for (int o = 4; o < 32; o <<= 1) {
-            slo += __shfl_xor_sync(0xFFFFFFFFu, slo, o);
-            shi += __shfl_xor_sync(0xFFFFFFFFu, shi, o);
+        for (int i = 0; i < 8; ++i) {
+            const int X = __float2int_rn(v[i] * scale);
+            sum += X;
+            d0[i >> 2] |= (uint32_t)((X >> 14) & 0xFF) << (8 * (i & 3));
+            d1[i >> 2] |= (uint32_t)((X >> 7) & 0x7F) << (8 * (i & 3));
+            d2[i >> 2] |= (uint32_t)(X & 0x7F) << (8 * (i & 3));
         }
-        if (wi == 0) *reinterpret_cast<float2*>(s.sx + blk * 8 + 2 * t) = make_float2(slo, shi);
-        if (lane == 0) s.xs[blk] = __uint_as_float((E - 9u) << 23);
+        const uint32_t u = (blk * 8 + sh * 4 + j) * 2;
+        s.xf[(u + 0) * 4 + t] = make_uint4(d0[0], d0[1], d2[0], d2[1]);
+        s.xf[(u + 1) * 4 + t] = make_uint4(d1[0], d1[1], 0u, 0u);
+        // sub-block sums: reduce over j (lane bits 3 and 4)
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 8);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 16);
+        if (j == 0) s.sx[blk * 8 + 2 * t + sh] = (float)sum;
+        if (lane == 0) s.xs[blk] = __uint_as_float((E + 1u - kFracBits) << 23);  // 2^-f = 2^(E-146)
     }
 }
 
@@ -180,6 +181,70 @@ __device__ __forceinline__ void scales_mins_pair(uint32_t s0, uint32_t s1, uint3
 
 constexpr uint32_t kSpinLimit = 1u << 26;
 
+// Ends a tile for this warp. v[i][r]: sums of stream i for rows g (r = 0) and g+8 (r = 1), already
+// reduced over the four lanes of a row.
+template <int NS, int EPI>
+__device__ __forceinline__ void finish_tile(const WarpArgs& a, const Smem& s, float (&v)[NS][2], uint32_t T,
+                                            uint32_t upt_all, uint32_t u0, uint32_t u1, uint32_t U, uint32_t G,
+                                            uint32_t me, int warp, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t first = T * upt_all, last = first + upt_all - 1;
+    if (u0 > first) {
+        // not the first contributor: publish the partial sums for the worker that owns `first`
+        const uint32_t fin = part_owner(first, U, G);
+        const bool same_cta = fin / kWarps == blockIdx.x;
+        float* dst = same_cta ? s.spartial + warp * 32 : a.gpartial + (size_t)me * 32;
+        if (t == 0) {
+#pragma unroll
+            for (int i = 0; i < NS; ++i) {
+                dst[i * 16 + g] = v[i][0];
+                dst[i * 16 + g + 8] = v[i][1];
+            }
+            if (same_cta) __threadfence_block(); else __threadfence();
+        }
+        __syncwarp();
+        if (lane == 0) {
+            if (same_cta) s.sflags[warp] = 1u;
+            else *reinterpret_cast<volatile uint32_t*>(a.gflags + me) = 1u;
+        }
+        return;
+    }
+    if (last >= u1) {
+        // first contributor of a tile that continues in later workers: add their parts in order
+        const uint32_t cl = part_owner(last, U, G);
+        for (uint32_t c = me + 1; c <= cl; ++c) {
+            const bool same_cta = c / kWarps == blockIdx.x;
+            volatile uint32_t* flag =
+                same_cta ? s.sflags + (c % kWarps) : reinterpret_cast<volatile uint32_t*>(a.gflags + c);
+            uint32_t spins = 0;
+            while (*flag == 0u) {
+                if (++spins > kSpinLimit) {
+                    if (lane == 0) { a.status[0] = 1; a.status[1] = 3; }
+                    break;
+                }
+            }
+            if (same_cta) __threadfence_block(); else __threadfence();
+            const float* src = same_cta ? s.spartial + (c % kWarps) * 32 : a.gpartial + (size_t)c * 32;
+            if (t == 0) {
+#pragma unroll
+                for (int i = 0; i < NS; ++i) {
+                    v[i][0] += same_cta ? src[i * 16 + g] : ld_cg_f32(src + i * 16 + g);
+                    v[i][1] += same_cta ? src[i * 16 + g + 8] : ld_cg_f32(src + i * 16 + g + 8);
+                }
+            }
+            __syncwarp();
+            if (!same_cta && lane == 0) *flag = 0u;  // leave the global flags clear for the next launch
+        }
+    }
+    if (t == 0) {
+        float r0[NS], r1[NS];
+#pragma unroll
+        for (int i = 0; i < NS; ++i) { r0[i] = v[i][0]; r1[i] = v[i][1]; }
+        write_row<NS, EPI>(a, T * 16 + g, r0);
+        write_row<NS, EPI>(a, T * 16 + g + 8, r1);
+    }
+}
+
 template <int NS, int EPI>
 __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -188,38 +253,42 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
     const int g = lane >> 2, t = lane & 3;
     const uint32_t bpr = a.K >> 8;
     const uint64_t row_bytes = (uint64_t)bpr * 144;
-    const uint32_t upt_all = bpr * NS;  // units per 16-row tile
+    const uint32_t upt = (bpr + kCB - 1) / kCB;  // row segments (units) per row
+    const uint32_t upt_all = upt * NS;            // units per 16-row tile
     const uint32_t tiles = (a.M + 15) / 16;
     const uint32_t U = tiles * upt_all, G = gridDim.x * kWarps;  // units, workers (G <= U)
     const uint32_t me = blockIdx.x * kWarps + warp;
     const uint32_t u0 = (uint32_t)part_begin(me, U, G), u1 = (uint32_t)part_begin(me + 1, U, G);
     const uint32_t n = u1 - u0;
-    uint8_t* ring = s.ring + (size_t)warp * kWarpRing + lane * 16;
+    uint8_t* ring = s.ring + (size_t)warp * kWarpRing;
+    uint64_t* full = s.full + warp * kDepth;
 
-    // ---- prefetch iterator: (tile, stream, block) of the next unit to request ----
-    uint32_t p_tile = u0 / upt_all, p_strm = (u0 % upt_all) / bpr, p_blk = (u0 % upt_all) % bpr;
+    if (lane == 0) {
+#pragma unroll
+        for (int i = 0; i < kDepth; ++i) mbar_init(&full[i], 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+
+    // ---- prefetch iterator: (tile, stream, segment) of the next unit to request ----
+    uint32_t p_tile = u0 / upt_all, p_strm = (u0 % upt_all) / upt, p_kc = (u0 % upt_all) % upt;
     auto request = [&](uint32_t slot) {
-        const uint32_t rA = min(p_tile * 16 + g, a.M - 1), rB = min(p_tile * 16 + g + 8, a.M - 1);
-        const uint8_t* base = a.A[p_strm] + (uint64_t)p_blk * 144;
-        const uint8_t* pa = base + rA * row_bytes;
-        const uint8_t* pb = base + rB * row_bytes;
-        uint8_t* dst = ring + slot * kSlotBytes;
-        cp_async16(dst, pa);
-        cp_async16(dst + 512, pb);
-        cp_async16(dst + 1024, pa + 16 + 32 * t);
-        cp_async16(dst + 1536, pa + 32 + 32 * t);
-        cp_async16(dst + 2048, pb + 16 + 32 * t);
-        cp_async16(dst + 2560, pb + 32 + 32 * t);
-        if (++p_blk == bpr) {
-            p_blk = 0;
+        const uint32_t bytes = min((uint32_t)kCB, bpr - p_kc * kCB) * 144;
+        if (lane == 0) mbar_expect_tx(&full[slot], 16 * bytes);
+        __syncwarp();
+        if (lane < 16) {
+            const uint32_t row = min(p_tile * 16 + lane, a.M - 1);  // rows past M repeat the last row; never written
+            bulk_g2s(ring + slot * kSlotBytes + lane * kRowSeg,
+                     a.A[p_strm] + (uint64_t)row * row_bytes + (uint64_t)p_kc * (kCB * 144), bytes, &full[slot]);
+        }
+        if (++p_kc == upt) {
+            p_kc = 0;
             if (++p_strm == NS) { p_strm = 0; ++p_tile; }
         }
     };
 #pragma unroll
-    for (int i = 0; i < kDepth; ++i) {
+    for (int i = 0; i < kDepth; ++i)
         if ((uint32_t)i < n) request(i);
-        cp_async_commit();
-    }
 
     // ---- activation vector -> B operand layout (all warps), zero region, flags ----
     if (tid < kZeroUnits) s.zeros[tid] = make_uint4(0u, 0u, 0u, 0u);
@@ -228,141 +297,99 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
     __syncthreads();
 
     // ---- consume ----
-    uint32_t tile = u0 / upt_all, strm = (u0 % upt_all) / bpr, blk = (u0 % upt_all) % bpr;
-    float acc[NS][2];
-#pragma unroll
-    for (int i = 0; i < NS; ++i) acc[i][0] = acc[i][1] = 0.f;
+    uint32_t tile = u0 / upt_all, strm = (u0 % upt_all) / upt, kc = (u0 % upt_all) % upt;
+    float acc0[2] = {0.f, 0.f}, acc1[2] = {0.f, 0.f};  // stream 0 / stream 1, rows g and g+8
     const bool b_live = (g >> 1) == t;  // lane (g, t) feeds B column g, live only for g in {2t, 2t+1}
     const uint4* xu_live = s.xf + (g & 1) * 4 + t;
+    const uint4* xu_dead = s.zeros + (g >> 1) + 1;  // a bank group no live lane of the same quarter-warp uses
+    bool aborted = false;
 
-    auto finish_tile = [&](uint32_t T) {
-        // rows g and g+8 of this warp: reduce over the four lanes of a row
-        float v[NS][2];
-#pragma unroll
-        for (int i = 0; i < NS; ++i) {
-#pragma unroll
-            for (int r = 0; r < 2; ++r) {
-                float w = acc[i][r];
-                w += __shfl_xor_sync(0xFFFFFFFFu, w, 1);
-                w += __shfl_xor_sync(0xFFFFFFFFu, w, 2);
-                v[i][r] = w;
-                acc[i][r] = 0.f;
-            }
-        }
-        const uint32_t first = T * upt_all, last = first + upt_all - 1;
-        if (u0 > first) {
-            // not the first contributor: publish the partial sums for the worker that owns `first`
-            const uint32_t fin = part_owner(first, U, G);
-            const bool same_cta = fin / kWarps == blockIdx.x;
-            float* dst = same_cta ? s.spartial + warp * 32 : a.gpartial + (size_t)me * 32;
-            if (t == 0) {
-#pragma unroll
-                for (int i = 0; i < NS; ++i) {
-                    dst[i * 16 + g] = v[i][0];
-                    dst[i * 16 + g + 8] = v[i][1];
-                }
-                if (same_cta) __threadfence_block(); else __threadfence();
-            }
-            __syncwarp();
-            if (lane == 0) {
-                if (same_cta) s.sflags[warp] = 1u;
-                else *reinterpret_cast<volatile uint32_t*>(a.gflags + me) = 1u;
-            }
-            return;
-        }
-        if (last >= u1) {
-            // first contributor of a tile that continues in later workers: add their parts in order
-            const uint32_t cl = part_owner(last, U, G);
-            for (uint32_t c = me + 1; c <= cl; ++c) {
-                const bool same_cta = c / kWarps == blockIdx.x;
-                volatile uint32_t* flag = same_cta ? s.sflags + (c % kWarps)
-                                                   : reinterpret_cast<volatile uint32_t*>(a.gflags + c);
-                uint32_t spins = 0;
-                while (*flag == 0u) {
-                    if (++spins > kSpinLimit) {
-                        if (lane == 0) { a.status[0] = 1; a.status[1] = 3; }
-                        break;
-                    }
-                }
-                if (same_cta) __threadfence_block(); else __threadfence();
-                const float* src = same_cta ? s.spartial + (c % kWarps) * 32 : a.gpartial + (size_t)c * 32;
-                if (t == 0) {
-#pragma unroll
-                    for (int i = 0; i < NS; ++i) {
-                        v[i][0] += same_cta ? src[i * 16 + g] : ld_cg_f32(src + i * 16 + g);
-                        v[i][1] += same_cta ? src[i * 16 + g + 8] : ld_cg_f32(src + i * 16 + g + 8);
-                    }
-                }
-                __syncwarp();
-                if (!same_cta && lane == 0) *flag = 0u;  // leave the global flags clear for the next launch
-            }
-        }
-        if (t == 0) {
-            float r0[NS], r1[NS];
-#pragma unroll
-            for (int i = 0; i < NS; ++i) { r0[i] = v[i][0]; r1[i] = v[i][1]; }
-            write_row<NS, EPI>(a, T * 16 + g, r0);
-            write_row<NS, EPI>(a, T * 16 + g + 8, r1);
-        }
-    };
-
-    constexpr uint32_t kMask = 0x00F000F0u, kMagic = 0x54005400u;  // f16 64.0 + nibble in mantissa bits 4..7
     for (uint32_t it = 0; it < n; ++it) {
-        cp_async_wait<kDepth - 1>();
-        const uint8_t* sl = ring + (it % kDepth) * kSlotBytes;
-        const uint4 hA = lds128(sl), hB = lds128(sl + 512);
-        const uint4 qa0 = lds128(sl + 1024), qa1 = lds128(sl + 1536);
-        const uint4 qb0 = lds128(sl + 2048), qb1 = lds128(sl + 2560);
-        const uint32_t qa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
-        const uint32_t qb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
-        const uint4* xu = b_live ? xu_live + (size_t)blk * 64 : s.zeros;
-        float dlo[4] = {0.f, 0.f, 0.f, 0.f}, dhi[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int wi = 0; wi < 8; ++wi) {
-            const uint4 b = xu[wi * 8];
-            const uint32_t wa = qa[wi], wb = qb[wi];
-            // low nibbles of bytes (0,2) and (1,3): shift them into bits 4..7
-            mma_f16(dlo, and_or(wa << 4, kMask, kMagic), and_or(wb << 4, kMask, kMagic),
-                    and_or(wa >> 4, kMask, kMagic), and_or(wb >> 4, kMask, kMagic), b.x, b.y);
-            // high nibbles already sit in bits 4..7
-            mma_f16(dhi, and_or(wa, kMask, kMagic), and_or(wb, kMask, kMagic),
-                    and_or(wa >> 8, kMask, kMagic), and_or(wb >> 8, kMask, kMagic), b.z, b.w);
+        const uint32_t slot = it % kDepth;
+        if (!aborted && !mbar_wait_bounded(&full[slot], (it / kDepth) & 1u)) {
+            if (lane == 0) { a.status[0] = 1; a.status[1] = 2; }
+            aborted = true;
         }
-        // the slot's bytes are in registers now: request the unit kDepth ahead into it
-        if (it + kDepth < n) request(it % kDepth);
-        cp_async_commit();
-
-        // lane t's accumulator columns (2t, 2t+1) = the two f16 terms of x for its own sub-blocks
-        const float DloA = dlo[0] + dlo[1], DloB = dlo[2] + dlo[3];
-        const float DhiA = dhi[0] + dhi[1], DhiB = dhi[2] + dhi[3];
-        uint32_t scA, mnA, scB, mnB;
-        scales_mins_pair(hA.y, hA.z, hA.w, t, scA, mnA);
-        scales_mins_pair(hB.y, hB.z, hB.w, t, scB, mnB);
-        const float xs = s.xs[blk];
-        const float2 sxv = *reinterpret_cast<const float2*>(s.sx + blk * 8 + 2 * t);
-        const float dA = h2f(hA.x) * xs, dmA = h2f(hA.x >> 16) * xs;
-        const float dB = h2f(hB.x) * xs, dmB = h2f(hB.x >> 16) * xs;
-        const float cA0 = dA * (float)(scA & 0xFFu), cA1 = dA * (float)(scA >> 8);
-        const float cB0 = dB * (float)(scB & 0xFFu), cB1 = dB * (float)(scB >> 8);
-        float vA = cA0 * DloA + cA1 * DhiA;
-        vA -= (64.f * cA0 + dmA * (float)(mnA & 0xFFu)) * sxv.x + (64.f * cA1 + dmA * (float)(mnA >> 8)) * sxv.y;
-        float vB = cB0 * DloB + cB1 * DhiB;
-        vB -= (64.f * cB0 + dmB * (float)(mnB & 0xFFu)) * sxv.x + (64.f * cB1 + dmB * (float)(mnB >> 8)) * sxv.y;
+        const uint32_t nblk = min((uint32_t)kCB, bpr - kc * kCB);
 #pragma unroll
-        for (int i = 0; i < NS; ++i) {
-            acc[i][0] += (strm == (uint32_t)i) ? vA : 0.f;
-            acc[i][1] += (strm == (uint32_t)i) ? vB : 0.f;
+        for (uint32_t bi = 0; bi < (uint32_t)kCB; ++bi) {
+            if (bi >= nblk || aborted) break;
+            const uint32_t blk = kc * kCB + bi;
+            const uint8_t* sb = ring + slot * kSlotBytes + bi * 144;
+            const uint8_t* rA = sb + g * kRowSeg;
+            const uint8_t* rB = sb + (g + 8) * kRowSeg;
+            const uint4 hA = lds128(rA), hB = lds128(rB);
+            const uint4 qa0 = lds128(rA + 16 + 32 * t), qa1 = lds128(rA + 32 + 32 * t);
+            const uint4 qb0 = lds128(rB + 16 + 32 * t), qb1 = lds128(rB + 32 + 32 * t);
+            const uint32_t qa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+            const uint32_t qb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
+            const uint4* xu = b_live ? xu_live + (size_t)blk * 64 : xu_dead;
+            // D01: digits 0 and 1 in this lane's columns 2t, 2t+1; D2: digit 2 in column 2t
+            int lo01[4] = {0, 0, 0, 0}, lo2[4] = {0, 0, 0, 0}, hi01[4] = {0, 0, 0, 0}, hi2[4] = {0, 0, 0, 0};
+            constexpr uint32_t kNib = 0x0F0F0F0Fu;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 bl = xu[j * 8], bh = xu[(4 + j) * 8];
+                const uint32_t a0 = qa[2 * j], a1 = qb[2 * j], a2 = qa[2 * j + 1], a3 = qb[2 * j + 1];
+                const uint32_t l0 = a0 & kNib, l1 = a1 & kNib, l2 = a2 & kNib, l3 = a3 & kNib;
+                mma_s8(lo01, l0, l1, l2, l3, bl.x, bl.y);
+                mma_s8(lo2, l0, l1, l2, l3, bl.z, bl.w);
+                const uint32_t h0 = (a0 >> 4) & kNib, h1 = (a1 >> 4) & kNib, h2 = (a2 >> 4) & kNib,
+                               h3 = (a3 >> 4) & kNib;
+                mma_s8(hi01, h0, h1, h2, h3, bh.x, bh.y);
+                mma_s8(hi2, h0, h1, h2, h3, bh.z, bh.w);
+            }
+            // P = D0 * 2^14 + D1 * 2^7 + D2, exact in s32 (|P| < 2^31 for 5-bit quants and below)
+            const float PloA = (float)((lo01[0] << 14) + (lo01[1] << 7) + lo2[0]);
+            const float PloB = (float)((lo01[2] << 14) + (lo01[3] << 7) + lo2[2]);
+            const float PhiA = (float)((hi01[0] << 14) + (hi01[1] << 7) + hi2[0]);
+            const float PhiB = (float)((hi01[2] << 14) + (hi01[3] << 7) + hi2[2]);
+            uint32_t scA, mnA, scB, mnB;
+            scales_mins_pair(hA.y, hA.z, hA.w, t, scA, mnA);
+            scales_mins_pair(hB.y, hB.z, hB.w, t, scB, mnB);
+            const float xs = s.xs[blk];
+            const float2 sxv = *reinterpret_cast<const float2*>(s.sx + blk * 8 + 2 * t);
+            const float dA = h2f(hA.x) * xs, dmA = h2f(hA.x >> 16) * xs;
+            const float dB = h2f(hB.x) * xs, dmB = h2f(hB.x >> 16) * xs;
+            const float vA = dA * ((float)(scA & 0xFFu) * PloA + (float)(scA >> 8) * PhiA) -
+                             dmA * ((float)(mnA & 0xFFu) * sxv.x + (float)(mnA >> 8) * sxv.y);
+            const float vB = dB * ((float)(scB & 0xFFu) * PloB + (float)(scB >> 8) * PhiB) -
+                             dmB * ((float)(mnB & 0xFFu) * sxv.x + (float)(mnB >> 8) * sxv.y);
+            if (NS == 1 || strm == 0) { acc0[0] += vA; acc0[1] += vB; }
+            else { acc1[0] += vA; acc1[1] += vB; }
+        }
+        // the stage's bytes have been consumed: request the unit kDepth ahead into it
+        if (it + kDepth < n && !aborted) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            request(slot);
         }
         // advance; a tile ends with its last unit or with this worker's range
         const uint32_t T = tile;
         bool tile_done = false;
-        if (++blk == bpr) {
-            blk = 0;
+        if (++kc == upt) {
+            kc = 0;
             if (++strm == NS) { strm = 0; ++tile; tile_done = true; }
         }
-        if (tile_done || it + 1 == n) finish_tile(T);
+        if (tile_done || it + 1 == n) {
+            float v[NS][2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float w = acc0[r];
+                w += __shfl_xor_sync(0xFFFFFFFFu, w, 1);
+                w += __shfl_xor_sync(0xFFFFFFFFu, w, 2);
+                v[0][r] = w;
+                acc0[r] = 0.f;
+                if (NS == 2) {
+                    float w1 = acc1[r];
+                    w1 += __shfl_xor_sync(0xFFFFFFFFu, w1, 1);
+                    w1 += __shfl_xor_sync(0xFFFFFFFFu, w1, 2);
+                    v[NS - 1][r] = w1;
+                    acc1[r] = 0.f;
+                }
+            }
+            finish_tile<NS, EPI>(a, s, v, T, upt_all, u0, u1, U, G, me, warp, lane);
+        }
     }
-    cp_async_wait<0>();
 }
 
 template <int NS, int EPI>
@@ -375,7 +402,7 @@ cudaError_t launch_cfg(const WarpArgs& a, cudaStream_t st, int sm_count) {
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    const uint64_t U = (uint64_t)((a.M + 15) / 16) * (a.K >> 8) * NS;
+    const uint64_t U = (uint64_t)((a.M + 15) / 16) * (((a.K >> 8) + kCB - 1) / kCB) * NS;
     uint64_t grid = (uint64_t)sm_count;  // one CTA per SM, kWarps workers each
     if (grid * kWarps > U) grid = U / kWarps;
     if (grid * kWarps > kStreamMaxWorkers) grid = kStreamMaxWorkers / kWarps;
@@ -393,7 +420,7 @@ bool warp_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a) {
     if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (a.A2 && (reinterpret_cast<uintptr_t>(a.A2) & 15u))) return false;
     if (smem_bytes(a.K) > 227 * 1024) return false;
     const int ns = mode == MODE_GATE_UP_SWIGLU ? 2 : 1;
-    const uint64_t U = (uint64_t)((a.M + 15) / 16) * (a.K >> 8) * ns;
+    const uint64_t U = (uint64_t)((a.M + 15) / 16) * (((a.K >> 8) + kCB - 1) / kCB) * ns;
     if (U < kWarps || U > 0xFFFFFFFFull) return false;
     return true;
 }
