@@ -1,9 +1,9 @@
 // Warp-autonomous streaming decode matvec for B200 (Q4_K), integer tensor-core dot engine.
 //
 // Every warp is an independent worker: it owns a contiguous range of work units (16 rows x
-// kCB 256-weight super-blocks), prefetches them with bulk asynchronous copies (1-D TMA, one copy
-// per row segment, completion on the warp's own mbarriers, depth kDepth: the copies cost no
-// load/store-unit bandwidth), masks the 4-bit quants into int8 lanes (one logic op per four
+// kCB 256-weight super-blocks), prefetches them with coalesced 16-byte asynchronous copies
+// (cp.async into the warp's own ring of padded row segments, depth kDepth; bulk TMA copies were
+// measured at ~14 cycles of issue each per SM, too slow for 288-byte row segments), masks the 4-bit quants into int8 lanes (one logic op per four
 // weights) and feeds them to the int8 tensor cores as a 16-row dot-product engine with exact
 // s32 accumulation. There is no block-wide synchronisation after the activation vector has
 // been converted. K is split across workers so that all SMs stream the same number of bytes;
@@ -45,6 +45,8 @@ constexpr int kSlotBytes = 16 * kRowSeg;
 constexpr int kWarpRing = kDepth * kSlotBytes;
 constexpr int kZeroUnits = 72;             // zeros: B operand of the lanes whose columns are dead
 constexpr int kFracBits = 20;              // |X| <= 2^20
+constexpr int kPiecesPerRow = kCB * 9;     // 16-byte pieces of one row segment
+constexpr int kPiecesPerLane = (16 * kPiecesPerRow + 31) / 32;
 
 struct WarpArgs {
     const uint8_t* A[2];
@@ -100,6 +102,15 @@ __device__ inline Smem carve(uint8_t* base, uint32_t K) {
 }
 
 __device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 // D(16x8,s32) += A(16x32,s8,row) * B(32x8,s8,col)
 __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -261,25 +272,30 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
     const uint32_t u0 = (uint32_t)part_begin(me, U, G), u1 = (uint32_t)part_begin(me + 1, U, G);
     const uint32_t n = u1 - u0;
     uint8_t* ring = s.ring + (size_t)warp * kWarpRing;
-    uint64_t* full = s.full + warp * kDepth;
 
-    if (lane == 0) {
+    // ---- prefetch: coalesced 16-byte asynchronous copies into padded row segments ----
+    // piece p = i*32 + lane of a unit covers row p / kPiecesPerRow, 16-byte column p % kPiecesPerRow,
+    // so one warp instruction reads 512 contiguous bytes of one or two rows.
+    uint32_t piece[kPiecesPerLane];  // row | column << 8
 #pragma unroll
-        for (int i = 0; i < kDepth; ++i) mbar_init(&full[i], 1);
-        mbar_fence_init();
+    for (int i = 0; i < kPiecesPerLane; ++i) {
+        const uint32_t p = i * 32 + lane;
+        const uint32_t r = p / kPiecesPerRow;
+        piece[i] = r | ((p - r * kPiecesPerRow) << 8);
     }
-    __syncwarp();
-
-    // ---- prefetch iterator: (tile, stream, segment) of the next unit to request ----
     uint32_t p_tile = u0 / upt_all, p_strm = (u0 % upt_all) / upt, p_kc = (u0 % upt_all) % upt;
     auto request = [&](uint32_t slot) {
-        const uint32_t bytes = min((uint32_t)kCB, bpr - p_kc * kCB) * 144;
-        if (lane == 0) mbar_expect_tx(&full[slot], 16 * bytes);
-        __syncwarp();
-        if (lane < 16) {
-            const uint32_t row = min(p_tile * 16 + lane, a.M - 1);  // rows past M repeat the last row; never written
-            bulk_g2s(ring + slot * kSlotBytes + lane * kRowSeg,
-                     a.A[p_strm] + (uint64_t)row * row_bytes + (uint64_t)p_kc * (kCB * 144), bytes, &full[slot]);
+        const uint32_t cols = min((uint32_t)kCB, bpr - p_kc * kCB) * 9;  // 16-byte columns in this segment
+        const uint8_t* src = a.A[p_strm] + (uint64_t)p_kc * (kCB * 144);
+        uint8_t* dst = ring + slot * kSlotBytes;
+        const uint32_t row0 = p_tile * 16;
+#pragma unroll
+        for (int i = 0; i < kPiecesPerLane; ++i) {
+            const uint32_t r = piece[i] & 0xFFu, c = piece[i] >> 8;
+            if (c < cols) {
+                const uint32_t row = min(row0 + r, a.M - 1);  // rows past M repeat the last row; never written
+                cp_async16(dst + r * kRowSeg + c * 16, src + (uint64_t)row * row_bytes + c * 16);
+            }
         }
         if (++p_kc == upt) {
             p_kc = 0;
@@ -287,8 +303,10 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
         }
     };
 #pragma unroll
-    for (int i = 0; i < kDepth; ++i)
+    for (int i = 0; i < kDepth; ++i) {
         if ((uint32_t)i < n) request(i);
+        cp_async_commit();
+    }
 
     // ---- activation vector -> B operand layout (all warps), zero region, flags ----
     if (tid < kZeroUnits) s.zeros[tid] = make_uint4(0u, 0u, 0u, 0u);
@@ -302,18 +320,15 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
     const bool b_live = (g >> 1) == t;  // lane (g, t) feeds B column g, live only for g in {2t, 2t+1}
     const uint4* xu_live = s.xf + (g & 1) * 4 + t;
     const uint4* xu_dead = s.zeros + (g >> 1) + 1;  // a bank group no live lane of the same quarter-warp uses
-    bool aborted = false;
 
     for (uint32_t it = 0; it < n; ++it) {
         const uint32_t slot = it % kDepth;
-        if (!aborted && !mbar_wait_bounded(&full[slot], (it / kDepth) & 1u)) {
-            if (lane == 0) { a.status[0] = 1; a.status[1] = 2; }
-            aborted = true;
-        }
+        cp_async_wait<kDepth - 1>();  // this lane's copies of unit `it` have landed
+        __syncwarp();                 // ... and so have the other lanes'
         const uint32_t nblk = min((uint32_t)kCB, bpr - kc * kCB);
 #pragma unroll
         for (uint32_t bi = 0; bi < (uint32_t)kCB; ++bi) {
-            if (bi >= nblk || aborted) break;
+            if (bi >= nblk) break;
             const uint32_t blk = kc * kCB + bi;
             const uint8_t* sb = ring + slot * kSlotBytes + bi * 144;
             const uint8_t* rA = sb + g * kRowSeg;
@@ -358,11 +373,10 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
             if (NS == 1 || strm == 0) { acc0[0] += vA; acc0[1] += vB; }
             else { acc1[0] += vA; acc1[1] += vB; }
         }
-        // the stage's bytes have been consumed: request the unit kDepth ahead into it
-        if (it + kDepth < n && !aborted) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            request(slot);
-        }
+        // every lane has consumed the stage: request the unit kDepth ahead into it
+        __syncwarp();
+        if (it + kDepth < n) request(slot);
+        cp_async_commit();
         // advance; a tile ends with its last unit or with this worker's range
         const uint32_t T = tile;
         bool tile_done = false;
