@@ -126,12 +126,32 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
 // of qs group t; s = 0 low nibbles, 1 high nibbles). Unit p = 0 holds (digit 0 | digit 2) of
 // those 8 elements, unit p = 1 (digit 1 | zeros): the two B register pairs of the lanes that
 // feed columns 2t and 2t+1.
-__device__ inline void prep_x(const Smem& s, const float* __restrict__ x, uint32_t K, int warp, int lane) {
+//
+// The loads are issued before the weight prefetch (so they are not queued behind it) and
+// converted afterwards: kPrepBlocks super-blocks per warp cover K <= kPrepBlocks * kWarps * 256.
+constexpr int kPrepBlocks = 3;
+struct XRegs {
+    float4 lo[kPrepBlocks], hi[kPrepBlocks];
+};
+__device__ __forceinline__ void load_x(XRegs& r, const float* __restrict__ x, uint32_t K, int warp, int lane) {
     const int j = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
-    for (uint32_t blk = warp; blk < (K >> 8); blk += kWarps) {
-        const float* xp = x + (size_t)blk * 256 + 64 * t + 32 * sh + 8 * j;
-        const float4 lo = __ldg(reinterpret_cast<const float4*>(xp));
-        const float4 hi = __ldg(reinterpret_cast<const float4*>(xp) + 1);
+#pragma unroll
+    for (int i = 0; i < kPrepBlocks; ++i) {
+        const uint32_t blk = warp + i * kWarps;
+        if (blk < (K >> 8)) {
+            const float* xp = x + (size_t)blk * 256 + 64 * t + 32 * sh + 8 * j;
+            r.lo[i] = __ldg(reinterpret_cast<const float4*>(xp));
+            r.hi[i] = __ldg(reinterpret_cast<const float4*>(xp) + 1);
+        }
+    }
+}
+__device__ __forceinline__ void prep_x(const Smem& s, const XRegs& r, uint32_t K, int warp, int lane) {
+    const int j = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
+#pragma unroll
+    for (int bi = 0; bi < kPrepBlocks; ++bi) {
+        const uint32_t blk = warp + bi * kWarps;
+        if (blk >= (K >> 8)) break;
+        const float4 lo = r.lo[bi], hi = r.hi[bi];
         const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
         float mx = 0.f;
 #pragma unroll
@@ -221,31 +241,54 @@ __device__ __forceinline__ void finish_tile(const WarpArgs& a, const Smem& s, fl
         return;
     }
     if (last >= u1) {
-        // first contributor of a tile that continues in later workers: add their parts in order
+        // first contributor of a tile that continues in later workers. They published early (the
+        // tile is the first thing they work on); wait for all flags at once, then let lane t of each
+        // row add parts t, t+4, ... so that the remote reads overlap. The order is fixed by lane
+        // index, not by timing.
         const uint32_t cl = part_owner(last, U, G);
-        for (uint32_t c = me + 1; c <= cl; ++c) {
+        const uint32_t cnt = cl - me;  // contributors me+1 .. cl
+        for (uint32_t base = 0; base < cnt; base += 32) {
+            const uint32_t c = me + 1 + base + lane;
+            bool ready = c > cl;
             const bool same_cta = c / kWarps == blockIdx.x;
             volatile uint32_t* flag =
-                same_cta ? s.sflags + (c % kWarps) : reinterpret_cast<volatile uint32_t*>(a.gflags + c);
+                same_cta ? s.sflags + (c % kWarps) : reinterpret_cast<volatile uint32_t*>(a.gflags + min(c, cl));
             uint32_t spins = 0;
-            while (*flag == 0u) {
+            while (!__all_sync(0xFFFFFFFFu, ready)) {
+                if (!ready) ready = *flag != 0u;
                 if (++spins > kSpinLimit) {
                     if (lane == 0) { a.status[0] = 1; a.status[1] = 3; }
                     break;
                 }
             }
-            if (same_cta) __threadfence_block(); else __threadfence();
-            const float* src = same_cta ? s.spartial + (c % kWarps) * 32 : a.gpartial + (size_t)c * 32;
-            if (t == 0) {
-#pragma unroll
-                for (int i = 0; i < NS; ++i) {
-                    v[i][0] += same_cta ? src[i * 16 + g] : ld_cg_f32(src + i * 16 + g);
-                    v[i][1] += same_cta ? src[i * 16 + g + 8] : ld_cg_f32(src + i * 16 + g + 8);
-                }
-            }
-            __syncwarp();
-            if (!same_cta && lane == 0) *flag = 0u;  // leave the global flags clear for the next launch
         }
+        __threadfence();
+        float w[NS][2];
+#pragma unroll
+        for (int i = 0; i < NS; ++i) w[i][0] = w[i][1] = 0.f;
+        for (uint32_t c = me + 1 + t; c <= cl; c += 4) {
+            const bool same_cta = c / kWarps == blockIdx.x;
+            const float* src = same_cta ? s.spartial + (c % kWarps) * 32 : a.gpartial + (size_t)c * 32;
+#pragma unroll
+            for (int i = 0; i < NS; ++i) {
+                w[i][0] += same_cta ? src[i * 16 + g] : ld_cg_f32(src + i * 16 + g);
+                w[i][1] += same_cta ? src[i * 16 + g + 8] : ld_cg_f32(src + i * 16 + g + 8);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float q = w[i][r];
+                q += __shfl_xor_sync(0xFFFFFFFFu, q, 1);
+                q += __shfl_xor_sync(0xFFFFFFFFu, q, 2);
+                v[i][r] += q;
+            }
+        }
+        __syncwarp();
+        // every part has been read: clear the global flags for the next launch
+        for (uint32_t c = me + 1 + lane; c <= cl; c += 32)
+            if (c / kWarps != blockIdx.x) *reinterpret_cast<volatile uint32_t*>(a.gflags + c) = 0u;
     }
     if (t == 0) {
         float r0[NS], r1[NS];
@@ -272,6 +315,8 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
     const uint32_t u0 = (uint32_t)part_begin(me, U, G), u1 = (uint32_t)part_begin(me + 1, U, G);
     const uint32_t n = u1 - u0;
     uint8_t* ring = s.ring + (size_t)warp * kWarpRing;
+    XRegs xr;
+    load_x(xr, a.x, a.K, warp, lane);  // ahead of the weight prefetch in the memory queues
 
     // ---- prefetch: coalesced 16-byte asynchronous copies into padded row segments ----
     // piece p = i*32 + lane of a unit covers row p / kPiecesPerRow, 16-byte column p % kPiecesPerRow,
@@ -311,7 +356,7 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
     // ---- activation vector -> B operand layout (all warps), zero region, flags ----
     if (tid < kZeroUnits) s.zeros[tid] = make_uint4(0u, 0u, 0u, 0u);
     if (tid < kWarps) s.sflags[tid] = 0u;
-    prep_x(s, a.x, a.K, warp, lane);
+    prep_x(s, xr, a.K, warp, lane);
     __syncthreads();
 
     // ---- consume ----
@@ -432,7 +477,7 @@ bool warp_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a) {
     if (mode != MODE_PLAIN && mode != MODE_GATE_UP_SWIGLU && mode != MODE_SIGMOID_ACC) return false;
     if (!a.scratch_partial || !a.scratch_flags || !a.status) return false;
     if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (a.A2 && (reinterpret_cast<uintptr_t>(a.A2) & 15u))) return false;
-    if (smem_bytes(a.K) > 227 * 1024) return false;
+    if (smem_bytes(a.K) > 227 * 1024 || (a.K >> 8) > (uint32_t)(kPrepBlocks * kWarps)) return false;
     const int ns = mode == MODE_GATE_UP_SWIGLU ? 2 : 1;
     const uint64_t U = (uint64_t)((a.M + 15) / 16) * (((a.K >> 8) + kCB - 1) / kCB) * ns;
     if (U < kWarps || U > 0xFFFFFFFFull) return false;
