@@ -81,9 +81,11 @@ typedef struct zc_ctx zc_ctx;
  * (src/compute/dmmv.zig:305-671, 1098-1129). */
 int32_t zc_init(int32_t device, zc_ctx** out_ctx);
 int32_t zc_destroy(zc_ctx* ctx);
-/* Use a caller-owned cudaStream_t (e.g. the framework's current stream).
- * NULL restores the context's own stream. */
+/* Use a caller-owned cudaStream_t (e.g. the framework's current stream); NULL is
+ * CUDA's default stream. zc_use_own_stream goes back to the stream the context
+ * created for itself (the initial state). */
 int32_t zc_set_stream(zc_ctx* ctx, void* cuda_stream);
+int32_t zc_use_own_stream(zc_ctx* ctx);
 void* zc_get_stream(zc_ctx* ctx);
 /* Text of the last error recorded on this context (never NULL). */
 const char* zc_last_error(zc_ctx* ctx);

@@ -230,8 +230,10 @@ def test_linearity_at_full_size(gpu):
             dd.recordDispatch(t, w, xv, yv, M, K)
         ctx.submit_and_wait()
         want = 0.5 * ys[0].double() - 2.0 * ys[1].double()
+        for i, yv in enumerate(ys):
+            assert bool(torch.isfinite(yv).all()), f"{zb.TYPE_NAMES[t]}: dispatch {i} left non-finite rows"
         err = (ys[2].double() - want).norm() / want.norm()
-        assert float(err) <= TOL
+        assert float(err) <= TOL, zb.TYPE_NAMES[t]
 
 
 def test_full_size_rows_match_oracle_sample(gpu, oracle):
@@ -270,3 +272,46 @@ def test_error_codes(gpu):
     dd.recordDispatch(zb.Q4_K, w, x, y, 4, 256)
     ctx.submit_and_wait()
     assert float(y.abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("t", [zb.Q4_K, zb.Q6_K], ids=["q4_k", "q6_k"])
+@pytest.mark.parametrize("M,K", [(16, 2048), (67, 2048), (300, 6144), (1000, 12288), (4099, 4096), (33, 14336)])
+def test_streaming_shapes(gpu, oracle, t, M, K):
+    """Shapes that take the split-K streaming kernels (rows not a multiple of 16, tiles split across
+    workers inside a CTA and across CTAs, K up to the shared-memory limit) and one beyond it."""
+    torch, ctx, dd = gpu
+    g = synth.rng(106, t * 100000 + M * 31 + K)
+    w = synth.quant_matrix(g, t, M, K)
+    x = synth.activations(g, K) * np.float32(3.0 if M % 2 else 1e-3)  # also exercise the per-block scaling
+    y0 = synth.activations(g, M)
+    y = out_with_canary(torch, M)
+    y[:M] = dev(torch, y0)
+    wd, xd = dev(torch, w), dev(torch, x)
+    dd.recordDispatch(t, wd, xd, y, M, K, acc_mode=1)
+    ctx.submit_and_wait()
+    want = oracle.dmmv_f64(w, t, M, K, x)
+    assert canary_intact(y, M)
+    assert rel_l2(y[:M].cpu().numpy() - y0, want) <= TOL
+    # twice in a row: the split-K hand-off state must be clean after a launch
+    for _ in range(2):
+        dd.recordDispatch(t, wd, xd, y, M, K, acc_mode=0)
+    ctx.submit_and_wait()
+    assert rel_l2(y[:M].cpu().numpy(), want) <= TOL
+
+
+def test_streaming_extreme_activations(gpu, oracle):
+    """Activation blocks that are all zero, tiny, huge, or mixed by 2^40 within a block."""
+    torch, ctx, dd = gpu
+    M, K = 48, 4096
+    g = synth.rng(107, 0)
+    x = synth.activations(g, K)
+    x[0:256] = 0.0
+    x[256:512] *= np.float32(1e-30)
+    x[512:768] *= np.float32(1e30)
+    x[768:1024:2] *= np.float32(2.0 ** -40)
+    for t in (zb.Q4_K, zb.Q6_K):
+        w = synth.quant_matrix(g, t, M, K)
+        y = out_with_canary(torch, M)
+        dd.recordDispatch(t, dev(torch, w), dev(torch, x), y, M, K)
+        ctx.submit_and_wait()
+        assert rel_l2(y[:M].cpu().numpy(), oracle.dmmv_f64(w, t, M, K, x)) <= TOL

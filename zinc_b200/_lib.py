@@ -52,6 +52,7 @@ _OPS = {
     "zc_download": [_vp, _vp, _u64, _u64],
     "zc_memset": [_vp, _u64, _i32, _u64],
     "zc_set_stream": [_vp],
+    "zc_use_own_stream": [],
     "zc_begin_record": [],
     "zc_end_record": [C.POINTER(_vp)],
     "zc_replay": [_vp],

@@ -185,7 +185,13 @@ int32_t zc_destroy(zc_ctx* ctx) {
 
 int32_t zc_set_stream(zc_ctx* ctx, void* cuda_stream) {
     if (!ctx) return ZC_ERR_INVALID_ARG;
-    ctx->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : ctx->own_stream;
+    ctx->stream = static_cast<cudaStream_t>(cuda_stream);  // NULL is CUDA's default stream
+    return ZC_OK;
+}
+
+int32_t zc_use_own_stream(zc_ctx* ctx) {
+    if (!ctx) return ZC_ERR_INVALID_ARG;
+    ctx->stream = ctx->own_stream;
     return ZC_OK;
 }
 

@@ -1,0 +1,338 @@
+// Warp-autonomous streaming decode matvec for B200 (Q6_K), integer tensor-core dot engine.
+// Same skeleton as the Q4_K kernel (stream_skel.cuh): every warp owns a contiguous range of
+// (16 rows x one 256-weight super-block) units, prefetches them with coalesced 16-byte
+// asynchronous copies and finishes split tiles in worker order.
+//
+// Stands in for src/shaders/dmmv_q6k.comp:58-156 (and its use for the down projection and the LM
+// head, src/compute/forward.zig:7420, 7714) for the Q6_K layout of src/compute/forward.zig:276-325:
+// 210-byte blocks ql[128] qh[64] scales[16] (int8) d (f16), 16-weight sub-blocks.
+//
+// Arithmetic per super-block of a row:  y += 2^-f * d * sum_s sc_s * P_s,
+//   P_s = sum_{i in s} (v_i - 32) * X_i = D_s - 32 * SX_s,   D_s = sum_i v_i * X_i
+// v_i = 6-bit quant 0..63 fed to the tensor core as u8, X_i = round(x_i * 2^f) the block of x in
+// 21-bit fixed point split into three 7-bit digits (s8), SX_s = sum_i X_i. D_s, SX_s and P_s are
+// exact integers; the only rounding before the f32 scaling is that of x to 21 bits.
+//
+// Blocks are only 2-byte aligned (210 = 13*16 + 2), so a unit is copied as the 16-byte aligned
+// superset of each row's block and read back with aligned 32-bit loads + a funnel shift whose
+// amount is the same for the whole warp. Rows must start 16-byte aligned (K a multiple of 2048).
+//
+// Lane (g = lane/4, t = lane%4) owns, for rows g and g+8, the 32 ql bytes 64h + 32c .. (h = t/2,
+// c = t%2) and the 32 qh bytes of half h: low nibbles are elements 128h + 32c + l, high nibbles
+// 128h + 64 + 32c + l, i.e. four 16-weight sub-blocks. B is block-diagonal as in the Q4_K kernel.
+#include "kernels.h"
+#include "stream_skel.cuh"
+
+namespace zc {
+
+namespace {
+
+constexpr int kDepth = 2;
+constexpr int kRow6 = 240;                  // bytes per row slot: 224-byte superset + pad (15 x 16: odd)
+constexpr int kSlot6 = 16 * kRow6;
+constexpr int kRing6 = kDepth * kSlot6;
+constexpr int kPieces6 = 14;                // 16-byte pieces per row superset
+constexpr int kPiecesLane6 = (16 * kPieces6 + 31) / 32;  // 7
+constexpr int kZeroUnits = 72;
+constexpr int kFracBits = 20;
+constexpr int kPrepBlocks = 3;
+
+struct Smem6 {
+    uint4* xf;       // x digits in B-operand order: unit ((blk*8 + s*4 + i)*2 + p)*4 + t
+    uint4* zeros;
+    int* sx;         // per 16-element sub-block sum of X (exact)
+    float* xs;       // per super-block 2^-f
+    uint8_t* ring;   // [kWarps][kDepth] stages of 16 row slots
+    float* spartial;
+    volatile uint32_t* sflags;
+};
+
+__host__ __device__ inline size_t smem_bytes6(uint32_t K) {
+    size_t n = (size_t)K * 4 + (size_t)kZeroUnits * 16;
+    n += (size_t)(K / 16) * 4 + (size_t)(K / 256) * 4;
+    n = (n + 127) & ~size_t(127);
+    n += (size_t)kWarps * kRing6;
+    n += (size_t)kWarps * 32 * 4 + (size_t)kWarps * 4 + 16;
+    return n + 128;
+}
+
+__device__ inline Smem6 carve6(uint8_t* base, uint32_t K) {
+    Smem6 s;
+    uintptr_t p = (reinterpret_cast<uintptr_t>(base) + 127) & ~uintptr_t(127);
+    s.xf = reinterpret_cast<uint4*>(p);
+    p += (size_t)K * 4;
+    s.zeros = reinterpret_cast<uint4*>(p);
+    p += (size_t)kZeroUnits * 16;
+    s.sx = reinterpret_cast<int*>(p);
+    p += (size_t)(K / 16) * 4;
+    s.xs = reinterpret_cast<float*>(p);
+    p += (size_t)(K / 256) * 4;
+    p = (p + 127) & ~uintptr_t(127);
+    s.ring = reinterpret_cast<uint8_t*>(p);
+    p += (size_t)kWarps * kRing6;
+    s.spartial = reinterpret_cast<float*>(p);
+    p += (size_t)kWarps * 32 * 4;
+    s.sflags = reinterpret_cast<volatile uint32_t*>(p);
+    return s;
+}
+
+struct XRegs6 {
+    float4 lo[kPrepBlocks], hi[kPrepBlocks];
+};
+// lane = i*8 + s*4 + t handles the 8 consecutive elements 128(t/2) + 64s + 32(t%2) + 8i .. +7
+__device__ __forceinline__ uint32_t x_elem6(int lane) {
+    const int i = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
+    return 128 * (t >> 1) + 64 * sh + 32 * (t & 1) + 8 * i;
+}
+__device__ __forceinline__ void load_x6(XRegs6& r, const float* __restrict__ x, uint32_t K, int warp, int lane) {
+#pragma unroll
+    for (int b = 0; b < kPrepBlocks; ++b) {
+        const uint32_t blk = warp + b * kWarps;
+        if (blk < (K >> 8)) {
+            const float* xp = x + (size_t)blk * 256 + x_elem6(lane);
+            r.lo[b] = __ldg(reinterpret_cast<const float4*>(xp));
+            r.hi[b] = __ldg(reinterpret_cast<const float4*>(xp) + 1);
+        }
+    }
+}
+__device__ __forceinline__ void prep_x6(const Smem6& s, const XRegs6& r, uint32_t K, int warp, int lane) {
+    const int i = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
+#pragma unroll
+    for (int b = 0; b < kPrepBlocks; ++b) {
+        const uint32_t blk = warp + b * kWarps;
+        if (blk >= (K >> 8)) break;
+        const float4 lo = r.lo[b], hi = r.hi[b];
+        const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        float mx = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mx = fmaxf(mx, fabsf(v[e]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+        uint32_t E = (__float_as_uint(mx) >> 23) & 0xFFu;
+        E = E < 32u ? 32u : E;
+        const float scale = __uint_as_float((127u + 126u + kFracBits - E) << 23);
+        uint32_t d0[2] = {0, 0}, d1[2] = {0, 0}, d2[2] = {0, 0};
+        int sum = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int X = __float2int_rn(v[e] * scale);
+            sum += X;
+            d0[e >> 2] |= (uint32_t)((X >> 14) & 0xFF) << (8 * (e & 3));
+            d1[e >> 2] |= (uint32_t)((X >> 7) & 0x7F) << (8 * (e & 3));
+            d2[e >> 2] |= (uint32_t)(X & 0x7F) << (8 * (e & 3));
+        }
+        const uint32_t u = (blk * 8 + sh * 4 + i) * 2;
+        s.xf[(u + 0) * 4 + t] = make_uint4(d0[0], d0[1], d2[0], d2[1]);
+        s.xf[(u + 1) * 4 + t] = make_uint4(d1[0], d1[1], 0u, 0u);
+        // 16-element sub-block sums: lanes i and i^1 hold the two halves
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 8);
+        if ((i & 1) == 0) s.sx[blk * 16 + (x_elem6(lane) >> 4)] = sum;
+        if (lane == 0) s.xs[blk] = __uint_as_float((E + 1u - kFracBits) << 23);
+    }
+}
+
+// N consecutive 32-bit words starting `sh` bits into the aligned word at p (sh = 0 or 16)
+template <int N>
+__device__ __forceinline__ void lds_words(const uint32_t* p, uint32_t sh, uint32_t (&w)[N]) {
+    uint32_t prev = p[0];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        const uint32_t next = p[i + 1];
+        w[i] = __funnelshift_r(prev, next, sh);
+        prev = next;
+    }
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1) dmmv_q6k_warp_kernel(const WarpArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const Smem6 s = carve6(smem_raw, a.K);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3, h = t >> 1, c = t & 1;
+    const uint32_t bpr = a.K >> 8;
+    const uint64_t row_bytes = (uint64_t)bpr * 210;
+    const uint32_t tiles = (a.M + 15) / 16;
+    const uint32_t U = tiles * bpr, G = gridDim.x * kWarps;
+    const uint32_t me = blockIdx.x * kWarps + warp;
+    const uint32_t u0 = (uint32_t)part_begin(me, U, G), u1 = (uint32_t)part_begin(me + 1, U, G);
+    const uint32_t n = u1 - u0;
+    uint8_t* ring = s.ring + (size_t)warp * kRing6;
+    XRegs6 xr;
+    load_x6(xr, a.x, a.K, warp, lane);
+
+    uint32_t piece[kPiecesLane6];  // row | column << 8
+#pragma unroll
+    for (int i = 0; i < kPiecesLane6; ++i) {
+        const uint32_t p = i * 32 + lane;
+        const uint32_t r = p / kPieces6;
+        piece[i] = r | ((p - r * kPieces6) << 8);
+    }
+    uint32_t p_tile = u0 / bpr, p_blk = u0 % bpr;
+    auto request = [&](uint32_t slot) {
+        const uint32_t al = (p_blk * 210u) & ~15u;  // aligned start of the block's superset within the row
+        uint8_t* dst = ring + slot * kSlot6;
+        const uint32_t row0 = p_tile * 16;
+#pragma unroll
+        for (int i = 0; i < kPiecesLane6; ++i) {
+            const uint32_t r = piece[i] & 0xFFu, col = piece[i] >> 8;
+            if (al + col * 16 < (uint32_t)row_bytes) {  // rows are 16-byte aligned: a piece never crosses the row end
+                const uint32_t row = min(row0 + r, a.M - 1);
+                cp_async16(dst + r * kRow6 + col * 16, a.A[0] + (uint64_t)row * row_bytes + al + col * 16);
+            }
+        }
+        if (++p_blk == bpr) { p_blk = 0; ++p_tile; }
+    };
+#pragma unroll
+    for (int i = 0; i < kDepth; ++i) {
+        if ((uint32_t)i < n) request(i);
+        cp_async_commit();
+    }
+
+    if (tid < kZeroUnits) s.zeros[tid] = make_uint4(0u, 0u, 0u, 0u);
+    if (tid < kWarps) s.sflags[tid] = 0u;
+    prep_x6(s, xr, a.K, warp, lane);
+    __syncthreads();
+
+    uint32_t tile = u0 / bpr, blk = u0 % bpr;
+    float acc[2] = {0.f, 0.f};
+    const bool b_live = (g >> 1) == t;
+    const uint4* xu_live = s.xf + (g & 1) * 4 + t;
+    const uint4* xu_dead = s.zeros + (g >> 1) + 1;
+    const uint32_t shl = 4 - 2 * c, shr = 2 * c;  // qh bit pairs: low nibbles use bits 2c.., high nibbles 4+2c..
+    constexpr uint32_t kNib = 0x0F0F0F0Fu, kTop = 0x30303030u;
+
+    for (uint32_t it = 0; it < n; ++it) {
+        const uint32_t slot = it % kDepth;
+        cp_async_wait<kDepth - 1>();
+        __syncwarp();
+        const uint32_t o0 = (blk * 210u) & 15u, fs = (o0 & 3u) * 8u;
+        const uint8_t* sb = ring + slot * kSlot6 + (o0 & ~3u);
+        const uint4* xu = b_live ? xu_live + (size_t)blk * 64 : xu_dead;
+        // both rows share the B operand; accumulators: [row-pair quad] per sub-block (lo k=0,1; hi k=0,1)
+        int d01[4][4], d2[4][4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) d01[q][e] = d2[q][e] = 0;
+        const uint32_t* wA = reinterpret_cast<const uint32_t*>(sb + g * kRow6);
+        const uint32_t* wB = reinterpret_cast<const uint32_t*>(sb + (g + 8) * kRow6);
+        uint32_t qlA[8], qhA[8], qlB[8], qhB[8];
+        lds_words<8>(wA + 16 * h + 8 * c, fs, qlA);
+        lds_words<8>(wA + 32 + 8 * h, fs, qhA);
+        lds_words<8>(wB + 16 * h + 8 * c, fs, qlB);
+        lds_words<8>(wB + 32 + 8 * h, fs, qhB);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint4 bl = xu[i * 8], bh = xu[(4 + i) * 8];
+            uint32_t lo[4], hi[4];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const uint32_t la = qlA[2 * i + e], ha = qhA[2 * i + e], lb = qlB[2 * i + e], hb = qhB[2 * i + e];
+                lo[2 * e] = (la & kNib) | ((ha << shl) & kTop);
+                lo[2 * e + 1] = (lb & kNib) | ((hb << shl) & kTop);
+                hi[2 * e] = ((la >> 4) & kNib) | ((ha >> shr) & kTop);
+                hi[2 * e + 1] = ((lb >> 4) & kNib) | ((hb >> shr) & kTop);
+            }
+            // words 2i, 2i+1 = elements l = 8i .. 8i+7: sub-block half k = i/2
+            mma_u8s8(d01[i >> 1], lo[0], lo[1], lo[2], lo[3], bl.x, bl.y);
+            mma_u8s8(d2[i >> 1], lo[0], lo[1], lo[2], lo[3], bl.z, bl.w);
+            mma_u8s8(d01[2 + (i >> 1)], hi[0], hi[1], hi[2], hi[3], bh.x, bh.y);
+            mma_u8s8(d2[2 + (i >> 1)], hi[0], hi[1], hi[2], hi[3], bh.z, bh.w);
+        }
+        // scales: the 8 int8 of half h; this lane's four are bytes 2c, 2c+1 (low) and 4+2c, 5+2c (high)
+        uint32_t scA[2], scB[2], dA[1], dB[1];
+        lds_words<2>(wA + 48 + 2 * h, fs, scA);
+        lds_words<2>(wB + 48 + 2 * h, fs, scB);
+        lds_words<1>(wA + 52, fs, dA);
+        lds_words<1>(wB + 52, fs, dB);
+        // every lane has read the stage: refill it
+        __syncwarp();
+        if (it + kDepth < n) request(slot);
+        cp_async_commit();
+
+        const int* sx = s.sx + blk * 16 + 8 * h + 2 * c;  // sub-blocks 8h+2c+k (low), 8h+4+2c+k (high)
+        const int sx0 = sx[0], sx1 = sx[1], sx2 = sx[4], sx3 = sx[5];
+        const int sxs[4] = {sx0, sx1, sx2, sx3};
+        float sumA = 0.f, sumB = 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const int PA = (d01[q][0] << 14) + (d01[q][1] << 7) + d2[q][0] - 32 * sxs[q];
+            const int PB = (d01[q][2] << 14) + (d01[q][3] << 7) + d2[q][2] - 32 * sxs[q];
+            const uint32_t wa = scA[q >> 1] >> (16 * c + 8 * (q & 1)), wb = scB[q >> 1] >> (16 * c + 8 * (q & 1));
+            sumA += (float)(int8_t)(wa & 0xFFu) * (float)PA;
+            sumB += (float)(int8_t)(wb & 0xFFu) * (float)PB;
+        }
+        const float xs = s.xs[blk];
+        acc[0] += h2f(dA[0]) * xs * sumA;
+        acc[1] += h2f(dB[0]) * xs * sumB;
+
+        const uint32_t T = tile;
+        bool tile_done = false;
+        if (++blk == bpr) { blk = 0; ++tile; tile_done = true; }
+        if (tile_done || it + 1 == n) {
+            float v[1][2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float w = acc[r];
+                w += __shfl_xor_sync(0xFFFFFFFFu, w, 1);
+                w += __shfl_xor_sync(0xFFFFFFFFu, w, 2);
+                v[0][r] = w;
+                acc[r] = 0.f;
+            }
+            finish_tile<1, EPI>(a, s.spartial, s.sflags, v, T, bpr, u0, u1, U, G, me, warp, lane);
+        }
+    }
+}
+
+template <int EPI>
+cudaError_t launch_cfg6(const WarpArgs& a, cudaStream_t st, int sm_count) {
+    auto kern = dmmv_q6k_warp_kernel<EPI>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    const uint64_t U = (uint64_t)((a.M + 15) / 16) * (a.K >> 8);
+    uint64_t grid = (uint64_t)sm_count;
+    if (grid * kWarps > U) grid = U / kWarps;
+    if (grid * kWarps > kStreamMaxWorkers) grid = kStreamMaxWorkers / kWarps;
+    if (grid == 0) return cudaErrorInvalidConfiguration;
+    kern<<<(uint32_t)grid, kThreads, smem_bytes6(a.K), st>>>(a);
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+bool q6k_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a) {
+    if (type != T_Q6_K) return false;
+    if (mode != MODE_PLAIN && mode != MODE_SIGMOID_ACC) return false;
+    if (!a.scratch_partial || !a.scratch_flags || !a.status) return false;
+    const uint32_t bpr = a.K >> 8;
+    if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (bpr % 8u) != 0) return false;  // rows must start 16-byte aligned
+    if (smem_bytes6(a.K) > 227 * 1024 || bpr > (uint32_t)(kPrepBlocks * kWarps)) return false;
+    const uint64_t U = (uint64_t)((a.M + 15) / 16) * bpr;
+    if (U < kWarps || U > 0xFFFFFFFFull) return false;
+    return true;
+}
+
+cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t st, uint64_t* launches) {
+    WarpArgs wa;
+    wa.A[0] = a.A;
+    wa.A[1] = a.A;
+    wa.x = a.x;
+    wa.y = a.y;
+    wa.gate = a.gate;
+    wa.M = a.M;
+    wa.K = a.K;
+    wa.acc_mode = a.acc_mode;
+    wa.gpartial = a.scratch_partial;
+    wa.gflags = a.scratch_flags;
+    wa.status = a.status;
+    cudaError_t e = mode == MODE_PLAIN ? launch_cfg6<EPI_PLAIN>(wa, st, a.sm_count)
+                                       : launch_cfg6<EPI_SIGMOID_ACC>(wa, st, a.sm_count);
+    if (e == cudaSuccess && launches) ++*launches;
+    return e;
+}
+
+}  // namespace zc

@@ -50,6 +50,8 @@ constexpr size_t kStreamFlagBytes = (size_t)kStreamMaxWorkers * sizeof(uint32_t)
 // Warp-autonomous streaming (cp.async + tensor-core) matvec: eligibility and launch.
 bool warp_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a);
 cudaError_t launch_warp_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
+bool q6k_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a);
+cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
 
 // Returns cudaSuccess or the launch error; *launches is incremented per kernel.
 cudaError_t launch_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);

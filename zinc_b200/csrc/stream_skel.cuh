@@ -1,0 +1,161 @@
+// Shared skeleton of the warp-autonomous streaming matvec kernels: launch arguments, the
+// asynchronous-copy and int8 tensor-core primitives, the fused epilogues and the ordered
+// hand-off of split-K partial sums between workers.
+#pragma once
+
+#include "common.cuh"
+#include "stream_common.cuh"
+
+namespace zc {
+namespace {
+
+constexpr int kWarps = 16;                 // workers (warps) per CTA; one CTA per SM
+constexpr int kThreads = kWarps * 32;
+
+struct WarpArgs {
+    const uint8_t* A[2];
+    const float* x;
+    float* y;
+    const float* gate;
+    uint32_t M, K, acc_mode;
+    float* gpartial;     // [workers][32] partial sums published across CTAs
+    uint32_t* gflags;    // [workers] 0 = empty, 1 = published; the reader clears it
+    uint32_t* status;    // [0] error code, [1] site
+};
+
+
+__device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// D(16x8,s32) += A(16x32,s8,row) * B(32x8,s8,col)
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Same with unsigned A (quants that are stored with an offset, e.g. Q6_K's 0..63)
+__device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+enum { EPI_PLAIN = 0, EPI_GATE_UP = 1, EPI_SIGMOID_ACC = 2 };
+
+template <int NS, int EPI>
+__device__ __forceinline__ void write_row(const WarpArgs& a, uint32_t row, const float (&v)[NS]) {
+    if (row >= a.M) return;
+    if constexpr (EPI == EPI_GATE_UP) {
+        a.y[row] = (v[0] / (1.0f + expf(-v[0]))) * v[1];
+    } else if constexpr (EPI == EPI_SIGMOID_ACC) {
+        a.y[row] += (1.0f / (1.0f + expf(-__ldg(a.gate)))) * v[0];
+    } else {
+        a.y[row] = a.acc_mode ? a.y[row] + v[0] : v[0];
+    }
+}
+
+
+constexpr uint32_t kSpinLimit = 1u << 26;
+
+// Ends a tile for this warp. v[i][r]: sums of stream i for rows g (r = 0) and g+8 (r = 1), already
+// reduced over the four lanes of a row.
+template <int NS, int EPI>
+__device__ __forceinline__ void finish_tile(const WarpArgs& a, float* spartial, volatile uint32_t* sflags, float (&v)[NS][2], uint32_t T,
+                                            uint32_t upt_all, uint32_t u0, uint32_t u1, uint32_t U, uint32_t G,
+                                            uint32_t me, int warp, int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t first = T * upt_all, last = first + upt_all - 1;
+    if (u0 > first) {
+        // not the first contributor: publish the partial sums for the worker that owns `first`
+        const uint32_t fin = part_owner(first, U, G);
+        const bool same_cta = fin / kWarps == blockIdx.x;
+        float* dst = same_cta ? spartial + warp * 32 : a.gpartial + (size_t)me * 32;
+        if (t == 0) {
+#pragma unroll
+            for (int i = 0; i < NS; ++i) {
+                dst[i * 16 + g] = v[i][0];
+                dst[i * 16 + g + 8] = v[i][1];
+            }
+            if (same_cta) __threadfence_block(); else __threadfence();
+        }
+        __syncwarp();
+        if (lane == 0) {
+            if (same_cta) sflags[warp] = 1u;
+            else *reinterpret_cast<volatile uint32_t*>(a.gflags + me) = 1u;
+        }
+        return;
+    }
+    if (last >= u1) {
+        // first contributor of a tile that continues in later workers. They published early (the
+        // tile is the first thing they work on); wait for all flags at once, then let lane t of each
+        // row add parts t, t+4, ... so that the remote reads overlap. The order is fixed by lane
+        // index, not by timing.
+        const uint32_t cl = part_owner(last, U, G);
+        const uint32_t cnt = cl - me;  // contributors me+1 .. cl
+        for (uint32_t base = 0; base < cnt; base += 32) {
+            const uint32_t c = me + 1 + base + lane;
+            bool ready = c > cl;
+            const bool same_cta = c / kWarps == blockIdx.x;
+            volatile uint32_t* flag =
+                same_cta ? sflags + (c % kWarps) : reinterpret_cast<volatile uint32_t*>(a.gflags + min(c, cl));
+            uint32_t spins = 0;
+            while (!__all_sync(0xFFFFFFFFu, ready)) {
+                if (!ready) ready = *flag != 0u;
+                if (++spins > kSpinLimit) {
+                    if (lane == 0) { a.status[0] = 1; a.status[1] = 3; }
+                    break;
+                }
+            }
+        }
+        __threadfence();
+        float w[NS][2];
+#pragma unroll
+        for (int i = 0; i < NS; ++i) w[i][0] = w[i][1] = 0.f;
+        for (uint32_t c = me + 1 + t; c <= cl; c += 4) {
+            const bool same_cta = c / kWarps == blockIdx.x;
+            const float* src = same_cta ? spartial + (c % kWarps) * 32 : a.gpartial + (size_t)c * 32;
+#pragma unroll
+            for (int i = 0; i < NS; ++i) {
+                w[i][0] += same_cta ? src[i * 16 + g] : ld_cg_f32(src + i * 16 + g);
+                w[i][1] += same_cta ? src[i * 16 + g + 8] : ld_cg_f32(src + i * 16 + g + 8);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NS; ++i) {
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float q = w[i][r];
+                q += __shfl_xor_sync(0xFFFFFFFFu, q, 1);
+                q += __shfl_xor_sync(0xFFFFFFFFu, q, 2);
+                v[i][r] += q;
+            }
+        }
+        __syncwarp();
+        // every part has been read: clear the global flags for the next launch
+        for (uint32_t c = me + 1 + lane; c <= cl; c += 32)
+            if (c / kWarps != blockIdx.x) *reinterpret_cast<volatile uint32_t*>(a.gflags + c) = 0u;
+    }
+    if (t == 0) {
+        float r0[NS], r1[NS];
+#pragma unroll
+        for (int i = 0; i < NS; ++i) { r0[i] = v[i][0]; r1[i] = v[i][1]; }
+        write_row<NS, EPI>(a, T * 16 + g, r0);
+        write_row<NS, EPI>(a, T * 16 + g + 8, r1);
+    }
+}
+
+}  // namespace
+}  // namespace zc

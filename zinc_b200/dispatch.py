@@ -100,7 +100,11 @@ class Context:
             raise _ERRORS.get(rc, ZincError)(f"{name}: {msg}")
 
     def set_stream(self, stream: Optional[int]) -> None:
+        """Launch on the given cudaStream_t handle (0 / None = CUDA's default stream)."""
         self.call("zc_set_stream", C.c_void_p(stream or 0))
+
+    def use_own_stream(self) -> None:
+        self.call("zc_use_own_stream")
 
     @property
     def stream(self) -> int:
