@@ -35,7 +35,8 @@ constexpr int kPieces6 = 14;                // 16-byte pieces per row superset
 constexpr int kPiecesLane6 = (16 * kPieces6 + 31) / 32;  // 7
 constexpr int kZeroUnits = 72;
 constexpr int kFracBits = 20;
-constexpr int kPrepBlocks = 3;
+constexpr int kPrepBlocks = 6;
+constexpr size_t kTwoPerSm = 113 * 1024;
 
 struct Smem6 {
     uint4* xf;       // x digits in B-operand order: unit ((blk*8 + s*4 + i)*2 + p)*4 + t
@@ -47,7 +48,7 @@ struct Smem6 {
     volatile uint32_t* sflags;
 };
 
-__host__ __device__ inline size_t smem_bytes6(uint32_t K) {
+__host__ __device__ inline size_t smem_bytes6(uint32_t K, int kWarps) {
     size_t n = (size_t)K * 4 + (size_t)kZeroUnits * 16;
     n += (size_t)(K / 16) * 4 + (size_t)(K / 256) * 4;
     n = (n + 127) & ~size_t(127);
@@ -56,7 +57,7 @@ __host__ __device__ inline size_t smem_bytes6(uint32_t K) {
     return n + 128;
 }
 
-__device__ inline Smem6 carve6(uint8_t* base, uint32_t K) {
+__device__ inline Smem6 carve6(uint8_t* base, uint32_t K, int kWarps) {
     Smem6 s;
     uintptr_t p = (reinterpret_cast<uintptr_t>(base) + 127) & ~uintptr_t(127);
     s.xf = reinterpret_cast<uint4*>(p);
@@ -84,6 +85,7 @@ __device__ __forceinline__ uint32_t x_elem6(int lane) {
     const int i = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
     return 128 * (t >> 1) + 64 * sh + 32 * (t & 1) + 8 * i;
 }
+template <int kWarps>
 __device__ __forceinline__ void load_x6(XRegs6& r, const float* __restrict__ x, uint32_t K, int warp, int lane) {
 #pragma unroll
     for (int b = 0; b < kPrepBlocks; ++b) {
@@ -95,6 +97,7 @@ __device__ __forceinline__ void load_x6(XRegs6& r, const float* __restrict__ x, 
         }
     }
 }
+template <int kWarps>
 __device__ __forceinline__ void prep_x6(const Smem6& s, const XRegs6& r, uint32_t K, int warp, int lane) {
     const int i = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
 #pragma unroll
@@ -143,10 +146,11 @@ __device__ __forceinline__ void lds_words(const uint32_t* p, uint32_t sh, uint32
     }
 }
 
-template <int EPI>
-__global__ void __launch_bounds__(kThreads, 1) dmmv_q6k_warp_kernel(const WarpArgs a) {
+template <int EPI, int kWarps>
+__global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel(const WarpArgs a) {
     extern __shared__ uint8_t smem_raw[];
-    const Smem6 s = carve6(smem_raw, a.K);
+    pdl_launch_dependents();
+    const Smem6 s = carve6(smem_raw, a.K, kWarps);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3, h = t >> 1, c = t & 1;
     const uint32_t bpr = a.K >> 8;
@@ -157,8 +161,6 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q6k_warp_kernel(const WarpAr
     const uint32_t u0 = (uint32_t)part_begin(me, U, G), u1 = (uint32_t)part_begin(me + 1, U, G);
     const uint32_t n = u1 - u0;
     uint8_t* ring = s.ring + (size_t)warp * kRing6;
-    XRegs6 xr;
-    load_x6(xr, a.x, a.K, warp, lane);
 
     uint32_t piece[kPiecesLane6];  // row | column << 8
 #pragma unroll
@@ -182,15 +184,20 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q6k_warp_kernel(const WarpAr
         }
         if (++p_blk == bpr) { p_blk = 0; ++p_tile; }
     };
+    if (n) request(0);
+    cp_async_commit();
+    pdl_wait();
+    XRegs6 xr;
+    load_x6<kWarps>(xr, a.x, a.K, warp, lane);
 #pragma unroll
-    for (int i = 0; i < kDepth; ++i) {
+    for (int i = 1; i < kDepth; ++i) {
         if ((uint32_t)i < n) request(i);
         cp_async_commit();
     }
 
     if (tid < kZeroUnits) s.zeros[tid] = make_uint4(0u, 0u, 0u, 0u);
     if (tid < kWarps) s.sflags[tid] = 0u;
-    prep_x6(s, xr, a.K, warp, lane);
+    prep_x6<kWarps>(s, xr, a.K, warp, lane);
     __syncthreads();
 
     uint32_t tile = u0 / bpr, blk = u0 % bpr;
@@ -256,8 +263,8 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q6k_warp_kernel(const WarpAr
         float sumA = 0.f, sumB = 0.f;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            const int PA = (d01[q][0] << 14) + (d01[q][1] << 7) + d2[q][0] - 32 * sxs[q];
-            const int PB = (d01[q][2] << 14) + (d01[q][3] << 7) + d2[q][2] - 32 * sxs[q];
+            const int PA = d01[q][0] * 16384 + d01[q][1] * 128 + d2[q][0] - 32 * sxs[q];
+            const int PB = d01[q][2] * 16384 + d01[q][3] * 128 + d2[q][2] - 32 * sxs[q];
             const uint32_t wa = scA[q >> 1] >> (16 * c + 8 * (q & 1)), wb = scB[q >> 1] >> (16 * c + 8 * (q & 1));
             sumA += (float)(int8_t)(wa & 0xFFu) * (float)PA;
             sumB += (float)(int8_t)(wb & 0xFFu) * (float)PB;
@@ -279,27 +286,34 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q6k_warp_kernel(const WarpAr
                 v[0][r] = w;
                 acc[r] = 0.f;
             }
-            finish_tile<1, EPI>(a, s.spartial, s.sflags, v, T, bpr, u0, u1, U, G, me, warp, lane);
+            finish_tile<1, EPI, kWarps>(a, s.spartial, s.sflags, v, T, bpr, u0, u1, U, G, me, warp, lane);
         }
     }
 }
 
-template <int EPI>
-cudaError_t launch_cfg6(const WarpArgs& a, cudaStream_t st, int sm_count) {
-    auto kern = dmmv_q6k_warp_kernel<EPI>;
+template <int EPI, int kWarps>
+cudaError_t launch_w6(const WarpArgs& a, cudaStream_t st, int sm_count, size_t smem) {
+    auto kern = dmmv_q6k_warp_kernel<EPI, kWarps>;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kWarps == 8 ? (int)kTwoPerSm : 227 * 1024);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
     const uint64_t U = (uint64_t)((a.M + 15) / 16) * (a.K >> 8);
-    uint64_t grid = (uint64_t)sm_count;
+    uint64_t grid = (uint64_t)sm_count * (16 / kWarps);
     if (grid * kWarps > U) grid = U / kWarps;
     if (grid * kWarps > kStreamMaxWorkers) grid = kStreamMaxWorkers / kWarps;
     if (grid == 0) return cudaErrorInvalidConfiguration;
-    kern<<<(uint32_t)grid, kThreads, smem_bytes6(a.K), st>>>(a);
-    return cudaGetLastError();
+    return launch_pdl(kern, (uint32_t)grid, kWarps * 32, smem, st, a);
+}
+
+template <int EPI>
+cudaError_t launch_cfg6(const WarpArgs& a, cudaStream_t st, int sm_count) {
+    const size_t s8 = smem_bytes6(a.K, 8);
+    if (s8 <= kTwoPerSm) return launch_w6<EPI, 8>(a, st, sm_count, s8);
+    return launch_w6<EPI, 16>(a, st, sm_count, smem_bytes6(a.K, 16));
 }
 
 }  // namespace
@@ -310,9 +324,9 @@ bool q6k_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a) {
     if (!a.scratch_partial || !a.scratch_flags || !a.status) return false;
     const uint32_t bpr = a.K >> 8;
     if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (bpr % 8u) != 0) return false;  // rows must start 16-byte aligned
-    if (smem_bytes6(a.K) > 227 * 1024 || bpr > (uint32_t)(kPrepBlocks * kWarps)) return false;
+    if (smem_bytes6(a.K, 16) > 227 * 1024 || bpr > (uint32_t)(kPrepBlocks * 8)) return false;
     const uint64_t U = (uint64_t)((a.M + 15) / 16) * bpr;
-    if (U < kWarps || U > 0xFFFFFFFFull) return false;
+    if (U < 16 || U > 0xFFFFFFFFull) return false;
     return true;
 }
 

@@ -40,6 +40,7 @@ constexpr int kCB = 2;                     // super-blocks per row segment
 constexpr int kRowSeg = kCB * 144 + 16;    // 304: rows land 16 B apart mod 32 B -> conflict-free 128-bit reads
 constexpr int kSlotBytes = 16 * kRowSeg;
 constexpr int kWarpRing = kDepth * kSlotBytes;
+constexpr size_t kTwoPerSm = 113 * 1024;   // shared memory per CTA that still lets two CTAs share an SM
 constexpr int kZeroUnits = 72;             // zeros: B operand of the lanes whose columns are dead
 constexpr int kFracBits = 20;              // |X| <= 2^20
 constexpr int kPiecesPerRow = kCB * 9;     // 16-byte pieces of one row segment
@@ -56,7 +57,7 @@ struct Smem {
     volatile uint32_t* sflags;  // [kWarps]
 };
 
-__host__ __device__ inline size_t smem_bytes(uint32_t K) {
+__host__ __device__ inline size_t smem_bytes(uint32_t K, int kWarps) {
     size_t n = (size_t)K * 4 + (size_t)kZeroUnits * 16;
     n += (size_t)(K / 32) * 4 + (size_t)(K / 256) * 4;
     n = (n + 127) & ~size_t(127);
@@ -65,7 +66,7 @@ __host__ __device__ inline size_t smem_bytes(uint32_t K) {
     return n + 128;
 }
 
-__device__ inline Smem carve(uint8_t* base, uint32_t K) {
+__device__ inline Smem carve(uint8_t* base, uint32_t K, int kWarps) {
     Smem s;
     uintptr_t p = (reinterpret_cast<uintptr_t>(base) + 127) & ~uintptr_t(127);
     s.xf = reinterpret_cast<uint4*>(p);
@@ -96,10 +97,11 @@ __device__ inline Smem carve(uint8_t* base, uint32_t K) {
 //
 // The loads are issued before the weight prefetch (so they are not queued behind it) and
 // converted afterwards: kPrepBlocks super-blocks per warp cover K <= kPrepBlocks * kWarps * 256.
-constexpr int kPrepBlocks = 3;
+constexpr int kPrepBlocks = 6;  // x super-blocks per warp: K <= kPrepBlocks * kWarps * 256
 struct XRegs {
     float4 lo[kPrepBlocks], hi[kPrepBlocks];
 };
+template <int kWarps>
 __device__ __forceinline__ void load_x(XRegs& r, const float* __restrict__ x, uint32_t K, int warp, int lane) {
     const int j = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
 #pragma unroll
@@ -112,6 +114,7 @@ __device__ __forceinline__ void load_x(XRegs& r, const float* __restrict__ x, ui
         }
     }
 }
+template <int kWarps>
 __device__ __forceinline__ void prep_x(const Smem& s, const XRegs& r, uint32_t K, int warp, int lane) {
     const int j = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
 #pragma unroll
@@ -164,10 +167,11 @@ __device__ __forceinline__ void scales_mins_pair(uint32_t s0, uint32_t s1, uint3
 }
 
 
-template <int NS, int EPI>
-__global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpArgs a) {
+template <int NS, int EPI, int kWarps>
+__global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel(const WarpArgs a) {
     extern __shared__ uint8_t smem_raw[];
-    const Smem s = carve(smem_raw, a.K);
+    pdl_launch_dependents();
+    const Smem s = carve(smem_raw, a.K, kWarps);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const uint32_t bpr = a.K >> 8;
@@ -180,8 +184,6 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
     const uint32_t u0 = (uint32_t)part_begin(me, U, G), u1 = (uint32_t)part_begin(me + 1, U, G);
     const uint32_t n = u1 - u0;
     uint8_t* ring = s.ring + (size_t)warp * kWarpRing;
-    XRegs xr;
-    load_x(xr, a.x, a.K, warp, lane);  // ahead of the weight prefetch in the memory queues
 
     // ---- prefetch: coalesced 16-byte asynchronous copies into padded row segments ----
     // piece p = i*32 + lane of a unit covers row p / kPiecesPerRow, 16-byte column p % kPiecesPerRow,
@@ -194,17 +196,31 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
         piece[i] = r | ((p - r * kPiecesPerRow) << 8);
     }
     uint32_t p_tile = u0 / upt_all, p_strm = (u0 % upt_all) / upt, p_kc = (u0 % upt_all) % upt;
+    // per-lane source / destination offsets of its pieces (rows inside the matrix)
+    uint32_t src_off[kPiecesPerLane], dst_off[kPiecesPerLane];
+#pragma unroll
+    for (int i = 0; i < kPiecesPerLane; ++i) {
+        const uint32_t r = piece[i] & 0xFFu, c = piece[i] >> 8;
+        src_off[i] = r * (uint32_t)row_bytes + c * 16;
+        dst_off[i] = r * kRowSeg + c * 16;
+    }
     auto request = [&](uint32_t slot) {
         const uint32_t cols = min((uint32_t)kCB, bpr - p_kc * kCB) * 9;  // 16-byte columns in this segment
-        const uint8_t* src = a.A[p_strm] + (uint64_t)p_kc * (kCB * 144);
-        uint8_t* dst = ring + slot * kSlotBytes;
         const uint32_t row0 = p_tile * 16;
+        const uint8_t* src = a.A[p_strm] + (uint64_t)row0 * row_bytes + (uint64_t)p_kc * (kCB * 144);
+        uint8_t* dst = ring + slot * kSlotBytes;
+        if (row0 + 16 <= a.M && cols == kPiecesPerRow) {
 #pragma unroll
-        for (int i = 0; i < kPiecesPerLane; ++i) {
-            const uint32_t r = piece[i] & 0xFFu, c = piece[i] >> 8;
-            if (c < cols) {
-                const uint32_t row = min(row0 + r, a.M - 1);  // rows past M repeat the last row; never written
-                cp_async16(dst + r * kRowSeg + c * 16, src + (uint64_t)row * row_bytes + c * 16);
+            for (int i = 0; i < kPiecesPerLane; ++i) cp_async16(dst + dst_off[i], src + src_off[i]);
+        } else {
+            // last tile / last segment: rows past M repeat the last row (never written), short segment
+#pragma unroll
+            for (int i = 0; i < kPiecesPerLane; ++i) {
+                const uint32_t r = piece[i] & 0xFFu, c = piece[i] >> 8;
+                if (c < cols) {
+                    const uint32_t row = min(row0 + r, a.M - 1);
+                    cp_async16(dst + dst_off[i], src + (uint64_t)(row - row0) * row_bytes + c * 16);
+                }
             }
         }
         if (++p_kc == upt) {
@@ -212,8 +228,15 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
             if (++p_strm == NS) { p_strm = 0; ++p_tile; }
         }
     };
+    // weights never depend on the previous kernel: start streaming them, then wait for it, then
+    // fetch x (ahead of the rest of the prefetch in the memory queues)
+    if (n) request(0);
+    cp_async_commit();
+    pdl_wait();
+    XRegs xr;
+    load_x<kWarps>(xr, a.x, a.K, warp, lane);
 #pragma unroll
-    for (int i = 0; i < kDepth; ++i) {
+    for (int i = 1; i < kDepth; ++i) {
         if ((uint32_t)i < n) request(i);
         cp_async_commit();
     }
@@ -221,7 +244,7 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
     // ---- activation vector -> B operand layout (all warps), zero region, flags ----
     if (tid < kZeroUnits) s.zeros[tid] = make_uint4(0u, 0u, 0u, 0u);
     if (tid < kWarps) s.sflags[tid] = 0u;
-    prep_x(s, xr, a.K, warp, lane);
+    prep_x<kWarps>(s, xr, a.K, warp, lane);
     __syncthreads();
 
     // ---- consume ----
@@ -265,10 +288,10 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
                 mma_s8(hi2, h0, h1, h2, h3, bh.z, bh.w);
             }
             // P = D0 * 2^14 + D1 * 2^7 + D2, exact in s32 (|P| < 2^31 for 5-bit quants and below)
-            const float PloA = (float)((lo01[0] << 14) + (lo01[1] << 7) + lo2[0]);
-            const float PloB = (float)((lo01[2] << 14) + (lo01[3] << 7) + lo2[2]);
-            const float PhiA = (float)((hi01[0] << 14) + (hi01[1] << 7) + hi2[0]);
-            const float PhiB = (float)((hi01[2] << 14) + (hi01[3] << 7) + hi2[2]);
+            const float PloA = (float)(lo01[0] * 16384 + lo01[1] * 128 + lo2[0]);
+            const float PloB = (float)(lo01[2] * 16384 + lo01[3] * 128 + lo2[2]);
+            const float PhiA = (float)(hi01[0] * 16384 + hi01[1] * 128 + hi2[0]);
+            const float PhiB = (float)(hi01[2] * 16384 + hi01[3] * 128 + hi2[2]);
             uint32_t scA, mnA, scB, mnB;
             scales_mins_pair(hA.y, hA.z, hA.w, t, scA, mnA);
             scales_mins_pair(hB.y, hB.z, hB.w, t, scB, mnB);
@@ -311,28 +334,34 @@ __global__ void __launch_bounds__(kThreads, 1) dmmv_q4k_warp_kernel(const WarpAr
                     acc1[r] = 0.f;
                 }
             }
-            finish_tile<NS, EPI>(a, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
+            finish_tile<NS, EPI, kWarps>(a, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
         }
     }
 }
 
-template <int NS, int EPI>
-cudaError_t launch_cfg(const WarpArgs& a, cudaStream_t st, int sm_count) {
-    auto kern = dmmv_q4k_warp_kernel<NS, EPI>;
+template <int NS, int EPI, int kWarps>
+cudaError_t launch_w(const WarpArgs& a, cudaStream_t st, int sm_count, size_t smem) {
+    auto kern = dmmv_q4k_warp_kernel<NS, EPI, kWarps>;
     static bool attr_set = false;
-    const size_t smem = smem_bytes(a.K);
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             kWarps == 8 ? (int)kTwoPerSm : 227 * 1024);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
     const uint64_t U = (uint64_t)((a.M + 15) / 16) * (((a.K >> 8) + kCB - 1) / kCB) * NS;
-    uint64_t grid = (uint64_t)sm_count;  // one CTA per SM, kWarps workers each
+    uint64_t grid = (uint64_t)sm_count * (16 / kWarps);  // 16 worker warps per SM
     if (grid * kWarps > U) grid = U / kWarps;
     if (grid * kWarps > kStreamMaxWorkers) grid = kStreamMaxWorkers / kWarps;
     if (grid == 0) return cudaErrorInvalidConfiguration;
-    kern<<<(uint32_t)grid, kThreads, smem, st>>>(a);
-    return cudaGetLastError();
+    return launch_pdl(kern, (uint32_t)grid, kWarps * 32, smem, st, a);
+}
+
+template <int NS, int EPI>
+cudaError_t launch_cfg(const WarpArgs& a, cudaStream_t st, int sm_count) {
+    const size_t s8 = smem_bytes(a.K, 8);
+    if (s8 <= kTwoPerSm) return launch_w<NS, EPI, 8>(a, st, sm_count, s8);  // two CTAs per SM
+    return launch_w<NS, EPI, 16>(a, st, sm_count, smem_bytes(a.K, 16));
 }
 
 }  // namespace
@@ -342,10 +371,10 @@ bool warp_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a) {
     if (mode != MODE_PLAIN && mode != MODE_GATE_UP_SWIGLU && mode != MODE_SIGMOID_ACC) return false;
     if (!a.scratch_partial || !a.scratch_flags || !a.status) return false;
     if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (a.A2 && (reinterpret_cast<uintptr_t>(a.A2) & 15u))) return false;
-    if (smem_bytes(a.K) > 227 * 1024 || (a.K >> 8) > (uint32_t)(kPrepBlocks * kWarps)) return false;
+    if (smem_bytes(a.K, 16) > 227 * 1024 || (a.K >> 8) > (uint32_t)(kPrepBlocks * 8)) return false;
     const int ns = mode == MODE_GATE_UP_SWIGLU ? 2 : 1;
     const uint64_t U = (uint64_t)((a.M + 15) / 16) * (((a.K >> 8) + kCB - 1) / kCB) * ns;
-    if (U < kWarps || U > 0xFFFFFFFFull) return false;
+    if (U < 16 || U > 0xFFFFFFFFull) return false;
     return true;
 }
 

@@ -9,8 +9,11 @@
 namespace zc {
 namespace {
 
-constexpr int kWarps = 16;                 // workers (warps) per CTA; one CTA per SM
-constexpr int kThreads = kWarps * 32;
+// Programmatic dependent launch: let the next kernel of the stream start its prologue while this
+// one runs, and wait for the previous kernel's results before touching anything it may have
+// written. Both are no-ops for kernels launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 struct WarpArgs {
     const uint8_t* A[2];
@@ -72,7 +75,7 @@ constexpr uint32_t kSpinLimit = 1u << 26;
 
 // Ends a tile for this warp. v[i][r]: sums of stream i for rows g (r = 0) and g+8 (r = 1), already
 // reduced over the four lanes of a row.
-template <int NS, int EPI>
+template <int NS, int EPI, int kWarps>
 __device__ __forceinline__ void finish_tile(const WarpArgs& a, float* spartial, volatile uint32_t* sflags, float (&v)[NS][2], uint32_t T,
                                             uint32_t upt_all, uint32_t u0, uint32_t u1, uint32_t U, uint32_t G,
                                             uint32_t me, int warp, int lane) {
@@ -155,6 +158,24 @@ __device__ __forceinline__ void finish_tile(const WarpArgs& a, float* spartial, 
         write_row<NS, EPI>(a, T * 16 + g, r0);
         write_row<NS, EPI>(a, T * 16 + g + 8, r1);
     }
+}
+
+// Launch with programmatic stream serialization: the kernel may begin while its predecessor
+// in the stream is still running and synchronises on it with pdl_wait().
+template <typename Kern>
+inline cudaError_t launch_pdl(Kern kern, uint32_t grid, uint32_t block, size_t smem, cudaStream_t st,
+                              const WarpArgs& a) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(block, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, a);
 }
 
 }  // namespace
