@@ -50,12 +50,17 @@ def measured_peaks():
 
 
 def ncu_traffic(kernel_key: str):
-    """DRAM bytes per launch of the dominant kernel from the committed ncu capture, or None."""
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary
+    (a line `traffic_bytes <key> <bytes>` in profiles/dmmv_q4k_warp_kernel_gate_up.txt), or None."""
     try:
-        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
-            return json.load(f).get(kernel_key)
+        with open(os.path.join(ROOT, "profiles", "dmmv_q4k_warp_kernel_gate_up.txt")) as f:
+            for line in f:
+                w = line.split()
+                if len(w) == 3 and w[0] == "traffic_bytes" and w[1] == kernel_key:
+                    return float(w[2])
     except Exception:
-        return None
+        pass
+    return None
 
 
 class ClockSampler:
