@@ -304,6 +304,37 @@ int32_t zc_dequant_rows(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_si
                         void* out, uint64_t out_size,
                         uint64_t first_row, uint32_t n_rows, uint32_t K, uint64_t a_offset);
 
+/* ---- matvec without a context and without any allocation ----------------------------------------
+ * No counterpart in the reference (its dispatch layer always owns descriptor pools and buffers).
+ * The streaming Q4_K matvec of zc_dmmv, y (+)= W x, with its split-K scratch in a __device__
+ * array that is part of the library image (540672 bytes: 4096 worker warps x 32 partial sums
+ * plus one flag word each) instead of scratch a context allocated. For hosts that cannot let
+ * the library allocate: all device memory already belongs to the host's own arena, or an
+ * allocation would synchronise the device in the middle of its decode loop. Neither this call
+ * nor its set-up allocates memory of any kind.
+ *
+ * Uses the calling thread's current device; `cuda_stream` (NULL = default stream), A, x, y and
+ * status_words must belong to it. Arguments as zc_dmmv for type Q4_K. Limits: K a multiple of
+ * 256 and at most 12288; at least 16 (16-row tile x 512-column segment) units, i.e. matrices
+ * from about 64 x 1024 up; W + a_offset and x + x_offset 16-byte aligned. Anything outside is
+ * refused with ZC_ERR_INVALID_ARG and a message in err_buf (may be NULL): use zc_dmmv there.
+ * status_words: two u32 words the device can write (device or mapped host memory), zero before
+ * the call; a bounded wait that gave up stores {1, site} there, the result is then invalid and
+ * the entry point must not be used again on that device.
+ *
+ * The first call on each device does the set-up (symbol address, SM count, one synchronous
+ * clear of the flag words): make it before any stream capture starts on that device.
+ * The scratch is shared by all calls on a device: calls ordered on one stream are safe; calls
+ * whose kernels may overlap (different streams, unordered threads) race and give wrong results. */
+int32_t zc_dmmv_q4k_static_scratch(void* cuda_stream,
+                                   const void* A, uint64_t a_size,
+                                   const void* x, uint64_t x_size,
+                                   void* y, uint64_t y_size,
+                                   uint32_t M, uint32_t K,
+                                   uint64_t a_offset, uint64_t x_offset, uint64_t y_offset,
+                                   uint32_t acc_mode, uint32_t* status_words,
+                                   char* err_buf, uint64_t err_cap);
+
 #ifdef __cplusplus
 }
 #endif

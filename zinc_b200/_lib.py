@@ -66,7 +66,7 @@ _OPS = {
 EXPORTS = sorted(list(_OPS) + [
     "zc_init", "zc_get_stream", "zc_last_error", "zc_status_string", "zc_launch_count",
     "zc_block_size", "zc_bytes_per_block", "zc_tensor_size_bytes", "zc_expert_slice_bytes",
-    "zc_dmmv_supported", "zc_moe_dmmv_supported",
+    "zc_dmmv_supported", "zc_moe_dmmv_supported", "zc_dmmv_q4k_static_scratch",
 ])
 
 _lib = None
@@ -106,5 +106,8 @@ def lib() -> C.CDLL:
         L.zc_dmmv_supported.argtypes = [_u32]
         L.zc_moe_dmmv_supported.restype = _i32
         L.zc_moe_dmmv_supported.argtypes = [_u32]
+        L.zc_dmmv_q4k_static_scratch.restype = _i32
+        L.zc_dmmv_q4k_static_scratch.argtypes = [_vp, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u64, _u64,
+                                                 _u32, _vp, C.c_char_p, _u64]
         _lib = L
     return _lib
