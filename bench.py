@@ -197,8 +197,8 @@ def cpu_baseline_leg(torch, step, budget_s=12.0):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=400)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="zinc_b200", choices=["zinc_b200", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug; invalidates the number)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -1,0 +1,108 @@
+"""Tensor-parallel host logic on two CPU ranks (gloo): each rank cuts its shard from the same GGUF
+tensor with zinc_b200.shard, the oracle stands in for the device matvec, and the collectives the
+decode step uses (all-gather for row shards, all-reduce for K shards, the FFN pairing
+gate/up row-sharded -> local SwiGLU -> down K-sharded) must reproduce the single-rank result."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, q):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+
+    import zinc_b200 as zb
+    from oracle import oracle as zo
+    from zinc_b200 import shard, synth
+
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        res = {}
+        hidden, ffn = 512, 1024
+        g = synth.rng(300, 0)  # the same stream on every rank: the "file" all ranks read
+        wg = synth.quant_matrix(g, zb.Q4_K, ffn, hidden)
+        wu = synth.quant_matrix(g, zb.Q4_K, ffn, hidden)
+        wd = synth.quant_matrix(g, zb.Q6_K, hidden, ffn)
+        x = synth.activations(g, hidden)
+        # single-rank result
+        act_full = zo.swiglu(zo.dmmv_f64(wg, zb.Q4_K, ffn, hidden, x).astype(np.float32),
+                             zo.dmmv_f64(wu, zb.Q4_K, ffn, hidden, x).astype(np.float32))
+        y_full = zo.dmmv_f64(wd, zb.Q6_K, hidden, ffn, act_full)
+
+        # row shard + all-gather
+        p = shard.plan("row", ffn, hidden, zb.Q4_K, rank, world)
+        gl = zo.dmmv_f64(shard.row_shard(wg, zb.Q4_K, ffn, hidden, rank, world), zb.Q4_K, p.M, p.K, x)
+        parts = [torch.zeros(p.M, dtype=torch.float64) for _ in range(world)]
+        dist.all_gather(parts, torch.from_numpy(gl))
+        res["row_gather"] = float(np.abs(torch.cat(parts).numpy() - zo.dmmv_f64(wg, zb.Q4_K, ffn, hidden, x)).max())
+
+        # FFN pairing: local SwiGLU on the local rows, down K-sharded over the same slice, one all-reduce
+        ul = zo.dmmv_f64(shard.row_shard(wu, zb.Q4_K, ffn, hidden, rank, world), zb.Q4_K, p.M, p.K, x)
+        act_local = zo.swiglu(gl.astype(np.float32), ul.astype(np.float32))
+        pk = shard.plan("k", hidden, ffn, zb.Q6_K, rank, world)
+        assert (pk.x_begin, pk.K) == (p.y_begin, p.M)  # the K slice of down is this rank's gate/up row slice
+        yl = zo.dmmv_f64(shard.k_shard(wd, zb.Q6_K, hidden, ffn, rank, world), zb.Q6_K, pk.M, pk.K, act_local)
+        t = torch.from_numpy(yl.copy())
+        dist.all_reduce(t)
+        res["ffn_pair"] = float(np.abs(t.numpy() - y_full).max() / np.abs(y_full).max())
+
+        # refusals
+        for fn, args in ((shard.row_range, (5, rank, world)), (shard.k_range, (zb.Q6_K, 768, rank, world))):
+            try:
+                fn(*args)
+                res["refusal"] = False
+            except ValueError:
+                res.setdefault("refusal", True)
+        q.put((rank, res))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(180)
+def test_two_rank_tensor_parallel_ffn():
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = dict(q.get(timeout=150) for _ in procs)
+    for p in procs:
+        p.join(30)
+        assert p.exitcode == 0
+    for r in range(2):
+        assert out[r]["row_gather"] == 0.0
+        assert out[r]["ffn_pair"] <= 1e-12
+        assert out[r]["refusal"] is True
+
+
+def test_shards_are_byte_ranges():
+    sys.path.insert(0, ROOT)
+    import zinc_b200 as zb
+    from zinc_b200 import shard, synth
+
+    g = synth.rng(301, 0)
+    M, K = 12, 1024
+    w = synth.quant_matrix(g, zb.Q5_K, M, K)
+    rb = zb.row_bytes(zb.Q5_K, K)
+    flat = w.reshape(-1)
+    for world in (1, 2, 4):
+        got = np.concatenate([shard.row_shard(w, zb.Q5_K, M, K, r, world) for r in range(world)])
+        assert np.array_equal(got, flat)
+        ks = [shard.k_shard(w, zb.Q5_K, M, K, r, world).reshape(M, -1) for r in range(world)]
+        assert np.array_equal(np.concatenate(ks, axis=1).reshape(-1), flat)
+        assert all(k.shape[1] == rb // world for k in ks)
