@@ -378,8 +378,21 @@ def main():
         }
         print(json.dumps(out), flush=True)
     if dist is not None:
+        # A captured graph holds references on the NCCL communicator, and destroying the communicator
+        # waits for them: release the graph first. A timer ends the process if teardown still stalls
+        # (the result line is already printed and flushed).
+        import threading
+
+        killer = threading.Timer(30.0, lambda: os._exit(0))
+        killer.daemon = True
+        killer.start()
+        torch.cuda.synchronize()
+        graph.reset()
+        del graph
         dist.barrier()
+        torch.cuda.synchronize()
         dist.destroy_process_group()
+        killer.cancel()
     return 0
 
 

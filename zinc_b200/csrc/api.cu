@@ -400,7 +400,7 @@ int32_t zc_dmmv_batch(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size
     // (Y[c][M] is D column-major with stride M, X[c][K] is B with stride K).
     if (num_cols >= 16)
         e = launch_mul_mm(type, u8(A, a_offset), f32p(X, x_offset), f32m(Y, y_offset), M, num_cols, K, K, M, false,
-                          ctx->stream, &ctx->launches);
+                          ctx->status_dev, ctx->stream, &ctx->launches);
     else
         e = cudaErrorNotSupported;
     if (e == cudaErrorNotSupported)
@@ -424,7 +424,7 @@ int32_t zc_mul_mm(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, co
     ZC_TRY(check_vec(ctx, fn, "D", D, d_size, d_offset * 4, ((uint64_t)(N - 1) * stride_d + M) * 4, 4));
     const void* Bp = static_cast<const uint8_t*>(B) + b_offset * esz;
     cudaError_t e = launch_mul_mm(type, u8(A, a_offset), Bp, f32m(D, d_offset * 4), M, N, K, stride_b, stride_d,
-                                  act_type == ZC_BF16, ctx->stream, &ctx->launches);
+                                  act_type == ZC_BF16, ctx->status_dev, ctx->stream, &ctx->launches);
     if (e == cudaErrorNotSupported)
         e = launch_mul_mm_simple(type, u8(A, a_offset), Bp, f32m(D, d_offset * 4), M, N, K, stride_b, stride_d,
                                  act_type == ZC_BF16, ctx->stream, &ctx->launches);

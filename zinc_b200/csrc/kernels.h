@@ -90,7 +90,7 @@ cudaError_t launch_moe_route_scatter(const uint32_t* routing, const float* src, 
 // act_bf16: B holds bf16 (else f32). Returns cudaErrorNotSupported for types
 // without a tile dequantiser.
 cudaError_t launch_mul_mm(uint32_t type, const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N,
-                          uint32_t K, uint32_t stride_b, uint32_t stride_d, bool act_bf16, cudaStream_t s,
-                          uint64_t* launches);
+                          uint32_t K, uint32_t stride_b, uint32_t stride_d, bool act_bf16, uint32_t* status,
+                          cudaStream_t s, uint64_t* launches);
 
 }  // namespace zc
