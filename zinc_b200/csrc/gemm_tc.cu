@@ -5,14 +5,18 @@
 //   X  bf16 activations [N][stride_b], fetched by TMA (cp.async.bulk.tensor, 128-byte swizzle)
 //   D  f32 [N][stride_d]; accumulators live in tensor memory and are read back with tcgen05.ld
 //
-// One CTA computes a 128-row x BN-token tile. Warp roles (10 warps):
-//   warp 0      allocates tensor memory; lane 0 issues tcgen05.mma and the commits
-//   warp 1      lane 0 issues the TMA loads of X
-//   warps 2-5   dequantise the even 64-column groups (one thread per row), then run the epilogue
-//   warps 6-9   dequantise the odd 64-column groups
-// Four shared-memory stages of 64 columns; every wait on an mbarrier is bounded and a wait that
-// gives up records {1, site} in the status words, raises a CTA-wide flag and lets every role fall
-// through to the common exit, where tensor memory is released.
+// One CTA computes a 128-row x (NACC x BN)-token tile: a dequantised weight stage is used for
+// NACC accumulators of BN tokens each, so with 512 tokens per tile every weight is unpacked once
+// per 512 tokens and tensor memory is fully used. Warp roles (19 warps):
+//   warp 0       allocates tensor memory; lane 0 issues tcgen05.mma and the commits
+//   warp 1       lane 0 issues the TMA loads of X
+//   warp 2       lane 0 issues the TMA loads of the raw weight blocks (128 rows x 144 bytes per box)
+//   warps 3-18   dequantise: set j (4 warps, one thread per row) owns 64-column group j of every
+//                256-column block, i.e. stage j of the bf16 weight ring; warps 3-6 also run the epilogue
+// Rings: 3 raw-block slots of 18 KB, 4 bf16 weight stages of 16 KB, 3 (BN = 256) or 6 (BN = 128)
+// activation slots of BN x 64 bf16. Every wait on an mbarrier
+// is bounded; a wait that gives up records {1, site} in the status words, raises a CTA-wide flag
+// and lets every role fall through to the common exit, where tensor memory is released.
 //
 // Replaces the reference's mul_mm_q4k.comp / gemm_q4k.metal tile kernels
 // (src/compute/dmmv.zig:1045 recordMulMmQ4K).
@@ -30,23 +34,31 @@ namespace {
 
 constexpr int kBM = 128;      // weight rows per tile (= TMEM lanes)
 constexpr int kBK = 64;       // columns per stage: 128 bytes of bf16, one swizzle row
-constexpr int kStages = 4;
-constexpr int kThreads = 320;
-constexpr uint32_t kABytes = kBM * kBK * 2;  // 16 KB
+constexpr int kAStages = 4;   // one per 64-column group of a 256-column block
+constexpr int kWSlots = 3;    // raw Q4_K blocks: 128 rows x 144 bytes
+constexpr int kCtlWarps = 3;
+constexpr int kThreads = kCtlWarps * 32 + 4 * 128;
+constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB
+constexpr uint32_t kWBytes = kBM * 144;       // 18 KB
 
 template <int BN>
 struct Tile {
+    static constexpr int kBSlots = BN == 256 ? 3 : 6;
     static constexpr uint32_t kBBytes = BN * kBK * 2;
-    static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-    static constexpr uint32_t kBarOffset = kStages * kStageBytes;
+    static constexpr uint32_t kWOffset = kAStages * kABytes;
+    static constexpr uint32_t kBOffset = kWOffset + kWSlots * kWBytes;
+    static constexpr uint32_t kBarOffset = kBOffset + kBSlots * kBBytes;
     static constexpr uint32_t kSmemBytes = kBarOffset + 256 + 1024;  // barriers + alignment slack
 };
 
-// Barrier block that follows the stages.
+// Barrier block that follows the rings.
 struct Bars {
-    uint64_t full_a[kStages];
-    uint64_t full_b[kStages];
-    uint64_t empty[kStages];
+    uint64_t full_a[kAStages];
+    uint64_t empty_a[kAStages];
+    uint64_t full_w[kWSlots];
+    uint64_t empty_w[kWSlots];
+    uint64_t full_b[6];
+    uint64_t empty_b[6];
     uint64_t accum;
     uint32_t tmem_base;
     volatile uint32_t failed;
@@ -91,10 +103,13 @@ __host__ __device__ constexpr uint32_t instr_desc() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
+// Bounded wait. kSleep: back off between polls (every role but the tensor-core issuer has slack).
+template <bool kSleep = true>
 __device__ __forceinline__ bool wait_or_fail(uint64_t* bar, uint32_t parity, Bars* bars, uint32_t* status,
                                              uint32_t site) {
     for (uint32_t i = 0; i < kWaitLimit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
+        if (kSleep) __nanosleep(64);
         if ((i & 63u) == 63u && bars->failed) return false;
     }
     bars->failed = 1;
@@ -109,22 +124,24 @@ __device__ __forceinline__ uint32_t bf2_bits(__nv_bfloat162 v) { return *reinter
 __device__ __forceinline__ __nv_bfloat162 bits_bf2(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
 
 // Four weights (the low nibbles of bytes 0..3 of `nib`, already masked to 0x0F0F0F0F) -> two bf16x2
-// words: (128 + q) built by byte permutation (exact in bf16), minus 128, times d*sc, minus dmin*m.
-__device__ __forceinline__ void deq4(uint32_t nib, __nv_bfloat162 dsc, __nv_bfloat162 ndm, uint32_t& o0,
+// words. (128 + q) is built by byte permutation (exact in bf16) and 136 subtracted, which leaves
+// q - 8 exactly; the weight d*sc*q - dmin*m is then formed as (q - 8) * dsc + c with
+// c = 8*d*sc - dmin*m, so that the bf16 rounding of dsc acts on a term of at most 8*dsc.
+__device__ __forceinline__ void deq4(uint32_t nib, __nv_bfloat162 dsc, __nv_bfloat162 c, uint32_t& o0,
                                      uint32_t& o1) {
-    const __nv_bfloat162 k128 = bits_bf2(0x43004300u);
+    const __nv_bfloat162 k136 = bits_bf2(0x43084308u);
     const uint32_t p0 = __byte_perm(nib, 0x43434343u, 0x4140);
     const uint32_t p1 = __byte_perm(nib, 0x43434343u, 0x4342);
-    o0 = bf2_bits(__hfma2(__hsub2(bits_bf2(p0), k128), dsc, ndm));
-    o1 = bf2_bits(__hfma2(__hsub2(bits_bf2(p1), k128), dsc, ndm));
+    o0 = bf2_bits(__hfma2(__hsub2(bits_bf2(p0), k136), dsc, c));
+    o1 = bf2_bits(__hfma2(__hsub2(bits_bf2(p1), k136), dsc, c));
 }
 
 // One 64-column group of a Q4_K row: 32 bytes of nibbles -> 8 chunks of 8 bf16 written to the
 // swizzled row `row` of the stage at `a_stage`.
 __device__ __forceinline__ void dequant_group_q4k(const uint4& q0, const uint4& q1, float d_sc_lo, float dm_lo,
                                                   float d_sc_hi, float dm_hi, uint8_t* a_stage, int row) {
-    const __nv_bfloat162 s_lo = __float2bfloat162_rn(d_sc_lo), m_lo = __float2bfloat162_rn(-dm_lo);
-    const __nv_bfloat162 s_hi = __float2bfloat162_rn(d_sc_hi), m_hi = __float2bfloat162_rn(-dm_hi);
+    const __nv_bfloat162 s_lo = __float2bfloat162_rn(d_sc_lo), m_lo = __float2bfloat162_rn(8.f * d_sc_lo - dm_lo);
+    const __nv_bfloat162 s_hi = __float2bfloat162_rn(d_sc_hi), m_hi = __float2bfloat162_rn(8.f * d_sc_hi - dm_hi);
     const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
     uint8_t* rowp = a_stage + row * 128;
     const int sw = row & 7;
@@ -148,21 +165,34 @@ struct GemmArgs {
     uint32_t* status;
 };
 
-template <int BN>
+template <int BN, int NACC>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g) {
+gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_w,
+                   const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // swizzle atoms: 1024-byte aligned
+    uint8_t* smem_b = smem + Tile<BN>::kBOffset;
+    uint8_t* smem_w = smem + Tile<BN>::kWOffset;
+    constexpr int kBSlots = Tile<BN>::kBSlots;
     Bars* bars = reinterpret_cast<Bars*>(smem + Tile<BN>::kBarOffset);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t m0 = blockIdx.x * kBM, n0 = blockIdx.y * BN;
+    const uint32_t m0 = blockIdx.x * kBM, n0 = blockIdx.y * (BN * NACC);
     const int n_it = g.K / kBK;
+    // accumulators of this tile that hold at least one real token
+    const int nacc = min(NACC, (int)((g.N - n0 + BN - 1) / BN));
 
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kAStages; ++s) {
             mbar_init(&bars->full_a[s], 4);  // one arrival per producer warp of the owning set
+            mbar_init(&bars->empty_a[s], 1);
+        }
+        for (int s = 0; s < kBSlots; ++s) {
             mbar_init(&bars->full_b[s], 1);
-            mbar_init(&bars->empty[s], 1);
+            mbar_init(&bars->empty_b[s], 1);
+        }
+        for (int s = 0; s < kWSlots; ++s) {
+            mbar_init(&bars->full_w[s], 1);
+            mbar_init(&bars->empty_w[s], 16);  // one arrival per producer warp
         }
         mbar_init(&bars->accum, 1);
         bars->failed = 0;
@@ -171,7 +201,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g)
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(&bars->tmem_base)),
-                     "r"((uint32_t)BN)
+                     "r"((uint32_t)(BN * NACC))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -183,88 +213,106 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g)
     if (warp == 0) {
         if (lane == 0) {  // ---- MMA issuer ----
             constexpr uint32_t idesc = instr_desc<BN>();
+            int sb = 0;
+            uint32_t pb = 0;
             bool ok = true;
             for (int it = 0; it < n_it && ok; ++it) {
-                const int s = it % kStages;
-                const uint32_t ph = (it / kStages) & 1;
-                ok = wait_or_fail(&bars->full_a[s], ph, bars, g.status, 101) &&
-                     wait_or_fail(&bars->full_b[s], ph, bars, g.status, 102);
-                if (!ok) break;
-                tc_fence_after();
-                const uint64_t da = smem_desc(smem_u32(smem + s * Tile<BN>::kStageBytes));
-                const uint64_t db = smem_desc(smem_u32(smem + s * Tile<BN>::kStageBytes + kABytes));
+                const int sa = it & 3;
+                ok = wait_or_fail<false>(&bars->full_a[sa], (it >> 2) & 1, bars, g.status, 101);
+                const uint64_t da = smem_desc(smem_u32(smem + sa * kABytes));
+                for (int acc = 0; acc < nacc && ok; ++acc) {
+                    ok = wait_or_fail<false>(&bars->full_b[sb], pb, bars, g.status, 102);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t db = smem_desc(smem_u32(smem_b + sb * Tile<BN>::kBBytes));
 #pragma unroll
-                for (int k = 0; k < kBK / 16; ++k)  // 16 columns = 32 bytes per instruction
-                    umma_bf16(tmem, da + 2 * k, db + 2 * k, idesc, (it | k) ? 1u : 0u);
-                umma_commit(&bars->empty[s]);
+                    for (int k = 0; k < kBK / 16; ++k)  // 16 columns = 32 bytes per instruction
+                        umma_bf16(tmem + acc * BN, da + 2 * k, db + 2 * k, idesc, (it | k) ? 1u : 0u);
+                    umma_commit(&bars->empty_b[sb]);
+                    if (++sb == kBSlots) {
+                        sb = 0;
+                        pb ^= 1;
+                    }
+                }
+                umma_commit(&bars->empty_a[sa]);
             }
             umma_commit(&bars->accum);
         }
     } else if (warp == 1) {
         if (lane == 0) {  // ---- TMA loader of X ----
-            for (int it = 0; it < n_it; ++it) {
-                const int s = it % kStages;
-                const uint32_t ph = ((it / kStages) & 1) ^ 1;
-                if (!wait_or_fail(&bars->empty[s], ph, bars, g.status, 103)) break;
-                mbar_expect_tx(&bars->full_b[s], Tile<BN>::kBBytes);
-                tma_load_2d(smem + s * Tile<BN>::kStageBytes + kABytes, &tmap_b, it * kBK, (int)n0, &bars->full_b[s]);
+            int sb = 0;
+            uint32_t pb = 1;
+            bool ok = true;
+            for (int it = 0; it < n_it && ok; ++it) {
+                for (int acc = 0; acc < nacc; ++acc) {
+                    ok = wait_or_fail(&bars->empty_b[sb], pb, bars, g.status, 103);
+                    if (!ok) break;
+                    mbar_expect_tx(&bars->full_b[sb], Tile<BN>::kBBytes);
+                    tma_load_2d(smem_b + sb * Tile<BN>::kBBytes, &tmap_b, it * kBK, (int)(n0 + acc * BN),
+                                &bars->full_b[sb]);
+                    if (++sb == kBSlots) {
+                        sb = 0;
+                        pb ^= 1;
+                    }
+                }
+            }
+        }
+    } else if (warp == 2) {
+        if (lane == 0) {  // ---- TMA loader of the raw weight blocks ----
+            const int nblk = g.K >> 8;
+            int sw = 0;
+            uint32_t pw = 1;
+            for (int b = 0; b < nblk; ++b) {
+                if (!wait_or_fail(&bars->empty_w[sw], pw, bars, g.status, 106)) break;
+                mbar_expect_tx(&bars->full_w[sw], kWBytes);
+                tma_load_2d(smem_w + sw * kWBytes, &tmap_w, b * 144, (int)m0, &bars->full_w[sw]);
+                if (++sw == kWSlots) {
+                    sw = 0;
+                    pw ^= 1;
+                }
             }
         }
     } else {
-        // ---- dequant producers: thread = one row, set h owns the 64-column groups with (it & 1) == h ----
-        const int p = tid - 64;
-        const int row = p & 127, h = p >> 7;
-        const uint32_t grow = min(m0 + (uint32_t)row, g.M - 1);  // rows past M are computed and dropped
-        const uint32_t nblk = g.K >> 8;
-        const uint8_t* rp = g.A + (uint64_t)grow * nblk * 144u;
-        // registers one block ahead: header (d, dmin, 12 scale bytes) and this set's two groups
-        uint4 hdr = __ldg(reinterpret_cast<const uint4*>(rp));
-        uint4 qa0 = __ldg(reinterpret_cast<const uint4*>(rp + 16 + h * 32));
-        uint4 qa1 = __ldg(reinterpret_cast<const uint4*>(rp + 32 + h * 32));
-        uint4 qb0 = __ldg(reinterpret_cast<const uint4*>(rp + 80 + h * 32));
-        uint4 qb1 = __ldg(reinterpret_cast<const uint4*>(rp + 96 + h * 32));
-        bool ok = true;
-        for (uint32_t b = 0; b < nblk && ok; ++b) {
-            const uint4 chdr = hdr, ca0 = qa0, ca1 = qa1, cb0 = qb0, cb1 = qb1;
-            if (b + 1 < nblk) {
-                const uint8_t* np = rp + (uint64_t)(b + 1) * 144u;
-                hdr = __ldg(reinterpret_cast<const uint4*>(np));
-                qa0 = __ldg(reinterpret_cast<const uint4*>(np + 16 + h * 32));
-                qa1 = __ldg(reinterpret_cast<const uint4*>(np + 32 + h * 32));
-                qb0 = __ldg(reinterpret_cast<const uint4*>(np + 80 + h * 32));
-                qb1 = __ldg(reinterpret_cast<const uint4*>(np + 96 + h * 32));
+        // ---- dequant producers: thread = one row; set j owns group j of every block = weight stage j ----
+        const int p = tid - kCtlWarps * 32;
+        const int row = p & 127, j = p >> 7;
+        const int nblk = g.K >> 8;
+        uint8_t* a_stage = smem + j * kABytes;
+        int sw = 0;
+        uint32_t pw = 0;
+        for (int b = 0; b < nblk; ++b) {
+            if (!wait_or_fail(&bars->full_w[sw], pw, bars, g.status, 107)) break;
+            const uint8_t* wp = smem_w + sw * kWBytes + row * 144;  // rows past M arrive as zeros
+            const uint4 chdr = *reinterpret_cast<const uint4*>(wp);
+            const uint4 c0 = *reinterpret_cast<const uint4*>(wp + 16 + j * 32);
+            const uint4 c1 = *reinterpret_cast<const uint4*>(wp + 32 + j * 32);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->empty_w[sw]);
+            if (++sw == kWSlots) {
+                sw = 0;
+                pw ^= 1;
             }
             const __half2 dd = *reinterpret_cast<const __half2*>(&chdr.x);
             const float d = __low2float(dd), dmin = __high2float(dd);
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {  // groups h and h + 2 of the block
-                const int grp = h + 2 * half;
-                const int it = (int)b * 4 + grp;
-                const int s = it % kStages;
-                const uint32_t ph = ((it / kStages) & 1) ^ 1;
-                uint32_t s0, mn0, s1, mn1;
-                scale_min_k4(2 * grp, chdr.y, chdr.z, chdr.w, s0, mn0);
-                scale_min_k4(2 * grp + 1, chdr.y, chdr.z, chdr.w, s1, mn1);
-                if (!wait_or_fail(&bars->empty[s], ph, bars, g.status, 104)) {
-                    ok = false;
-                    break;
-                }
-                dequant_group_q4k(half ? cb0 : ca0, half ? cb1 : ca1, d * (float)s0, dmin * (float)mn0,
-                                  d * (float)s1, dmin * (float)mn1, smem + s * Tile<BN>::kStageBytes, row);
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bars->full_a[s]);
-            }
+            uint32_t s0, mn0, s1, mn1;
+            scale_min_k4(2 * j, chdr.y, chdr.z, chdr.w, s0, mn0);
+            scale_min_k4(2 * j + 1, chdr.y, chdr.z, chdr.w, s1, mn1);
+            if (!wait_or_fail(&bars->empty_a[j], (b & 1) ^ 1, bars, g.status, 104)) break;
+            dequant_group_q4k(c0, c1, d * (float)s0, dmin * (float)mn0, d * (float)s1, dmin * (float)mn1, a_stage,
+                              row);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->full_a[j]);
         }
-        // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----
-        if (warp < 6) {
+        // ---- epilogue: warps 3..6, TMEM lane quarter = warp % 4 ----
+        if (warp < 7) {
             if (wait_or_fail(&bars->accum, 0, bars, g.status, 105)) {
                 __syncwarp();
                 tc_fence_after();
                 const uint32_t q = warp & 3;
                 const uint32_t m = m0 + q * 32 + lane;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 0; c < nacc * (BN / 32); ++c) {
                     uint32_t v[32];
                     const uint32_t taddr = tmem + ((q * 32u) << 16) + c * 32;
                     asm volatile(
@@ -281,9 +329,9 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g)
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     if (m < g.M) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const uint32_t n = n0 + c * 32 + j;
-                            if (n < g.N) g.D[(uint64_t)n * g.stride_d + m] = __uint_as_float(v[j]);
+                        for (int jj = 0; jj < 32; ++jj) {
+                            const uint32_t n = n0 + c * 32 + jj;
+                            if (n < g.N) g.D[(uint64_t)n * g.stride_d + m] = __uint_as_float(v[jj]);
                         }
                     }
                 }
@@ -294,7 +342,8 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const GemmArgs g)
     __syncthreads();
     if (warp == 0) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(BN * NACC))
+                     : "memory");
     }
 }
 
@@ -314,7 +363,7 @@ EncodeFn encode_fn() {
     return fn;
 }
 
-template <int BN>
+template <int BN, int NACC>
 cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N, uint32_t K,
                         uint32_t stride_b, uint32_t stride_d, uint32_t* status, cudaStream_t s) {
     EncodeFn enc = encode_fn();
@@ -328,7 +377,16 @@ cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, u
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    auto kern = gemm_q4k_tc_kernel<BN>;
+    // raw weight bytes as a 2-D byte tensor [M][row_bytes]; a box is one 144-byte block of 128 rows
+    CUtensorMap wmap;
+    const cuuint64_t wdims[2] = {(cuuint64_t)(K >> 8) * 144u, M};
+    const cuuint64_t wstrides[1] = {(cuuint64_t)(K >> 8) * 144u};
+    const cuuint32_t wbox[2] = {144, kBM};
+    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(A), wdims, wstrides, wbox, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    auto kern = gemm_q4k_tc_kernel<BN, NACC>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -337,8 +395,8 @@ cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, u
         attr_set = true;
     }
     GemmArgs g{A, D, M, N, K, stride_d, status};
-    const dim3 grid((M + kBM - 1) / kBM, (N + BN - 1) / BN);
-    kern<<<grid, kThreads, Tile<BN>::kSmemBytes, s>>>(map, g);
+    const dim3 grid((M + kBM - 1) / kBM, (N + BN * NACC - 1) / (BN * NACC));
+    kern<<<grid, kThreads, Tile<BN>::kSmemBytes, s>>>(map, wmap, g);
     return cudaGetLastError();
 }
 
@@ -352,8 +410,13 @@ cudaError_t launch_mul_mm(uint32_t type, const uint8_t* A, const void* B, float*
         (reinterpret_cast<uintptr_t>(A) & 15u))
         return cudaErrorNotSupported;
     if (N < 16) return cudaErrorNotSupported;  // a handful of tokens: the matvec-style kernels are the better fit
-    cudaError_t e = N <= 128 ? launch_tile<128>(A, B, D, M, N, K, stride_b, stride_d, status, s)
-                             : launch_tile<256>(A, B, D, M, N, K, stride_b, stride_d, status, s);
+    cudaError_t e;
+    if (N <= 128)
+        e = launch_tile<128, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
+    else if (N <= 256)
+        e = launch_tile<256, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
+    else
+        e = launch_tile<256, 2>(A, B, D, M, N, K, stride_b, stride_d, status, s);
     if (e == cudaSuccess && launches) ++*launches;
     return e;
 }
