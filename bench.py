@@ -194,12 +194,63 @@ def cpu_baseline_leg(torch, step, budget_s=12.0):
                       f"{nbytes} weight bytes x {reps} repetitions"}
 
 
+def prefill_gemm_bench(torch, zb, args, local_rank):
+    """Batched-prefill dequant-GEMM D[T][M] = X[T][K] W[M][K]^T (bf16 activations, f32 out), one JSON
+    line per case: gate-shaped Q4_K 12288 x 4096 and down-shaped Q6_K 4096 x 12288 at T = 128, 512,
+    2048. Each timed launch uses the next of 8 weight copies (more than L2 in total)."""
+    from zinc_b200 import synth
+
+    peak_burst = peak_sust = None
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        peak_burst, peak_sust = float(p["bf16_tflops"]), float(p["bf16_tflops_sustained"])
+    except Exception:
+        peak_burst, peak_sust = 1590.0, 1400.0
+    ctx = zb.Context(local_rank, stream=torch.cuda.current_stream().cuda_stream)
+    dd = zb.DmmvDispatch(ctx)
+    dev = f"cuda:{local_rank}"
+    copies = 8
+    for qt, name, M, K in ((zb.Q4_K, "q4_k", 12288, 4096), (zb.Q6_K, "q6_k", 4096, 12288)):
+        ws = [synth.torch_quant_matrix(qt, M, K, dev, 100 + i) for i in range(copies)]
+        for T in (128, 512, 2048):
+            X = torch.randn(T, K, device=dev).to(torch.bfloat16)
+            D = torch.zeros(T * M, dtype=torch.float32, device=dev)
+            n0 = ctx.launch_count
+            for i in range(max(args.warmup, 3)):
+                dd.recordMulMm(qt, ws[i % copies], X, D, M, T, K, K, M, 0, 0, 0, zb.BF16)
+            per_call = (ctx.launch_count - n0) // max(args.warmup, 3)
+            reps = max(20, min(args.steps, 200))
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            for i in range(reps):
+                dd.recordMulMm(qt, ws[i % copies], X, D, M, T, K, K, M, 0, 0, 0, zb.BF16)
+            ev1.record()
+            ctx.submit_and_wait()
+            us = ev0.elapsed_time(ev1) * 1e3 / reps
+            tf = 2.0 * M * K * T / us / 1e6
+            print(json.dumps({
+                "metric": "prefill_gemm_tflops", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": reps,
+                "warmup": max(args.warmup, 3), "ms_per_step": us / 1e3, "higher_is_better": True, "dtype": "bf16",
+                "data": "synthetic",
+                "config": {"workload": f"prefill dequant-GEMM {name} {M}x{K}, T={T}, bf16 activations, f32 out",
+                           "l2": f"{copies} weight copies in rotation ({copies * ws[0].numel() / 1e6:.0f} MB)"},
+                "gpu_launches": per_call * reps,
+                "roofline": {"bound": "tensor", "achieved": tf, "peak": peak_burst, "unit": "TFLOP/s",
+                             "frac": tf / peak_burst, "frac_of_sustained": tf / peak_sust, "traffic": None},
+            }), flush=True)
+        del ws
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="zinc_b200", choices=["zinc_b200", "reference"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill_gemm"],
+                    help="decode: the headline decode step; prefill_gemm: the batched-prefill dequant-GEMM cases")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug; invalidates the number)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -229,6 +280,9 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     if args.gpus != world and rank == 0 and world > 1:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE {world}", file=sys.stderr)
+
+    if args.workload == "prefill_gemm":
+        return prefill_gemm_bench(torch, zb, args, local_rank)
 
     stream = torch.cuda.Stream()
     shape = StepShape() if not args.layers else StepShape(n_layers=args.layers)

@@ -1,6 +1,6 @@
 // Prefill dequant-GEMM on the 5th-generation tensor cores: D[n][m] = sum_k W[m][k] * X[n][k].
 //
-//   W  quantised GGUF rows (Q4_K), read in place and dequantised to bf16 by producer warps straight
+//   W  quantised GGUF rows (Q4_K or Q6_K), read in place and dequantised to bf16 by producer warps straight
 //      into the shared-memory layout tcgen05.mma consumes (K-major, 128-byte swizzle)
 //   X  bf16 activations [N][stride_b], fetched by TMA (cp.async.bulk.tensor, 128-byte swizzle)
 //   D  f32 [N][stride_d]; accumulators live in tensor memory and are read back with tcgen05.ld
@@ -10,10 +10,10 @@
 // per 512 tokens and tensor memory is fully used. Warp roles (19 warps):
 //   warp 0       allocates tensor memory; lane 0 issues tcgen05.mma and the commits
 //   warp 1       lane 0 issues the TMA loads of X
-//   warp 2       lane 0 issues the TMA loads of the raw weight blocks (128 rows x 144 bytes per box)
+//   warp 2       lane 0 issues the TMA loads of the raw weight blocks (one 256-column block of 128 rows per box)
 //   warps 3-18   dequantise: set j (4 warps, one thread per row) owns 64-column group j of every
 //                256-column block, i.e. stage j of the bf16 weight ring; warps 3-6 also run the epilogue
-// Rings: 3 raw-block slots of 18 KB, 4 bf16 weight stages of 16 KB, 3 (BN = 256) or 6 (BN = 128)
+// Rings: 3 raw-block slots of 18 KB (Q4_K) or 2 of 30 KB (Q6_K), 4 bf16 weight stages of 16 KB, 3 (BN = 256) or 6 (BN = 128)
 // activation slots of BN x 64 bf16. Every wait on an mbarrier
 // is bounded; a wait that gives up records {1, site} in the status words, raises a CTA-wide flag
 // and lets every role fall through to the common exit, where tensor memory is released.
@@ -35,15 +35,28 @@ namespace {
 constexpr int kBM = 128;      // weight rows per tile (= TMEM lanes)
 constexpr int kBK = 64;       // columns per stage: 128 bytes of bf16, one swizzle row
 constexpr int kAStages = 4;   // one per 64-column group of a 256-column block
-constexpr int kWSlots = 3;    // raw Q4_K blocks: 128 rows x 144 bytes
 constexpr int kCtlWarps = 3;
 constexpr int kThreads = kCtlWarps * 32 + 4 * 128;
 constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB
-constexpr uint32_t kWBytes = kBM * 144;       // 18 KB
 
-template <int BN>
+// Raw-block staging per weight type. A box is one 256-column block of 128 rows; Q6_K blocks are 210
+// bytes and only 2-byte aligned, so their box is the 240-byte aligned superset that contains them.
+template <int TYPE>
+struct Raw;
+template <>
+struct Raw<T_Q4_K> {
+    static constexpr uint32_t kBlock = 144, kBox = 144, kSlots = 3;
+};
+template <>
+struct Raw<T_Q6_K> {
+    static constexpr uint32_t kBlock = 210, kBox = 240, kSlots = 2;
+};
+
+template <int TYPE, int BN>
 struct Tile {
     static constexpr int kBSlots = BN == 256 ? 3 : 6;
+    static constexpr int kWSlots = Raw<TYPE>::kSlots;
+    static constexpr uint32_t kWBytes = kBM * Raw<TYPE>::kBox;
     static constexpr uint32_t kBBytes = BN * kBK * 2;
     static constexpr uint32_t kWOffset = kAStages * kABytes;
     static constexpr uint32_t kBOffset = kWOffset + kWSlots * kWBytes;
@@ -55,8 +68,8 @@ struct Tile {
 struct Bars {
     uint64_t full_a[kAStages];
     uint64_t empty_a[kAStages];
-    uint64_t full_w[kWSlots];
-    uint64_t empty_w[kWSlots];
+    uint64_t full_w[3];
+    uint64_t empty_w[3];
     uint64_t full_b[6];
     uint64_t empty_b[6];
     uint64_t accum;
@@ -157,6 +170,70 @@ __device__ __forceinline__ void dequant_group_q4k(const uint4& q0, const uint4& 
     }
 }
 
+// N consecutive 32-bit words starting `sh` bits (0 or 16) into the aligned word at p.
+template <int N>
+__device__ __forceinline__ void lds_shifted(const uint32_t* p, uint32_t sh, uint32_t (&w)[N]) {
+    uint32_t prev = p[0];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+        const uint32_t next = p[i + 1];
+        w[i] = __funnelshift_r(prev, next, sh);
+        prev = next;
+    }
+}
+
+// Four 6-bit weights (one per byte of q4, values 0..63) -> two bf16x2 words: (128 + q) - 160 = q - 32
+// exactly, times d*scale.
+__device__ __forceinline__ void deq4_q6(uint32_t q4, __nv_bfloat162 dsc, uint32_t& o0, uint32_t& o1) {
+    const __nv_bfloat162 k160 = bits_bf2(0x43204320u);
+    const uint32_t p0 = __byte_perm(q4, 0x43434343u, 0x4140);
+    const uint32_t p1 = __byte_perm(q4, 0x43434343u, 0x4342);
+    o0 = bf2_bits(__hmul2(__hsub2(bits_bf2(p0), k160), dsc));
+    o1 = bf2_bits(__hmul2(__hsub2(bits_bf2(p1), k160), dsc));
+}
+
+// One 64-column group g of a Q6_K block (layout: ql[128] qh[64] scales[16] d, src/model/gguf.zig:38-123;
+// element order as dequantRow, src/compute/forward.zig:335-383): half n = g / 2 of the block, low
+// (g even) or high (g odd) nibbles of ql[64n .. 64n+64), bit pairs 4*(g&1) and 4*(g&1)+2 of
+// qh[32n .. 32n+32), scales[8n + 4*(g&1) .. +4) each covering 16 columns. `blk` points at the aligned
+// word that contains the block's first byte, `sh` = 0 or 16.
+__device__ __forceinline__ void dequant_group_q6k(const uint32_t* blk, uint32_t sh, int g, uint8_t* a_stage,
+                                                  int row) {
+    const int n = g >> 1, hi = g & 1;
+    uint32_t ql[16], qh[8], scw[1], dw[1];
+    lds_shifted<16>(blk + 16 * n, sh, ql);
+    lds_shifted<8>(blk + 32 + 8 * n, sh, qh);
+    lds_shifted<1>(blk + 48 + 2 * n + hi, sh, scw);
+    lds_shifted<1>(blk + 52, sh, dw);
+    const float d = __half2float(__ushort_as_half((unsigned short)(dw[0] & 0xFFFFu)));
+    uint8_t* rowp = a_stage + row * 128;
+    const int sw = row & 7;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {  // chunk c = columns 8c .. 8c+7 of the group; scale index c / 2
+        const float sc = (float)(int)(int8_t)((scw[0] >> (8 * (c >> 1))) & 0xFFu);
+        const __nv_bfloat162 dsc = __float2bfloat162_rn(d * sc);
+        uint4 o;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            // columns 8c+4e .. +3: ql byte index (c < 4 ? 0 : 32) + 8*(c&3) + 4e, qh byte index 8*(c&3) + 4e
+            const uint32_t lw = ql[(c >> 2) * 8 + (c & 3) * 2 + e];
+            const uint32_t hw = qh[(c & 3) * 2 + e];
+            const uint32_t nib = (lw >> (4 * hi)) & 0x0F0F0F0Fu;
+            const uint32_t top = ((hw >> (4 * hi + 2 * (c >> 2))) & 0x03030303u) << 4;
+            uint32_t a, b;
+            deq4_q6(nib | top, dsc, a, b);
+            if (e == 0) {
+                o.x = a;
+                o.y = b;
+            } else {
+                o.z = a;
+                o.w = b;
+            }
+        }
+        *reinterpret_cast<uint4*>(rowp + ((c ^ sw) << 4)) = o;
+    }
+}
+
 struct GemmArgs {
     const uint8_t* A;
     float* D;
@@ -165,19 +242,26 @@ struct GemmArgs {
     uint32_t* status;
 };
 
-template <int BN, int NACC>
+template <int TYPE, int BN, int NACC>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_w,
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_w,
                    const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // swizzle atoms: 1024-byte aligned
-    uint8_t* smem_b = smem + Tile<BN>::kBOffset;
-    uint8_t* smem_w = smem + Tile<BN>::kWOffset;
-    constexpr int kBSlots = Tile<BN>::kBSlots;
-    Bars* bars = reinterpret_cast<Bars*>(smem + Tile<BN>::kBarOffset);
+    uint8_t* smem_b = smem + Tile<TYPE, BN>::kBOffset;
+    uint8_t* smem_w = smem + Tile<TYPE, BN>::kWOffset;
+    constexpr int kBSlots = Tile<TYPE, BN>::kBSlots;
+    constexpr int kWSlots = Tile<TYPE, BN>::kWSlots;
+    constexpr uint32_t kWBytes = Tile<TYPE, BN>::kWBytes;
+    Bars* bars = reinterpret_cast<Bars*>(smem + Tile<TYPE, BN>::kBarOffset);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t m0 = blockIdx.x * kBM, n0 = blockIdx.y * (BN * NACC);
-    const int n_it = g.K / kBK;
+    // split-K: CTA z handles blocks [b_begin, b_end) of every row and adds its partial tile into D
+    const int nblk_all = g.K >> 8;
+    const int b_begin = (int)((long long)blockIdx.z * nblk_all / gridDim.z);
+    const int b_end = (int)((long long)(blockIdx.z + 1) * nblk_all / gridDim.z);
+    const int n_it = (b_end - b_begin) * 4;
+    const int it0 = b_begin * 4;
     // accumulators of this tile that hold at least one real token
     const int nacc = min(NACC, (int)((g.N - n0 + BN - 1) / BN));
 
@@ -224,7 +308,7 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_cons
                     ok = wait_or_fail<false>(&bars->full_b[sb], pb, bars, g.status, 102);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t db = smem_desc(smem_u32(smem_b + sb * Tile<BN>::kBBytes));
+                    const uint64_t db = smem_desc(smem_u32(smem_b + sb * Tile<TYPE, BN>::kBBytes));
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k)  // 16 columns = 32 bytes per instruction
                         umma_bf16(tmem + acc * BN, da + 2 * k, db + 2 * k, idesc, (it | k) ? 1u : 0u);
@@ -247,8 +331,8 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_cons
                 for (int acc = 0; acc < nacc; ++acc) {
                     ok = wait_or_fail(&bars->empty_b[sb], pb, bars, g.status, 103);
                     if (!ok) break;
-                    mbar_expect_tx(&bars->full_b[sb], Tile<BN>::kBBytes);
-                    tma_load_2d(smem_b + sb * Tile<BN>::kBBytes, &tmap_b, it * kBK, (int)(n0 + acc * BN),
+                    mbar_expect_tx(&bars->full_b[sb], Tile<TYPE, BN>::kBBytes);
+                    tma_load_2d(smem_b + sb * Tile<TYPE, BN>::kBBytes, &tmap_b, (it0 + it) * kBK, (int)(n0 + acc * BN),
                                 &bars->full_b[sb]);
                     if (++sb == kBSlots) {
                         sb = 0;
@@ -259,13 +343,13 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_cons
         }
     } else if (warp == 2) {
         if (lane == 0) {  // ---- TMA loader of the raw weight blocks ----
-            const int nblk = g.K >> 8;
             int sw = 0;
             uint32_t pw = 1;
-            for (int b = 0; b < nblk; ++b) {
+            for (int b = b_begin; b < b_end; ++b) {
                 if (!wait_or_fail(&bars->empty_w[sw], pw, bars, g.status, 106)) break;
                 mbar_expect_tx(&bars->full_w[sw], kWBytes);
-                tma_load_2d(smem_w + sw * kWBytes, &tmap_w, b * 144, (int)m0, &bars->full_w[sw]);
+                tma_load_2d(smem_w + sw * kWBytes, &tmap_w, (int)((b * Raw<TYPE>::kBlock) & ~15u), (int)m0,
+                            &bars->full_w[sw]);
                 if (++sw == kWSlots) {
                     sw = 0;
                     pw ^= 1;
@@ -276,30 +360,39 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_cons
         // ---- dequant producers: thread = one row; set j owns group j of every block = weight stage j ----
         const int p = tid - kCtlWarps * 32;
         const int row = p & 127, j = p >> 7;
-        const int nblk = g.K >> 8;
         uint8_t* a_stage = smem + j * kABytes;
         int sw = 0;
         uint32_t pw = 0;
-        for (int b = 0; b < nblk; ++b) {
+        for (int b = b_begin; b < b_end; ++b) {
             if (!wait_or_fail(&bars->full_w[sw], pw, bars, g.status, 107)) break;
-            const uint8_t* wp = smem_w + sw * kWBytes + row * 144;  // rows past M arrive as zeros
-            const uint4 chdr = *reinterpret_cast<const uint4*>(wp);
-            const uint4 c0 = *reinterpret_cast<const uint4*>(wp + 16 + j * 32);
-            const uint4 c1 = *reinterpret_cast<const uint4*>(wp + 32 + j * 32);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->empty_w[sw]);
+            if constexpr (TYPE == T_Q4_K) {
+                const uint8_t* wp = smem_w + sw * kWBytes + row * 144;  // rows past M arrive as zeros
+                const uint4 chdr = *reinterpret_cast<const uint4*>(wp);
+                const uint4 c0 = *reinterpret_cast<const uint4*>(wp + 16 + j * 32);
+                const uint4 c1 = *reinterpret_cast<const uint4*>(wp + 32 + j * 32);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->empty_w[sw]);
+                const __half2 dd = *reinterpret_cast<const __half2*>(&chdr.x);
+                const float d = __low2float(dd), dmin = __high2float(dd);
+                uint32_t s0, mn0, s1, mn1;
+                scale_min_k4(2 * j, chdr.y, chdr.z, chdr.w, s0, mn0);
+                scale_min_k4(2 * j + 1, chdr.y, chdr.z, chdr.w, s1, mn1);
+                if (!wait_or_fail(&bars->empty_a[j], ((b - b_begin) & 1) ^ 1, bars, g.status, 104)) break;
+                dequant_group_q4k(c0, c1, d * (float)s0, dmin * (float)mn0, d * (float)s1, dmin * (float)mn1,
+                                  a_stage, row);
+            } else {
+                // the block starts (b * 210) & 15 bytes into the box; that offset is even
+                const uint32_t off = ((uint32_t)b * 210u) & 15u;
+                const uint8_t* wp = smem_w + sw * kWBytes + row * 240 + (off & ~3u);
+                if (!wait_or_fail(&bars->empty_a[j], ((b - b_begin) & 1) ^ 1, bars, g.status, 104)) break;
+                dequant_group_q6k(reinterpret_cast<const uint32_t*>(wp), (off & 2u) * 8u, j, a_stage, row);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->empty_w[sw]);
+            }
             if (++sw == kWSlots) {
                 sw = 0;
                 pw ^= 1;
             }
-            const __half2 dd = *reinterpret_cast<const __half2*>(&chdr.x);
-            const float d = __low2float(dd), dmin = __high2float(dd);
-            uint32_t s0, mn0, s1, mn1;
-            scale_min_k4(2 * j, chdr.y, chdr.z, chdr.w, s0, mn0);
-            scale_min_k4(2 * j + 1, chdr.y, chdr.z, chdr.w, s1, mn1);
-            if (!wait_or_fail(&bars->empty_a[j], (b & 1) ^ 1, bars, g.status, 104)) break;
-            dequant_group_q4k(c0, c1, d * (float)s0, dmin * (float)mn0, d * (float)s1, dmin * (float)mn1, a_stage,
-                              row);
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->full_a[j]);
@@ -331,7 +424,13 @@ gemm_q4k_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_cons
 #pragma unroll
                         for (int jj = 0; jj < 32; ++jj) {
                             const uint32_t n = n0 + c * 32 + jj;
-                            if (n < g.N) g.D[(uint64_t)n * g.stride_d + m] = __uint_as_float(v[jj]);
+                            if (n < g.N) {
+                                float* dst = g.D + (uint64_t)n * g.stride_d + m;
+                                if (gridDim.z == 1)
+                                    *dst = __uint_as_float(v[jj]);
+                                else
+                                    atomicAdd(dst, __uint_as_float(v[jj]));
+                            }
                         }
                     }
                 }
@@ -363,7 +462,7 @@ EncodeFn encode_fn() {
     return fn;
 }
 
-template <int BN, int NACC>
+template <int TYPE, int BN, int NACC>
 cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N, uint32_t K,
                         uint32_t stride_b, uint32_t stride_d, uint32_t* status, cudaStream_t s) {
     EncodeFn enc = encode_fn();
@@ -377,27 +476,50 @@ cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, u
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    // raw weight bytes as a 2-D byte tensor [M][row_bytes]; a box is one 144-byte block of 128 rows
+    // raw weight bytes as a 2-D byte tensor [M][row_bytes]; a box holds one block of 128 rows
     CUtensorMap wmap;
-    const cuuint64_t wdims[2] = {(cuuint64_t)(K >> 8) * 144u, M};
-    const cuuint64_t wstrides[1] = {(cuuint64_t)(K >> 8) * 144u};
-    const cuuint32_t wbox[2] = {144, kBM};
+    const cuuint64_t row_bytes = (cuuint64_t)(K >> 8) * Raw<TYPE>::kBlock;
+    const cuuint64_t wdims[2] = {row_bytes, M};
+    const cuuint64_t wstrides[1] = {row_bytes};
+    const cuuint32_t wbox[2] = {Raw<TYPE>::kBox, kBM};
     if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(A), wdims, wstrides, wbox, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    auto kern = gemm_q4k_tc_kernel<BN, NACC>;
+    auto kern = gemm_tc_kernel<TYPE, BN, NACC>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)Tile<BN>::kSmemBytes);
+                                             (int)Tile<TYPE, BN>::kSmemBytes);
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
     GemmArgs g{A, D, M, N, K, stride_d, status};
-    const dim3 grid((M + kBM - 1) / kBM, (N + BN * NACC - 1) / (BN * NACC));
-    kern<<<grid, kThreads, Tile<BN>::kSmemBytes, s>>>(map, wmap, g);
+    dim3 grid((M + kBM - 1) / kBM, (N + BN * NACC - 1) / (BN * NACC), 1);
+    // Few tiles (short M or few tokens): split K over up to 8 CTAs per tile, at least 4 blocks each, and
+    // let the partial tiles add into a zeroed D.
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const uint32_t tiles = grid.x * grid.y;
+    uint32_t splits = tiles ? (uint32_t)sms / tiles : 1;
+    splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
+    while (splits > 1 && (K >> 8) / splits < 4) --splits;
+    if (splits > 1) {
+        cudaError_t e = cudaMemset2DAsync(D, (size_t)stride_d * 4, 0, (size_t)M * 4, N, s);
+        if (e != cudaSuccess) return e;
+        grid.z = splits;
+    }
+    kern<<<grid, kThreads, Tile<TYPE, BN>::kSmemBytes, s>>>(map, wmap, g);
     return cudaGetLastError();
+}
+
+template <int TYPE>
+cudaError_t launch_typed(const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N, uint32_t K,
+                         uint32_t stride_b, uint32_t stride_d, uint32_t* status, cudaStream_t s) {
+    if (N <= 128) return launch_tile<TYPE, 128, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
+    if (N <= 256) return launch_tile<TYPE, 256, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
+    return launch_tile<TYPE, 256, 2>(A, B, D, M, N, K, stride_b, stride_d, status, s);
 }
 
 }  // namespace
@@ -405,18 +527,15 @@ cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, u
 cudaError_t launch_mul_mm(uint32_t type, const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N,
                           uint32_t K, uint32_t stride_b, uint32_t stride_d, bool act_bf16, uint32_t* status,
                           cudaStream_t s, uint64_t* launches) {
-    if (type != T_Q4_K || !act_bf16 || !status) return cudaErrorNotSupported;
+    if ((type != T_Q4_K && type != T_Q6_K) || !act_bf16 || !status) return cudaErrorNotSupported;
     if ((K & 255u) || (stride_b & 7u) || (reinterpret_cast<uintptr_t>(B) & 15u) ||
         (reinterpret_cast<uintptr_t>(A) & 15u))
         return cudaErrorNotSupported;
+    // Q6_K rows are 210 bytes per block: the TMA row pitch is a multiple of 16 only for K % 2048 == 0
+    if (type == T_Q6_K && (K & 2047u)) return cudaErrorNotSupported;
     if (N < 16) return cudaErrorNotSupported;  // a handful of tokens: the matvec-style kernels are the better fit
-    cudaError_t e;
-    if (N <= 128)
-        e = launch_tile<128, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
-    else if (N <= 256)
-        e = launch_tile<256, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
-    else
-        e = launch_tile<256, 2>(A, B, D, M, N, K, stride_b, stride_d, status, s);
+    cudaError_t e = type == T_Q4_K ? launch_typed<T_Q4_K>(A, B, D, M, N, K, stride_b, stride_d, status, s)
+                                   : launch_typed<T_Q6_K>(A, B, D, M, N, K, stride_b, stride_d, status, s);
     if (e == cudaSuccess && launches) ++*launches;
     return e;
 }
