@@ -150,6 +150,17 @@ int32_t zc_dmmv(zc_ctx* ctx, uint32_t type,
                 uint32_t M, uint32_t K,
                 uint64_t a_offset, uint64_t x_offset, uint64_t y_offset, uint32_t acc_mode);
 
+/* Grouped matvec: y_i (+)= W_i x for n = 1..3 matrices of one type that share x and K, e.g. the Q, K
+ * and V projections the reference records as three dispatches on the same input
+ * (src/compute/forward.zig:4530-4564). One kernel launch when the matrices are Q4_K (16-byte aligned);
+ * otherwise the same result through one launch per matrix. Arguments are those of zc_dmmv, per matrix
+ * in arrays of length n. */
+int32_t zc_dmmv_multi(zc_ctx* ctx, uint32_t quant_type, uint32_t n,
+                      const void* const* A, const uint64_t* a_size, const uint64_t* a_offset,
+                      const void* x, uint64_t x_size, uint64_t x_offset,
+                      void* const* y, const uint64_t* y_size, const uint64_t* y_offset,
+                      const uint32_t* M, uint32_t K, uint32_t acc_mode);
+
 /* out[r] = silu(Wg[r].x) * (Wu[r].x), one pass over both weight streams.
  * Replaces dispatchDmmvFusedGateUpSwiglu and its Q8_0 sibling
  * (src/compute/forward.zig:8237-8313; src/shaders/dmmv_q4k_fused_gate_up_swiglu.comp:195-218).

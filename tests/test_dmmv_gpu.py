@@ -315,3 +315,25 @@ def test_streaming_extreme_activations(gpu, oracle):
         dd.recordDispatch(t, dev(torch, w), dev(torch, x), y, M, K)
         ctx.submit_and_wait()
         assert rel_l2(y[:M].cpu().numpy(), oracle.dmmv_f64(w, t, M, K, x)) <= TOL
+
+
+@pytest.mark.parametrize("t,Ms,K", [(zb.Q4_K, (4096, 1024, 1024), 4096), (zb.Q4_K, (1000, 37), 2048),
+                                   (zb.Q4_K, (16, 16, 48), 512), (zb.Q6_K, (64, 32, 32), 2048),
+                                   (zb.Q8_0, (40, 24), 256)],
+                         ids=["q4k_qkv", "q4k_ragged_pair", "q4k_tiny", "q6k_fallback", "q8_0_fallback"])
+def test_dispatch_multi(gpu, oracle, t, Ms, K):
+    """Grouped matvec (the Q, K, V dispatches of one token as one call) against the oracle, twice in
+    a row, with accumulate mode on the second call."""
+    torch, ctx, dd = gpu
+    g = synth.rng(108, t * 1000 + sum(Ms))
+    ws = [synth.quant_matrix(g, t, M, K) for M in Ms]
+    x = synth.activations(g, K)
+    xd = dev(torch, x)
+    wds = [dev(torch, w) for w in ws]
+    ys = [out_with_canary(torch, M) for M in Ms]
+    dd.recordDispatchMulti(t, wds, xd, ys, list(Ms), K)
+    dd.recordDispatchMulti(t, wds, xd, ys, list(Ms), K, acc_mode=1)
+    ctx.submit_and_wait()
+    for w, M, y in zip(ws, Ms, ys):
+        assert canary_intact(y, M)
+        assert rel_l2(y[:M].cpu().numpy(), 2.0 * oracle.dmmv_f64(w, t, M, K, x)) <= TOL

@@ -29,6 +29,8 @@ _OPS = {
     "zc_dmmv_fused_gate_up_swiglu": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32,
                                      _u64, _u64, _u64, _u64],
     "zc_dmmv_sigmoid_acc": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u64, _u64, _u32],
+    "zc_dmmv_multi": [_u32, _u32, C.POINTER(_vp), C.POINTER(_u64), C.POINTER(_u64), _vp, _u64, _u64,
+                      C.POINTER(_vp), C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u32), _u32, _u32],
     "zc_dmmv_batch": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u64, _u64, _u32],
     "zc_mul_mm": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _u32, _u32, _u64, _u64, _u64, _u32],
     "zc_moe_dmmv": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u32, _u32, _u64, _u64],

@@ -342,6 +342,44 @@ int32_t zc_dmmv(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, cons
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_dmmv");
 }
 
+int32_t zc_dmmv_multi(zc_ctx* ctx, uint32_t type, uint32_t n, const void* const* A, const uint64_t* a_size,
+                      const uint64_t* a_offset, const void* x, uint64_t x_size, uint64_t x_offset, void* const* y,
+                      const uint64_t* y_size, const uint64_t* y_offset, const uint32_t* M, uint32_t K,
+                      uint32_t acc_mode) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_dmmv_multi";
+    if (n == 0 || n > 3) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: n must be 1, 2 or 3", fn);
+    if (!A || !a_size || !a_offset || !y || !y_size || !y_offset || !M)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: null argument array", fn);
+    ZC_TRY(check_vec(ctx, fn, "x", x, x_size, x_offset, (uint64_t)K * 4, 16));
+    const uint8_t* Ap[3];
+    float* yp[3];
+    for (uint32_t i = 0; i < n; ++i) {
+        ZC_TRY(check_mat(ctx, fn, type, A[i], a_size[i], a_offset[i], (uint64_t)M[i] * row_bytes_of(type, K), M[i], K));
+        ZC_TRY(check_vec(ctx, fn, "y", y[i], y_size[i], y_offset[i], (uint64_t)M[i] * 4, 4));
+        Ap[i] = u8(A[i], a_offset[i]);
+        yp[i] = f32m(y[i], y_offset[i]);
+    }
+    DmmvArgs a;
+    a.x = f32p(x, x_offset);
+    a.K = K;
+    a.acc_mode = acc_mode;
+    attach_scratch(ctx, a);
+    cudaError_t e = cudaSuccess;
+    if (warp_dmmv_multi_eligible(type, n, Ap, M, K, a)) {
+        e = launch_warp_dmmv_multi(n, Ap, yp, M, a, ctx->stream, &ctx->launches);
+    } else {
+        for (uint32_t i = 0; i < n && e == cudaSuccess; ++i) {  // any type, any shape: one launch per matrix
+            DmmvArgs ai = a;
+            ai.A = Ap[i];
+            ai.y = yp[i];
+            ai.M = M[i];
+            e = launch_dmmv(type, MODE_PLAIN, ai, ctx->stream, &ctx->launches);
+        }
+    }
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
 int32_t zc_dmmv_fused_gate_up_swiglu(zc_ctx* ctx, uint32_t type, const void* Wg, uint64_t wg_size, const void* Wu,
                                      uint64_t wu_size, const void* x, uint64_t x_size, void* out, uint64_t out_size,
                                      uint32_t M, uint32_t K, uint64_t gate_offset, uint64_t up_offset,

@@ -167,7 +167,12 @@ __device__ __forceinline__ void scales_mins_pair(uint32_t s0, uint32_t s1, uint3
 }
 
 
-template <int NS, int EPI, int kWarps>
+// Segment of a grouped launch that holds tile T.
+__device__ __forceinline__ int seg_of(const WarpArgs& a, uint32_t T) {
+    return (T >= a.seg_end[0] ? 1 : 0) + (T >= a.seg_end[1] ? 1 : 0);
+}
+
+template <int NS, int EPI, int kWarps, bool kMulti = false>
 __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel(const WarpArgs a) {
     extern __shared__ uint8_t smem_raw[];
     pdl_launch_dependents();
@@ -178,7 +183,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
     const uint64_t row_bytes = (uint64_t)bpr * 144;
     const uint32_t upt = (bpr + kCB - 1) / kCB;  // row segments (units) per row
     const uint32_t upt_all = upt * NS;            // units per 16-row tile
-    const uint32_t tiles = (a.M + 15) / 16;
+    const uint32_t tiles = kMulti ? a.seg_end[a.nseg - 1] : (a.M + 15) / 16;
     const uint32_t U = tiles * upt_all, G = gridDim.x * kWarps;  // units, workers (G <= U)
     const uint32_t me = blockIdx.x * kWarps + warp;
     const uint32_t u0 = (uint32_t)part_begin(me, U, G), u1 = (uint32_t)part_begin(me + 1, U, G);
@@ -207,9 +212,12 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
     auto request = [&](uint32_t slot) {
         const uint32_t cols = min((uint32_t)kCB, bpr - p_kc * kCB) * 9;  // 16-byte columns in this segment
         const uint32_t row0 = p_tile * 16;
-        const uint8_t* src = a.A[p_strm] + (uint64_t)row0 * row_bytes + (uint64_t)p_kc * (kCB * 144);
+        const int sg = kMulti ? seg_of(a, p_tile) : 0;
+        const uint8_t* base = kMulti ? a.segA[sg] : a.A[p_strm];
+        const uint32_t Mb = kMulti ? a.segM[sg] : a.M;  // row bound in the indexing of `base`
+        const uint8_t* src = base + (uint64_t)row0 * row_bytes + (uint64_t)p_kc * (kCB * 144);
         uint8_t* dst = ring + slot * kSlotBytes;
-        if (row0 + 16 <= a.M && cols == kPiecesPerRow) {
+        if (row0 + 16 <= Mb && cols == kPiecesPerRow) {
 #pragma unroll
             for (int i = 0; i < kPiecesPerLane; ++i) cp_async16(dst + dst_off[i], src + src_off[i]);
         } else {
@@ -218,7 +226,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
             for (int i = 0; i < kPiecesPerLane; ++i) {
                 const uint32_t r = piece[i] & 0xFFu, c = piece[i] >> 8;
                 if (c < cols) {
-                    const uint32_t row = min(row0 + r, a.M - 1);
+                    const uint32_t row = min(row0 + r, Mb - 1);
                     cp_async16(dst + dst_off[i], src + (uint64_t)(row - row0) * row_bytes + c * 16);
                 }
             }
@@ -334,14 +342,22 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
                     acc1[r] = 0.f;
                 }
             }
-            finish_tile<NS, EPI, kWarps>(a, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
+            if constexpr (kMulti) {
+                WarpArgs am = a;
+                const int sg = seg_of(a, T);
+                am.y = a.segY[sg];
+                am.M = a.segM[sg];
+                finish_tile<NS, EPI, kWarps>(am, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
+            } else {
+                finish_tile<NS, EPI, kWarps>(a, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
+            }
         }
     }
 }
 
-template <int NS, int EPI, int kWarps>
+template <int NS, int EPI, int kWarps, bool kMulti = false>
 cudaError_t launch_w(const WarpArgs& a, cudaStream_t st, int sm_count, size_t smem) {
-    auto kern = dmmv_q4k_warp_kernel<NS, EPI, kWarps>;
+    auto kern = dmmv_q4k_warp_kernel<NS, EPI, kWarps, kMulti>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -349,7 +365,8 @@ cudaError_t launch_w(const WarpArgs& a, cudaStream_t st, int sm_count, size_t sm
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    const uint64_t U = (uint64_t)((a.M + 15) / 16) * (((a.K >> 8) + kCB - 1) / kCB) * NS;
+    const uint64_t tiles = kMulti ? a.seg_end[a.nseg - 1] : (a.M + 15) / 16;
+    const uint64_t U = tiles * (((a.K >> 8) + kCB - 1) / kCB) * NS;
     uint64_t grid = (uint64_t)sm_count * (16 / kWarps);  // 16 worker warps per SM
     if (grid * kWarps > U) grid = U / kWarps;
     if (grid * kWarps > kStreamMaxWorkers) grid = kStreamMaxWorkers / kWarps;
@@ -392,6 +409,7 @@ cudaError_t launch_warp_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStr
     wa.gpartial = a.scratch_partial;
     wa.gflags = a.scratch_flags;
     wa.status = a.status;
+    wa.nseg = 0;
     cudaError_t e;
     switch (mode) {
         case MODE_PLAIN: e = launch_cfg<1, EPI_PLAIN>(wa, st, a.sm_count); break;
@@ -399,6 +417,62 @@ cudaError_t launch_warp_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStr
         case MODE_SIGMOID_ACC: e = launch_cfg<1, EPI_SIGMOID_ACC>(wa, st, a.sm_count); break;
         default: return cudaErrorInvalidValue;
     }
+    if (e == cudaSuccess && launches) ++*launches;
+    return e;
+}
+
+// Grouped launch: n <= 3 Q4_K matrices with the same K and the same x, y_i = W_i x, in one kernel.
+bool warp_dmmv_multi_eligible(uint32_t type, uint32_t n, const uint8_t* const* A, const uint32_t* M, uint32_t K,
+                              const DmmvArgs& common) {
+    if (type != T_Q4_K || n < 2 || n > 3) return false;
+    if (!common.scratch_partial || !common.scratch_flags || !common.status) return false;
+    if (smem_bytes(K, 16) > 227 * 1024 || (K >> 8) > (uint32_t)(kPrepBlocks * 8) || (K & 255u)) return false;
+    uint64_t tiles = 0;
+    for (uint32_t i = 0; i < n; ++i) {
+        if (reinterpret_cast<uintptr_t>(A[i]) & 15u) return false;
+        if (M[i] == 0) return false;
+        tiles += (M[i] + 15) / 16;
+    }
+    const uint64_t U = tiles * (((K >> 8) + kCB - 1) / kCB);
+    return U >= 16 && U <= 0xFFFFFFFFull;
+}
+
+cudaError_t launch_warp_dmmv_multi(uint32_t n, const uint8_t* const* A, float* const* y, const uint32_t* M,
+                                   const DmmvArgs& common, cudaStream_t st, uint64_t* launches) {
+    WarpArgs wa;
+    wa.A[0] = wa.A[1] = A[0];
+    wa.x = common.x;
+    wa.y = y[0];
+    wa.gate = nullptr;
+    wa.M = M[0];
+    wa.K = common.K;
+    wa.acc_mode = common.acc_mode;
+    wa.gpartial = common.scratch_partial;
+    wa.gflags = common.scratch_flags;
+    wa.status = common.status;
+    wa.nseg = n;
+    const uint64_t row_bytes = (uint64_t)(common.K >> 8) * 144;
+    uint32_t t0 = 0;
+    for (uint32_t i = 0; i < 3; ++i) {
+        if (i < n) {
+            // shift by the segment's first tile: the kernel indexes with global tile / row numbers
+            wa.segA[i] = A[i] - (uint64_t)t0 * 16 * row_bytes;
+            wa.segY[i] = y[i] - (uint64_t)t0 * 16;
+            wa.segM[i] = t0 * 16 + M[i];
+            t0 += (M[i] + 15) / 16;
+            wa.seg_end[i] = t0;
+        } else {
+            wa.segA[i] = nullptr;
+            wa.segY[i] = nullptr;
+            wa.segM[i] = 0;
+            wa.seg_end[i] = 0xFFFFFFFFu;
+        }
+    }
+    if (n == 2) wa.seg_end[1] = t0;
+    const size_t s8 = smem_bytes(common.K, 8);
+    cudaError_t e = s8 <= kTwoPerSm ? launch_w<1, EPI_PLAIN, 8, true>(wa, st, common.sm_count, s8)
+                                    : launch_w<1, EPI_PLAIN, 16, true>(wa, st, common.sm_count,
+                                                                        smem_bytes(common.K, 16));
     if (e == cudaSuccess && launches) ++*launches;
     return e;
 }

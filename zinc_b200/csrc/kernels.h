@@ -50,6 +50,12 @@ constexpr size_t kStreamFlagBytes = (size_t)kStreamMaxWorkers * sizeof(uint32_t)
 // Warp-autonomous streaming (cp.async + tensor-core) matvec: eligibility and launch.
 bool warp_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a);
 cudaError_t launch_warp_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
+// Grouped form: n (2 or 3) Q4_K matrices that share x and K, one launch. `common` carries x, K, acc_mode,
+// the scratch, the status words and the SM count.
+bool warp_dmmv_multi_eligible(uint32_t type, uint32_t n, const uint8_t* const* A, const uint32_t* M, uint32_t K,
+                              const DmmvArgs& common);
+cudaError_t launch_warp_dmmv_multi(uint32_t n, const uint8_t* const* A, float* const* y, const uint32_t* M,
+                                   const DmmvArgs& common, cudaStream_t s, uint64_t* launches);
 bool q6k_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a);
 cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
 

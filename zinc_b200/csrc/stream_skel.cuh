@@ -24,6 +24,14 @@ struct WarpArgs {
     float* gpartial;     // [workers][32] partial sums published across CTAs
     uint32_t* gflags;    // [workers] 0 = empty, 1 = published; the reader clears it
     uint32_t* status;    // [0] error code, [1] site
+    // Grouped launch (several matrices that share x and K, e.g. Q, K and V): segment i covers the
+    // 16-row tiles [seg_end[i-1], seg_end[i]). Its pointers and row bound are pre-shifted by the
+    // segment's first tile, so that the kernel can index them with the global tile / row number.
+    uint32_t nseg;       // 0: single matrix (A[0], y, M)
+    uint32_t seg_end[3];
+    const uint8_t* segA[3];
+    float* segY[3];
+    uint32_t segM[3];
 };
 
 

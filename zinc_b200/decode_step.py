@@ -134,9 +134,9 @@ class DecodeStep:
         s, dd, g = self.shape, self.dd, self.world
         n0 = dd.ctx.launch_count
         for lw in self.layers:
-            dd.recordDispatch(s.t_attn, lw.wq, self.x_norm, self.q, s.q_dim // g, s.hidden)
-            dd.recordDispatch(s.t_attn, lw.wk, self.x_norm, self.k, s.kv_dim // g, s.hidden)
-            dd.recordDispatch(s.t_attn, lw.wv, self.x_norm, self.v, s.kv_dim // g, s.hidden)
+            # Q, K and V read the same normalised hidden state: one grouped call
+            dd.recordDispatchMulti(s.t_attn, [lw.wq, lw.wk, lw.wv], self.x_norm, [self.q, self.k, self.v],
+                                   [s.q_dim // g, s.kv_dim // g, s.kv_dim // g], s.hidden)
             if g == 1:
                 dd.recordDispatch(s.t_attn, lw.wo, self.attn_out, self.hidden, s.hidden, s.q_dim, acc_mode=1)
             else:  # K-sharded: partial sums, then all-reduce into the replicated hidden vector

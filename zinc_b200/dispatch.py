@@ -221,6 +221,21 @@ class DmmvDispatch:
                       a_offset, x_offset, y_offset, acc_mode)
 
     # recordBatchDispatchPush (src/compute/dmmv.zig:880-926) + dispatchProjectionBatched chunk loop
+    def recordDispatchMulti(self, quant_type, As, x, ys, Ms, K, a_offsets=None, x_offset=0, y_offsets=None,
+                            acc_mode=0):
+        """Several recordDispatch calls on the same input (the reference's Q, K, V sequence,
+        src/compute/forward.zig:4530-4564) as one call: y_i (+)= W_i x."""
+        n = len(As)
+        if not (n == len(ys) == len(Ms)) or not 1 <= n <= 3:
+            raise InvalidArgument("recordDispatchMulti needs 1..3 matrices with matching outputs and row counts")
+        Ab, yb, xb = [_buf(a) for a in As], [_buf(y) for y in ys], _buf(x)
+        a_offsets = a_offsets or [0] * n
+        y_offsets = y_offsets or [0] * n
+        vp, u64, u32 = C.c_void_p * n, C.c_uint64 * n, C.c_uint32 * n
+        self.ctx.call("zc_dmmv_multi", quant_type, n, vp(*[b.ptr for b in Ab]), u64(*[b.size for b in Ab]),
+                      u64(*a_offsets), xb.ptr, xb.size, x_offset, vp(*[b.ptr for b in yb]),
+                      u64(*[b.size for b in yb]), u64(*y_offsets), u32(*Ms), K, acc_mode)
+
     def recordBatchDispatchPush(self, quant_type, A, X, Y, M, K, a_offset, x_offset, y_offset, num_cols):
         A, X, Y = _buf(A), _buf(X), _buf(Y)
         self.ctx.call("zc_dmmv_batch", quant_type, A.ptr, A.size, X.ptr, X.size, Y.ptr, Y.size, M, K,
