@@ -251,6 +251,8 @@ def main():
     ap.add_argument("--impl", default="zinc_b200", choices=["zinc_b200", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill_gemm"],
                     help="decode: the headline decode step; prefill_gemm: the batched-prefill dequant-GEMM cases")
+    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: the library's one-shot peer all-reduce (default) or NCCL for the hidden-state sums")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug; invalidates the number)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -290,11 +292,23 @@ def main():
         ctx = zb.Context(local_rank, stream=stream.cuda_stream)
         dd = zb.DmmvDispatch(ctx)
 
-        def allreduce(t):
-            dist.all_reduce(t)
+        if world > 1:  # peer exchange of the library: IPC handles travel through the process group
+            handles = [None] * world
+            dist.all_gather_object(handles, ctx.comm_init(rank, world))
+            ctx.comm_connect(handles)
+            dist.barrier()
 
-        def allgather(t, r, n):
-            dist.all_gather_into_tensor(t, t.narrow(0, r * n, n))  # in place: rank r's slice is already there
+        def allreduce(t):
+            if args.collective == "nccl":
+                dist.all_reduce(t)
+            else:
+                ctx.allreduce_sum(t, t.numel())
+
+        def allgather(t, r, n):  # in place: rank r's slice is already there
+            if args.collective == "nccl":
+                dist.all_gather_into_tensor(t, t.narrow(0, r * n, n))
+            else:
+                ctx.allgather(t, t, n, src_offset=r * n * 4)
 
         step = DecodeStep.build(torch, dd, shape, rank=rank, world=world, allreduce=allreduce, allgather=allgather)
         gen = torch.Generator(device="cuda").manual_seed(1234)
@@ -327,6 +341,7 @@ def main():
         if rank == 0:
             sampler.start()
             time.sleep(0.25)
+        barrier()  # every rank enters the timed region together (a rank that starts early waits in its collectives)
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t_wall0 = time.time()
         ev0.record(stream)
@@ -410,7 +425,7 @@ def main():
                 "workload": "qwen3-8b-shaped decode step, batch 1, Q4_K_M mix (Q4_K attn/gate/up, Q6_K down + LM head)",
                 "layers": shape.n_layers, "hidden": shape.hidden, "ffn": shape.ffn, "vocab": shape.vocab,
                 "weight_bytes_per_token": total_bytes,
-                "parallelism": "single GPU" if world == 1 else f"tp{world} (rows: QKV/gate/up/head, K: O/down; NCCL)",
+                "parallelism": "single GPU" if world == 1 else f"tp{world} (rows: QKV/gate/up/head, K: O/down; collectives: {'one-shot peer all-reduce / all-gather kernels' if args.collective == 'peer' else 'NCCL'})",
                 "l2": "inputs larger than L2: 4.88 GB of distinct weights per step, no flush needed",
                 "launch": "CUDA graph replay of the recorded op sequence",
             },
@@ -444,6 +459,7 @@ def main():
         graph.reset()
         del graph
         dist.barrier()
+        ctx.comm_destroy()
         torch.cuda.synchronize()
         dist.destroy_process_group()
         killer.cancel()

@@ -315,6 +315,22 @@ int32_t zc_dequant_rows(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_si
                         void* out, uint64_t out_size,
                         uint64_t first_row, uint32_t n_rows, uint32_t K, uint64_t a_offset);
 
+/* ---- tensor-parallel exchange (no counterpart in the reference, which is single-GPU) -------------
+ * One process per GPU. zc_comm_init allocates this rank's receive buffer (3 MB) and returns its
+ * 64-byte CUDA IPC handle; the host exchanges the handles of all ranks by any means and passes
+ * them, rank-major, to zc_comm_connect. zc_allreduce_sum_f32 then sums buf[0..n) over all ranks
+ * in place with one kernel on the context's stream (peer stores over NVLink, bounded flag wait
+ * -> ZC_ERR_TIMEOUT at the next zc_submit_and_wait); n a multiple of 4, at most 16384; every rank
+ * must issue the same sequence of calls. Sums are formed in rank order: all ranks get identical bits. */
+int32_t zc_comm_init(zc_ctx* ctx, uint32_t rank, uint32_t world, uint8_t* out_handle64);
+int32_t zc_comm_connect(zc_ctx* ctx, const uint8_t* all_handles);
+int32_t zc_allreduce_sum_f32(zc_ctx* ctx, void* buf, uint64_t buf_size, uint64_t offset, uint32_t n);
+/* dst[r*n .. r*n+n) <- rank r's src[0..n) for every rank r (src may be the rank's own slice of dst);
+ * n a multiple of 4, world * n <= 262144. Same protocol and ordering rule as the all-reduce. */
+int32_t zc_allgather_f32(zc_ctx* ctx, const void* src, uint64_t src_size, uint64_t src_offset,
+                         void* dst, uint64_t dst_size, uint64_t dst_offset, uint32_t n);
+int32_t zc_comm_destroy(zc_ctx* ctx);
+
 /* ---- matvec without a context and without any allocation ----------------------------------------
  * No counterpart in the reference (its dispatch layer always owns descriptor pools and buffers).
  * The streaming Q4_K matvec of zc_dmmv, y (+)= W x, with its split-K scratch in a __device__

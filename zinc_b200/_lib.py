@@ -55,6 +55,11 @@ _OPS = {
     "zc_memset": [_vp, _u64, _i32, _u64],
     "zc_set_stream": [_vp],
     "zc_use_own_stream": [],
+    "zc_comm_init": [_u32, _u32, _vp],
+    "zc_comm_connect": [_vp],
+    "zc_allreduce_sum_f32": [_vp, _u64, _u64, _u32],
+    "zc_allgather_f32": [_vp, _u64, _u64, _vp, _u64, _u64, _u32],
+    "zc_comm_destroy": [],
     "zc_begin_record": [],
     "zc_end_record": [C.POINTER(_vp)],
     "zc_replay": [_vp],

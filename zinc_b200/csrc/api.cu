@@ -28,6 +28,10 @@ struct zc_ctx {
     float* scratch_partial = nullptr;     // split-K partial sums of the streaming matvec
     uint32_t* scratch_flags = nullptr; // publication flags (zero between launches)
     int sm_count = 0;
+    // tensor-parallel peer exchange (zc_comm_*)
+    zc::CommArgs comm;
+    uint8_t* comm_local = nullptr;
+    bool comm_open[zc::kCommMaxRanks] = {false};
     char err[512] = {0};
 };
 
@@ -175,11 +179,102 @@ int32_t zc_destroy(zc_ctx* ctx) {
     if (!ctx) return ZC_ERR_INVALID_ARG;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    zc_comm_destroy(ctx);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->scratch_partial) cudaFree(ctx->scratch_partial);
     if (ctx->scratch_flags) cudaFree(ctx->scratch_flags);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
+    return ZC_OK;
+}
+
+int32_t zc_comm_init(zc_ctx* ctx, uint32_t rank, uint32_t world, uint8_t* out_handle) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_comm_init";
+    if (world < 2 || world > kCommMaxRanks || rank >= world || !out_handle)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: need 2 <= world <= %u, rank < world and a 64-byte handle buffer", fn,
+                    kCommMaxRanks);
+    if (ctx->comm_local) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: already initialised", fn);
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&ctx->comm_local), kCommBufBytes);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, fn);
+    e = cudaMemset(ctx->comm_local, 0, kCommBufBytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, ctx->comm_local);
+    if (e != cudaSuccess) {
+        cudaFree(ctx->comm_local);
+        ctx->comm_local = nullptr;
+        return cuda_fail(ctx, e, fn);
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    memcpy(out_handle, &h, 64);
+    ctx->comm = CommArgs();
+    ctx->comm.rank = rank;
+    ctx->comm.world = world;
+    ctx->comm.status = ctx->status_dev;
+    ctx->comm.peers[rank] = ctx->comm_local;
+    return ZC_OK;
+}
+
+int32_t zc_comm_connect(zc_ctx* ctx, const uint8_t* all_handles) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_comm_connect";
+    if (!ctx->comm_local || !all_handles) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: call zc_comm_init first", fn);
+    for (uint32_t r = 0; r < ctx->comm.world; ++r) {
+        if (r == ctx->comm.rank || ctx->comm_open[r]) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, all_handles + (size_t)r * 64, 64);
+        void* p = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, fn);
+        ctx->comm.peers[r] = static_cast<uint8_t*>(p);
+        ctx->comm_open[r] = true;
+    }
+    return ZC_OK;
+}
+
+int32_t zc_allreduce_sum_f32(zc_ctx* ctx, void* buf, uint64_t buf_size, uint64_t offset, uint32_t n) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_allreduce_sum_f32";
+    if (!ctx->comm_local) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: no communicator (zc_comm_init / zc_comm_connect)", fn);
+    for (uint32_t r = 0; r < ctx->comm.world; ++r)
+        if (!ctx->comm.peers[r]) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: rank %u is not connected", fn, r);
+    if (n == 0 || (n & 3u) || (uint64_t)n * 4 > kCommSlotBytes)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: n=%u must be a non-zero multiple of 4, at most %llu", fn, n,
+                    (unsigned long long)(kCommSlotBytes / 4));
+    ZC_TRY(check_vec(ctx, fn, "buf", buf, buf_size, offset, (uint64_t)n * 4, 16));
+    const cudaError_t e = launch_allreduce_oneshot(ctx->comm, f32m(buf, offset), n, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_allgather_f32(zc_ctx* ctx, const void* src, uint64_t src_size, uint64_t src_offset, void* dst,
+                         uint64_t dst_size, uint64_t dst_offset, uint32_t n) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_allgather_f32";
+    if (!ctx->comm_local) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: no communicator (zc_comm_init / zc_comm_connect)", fn);
+    for (uint32_t r = 0; r < ctx->comm.world; ++r)
+        if (!ctx->comm.peers[r]) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: rank %u is not connected", fn, r);
+    if (n == 0 || (n & 3u) || (uint64_t)n * 4 * ctx->comm.world > kCommGatherBytes)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: n=%u must be a non-zero multiple of 4 with world * n <= %llu", fn, n,
+                    (unsigned long long)(kCommGatherBytes / 4));
+    ZC_TRY(check_vec(ctx, fn, "src", src, src_size, src_offset, (uint64_t)n * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "dst", dst, dst_size, dst_offset, (uint64_t)n * 4 * ctx->comm.world, 16));
+    const cudaError_t e = launch_allgather_oneshot(ctx->comm, f32p(src, src_offset), f32m(dst, dst_offset), n,
+                                                   ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_comm_destroy(zc_ctx* ctx) {
+    ZC_ENTER(ctx);
+    if (!ctx->comm_local) return ZC_OK;
+    cudaStreamSynchronize(ctx->stream);
+    for (uint32_t r = 0; r < kCommMaxRanks; ++r)
+        if (ctx->comm_open[r]) {
+            cudaIpcCloseMemHandle(ctx->comm.peers[r]);
+            ctx->comm_open[r] = false;
+        }
+    cudaFree(ctx->comm_local);
+    ctx->comm_local = nullptr;
+    ctx->comm = CommArgs();
     return ZC_OK;
 }
 

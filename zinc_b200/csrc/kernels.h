@@ -92,6 +92,27 @@ cudaError_t launch_moe_route_scatter(const uint32_t* routing, const float* src, 
                                      uint32_t hidden, uint32_t k, uint32_t routing_stride, cudaStream_t s,
                                      uint64_t* launches);
 
+// ---- one-shot all-reduce over peer memory (comm.cu) -------------------------------------------
+constexpr uint32_t kCommMaxRanks = 8;
+constexpr size_t kCommSlotBytes = 64 * 1024;  // largest vector: 16384 floats
+constexpr size_t kCommGatherBytes = 1024 * 1024;  // largest gathered vector: 262144 floats over all ranks
+constexpr size_t kCommGatherOffset = 2 * kCommMaxRanks * kCommSlotBytes;       // [2 parities][kCommGatherBytes]
+constexpr size_t kCommFlagOffset = kCommGatherOffset + 2 * kCommGatherBytes;   // reduce flags [2][ranks]
+constexpr size_t kCommGatherFlagOffset = kCommFlagOffset + 2 * kCommMaxRanks * sizeof(uint32_t);
+constexpr size_t kCommEpochOffset = kCommGatherFlagOffset + 2 * kCommMaxRanks * sizeof(uint32_t);
+// words at kCommEpochOffset: [0] reduce epoch, [1] gather epoch, [2] gather arrivals, [3] gather departures
+constexpr size_t kCommBufBytes = kCommEpochOffset + 256;
+struct CommArgs {
+    uint8_t* peers[kCommMaxRanks];  // receive buffer of every rank as mapped in this process; [rank] is local
+    uint32_t rank = 0, world = 0;
+    uint32_t* status = nullptr;
+};
+// buf[0..n) <- sum over ranks, in place; n a multiple of 4, n * 4 <= kCommSlotBytes
+cudaError_t launch_allreduce_oneshot(const CommArgs& c, float* buf, uint32_t n, cudaStream_t s, uint64_t* launches);
+// dst[r*n .. r*n+n) <- rank r's src[0..n) for every r; n a multiple of 4, world * n * 4 <= kCommGatherBytes
+cudaError_t launch_allgather_oneshot(const CommArgs& c, const float* src, float* dst, uint32_t n, cudaStream_t s,
+                                     uint64_t* launches);
+
 // Tensor-core dequant-GEMM: D[col][row] = sum_k A[row][k] B[col][k].
 // act_bf16: B holds bf16 (else f32). Returns cudaErrorNotSupported for types
 // without a tile dequantiser.

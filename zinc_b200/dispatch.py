@@ -168,6 +168,30 @@ class Context:
     def free_recording(self, recording: int) -> None:
         self.call("zc_free_recording", C.c_void_p(recording))
 
+    # -- tensor-parallel exchange ------------------------------------------------------------
+    def comm_init(self, rank: int, world: int) -> bytes:
+        """Allocate this rank's receive buffer; returns its 64-byte IPC handle for the other ranks."""
+        h = (C.c_uint8 * 64)()
+        self.call("zc_comm_init", rank, world, C.cast(h, C.c_void_p))
+        return bytes(h)
+
+    def comm_connect(self, handles: "list[bytes]") -> None:
+        """Map the receive buffers of all ranks (handles in rank order, this rank's own included)."""
+        blob = b"".join(handles)
+        arr = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        self.call("zc_comm_connect", C.cast(arr, C.c_void_p))
+
+    def allreduce_sum(self, buf, n: int, offset: int = 0) -> None:
+        b = _buf(buf)
+        self.call("zc_allreduce_sum_f32", b.ptr, b.size, offset, n)
+
+    def allgather(self, src, dst, n: int, src_offset: int = 0, dst_offset: int = 0) -> None:
+        a, b = _buf(src), _buf(dst)
+        self.call("zc_allgather_f32", a.ptr, a.size, src_offset, b.ptr, b.size, dst_offset, n)
+
+    def comm_destroy(self) -> None:
+        self.call("zc_comm_destroy")
+
     def close(self) -> None:
         if getattr(self, "_h", None):
             self._lib.zc_destroy(self._h)
