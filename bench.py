@@ -194,6 +194,98 @@ def cpu_baseline_leg(torch, step, budget_s=12.0):
                       f"{nbytes} weight bytes x {reps} repetitions"}
 
 
+def _timed_graph(torch, stream, fn, reps):
+    """Capture fn() once into a CUDA graph on `stream`, replay it `reps` times, return ms per replay."""
+    fn()
+    stream.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        fn()
+    for _ in range(3):
+        g.replay()
+    stream.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(reps):
+        g.replay()
+    ev1.record(stream)
+    stream.synchronize()
+    return ev0.elapsed_time(ev1) / reps
+
+
+def dmmv_single_bench(torch, zb, args, local_rank):
+    """One Q4_K 4096 x 4096 matvec (9 437 184 weight bytes), 64 weight copies in rotation (604 MB > L2),
+    and the same on one copy (L2-hot), labelled."""
+    from zinc_b200 import synth
+
+    peak, peak_kind = measured_peaks()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ctx = zb.Context(local_rank, stream=stream.cuda_stream)
+        dd = zb.DmmvDispatch(ctx)
+        M = K = 4096
+        copies = 64
+        ws = [synth.torch_quant_matrix(zb.Q4_K, M, K, f"cuda:{local_rank}", 300 + i) for i in range(copies)]
+        x = torch.randn(K, device="cuda")
+        y = torch.zeros(M, device="cuda")
+        wbytes = M * zb.row_bytes(zb.Q4_K, K)
+
+        def rotating():
+            for w in ws:
+                dd.recordDispatch(zb.Q4_K, w, x, y, M, K)
+
+        def hot():
+            for _ in range(copies):
+                dd.recordDispatch(zb.Q4_K, ws[0], x, y, M, K)
+
+        reps = max(5, min(args.steps, 50))
+        for label, fn in (("64 weight copies in rotation (604 MB, larger than L2)", rotating),
+                          ("one weight copy, L2-hot", hot)):
+            us = _timed_graph(torch, stream, fn, reps) * 1e3 / copies
+            gbs = wbytes / us / 1e3
+            print(json.dumps({
+                "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": 1, "steps": reps * copies, "warmup": 3 * copies,
+                "ms_per_step": us / 1e3, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": "single Q4_K matvec 4096x4096, f32 x", "l2": label,
+                           "weight_bytes": wbytes, "reference_bytes_model": wbytes + 4 * K + 4 * M},
+                "gpu_launches": reps * copies,
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                             "frac": gbs / peak, "traffic": None},
+            }), flush=True)
+    return 0
+
+
+def moe_decode_bench(torch, zb, args, local_rank):
+    """One token through the MoE layers of the two MoE configurations (batch 1, single GPU)."""
+    from zinc_b200.moe_step import GPT_OSS_MOE, QWEN35_MOE, MoeDecode
+
+    peak, peak_kind = measured_peaks()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        ctx = zb.Context(local_rank, stream=stream.cuda_stream)
+        dd = zb.DmmvDispatch(ctx)
+        for name, shape in (("qwen3.5-35b-a3b-like MoE layers (256 experts top-8 + shared, Q4_K / Q6_K)", QWEN35_MOE),
+                            ("gpt-oss-20b-shaped MoE layers (32 experts top-4, MXFP4)", GPT_OSS_MOE)):
+            step = MoeDecode.build(torch, dd, shape)
+            launches = step.record()
+            reps = max(20, min(args.steps, 200))
+            ms = _timed_graph(torch, stream, step.record, reps)
+            gbs = shape.weight_bytes() / (ms * 1e-3) / 1e9
+            print(json.dumps({
+                "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": 1, "steps": reps, "warmup": 4,
+                "ms_per_step": ms, "higher_is_better": True, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": name + ", decode batch 1", "layers": shape.n_layers,
+                           "weight_bytes_per_token": shape.weight_bytes(),
+                           "l2": "weights touched per token (all layers) are larger than L2"},
+                "gpu_launches": launches * reps, "gpu_launches_per_step": launches,
+                "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                             "frac": gbs / peak, "traffic": None},
+            }), flush=True)
+            del step
+            torch.cuda.empty_cache()
+    return 0
+
+
 def prefill_gemm_bench(torch, zb, args, local_rank):
     """Batched-prefill dequant-GEMM D[T][M] = X[T][K] W[M][K]^T (bf16 activations, f32 out), one JSON
     line per case: gate-shaped Q4_K 12288 x 4096 and down-shaped Q6_K 4096 x 12288 at T = 128, 512,
@@ -249,8 +341,9 @@ def main():
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="zinc_b200", choices=["zinc_b200", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill_gemm"],
-                    help="decode: the headline decode step; prefill_gemm: the batched-prefill dequant-GEMM cases")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill_gemm", "dmmv_single", "moe_decode"],
+                    help="decode: the headline decode step; prefill_gemm: the batched-prefill dequant-GEMM cases; "
+                         "dmmv_single: one Q4_K 4096x4096 matvec; moe_decode: the two MoE layers at batch 1")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: the library's one-shot peer all-reduce (default) or NCCL for the hidden-state sums")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug; invalidates the number)")
@@ -285,6 +378,10 @@ def main():
 
     if args.workload == "prefill_gemm":
         return prefill_gemm_bench(torch, zb, args, local_rank)
+    if args.workload == "dmmv_single":
+        return dmmv_single_bench(torch, zb, args, local_rank)
+    if args.workload == "moe_decode":
+        return moe_decode_bench(torch, zb, args, local_rank)
 
     stream = torch.cuda.Stream()
     shape = StepShape() if not args.layers else StepShape(n_layers=args.layers)

@@ -106,3 +106,14 @@ def test_shards_are_byte_ranges():
         ks = [shard.k_shard(w, zb.Q5_K, M, K, r, world).reshape(M, -1) for r in range(world)]
         assert np.array_equal(np.concatenate(ks, axis=1).reshape(-1), flat)
         assert all(k.shape[1] == rb // world for k in ks)
+
+
+def test_moe_bytes_per_token():
+    """Weight bytes one token reads per MoE layer: routed experts + shared expert + f32 router."""
+    sys.path.insert(0, ROOT)
+    from zinc_b200.moe_step import GPT_OSS_MOE, QWEN35_MOE
+
+    assert QWEN35_MOE.expert_bytes() == 2_039_808
+    assert QWEN35_MOE.layer_weight_bytes() == 8 * 2_039_808 + 2_039_808 + 2_097_152
+    assert GPT_OSS_MOE.expert_bytes() == 3 * 4_406_400
+    assert GPT_OSS_MOE.layer_weight_bytes() == 52_876_800 + 32 * 2880 * 4

@@ -1,0 +1,126 @@
+"""MoE decode layers of the two MoE benchmark configurations, as op sequences over the dispatch mirror.
+
+`QwenMoeLayer`: hidden 2048, 256 routed experts + 1 shared, top-8, expert FFN 512, gate/up Q4_K and
+down Q6_K, GPU-side routing with softmax over all experts then renormalisation. Op order follows the
+reference's GPU-routed MoE layer (src/compute/forward.zig:6139-6545): router DMMV, softmax_topk,
+fused gate+up expert DMMV, SwiGLU, fused down + weighted accumulate, then the shared expert.
+
+`GptOssMoeLayer`: hidden 2880, 32 experts top-4, expert FFN 2880, MXFP4 gate / up / down, routing by
+top-k then softmax, `swiglu_oai` (src/compute/forward.zig:6712-6930; biases are not part of the
+matmul path and are left out).
+
+Attention, norms and the residual stream are stood in for by fixed N(0,1) vectors, as in the dense
+decode step.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import List
+
+from . import synth
+from ._lib import F32, MXFP4, Q4_K, Q6_K, ROUTE_SOFTMAX_ALL_RENORM, ROUTE_TOPK_THEN_SOFTMAX
+from .dispatch import DmmvDispatch, row_bytes
+
+
+@dataclass
+class MoeShape:
+    hidden: int
+    n_experts: int
+    top_k: int
+    ffn: int
+    t_gate_up: int
+    t_down: int
+    rule: int
+    shared: bool
+    oai: bool
+    n_layers: int
+
+    def expert_bytes(self) -> int:
+        return 2 * self.ffn * row_bytes(self.t_gate_up, self.hidden) + self.hidden * row_bytes(self.t_down, self.ffn)
+
+    def layer_weight_bytes(self) -> int:
+        """Weight bytes one token reads in one layer: selected experts, shared expert, f32 router."""
+        return (self.top_k + (1 if self.shared else 0)) * self.expert_bytes() + self.n_experts * self.hidden * 4
+
+    def weight_bytes(self) -> int:
+        return self.n_layers * self.layer_weight_bytes()
+
+
+QWEN35_MOE = MoeShape(hidden=2048, n_experts=256, top_k=8, ffn=512, t_gate_up=Q4_K, t_down=Q6_K,
+                      rule=ROUTE_SOFTMAX_ALL_RENORM, shared=True, oai=False, n_layers=40)
+GPT_OSS_MOE = MoeShape(hidden=2880, n_experts=32, top_k=4, ffn=2880, t_gate_up=MXFP4, t_down=MXFP4,
+                       rule=ROUTE_TOPK_THEN_SOFTMAX, shared=False, oai=True, n_layers=24)
+
+
+@dataclass
+class MoeLayerWeights:
+    router: object
+    wg: object
+    wu: object
+    wd: object
+    sg: object = None
+    su: object = None
+    sd: object = None
+
+
+@dataclass
+class MoeDecode:
+    shape: MoeShape
+    dd: DmmvDispatch
+    layers: List[MoeLayerWeights] = field(default_factory=list)
+    x: object = None
+    hidden: object = None
+    logits: object = None
+    routing: object = None
+    yg: object = None
+    yu: object = None
+    act: object = None
+    sact: object = None
+
+    @staticmethod
+    def build(torch, dd: DmmvDispatch, shape: MoeShape, seed: int = 3) -> "MoeDecode":
+        s = shape
+        dev = f"cuda:{torch.cuda.current_device()}"
+        st = MoeDecode(shape=s, dd=dd)
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        for layer in range(s.n_layers):
+            sd = seed * 7919 + layer * 16
+            w = MoeLayerWeights(
+                router=torch.randn(s.n_experts, s.hidden, device=dev, generator=gen) * 0.05,
+                wg=synth.torch_quant_matrix(s.t_gate_up, s.n_experts * s.ffn, s.hidden, dev, sd + 0),
+                wu=synth.torch_quant_matrix(s.t_gate_up, s.n_experts * s.ffn, s.hidden, dev, sd + 1),
+                wd=synth.torch_quant_matrix(s.t_down, s.n_experts * s.hidden, s.ffn, dev, sd + 2))
+            if s.shared:
+                w.sg = synth.torch_quant_matrix(s.t_gate_up, s.ffn, s.hidden, dev, sd + 3)
+                w.su = synth.torch_quant_matrix(s.t_gate_up, s.ffn, s.hidden, dev, sd + 4)
+                w.sd = synth.torch_quant_matrix(s.t_down, s.hidden, s.ffn, dev, sd + 5)
+            st.layers.append(w)
+        f32 = dict(dtype=torch.float32, device=dev)
+        st.x = torch.randn(s.hidden, device=dev, generator=gen)
+        st.hidden = torch.zeros(s.hidden, **f32)
+        st.logits = torch.zeros(s.n_experts, **f32)
+        st.routing = torch.zeros(2 * s.top_k, dtype=torch.int32, device=dev)
+        st.yg = torch.zeros(s.top_k * s.ffn, **f32)
+        st.yu = torch.zeros(s.top_k * s.ffn, **f32)
+        st.act = torch.zeros(s.top_k * s.ffn, **f32)
+        st.sact = torch.zeros(s.ffn, **f32)
+        return st
+
+    def record(self) -> int:
+        """Enqueue one token's MoE layers; returns the number of kernels launched."""
+        s, dd = self.shape, self.dd
+        n0 = dd.ctx.launch_count
+        es_gu = s.ffn * row_bytes(s.t_gate_up, s.hidden)
+        es_d = s.hidden * row_bytes(s.t_down, s.ffn)
+        for w in self.layers:
+            dd.recordDispatch(F32, w.router, self.x, self.logits, s.n_experts, s.hidden)
+            dd.dispatchSoftmaxTopk(self.logits, self.routing, s.n_experts, s.top_k, rule=s.rule)
+            dd.dispatchMoeFusedGateUp(s.t_gate_up, w.wg, w.wu, self.x, self.yg, self.yu, self.routing, s.ffn,
+                                      s.hidden, es_gu, s.top_k, 0)
+            dd.dispatchSwiglu(self.yg, self.yu, self.act, s.top_k * s.ffn, oai=s.oai)
+            dd.dispatchMoeFusedDownAcc(s.t_down, w.wd, self.act, self.hidden, self.routing, s.hidden, s.ffn, es_d,
+                                       s.top_k, s.ffn)
+            if s.shared:
+                dd.dispatchDmmvFusedGateUpSwiglu(s.t_gate_up, w.sg, w.su, self.x, self.sact, s.ffn, s.hidden)
+                dd.recordDispatch(s.t_down, w.sd, self.sact, self.hidden, s.hidden, s.ffn, acc_mode=1)
+        return dd.ctx.launch_count - n0
