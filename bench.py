@@ -266,6 +266,10 @@ def moe_decode_bench(torch, zb, args, local_rank):
         dd = zb.DmmvDispatch(ctx)
         for name, shape in (("qwen3.5-35b-a3b-like MoE layers (256 experts top-8 + shared, Q4_K / Q6_K)", QWEN35_MOE),
                             ("gpt-oss-20b-shaped MoE layers (32 experts top-4, MXFP4)", GPT_OSS_MOE)):
+            if args.layers:
+                import dataclasses
+
+                shape = dataclasses.replace(shape, n_layers=args.layers)
             step = MoeDecode.build(torch, dd, shape)
             launches = step.record()
             reps = max(20, min(args.steps, 200))

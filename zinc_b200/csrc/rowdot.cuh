@@ -164,6 +164,25 @@ __device__ __forceinline__ void rowdot_q8_0(const uint8_t* const (&rows)[NR], co
 
 // MXFP4 (17 B): E8M0 scale byte, 16 bytes of E2M1 nibbles; low nibble j -> element j,
 // high nibble -> element j+16.
+// The eight E2M1 magnitudes {0, .5, 1, 1.5, 2, 3, 4, 6} as f32 have bit patterns 0x0000, 0x3F00, 0x3F80,
+// 0x3FC0, 0x4000, 0x4040, 0x4080, 0x40C0 in their upper halves: two byte tables, looked up four
+// nibbles at a time with one byte permute each, then one permute per element assembles the float and
+// the nibble's bit 3 is moved to the sign bit. Values are exactly those of the table in
+// src/compute/forward.zig:445.
+__device__ __forceinline__ void e2m1x4_to_f32(uint32_t nib16, float (&out)[4]) {
+    // nib16: four nibbles in bits 0..15; out[i] = value of nibble i
+    const uint32_t sel = nib16 & 0x7777u;
+    const uint32_t hi = __byte_perm(0x3F3F3F00u, 0x40404040u, sel);  // top bytes
+    const uint32_t lo = __byte_perm(0xC0800000u, 0xC0804000u, sel);  // second bytes
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        // bytes (LSB first): 0, 0, lo[i], hi[i]; 'lo' is operand a (bytes 0..3), 'hi' operand b (bytes 4..7)
+        const uint32_t mag = __byte_perm(lo, hi, 0x0000u | ((4u + i) << 12) | ((uint32_t)i << 8)) & 0xFFFF0000u;
+        const uint32_t sign = (nib16 << (28 - 4 * i)) & 0x80000000u;
+        out[i] = __uint_as_float(mag | sign);
+    }
+}
+
 template <int NR>
 __device__ __forceinline__ void rowdot_mxfp4(const uint8_t* const (&rows)[NR], const float* __restrict__ x,
                                              uint32_t K, int lane, float (&acc)[NR]) {
@@ -186,10 +205,15 @@ __device__ __forceinline__ void rowdot_mxfp4(const uint8_t* const (&rows)[NR], c
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
 #pragma unroll
-                for (int bb = 0; bb < 4; ++bb) {
-                    const uint32_t byte = (q[w] >> (8 * bb)) & 0xFFu;
-                    s = fmaf(e2m1_to_f32(byte & 0xFu), xv[4 * w + bb], s);
-                    s = fmaf(e2m1_to_f32(byte >> 4), xv[4 * w + bb + 16], s);
+                for (int hf = 0; hf < 2; ++hf) {
+                    // 16 bits = bytes 4w+2hf, 4w+2hf+1: nibbles (lo0, hi0, lo1, hi1) = elements j, j+16, j+1, j+17
+                    float v[4];
+                    e2m1x4_to_f32((q[w] >> (16 * hf)) & 0xFFFFu, v);
+                    const int j = 4 * w + 2 * hf;
+                    s = fmaf(v[0], xv[j], s);
+                    s = fmaf(v[1], xv[j + 16], s);
+                    s = fmaf(v[2], xv[j + 1], s);
+                    s = fmaf(v[3], xv[j + 17], s);
                 }
             }
             acc[r] = fmaf(d, s, acc[r]);
