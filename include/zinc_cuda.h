@@ -201,10 +201,11 @@ int32_t zc_dmmv_batch(zc_ctx* ctx, uint32_t type,
  * and the Metal tiled GEMMs (src/shaders/metal/gemm_q4k.metal:54-225, gemm_q6k.metal:38-68).
  * B and D are column-major with element strides stride_b / stride_d; b_offset
  * and d_offset count ELEMENTS, a_offset BYTES (src/compute/dmmv.zig:139-145).
- * act_type selects B's element type: ZC_F32 (rounded to bf16 on load) or
- * ZC_BF16. D is f32. Weights are dequantised to bf16 tiles and multiplied with
- * f32 accumulation. K must be a multiple of 256 for K-quants (InvalidArgument
- * otherwise, as the reference). */
+ * act_type selects B's element type, ZC_F32 or ZC_BF16; D is f32. bf16 activations with Q4_K or Q6_K
+ * weights (16-byte aligned, N >= 16, stride_b a multiple of 8; Q6_K also K a multiple of 2048) run
+ * on the tensor cores: weights dequantised to bf16 tiles, f32 accumulation in tensor memory. Every
+ * other combination (f32 activations included, which keep f32 precision) runs a CUDA-core kernel.
+ * K must be a multiple of 256 for K-quants (InvalidArgument otherwise, as the reference). */
 int32_t zc_mul_mm(zc_ctx* ctx, uint32_t type,
                   const void* A, uint64_t a_size, const void* B, uint64_t b_size,
                   void* D, uint64_t d_size,
@@ -252,8 +253,8 @@ int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type,
  * routing is the flattened [n_tokens][n_experts_used] id table; strides in
  * elements. K % 256 != 0 returns ZC_ERR_INVALID_ARG for K-quants. Replaces
  * recordMoeBatchedDispatch (src/compute/dmmv.zig:746-792;
- * src/shaders/dmmv_q4k_moe_batched.comp:70-164). Tokens that share an expert
- * are grouped so each expert's weights are read once. */
+ * src/shaders/dmmv_q4k_moe_batched.comp:70-164). Like the reference's kernel, every (token, slot)
+ * pair is computed on its own; tokens that share an expert are not grouped yet. */
 int32_t zc_moe_dmmv_batched(zc_ctx* ctx, uint32_t type,
                             const void* A, uint64_t a_size, const void* X, uint64_t x_size,
                             void* Y, uint64_t y_size, const void* routing, uint64_t routing_size,
