@@ -3,8 +3,8 @@
 // Every warp is an independent worker: it owns a contiguous range of work units (16 rows x
 // kCB 256-weight super-blocks), prefetches them with coalesced 16-byte asynchronous copies
 // (cp.async into the warp's own ring of padded row segments, depth kDepth; bulk TMA copies were
-// measured at ~14 cycles of issue each per SM, too slow for 288-byte row segments), masks the 4-bit quants into int8 lanes (one logic op per four
-// weights) and feeds them to the int8 tensor cores as a 16-row dot-product engine with exact
+// measured at ~14 cycles of issue each per SM, too slow for 288-byte row segments), masks the 4-bit
+// quants into int8 lanes (one logic op per four weights) and feeds them to the int8 tensor cores as a 16-row dot-product engine with exact
 // s32 accumulation. There is no block-wide synchronisation after the activation vector has
 // been converted. K is split across workers so that all SMs stream the same number of bytes;
 // a tile that spans several workers is finished by the worker that owns its first unit, which
@@ -52,7 +52,6 @@ struct Smem {
     float* sx;       // per 32-element sub-block sum of X
     float* xs;       // per super-block 2^-f
     uint8_t* ring;   // [kWarps][kDepth] stages of 16 padded row segments
-    uint64_t* full;  // [kWarps][kDepth] "stage landed" barriers
     float* spartial; // [kWarps][32] partial sums published inside the CTA
     volatile uint32_t* sflags;  // [kWarps]
 };
@@ -62,7 +61,7 @@ __host__ __device__ inline size_t smem_bytes(uint32_t K, int kWarps) {
     n += (size_t)(K / 32) * 4 + (size_t)(K / 256) * 4;
     n = (n + 127) & ~size_t(127);
     n += (size_t)kWarps * kWarpRing;
-    n += (size_t)kWarps * 32 * 4 + (size_t)kWarps * 4 + (size_t)kWarps * kDepth * 8 + 16;
+    n += (size_t)kWarps * 32 * 4 + (size_t)kWarps * 4 + 16;
     return n + 128;
 }
 
@@ -80,8 +79,6 @@ __device__ inline Smem carve(uint8_t* base, uint32_t K, int kWarps) {
     p = (p + 127) & ~uintptr_t(127);
     s.ring = reinterpret_cast<uint8_t*>(p);
     p += (size_t)kWarps * kWarpRing;
-    s.full = reinterpret_cast<uint64_t*>(p);
-    p += (size_t)kWarps * kDepth * 8;
     s.spartial = reinterpret_cast<float*>(p);
     p += (size_t)kWarps * 32 * 4;
     s.sflags = reinterpret_cast<volatile uint32_t*>(p);
