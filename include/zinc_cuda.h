@@ -150,6 +150,17 @@ int32_t zc_dmmv(zc_ctx* ctx, uint32_t type,
                 uint32_t M, uint32_t K,
                 uint64_t a_offset, uint64_t x_offset, uint64_t y_offset, uint32_t acc_mode);
 
+/* Fused RMS norm + f32 router matvec (src/shaders/rms_norm_dmmv_f32.comp:68-127, push block
+ * RmsNormDmmvF32Push src/compute/elementwise.zig:177-181): rms_inv = 1/sqrt(mean(hidden^2) + eps),
+ * norm_out[i] = norm_weights[i] * (hidden[i] * rms_inv) (optional; must not alias hidden),
+ * logits[m] = sum_i router_weights[m][i] * norm_out[i]. All f32; K a multiple of 4. */
+int32_t zc_rms_norm_dmmv_f32(zc_ctx* ctx, const void* hidden, uint64_t hidden_size,
+                             const void* norm_weights, uint64_t norm_size,
+                             const void* router_weights, uint64_t router_size,
+                             void* norm_out, uint64_t norm_out_size,
+                             void* logits, uint64_t logits_size,
+                             uint32_t M, uint32_t K, float eps);
+
 /* Grouped matvec: y_i (+)= W_i x for n = 1..3 matrices of one type that share x and K, e.g. the Q, K
  * and V projections the reference records as three dispatches on the same input
  * (src/compute/forward.zig:4530-4564). One kernel launch when the matrices are Q4_K (16-byte aligned);

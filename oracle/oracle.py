@@ -57,6 +57,8 @@ def lib() -> C.CDLL:
                                            C.c_uint32, C.c_int32]
         L.zo_topk_softmax.argtypes = [f32p, C.c_uint32, C.c_uint32, u32p, f32p]
         L.zo_topk_softmax_weight.argtypes = [f32p, C.c_uint32, C.c_uint32, u32p, f32p]
+        L.zo_rms_norm_dmmv_f32.argtypes = [f32p, f32p, f32p, f32p, C.POINTER(C.c_double), C.c_uint32, C.c_uint32,
+                                           C.c_float]
         L.zo_swiglu.argtypes = [f32p, f32p, f32p, C.c_uint32]
         L.zo_swiglu_oai.argtypes = [f32p, f32p, f32p, C.c_uint32]
         L.zo_moe_weighted_acc.argtypes = [f32p, f32p, u32p, C.c_uint32, C.c_uint32, C.c_uint32]
@@ -182,6 +184,18 @@ def topk_softmax_weight(logits, k: int):
     w = np.empty(k, dtype=np.float32)
     lib().zo_topk_softmax_weight(_p(lg, C.c_float), lg.size, k, _p(ids, C.c_uint32), _p(w, C.c_float))
     return ids, w
+
+
+def rms_norm_dmmv_f32(x, norm_w, W, M: int, K: int, eps: float):
+    """(normalised vector f32 [K], router logits f64 [M]) of the fused RMS norm + f32 router matvec."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(norm_w, dtype=np.float32)
+    Wm = np.ascontiguousarray(W, dtype=np.float32)
+    xn = np.empty(K, dtype=np.float32)
+    logits = np.empty(M, dtype=np.float64)
+    lib().zo_rms_norm_dmmv_f32(_p(x, C.c_float), _p(w, C.c_float), _p(Wm, C.c_float), _p(xn, C.c_float),
+                               _p(logits, C.c_double), M, K, eps)
+    return xn, logits
 
 
 def swiglu(gate, up, oai: bool = False) -> np.ndarray:

@@ -644,6 +644,22 @@ void zo_topk_softmax_weight(const float* logits, uint32_t n, uint32_t k, uint32_
 // Activation and combine steps either side of the expert matmuls.
 // ---------------------------------------------------------------------------
 
+// Fused RMS norm + f32 router matvec, src/shaders/rms_norm_dmmv_f32.comp:78-127:
+// rms_inv = 1 / sqrt(sum(x^2) / K + eps); norm_out[i] = w[i] * (x[i] * rms_inv) in f32 with that
+// multiplication order; logits[m] = sum_i W[m][i] * norm_out[i] (accumulated in f64 here).
+void zo_rms_norm_dmmv_f32(const float* x, const float* w, const float* W, float* norm_out, double* logits, uint32_t M,
+                          uint32_t K, float eps) {
+    double ss = 0.0;
+    for (uint32_t i = 0; i < K; ++i) ss += (double)x[i] * (double)x[i];
+    const float rms_inv = (float)(1.0 / std::sqrt(ss / (double)K + (double)eps));
+    for (uint32_t i = 0; i < K; ++i) norm_out[i] = w[i] * (x[i] * rms_inv);
+    for (uint32_t m = 0; m < M; ++m) {
+        double acc = 0.0;
+        for (uint32_t i = 0; i < K; ++i) acc += (double)W[(size_t)m * K + i] * (double)norm_out[i];
+        logits[m] = acc;
+    }
+}
+
 // src/shaders/swiglu.comp:25-33
 void zo_swiglu(const float* gate, const float* up, float* out, uint32_t n) {
     for (uint32_t i = 0; i < n; ++i) {

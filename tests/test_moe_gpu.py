@@ -229,3 +229,34 @@ def test_weighted_acc_swiglu_count_pack_scatter(gpu, oracle):
     want = oracle.moe_route_scatter(routing, src, dst0, T, H, k, stride)
     assert canary_intact(dst, T * H)
     assert rel_l2(dst[:T * H].cpu().numpy(), want) <= 1e-6
+
+
+@pytest.mark.parametrize("M,K", [(256, 2048), (32, 2880), (7, 64)])
+def test_rms_norm_dmmv_f32(gpu, oracle, M, K):
+    """Fused RMS norm + f32 router matvec (src/shaders/rms_norm_dmmv_f32.comp) and the plain small-M f32
+    matvec that shares its kernel."""
+    torch, ctx, dd = gpu
+    g = synth.rng(410, M + K)
+    x = synth.activations(g, K) * np.float32(3.0)
+    w = (synth.activations(g, K) * np.float32(0.1) + np.float32(1.0)).astype(np.float32)
+    W = synth.activations(g, M, K) * np.float32(0.05)
+    eps = 1e-6
+    xn, logits = oracle.rms_norm_dmmv_f32(x, w, W, M, K, eps)
+    xd, wd, Wd = dev(torch, x), dev(torch, w), dev(torch, W.reshape(-1))
+    out_n = out_with_canary(torch, K)
+    out_l = out_with_canary(torch, M)
+    dd.dispatchRmsNormDmmvF32(xd, wd, Wd, out_n, out_l, M, K, eps)
+    ctx.submit_and_wait()
+    assert canary_intact(out_n, K) and canary_intact(out_l, M)
+    assert rel_l2(out_n[:K].cpu().numpy(), xn) <= 1e-6
+    assert rel_l2(out_l[:M].cpu().numpy(), logits) <= 1e-5
+    # without the normalised-vector output, and the plain f32 matvec on the same rows
+    out_l2 = out_with_canary(torch, M)
+    dd.dispatchRmsNormDmmvF32(xd, wd, Wd, None, out_l2, M, K, eps)
+    y = out_with_canary(torch, M)
+    dd.recordDispatch(zb.F32, Wd, xd, y, M, K)
+    ctx.submit_and_wait()
+    assert rel_l2(out_l2[:M].cpu().numpy(), logits) <= 1e-5
+    assert rel_l2(y[:M].cpu().numpy(), W.astype(np.float64) @ x.astype(np.float64)) <= 1e-5
+    with pytest.raises(zb.InvalidArgument):
+        dd.dispatchRmsNormDmmvF32(xd, wd, Wd, xd, out_l, M, K, eps)  # in-place normalisation races

@@ -29,6 +29,7 @@ _OPS = {
     "zc_dmmv_fused_gate_up_swiglu": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32,
                                      _u64, _u64, _u64, _u64],
     "zc_dmmv_sigmoid_acc": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u64, _u64, _u32],
+    "zc_rms_norm_dmmv_f32": [_vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, C.c_float],
     "zc_dmmv_multi": [_u32, _u32, C.POINTER(_vp), C.POINTER(_u64), C.POINTER(_u64), _vp, _u64, _u64,
                       C.POINTER(_vp), C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u32), _u32, _u32],
     "zc_dmmv_batch": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u64, _u64, _u32],

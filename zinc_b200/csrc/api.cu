@@ -433,8 +433,37 @@ int32_t zc_dmmv(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, cons
     a.K = K;
     a.acc_mode = acc_mode;
     attach_scratch(ctx, a);
-    cudaError_t e = launch_dmmv(type, MODE_PLAIN, a, ctx->stream, &ctx->launches);
+    cudaError_t e;
+    if (type == T_F32 && M <= 2048 && (K & 3u) == 0 && acc_mode == 0 && aligned(A, a_offset, 16))
+        // few f32 rows (a router): one CTA per row instead of one warp per row
+        e = launch_rms_norm_dmmv_f32(a.x, nullptr, reinterpret_cast<const float*>(a.A), nullptr, a.y, M, K, 0.f,
+                                     ctx->stream, &ctx->launches);
+    else
+        e = launch_dmmv(type, MODE_PLAIN, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_dmmv");
+}
+
+int32_t zc_rms_norm_dmmv_f32(zc_ctx* ctx, const void* hidden, uint64_t hidden_size, const void* norm_weights,
+                             uint64_t norm_size, const void* router_weights, uint64_t router_size, void* norm_out,
+                             uint64_t norm_out_size, void* logits, uint64_t logits_size, uint32_t M, uint32_t K,
+                             float eps) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_rms_norm_dmmv_f32";
+    if (M == 0 || K == 0 || (K & 3u))  // the reference's dispatch gate: K % 4 == 0 (vec4 reads)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: M and K must be non-zero and K a multiple of 4", fn);
+    ZC_TRY(check_vec(ctx, fn, "hidden", hidden, hidden_size, 0, (uint64_t)K * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "norm_weights", norm_weights, norm_size, 0, (uint64_t)K * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "router_weights", router_weights, router_size, 0, (uint64_t)M * K * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "logits", logits, logits_size, 0, (uint64_t)M * 4, 4));
+    if (norm_out) {
+        ZC_TRY(check_vec(ctx, fn, "norm_out", norm_out, norm_out_size, 0, (uint64_t)K * 4, 16));
+        if (norm_out == hidden)  // other CTAs still read hidden while CTA 0 writes the normalised vector
+            return fail(ctx, ZC_ERR_INVALID_ARG, "%s: norm_out must not alias hidden", fn);
+    }
+    const cudaError_t e = launch_rms_norm_dmmv_f32(f32p(hidden, 0), f32p(norm_weights, 0), f32p(router_weights, 0),
+                                                   norm_out ? f32m(norm_out, 0) : nullptr, f32m(logits, 0), M, K, eps,
+                                                   ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 
 int32_t zc_dmmv_multi(zc_ctx* ctx, uint32_t type, uint32_t n, const void* const* A, const uint64_t* a_size,

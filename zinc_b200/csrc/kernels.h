@@ -82,6 +82,10 @@ cudaError_t launch_moe_weighted_acc(float* a, const float* b, const uint32_t* ro
                                     uint32_t src_stride, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_swiglu(const float* gate, const float* up, float* y, uint32_t n, bool oai, cudaStream_t s,
                           uint64_t* launches);
+// y[m] = sum_k W[m][k] * xn[k], xn = norm_w * (x * rsqrt(mean(x^2) + eps)) (also written to norm_out when
+// given); norm_w == nullptr: xn = x. One CTA per row: for matrices with few rows (routers). K % 4 == 0.
+cudaError_t launch_rms_norm_dmmv_f32(const float* x, const float* norm_w, const float* W, float* norm_out, float* y,
+                                     uint32_t M, uint32_t K, float eps, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_count_experts(const uint32_t* a, uint32_t* counts, uint32_t n_experts, uint32_t ne00,
                                  uint32_t ne01, uint32_t nb00, uint32_t nb01, uint32_t a_offset, cudaStream_t s,
                                  uint64_t* launches);

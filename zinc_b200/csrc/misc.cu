@@ -162,6 +162,61 @@ __global__ void swiglu_kernel(const float* __restrict__ gate, const float* __res
     }
 }
 
+
+// ---- fused RMS norm + f32 router matvec -------------------------------------------------
+// src/shaders/rms_norm_dmmv_f32.comp:68-127: every CTA recomputes rms_inv = rsqrt(mean(x^2) + eps) (same
+// reads in the same order everywhere), CTA 0 also writes the normalised vector
+// norm_out[i] = w[i] * (x[i] * rms_inv), and each CTA dots one router row with the normalised vector.
+// One CTA per row: a router has a few hundred rows at most, so rows are the only parallelism.
+// With norm_w == nullptr the kernel is a plain f32 matvec for small M (no normalisation).
+constexpr int kRouterThreads = 256;
+
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();  // scratch may still be read from a previous call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < kRouterThreads / 32; ++i) t += scratch[i];
+    return t;
+}
+
+__global__ void __launch_bounds__(kRouterThreads) rms_norm_dmmv_f32_kernel(
+    const float* __restrict__ x, const float* __restrict__ norm_w, const float* __restrict__ W,
+    float* __restrict__ norm_out, float* __restrict__ y, uint32_t M, uint32_t K, float eps) {
+    __shared__ float scratch[kRouterThreads / 32];
+    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    const uint32_t K4 = K >> 2;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    float rms_inv = 1.f;
+    if (norm_w) {
+        float ss = 0.f;
+        for (uint32_t i = tid; i < K4; i += kRouterThreads) {
+            const float4 v = __ldg(x4 + i);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = block_sum(ss, scratch);
+        rms_inv = rsqrtf(ss / (float)K + eps);
+    }
+    const float4* w4 = reinterpret_cast<const float4*>(norm_w);
+    const float4* r4 = reinterpret_cast<const float4*>(W + (size_t)row * K);
+    float sum = 0.f;
+    for (uint32_t i = tid; i < K4; i += kRouterThreads) {
+        float4 v = __ldg(x4 + i);
+        if (norm_w) {
+            const float4 w = __ldg(w4 + i);
+            v = make_float4(w.x * (v.x * rms_inv), w.y * (v.y * rms_inv), w.z * (v.z * rms_inv), w.w * (v.w * rms_inv));
+            if (row == 0 && norm_out) reinterpret_cast<float4*>(norm_out)[i] = v;
+        }
+        const float4 r = __ldg(r4 + i);
+        sum += v.x * r.x + v.y * r.y + v.z * r.z + v.w * r.w;
+    }
+    sum = block_sum(sum, scratch);
+    if (tid == 0) y[row] = sum;
+}
+
 // src/shaders/count_experts.comp:58-83: one CTA per expert.
 __global__ void __launch_bounds__(256) count_experts_kernel(const uint32_t* __restrict__ a,
                                                             uint32_t* __restrict__ counts, uint32_t ne00,
@@ -303,6 +358,13 @@ cudaError_t launch_moe_route_scatter(const uint32_t* routing, const float* src, 
     if (total == 0) return cudaSuccess;
     moe_route_scatter_kernel<<<(uint32_t)((total + 255) / 256), 256, 0, s>>>(routing, src, dst, n_tokens, hidden, k,
                                                                              routing_stride);
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rms_norm_dmmv_f32(const float* x, const float* norm_w, const float* W, float* norm_out, float* y,
+                                     uint32_t M, uint32_t K, float eps, cudaStream_t s, uint64_t* launches) {
+    rms_norm_dmmv_f32_kernel<<<M, kRouterThreads, 0, s>>>(x, norm_w, W, norm_out, y, M, K, eps);
     if (launches) ++*launches;
     return cudaGetLastError();
 }

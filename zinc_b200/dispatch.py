@@ -337,6 +337,13 @@ class DmmvDispatch:
                       n_tokens, n_experts if logits_stride is None else logits_stride,
                       2 * k if out_stride is None else out_stride)
 
+    # fused RMS norm + f32 router DMMV (src/shaders/rms_norm_dmmv_f32.comp; src/compute/forward.zig:3469)
+    def dispatchRmsNormDmmvF32(self, hidden, norm_weights, router_weights, norm_out, logits, M, K, eps):
+        h, w, r, lg = _buf(hidden), _buf(norm_weights), _buf(router_weights), _buf(logits)
+        no = _buf(norm_out) if norm_out is not None else Buffer(None, 0)
+        self.ctx.call("zc_rms_norm_dmmv_f32", h.ptr, h.size, w.ptr, w.size, r.ptr, r.size, no.ptr, no.size,
+                      lg.ptr, lg.size, M, K, C.c_float(eps))
+
     # dispatchMoeWeightedAcc (src/shaders/moe_weighted_acc.comp:23-33)
     def dispatchMoeWeightedAcc(self, a, b, routing, n, n_used, src_stride):
         a, b, routing = map(_buf, (a, b, routing))
