@@ -260,3 +260,24 @@ def test_rms_norm_dmmv_f32(gpu, oracle, M, K):
     assert rel_l2(y[:M].cpu().numpy(), W.astype(np.float64) @ x.astype(np.float64)) <= 1e-5
     with pytest.raises(zb.InvalidArgument):
         dd.dispatchRmsNormDmmvF32(xd, wd, Wd, xd, out_l, M, K, eps)  # in-place normalisation races
+
+
+@pytest.mark.parametrize("E,M,K,n_used", [(12, 512, 2048, 8), (5, 100, 1024, 3), (3, 16, 512, 2)])
+def test_moe_fused_gate_up_streaming(gpu, oracle, E, M, K, n_used):
+    """Shapes that take the streaming kernel with device-side expert selection (Q4_K, shared x), run
+    twice in a row with different routings."""
+    torch, ctx, dd = gpu
+    g = synth.rng(202, E * 1000 + M)
+    wg, stride = stacked(g, zb.Q4_K, E, M, K)
+    wu, _ = stacked(g, zb.Q4_K, E, M, K)
+    x = synth.activations(g, 1, K)
+    wgd, wud, xd = dev(torch, wg), dev(torch, wu), dev(torch, x)
+    xs = np.repeat(x, n_used, axis=0)
+    for rep in range(2):
+        ids = np.array([(5 * i + 3 * rep + 1) % E for i in range(n_used)], np.uint32)
+        yg, yu = out_with_canary(torch, n_used * M), out_with_canary(torch, n_used * M)
+        dd.dispatchMoeFusedGateUp(zb.Q4_K, wgd, wud, xd, yg, yu, dev(torch, routing_buf(ids)), M, K, stride, n_used, 0)
+        ctx.submit_and_wait()
+        assert canary_intact(yg, n_used * M) and canary_intact(yu, n_used * M)
+        assert rel_l2(yg[:n_used * M].cpu().numpy(), oracle.moe_dmmv_f64(wg, zb.Q4_K, M, K, stride, ids, K, xs)) <= TOL
+        assert rel_l2(yu[:n_used * M].cpu().numpy(), oracle.moe_dmmv_f64(wu, zb.Q4_K, M, K, stride, ids, K, xs)) <= TOL

@@ -658,7 +658,9 @@ int32_t zc_moe_fused_gate_up(zc_ctx* ctx, uint32_t type, const void* Wg, uint64_
     a.expert_stride = expert_stride;
     a.n_used = n_used;
     a.x_expert_stride = x_expert_stride;
-    cudaError_t e = launch_dmmv(type, MODE_MOE_GATE_UP, a, ctx->stream, &ctx->launches);
+    attach_scratch(ctx, a);
+    cudaError_t e = warp_moe_gate_up_eligible(type, a) ? launch_warp_moe_gate_up(a, ctx->stream, &ctx->launches)
+                                                       : launch_dmmv(type, MODE_MOE_GATE_UP, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 

@@ -75,18 +75,32 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
                 if (row0 + r < a.M) a.y[(size_t)slot * a.M + row0 + r] = acc[r];
         }
     } else if constexpr (MODE == MODE_MOE_GATE_UP) {
+        // NR row pairs (gate row, up row) per warp: independent load chains share the x loads
         const uint32_t slot = blockIdx.y;
-        const uint32_t row = blockIdx.x * kWarps + warp;
-        if (row >= a.M) return;
-        const uint64_t eoff = (uint64_t)__ldg(a.routing + slot) * a.expert_stride + (uint64_t)row * row_bytes;
+        const uint32_t row0 = (blockIdx.x * kWarps + warp) * NR;
+        if (row0 >= a.M) return;
+        const uint64_t ebase = (uint64_t)__ldg(a.routing + slot) * a.expert_stride;
         const float* x = a.x + (size_t)slot * a.x_expert_stride;
-        const uint8_t* rows[2] = {a.A + eoff, a.A2 + eoff};
-        float acc[2] = {0.f, 0.f};
-        rowdot<TYPE, 2, ALIGNED>(rows, x, a.K, lane, acc);
-        const float g = warp_sum(acc[0]), u = warp_sum(acc[1]);
+        const uint8_t* rows[2 * NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const uint64_t off = ebase + (uint64_t)min(row0 + r, a.M - 1) * row_bytes;
+            rows[2 * r] = a.A + off;
+            rows[2 * r + 1] = a.A2 + off;
+        }
+        float acc[2 * NR];
+#pragma unroll
+        for (int r = 0; r < 2 * NR; ++r) acc[r] = 0.f;
+        rowdot<TYPE, 2 * NR, ALIGNED>(rows, x, a.K, lane, acc);
+#pragma unroll
+        for (int r = 0; r < 2 * NR; ++r) acc[r] = warp_sum(acc[r]);
         if (lane == 0) {
-            a.y[(size_t)slot * a.M + row] = g;
-            a.y2[(size_t)slot * a.M + row] = u;
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+                if (row0 + r < a.M) {
+                    a.y[(size_t)slot * a.M + row0 + r] = acc[2 * r];
+                    a.y2[(size_t)slot * a.M + row0 + r] = acc[2 * r + 1];
+                }
         }
     } else if constexpr (MODE == MODE_BATCH) {
         const uint32_t col = blockIdx.y;
@@ -116,20 +130,32 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
         rowdot<TYPE, 1, ALIGNED>(rows, a.x + (size_t)tok * a.x_token_stride, a.K, lane, acc);
         const float v = warp_sum(acc[0]);
         if (lane == 0) a.y[(size_t)tok * a.y_token_stride + (size_t)slot * a.M + row] = v;
-    } else {  // MODE_MOE_DOWN_ACC
-        const uint32_t row = blockIdx.x * kWarps + warp;
-        if (row >= a.M) return;
-        float total = 0.f;
+    } else {  // MODE_MOE_DOWN_ACC: NR rows per warp, the slots in sequence
+        const uint32_t row0 = (blockIdx.x * kWarps + warp) * NR;
+        if (row0 >= a.M) return;
+        float total[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) total[r] = 0.f;
         for (uint32_t s = 0; s < a.n_used; ++s) {
-            const uint8_t* rows[1] = {a.A + (uint64_t)__ldg(a.routing + s) * a.expert_stride +
-                                      (uint64_t)row * row_bytes};
+            const uint8_t* base = a.A + (uint64_t)__ldg(a.routing + s) * a.expert_stride;
+            const uint8_t* rows[NR];
+#pragma unroll
+            for (int r = 0; r < NR; ++r) rows[r] = base + (uint64_t)min(row0 + r, a.M - 1) * row_bytes;
             const float w = __uint_as_float(__ldg(a.routing + a.n_used + s));
-            float acc[1] = {0.f};
-            rowdot<TYPE, 1, ALIGNED>(rows, a.x + (size_t)s * a.x_expert_stride, a.K, lane, acc);
-            total = fmaf(w, acc[0], total);
+            float acc[NR];
+#pragma unroll
+            for (int r = 0; r < NR; ++r) acc[r] = 0.f;
+            rowdot<TYPE, NR, ALIGNED>(rows, a.x + (size_t)s * a.x_expert_stride, a.K, lane, acc);
+#pragma unroll
+            for (int r = 0; r < NR; ++r) total[r] = fmaf(w, acc[r], total[r]);
         }
-        total = warp_sum(total);
-        if (lane == 0) a.y[row] += total;
+#pragma unroll
+        for (int r = 0; r < NR; ++r) total[r] = warp_sum(total[r]);
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < NR; ++r)
+                if (row0 + r < a.M) a.y[row0 + r] += total[r];
+        }
     }
 }
 
@@ -137,7 +163,8 @@ template <uint32_t TYPE, int MODE, int NR, bool ALIGNED>
 cudaError_t launch_one(const DmmvArgs& a, cudaStream_t s) {
     const bool per_slot = MODE == MODE_MOE || MODE == MODE_MOE_GATE_UP || MODE == MODE_BATCH || MODE == MODE_MOE_BATCHED;
     const uint32_t rows_per_cta =
-        kWarps * ((MODE == MODE_PLAIN || MODE == MODE_SIGMOID_ACC || MODE == MODE_MOE || MODE == MODE_BATCH) ? NR : 1);
+        kWarps * ((MODE == MODE_PLAIN || MODE == MODE_SIGMOID_ACC || MODE == MODE_MOE || MODE == MODE_BATCH ||
+                   MODE == MODE_MOE_GATE_UP || MODE == MODE_MOE_DOWN_ACC) ? NR : 1);
     dim3 grid((a.M + rows_per_cta - 1) / rows_per_cta, per_slot ? a.n_used : 1,
               MODE == MODE_MOE_BATCHED ? a.n_tokens : 1);
     dmmv_kernel<TYPE, MODE, NR, ALIGNED><<<grid, kWarps * 32, 0, s>>>(a);
@@ -154,8 +181,13 @@ cudaError_t launch_type(int mode, const DmmvArgs& a, cudaStream_t s) {
         case MODE_GATE_UP_SWIGLU: return launch_one<TYPE, MODE_GATE_UP_SWIGLU, 1, ALIGNED>(a, s);
         case MODE_SIGMOID_ACC: return launch_one<TYPE, MODE_SIGMOID_ACC, 1, ALIGNED>(a, s);
         case MODE_MOE: return launch_one<TYPE, MODE_MOE, 1, ALIGNED>(a, s);
-        case MODE_MOE_GATE_UP: return launch_one<TYPE, MODE_MOE_GATE_UP, 1, ALIGNED>(a, s);
-        case MODE_MOE_DOWN_ACC: return launch_one<TYPE, MODE_MOE_DOWN_ACC, 1, ALIGNED>(a, s);
+        // two rows (row pairs) per warp when there are rows enough to keep every SM busy regardless
+        case MODE_MOE_GATE_UP:
+            return (uint64_t)a.M * a.n_used >= 8192 ? launch_one<TYPE, MODE_MOE_GATE_UP, 2, ALIGNED>(a, s)
+                                                    : launch_one<TYPE, MODE_MOE_GATE_UP, 1, ALIGNED>(a, s);
+        case MODE_MOE_DOWN_ACC:
+            return a.M >= 2560 ? launch_one<TYPE, MODE_MOE_DOWN_ACC, 2, ALIGNED>(a, s)
+                               : launch_one<TYPE, MODE_MOE_DOWN_ACC, 1, ALIGNED>(a, s);
         case MODE_BATCH: return launch_one<TYPE, MODE_BATCH, 1, ALIGNED>(a, s);
         case MODE_MOE_BATCHED: return launch_one<TYPE, MODE_MOE_BATCHED, 1, ALIGNED>(a, s);
         default: return cudaErrorInvalidValue;

@@ -169,7 +169,8 @@ __device__ __forceinline__ int seg_of(const WarpArgs& a, uint32_t T) {
     return (T >= a.seg_end[0] ? 1 : 0) + (T >= a.seg_end[1] ? 1 : 0);
 }
 
-template <int NS, int EPI, int kWarps, bool kMulti = false>
+// kSeg: 0 one matrix (pair), 1 grouped matrices (host-side segment table), 2 MoE slots (device-side routing)
+template <int NS, int EPI, int kWarps, int kSeg = 0>
 __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel(const WarpArgs a) {
     extern __shared__ uint8_t smem_raw[];
     pdl_launch_dependents();
@@ -180,7 +181,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
     const uint64_t row_bytes = (uint64_t)bpr * 144;
     const uint32_t upt = (bpr + kCB - 1) / kCB;  // row segments (units) per row
     const uint32_t upt_all = upt * NS;            // units per 16-row tile
-    const uint32_t tiles = kMulti ? a.seg_end[a.nseg - 1] : (a.M + 15) / 16;
+    const uint32_t tiles = kSeg == 1 ? a.seg_end[a.nseg - 1] : kSeg == 2 ? a.nseg * a.tiles_per_expert : (a.M + 15) / 16;
     const uint32_t U = tiles * upt_all, G = gridDim.x * kWarps;  // units, workers (G <= U)
     const uint32_t me = blockIdx.x * kWarps + warp;
     const uint32_t u0 = (uint32_t)part_begin(me, U, G), u1 = (uint32_t)part_begin(me + 1, U, G);
@@ -209,9 +210,20 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
     auto request = [&](uint32_t slot) {
         const uint32_t cols = min((uint32_t)kCB, bpr - p_kc * kCB) * 9;  // 16-byte columns in this segment
         const uint32_t row0 = p_tile * 16;
-        const int sg = kMulti ? seg_of(a, p_tile) : 0;
-        const uint8_t* base = kMulti ? a.segA[sg] : a.A[p_strm];
-        const uint32_t Mb = kMulti ? a.segM[sg] : a.M;  // row bound in the indexing of `base`
+        const uint8_t* base;
+        uint32_t Mb;  // row bound in the indexing of `base`
+        if constexpr (kSeg == 1) {
+            const int sg = seg_of(a, p_tile);
+            base = a.segA[sg];
+            Mb = a.segM[sg];
+        } else if constexpr (kSeg == 2) {
+            const uint32_t slot = p_tile / a.tiles_per_expert, t0 = slot * a.tiles_per_expert * 16;
+            base = a.A[p_strm] + (uint64_t)__ldg(a.routing + slot) * a.expert_stride - (uint64_t)t0 * row_bytes;
+            Mb = t0 + a.M;
+        } else {
+            base = a.A[p_strm];
+            Mb = a.M;
+        }
         const uint8_t* src = base + (uint64_t)row0 * row_bytes + (uint64_t)p_kc * (kCB * 144);
         uint8_t* dst = ring + slot * kSlotBytes;
         if (row0 + 16 <= Mb && cols == kPiecesPerRow) {
@@ -339,7 +351,14 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
                     acc1[r] = 0.f;
                 }
             }
-            if constexpr (kMulti) {
+            if constexpr (kSeg == 2) {
+                WarpArgs am = a;
+                const uint32_t slot = T / a.tiles_per_expert, t0 = slot * a.tiles_per_expert * 16;
+                am.y = a.y + (size_t)slot * a.M - t0;
+                am.y2 = a.y2 + (size_t)slot * a.M - t0;
+                am.M = t0 + a.M;
+                finish_tile<NS, EPI, kWarps>(am, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
+            } else if constexpr (kSeg == 1) {
                 WarpArgs am = a;
                 const int sg = seg_of(a, T);
                 am.y = a.segY[sg];
@@ -352,9 +371,9 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
     }
 }
 
-template <int NS, int EPI, int kWarps, bool kMulti = false>
+template <int NS, int EPI, int kWarps, int kSeg = 0>
 cudaError_t launch_w(const WarpArgs& a, cudaStream_t st, int sm_count, size_t smem) {
-    auto kern = dmmv_q4k_warp_kernel<NS, EPI, kWarps, kMulti>;
+    auto kern = dmmv_q4k_warp_kernel<NS, EPI, kWarps, kSeg>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -362,7 +381,7 @@ cudaError_t launch_w(const WarpArgs& a, cudaStream_t st, int sm_count, size_t sm
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    const uint64_t tiles = kMulti ? a.seg_end[a.nseg - 1] : (a.M + 15) / 16;
+    const uint64_t tiles = kSeg == 1 ? a.seg_end[a.nseg - 1] : kSeg == 2 ? (uint64_t)a.nseg * a.tiles_per_expert : (a.M + 15) / 16;
     const uint64_t U = tiles * (((a.K >> 8) + kCB - 1) / kCB) * NS;
     uint64_t grid = (uint64_t)sm_count * (16 / kWarps);  // 16 worker warps per SM
     if (grid * kWarps > U) grid = U / kWarps;
@@ -467,9 +486,45 @@ cudaError_t launch_warp_dmmv_multi(uint32_t n, const uint8_t* const* A, float* c
     }
     if (n == 2) wa.seg_end[1] = t0;
     const size_t s8 = smem_bytes(common.K, 8);
-    cudaError_t e = s8 <= kTwoPerSm ? launch_w<1, EPI_PLAIN, 8, true>(wa, st, common.sm_count, s8)
-                                    : launch_w<1, EPI_PLAIN, 16, true>(wa, st, common.sm_count,
+    cudaError_t e = s8 <= kTwoPerSm ? launch_w<1, EPI_PLAIN, 8, 1>(wa, st, common.sm_count, s8)
+                                    : launch_w<1, EPI_PLAIN, 16, 1>(wa, st, common.sm_count,
                                                                         smem_bytes(common.K, 16));
+    if (e == cudaSuccess && launches) ++*launches;
+    return e;
+}
+
+// MoE fused gate + up: y_gate[s][M], y_up[s][M] = Wg[routing[s]] x, Wu[routing[s]] x for the n_used slots, x shared.
+bool warp_moe_gate_up_eligible(uint32_t type, const DmmvArgs& a) {
+    if (type != T_Q4_K || a.x_expert_stride != 0 || !a.routing || !a.A2 || !a.y2) return false;
+    if (!a.scratch_partial || !a.scratch_flags || !a.status) return false;
+    if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (reinterpret_cast<uintptr_t>(a.A2) & 15u) || (a.expert_stride & 15u))
+        return false;
+    if ((a.K & 255u) || smem_bytes(a.K, 16) > 227 * 1024 || (a.K >> 8) > (uint32_t)(kPrepBlocks * 8)) return false;
+    const uint64_t U = (uint64_t)a.n_used * ((a.M + 15) / 16) * (((a.K >> 8) + kCB - 1) / kCB) * 2;
+    return a.n_used >= 1 && U >= 16 && U <= 0xFFFFFFFFull;
+}
+
+cudaError_t launch_warp_moe_gate_up(const DmmvArgs& a, cudaStream_t st, uint64_t* launches) {
+    WarpArgs wa;
+    wa.A[0] = a.A;
+    wa.A[1] = a.A2;
+    wa.x = a.x;
+    wa.y = a.y;
+    wa.y2 = a.y2;
+    wa.gate = nullptr;
+    wa.M = a.M;
+    wa.K = a.K;
+    wa.acc_mode = 0;
+    wa.gpartial = a.scratch_partial;
+    wa.gflags = a.scratch_flags;
+    wa.status = a.status;
+    wa.nseg = a.n_used;
+    wa.routing = a.routing;
+    wa.expert_stride = a.expert_stride;
+    wa.tiles_per_expert = (a.M + 15) / 16;
+    const size_t s8 = smem_bytes(a.K, 8);
+    cudaError_t e = s8 <= kTwoPerSm ? launch_w<2, EPI_PAIR, 8, 2>(wa, st, a.sm_count, s8)
+                                    : launch_w<2, EPI_PAIR, 16, 2>(wa, st, a.sm_count, smem_bytes(a.K, 16));
     if (e == cudaSuccess && launches) ++*launches;
     return e;
 }

@@ -56,6 +56,10 @@ bool warp_dmmv_multi_eligible(uint32_t type, uint32_t n, const uint8_t* const* A
                               const DmmvArgs& common);
 cudaError_t launch_warp_dmmv_multi(uint32_t n, const uint8_t* const* A, float* const* y, const uint32_t* M,
                                    const DmmvArgs& common, cudaStream_t s, uint64_t* launches);
+// MoE fused gate + up through the streaming kernel (Q4_K, x shared by the slots): a.A / a.A2 the stacked
+// expert matrices, a.y / a.y2 the [n_used][M] outputs, a.routing the slot -> expert ids.
+bool warp_moe_gate_up_eligible(uint32_t type, const DmmvArgs& a);
+cudaError_t launch_warp_moe_gate_up(const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
 bool q6k_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a);
 cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
 

@@ -32,6 +32,13 @@ struct WarpArgs {
     const uint8_t* segA[3];
     float* segY[3];
     uint32_t segM[3];
+    // MoE launch (expert slots chosen by a routing buffer on the device): slot s covers the tiles
+    // [s * tiles_per_expert, (s+1) * tiles_per_expert) of the matrices A[i] + routing[s] * expert_stride and
+    // writes rows [s * M, (s+1) * M) of y (stream 0) and y2 (stream 1). x is shared by all slots.
+    const uint32_t* routing;
+    uint64_t expert_stride;
+    uint32_t tiles_per_expert;
+    float* y2;
 };
 
 
@@ -64,13 +71,16 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-enum { EPI_PLAIN = 0, EPI_GATE_UP = 1, EPI_SIGMOID_ACC = 2 };
+enum { EPI_PLAIN = 0, EPI_GATE_UP = 1, EPI_SIGMOID_ACC = 2, EPI_PAIR = 3 };
 
 template <int NS, int EPI>
 __device__ __forceinline__ void write_row(const WarpArgs& a, uint32_t row, const float (&v)[NS]) {
     if (row >= a.M) return;
     if constexpr (EPI == EPI_GATE_UP) {
         a.y[row] = (v[0] / (1.0f + expf(-v[0]))) * v[1];
+    } else if constexpr (EPI == EPI_PAIR) {  // two streams, two outputs (MoE gate and up rows)
+        a.y[row] = v[0];
+        a.y2[row] = v[NS - 1];
     } else if constexpr (EPI == EPI_SIGMOID_ACC) {
         a.y[row] += (1.0f / (1.0f + expf(-__ldg(a.gate)))) * v[0];
     } else {
