@@ -337,3 +337,36 @@ def test_dispatch_multi(gpu, oracle, t, Ms, K):
     for w, M, y in zip(ws, Ms, ys):
         assert canary_intact(y, M)
         assert rel_l2(y[:M].cpu().numpy(), 2.0 * oracle.dmmv_f64(w, t, M, K, x)) <= TOL
+
+
+@pytest.mark.parametrize("M,K", [(64, 2880), (300, 2880), (2880, 2880), (100, 512), (48, 1056), (1000, 8192)])
+def test_streaming_mxfp4(gpu, oracle, M, K):
+    """MXFP4 shapes that take the streaming kernel: 17-byte blocks, rows that are only 2-byte aligned,
+    K not a multiple of 256, ragged row tiles, the last piece at the very end of the buffer, scale
+    byte 0, overwrite and accumulate, twice in a row."""
+    torch, ctx, dd = gpu
+    g = synth.rng(109, M * 7 + K)
+    w = synth.quant_matrix(g, zb.MXFP4, M, K).copy()
+    wb = w.reshape(M, K // 32, 17)
+    wb[::3, ::5, 0] = 0          # E8M0 byte 0 (2^-127)
+    wb[1::4, 1::7, 0] = 127 + 3  # larger scales
+    x = synth.activations(g, K) * np.float32(2.0 if M % 2 else 1e-2)
+    y0 = synth.activations(g, M)
+    y = out_with_canary(torch, M)
+    y[:M] = dev(torch, y0)
+    wd, xd = dev(torch, w), dev(torch, x)
+    dd.recordDispatch(zb.MXFP4, wd, xd, y, M, K, acc_mode=1)
+    ctx.submit_and_wait()
+    want = oracle.dmmv_f64(w, zb.MXFP4, M, K, x)
+    assert canary_intact(y, M)
+    assert rel_l2(y[:M].cpu().numpy() - y0, want) <= TOL
+    for _ in range(2):
+        dd.recordDispatch(zb.MXFP4, wd, xd, y, M, K, acc_mode=0)
+    ctx.submit_and_wait()
+    assert rel_l2(y[:M].cpu().numpy(), want) <= TOL
+    # weights at a 16-byte offset inside a poisoned buffer
+    wpad, off = dev_padded(torch, w, front=48, back=16)
+    y2 = out_with_canary(torch, M)
+    dd.recordDispatch(zb.MXFP4, wpad, xd, y2, M, K, a_offset=off)
+    ctx.submit_and_wait()
+    assert rel_l2(y2[:M].cpu().numpy(), want) <= TOL

@@ -281,3 +281,48 @@ def test_moe_fused_gate_up_streaming(gpu, oracle, E, M, K, n_used):
         assert canary_intact(yg, n_used * M) and canary_intact(yu, n_used * M)
         assert rel_l2(yg[:n_used * M].cpu().numpy(), oracle.moe_dmmv_f64(wg, zb.Q4_K, M, K, stride, ids, K, xs)) <= TOL
         assert rel_l2(yu[:n_used * M].cpu().numpy(), oracle.moe_dmmv_f64(wu, zb.Q4_K, M, K, stride, ids, K, xs)) <= TOL
+
+
+@pytest.mark.parametrize("E,M,K,n_used", [(6, 300, 2880, 4), (3, 32, 512, 2)])
+def test_moe_fused_gate_up_streaming_mxfp4(gpu, oracle, E, M, K, n_used):
+    torch, ctx, dd = gpu
+    g = synth.rng(203, E * 1000 + M)
+    wg, stride = stacked(g, zb.MXFP4, E, M, K)
+    wu, _ = stacked(g, zb.MXFP4, E, M, K)
+    x = synth.activations(g, 1, K)
+    wgd, wud, xd = dev(torch, wg), dev(torch, wu), dev(torch, x)
+    xs = np.repeat(x, n_used, axis=0)
+    for rep in range(2):
+        ids = np.array([(5 * i + 2 * rep + E - 1) % E for i in range(n_used)], np.uint32)  # includes the last expert
+        yg, yu = out_with_canary(torch, n_used * M), out_with_canary(torch, n_used * M)
+        dd.dispatchMoeFusedGateUp(zb.MXFP4, wgd, wud, xd, yg, yu, dev(torch, routing_buf(ids)), M, K, stride, n_used, 0)
+        ctx.submit_and_wait()
+        assert canary_intact(yg, n_used * M) and canary_intact(yu, n_used * M)
+        assert rel_l2(yg[:n_used * M].cpu().numpy(), oracle.moe_dmmv_f64(wg, zb.MXFP4, M, K, stride, ids, K, xs)) <= TOL
+        assert rel_l2(yu[:n_used * M].cpu().numpy(), oracle.moe_dmmv_f64(wu, zb.MXFP4, M, K, stride, ids, K, xs)) <= TOL
+
+
+@pytest.mark.parametrize("E,M,K,n_used,xs", [(6, 300, 2880, 4, 2880), (4, 64, 512, 3, 520), (3, 2880, 2880, 4, 2880)])
+def test_moe_fused_down_acc_streaming_mxfp4(gpu, oracle, E, M, K, n_used, xs):
+    """y += sum_s w_s W[id_s] x_s through the streaming MXFP4 kernel (slots side by side along K), with a
+    padded per-slot activation stride, twice in a row."""
+    torch, ctx, dd = gpu
+    g = synth.rng(204, E * 1000 + M)
+    w, stride = stacked(g, zb.MXFP4, E, M, K)
+    wd = dev(torch, w)
+    for rep in range(2):
+        ids = np.array([(3 * i + rep + E - 1) % E for i in range(n_used)], np.uint32)
+        wts = (g.random(n_used).astype(np.float32) + np.float32(0.1))
+        x = synth.activations(g, n_used, K)
+        xpad = np.zeros((n_used, xs), np.float32)
+        xpad[:, :K] = x
+        h0 = synth.activations(g, M)
+        y = out_with_canary(torch, M)
+        y[:M] = dev(torch, h0)
+        dd.dispatchMoeFusedDownAcc(zb.MXFP4, wd, dev(torch, xpad.reshape(-1)), y, dev(torch, routing_buf(ids, wts)), M, K,
+                                   stride, n_used, xs)
+        ctx.submit_and_wait()
+        per = oracle.moe_dmmv_f64(w, zb.MXFP4, M, K, stride, ids, K, x)
+        want = h0 + (wts.astype(np.float64)[:, None] * per).sum(0)
+        assert canary_intact(y, M)
+        assert rel_l2(y[:M].cpu().numpy() - h0, want - h0) <= TOL

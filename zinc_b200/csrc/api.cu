@@ -432,6 +432,7 @@ int32_t zc_dmmv(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, cons
     a.M = M;
     a.K = K;
     a.acc_mode = acc_mode;
+    a.a_end = u8(A, a_size);
     attach_scratch(ctx, a);
     cudaError_t e;
     if (type == T_F32 && M <= 2048 && (K & 3u) == 0 && acc_mode == 0 && aligned(A, a_offset, 16))
@@ -658,9 +659,16 @@ int32_t zc_moe_fused_gate_up(zc_ctx* ctx, uint32_t type, const void* Wg, uint64_
     a.expert_stride = expert_stride;
     a.n_used = n_used;
     a.x_expert_stride = x_expert_stride;
+    a.a_end = u8(Wg, wg_size);
+    a.a2_end = u8(Wu, wu_size);
     attach_scratch(ctx, a);
-    cudaError_t e = warp_moe_gate_up_eligible(type, a) ? launch_warp_moe_gate_up(a, ctx->stream, &ctx->launches)
-                                                       : launch_dmmv(type, MODE_MOE_GATE_UP, a, ctx->stream, &ctx->launches);
+    cudaError_t e;
+    if (warp_moe_gate_up_eligible(type, a))
+        e = launch_warp_moe_gate_up(a, ctx->stream, &ctx->launches);
+    else if (mxfp4_moe_gate_up_eligible(type, a))
+        e = launch_mxfp4_moe_gate_up(a, ctx->stream, &ctx->launches);
+    else
+        e = launch_dmmv(type, MODE_MOE_GATE_UP, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 
@@ -683,7 +691,11 @@ int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type, const void* A, uint64_
     a.expert_stride = expert_stride;
     a.n_used = n_used;
     a.x_expert_stride = x_expert_stride;
-    cudaError_t e = launch_dmmv(type, MODE_MOE_DOWN_ACC, a, ctx->stream, &ctx->launches);
+    a.a_end = u8(A, a_size);
+    attach_scratch(ctx, a);
+    cudaError_t e = mxfp4_moe_down_acc_eligible(type, a)
+                        ? launch_mxfp4_moe_down_acc(a, ctx->stream, &ctx->launches)
+                        : launch_dmmv(type, MODE_MOE_DOWN_ACC, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 

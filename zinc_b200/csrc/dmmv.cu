@@ -202,6 +202,7 @@ cudaError_t launch_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t
     if (a.M == 0) return cudaSuccess;
     if (warp_dmmv_eligible(type, mode, a)) return launch_warp_dmmv(type, mode, a, s, launches);
     if (q6k_dmmv_eligible(type, mode, a)) return launch_q6k_dmmv(mode, a, s, launches);
+    if (mxfp4_dmmv_eligible(type, mode, a)) return launch_mxfp4_dmmv(a, s, launches);
     cudaError_t e;
     // 128-bit weight loads need every block start 16-byte aligned: true for the
     // 144/176-byte K-quant blocks when the base, the second base and the expert

@@ -40,6 +40,10 @@ struct DmmvArgs {
     uint32_t* scratch_flags = nullptr;  // [kStreamMaxWorkers] publication flags, zero between launches
     uint32_t* status = nullptr;
     int sm_count = 0;
+    // first byte past the buffers that hold A / A2 (kernels that fetch aligned supersets of unaligned rows
+    // must not read beyond them)
+    const uint8_t* a_end = nullptr;
+    const uint8_t* a2_end = nullptr;
 };
 
 // Capacity of the split-K scratch a context owns.
@@ -60,6 +64,14 @@ cudaError_t launch_warp_dmmv_multi(uint32_t n, const uint8_t* const* A, float* c
 // expert matrices, a.y / a.y2 the [n_used][M] outputs, a.routing the slot -> expert ids.
 bool warp_moe_gate_up_eligible(uint32_t type, const DmmvArgs& a);
 cudaError_t launch_warp_moe_gate_up(const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
+// Streaming MXFP4 matvec (dmmv_mxfp4.cu): plain / accumulate, and the MoE fused gate + up form.
+bool mxfp4_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a);
+cudaError_t launch_mxfp4_dmmv(const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
+bool mxfp4_moe_gate_up_eligible(uint32_t type, const DmmvArgs& a);
+cudaError_t launch_mxfp4_moe_gate_up(const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
+// y += sum_s w_s * W[routing[s]] x_s (the fused MoE down projection + weighted accumulate)
+bool mxfp4_moe_down_acc_eligible(uint32_t type, const DmmvArgs& a);
+cudaError_t launch_mxfp4_moe_down_acc(const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
 bool q6k_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a);
 cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
 

@@ -39,6 +39,7 @@ struct WarpArgs {
     uint64_t expert_stride;
     uint32_t tiles_per_expert;
     float* y2;
+    uint32_t x_slot_stride;  // MoE down projection: elements between the slots' activation vectors
 };
 
 
@@ -71,13 +72,15 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-enum { EPI_PLAIN = 0, EPI_GATE_UP = 1, EPI_SIGMOID_ACC = 2, EPI_PAIR = 3 };
+enum { EPI_PLAIN = 0, EPI_GATE_UP = 1, EPI_SIGMOID_ACC = 2, EPI_PAIR = 3, EPI_ACC = 4 };
 
 template <int NS, int EPI>
 __device__ __forceinline__ void write_row(const WarpArgs& a, uint32_t row, const float (&v)[NS]) {
     if (row >= a.M) return;
     if constexpr (EPI == EPI_GATE_UP) {
         a.y[row] = (v[0] / (1.0f + expf(-v[0]))) * v[1];
+    } else if constexpr (EPI == EPI_ACC) {  // y += result, whatever acc_mode says
+        a.y[row] += v[0];
     } else if constexpr (EPI == EPI_PAIR) {  // two streams, two outputs (MoE gate and up rows)
         a.y[row] = v[0];
         a.y2[row] = v[NS - 1];
