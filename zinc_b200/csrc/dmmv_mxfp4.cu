@@ -144,6 +144,17 @@ __device__ __forceinline__ void prep_x_x(const SmemX& s, const XRegsX& r, uint32
     }
 }
 
+__device__ __forceinline__ uint32_t lds_u32(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_u128(uint32_t saddr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(saddr));
+    return v;
+}
+
 // Four nibbles (bits 0..15 of h) -> four signed bytes 2 * E2M1, in nibble order.
 __device__ __forceinline__ uint32_t e2m1x4_to_s8(uint32_t h) {
     const uint32_t sel = h & 0x7777u;
@@ -200,6 +211,17 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
     };
 
     uint32_t p_tile = u0 / upt_all, p_strm = (u0 % upt_all) / upt, p_kc = (u0 % upt_all) % upt;
+    // per-lane constants of its nine pieces: row r, 16-byte column c, r * row_bytes + c * 16, and the row's
+    // contribution to the byte offset inside the aligned superset (the unit start, and 272-byte steps
+    // along K, add the same amount to every row)
+    uint32_t pc_rc[kPiecesLane], pc_off[kPiecesLane];
+#pragma unroll
+    for (int i = 0; i < kPiecesLane; ++i) {
+        const uint32_t p = i * 32 + lane;
+        const uint32_t r = p / kPiecesRow, c = p - r * kPiecesRow;
+        pc_rc[i] = r | (c << 8) | (((r * row_bytes) & 15u) << 16);
+        pc_off[i] = r * row_bytes + c * 16;
+    }
     auto request = [&](uint32_t slot) {
         const uint8_t* base;
         uint32_t Mb;
@@ -208,20 +230,33 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
         const uint32_t row0 = p_tile * 16;
         const uint8_t* a_end = (kSeg == 3 || p_strm == 0) ? a_end0 : a_end1;  // first byte past this stream's weight buffer
         uint8_t* dst = ring + slot * kSlotBytesX;
+        const uint8_t* ubase = base + (uint64_t)row0 * row_bytes + (uint64_t)p_kc * kSegBytes;  // row 0 of the unit
+        if (row0 + 16 <= Mb && ubase + 16 * row_bytes + 32 <= a_end) {
+            // whole tile inside the matrix and away from the end of the buffer
+            const uint32_t tb = (uint32_t)(reinterpret_cast<uintptr_t>(ubase) & 15u);
 #pragma unroll
-        for (int i = 0; i < kPiecesLane; ++i) {
-            const uint32_t p = i * 32 + lane;
-            const uint32_t r = p / kPiecesRow, c = p - r * kPiecesRow;
-            const uint32_t row = min(row0 + r, Mb - 1);
-            const uint8_t* start = base + (uint64_t)row * row_bytes + (uint64_t)p_kc * kSegBytes;
-            const uint32_t o = (uint32_t)(reinterpret_cast<uintptr_t>(start) & 15u);
-            if (c * 16 < o + seg) {  // the piece holds bytes of the segment
-                const uint8_t* src = start - o + c * 16;
-                uint8_t* d = dst + r * kRowSlot + c * 16;
-                if (src + 16 <= a_end) {
-                    cp_async16(d, src);
-                } else {  // the very end of the tensor: copy only the bytes that exist
-                    for (const uint8_t* q = src; q < a_end; ++q) d[q - src] = __ldg(q);
+            for (int i = 0; i < kPiecesLane; ++i) {
+                const uint32_t c16 = (pc_rc[i] >> 4) & 0xFF0u;           // c * 16
+                const uint32_t o = (tb + (pc_rc[i] >> 16)) & 15u;        // this row's offset in its superset
+                if (c16 < o + seg)
+                    cp_async16(dst + (pc_rc[i] & 0xFFu) * kRowSlot + c16, ubase + pc_off[i] - o);
+            }
+        } else {
+#pragma unroll 1
+            for (int i = 0; i < kPiecesLane; ++i) {
+                const uint32_t p = i * 32 + lane;
+                const uint32_t r = p / kPiecesRow, c = p - r * kPiecesRow;
+                const uint32_t row = min(row0 + r, Mb - 1);
+                const uint8_t* start = base + (uint64_t)row * row_bytes + (uint64_t)p_kc * kSegBytes;
+                const uint32_t o = (uint32_t)(reinterpret_cast<uintptr_t>(start) & 15u);
+                if (c * 16 < o + seg) {  // the piece holds bytes of the segment
+                    const uint8_t* src = start - o + c * 16;
+                    uint8_t* d = dst + r * kRowSlot + c * 16;
+                    if (src + 16 <= a_end) {
+                        cp_async16(d, src);
+                    } else {  // the very end of the tensor: copy only the bytes that exist
+                        for (const uint8_t* q = src; q < a_end; ++q) d[q - src] = __ldg(q);
+                    }
                 }
             }
         }
@@ -249,8 +284,9 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
     uint32_t tile = u0 / upt_all, strm = (u0 % upt_all) / upt, kc = (u0 % upt_all) % upt;
     float acc0[2] = {0.f, 0.f}, acc1[2] = {0.f, 0.f};
     const bool b_live = (g >> 1) == t;
-    const uint4* xu_live = s.xf + (g & 1) * 4 + t;
-    const uint4* xu_dead = s.zeros + (g >> 1) + 1;
+    const uint32_t xu_live = smem_u32(s.xf + (g & 1) * 4 + t);
+    const uint32_t xu_dead = smem_u32(s.zeros + (g >> 1) + 1);
+    const uint32_t ring_s = smem_u32(ring);
 
     for (uint32_t it = 0; it < n; ++it) {
         const uint32_t slot = it % kDepthX;
@@ -263,8 +299,9 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
         const uint32_t rA = min(tile * 16 + g, Mb - 1), rB = min(tile * 16 + g + 8, Mb - 1);
         const uint32_t oA = (uint32_t)(reinterpret_cast<uintptr_t>(base + (uint64_t)rA * row_bytes + (uint64_t)kc * kSegBytes) & 15u);
         const uint32_t oB = (uint32_t)(reinterpret_cast<uintptr_t>(base + (uint64_t)rB * row_bytes + (uint64_t)kc * kSegBytes) & 15u);
-        const uint8_t* sA = ring + slot * kSlotBytesX + g * kRowSlot + oA;
-        const uint8_t* sB = ring + slot * kSlotBytesX + (g + 8) * kRowSlot + oB;
+        // shared-window byte addresses of the two rows' segments
+        const uint32_t sA = ring_s + slot * kSlotBytesX + g * kRowSlot + oA;
+        const uint32_t sB = ring_s + slot * kSlotBytesX + (g + 8) * kRowSlot + oB;
         const uint32_t nblk = min((uint32_t)kUnitBlocks, nb - kc * kUnitBlocks);
 #pragma unroll 1
         for (uint32_t gq = 0; gq * 4 < nblk; ++gq) {
@@ -274,14 +311,13 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
             // 17 bytes per row at an arbitrary byte offset: six aligned words, funnel-shifted
             uint32_t wa[5], wb[5];
             {
-                const uintptr_t pa = reinterpret_cast<uintptr_t>(sA + bl * 17), pb = reinterpret_cast<uintptr_t>(sB + bl * 17);
-                const uint32_t* ba = reinterpret_cast<const uint32_t*>(pa & ~uintptr_t(3));
-                const uint32_t* bb = reinterpret_cast<const uint32_t*>(pb & ~uintptr_t(3));
-                const uint32_t sa = (uint32_t)(pa & 3u) * 8u, sb2 = (uint32_t)(pb & 3u) * 8u;
-                uint32_t pva = ba[0], pvb = bb[0];
+                const uint32_t pa = sA + bl * 17, pb = sB + bl * 17;
+                const uint32_t ba = pa & ~3u, bb = pb & ~3u;
+                const uint32_t sa = (pa & 3u) * 8u, sb2 = (pb & 3u) * 8u;
+                uint32_t pva = lds_u32(ba), pvb = lds_u32(bb);
 #pragma unroll
                 for (int i = 0; i < 5; ++i) {
-                    const uint32_t na = ba[i + 1], nbw = bb[i + 1];
+                    const uint32_t na = lds_u32(ba + 4 * (i + 1)), nbw = lds_u32(bb + 4 * (i + 1));
                     wa[i] = __funnelshift_r(pva, na, sa);
                     wb[i] = __funnelshift_r(pvb, nbw, sb2);
                     pva = na;
@@ -289,14 +325,14 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
                 }
             }
             // wa[0] byte 0 = scale, bytes 1.. = nibbles: nibble word i = bytes 1+4i .. 4+4i
-            const uint4* xu = b_live ? xu_live + (size_t)q * 32 : xu_dead;
+            const uint32_t xu = b_live ? xu_live + q * 512u : xu_dead;  // 32 units of 16 bytes per group
             int d01[4] = {0, 0, 0, 0}, d2[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const uint32_t qa = __funnelshift_r(wa[j], wa[j + 1], 8), qb = __funnelshift_r(wb[j], wb[j + 1], 8);
                 const uint32_t a0 = e2m1x4_to_s8(qa & 0xFFFFu), a2 = e2m1x4_to_s8(qa >> 16);
                 const uint32_t a1 = e2m1x4_to_s8(qb & 0xFFFFu), a3 = e2m1x4_to_s8(qb >> 16);
-                const uint4 bx = xu[j * 8];
+                const uint4 bx = lds_u128(xu + j * 128);
                 mma_s8(d01, a0, a1, a2, a3, bx.x, bx.y);
                 mma_s8(d2, a0, a1, a2, a3, bx.z, bx.w);
             }

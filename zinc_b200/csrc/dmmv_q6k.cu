@@ -134,13 +134,19 @@ __device__ __forceinline__ void prep_x6(const Smem6& s, const XRegs6& r, uint32_
     }
 }
 
-// N consecutive 32-bit words starting `sh` bits into the aligned word at p (sh = 0 or 16)
+__device__ __forceinline__ uint32_t lds_u32s(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr));
+    return v;
+}
+
+// N consecutive 32-bit words starting `sh` bits into the aligned word at shared address saddr (sh = 0 or 16)
 template <int N>
-__device__ __forceinline__ void lds_words(const uint32_t* p, uint32_t sh, uint32_t (&w)[N]) {
-    uint32_t prev = p[0];
+__device__ __forceinline__ void lds_words(uint32_t saddr, uint32_t sh, uint32_t (&w)[N]) {
+    uint32_t prev = lds_u32s(saddr);
 #pragma unroll
     for (int i = 0; i < N; ++i) {
-        const uint32_t next = p[i + 1];
+        const uint32_t next = lds_u32s(saddr + 4 * (i + 1));
         w[i] = __funnelshift_r(prev, next, sh);
         prev = next;
     }
@@ -203,8 +209,9 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
     uint32_t tile = u0 / bpr, blk = u0 % bpr;
     float acc[2] = {0.f, 0.f};
     const bool b_live = (g >> 1) == t;
-    const uint4* xu_live = s.xf + (g & 1) * 4 + t;
-    const uint4* xu_dead = s.zeros + (g >> 1) + 1;
+    const uint32_t xu_live = smem_u32(s.xf + (g & 1) * 4 + t);
+    const uint32_t xu_dead = smem_u32(s.zeros + (g >> 1) + 1);
+    const uint32_t ring_s = smem_u32(ring), xs_s = smem_u32(s.xs), sx_s = smem_u32(s.sx);
     const uint32_t shl = 4 - 2 * c, shr = 2 * c;  // qh bit pairs: low nibbles use bits 2c.., high nibbles 4+2c..
     constexpr uint32_t kNib = 0x0F0F0F0Fu, kTop = 0x30303030u;
 
@@ -213,24 +220,23 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
         cp_async_wait<kDepth - 1>();
         __syncwarp();
         const uint32_t o0 = (blk * 210u) & 15u, fs = (o0 & 3u) * 8u;
-        const uint8_t* sb = ring + slot * kSlot6 + (o0 & ~3u);
-        const uint4* xu = b_live ? xu_live + (size_t)blk * 64 : xu_dead;
+        const uint32_t sb = ring_s + slot * kSlot6 + (o0 & ~3u);
+        const uint32_t xu = b_live ? xu_live + blk * 1024u : xu_dead;  // 64 units of 16 bytes per super-block
         // both rows share the B operand; accumulators: [row-pair quad] per sub-block (lo k=0,1; hi k=0,1)
         int d01[4][4], d2[4][4];
 #pragma unroll
         for (int q = 0; q < 4; ++q)
 #pragma unroll
             for (int e = 0; e < 4; ++e) d01[q][e] = d2[q][e] = 0;
-        const uint32_t* wA = reinterpret_cast<const uint32_t*>(sb + g * kRow6);
-        const uint32_t* wB = reinterpret_cast<const uint32_t*>(sb + (g + 8) * kRow6);
+        const uint32_t wA = sb + g * kRow6, wB = sb + (g + 8) * kRow6;  // byte addresses; word offsets below x 4
         uint32_t qlA[8], qhA[8], qlB[8], qhB[8];
-        lds_words<8>(wA + 16 * h + 8 * c, fs, qlA);
-        lds_words<8>(wA + 32 + 8 * h, fs, qhA);
-        lds_words<8>(wB + 16 * h + 8 * c, fs, qlB);
-        lds_words<8>(wB + 32 + 8 * h, fs, qhB);
+        lds_words<8>(wA + 4 * (16 * h + 8 * c), fs, qlA);
+        lds_words<8>(wA + 4 * (32 + 8 * h), fs, qhA);
+        lds_words<8>(wB + 4 * (16 * h + 8 * c), fs, qlB);
+        lds_words<8>(wB + 4 * (32 + 8 * h), fs, qhB);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint4 bl = xu[i * 8], bh = xu[(4 + i) * 8];
+            const uint4 bl = lds_v4(xu + i * 128), bh = lds_v4(xu + (4 + i) * 128);
             uint32_t lo[4], hi[4];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
@@ -248,17 +254,17 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
         }
         // scales: the 8 int8 of half h; this lane's four are bytes 2c, 2c+1 (low) and 4+2c, 5+2c (high)
         uint32_t scA[2], scB[2], dA[1], dB[1];
-        lds_words<2>(wA + 48 + 2 * h, fs, scA);
-        lds_words<2>(wB + 48 + 2 * h, fs, scB);
-        lds_words<1>(wA + 52, fs, dA);
-        lds_words<1>(wB + 52, fs, dB);
+        lds_words<2>(wA + 4 * (48 + 2 * h), fs, scA);
+        lds_words<2>(wB + 4 * (48 + 2 * h), fs, scB);
+        lds_words<1>(wA + 4 * 52, fs, dA);
+        lds_words<1>(wB + 4 * 52, fs, dB);
         // every lane has read the stage: refill it
         __syncwarp();
         if (it + kDepth < n) request(slot);
         cp_async_commit();
 
-        const int* sx = s.sx + blk * 16 + 8 * h + 2 * c;  // sub-blocks 8h+2c+k (low), 8h+4+2c+k (high)
-        const int sx0 = sx[0], sx1 = sx[1], sx2 = sx[4], sx3 = sx[5];
+        const uint32_t sx = sx_s + 4 * (blk * 16 + 8 * h + 2 * c);  // sub-blocks 8h+2c+k (low), 8h+4+2c+k (high)
+        const int sx0 = (int)lds_u32s(sx), sx1 = (int)lds_u32s(sx + 4), sx2 = (int)lds_u32s(sx + 16), sx3 = (int)lds_u32s(sx + 20);
         const int sxs[4] = {sx0, sx1, sx2, sx3};
         float sumA = 0.f, sumB = 0.f;
 #pragma unroll
@@ -269,7 +275,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
             sumA += (float)(int8_t)(wa & 0xFFu) * (float)PA;
             sumB += (float)(int8_t)(wb & 0xFFu) * (float)PB;
         }
-        const float xs = s.xs[blk];
+        const float xs = lds_f1(xs_s + blk * 4);
         acc[0] += h2f(dA[0]) * xs * sumA;
         acc[1] += h2f(dB[0]) * xs * sumB;
 

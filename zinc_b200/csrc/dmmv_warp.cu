@@ -268,8 +268,9 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
     uint32_t tile = u0 / upt_all, strm = (u0 % upt_all) / upt, kc = (u0 % upt_all) % upt;
     float acc0[2] = {0.f, 0.f}, acc1[2] = {0.f, 0.f};  // stream 0 / stream 1, rows g and g+8
     const bool b_live = (g >> 1) == t;  // lane (g, t) feeds B column g, live only for g in {2t, 2t+1}
-    const uint4* xu_live = s.xf + (g & 1) * 4 + t;
-    const uint4* xu_dead = s.zeros + (g >> 1) + 1;  // a bank group no live lane of the same quarter-warp uses
+    const uint32_t xu_live = smem_u32(s.xf + (g & 1) * 4 + t);
+    const uint32_t xu_dead = smem_u32(s.zeros + (g >> 1) + 1);  // a bank group no live lane of the same quarter-warp uses
+    const uint32_t ring_s = smem_u32(ring), xs_s = smem_u32(s.xs), sx_s = smem_u32(s.sx);
 
     for (uint32_t it = 0; it < n; ++it) {
         const uint32_t slot = it % kDepth;
@@ -280,21 +281,21 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
         for (uint32_t bi = 0; bi < (uint32_t)kCB; ++bi) {
             if (bi >= nblk) break;
             const uint32_t blk = kc * kCB + bi;
-            const uint8_t* sb = ring + slot * kSlotBytes + bi * 144;
-            const uint8_t* rA = sb + g * kRowSeg;
-            const uint8_t* rB = sb + (g + 8) * kRowSeg;
-            const uint4 hA = lds128(rA), hB = lds128(rB);
-            const uint4 qa0 = lds128(rA + 16 + 32 * t), qa1 = lds128(rA + 32 + 32 * t);
-            const uint4 qb0 = lds128(rB + 16 + 32 * t), qb1 = lds128(rB + 32 + 32 * t);
+            const uint32_t sb = ring_s + slot * kSlotBytes + bi * 144;
+            const uint32_t rA = sb + g * kRowSeg;
+            const uint32_t rB = sb + (g + 8) * kRowSeg;
+            const uint4 hA = lds_v4(rA), hB = lds_v4(rB);
+            const uint4 qa0 = lds_v4(rA + 16 + 32 * t), qa1 = lds_v4(rA + 32 + 32 * t);
+            const uint4 qb0 = lds_v4(rB + 16 + 32 * t), qb1 = lds_v4(rB + 32 + 32 * t);
             const uint32_t qa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
             const uint32_t qb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
-            const uint4* xu = b_live ? xu_live + (size_t)blk * 64 : xu_dead;
+            const uint32_t xu = b_live ? xu_live + blk * 1024u : xu_dead;  // 64 units of 16 bytes per super-block
             // D01: digits 0 and 1 in this lane's columns 2t, 2t+1; D2: digit 2 in column 2t
             int lo01[4] = {0, 0, 0, 0}, lo2[4] = {0, 0, 0, 0}, hi01[4] = {0, 0, 0, 0}, hi2[4] = {0, 0, 0, 0};
             constexpr uint32_t kNib = 0x0F0F0F0Fu;
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint4 bl = xu[j * 8], bh = xu[(4 + j) * 8];
+                const uint4 bl = lds_v4(xu + j * 128), bh = lds_v4(xu + (4 + j) * 128);
                 const uint32_t a0 = qa[2 * j], a1 = qb[2 * j], a2 = qa[2 * j + 1], a3 = qb[2 * j + 1];
                 const uint32_t l0 = a0 & kNib, l1 = a1 & kNib, l2 = a2 & kNib, l3 = a3 & kNib;
                 mma_s8(lo01, l0, l1, l2, l3, bl.x, bl.y);
@@ -312,8 +313,8 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
             uint32_t scA, mnA, scB, mnB;
             scales_mins_pair(hA.y, hA.z, hA.w, t, scA, mnA);
             scales_mins_pair(hB.y, hB.z, hB.w, t, scB, mnB);
-            const float xs = s.xs[blk];
-            const float2 sxv = *reinterpret_cast<const float2*>(s.sx + blk * 8 + 2 * t);
+            const float xs = lds_f1(xs_s + blk * 4);
+            const float2 sxv = lds_f2(sx_s + (blk * 8 + 2 * t) * 4);
             const float dA = h2f(hA.x) * xs, dmA = h2f(hA.x >> 16) * xs;
             const float dB = h2f(hB.x) * xs, dmB = h2f(hB.x >> 16) * xs;
             const float vA = dA * ((float)(scA & 0xFFu) * PloA + (float)(scA >> 8) * PhiA) -
