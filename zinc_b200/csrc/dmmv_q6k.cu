@@ -152,8 +152,11 @@ __device__ __forceinline__ void lds_words(uint32_t saddr, uint32_t sh, uint32_t 
     }
 }
 
-template <int EPI, int kWarps>
-__global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel(const WarpArgs a) {
+// kRowsAligned: every row starts on a 16-byte boundary (K a multiple of 2048), so all rows of a unit share
+// one offset inside their aligned supersets; otherwise each row has its own (rows are 2-byte aligned).
+template <int EPI, int kWarps, bool kRowsAligned>
+__global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel(const WarpArgs a,
+                                                                                 const uint8_t* a_end) {
     extern __shared__ uint8_t smem_raw[];
     pdl_launch_dependents();
     const Smem6 s = carve6(smem_raw, a.K, kWarps);
@@ -177,15 +180,34 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
     }
     uint32_t p_tile = u0 / bpr, p_blk = u0 % bpr;
     auto request = [&](uint32_t slot) {
-        const uint32_t al = (p_blk * 210u) & ~15u;  // aligned start of the block's superset within the row
         uint8_t* dst = ring + slot * kSlot6;
         const uint32_t row0 = p_tile * 16;
+        if constexpr (kRowsAligned) {
+            const uint32_t al = (p_blk * 210u) & ~15u;  // aligned start of the block's superset within the row
 #pragma unroll
-        for (int i = 0; i < kPiecesLane6; ++i) {
-            const uint32_t r = piece[i] & 0xFFu, col = piece[i] >> 8;
-            if (al + col * 16 < (uint32_t)row_bytes) {  // rows are 16-byte aligned: a piece never crosses the row end
+            for (int i = 0; i < kPiecesLane6; ++i) {
+                const uint32_t r = piece[i] & 0xFFu, col = piece[i] >> 8;
+                if (al + col * 16 < (uint32_t)row_bytes) {  // rows are 16-byte aligned: a piece never crosses the row end
+                    const uint32_t row = min(row0 + r, a.M - 1);
+                    cp_async16(dst + r * kRow6 + col * 16, a.A[0] + (uint64_t)row * row_bytes + al + col * 16);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < kPiecesLane6; ++i) {
+                const uint32_t r = piece[i] & 0xFFu, col = piece[i] >> 8;
                 const uint32_t row = min(row0 + r, a.M - 1);
-                cp_async16(dst + r * kRow6 + col * 16, a.A[0] + (uint64_t)row * row_bytes + al + col * 16);
+                const uint8_t* start = a.A[0] + (uint64_t)row * row_bytes + p_blk * 210u;
+                const uint32_t o = (uint32_t)(reinterpret_cast<uintptr_t>(start) & 15u);
+                if (col * 16 < o + 210u) {  // the piece holds bytes of the block
+                    const uint8_t* src = start - o + col * 16;
+                    uint8_t* d = dst + r * kRow6 + col * 16;
+                    if (src + 16 <= a_end) {
+                        cp_async16(d, src);
+                    } else {  // the very end of the tensor: copy only the bytes that exist
+                        for (const uint8_t* q = src; q < a_end; ++q) d[q - src] = __ldg(q);
+                    }
+                }
             }
         }
         if (++p_blk == bpr) { p_blk = 0; ++p_tile; }
@@ -219,8 +241,17 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
         const uint32_t slot = it % kDepth;
         cp_async_wait<kDepth - 1>();
         __syncwarp();
-        const uint32_t o0 = (blk * 210u) & 15u, fs = (o0 & 3u) * 8u;
-        const uint32_t sb = ring_s + slot * kSlot6 + (o0 & ~3u);
+        // byte offset of the block inside each row's aligned superset, and the funnel shift it implies
+        uint32_t oA, oB;
+        if constexpr (kRowsAligned) {
+            oA = oB = (blk * 210u) & 15u;
+        } else {
+            const uint32_t rA = min(tile * 16 + g, a.M - 1), rB = min(tile * 16 + g + 8, a.M - 1);
+            oA = (uint32_t)(reinterpret_cast<uintptr_t>(a.A[0] + (uint64_t)rA * row_bytes + blk * 210u) & 15u);
+            oB = (uint32_t)(reinterpret_cast<uintptr_t>(a.A[0] + (uint64_t)rB * row_bytes + blk * 210u) & 15u);
+        }
+        const uint32_t fsA = (oA & 3u) * 8u, fsB = (oB & 3u) * 8u;
+        const uint32_t sb = ring_s + slot * kSlot6;
         const uint32_t xu = b_live ? xu_live + blk * 1024u : xu_dead;  // 64 units of 16 bytes per super-block
         // both rows share the B operand; accumulators: [row-pair quad] per sub-block (lo k=0,1; hi k=0,1)
         int d01[4][4], d2[4][4];
@@ -228,12 +259,12 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
         for (int q = 0; q < 4; ++q)
 #pragma unroll
             for (int e = 0; e < 4; ++e) d01[q][e] = d2[q][e] = 0;
-        const uint32_t wA = sb + g * kRow6, wB = sb + (g + 8) * kRow6;  // byte addresses; word offsets below x 4
+        const uint32_t wA = sb + g * kRow6 + (oA & ~3u), wB = sb + (g + 8) * kRow6 + (oB & ~3u);  // byte addresses; word offsets below x 4
         uint32_t qlA[8], qhA[8], qlB[8], qhB[8];
-        lds_words<8>(wA + 4 * (16 * h + 8 * c), fs, qlA);
-        lds_words<8>(wA + 4 * (32 + 8 * h), fs, qhA);
-        lds_words<8>(wB + 4 * (16 * h + 8 * c), fs, qlB);
-        lds_words<8>(wB + 4 * (32 + 8 * h), fs, qhB);
+        lds_words<8>(wA + 4 * (16 * h + 8 * c), fsA, qlA);
+        lds_words<8>(wA + 4 * (32 + 8 * h), fsA, qhA);
+        lds_words<8>(wB + 4 * (16 * h + 8 * c), fsB, qlB);
+        lds_words<8>(wB + 4 * (32 + 8 * h), fsB, qhB);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const uint4 bl = lds_v4(xu + i * 128), bh = lds_v4(xu + (4 + i) * 128);
@@ -254,10 +285,10 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
         }
         // scales: the 8 int8 of half h; this lane's four are bytes 2c, 2c+1 (low) and 4+2c, 5+2c (high)
         uint32_t scA[2], scB[2], dA[1], dB[1];
-        lds_words<2>(wA + 4 * (48 + 2 * h), fs, scA);
-        lds_words<2>(wB + 4 * (48 + 2 * h), fs, scB);
-        lds_words<1>(wA + 4 * 52, fs, dA);
-        lds_words<1>(wB + 4 * 52, fs, dB);
+        lds_words<2>(wA + 4 * (48 + 2 * h), fsA, scA);
+        lds_words<2>(wB + 4 * (48 + 2 * h), fsB, scB);
+        lds_words<1>(wA + 4 * 52, fsA, dA);
+        lds_words<1>(wB + 4 * 52, fsB, dB);
         // every lane has read the stage: refill it
         __syncwarp();
         if (it + kDepth < n) request(slot);
@@ -297,9 +328,9 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
     }
 }
 
-template <int EPI, int kWarps>
-cudaError_t launch_w6(const WarpArgs& a, cudaStream_t st, int sm_count, size_t smem) {
-    auto kern = dmmv_q6k_warp_kernel<EPI, kWarps>;
+template <int EPI, int kWarps, bool kRowsAligned>
+cudaError_t launch_w6(const WarpArgs& a, const uint8_t* a_end, cudaStream_t st, int sm_count, size_t smem) {
+    auto kern = dmmv_q6k_warp_kernel<EPI, kWarps, kRowsAligned>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -312,14 +343,27 @@ cudaError_t launch_w6(const WarpArgs& a, cudaStream_t st, int sm_count, size_t s
     if (grid * kWarps > U) grid = U / kWarps;
     if (grid * kWarps > kStreamMaxWorkers) grid = kStreamMaxWorkers / kWarps;
     if (grid == 0) return cudaErrorInvalidConfiguration;
-    return launch_pdl(kern, (uint32_t)grid, kWarps * 32, smem, st, a);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((uint32_t)grid, 1, 1);
+    cfg.blockDim = dim3(kWarps * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, a, a_end);
 }
 
 template <int EPI>
-cudaError_t launch_cfg6(const WarpArgs& a, cudaStream_t st, int sm_count) {
+cudaError_t launch_cfg6(const WarpArgs& a, const uint8_t* a_end, cudaStream_t st, int sm_count) {
     const size_t s8 = smem_bytes6(a.K, 8);
-    if (s8 <= kTwoPerSm) return launch_w6<EPI, 8>(a, st, sm_count, s8);
-    return launch_w6<EPI, 16>(a, st, sm_count, smem_bytes6(a.K, 16));
+    const bool al = ((a.K >> 8) % 8u) == 0;  // 210 * K/256 bytes per row: a multiple of 16 for K % 2048 == 0
+    if (s8 <= kTwoPerSm)
+        return al ? launch_w6<EPI, 8, true>(a, a_end, st, sm_count, s8) : launch_w6<EPI, 8, false>(a, a_end, st, sm_count, s8);
+    const size_t s16 = smem_bytes6(a.K, 16);
+    return al ? launch_w6<EPI, 16, true>(a, a_end, st, sm_count, s16) : launch_w6<EPI, 16, false>(a, a_end, st, sm_count, s16);
 }
 
 }  // namespace
@@ -329,7 +373,8 @@ bool q6k_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a) {
     if (mode != MODE_PLAIN && mode != MODE_SIGMOID_ACC) return false;
     if (!a.scratch_partial || !a.scratch_flags || !a.status) return false;
     const uint32_t bpr = a.K >> 8;
-    if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (bpr % 8u) != 0) return false;  // rows must start 16-byte aligned
+    if (reinterpret_cast<uintptr_t>(a.A) & 15u) return false;  // supersets are fetched in 16-byte pieces from the base
+    if ((bpr % 8u) != 0 && !a.a_end) return false;          // unaligned rows: the end of the buffer must be known
     if (smem_bytes6(a.K, 16) > 227 * 1024 || bpr > (uint32_t)(kPrepBlocks * 8)) return false;
     const uint64_t U = (uint64_t)((a.M + 15) / 16) * bpr;
     if (U < 16 || U > 0xFFFFFFFFull) return false;
@@ -349,8 +394,8 @@ cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t st, uint64
     wa.gpartial = a.scratch_partial;
     wa.gflags = a.scratch_flags;
     wa.status = a.status;
-    cudaError_t e = mode == MODE_PLAIN ? launch_cfg6<EPI_PLAIN>(wa, st, a.sm_count)
-                                       : launch_cfg6<EPI_SIGMOID_ACC>(wa, st, a.sm_count);
+    cudaError_t e = mode == MODE_PLAIN ? launch_cfg6<EPI_PLAIN>(wa, a.a_end, st, a.sm_count)
+                                       : launch_cfg6<EPI_SIGMOID_ACC>(wa, a.a_end, st, a.sm_count);
     if (e == cudaSuccess && launches) ++*launches;
     return e;
 }
