@@ -276,7 +276,7 @@ def test_error_codes(gpu):
 
 @pytest.mark.parametrize("t", [zb.Q4_K, zb.Q6_K], ids=["q4_k", "q6_k"])
 @pytest.mark.parametrize("M,K", [(16, 2048), (67, 2048), (300, 6144), (1000, 12288), (4099, 4096), (33, 14336),
-                                 (2048, 512), (4096, 3072), (300, 1536), (100, 768)])
+                                 (2048, 512), (4096, 3072), (300, 1536), (4100, 768)])
 def test_streaming_shapes(gpu, oracle, t, M, K):
     """Shapes that take the split-K streaming kernels (rows not a multiple of 16, tiles split across
     workers inside a CTA and across CTAs, K up to the shared-memory limit, Q6_K rows that are not

@@ -326,3 +326,30 @@ def test_moe_fused_down_acc_streaming_mxfp4(gpu, oracle, E, M, K, n_used, xs):
         want = h0 + (wts.astype(np.float64)[:, None] * per).sum(0)
         assert canary_intact(y, M)
         assert rel_l2(y[:M].cpu().numpy() - h0, want - h0) <= TOL
+
+
+@pytest.mark.parametrize("E,M,K,n_used,xs", [(12, 2048, 512, 8, 512), (5, 100, 768, 3, 776), (3, 64, 2048, 2, 2048),
+                                           (3, 4100, 1024, 3, 1032)])
+def test_moe_fused_down_acc_streaming_q6k(gpu, oracle, E, M, K, n_used, xs):
+    """y += sum_s w_s W[id_s] x_s through the streaming Q6_K kernel (rows that are not 16-byte aligned,
+    slots side by side along K), twice in a row."""
+    torch, ctx, dd = gpu
+    g = synth.rng(205, E * 1000 + M)
+    w, stride = stacked(g, zb.Q6_K, E, M, K)
+    wd = dev(torch, w)
+    for rep in range(2):
+        ids = np.array([(3 * i + rep + E - 1) % E for i in range(n_used)], np.uint32)
+        wts = (g.random(n_used).astype(np.float32) + np.float32(0.1))
+        x = synth.activations(g, n_used, K)
+        xpad = np.zeros((n_used, xs), np.float32)
+        xpad[:, :K] = x
+        h0 = synth.activations(g, M)
+        y = out_with_canary(torch, M)
+        y[:M] = dev(torch, h0)
+        dd.dispatchMoeFusedDownAcc(zb.Q6_K, wd, dev(torch, xpad.reshape(-1)), y, dev(torch, routing_buf(ids, wts)), M, K,
+                                   stride, n_used, xs)
+        ctx.submit_and_wait()
+        per = oracle.moe_dmmv_f64(w, zb.Q6_K, M, K, stride, ids, K, x)
+        want = h0 + (wts.astype(np.float64)[:, None] * per).sum(0)
+        assert canary_intact(y, M)
+        assert rel_l2(y[:M].cpu().numpy() - h0, want - h0) <= TOL

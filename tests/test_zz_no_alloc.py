@@ -48,7 +48,10 @@ def test_matches_zc_dmmv_twice_in_a_row(gpu, oracle, M, K):
         assert canary_intact(y_new, M) and canary_intact(y_ref, M)
         ref = y_ref[:M].cpu().numpy()
         got = y_new[:M].cpu().numpy()
-        assert np.array_equal(got, ref + ref)  # same kernel, same worker split: bit-identical
+        if M * (K // 256) * 144 >= (2 << 20):
+            assert np.array_equal(got, ref + ref)  # zc_dmmv streams too: same kernel, same worker split, same bits
+        else:  # zc_dmmv runs small matrices one warp per row: same value, different summation order
+            assert rel_l2(got, ref + ref) <= 1e-5
         assert rel_l2(ref, oracle.dmmv_f64(w, zb.Q4_K, M, K, x)) <= TOL
 
 

@@ -693,9 +693,13 @@ int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type, const void* A, uint64_
     a.x_expert_stride = x_expert_stride;
     a.a_end = u8(A, a_size);
     attach_scratch(ctx, a);
-    cudaError_t e = mxfp4_moe_down_acc_eligible(type, a)
-                        ? launch_mxfp4_moe_down_acc(a, ctx->stream, &ctx->launches)
-                        : launch_dmmv(type, MODE_MOE_DOWN_ACC, a, ctx->stream, &ctx->launches);
+    cudaError_t e;
+    if (mxfp4_moe_down_acc_eligible(type, a))
+        e = launch_mxfp4_moe_down_acc(a, ctx->stream, &ctx->launches);
+    else if (q6k_moe_down_acc_eligible(type, a))
+        e = launch_q6k_moe_down_acc(a, ctx->stream, &ctx->launches);
+    else
+        e = launch_dmmv(type, MODE_MOE_DOWN_ACC, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 

@@ -200,9 +200,15 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 
 cudaError_t launch_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches) {
     if (a.M == 0) return cudaSuccess;
-    if (warp_dmmv_eligible(type, mode, a)) return launch_warp_dmmv(type, mode, a, s, launches);
-    if (q6k_dmmv_eligible(type, mode, a)) return launch_q6k_dmmv(mode, a, s, launches);
-    if (mxfp4_dmmv_eligible(type, mode, a)) return launch_mxfp4_dmmv(a, s, launches);
+    // Below a couple of megabytes a matvec is latency-bound and one warp per row (more CTAs) wins over the
+    // streaming kernels.
+    const uint64_t wbytes = (uint64_t)a.M * (a.K / block_size(type)) * bytes_per_block(type) *
+                            (mode == MODE_GATE_UP_SWIGLU ? 2 : 1);
+    if (wbytes >= kStreamMinBytes) {
+        if (warp_dmmv_eligible(type, mode, a)) return launch_warp_dmmv(type, mode, a, s, launches);
+        if (q6k_dmmv_eligible(type, mode, a)) return launch_q6k_dmmv(mode, a, s, launches);
+        if (mxfp4_dmmv_eligible(type, mode, a)) return launch_mxfp4_dmmv(a, s, launches);
+    }
     cudaError_t e;
     // 128-bit weight loads need every block start 16-byte aligned: true for the
     // 144/176-byte K-quant blocks when the base, the second base and the expert

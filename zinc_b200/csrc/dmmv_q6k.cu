@@ -85,15 +85,25 @@ __device__ __forceinline__ uint32_t x_elem6(int lane) {
     const int i = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
     return 128 * (t >> 1) + 64 * sh + 32 * (t & 1) + 8 * i;
 }
+// K: length of the (concatenated) activation. bpe > 0 (MoE down projection): the activation is n_slots
+// vectors of bpe * 256 elements, x + s * x_stride, each scaled by the slot's routing weight wts[s].
 template <int kWarps>
-__device__ __forceinline__ void load_x6(XRegs6& r, const float* __restrict__ x, uint32_t K, int warp, int lane) {
+__device__ __forceinline__ void load_x6(XRegs6& r, const float* __restrict__ x, uint32_t K, uint32_t bpe,
+                                        uint32_t x_stride, const uint32_t* __restrict__ wts, int warp, int lane) {
 #pragma unroll
     for (int b = 0; b < kPrepBlocks; ++b) {
         const uint32_t blk = warp + b * kWarps;
         if (blk < (K >> 8)) {
-            const float* xp = x + (size_t)blk * 256 + x_elem6(lane);
-            r.lo[b] = __ldg(reinterpret_cast<const float4*>(xp));
-            r.hi[b] = __ldg(reinterpret_cast<const float4*>(xp) + 1);
+            const uint32_t slot = bpe ? blk / bpe : 0u, lb = bpe ? blk - slot * bpe : blk;
+            const float* xp = x + (size_t)slot * x_stride + (size_t)lb * 256 + x_elem6(lane);
+            float4 lo = __ldg(reinterpret_cast<const float4*>(xp)), hi = __ldg(reinterpret_cast<const float4*>(xp) + 1);
+            if (wts) {
+                const float w = __uint_as_float(__ldg(wts + slot));
+                lo = make_float4(lo.x * w, lo.y * w, lo.z * w, lo.w * w);
+                hi = make_float4(hi.x * w, hi.y * w, hi.z * w, hi.w * w);
+            }
+            r.lo[b] = lo;
+            r.hi[b] = hi;
         }
     }
 }
@@ -152,18 +162,32 @@ __device__ __forceinline__ void lds_words(uint32_t saddr, uint32_t sh, uint32_t 
     }
 }
 
+// kMoe: MoE down projection, y += sum_s w_s W[routing[s]] x_s: the n_used selected matrices side by side along
+// K, each with its own activation (scaled by w_s while it is converted to fixed point).
 // kRowsAligned: every row starts on a 16-byte boundary (K a multiple of 2048), so all rows of a unit share
 // one offset inside their aligned supersets; otherwise each row has its own (rows are 2-byte aligned).
-template <int EPI, int kWarps, bool kRowsAligned>
+template <int EPI, int kWarps, bool kRowsAligned, bool kMoe = false>
 __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel(const WarpArgs a,
                                                                                  const uint8_t* a_end) {
     extern __shared__ uint8_t smem_raw[];
     pdl_launch_dependents();
-    const Smem6 s = carve6(smem_raw, a.K, kWarps);
+    const uint32_t bpe = a.K >> 8;                        // blocks per row of one matrix
+    const uint32_t bpr = kMoe ? bpe * a.nseg : bpe;       // blocks per (concatenated) row = units per tile
+    const Smem6 s = carve6(smem_raw, bpr * 256, kWarps);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3, h = t >> 1, c = t & 1;
-    const uint32_t bpr = a.K >> 8;
-    const uint64_t row_bytes = (uint64_t)bpr * 210;
+    const uint64_t row_bytes = (uint64_t)bpe * 210;
+    // matrix that holds block `b` of the concatenated row, and the block's index inside it
+    auto matrix_of = [&](uint32_t b, uint32_t& lb) -> const uint8_t* {
+        if constexpr (kMoe) {
+            const uint32_t slot = b / bpe;
+            lb = b - slot * bpe;
+            return a.A[0] + (uint64_t)__ldg(a.routing + slot) * a.expert_stride;
+        } else {
+            lb = b;
+            return a.A[0];
+        }
+    };
     const uint32_t tiles = (a.M + 15) / 16;
     const uint32_t U = tiles * bpr, G = gridDim.x * kWarps;
     const uint32_t me = blockIdx.x * kWarps + warp;
@@ -193,11 +217,13 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
                 }
             }
         } else {
+            uint32_t lb;
+            const uint8_t* mat = matrix_of(p_blk, lb);
 #pragma unroll
             for (int i = 0; i < kPiecesLane6; ++i) {
                 const uint32_t r = piece[i] & 0xFFu, col = piece[i] >> 8;
                 const uint32_t row = min(row0 + r, a.M - 1);
-                const uint8_t* start = a.A[0] + (uint64_t)row * row_bytes + p_blk * 210u;
+                const uint8_t* start = mat + (uint64_t)row * row_bytes + lb * 210u;
                 const uint32_t o = (uint32_t)(reinterpret_cast<uintptr_t>(start) & 15u);
                 if (col * 16 < o + 210u) {  // the piece holds bytes of the block
                     const uint8_t* src = start - o + col * 16;
@@ -216,7 +242,8 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
     cp_async_commit();
     pdl_wait();
     XRegs6 xr;
-    load_x6<kWarps>(xr, a.x, a.K, warp, lane);
+    load_x6<kWarps>(xr, a.x, bpr * 256, kMoe ? bpe : 0u, kMoe ? a.x_slot_stride : 0u,
+                    kMoe ? a.routing + a.nseg : nullptr, warp, lane);
 #pragma unroll
     for (int i = 1; i < kDepth; ++i) {
         if ((uint32_t)i < n) request(i);
@@ -225,7 +252,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
 
     if (tid < kZeroUnits) s.zeros[tid] = make_uint4(0u, 0u, 0u, 0u);
     if (tid < kWarps) s.sflags[tid] = 0u;
-    prep_x6<kWarps>(s, xr, a.K, warp, lane);
+    prep_x6<kWarps>(s, xr, bpr * 256, warp, lane);
     __syncthreads();
 
     uint32_t tile = u0 / bpr, blk = u0 % bpr;
@@ -247,8 +274,10 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
             oA = oB = (blk * 210u) & 15u;
         } else {
             const uint32_t rA = min(tile * 16 + g, a.M - 1), rB = min(tile * 16 + g + 8, a.M - 1);
-            oA = (uint32_t)(reinterpret_cast<uintptr_t>(a.A[0] + (uint64_t)rA * row_bytes + blk * 210u) & 15u);
-            oB = (uint32_t)(reinterpret_cast<uintptr_t>(a.A[0] + (uint64_t)rB * row_bytes + blk * 210u) & 15u);
+            uint32_t lb;
+            const uint8_t* mat = matrix_of(blk, lb);
+            oA = (uint32_t)(reinterpret_cast<uintptr_t>(mat + (uint64_t)rA * row_bytes + lb * 210u) & 15u);
+            oB = (uint32_t)(reinterpret_cast<uintptr_t>(mat + (uint64_t)rB * row_bytes + lb * 210u) & 15u);
         }
         const uint32_t fsA = (oA & 3u) * 8u, fsB = (oB & 3u) * 8u;
         const uint32_t sb = ring_s + slot * kSlot6;
@@ -328,9 +357,9 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
     }
 }
 
-template <int EPI, int kWarps, bool kRowsAligned>
+template <int EPI, int kWarps, bool kRowsAligned, bool kMoe = false>
 cudaError_t launch_w6(const WarpArgs& a, const uint8_t* a_end, cudaStream_t st, int sm_count, size_t smem) {
-    auto kern = dmmv_q6k_warp_kernel<EPI, kWarps, kRowsAligned>;
+    auto kern = dmmv_q6k_warp_kernel<EPI, kWarps, kRowsAligned, kMoe>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -338,7 +367,7 @@ cudaError_t launch_w6(const WarpArgs& a, const uint8_t* a_end, cudaStream_t st, 
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    const uint64_t U = (uint64_t)((a.M + 15) / 16) * (a.K >> 8);
+    const uint64_t U = (uint64_t)((a.M + 15) / 16) * (a.K >> 8) * (kMoe ? a.nseg : 1u);
     uint64_t grid = (uint64_t)sm_count * (16 / kWarps);
     if (grid * kWarps > U) grid = U / kWarps;
     if (grid * kWarps > kStreamMaxWorkers) grid = kStreamMaxWorkers / kWarps;
@@ -381,6 +410,44 @@ bool q6k_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a) {
     return true;
 }
 
+// MoE down projection + weighted accumulate (y += sum_s w_s W[routing[s]] x_s) through the streaming kernel.
+bool q6k_moe_down_acc_eligible(uint32_t type, const DmmvArgs& a) {
+    if (type != T_Q6_K || !a.routing || a.n_used == 0 || !a.a_end) return false;
+    if (!a.scratch_partial || !a.scratch_flags || !a.status) return false;
+    if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (a.expert_stride & 15u) || (a.K & 255u)) return false;
+    if ((a.x_expert_stride & 3u) || (reinterpret_cast<uintptr_t>(a.x) & 15u)) return false;
+    const uint32_t bpr = (a.K >> 8) * a.n_used;
+    if (smem_bytes6(bpr * 256, 16) > 227 * 1024 || bpr > (uint32_t)(kPrepBlocks * 8)) return false;
+    const uint64_t U = (uint64_t)((a.M + 15) / 16) * bpr;
+    if ((uint64_t)a.M * bpr * 210u < 4 * kStreamMinBytes) return false;  // small expert sets: latency-bound either way
+    return U >= 16 && U <= 0xFFFFFFFFull;
+}
+
+cudaError_t launch_q6k_moe_down_acc(const DmmvArgs& a, cudaStream_t st, uint64_t* launches) {
+    WarpArgs wa;
+    wa.A[0] = wa.A[1] = a.A;
+    wa.x = a.x;
+    wa.y = a.y;
+    wa.gate = nullptr;
+    wa.M = a.M;
+    wa.K = a.K;
+    wa.acc_mode = 1;
+    wa.gpartial = a.scratch_partial;
+    wa.gflags = a.scratch_flags;
+    wa.status = a.status;
+    wa.nseg = a.n_used;
+    wa.routing = a.routing;
+    wa.expert_stride = a.expert_stride;
+    wa.x_slot_stride = a.x_expert_stride;
+    const uint32_t Kt = a.K * a.n_used;
+    const size_t s8 = smem_bytes6(Kt, 8);
+    const cudaError_t e = s8 <= kTwoPerSm ? launch_w6<EPI_ACC, 8, false, true>(wa, a.a_end, st, a.sm_count, s8)
+                                          : launch_w6<EPI_ACC, 16, false, true>(wa, a.a_end, st, a.sm_count,
+                                                                                 smem_bytes6(Kt, 16));
+    if (e == cudaSuccess && launches) ++*launches;
+    return e;
+}
+
 cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t st, uint64_t* launches) {
     WarpArgs wa;
     wa.A[0] = a.A;
@@ -394,6 +461,7 @@ cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t st, uint64
     wa.gpartial = a.scratch_partial;
     wa.gflags = a.scratch_flags;
     wa.status = a.status;
+    wa.nseg = 0;
     cudaError_t e = mode == MODE_PLAIN ? launch_cfg6<EPI_PLAIN>(wa, a.a_end, st, a.sm_count)
                                        : launch_cfg6<EPI_SIGMOID_ACC>(wa, a.a_end, st, a.sm_count);
     if (e == cudaSuccess && launches) ++*launches;

@@ -47,6 +47,8 @@ struct DmmvArgs {
 };
 
 // Capacity of the split-K scratch a context owns.
+// Below this many weight bytes a matvec is latency-bound and the one-warp-per-row kernels (more CTAs) win.
+constexpr uint64_t kStreamMinBytes = 2u << 20;
 constexpr uint32_t kStreamMaxWorkers = 4096;  // warps that may publish a partial tile
 constexpr size_t kStreamPartialBytes = (size_t)kStreamMaxWorkers * 32 * sizeof(float);
 constexpr size_t kStreamFlagBytes = (size_t)kStreamMaxWorkers * sizeof(uint32_t);
@@ -74,6 +76,8 @@ bool mxfp4_moe_down_acc_eligible(uint32_t type, const DmmvArgs& a);
 cudaError_t launch_mxfp4_moe_down_acc(const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
 bool q6k_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a);
 cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
+bool q6k_moe_down_acc_eligible(uint32_t type, const DmmvArgs& a);
+cudaError_t launch_q6k_moe_down_acc(const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
 
 // Returns cudaSuccess or the launch error; *launches is incremented per kernel.
 cudaError_t launch_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t s, uint64_t* launches);
