@@ -126,7 +126,7 @@ def test_moe_dmmv_batched(gpu, oracle):
 
 
 @pytest.mark.parametrize("rule", [zb.ROUTE_SOFTMAX_ALL_RENORM, zb.ROUTE_TOPK_THEN_SOFTMAX])
-@pytest.mark.parametrize("n,k,T", [(8, 3, 1), (256, 8, 64), (32, 4, 17), (1000, 20, 3)])
+@pytest.mark.parametrize("n,k,T", [(8, 3, 1), (256, 8, 64), (32, 4, 17), (1000, 20, 3), (2000, 6, 2), (129, 8, 5)])
 def test_softmax_topk(gpu, oracle, rule, n, k, T):
     torch, ctx, dd = gpu
     g = synth.rng(204, n * 10 + rule)

@@ -133,6 +133,86 @@ __global__ void __launch_bounds__(kTopkThreads) softmax_topk_kernel(
     }
 }
 
+// The same selection for up to 32 * VPL experts with one warp per token and no block-wide barrier: lane l
+// holds experts l, l + 32, ... in registers. A router has at most a few hundred experts, and the k rounds
+// of block-wide barriers of the kernel above cost more than the arithmetic.
+template <int VPL>
+__global__ void __launch_bounds__(128) softmax_topk_warp_kernel(
+    const float* __restrict__ logits, const float* __restrict__ bias, uint32_t* __restrict__ out,
+    uint32_t n, uint32_t k, uint32_t rule, uint32_t n_tokens, uint32_t logits_stride, uint32_t out_stride) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t tok = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (tok >= n_tokens) return;
+    const float* lg = logits + (size_t)tok * logits_stride;
+    uint32_t* o = out + (size_t)tok * out_stride;
+    const float floor_v = rule == 0u ? -1.0f : -INFINITY;
+    const float gone = rule == 0u ? -2.0f : -INFINITY;  // never selected (again)
+
+    float v[VPL];
+    float lmax = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        const uint32_t i = lane + 32 * j;
+        v[j] = i < n ? lg[i] + (bias ? bias[i] : 0.0f) : -INFINITY;
+        lmax = fmaxf(lmax, v[j]);
+    }
+    if (rule == 0u) {  // softmax over all experts first
+        for (int o2 = 16; o2 > 0; o2 >>= 1) lmax = fmaxf(lmax, __shfl_xor_sync(0xFFFFFFFFu, lmax, o2));
+        float lsum = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+            const uint32_t i = lane + 32 * j;
+            v[j] = i < n ? expf(v[j] - lmax) : 0.f;
+            lsum += v[j];
+        }
+        const float sum = warp_sum(lsum);
+#pragma unroll
+        for (int j = 0; j < VPL; ++j) {
+            const uint32_t i = lane + 32 * j;
+            if (sum > 0.f) v[j] = v[j] / sum;
+            if (i >= n) v[j] = gone;
+        }
+    }
+    const float v0 = __shfl_sync(0xFFFFFFFFu, v[0], 0);  // expert 0, for the "nothing above the floor" case
+    for (uint32_t ki = 0; ki < k; ++ki) {
+        ValIdx best{floor_v, 0u};
+#pragma unroll
+        for (int j = 0; j < VPL; ++j)
+            if (v[j] > best.v) best = ValIdx{v[j], (uint32_t)(lane + 32 * j)};
+        for (int o2 = 16; o2 > 0; o2 >>= 1) {
+            ValIdx other{__shfl_xor_sync(0xFFFFFFFFu, best.v, o2), __shfl_xor_sync(0xFFFFFFFFu, best.i, o2)};
+            best = better(best, other);
+        }
+        if (!(best.v > floor_v)) best = ValIdx{rule == 0u ? floor_v : v0, 0u};
+        if (lane == 0) {
+            o[ki] = best.i;
+            o[k + ki] = __float_as_uint(best.v);
+        }
+#pragma unroll
+        for (int j = 0; j < VPL; ++j)
+            if (best.i == (uint32_t)(lane + 32 * j)) v[j] = gone;
+    }
+    if (lane == 0) {
+        if (rule == 0u) {
+            float ws = 0.f;
+            for (uint32_t i = 0; i < k; ++i) ws += __uint_as_float(o[k + i]);
+            if (ws > 0.f)
+                for (uint32_t i = 0; i < k; ++i) o[k + i] = __float_as_uint(__uint_as_float(o[k + i]) / ws);
+        } else {
+            float mx = -INFINITY;
+            for (uint32_t i = 0; i < k; ++i) mx = fmaxf(mx, __uint_as_float(o[k + i]));
+            float sum = 0.f;
+            for (uint32_t i = 0; i < k; ++i) {
+                const float w = expf(__uint_as_float(o[k + i]) - mx);
+                o[k + i] = __float_as_uint(w);
+                sum += w;
+            }
+            if (sum > 0.f)
+                for (uint32_t i = 0; i < k; ++i) o[k + i] = __float_as_uint(__uint_as_float(o[k + i]) / sum);
+        }
+    }
+}
+
 // ---- combine / activation ------------------------------------------------------------
 // src/shaders/moe_weighted_acc.comp:23-33
 __global__ void moe_weighted_acc_kernel(float* __restrict__ a, const float* __restrict__ b,
@@ -303,6 +383,20 @@ cudaError_t launch_softmax_topk(const float* logits, const float* bias, uint32_t
                                 uint32_t k, uint32_t rule, uint32_t n_tokens, uint32_t logits_stride,
                                 uint32_t out_stride, cudaStream_t s, uint64_t* launches) {
     if (n_tokens == 0) return cudaSuccess;
+    if (n_experts <= 1024) {  // one warp per token, values in registers
+        const uint32_t grid = (n_tokens + 3) / 4;
+        if (n_experts <= 32)
+            softmax_topk_warp_kernel<1><<<grid, 128, 0, s>>>(logits, bias, out, n_experts, k, rule, n_tokens,
+                                                             logits_stride, out_stride);
+        else if (n_experts <= 256)
+            softmax_topk_warp_kernel<8><<<grid, 128, 0, s>>>(logits, bias, out, n_experts, k, rule, n_tokens,
+                                                             logits_stride, out_stride);
+        else
+            softmax_topk_warp_kernel<32><<<grid, 128, 0, s>>>(logits, bias, out, n_experts, k, rule, n_tokens,
+                                                              logits_stride, out_stride);
+        if (launches) ++*launches;
+        return cudaGetLastError();
+    }
     const size_t smem = (size_t)n_experts * sizeof(float);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(softmax_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
