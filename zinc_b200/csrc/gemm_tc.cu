@@ -446,6 +446,187 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     }
 }
 
+// ---- few tokens (N <= 128): tokens on the TMEM lanes, weight rows on the columns ------------------------
+// With at most 128 tokens a 128-row x 128-token tile issues tcgen05.mma with N = 128, and the issuing
+// thread (about 73 cycles per instruction) cannot keep up with 64-cycle instructions. Here the roles are
+// swapped: the MMA's M operand is the activation tile (128 tokens x 64 columns, TMA), its N operand the
+// dequantised weights (256 rows x 64 columns per stage), so every instruction is a full 128 x 256 x 16.
+// Q4_K only; weights are read straight from global memory into registers one block ahead (no raw
+// staging ring: the 32 KB weight stages need the room); split K over up to 8 CTAs per tile.
+constexpr int kSmRows = 256;                                   // weight rows per tile = accumulator columns
+constexpr uint32_t kSmWBytes = kSmRows * kBK * 2;              // 32 KB per weight stage
+constexpr uint32_t kSmXBytes = 128 * kBK * 2;                  // 16 KB per activation stage
+constexpr int kSmXSlots = 4;
+constexpr uint32_t kSmXOffset = kAStages * kSmWBytes;
+constexpr uint32_t kSmBarOffset = kSmXOffset + kSmXSlots * kSmXBytes;
+constexpr uint32_t kSmSmemBytes = kSmBarOffset + 256 + 1024;
+constexpr int kSmThreads = 64 + 512;                           // MMA warp, TMA warp, 16 dequant warps
+
+__global__ void __launch_bounds__(kSmThreads, 1)
+gemm_tc_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* smem_x = smem + kSmXOffset;
+    Bars* bars = reinterpret_cast<Bars*>(smem + kSmBarOffset);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t m0 = blockIdx.x * kSmRows, n0 = blockIdx.y * 128;
+    const int nblk_all = g.K >> 8;
+    const int b_begin = (int)((long long)blockIdx.z * nblk_all / gridDim.z);
+    const int b_end = (int)((long long)(blockIdx.z + 1) * nblk_all / gridDim.z);
+    const int n_it = (b_end - b_begin) * 4;
+
+    if (tid == 0) {
+        for (int s = 0; s < kAStages; ++s) {
+            mbar_init(&bars->full_a[s], 8);   // weight stage: one arrival per warp of the owning half
+            mbar_init(&bars->empty_a[s], 1);
+            mbar_init(&bars->full_b[s], 1);   // activation slot
+        }
+        mbar_init(&bars->accum, 1);
+        bars->failed = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(&bars->tmem_base)),
+                     "r"((uint32_t)kSmRows)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {  // ---- MMA issuer: activation stage it & 3, weight stage it & 3 ----
+            constexpr uint32_t idesc = instr_desc<kSmRows>();  // M = 128 tokens, N = 256 weight rows
+            bool ok = true;
+            for (int it = 0; it < n_it && ok; ++it) {
+                const int st = it & 3;
+                const uint32_t ph = (it >> 2) & 1;
+                ok = wait_or_fail<false>(&bars->full_a[st], ph, bars, g.status, 111) &&
+                     wait_or_fail<false>(&bars->full_b[st], ph, bars, g.status, 112);
+                if (!ok) break;
+                tc_fence_after();
+                const uint64_t dx = smem_desc(smem_u32(smem_x + st * kSmXBytes));
+                const uint64_t dw = smem_desc(smem_u32(smem + st * kSmWBytes));
+#pragma unroll
+                for (int k = 0; k < kBK / 16; ++k) umma_bf16(tmem, dx + 2 * k, dw + 2 * k, idesc, (it | k) ? 1u : 0u);
+                umma_commit(&bars->empty_a[st]);  // frees the weight stage and the activation slot
+            }
+            umma_commit(&bars->accum);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {  // ---- TMA loader of the activations ----
+            for (int it = 0; it < n_it; ++it) {
+                const int st = it & 3;
+                if (!wait_or_fail(&bars->empty_a[st], ((it >> 2) & 1) ^ 1, bars, g.status, 113)) break;
+                mbar_expect_tx(&bars->full_b[st], kSmXBytes);
+                tma_load_2d(smem_x + st * kSmXBytes, &tmap_x, (b_begin * 4 + it) * kBK, (int)n0, &bars->full_b[st]);
+            }
+        }
+    } else {
+        // ---- dequant producers: thread = (row, half); half h owns groups h and h + 2 of every block ----
+        const int p = tid - 64;
+        const int row = p & 255, h = p >> 8;
+        const uint32_t grow = min(m0 + (uint32_t)row, g.M - 1);  // rows past M are computed and dropped
+        const uint8_t* rp = g.A + (uint64_t)grow * nblk_all * 144u + (uint64_t)b_begin * 144u;
+        uint4 hdr = __ldg(reinterpret_cast<const uint4*>(rp));
+        uint4 qa0 = __ldg(reinterpret_cast<const uint4*>(rp + 16 + h * 32));
+        uint4 qa1 = __ldg(reinterpret_cast<const uint4*>(rp + 32 + h * 32));
+        uint4 qb0 = __ldg(reinterpret_cast<const uint4*>(rp + 80 + h * 32));
+        uint4 qb1 = __ldg(reinterpret_cast<const uint4*>(rp + 96 + h * 32));
+        bool ok = true;
+        for (int b = 0; b < b_end - b_begin && ok; ++b) {
+            const uint4 chdr = hdr, ca0 = qa0, ca1 = qa1, cb0 = qb0, cb1 = qb1;
+            if (b + 1 < b_end - b_begin) {
+                const uint8_t* np = rp + (uint64_t)(b + 1) * 144u;
+                hdr = __ldg(reinterpret_cast<const uint4*>(np));
+                qa0 = __ldg(reinterpret_cast<const uint4*>(np + 16 + h * 32));
+                qa1 = __ldg(reinterpret_cast<const uint4*>(np + 32 + h * 32));
+                qb0 = __ldg(reinterpret_cast<const uint4*>(np + 80 + h * 32));
+                qb1 = __ldg(reinterpret_cast<const uint4*>(np + 96 + h * 32));
+            }
+            const __half2 dd = *reinterpret_cast<const __half2*>(&chdr.x);
+            const float d = __low2float(dd), dmin = __high2float(dd);
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int grp = h + 2 * half;
+                uint32_t s0, mn0, s1, mn1;
+                scale_min_k4(2 * grp, chdr.y, chdr.z, chdr.w, s0, mn0);
+                scale_min_k4(2 * grp + 1, chdr.y, chdr.z, chdr.w, s1, mn1);
+                if (!wait_or_fail(&bars->empty_a[grp], (b & 1) ^ 1, bars, g.status, 114)) {
+                    ok = false;
+                    break;
+                }
+                dequant_group_q4k(half ? cb0 : ca0, half ? cb1 : ca1, d * (float)s0, dmin * (float)mn0, d * (float)s1,
+                                  dmin * (float)mn1, smem + grp * kSmWBytes, row);
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bars->full_a[grp]);
+            }
+        }
+        // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4; a lane is a token, columns are rows ----
+        if (warp < 6) {
+            if (wait_or_fail(&bars->accum, 0, bars, g.status, 115)) {
+                __syncwarp();
+                tc_fence_after();
+                const uint32_t q = warp & 3;
+                const uint32_t n = n0 + q * 32 + lane;
+#pragma unroll 1
+                for (int c = 0; c < kSmRows / 32; ++c) {
+                    uint32_t v[32];
+                    const uint32_t taddr = tmem + ((q * 32u) << 16) + c * 32;
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+                          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+                          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+                          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                        : "r"(taddr)
+                        : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (n < g.N) {
+                        float* dst = g.D + (uint64_t)n * g.stride_d + m0 + c * 32;
+                        const bool vec = m0 + c * 32 + 32 <= g.M && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
+                        if (vec) {  // 32 consecutive rows of one token: 16-byte stores / vector reductions
+#pragma unroll
+                            for (int jj = 0; jj < 32; jj += 4) {
+                                const float4 f = make_float4(__uint_as_float(v[jj]), __uint_as_float(v[jj + 1]),
+                                                             __uint_as_float(v[jj + 2]), __uint_as_float(v[jj + 3]));
+                                if (gridDim.z == 1)
+                                    *reinterpret_cast<float4*>(dst + jj) = f;
+                                else
+                                    atomicAdd(reinterpret_cast<float4*>(dst + jj), f);
+                            }
+                        } else {
+#pragma unroll
+                            for (int jj = 0; jj < 32; ++jj) {
+                                if (m0 + c * 32 + jj < g.M) {
+                                    if (gridDim.z == 1)
+                                        dst[jj] = __uint_as_float(v[jj]);
+                                    else
+                                        atomicAdd(dst + jj, __uint_as_float(v[jj]));
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kSmRows)
+                     : "memory");
+    }
+}
+
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -514,10 +695,51 @@ cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, u
     return cudaGetLastError();
 }
 
+cudaError_t launch_small(const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N, uint32_t K,
+                         uint32_t stride_b, uint32_t stride_d, uint32_t* status, cudaStream_t s) {
+    EncodeFn enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {K, N};
+    const cuuint64_t strides[1] = {(cuuint64_t)stride_b * 2};
+    const cuuint32_t box[2] = {kBK, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(B), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)kSmSmemBytes);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    GemmArgs g{A, D, M, N, K, stride_d, status};
+    dim3 grid((M + kSmRows - 1) / kSmRows, (N + 127) / 128, 1);
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const uint32_t tiles = grid.x * grid.y;
+    uint32_t splits = tiles ? (uint32_t)sms / tiles : 1;
+    splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
+    while (splits > 1 && (K >> 8) / splits < 2) --splits;
+    if (splits > 1) {
+        cudaError_t e = cudaMemset2DAsync(D, (size_t)stride_d * 4, 0, (size_t)M * 4, N, s);
+        if (e != cudaSuccess) return e;
+        grid.z = splits;
+    }
+    gemm_tc_small_kernel<<<grid, kSmThreads, kSmSmemBytes, s>>>(map, g);
+    return cudaGetLastError();
+}
+
 template <int TYPE>
 cudaError_t launch_typed(const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N, uint32_t K,
                          uint32_t stride_b, uint32_t stride_d, uint32_t* status, cudaStream_t s) {
-    if (N <= 128) return launch_tile<TYPE, 128, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
+    if (N <= 128) {
+        if constexpr (TYPE == T_Q4_K) return launch_small(A, B, D, M, N, K, stride_b, stride_d, status, s);
+        return launch_tile<TYPE, 128, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
+    }
     if (N <= 256) return launch_tile<TYPE, 256, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
     return launch_tile<TYPE, 256, 2>(A, B, D, M, N, K, stride_b, stride_d, status, s);
 }
