@@ -290,6 +290,79 @@ def moe_decode_bench(torch, zb, args, local_rank):
     return 0
 
 
+def moe_prefill_bench(torch, zb, args, local_rank):
+    """The routed-expert matmuls of one MoE layer over a prefill batch: gate and up (one activation row per
+    token, n_used experts each), SwiGLU, down (one row per (token, slot) pair) and the weighted scatter
+    back to the tokens. Routing ids come from softmax_topk over N(0,1) logits, before the timed region.
+    One JSON line per configuration and path: grouped by expert on the tensor cores (Q4_K / Q6_K, with a
+    workspace) and the per-pair kernel the reference's Vulkan path uses."""
+    from zinc_b200 import synth
+    from zinc_b200.moe_step import GPT_OSS_MOE, QWEN35_MOE
+
+    peak, peak_kind = measured_peaks()
+    stream = torch.cuda.Stream()
+    dev = f"cuda:{local_rank}"
+    with torch.cuda.stream(stream):
+        ctx = zb.Context(local_rank, stream=stream.cuda_stream)
+        dd = zb.DmmvDispatch(ctx)
+        for name, S, T in (("qwen3.5-35b-a3b-like MoE layer (256 experts top-8, Q4_K gate/up, Q6_K down)", QWEN35_MOE, 512),
+                           ("gpt-oss-20b-shaped MoE layer (32 experts top-4, MXFP4)", GPT_OSS_MOE, 1024)):
+            T = args.tokens or T
+            E, k, H, F = S.n_experts, S.top_k, S.hidden, S.ffn
+            Wg = synth.torch_quant_matrix(S.t_gate_up, E * F, H, dev, 11)
+            Wu = synth.torch_quant_matrix(S.t_gate_up, E * F, H, dev, 12)
+            Wd = synth.torch_quant_matrix(S.t_down, E * H, F, dev, 13)
+            sg, sd = zb.expert_slice_bytes(S.t_gate_up, F, H), zb.expert_slice_bytes(S.t_down, H, F)
+            X = torch.randn(T, H, device=dev)
+            logits = torch.randn(T, E, device=dev)
+            routing = torch.zeros(T * 2 * k, dtype=torch.int32, device=dev)
+            dd.dispatchSoftmaxTopk(logits, routing, E, k, S.rule, T)
+            ctx.submit_and_wait()
+            ids = routing.view(T, 2 * k)[:, :k].contiguous()
+            gate = torch.empty(T * k * F, device=dev)
+            up = torch.empty(T * k * F, device=dev)
+            act = torch.empty(T * k * F, device=dev)
+            down = torch.empty(T * k * H, device=dev)
+            hidden = torch.zeros(T * H, device=dev)
+            touched = int(torch.unique(ids).numel())
+            wbytes = touched * (2 * sg + sd)
+            flops = 2.0 * T * k * 3 * F * H
+
+            def layer():
+                dd.recordMoeBatchedDispatch(S.t_gate_up, Wg, X, gate, ids, F, H, sg, E, k, T, H, k * F)
+                dd.recordMoeBatchedDispatch(S.t_gate_up, Wu, X, up, ids, F, H, sg, E, k, T, H, k * F)
+                dd.dispatchSwiglu(gate, up, act, T * k * F, oai=S.oai)
+                dd.recordMoeBatchedDispatch(S.t_down, Wd, act, down, ids, H, F, sd, E, 1, T * k, F, H)
+                dd.dispatchMoeRouteScatter(routing, down, hidden, T, H, k, 2 * k)
+
+            ws = torch.empty(max(dd.moeGroupedWorkspaceBytes(T, k, H, E), dd.moeGroupedWorkspaceBytes(T * k, 1, F, E)),
+                             dtype=torch.uint8, device=dev)
+            for path in ("grouped", "per_pair"):
+                dd.setWorkspace(ws if path == "grouped" else None)
+                n0 = ctx.launch_count
+                layer()
+                launches = ctx.launch_count - n0
+                reps = max(5, min(args.steps, 50 if path == "grouped" else 5))
+                ms = _timed_graph(torch, stream, layer, reps)
+                gbs = wbytes / (ms * 1e-3) / 1e9
+                print(json.dumps({
+                    "metric": METRIC, "value": gbs, "unit": UNIT, "n_gpus": 1, "steps": reps, "warmup": 4,
+                    "ms_per_step": ms, "higher_is_better": True,
+                    "dtype": "bf16" if path == "grouped" and launches > 5 else "f32", "data": "synthetic",
+                    "config": {"workload": f"{name}, prefill T={T}, routed experts only", "path": path,
+                               "experts_touched": touched, "weight_bytes_touched": wbytes,
+                               "tokens_per_s": T / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
+                               "l2": "expert weights of the layer are larger than L2"},
+                    "gpu_launches": launches * reps, "gpu_launches_per_step": launches,
+                    "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "peak_kind": peak_kind,
+                                 "unit": "GB/s", "frac": gbs / peak, "traffic": None},
+                }), flush=True)
+            dd.setWorkspace(None)
+            del Wg, Wu, Wd, ws
+            torch.cuda.empty_cache()
+    return 0
+
+
 def prefill_gemm_bench(torch, zb, args, local_rank):
     """Batched-prefill dequant-GEMM D[T][M] = X[T][K] W[M][K]^T (bf16 activations, f32 out), one JSON
     line per case: gate-shaped Q4_K 12288 x 4096 and down-shaped Q6_K 4096 x 12288 at T = 128, 512,
@@ -345,12 +418,14 @@ def main():
     ap.add_argument("--steps", type=int, default=400)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="zinc_b200", choices=["zinc_b200", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill_gemm", "dmmv_single", "moe_decode"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill_gemm", "dmmv_single", "moe_decode", "moe_prefill"],
                     help="decode: the headline decode step; prefill_gemm: the batched-prefill dequant-GEMM cases; "
-                         "dmmv_single: one Q4_K 4096x4096 matvec; moe_decode: the two MoE layers at batch 1")
+                         "dmmv_single: one Q4_K 4096x4096 matvec; moe_decode: the two MoE layers at batch 1; "
+                         "moe_prefill: one MoE layer's routed experts over a prefill batch")
     ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
                     help="N > 1: the library's one-shot peer all-reduce (default) or NCCL for the hidden-state sums")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug; invalidates the number)")
+    ap.add_argument("--tokens", type=int, default=0, help="moe_prefill: override the prefill batch (default 512 / 1024)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
@@ -384,6 +459,8 @@ def main():
         return prefill_gemm_bench(torch, zb, args, local_rank)
     if args.workload == "dmmv_single":
         return dmmv_single_bench(torch, zb, args, local_rank)
+    if args.workload == "moe_prefill":
+        return moe_prefill_bench(torch, zb, args, local_rank)
     if args.workload == "moe_decode":
         return moe_decode_bench(torch, zb, args, local_rank)
 

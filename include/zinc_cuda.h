@@ -264,14 +264,26 @@ int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type,
  * routing is the flattened [n_tokens][n_experts_used] id table; strides in
  * elements. K % 256 != 0 returns ZC_ERR_INVALID_ARG for K-quants. Replaces
  * recordMoeBatchedDispatch (src/compute/dmmv.zig:746-792;
- * src/shaders/dmmv_q4k_moe_batched.comp:70-164). Like the reference's kernel, every (token, slot)
- * pair is computed on its own; tokens that share an expert are not grouped yet. */
+ * src/shaders/dmmv_q4k_moe_batched.comp:70-164). Without a workspace every (token, slot) pair is
+ * computed on its own in f32, like the reference's kernel. With a workspace (zc_set_workspace) of at
+ * least zc_moe_grouped_workspace_bytes(...), n_tokens >= 16, type Q4_K or Q6_K and 16-byte aligned
+ * A / expert_stride / X, the pairs are grouped by expert (as the reference's Metal path does,
+ * src/shaders/metal/moe_route_pack.metal:13-36) and each expert's weights are dequantised once per
+ * tile of its tokens on the tensor cores: bf16 operands, f32 accumulation (relative L2 <= 5e-3).
+ * Ids >= n_experts are skipped there (their output rows are left untouched). */
 int32_t zc_moe_dmmv_batched(zc_ctx* ctx, uint32_t type,
                             const void* A, uint64_t a_size, const void* X, uint64_t x_size,
                             void* Y, uint64_t y_size, const void* routing, uint64_t routing_size,
                             uint32_t M, uint32_t K, uint64_t expert_stride,
                             uint32_t n_experts, uint32_t n_experts_used, uint32_t n_tokens,
                             uint32_t x_token_stride, uint32_t y_token_stride);
+
+/* Caller-owned device scratch for the grouped MoE prefill path; NULL / 0 removes it. The library never
+ * allocates on the hot path, so the engine lends the bytes (its prefill scratch arena). 256-byte aligned.
+ * The contents are only meaningful during one zc_moe_dmmv_batched call (in stream order). No counterpart
+ * in the reference, whose Metal path owns route_ids / route_counts buffers (src/compute/forward_metal.zig). */
+int32_t zc_set_workspace(zc_ctx* ctx, void* workspace, uint64_t size);
+uint64_t zc_moe_grouped_workspace_bytes(uint32_t n_tokens, uint32_t n_experts_used, uint32_t K, uint32_t n_experts);
 
 /* ---- routing, combine, activation -----------------------------------------------------------
  * zc_softmax_topk: per token t, out[t*out_stride ..] = [k ids u32][k weights f32 bits].

@@ -125,6 +125,46 @@ def test_moe_dmmv_batched(gpu, oracle):
                                     k * M)
 
 
+TOL_TC = 5e-3  # bf16 operands on the tensor cores (prefill bar)
+
+
+@pytest.mark.parametrize("t,E,M,K,k,T,pad", [
+    (zb.Q4_K, 8, 192, 512, 2, 64, 0),     # 32-pair tiles, last row tile half empty
+    (zb.Q4_K, 4, 256, 1024, 2, 300, 8),   # 128-pair tiles, several tiles per expert, padded token strides
+    (zb.Q6_K, 8, 200, 512, 2, 64, 0),     # 420-byte rows: only 4-byte aligned
+    (zb.Q6_K, 3, 128, 768, 1, 400, 0),    # 630-byte rows: only 2-byte aligned; one slot per row (down-projection form)
+])
+def test_moe_dmmv_batched_grouped(gpu, oracle, t, E, M, K, k, T, pad):
+    # the same entry point with a workspace: pairs grouped by expert, tensor-core tiles
+    torch, ctx, dd = gpu
+    g = synth.rng(207, E * 1000 + T)
+    w, stride = stacked(g, t, E, M, K)
+    if stride % 16:
+        pytest.skip("expert stride not 16-byte aligned: the per-pair kernel serves it")
+    ids = g.integers(0, E - 1, size=(T, k)).astype(np.uint32)  # the last expert gets no pair
+    ids[: T // 2, 0] = 1                                        # and expert 1 many
+    xs, ys = K + pad, k * M + pad
+    X = np.zeros((T, xs), np.float32)
+    X[:, :K] = synth.activations(g, T, K)
+    Y = out_with_canary(torch, T * ys)
+    ws = torch.empty(dd.moeGroupedWorkspaceBytes(T, k, K, E), dtype=torch.uint8, device="cuda")
+    dd.setWorkspace(ws)
+    try:
+        dd.recordMoeBatchedDispatch(t, dev(torch, w), dev(torch, X), Y, dev(torch, ids), M, K, stride, E, k, T, xs, ys)
+        ctx.submit_and_wait()
+    finally:
+        dd.setWorkspace(None)
+    got = Y[:T * ys].cpu().numpy().reshape(T, ys)
+    want = np.stack([oracle.moe_dmmv_f64(w, t, M, K, stride, ids[tok], K, np.repeat(X[tok:tok + 1, :K], k, axis=0))
+                     for tok in range(T)])
+    have = got[:, :k * M].reshape(T, k, M)
+    assert rel_l2(have, want) <= TOL_TC                                     # the bar: all outputs of the call
+    assert max(rel_l2(have[tok], want[tok]) for tok in range(T)) <= 2e-2    # and no single token far off
+    assert canary_intact(Y, T * ys)
+    if pad:  # the padding between token rows is not written
+        assert np.all(got[:, k * M:] == got[0, k * M])
+
+
 @pytest.mark.parametrize("rule", [zb.ROUTE_SOFTMAX_ALL_RENORM, zb.ROUTE_TOPK_THEN_SOFTMAX])
 @pytest.mark.parametrize("n,k,T", [(8, 3, 1), (256, 8, 64), (32, 4, 17), (1000, 20, 3), (2000, 6, 2), (129, 8, 5)])
 def test_softmax_topk(gpu, oracle, rule, n, k, T):

@@ -56,6 +56,7 @@ _OPS = {
     "zc_memset": [_vp, _u64, _i32, _u64],
     "zc_set_stream": [_vp],
     "zc_use_own_stream": [],
+    "zc_set_workspace": [_vp, _u64],
     "zc_comm_init": [_u32, _u32, _vp],
     "zc_comm_connect": [_vp],
     "zc_allreduce_sum_f32": [_vp, _u64, _u64, _u32],
@@ -74,7 +75,7 @@ _OPS = {
 EXPORTS = sorted(list(_OPS) + [
     "zc_init", "zc_get_stream", "zc_last_error", "zc_status_string", "zc_launch_count",
     "zc_block_size", "zc_bytes_per_block", "zc_tensor_size_bytes", "zc_expert_slice_bytes",
-    "zc_dmmv_supported", "zc_moe_dmmv_supported", "zc_dmmv_q4k_static_scratch",
+    "zc_dmmv_supported", "zc_moe_dmmv_supported", "zc_dmmv_q4k_static_scratch", "zc_moe_grouped_workspace_bytes",
 ])
 
 _lib = None
@@ -106,6 +107,8 @@ def lib() -> C.CDLL:
         for name in ("zc_block_size", "zc_bytes_per_block"):
             getattr(L, name).restype = _u32
             getattr(L, name).argtypes = [_u32]
+        L.zc_moe_grouped_workspace_bytes.restype = _u64
+        L.zc_moe_grouped_workspace_bytes.argtypes = [_u32, _u32, _u32, _u32]
         L.zc_tensor_size_bytes.restype = _u64
         L.zc_tensor_size_bytes.argtypes = [_u32, _u64]
         L.zc_expert_slice_bytes.restype = _u64

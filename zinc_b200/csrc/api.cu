@@ -32,6 +32,9 @@ struct zc_ctx {
     zc::CommArgs comm;
     uint8_t* comm_local = nullptr;
     bool comm_open[zc::kCommMaxRanks] = {false};
+    // caller-owned scratch for the grouped MoE prefill path (zc_set_workspace)
+    void* workspace = nullptr;
+    uint64_t workspace_size = 0;
     char err[512] = {0};
 };
 
@@ -721,11 +724,34 @@ int32_t zc_moe_dmmv_batched(zc_ctx* ctx, uint32_t type, const void* A, uint64_t 
     ZC_TRY(check_vec(ctx, fn, "Y", Y, y_size, 0,
                      ((uint64_t)(n_tokens - 1) * y_token_stride + (uint64_t)n_experts_used * M) * 4, 4));
     ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0, (uint64_t)n_tokens * n_experts_used * 4, 4));
+    // With a workspace and a prefill-sized batch: group the pairs by expert and run the tensor-core tiles.
+    if (ctx->workspace && n_tokens >= 16 &&
+        moe_grouped_eligible(type, u8(A, 0), K, expert_stride, n_experts, (uint64_t)n_tokens * n_experts_used,
+                             f32p(X, 0), x_token_stride, ctx->workspace_size)) {
+        cudaError_t eg = launch_moe_grouped(type, u8(A, 0), a_size, f32p(X, 0), f32m(Y, 0),
+                                            static_cast<const uint32_t*>(routing), M, K, expert_stride, n_experts,
+                                            n_experts_used, n_tokens, x_token_stride, y_token_stride, ctx->workspace,
+                                            ctx->status_dev, ctx->stream, &ctx->launches);
+        return eg == cudaSuccess ? ZC_OK : cuda_fail(ctx, eg, fn);
+    }
     cudaError_t e = launch_moe_dmmv_batched(type, u8(A, 0), f32p(X, 0), f32m(Y, 0),
                                             static_cast<const uint32_t*>(routing), M, K, expert_stride,
                                             n_experts_used, n_tokens, x_token_stride, y_token_stride, ctx->stream,
                                             &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+uint64_t zc_moe_grouped_workspace_bytes(uint32_t n_tokens, uint32_t n_experts_used, uint32_t K, uint32_t n_experts) {
+    return moe_grouped_workspace_bytes((uint64_t)n_tokens * n_experts_used, K, n_experts);
+}
+
+int32_t zc_set_workspace(zc_ctx* ctx, void* workspace, uint64_t size) {
+    ZC_ENTER(ctx);
+    if ((workspace == nullptr) != (size == 0) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "zc_set_workspace: need a 256-byte aligned pointer with its size, or NULL and 0");
+    ctx->workspace = workspace;
+    ctx->workspace_size = size;
+    return ZC_OK;
 }
 
 int32_t zc_softmax_topk(zc_ctx* ctx, const void* logits, uint64_t logits_size, const void* bias, void* out,

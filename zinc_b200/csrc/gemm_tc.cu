@@ -20,219 +20,11 @@
 //
 // Replaces the reference's mul_mm_q4k.comp / gemm_q4k.metal tile kernels
 // (src/compute/dmmv.zig:1045 recordMulMmQ4K).
-#include <cuda.h>
-#include <cuda_bf16.h>
-#include <cuda_runtime.h>
-#include <stdint.h>
-
-#include "common.cuh"
 #include "kernels.h"
-#include "stream_common.cuh"
+#include "tc_common.cuh"
 
 namespace zc {
 namespace {
-
-constexpr int kBM = 128;      // weight rows per tile (= TMEM lanes)
-constexpr int kBK = 64;       // columns per stage: 128 bytes of bf16, one swizzle row
-constexpr int kAStages = 4;   // one per 64-column group of a 256-column block
-constexpr int kCtlWarps = 3;
-constexpr int kThreads = kCtlWarps * 32 + 4 * 128;
-constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB
-
-// Raw-block staging per weight type. A box is one 256-column block of 128 rows; Q6_K blocks are 210
-// bytes and only 2-byte aligned, so their box is the 240-byte aligned superset that contains them.
-template <int TYPE>
-struct Raw;
-template <>
-struct Raw<T_Q4_K> {
-    static constexpr uint32_t kBlock = 144, kBox = 144, kSlots = 3;
-};
-template <>
-struct Raw<T_Q6_K> {
-    static constexpr uint32_t kBlock = 210, kBox = 240, kSlots = 2;
-};
-
-template <int TYPE, int BN>
-struct Tile {
-    static constexpr int kBSlots = BN == 256 ? 3 : 6;
-    static constexpr int kWSlots = Raw<TYPE>::kSlots;
-    static constexpr uint32_t kWBytes = kBM * Raw<TYPE>::kBox;
-    static constexpr uint32_t kBBytes = BN * kBK * 2;
-    static constexpr uint32_t kWOffset = kAStages * kABytes;
-    static constexpr uint32_t kBOffset = kWOffset + kWSlots * kWBytes;
-    static constexpr uint32_t kBarOffset = kBOffset + kBSlots * kBBytes;
-    static constexpr uint32_t kSmemBytes = kBarOffset + 256 + 1024;  // barriers + alignment slack
-};
-
-// Barrier block that follows the rings.
-struct Bars {
-    uint64_t full_a[kAStages];
-    uint64_t empty_a[kAStages];
-    uint64_t full_w[3];
-    uint64_t empty_w[3];
-    uint64_t full_b[6];
-    uint64_t empty_b[6];
-    uint64_t accum;
-    uint32_t tmem_base;
-    volatile uint32_t failed;
-};
-
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
-}
-
-// D[tmem] (+)= A[smem desc] * B[smem desc]^T, bf16 x bf16 -> f32, issued by one thread.
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
-    const uint32_t lo = ((saddr >> 4) & 0x3FFFu) | (1u << 16);         // start address, leading offset (unused) = 1
-    const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);         // stride offset, version 1, SWIZZLE_128B
-    return ((uint64_t)hi << 32) | lo;
-}
-
-// Instruction descriptor: f32 accumulator, bf16 A and B, both K-major, M = 128, N = BN.
-template <int BN>
-__host__ __device__ constexpr uint32_t instr_desc() {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
-}
-
-// Bounded wait. kSleep: back off between polls (every role but the tensor-core issuer has slack).
-template <bool kSleep = true>
-__device__ __forceinline__ bool wait_or_fail(uint64_t* bar, uint32_t parity, Bars* bars, uint32_t* status,
-                                             uint32_t site) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if (kSleep) __nanosleep(64);
-        if ((i & 63u) == 63u && bars->failed) return false;
-    }
-    bars->failed = 1;
-    if (status) {
-        status[0] = 1;
-        status[1] = site;
-    }
-    return false;
-}
-
-__device__ __forceinline__ uint32_t bf2_bits(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
-__device__ __forceinline__ __nv_bfloat162 bits_bf2(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
-
-// Four weights (the low nibbles of bytes 0..3 of `nib`, already masked to 0x0F0F0F0F) -> two bf16x2
-// words. (128 + q) is built by byte permutation (exact in bf16) and 136 subtracted, which leaves
-// q - 8 exactly; the weight d*sc*q - dmin*m is then formed as (q - 8) * dsc + c with
-// c = 8*d*sc - dmin*m, so that the bf16 rounding of dsc acts on a term of at most 8*dsc.
-__device__ __forceinline__ void deq4(uint32_t nib, __nv_bfloat162 dsc, __nv_bfloat162 c, uint32_t& o0,
-                                     uint32_t& o1) {
-    const __nv_bfloat162 k136 = bits_bf2(0x43084308u);
-    const uint32_t p0 = __byte_perm(nib, 0x43434343u, 0x4140);
-    const uint32_t p1 = __byte_perm(nib, 0x43434343u, 0x4342);
-    o0 = bf2_bits(__hfma2(__hsub2(bits_bf2(p0), k136), dsc, c));
-    o1 = bf2_bits(__hfma2(__hsub2(bits_bf2(p1), k136), dsc, c));
-}
-
-// One 64-column group of a Q4_K row: 32 bytes of nibbles -> 8 chunks of 8 bf16 written to the
-// swizzled row `row` of the stage at `a_stage`.
-__device__ __forceinline__ void dequant_group_q4k(const uint4& q0, const uint4& q1, float d_sc_lo, float dm_lo,
-                                                  float d_sc_hi, float dm_hi, uint8_t* a_stage, int row) {
-    const __nv_bfloat162 s_lo = __float2bfloat162_rn(d_sc_lo), m_lo = __float2bfloat162_rn(8.f * d_sc_lo - dm_lo);
-    const __nv_bfloat162 s_hi = __float2bfloat162_rn(d_sc_hi), m_hi = __float2bfloat162_rn(8.f * d_sc_hi - dm_hi);
-    const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
-    uint8_t* rowp = a_stage + row * 128;
-    const int sw = row & 7;
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {  // chunk c: bytes 8c..8c+7 -> low nibbles = columns 8c.., high = 32+8c..
-        uint4 lo, hi;
-        deq4(w[2 * c] & 0x0F0F0F0Fu, s_lo, m_lo, lo.x, lo.y);
-        deq4(w[2 * c + 1] & 0x0F0F0F0Fu, s_lo, m_lo, lo.z, lo.w);
-        deq4((w[2 * c] >> 4) & 0x0F0F0F0Fu, s_hi, m_hi, hi.x, hi.y);
-        deq4((w[2 * c + 1] >> 4) & 0x0F0F0F0Fu, s_hi, m_hi, hi.z, hi.w);
-        *reinterpret_cast<uint4*>(rowp + ((c ^ sw) << 4)) = lo;
-        *reinterpret_cast<uint4*>(rowp + (((c + 4) ^ sw) << 4)) = hi;
-    }
-}
-
-// N consecutive 32-bit words starting `sh` bits (0 or 16) into the aligned word at p.
-template <int N>
-__device__ __forceinline__ void lds_shifted(const uint32_t* p, uint32_t sh, uint32_t (&w)[N]) {
-    uint32_t prev = p[0];
-#pragma unroll
-    for (int i = 0; i < N; ++i) {
-        const uint32_t next = p[i + 1];
-        w[i] = __funnelshift_r(prev, next, sh);
-        prev = next;
-    }
-}
-
-// Four 6-bit weights (one per byte of q4, values 0..63) -> two bf16x2 words: (128 + q) - 160 = q - 32
-// exactly, times d*scale.
-__device__ __forceinline__ void deq4_q6(uint32_t q4, __nv_bfloat162 dsc, uint32_t& o0, uint32_t& o1) {
-    const __nv_bfloat162 k160 = bits_bf2(0x43204320u);
-    const uint32_t p0 = __byte_perm(q4, 0x43434343u, 0x4140);
-    const uint32_t p1 = __byte_perm(q4, 0x43434343u, 0x4342);
-    o0 = bf2_bits(__hmul2(__hsub2(bits_bf2(p0), k160), dsc));
-    o1 = bf2_bits(__hmul2(__hsub2(bits_bf2(p1), k160), dsc));
-}
-
-// One 64-column group g of a Q6_K block (layout: ql[128] qh[64] scales[16] d, src/model/gguf.zig:38-123;
-// element order as dequantRow, src/compute/forward.zig:335-383): half n = g / 2 of the block, low
-// (g even) or high (g odd) nibbles of ql[64n .. 64n+64), bit pairs 4*(g&1) and 4*(g&1)+2 of
-// qh[32n .. 32n+32), scales[8n + 4*(g&1) .. +4) each covering 16 columns. `blk` points at the aligned
-// word that contains the block's first byte, `sh` = 0 or 16.
-__device__ __forceinline__ void dequant_group_q6k(const uint32_t* blk, uint32_t sh, int g, uint8_t* a_stage,
-                                                  int row) {
-    const int n = g >> 1, hi = g & 1;
-    uint32_t ql[16], qh[8], scw[1], dw[1];
-    lds_shifted<16>(blk + 16 * n, sh, ql);
-    lds_shifted<8>(blk + 32 + 8 * n, sh, qh);
-    lds_shifted<1>(blk + 48 + 2 * n + hi, sh, scw);
-    lds_shifted<1>(blk + 52, sh, dw);
-    const float d = __half2float(__ushort_as_half((unsigned short)(dw[0] & 0xFFFFu)));
-    uint8_t* rowp = a_stage + row * 128;
-    const int sw = row & 7;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {  // chunk c = columns 8c .. 8c+7 of the group; scale index c / 2
-        const float sc = (float)(int)(int8_t)((scw[0] >> (8 * (c >> 1))) & 0xFFu);
-        const __nv_bfloat162 dsc = __float2bfloat162_rn(d * sc);
-        uint4 o;
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            // columns 8c+4e .. +3: ql byte index (c < 4 ? 0 : 32) + 8*(c&3) + 4e, qh byte index 8*(c&3) + 4e
-            const uint32_t lw = ql[(c >> 2) * 8 + (c & 3) * 2 + e];
-            const uint32_t hw = qh[(c & 3) * 2 + e];
-            const uint32_t nib = (lw >> (4 * hi)) & 0x0F0F0F0Fu;
-            const uint32_t top = ((hw >> (4 * hi + 2 * (c >> 2))) & 0x03030303u) << 4;
-            uint32_t a, b;
-            deq4_q6(nib | top, dsc, a, b);
-            if (e == 0) {
-                o.x = a;
-                o.y = b;
-            } else {
-                o.z = a;
-                o.w = b;
-            }
-        }
-        *reinterpret_cast<uint4*>(rowp + ((c ^ sw) << 4)) = o;
-    }
-}
 
 struct GemmArgs {
     const uint8_t* A;
@@ -625,22 +417,6 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)kSmRows)
                      : "memory");
     }
-}
-
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-    static EncodeFn fn = [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-            q != cudaDriverEntryPointSuccess)
-            p = nullptr;
-        return reinterpret_cast<EncodeFn>(p);
-    }();
-    return fn;
 }
 
 template <int TYPE, int BN, int NACC>

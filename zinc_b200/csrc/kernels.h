@@ -92,6 +92,17 @@ cudaError_t launch_moe_dmmv_batched(uint32_t type, const uint8_t* A, const float
                                     uint32_t n_experts_used, uint32_t n_tokens, uint32_t x_token_stride,
                                     uint32_t y_token_stride, cudaStream_t s, uint64_t* launches);
 
+// Grouped-by-expert tensor-core form of the cross-token MoE matmul (moe_gemm_tc.cu): Q4_K / Q6_K, bf16
+// operands, needs a device workspace of moe_grouped_workspace_bytes(n_tokens * n_used, K, n_experts).
+uint64_t moe_grouped_workspace_bytes(uint64_t n_pairs, uint32_t K, uint32_t n_experts);
+bool moe_grouped_eligible(uint32_t type, const uint8_t* A, uint32_t K, uint64_t expert_stride, uint32_t n_experts,
+                          uint64_t n_pairs, const float* X, uint32_t x_token_stride, uint64_t ws_size);
+cudaError_t launch_moe_grouped(uint32_t type, const uint8_t* A, uint64_t a_bytes, const float* X, float* Y,
+                               const uint32_t* routing, uint32_t M, uint32_t K, uint64_t expert_stride,
+                               uint32_t n_experts, uint32_t n_used, uint32_t n_tokens, uint32_t x_token_stride,
+                               uint32_t y_token_stride, void* ws, uint32_t* status, cudaStream_t s,
+                               uint64_t* launches);
+
 cudaError_t launch_dequant_rows(uint32_t type, const uint8_t* A, float* out, uint64_t first_row, uint32_t n_rows,
                                 uint32_t K, cudaStream_t s, uint64_t* launches);
 

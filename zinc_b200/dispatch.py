@@ -281,6 +281,21 @@ class DmmvDispatch:
                       routing.ptr, routing.size, M, K, expert_stride, n_experts, n_experts_used, n_tokens,
                       x_token_stride, y_token_stride)
 
+    # Lend the library scratch for the grouped MoE prefill path (no counterpart in the reference's
+    # DmmvDispatch; its Metal path owns route_ids / route_counts buffers). None removes it.
+    def setWorkspace(self, workspace=None):
+        if workspace is None:
+            self.ctx.call("zc_set_workspace", None, 0)
+        else:
+            w = _buf(workspace)
+            self.ctx.call("zc_set_workspace", w.ptr, w.size)
+        self._workspace = workspace  # keep the tensor alive while the library may use it
+
+    @staticmethod
+    def moeGroupedWorkspaceBytes(n_tokens, n_experts_used, K, n_experts) -> int:
+        from ._lib import lib
+        return int(lib().zc_moe_grouped_workspace_bytes(n_tokens, n_experts_used, K, n_experts))
+
     # recordCountExperts (src/compute/dmmv.zig:981-1028)
     def recordCountExperts(self, routing, counts, n_tokens, n_layers, layer, n_experts_used, n_experts,
                            d_offset_bytes=0):
