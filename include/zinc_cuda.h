@@ -266,7 +266,7 @@ int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type,
  * recordMoeBatchedDispatch (src/compute/dmmv.zig:746-792;
  * src/shaders/dmmv_q4k_moe_batched.comp:70-164). Without a workspace every (token, slot) pair is
  * computed on its own in f32, like the reference's kernel. With a workspace (zc_set_workspace) of at
- * least zc_moe_grouped_workspace_bytes(...), n_tokens >= 16, type Q4_K or Q6_K and 16-byte aligned
+ * least zc_moe_grouped_workspace_bytes(...), n_tokens >= 16, type Q4_K, Q6_K or MXFP4 (K % 64 == 0) and 16-byte aligned
  * A / expert_stride / X, the pairs are grouped by expert (as the reference's Metal path does,
  * src/shaders/metal/moe_route_pack.metal:13-36) and each expert's weights are dequantised once per
  * tile of its tokens on the tensor cores: bf16 operands, f32 accumulation (relative L2 <= 5e-3).

@@ -133,6 +133,9 @@ TOL_TC = 5e-3  # bf16 operands on the tensor cores (prefill bar)
     (zb.Q4_K, 4, 256, 1024, 2, 300, 8),   # 128-pair tiles, several tiles per expert, padded token strides
     (zb.Q6_K, 8, 200, 512, 2, 64, 0),     # 420-byte rows: only 4-byte aligned
     (zb.Q6_K, 3, 128, 768, 1, 400, 0),    # 630-byte rows: only 2-byte aligned; one slot per row (down-projection form)
+    (zb.MXFP4, 8, 160, 320, 2, 64, 0),    # 170-byte rows, K = 5 groups of 64: a short last block
+    (zb.MXFP4, 4, 256, 2880, 2, 200, 0),  # GPT-OSS row length (1530 bytes), 128-pair tiles
+    (zb.MXFP4, 16, 64, 64, 1, 40, 0),     # K = 64: one group per row, 34-byte rows
 ])
 def test_moe_dmmv_batched_grouped(gpu, oracle, t, E, M, K, k, T, pad):
     # the same entry point with a workspace: pairs grouped by expert, tensor-core tiles

@@ -10,8 +10,9 @@
 //                           activation box (BN rows from the tile's first pair) comes by TMA and may
 //                           run into the next expert's rows, whose columns are never stored
 // Raw weight blocks are fetched by the dequant warps themselves with 16-byte cp.async pieces of the
-// aligned superset of each row's block (Q6_K blocks are only 2-byte aligned, and rows of 210-byte blocks
-// have no 16-byte pitch in general, so a tensor map cannot describe them), two blocks deep.
+// aligned superset of each row's block (Q6_K blocks are only 2-byte aligned and MXFP4 blocks not aligned
+// at all, and their rows have no 16-byte pitch in general, so a tensor map cannot describe them), two
+// blocks deep. Types: Q4_K, Q6_K (K % 256 == 0) and MXFP4 (K % 64 == 0; dequantised exactly to bf16).
 // Warp roles (23 warps): 0 tensor-memory owner + MMA issuer, 1 TMA loader of the activations, 2 idle,
 // 3-18 dequant (set j = 4 warps = group j of every 256-column block = weight stage j), 19-22 epilogue.
 // Two accumulators in tensor memory let the epilogue of one item overlap the MMAs of the next.
@@ -108,10 +109,11 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
     MoeBars* bars = reinterpret_cast<MoeBars*>(smem + T::kBarOffset);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t n_items = g.header[0] * g.row_tiles;
-    const int nblk = g.K >> 8;
-    const int n_stages = nblk * 4;
+    const int n_stages = g.K >> 6;           // 64 columns each
+    const int nblk = (n_stages + 3) >> 2;    // 256-column blocks, the last one possibly short (MXFP4)
     constexpr uint32_t kBlock = Raw<TYPE>::kBlock, kBox = Raw<TYPE>::kBox;
-    const uint64_t row_bytes = (uint64_t)nblk * kBlock;
+    constexpr int kPieces = TYPE == T_MXFP4 ? 10 : (int)kBox / 16;
+    const uint64_t row_bytes = TYPE == T_MXFP4 ? (uint64_t)(g.K >> 5) * 17u : (uint64_t)nblk * kBlock;
 
     if (tid == 0) {
         for (int s = 0; s < kAStages; ++s) {
@@ -181,7 +183,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
             }
         }
     } else if (warp >= kMoeDeqWarp0 && warp < kMoeEpiWarp0) {
-        // ---- dequant producers: thread = (row, set j) ----
+        // ---- dequant producers: thread = (row, set j); set j always fills weight stage j. A block that
+        // starts at running stage gs hands its group q to set (gs + q) & 3 ----
         const int p = tid - kMoeDeqWarp0 * 32;
         const int row = p & 127, j = p >> 7;
         uint8_t* a_stage = smem + j * kABytes;
@@ -202,9 +205,9 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
             const uint8_t* src = c.expert + (o & ~(uint64_t)15);
             uint8_t* dst = smem_w + (gb & 1) * T::kRawBytes + row * kBox;
 #pragma unroll
-            for (int pc = 0; pc < (int)kBox / 16; pc += 4) {
+            for (int pc = 0; pc < kPieces; pc += 4) {
                 const int piece = pc + j;
-                if (piece < (int)kBox / 16) {
+                if (piece < kPieces) {
                     const uint8_t* s = src + piece * 16;
                     const uint32_t n = s + 16 <= g.a_end ? 16u : (s < g.a_end ? (uint32_t)(g.a_end - s) : 0u);
                     cp_async16_zfill(dst + piece * 16, n ? s : g.A, n);
@@ -214,7 +217,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
         };
         BlockCursor cur, nxt;
         locate(blockIdx.x, cur);
-        uint32_t gb = 0;
+        uint32_t gb = 0, gs = 0;
         bool dead = false;
         if (cur.w < n_items) fetch(cur, gb);
         while (cur.w < n_items) {
@@ -226,24 +229,32 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
             cp_async_wait_all();
             deq_barrier();  // block gb has landed for every row; everyone is done with block gb - 1
             if (nxt.w < n_items) fetch(nxt, gb + 1);
-            if (!dead) dead = !moe_wait(&bars->empty_a[j], (gb & 1) ^ 1, bars, g.status, 125);
-            if (!dead) {
+            const int ns = min(4, n_stages - 4 * cur.b);
+            const int q = (j - (int)gs) & 3;  // this set's group of the block, if the block has that many
+            const bool mine = q < ns;
+            if (mine && !dead)
+                dead = !moe_wait(&bars->empty_a[j], (((gs + q) >> 2) & 1) ^ 1, bars, g.status, 125);
+            if (mine && !dead) {
                 const uint8_t* slot = smem_w + (gb & 1) * T::kRawBytes + row * kBox;
                 if constexpr (TYPE == T_Q4_K) {
                     const uint4 chdr = *reinterpret_cast<const uint4*>(slot);
-                    const uint4 c0 = *reinterpret_cast<const uint4*>(slot + 16 + j * 32);
-                    const uint4 c1 = *reinterpret_cast<const uint4*>(slot + 32 + j * 32);
+                    const uint4 c0 = *reinterpret_cast<const uint4*>(slot + 16 + q * 32);
+                    const uint4 c1 = *reinterpret_cast<const uint4*>(slot + 32 + q * 32);
                     const __half2 dd = *reinterpret_cast<const __half2*>(&chdr.x);
                     const float d = __low2float(dd), dmin = __high2float(dd);
                     uint32_t s0, mn0, s1, mn1;
-                    scale_min_k4(2 * j, chdr.y, chdr.z, chdr.w, s0, mn0);
-                    scale_min_k4(2 * j + 1, chdr.y, chdr.z, chdr.w, s1, mn1);
+                    scale_min_k4(2 * q, chdr.y, chdr.z, chdr.w, s0, mn0);
+                    scale_min_k4(2 * q + 1, chdr.y, chdr.z, chdr.w, s1, mn1);
                     dequant_group_q4k(c0, c1, d * (float)s0, dmin * (float)mn0, d * (float)s1, dmin * (float)mn1,
                                       a_stage, row);
-                } else {
+                } else if constexpr (TYPE == T_Q6_K) {
                     const uint32_t off = (uint32_t)((cur.row_off + (uint64_t)cur.b * kBlock) & 15u);
-                    dequant_group_q6k(reinterpret_cast<const uint32_t*>(slot + (off & ~3u)), (off & 2u) * 8u, j,
+                    dequant_group_q6k(reinterpret_cast<const uint32_t*>(slot + (off & ~3u)), (off & 2u) * 8u, q,
                                       a_stage, row);
+                } else {
+                    const uint32_t off = (uint32_t)((cur.row_off + (uint64_t)cur.b * kBlock) & 15u) + 34u * q;
+                    dequant_group_mxfp4(reinterpret_cast<const uint32_t*>(slot + (off & ~3u)), (off & 3u) * 8u,
+                                        a_stage, row);
                 }
                 fence_proxy_async();
                 __syncwarp();
@@ -251,6 +262,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
             }
             cur = nxt;
             ++gb;
+            gs += ns;
         }
     } else if (warp >= kMoeEpiWarp0) {
         // ---- epilogue: lane = weight row, column = pair of the tile ----
@@ -431,8 +443,9 @@ uint64_t moe_grouped_workspace_bytes(uint64_t n_pairs, uint32_t K, uint32_t n_ex
 
 bool moe_grouped_eligible(uint32_t type, const uint8_t* A, uint32_t K, uint64_t expert_stride, uint32_t n_experts,
                           uint64_t n_pairs, const float* X, uint32_t x_token_stride, uint64_t ws_size) {
-    if (type != T_Q4_K && type != T_Q6_K) return false;
-    if ((K & 255u) || n_experts > kMoeMaxExperts || n_pairs > 0x7FFFFFFFull) return false;
+    if (type != T_Q4_K && type != T_Q6_K && type != T_MXFP4) return false;
+    if ((type == T_MXFP4 ? (K & 63u) : (K & 255u)) || K < 64 || n_experts > kMoeMaxExperts || n_pairs > 0x7FFFFFFFull)
+        return false;
     if ((reinterpret_cast<uintptr_t>(A) & 15u) || (expert_stride & 15u)) return false;
     if ((reinterpret_cast<uintptr_t>(X) & 15u) || (x_token_stride & 3u)) return false;
     return ws_size >= moe_grouped_workspace_bytes(n_pairs, K, n_experts);
@@ -477,6 +490,9 @@ cudaError_t launch_moe_grouped(uint32_t type, const uint8_t* A, uint64_t a_bytes
     const uint32_t max_items = max_items64 > 0xFFFFFFFFull ? 0xFFFFFFFFu : (uint32_t)max_items64;
     if (type == T_Q4_K)
         e = bn == 32 ? launch_gemm<T_Q4_K, 32>(map, g, max_items, s) : launch_gemm<T_Q4_K, 128>(map, g, max_items, s);
+    else if (type == T_MXFP4)
+        e = bn == 32 ? launch_gemm<T_MXFP4, 32>(map, g, max_items, s)
+                     : launch_gemm<T_MXFP4, 128>(map, g, max_items, s);
     else
         e = bn == 32 ? launch_gemm<T_Q6_K, 32>(map, g, max_items, s) : launch_gemm<T_Q6_K, 128>(map, g, max_items, s);
     if (e == cudaSuccess && launches) *launches += 3;

@@ -34,6 +34,13 @@ struct Raw<T_Q6_K> {
     static constexpr uint32_t kBlock = 210, kBox = 240, kSlots = 2;
 };
 
+// MXFP4: a "block" here is 8 GGUF blocks of 17 bytes (256 columns, 136 bytes, no alignment at all); the box
+// is the 16-byte aligned superset (at most 160 bytes) in a 176-byte slot row.
+template <>
+struct Raw<T_MXFP4> {
+    static constexpr uint32_t kBlock = 136, kBox = 176, kSlots = 2;
+};
+
 template <int TYPE, int BN>
 struct Tile {
     static constexpr int kBSlots = BN == 256 ? 3 : 6;
@@ -213,6 +220,59 @@ __device__ __forceinline__ void dequant_group_q6k(const uint32_t* blk, uint32_t 
             }
         }
         *reinterpret_cast<uint4*>(rowp + ((c ^ sw) << 4)) = o;
+    }
+}
+
+// Byte permute with the full selector semantics (bit 3 of a selector nibble replicates the sign bit of
+// the selected byte); the __byte_perm intrinsic masks that bit off.
+__device__ __forceinline__ uint32_t prmt_full(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+
+// Four E2M1 weights in 16 bits (two bytes of a block: nibbles lo0, hi0, lo1, hi1 = columns j, j+16, j+1,
+// j+17) -> bf16x2 words for columns (j, j+1) and (j+16, j+17), times the block scale. The magnitudes
+// {0, .5, 1, 1.5, 2, 3, 4, 6} are the bf16 patterns 0x0000 3F00 3F80 3FC0 4000 4040 4080 40C0: two byte
+// tables looked up with one permute each; the sign bits come from a sign-replicating permute. The
+// product with the power-of-two scale is exact (src/compute/forward.zig:441-459).
+__device__ __forceinline__ void deq_mx16(uint32_t x16, __nv_bfloat162 scale, uint32_t& lo_pair, uint32_t& hi_pair) {
+    const uint32_t sel = x16 & 0x7777u;
+    const uint32_t hi4 = __byte_perm(0x3F3F3F00u, 0x40404040u, sel);
+    const uint32_t lo4 = __byte_perm(0xC0800000u, 0xC0804000u, sel);
+    const uint32_t a = __byte_perm(lo4, hi4, 0x6240) | (prmt_full(x16 << 4, 0u, 0x9988u) & 0x80008000u);
+    const uint32_t b = __byte_perm(lo4, hi4, 0x7351) | (prmt_full(x16, 0u, 0x9988u) & 0x80008000u);
+    lo_pair = bf2_bits(__hmul2(bits_bf2(a), scale));
+    hi_pair = bf2_bits(__hmul2(bits_bf2(b), scale));
+}
+
+// One 64-column group (two 17-byte blocks, 34 bytes) of an MXFP4 row -> the swizzled row `row` of the
+// stage at `a_stage`. `p` points at the aligned word that holds the group's first byte, `sh` = 8 * (its
+// byte position in that word).
+__device__ __forceinline__ void dequant_group_mxfp4(const uint32_t* p, uint32_t sh, uint8_t* a_stage, int row) {
+    uint32_t w[9];
+    lds_shifted<9>(p, sh, w);  // bytes 0..35 of the group: e0, 16 nibble bytes, e1, 16 nibble bytes
+    uint8_t* rowp = a_stage + row * 128;
+    const int sw = row & 7;
+#pragma unroll
+    for (int blk = 0; blk < 2; ++blk) {
+        const uint32_t e = blk == 0 ? (w[0] & 0xFFu) : ((w[4] >> 8) & 0xFFu);
+        const uint32_t sb = e ? (e << 7) : 0x40u;  // 2^(e-127) as bf16; e = 0 -> 2^-127 as in the reference
+        const __nv_bfloat162 scale = bits_bf2(sb | (sb << 16));
+        uint32_t q[4];  // the 16 nibble bytes
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+            q[i] = blk == 0 ? __funnelshift_r(w[i], w[i + 1], 8) : __funnelshift_r(w[4 + i], w[5 + i], 16);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {  // bytes 8h .. 8h+7: low nibbles = columns 8h.., high = 16 + 8h..
+            uint4 lo, hi;
+            deq_mx16(q[2 * h] & 0xFFFFu, scale, lo.x, hi.x);
+            deq_mx16(q[2 * h] >> 16, scale, lo.y, hi.y);
+            deq_mx16(q[2 * h + 1] & 0xFFFFu, scale, lo.z, hi.z);
+            deq_mx16(q[2 * h + 1] >> 16, scale, lo.w, hi.w);
+            *reinterpret_cast<uint4*>(rowp + (((4 * blk + h) ^ sw) << 4)) = lo;
+            *reinterpret_cast<uint4*>(rowp + (((4 * blk + 2 + h) ^ sw) << 4)) = hi;
+        }
     }
 }
 
