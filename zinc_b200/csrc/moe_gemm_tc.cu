@@ -9,10 +9,10 @@
 //                           128 weight rows on the TMEM lanes and the tile's pairs on the columns; the
 //                           activation box (BN rows from the tile's first pair) comes by TMA and may
 //                           run into the next expert's rows, whose columns are never stored
-// Raw weight blocks are fetched by the dequant warps themselves with 16-byte cp.async pieces of the
+// Raw weight blocks are fetched by the dequant threads themselves with 16-byte cp.async pieces of the
 // aligned superset of each row's block (Q6_K blocks are only 2-byte aligned and MXFP4 blocks not aligned
-// at all, and their rows have no 16-byte pitch in general, so a tensor map cannot describe them), two
-// blocks deep. Types: Q4_K, Q6_K (K % 256 == 0) and MXFP4 (K % 64 == 0; dequantised exactly to bf16).
+// at all, and their rows have no 16-byte pitch in general, so a tensor map cannot describe them) into a
+// ring as deep as shared memory allows (3 to 8 blocks); each copy reports to the slot's mbarrier itself. Types: Q4_K, Q6_K (K % 256 == 0) and MXFP4 (K % 64 == 0; dequantised exactly to bf16).
 // Warp roles (23 warps): 0 tensor-memory owner + MMA issuer, 1 TMA loader of the activations, 2 idle,
 // 3-18 dequant (set j = 4 warps = group j of every 256-column block = weight stage j), 19-22 epilogue.
 // Two accumulators in tensor memory let the epilogue of one item overlap the MMAs of the next.
@@ -30,17 +30,21 @@ namespace {
 
 constexpr int kMoeDeqWarp0 = 3, kMoeEpiWarp0 = 19;
 constexpr int kMoeThreads = 23 * 32;
-constexpr int kMoeRawSlots = 2;
 constexpr int kMoeXSlots = 4;
+constexpr uint32_t kMoeSmemMax = 227u * 1024u;
 
+// The raw-block ring takes what the weight stages and activation slots leave of the 227 KB: its depth is
+// what hides the memory latency (one CTA per SM, so blocks in flight per SM = slots - 1).
 template <int TYPE, int BN>
 struct MoeTile {
     static constexpr uint32_t kRawBytes = kBM * Raw<TYPE>::kBox;
     static constexpr uint32_t kXBytes = BN * kBK * 2;
     static constexpr uint32_t kRawOffset = kAStages * kABytes;
-    static constexpr uint32_t kXOffset = (kRawOffset + kMoeRawSlots * kRawBytes + 1023u) & ~1023u;
+    static constexpr uint32_t kAvail = kMoeSmemMax - (512 + 1024) - 1024 - kRawOffset - kMoeXSlots * kXBytes;
+    static constexpr int kRawSlots = kAvail / kRawBytes > 8 ? 8 : (int)(kAvail / kRawBytes);
+    static constexpr uint32_t kXOffset = (kRawOffset + kRawSlots * kRawBytes + 1023u) & ~1023u;
     static constexpr uint32_t kBarOffset = kXOffset + kMoeXSlots * kXBytes;
-    static constexpr uint32_t kSmemBytes = kBarOffset + 256 + 1024;
+    static constexpr uint32_t kSmemBytes = kBarOffset + 512 + 1024;
 };
 
 struct MoeBars {
@@ -49,6 +53,8 @@ struct MoeBars {
     uint64_t full_x[kMoeXSlots];
     uint64_t accum_full[2];
     uint64_t accum_empty[2];
+    uint64_t full_w[8];   // raw ring: 512 copy-completion arrivals per fill
+    uint64_t empty_w[8];  // 16 warp releases per use
     uint32_t tmem_base;
     volatile uint32_t failed;
 };
@@ -86,9 +92,6 @@ __device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gme
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(n)
                  : "memory");
 }
-__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-__device__ __forceinline__ void deq_barrier() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
 // Position of the dequant warps in the flat sequence of (work item, 256-column block).
 struct BlockCursor {
@@ -120,6 +123,10 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
             mbar_init(&bars->full_a[s], 4);  // one arrival per warp of the owning set
             mbar_init(&bars->empty_a[s], 1);
             mbar_init(&bars->full_x[s], 1);
+        }
+        for (int s = 0; s < T::kRawSlots; ++s) {
+            mbar_init(&bars->full_w[s], 512);
+            mbar_init(&bars->empty_w[s], 16);
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&bars->accum_full[s], 1);
@@ -200,10 +207,10 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
             }
         };
         // this thread's pieces (j, j + 4, ...) of the aligned superset of its row's block
-        auto fetch = [&](const BlockCursor& c, uint32_t gb) {
+        auto fetch = [&](const BlockCursor& c, uint32_t slot_idx) {
             const uint64_t o = c.row_off + (uint64_t)c.b * kBlock;
             const uint8_t* src = c.expert + (o & ~(uint64_t)15);
-            uint8_t* dst = smem_w + (gb & 1) * T::kRawBytes + row * kBox;
+            uint8_t* dst = smem_w + slot_idx * T::kRawBytes + row * kBox;
 #pragma unroll
             for (int pc = 0; pc < kPieces; pc += 4) {
                 const int piece = pc + j;
@@ -213,29 +220,45 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
                     cp_async16_zfill(dst + piece * 16, n ? s : g.A, n);
                 }
             }
-            cp_async_commit_group();
         };
-        BlockCursor cur, nxt;
-        locate(blockIdx.x, cur);
-        uint32_t gb = 0, gs = 0;
-        bool dead = false;
-        if (cur.w < n_items) fetch(cur, gb);
-        while (cur.w < n_items) {
-            nxt = cur;
-            if (cur.b + 1 < nblk)
-                nxt.b = cur.b + 1;
+        auto advance = [&](BlockCursor& c) {
+            if (c.b + 1 < nblk)
+                ++c.b;
             else
-                locate(cur.w + gridDim.x, nxt);
-            cp_async_wait_all();
-            deq_barrier();  // block gb has landed for every row; everyone is done with block gb - 1
-            if (nxt.w < n_items) fetch(nxt, gb + 1);
+                locate(c.w + gridDim.x, c);
+        };
+        // The raw ring: a slot is filled by all 512 threads (each its pieces) and every copy reports to the
+        // slot's mbarrier by itself when it lands (cp.async.mbarrier.arrive.noinc), so no thread has to
+        // reach a program point for the others and the four sets drift apart as the MMA order wants.
+        // A warp releases a slot once it has read its part; the refill waits for all 16 releases.
+        constexpr int kSlots = T::kRawSlots;
+        BlockCursor cur, ahead;
+        locate(blockIdx.x, cur);
+        ahead = cur;
+        uint32_t gs = 0, slot_c = 0, use_c = 0, slot_f = 0, use_f = 0;
+        bool dead = false;
+        auto issue_fetch = [&]() {
+            if (ahead.w >= n_items) return;
+            if (!dead) dead = !moe_wait(&bars->empty_w[slot_f], (use_f & 1) ^ 1, bars, g.status, 127);
+            if (!dead) fetch(ahead, slot_f);
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bars->full_w[slot_f]))
+                         : "memory");
+            advance(ahead);
+            if (++slot_f == (uint32_t)kSlots) {
+                slot_f = 0;
+                ++use_f;
+            }
+        };
+        for (int d = 0; d < kSlots - 1; ++d) issue_fetch();
+        while (cur.w < n_items) {
             const int ns = min(4, n_stages - 4 * cur.b);
             const int q = (j - (int)gs) & 3;  // this set's group of the block, if the block has that many
             const bool mine = q < ns;
+            if (mine && !dead) dead = !moe_wait(&bars->full_w[slot_c], use_c & 1, bars, g.status, 128);
             if (mine && !dead)
                 dead = !moe_wait(&bars->empty_a[j], (((gs + q) >> 2) & 1) ^ 1, bars, g.status, 125);
             if (mine && !dead) {
-                const uint8_t* slot = smem_w + (gb & 1) * T::kRawBytes + row * kBox;
+                const uint8_t* slot = smem_w + slot_c * T::kRawBytes + row * kBox;
                 if constexpr (TYPE == T_Q4_K) {
                     const uint4 chdr = *reinterpret_cast<const uint4*>(slot);
                     const uint4 c0 = *reinterpret_cast<const uint4*>(slot + 16 + q * 32);
@@ -260,10 +283,17 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bars->full_a[j]);
             }
-            cur = nxt;
-            ++gb;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->empty_w[slot_c]);  // this warp is done with the slot
+            advance(cur);
+            if (++slot_c == (uint32_t)kSlots) {
+                slot_c = 0;
+                ++use_c;
+            }
             gs += ns;
+            issue_fetch();
         }
+        asm volatile("cp.async.wait_all;" ::: "memory");
     } else if (warp >= kMoeEpiWarp0) {
         // ---- epilogue: lane = weight row, column = pair of the tile ----
         const uint32_t q = warp & 3;
