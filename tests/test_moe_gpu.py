@@ -396,3 +396,31 @@ def test_moe_fused_down_acc_streaming_q6k(gpu, oracle, E, M, K, n_used, xs):
         want = h0 + (wts.astype(np.float64)[:, None] * per).sum(0)
         assert canary_intact(y, M)
         assert rel_l2(y[:M].cpu().numpy() - h0, want - h0) <= TOL
+
+
+@pytest.mark.parametrize("cfg", ["mxfp4", "kquant_shared"])
+def test_moe_decode_tensor_parallel_slices(gpu, cfg):
+    # the per-rank slices of a two-rank tensor-parallel MoE step, run one after the other on this GPU
+    # without the collective: the ranks' hidden vectors must add up to the single-rank result
+    torch, ctx, dd = gpu
+    from zinc_b200.moe_step import MoeDecode, MoeShape
+
+    if cfg == "mxfp4":   # 5 blocks of 32: an uneven cut (96 + 64)
+        shape = MoeShape(hidden=256, n_experts=8, top_k=2, ffn=160, t_gate_up=zb.MXFP4, t_down=zb.MXFP4,
+                         rule=zb.ROUTE_TOPK_THEN_SOFTMAX, shared=False, oai=True, n_layers=2)
+    else:
+        shape = MoeShape(hidden=512, n_experts=8, top_k=2, ffn=512, t_gate_up=zb.Q4_K, t_down=zb.Q6_K,
+                         rule=zb.ROUTE_SOFTMAX_ALL_RENORM, shared=True, oai=False, n_layers=2)
+    full = MoeDecode.build(torch, dd, shape, seed=5)
+    n_full = full.record()
+    ctx.submit_and_wait()
+    want = full.hidden.cpu().numpy().astype(np.float64)
+    total = np.zeros_like(want)
+    for rank in range(2):
+        part = MoeDecode.build(torch, dd, shape, seed=5, rank=rank, world=2, allreduce=None)
+        assert part.ffn_local in ((96, 64)[rank], 256)
+        n_part = part.record()
+        ctx.submit_and_wait()
+        total += part.hidden.cpu().numpy().astype(np.float64)
+        assert n_part == n_full + shape.n_layers   # hidden += partial (the zeroing is a memset, not a kernel)
+    assert rel_l2(total, want) <= 1e-5

@@ -58,6 +58,38 @@ def _worker(rank: int, world: int, port: int, q):
         dist.all_reduce(t)
         res["ffn_pair"] = float(np.abs(t.numpy() - y_full).max() / np.abs(y_full).max())
 
+        # MoE experts, tensor parallel: every expert's FFN dimension cut on down-projection blocks
+        # (uneven: 5 MXFP4 blocks over 2 ranks), partial hidden vectors summed by one all-reduce
+        from zinc_b200 import moe_step
+
+        E, H, F, k = 4, 256, 160, 2
+        wg_e = synth.quant_matrix(g, zb.MXFP4, E * F, H)
+        wu_e = synth.quant_matrix(g, zb.MXFP4, E * F, H)
+        wd_e = synth.quant_matrix(g, zb.MXFP4, E * H, F)
+        ids = np.array([2, 0], np.uint32)
+        wts = np.array([0.7, 0.3], np.float64)
+        sg, sdn = zb.expert_slice_bytes(zb.MXFP4, F, H), zb.expert_slice_bytes(zb.MXFP4, H, F)
+        xr = np.repeat(x[None, :H], k, axis=0)
+
+        def moe(wg_, wu_, wd_, f):
+            s_g, s_d = zb.expert_slice_bytes(zb.MXFP4, f, H), zb.expert_slice_bytes(zb.MXFP4, H, f)
+            gate = zo.moe_dmmv_f64(wg_, zb.MXFP4, f, H, s_g, ids, H, xr).astype(np.float32)
+            up = zo.moe_dmmv_f64(wu_, zb.MXFP4, f, H, s_g, ids, H, xr).astype(np.float32)
+            act = zo.swiglu(gate.reshape(-1), up.reshape(-1)).reshape(k, f)
+            return (wts[:, None] * zo.moe_dmmv_f64(wd_, zb.MXFP4, H, f, s_d, ids, f, act)).sum(0)
+
+        full = moe(wg_e, wu_e, wd_e, F)
+        cuts = moe_step.ffn_split(F, 32, world)
+        assert cuts == [(0, 96), (96, 160)]
+        lo, hi = cuts[rank]
+        tw = lambda a: torch.from_numpy(a)
+        wg_l = moe_step.shard_expert_rows(torch, tw(wg_e), E, F, sg // F, lo, hi).numpy()
+        wu_l = moe_step.shard_expert_rows(torch, tw(wu_e), E, F, sg // F, lo, hi).numpy()
+        wd_l = moe_step.shard_expert_k(torch, tw(wd_e), E, H, zb.MXFP4, F, lo, hi).numpy()
+        tm = torch.from_numpy(moe(wg_l, wu_l, wd_l, hi - lo).copy())
+        dist.all_reduce(tm)
+        res["moe_tp"] = float(np.abs(tm.numpy() - full).max() / np.abs(full).max())
+
         # refusals
         for fn, args in ((shard.row_range, (5, rank, world)), (shard.k_range, (zb.Q6_K, 768, rank, world))):
             try:
@@ -87,7 +119,20 @@ def test_two_rank_tensor_parallel_ffn():
     for r in range(2):
         assert out[r]["row_gather"] == 0.0
         assert out[r]["ffn_pair"] <= 1e-12
+        assert out[r]["moe_tp"] <= 1e-6   # f32 SwiGLU outputs feed the down projection
         assert out[r]["refusal"] is True
+
+
+def test_moe_ffn_split():
+    sys.path.insert(0, ROOT)
+    from zinc_b200.moe_step import ffn_split
+
+    assert ffn_split(2880, 32, 4) == [(0, 736), (736, 1472), (1472, 2176), (2176, 2880)]  # 23, 23, 22, 22 blocks
+    assert ffn_split(512, 256, 2) == [(0, 256), (256, 512)]
+    with pytest.raises(ValueError):
+        ffn_split(512, 256, 4)   # two Q6_K blocks cannot feed four ranks
+    with pytest.raises(ValueError):
+        ffn_split(100, 32, 2)
 
 
 def test_shards_are_byte_ranges():

@@ -11,6 +11,12 @@ matmul path and are left out).
 
 Attention, norms and the residual stream are stood in for by fixed N(0,1) vectors, as in the dense
 decode step.
+
+Tensor parallelism (world > 1): every expert's FFN dimension is cut into per-rank slices on block
+boundaries of the down projection's type (`ffn_split`): a rank holds rows [lo, hi) of every expert's
+gate and up matrices and the matching K slice of every expert's down matrix, computes a partial hidden
+vector per layer, and the ranks sum it (one all-reduce of the hidden vector per layer). The router is
+replicated.
 """
 from __future__ import annotations
 
@@ -52,6 +58,34 @@ GPT_OSS_MOE = MoeShape(hidden=2880, n_experts=32, top_k=4, ffn=2880, t_gate_up=M
                        rule=ROUTE_TOPK_THEN_SOFTMAX, shared=False, oai=True, n_layers=24)
 
 
+def ffn_split(ffn: int, block: int, world: int):
+    """Per-rank [lo, hi) element ranges of the FFN dimension: whole blocks of `block` elements, as even as
+    the block count allows (the first ranks take the remainder). Raises when a rank would get nothing."""
+    if ffn % block:
+        raise ValueError("ffn is not a multiple of the block size")
+    nb = ffn // block
+    if nb < world:
+        raise ValueError(f"{nb} blocks of {block} cannot be cut over {world} ranks")
+    base, rem = divmod(nb, world)
+    out, lo = [], 0
+    for r in range(world):
+        n = base + (1 if r < rem else 0)
+        out.append((lo * block, (lo + n) * block))
+        lo += n
+    return out
+
+
+def shard_expert_rows(torch, w, n_experts: int, rows: int, row_nbytes: int, lo: int, hi: int):
+    """Rows [lo, hi) of every expert of a stacked [n_experts][rows][row bytes] tensor, stacked again."""
+    return w.view(n_experts, rows, row_nbytes)[:, lo:hi, :].contiguous().view(-1)
+
+
+def shard_expert_k(torch, w, n_experts: int, rows: int, qtype: int, K: int, lo: int, hi: int):
+    """Columns [lo, hi) (block aligned) of every row of every expert, re-laid out as dense rows of hi - lo."""
+    bs, bpb = synth.BLOCK[qtype]
+    return w.view(n_experts * rows, K // bs, bpb)[:, lo // bs:hi // bs, :].contiguous().view(-1)
+
+
 @dataclass
 class MoeLayerWeights:
     router: object
@@ -76,12 +110,21 @@ class MoeDecode:
     yu: object = None
     act: object = None
     sact: object = None
+    ffn_local: int = 0
+    world: int = 1
+    allreduce: object = None   # callable(tensor): in-place sum over the ranks
+    partial: object = None
+    one: object = None
 
     @staticmethod
-    def build(torch, dd: DmmvDispatch, shape: MoeShape, seed: int = 3) -> "MoeDecode":
+    def build(torch, dd: DmmvDispatch, shape: MoeShape, seed: int = 3, rank: int = 0, world: int = 1,
+              allreduce=None) -> "MoeDecode":
         s = shape
         dev = f"cuda:{torch.cuda.current_device()}"
-        st = MoeDecode(shape=s, dd=dd)
+        st = MoeDecode(shape=s, dd=dd, world=world, allreduce=allreduce)
+        lo, hi = ffn_split(s.ffn, synth.BLOCK[s.t_down][0], world)[rank]
+        st.ffn_local = hi - lo
+        rb_h = row_bytes(s.t_gate_up, s.hidden)
         gen = torch.Generator(device=dev).manual_seed(seed)
         for layer in range(s.n_layers):
             sd = seed * 7919 + layer * 16
@@ -94,33 +137,60 @@ class MoeDecode:
                 w.sg = synth.torch_quant_matrix(s.t_gate_up, s.ffn, s.hidden, dev, sd + 3)
                 w.su = synth.torch_quant_matrix(s.t_gate_up, s.ffn, s.hidden, dev, sd + 4)
                 w.sd = synth.torch_quant_matrix(s.t_down, s.hidden, s.ffn, dev, sd + 5)
+            if world > 1:  # every rank generates the same full tensors and keeps its slice
+                w.wg = shard_expert_rows(torch, w.wg, s.n_experts, s.ffn, rb_h, lo, hi)
+                w.wu = shard_expert_rows(torch, w.wu, s.n_experts, s.ffn, rb_h, lo, hi)
+                w.wd = shard_expert_k(torch, w.wd, s.n_experts, s.hidden, s.t_down, s.ffn, lo, hi)
+                if s.shared:
+                    w.sg = shard_expert_rows(torch, w.sg, 1, s.ffn, rb_h, lo, hi)
+                    w.su = shard_expert_rows(torch, w.su, 1, s.ffn, rb_h, lo, hi)
+                    w.sd = shard_expert_k(torch, w.sd, 1, s.hidden, s.t_down, s.ffn, lo, hi)
+                torch.cuda.empty_cache()
             st.layers.append(w)
         f32 = dict(dtype=torch.float32, device=dev)
         st.x = torch.randn(s.hidden, device=dev, generator=gen)
         st.hidden = torch.zeros(s.hidden, **f32)
         st.logits = torch.zeros(s.n_experts, **f32)
         st.routing = torch.zeros(2 * s.top_k, dtype=torch.int32, device=dev)
-        st.yg = torch.zeros(s.top_k * s.ffn, **f32)
-        st.yu = torch.zeros(s.top_k * s.ffn, **f32)
-        st.act = torch.zeros(s.top_k * s.ffn, **f32)
-        st.sact = torch.zeros(s.ffn, **f32)
+        st.yg = torch.zeros(s.top_k * st.ffn_local, **f32)
+        st.yu = torch.zeros(s.top_k * st.ffn_local, **f32)
+        st.act = torch.zeros(s.top_k * st.ffn_local, **f32)
+        st.sact = torch.zeros(st.ffn_local, **f32)
+        if world > 1:
+            st.partial = torch.zeros(s.hidden, **f32)
+            # routing buffer {id 0, weight 1.0} for hidden += partial through moe_weighted_acc
+            st.one = torch.tensor([0, 0x3F800000], dtype=torch.int32, device=dev)
         return st
 
     def record(self) -> int:
-        """Enqueue one token's MoE layers; returns the number of kernels launched."""
+        """Enqueue one token's MoE layers; returns the number of kernels launched (collectives included
+        when they are the library's own)."""
         s, dd = self.shape, self.dd
         n0 = dd.ctx.launch_count
-        es_gu = s.ffn * row_bytes(s.t_gate_up, s.hidden)
-        es_d = s.hidden * row_bytes(s.t_down, s.ffn)
+        f = self.ffn_local
+        es_gu = f * row_bytes(s.t_gate_up, s.hidden)
+        es_d = s.hidden * row_bytes(s.t_down, f)
+        tp = self.world > 1
         for w in self.layers:
             dd.recordDispatch(F32, w.router, self.x, self.logits, s.n_experts, s.hidden)
             dd.dispatchSoftmaxTopk(self.logits, self.routing, s.n_experts, s.top_k, rule=s.rule)
-            dd.dispatchMoeFusedGateUp(s.t_gate_up, w.wg, w.wu, self.x, self.yg, self.yu, self.routing, s.ffn,
+            dd.dispatchMoeFusedGateUp(s.t_gate_up, w.wg, w.wu, self.x, self.yg, self.yu, self.routing, f,
                                       s.hidden, es_gu, s.top_k, 0)
-            dd.dispatchSwiglu(self.yg, self.yu, self.act, s.top_k * s.ffn, oai=s.oai)
-            dd.dispatchMoeFusedDownAcc(s.t_down, w.wd, self.act, self.hidden, self.routing, s.hidden, s.ffn, es_d,
-                                       s.top_k, s.ffn)
+            dd.dispatchSwiglu(self.yg, self.yu, self.act, s.top_k * f, oai=s.oai)
+            acc = self.partial if tp else self.hidden
+            if tp:
+                dd.ctx.memset(_as_buffer(self.partial), 0)
+            dd.dispatchMoeFusedDownAcc(s.t_down, w.wd, self.act, acc, self.routing, s.hidden, f, es_d, s.top_k, f)
             if s.shared:
-                dd.dispatchDmmvFusedGateUpSwiglu(s.t_gate_up, w.sg, w.su, self.x, self.sact, s.ffn, s.hidden)
-                dd.recordDispatch(s.t_down, w.sd, self.sact, self.hidden, s.hidden, s.ffn, acc_mode=1)
+                dd.dispatchDmmvFusedGateUpSwiglu(s.t_gate_up, w.sg, w.su, self.x, self.sact, f, s.hidden)
+                dd.recordDispatch(s.t_down, w.sd, self.sact, acc, s.hidden, f, acc_mode=1)
+            if tp:
+                if self.allreduce is not None:
+                    self.allreduce(self.partial)
+                dd.dispatchMoeWeightedAcc(self.hidden, self.partial, self.one, s.hidden, 1, s.hidden)
         return dd.ctx.launch_count - n0
+
+
+def _as_buffer(t):
+    from .dispatch import Buffer
+    return Buffer.from_torch(t)
