@@ -422,8 +422,8 @@ def moe_prefill_bench(torch, zb, args, local_rank):
 
 def prefill_gemm_bench(torch, zb, args, local_rank):
     """Batched-prefill dequant-GEMM D[T][M] = X[T][K] W[M][K]^T (bf16 activations, f32 out), one JSON
-    line per case: gate-shaped Q4_K 12288 x 4096 and down-shaped Q6_K 4096 x 12288 at T = 128, 512,
-    2048. Each timed launch uses the next of 8 weight copies (more than L2 in total)."""
+    line per case: gate-shaped Q4_K 12288 x 4096, down-shaped Q6_K 4096 x 12288 and a GPT-OSS gate+up-shaped
+    MXFP4 5760 x 2880 at T = 128, 512, 2048. Each timed launch uses the next of 8 weight copies (more than L2 in total)."""
     from zinc_b200 import synth
 
     peak_burst = peak_sust = None
@@ -437,7 +437,8 @@ def prefill_gemm_bench(torch, zb, args, local_rank):
     dd = zb.DmmvDispatch(ctx)
     dev = f"cuda:{local_rank}"
     copies = 8
-    for qt, name, M, K in ((zb.Q4_K, "q4_k", 12288, 4096), (zb.Q6_K, "q6_k", 4096, 12288)):
+    for qt, name, M, K in ((zb.Q4_K, "q4_k", 12288, 4096), (zb.Q6_K, "q6_k", 4096, 12288),
+                           (zb.MXFP4, "mxfp4", 5760, 2880)):
         ws = [synth.torch_quant_matrix(qt, M, K, dev, 100 + i) for i in range(copies)]
         for T in (128, 512, 2048):
             X = torch.randn(T, K, device=dev).to(torch.bfloat16)

@@ -212,10 +212,11 @@ int32_t zc_dmmv_batch(zc_ctx* ctx, uint32_t type,
  * and the Metal tiled GEMMs (src/shaders/metal/gemm_q4k.metal:54-225, gemm_q6k.metal:38-68).
  * B and D are column-major with element strides stride_b / stride_d; b_offset
  * and d_offset count ELEMENTS, a_offset BYTES (src/compute/dmmv.zig:139-145).
- * act_type selects B's element type, ZC_F32 or ZC_BF16; D is f32. bf16 activations with Q4_K or Q6_K
- * weights (16-byte aligned, N >= 16, stride_b a multiple of 8; Q6_K also K a multiple of 2048) run
- * on the tensor cores: weights dequantised to bf16 tiles, f32 accumulation in tensor memory. Every
- * other combination (f32 activations included, which keep f32 precision) runs a CUDA-core kernel.
+ * act_type selects B's element type, ZC_F32 or ZC_BF16; D is f32. bf16 activations with Q4_K, Q6_K or
+ * MXFP4 weights (A and B 16-byte aligned, N >= 16, stride_b a multiple of 8; MXFP4: K a multiple of 64)
+ * run on the tensor cores: weights dequantised to bf16 tiles (exactly, for MXFP4), f32 accumulation in
+ * tensor memory. Every other combination (f32 activations included, which keep f32 precision) runs a
+ * CUDA-core kernel.
  * K must be a multiple of 256 for K-quants (InvalidArgument otherwise, as the reference). */
 int32_t zc_mul_mm(zc_ctx* ctx, uint32_t type,
                   const void* A, uint64_t a_size, const void* B, uint64_t b_size,

@@ -73,6 +73,25 @@ def test_mul_mm(gpu, oracle, t, act, M, N, K):
         assert rel_l2(got[:, :M], oracle.gemm_f64(w, t, M, K, Bexact, round_bf16=True)) <= TOL_BF16_OPERANDS
 
 
+@pytest.mark.parametrize("M,N,K", [(64, 16, 64), (300, 77, 320), (200, 32, 2880), (256, 300, 2880)])
+def test_mul_mm_mxfp4_bf16(gpu, oracle, M, N, K):
+    # MXFP4 weights dequantise exactly to bf16, so with bf16 activations the tensor-core product differs
+    # from the exact one only by the f32 accumulation order (rows of 17-byte blocks: no alignment at all)
+    torch, ctx, dd = gpu
+    t = zb.MXFP4
+    g = synth.rng(302, M + K)
+    w = synth.quant_matrix(g, t, M, K)
+    Bm = synth.activations(g, N, K)
+    bits = synth.to_bf16_bits(Bm.reshape(-1))
+    Bexact = synth.bf16_bits_to_f32(bits).reshape(N, K)
+    D = out_with_canary(torch, N * M)
+    dd.recordMulMm(t, dev(torch, w), dev(torch, bits.view(np.int16)), D, M, N, K, K, M, 0, 0, 0, zb.BF16)
+    ctx.submit_and_wait()
+    got = D[:N * M].cpu().numpy().reshape(N, M)
+    assert canary_intact(D, N * M)
+    assert rel_l2(got, oracle.gemm_f64(w, t, M, K, Bexact)) <= 1e-5
+
+
 def test_mul_mm_errors(gpu):
     torch, ctx, dd = gpu
     w = torch.zeros(144 * 8, dtype=torch.uint8, device="cuda")

@@ -591,6 +591,11 @@ int32_t zc_mul_mm(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, co
     const void* Bp = static_cast<const uint8_t*>(B) + b_offset * esz;
     cudaError_t e = launch_mul_mm(type, u8(A, a_offset), Bp, f32m(D, d_offset * 4), M, N, K, stride_b, stride_d,
                                   act_type == ZC_BF16, ctx->status_dev, ctx->stream, &ctx->launches);
+    // layouts a tensor map cannot describe (MXFP4; Q6_K rows without a 16-byte pitch): still tensor cores
+    if (e == cudaErrorNotSupported && act_type == ZC_BF16 &&
+        mul_mm_cp_async_eligible(type, u8(A, a_offset), Bp, N, K, stride_b))
+        e = launch_mul_mm_cp_async(type, u8(A, a_offset), a_size - a_offset, Bp, f32m(D, d_offset * 4), M, N, K,
+                                   stride_b, stride_d, ctx->status_dev, ctx->stream, &ctx->launches);
     if (e == cudaErrorNotSupported)
         e = launch_mul_mm_simple(type, u8(A, a_offset), Bp, f32m(D, d_offset * 4), M, N, K, stride_b, stride_d,
                                  act_type == ZC_BF16, ctx->stream, &ctx->launches);

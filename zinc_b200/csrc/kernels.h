@@ -103,6 +103,14 @@ cudaError_t launch_moe_grouped(uint32_t type, const uint8_t* A, uint64_t a_bytes
                                uint32_t y_token_stride, void* ws, uint32_t* status, cudaStream_t s,
                                uint64_t* launches);
 
+// Prefill GEMM for the weight layouts without a 16-byte row pitch (MXFP4, Q6_K with K % 2048 != 0): bf16
+// activations, raw blocks fetched with cp.async, same tile kernel as the grouped MoE path (moe_gemm_tc.cu).
+bool mul_mm_cp_async_eligible(uint32_t type, const uint8_t* A, const void* B, uint32_t N, uint32_t K,
+                              uint32_t stride_b);
+cudaError_t launch_mul_mm_cp_async(uint32_t type, const uint8_t* A, uint64_t a_bytes, const void* B, float* D,
+                                   uint32_t M, uint32_t N, uint32_t K, uint32_t stride_b, uint32_t stride_d,
+                                   uint32_t* status, cudaStream_t s, uint64_t* launches);
+
 cudaError_t launch_dequant_rows(uint32_t type, const uint8_t* A, float* out, uint64_t first_row, uint32_t n_rows,
                                 uint32_t K, cudaStream_t s, uint64_t* launches);
 

@@ -75,7 +75,15 @@ struct MoeGemmArgs {
     const uint32_t* list;         // pair ids (token * n_used + slot) grouped by expert
     uint32_t M, K, n_used, y_token_stride, row_tiles;
     uint32_t* status;
+    uint32_t dense_n;             // > 0: plain GEMM over dense_n tokens (one "expert", identity pair list, no tables)
 };
+
+// Tile t: from the table, or (dense) tokens [t * BN, min(dense_n, (t + 1) * BN)) of the only matrix.
+template <int BN>
+__device__ __forceinline__ uint4 moe_tile(const MoeGemmArgs& g, uint32_t t) {
+    if (g.dense_n) return make_uint4(0u, t * BN, min((uint32_t)BN, g.dense_n - t * BN), 0u);
+    return __ldg(&g.tiles[t]);
+}
 
 template <bool kSleep = true>
 __device__ __forceinline__ bool moe_wait(uint64_t* bar, uint32_t parity, MoeBars* bars, uint32_t* status,
@@ -117,7 +125,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
     uint8_t* smem_x = smem + T::kXOffset;
     MoeBars* bars = reinterpret_cast<MoeBars*>(smem + T::kBarOffset);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t n_items = g.header[0] * g.row_tiles;
+    const uint32_t n_items = (g.dense_n ? (g.dense_n + BN - 1) / BN : g.header[0]) * g.row_tiles;
     const int n_stages = g.K >> 6;           // 64 columns each
     const int nblk = (n_stages + 3) >> 2;    // 256-column blocks, the last one possibly short (MXFP4)
     constexpr uint32_t kBlock = Raw<TYPE>::kBlock, kBox = Raw<TYPE>::kBox;
@@ -193,7 +201,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
             uint32_t sx = 0, px = 1;
             bool ok = true;
             for (uint32_t w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
-                const uint4 tile = __ldg(&g.tiles[w / g.row_tiles]);
+                const uint4 tile = moe_tile<BN>(g, w / g.row_tiles);
                 for (int s = 0; s < n_stages; ++s) {
                     ok = moe_wait(&bars->empty_x[sx], px, bars, g.status, 124);
                     if (!ok) break;
@@ -216,7 +224,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
             c.w = w;
             c.b = 0;
             if (w < n_items) {
-                const uint4 tile = __ldg(&g.tiles[w / g.row_tiles]);
+                const uint4 tile = moe_tile<BN>(g, w / g.row_tiles);
                 const uint32_t m0 = (w % g.row_tiles) * kBM;
                 const uint32_t grow = min(m0 + (uint32_t)row, g.M - 1);  // rows past M are computed and dropped
                 c.expert = g.A + (uint64_t)tile.x * g.expert_stride;
@@ -317,7 +325,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
         uint32_t i = 0;
         for (uint32_t w = blockIdx.x; w < n_items; w += gridDim.x, ++i) {
             const uint32_t ab = i & 1;
-            const uint4 tile = __ldg(&g.tiles[w / g.row_tiles]);
+            const uint4 tile = moe_tile<BN>(g, w / g.row_tiles);
             const uint32_t m = (w % g.row_tiles) * kBM + q * 32 + lane;
             if (!moe_wait(&bars->accum_full[ab], (i >> 1) & 1, bars, g.status, 126)) break;
             __syncwarp();
@@ -340,7 +348,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 // pair of column c*32 + lane; its output row starts at Y + token * y_token_stride + slot * M
                 const uint32_t idx = c * 32 + lane;
-                const uint32_t pair = idx < tile.z ? __ldg(&g.list[tile.y + idx]) : 0u;
+                const uint32_t pair = idx >= tile.z ? 0u : (g.dense_n ? tile.y + idx : __ldg(&g.list[tile.y + idx]));
                 const uint32_t tok = pair / g.n_used, slot = pair - tok * g.n_used;
 #pragma unroll
                 for (int jj = 0; jj < 32; ++jj) {
@@ -532,7 +540,7 @@ cudaError_t launch_moe_grouped(uint32_t type, const uint8_t* A, uint64_t a_bytes
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
     MoeGemmArgs g{A, A + a_bytes, expert_stride, Y, header, tiles, list, M, K, n_used, y_token_stride,
-                  (M + kBM - 1) / kBM, status};
+                  (M + kBM - 1) / kBM, status, 0u};
     const uint64_t max_items64 = (uint64_t)l.max_tiles * g.row_tiles;
     const uint32_t max_items = max_items64 > 0xFFFFFFFFull ? 0xFFFFFFFFu : (uint32_t)max_items64;
     if (type == T_Q4_K)
@@ -543,6 +551,45 @@ cudaError_t launch_moe_grouped(uint32_t type, const uint8_t* A, uint64_t a_bytes
     else
         e = bn == 32 ? launch_gemm<T_Q6_K, 32>(map, g, max_items, s) : launch_gemm<T_Q6_K, 128>(map, g, max_items, s);
     if (e == cudaSuccess && launches) *launches += 3;
+    return e;
+}
+
+// Plain prefill GEMM D[n][m] = sum_k W[m][k] X[n][k] through the same tile kernel (one matrix, token tiles in
+// order, no grouping tables): serves the weight layouts a tensor map cannot describe, i.e. MXFP4 (K % 64 == 0)
+// and Q6_K with a row pitch that is not a multiple of 16 bytes. X is bf16 [N][stride_b].
+bool mul_mm_cp_async_eligible(uint32_t type, const uint8_t* A, const void* B, uint32_t N, uint32_t K,
+                              uint32_t stride_b) {
+    if (type != T_MXFP4 && type != T_Q6_K && type != T_Q4_K) return false;
+    if ((type == T_MXFP4 ? (K & 63u) : (K & 255u)) || K < 64 || N < 16) return false;
+    return !(reinterpret_cast<uintptr_t>(A) & 15u) && !(reinterpret_cast<uintptr_t>(B) & 15u) && !(stride_b & 7u);
+}
+
+cudaError_t launch_mul_mm_cp_async(uint32_t type, const uint8_t* A, uint64_t a_bytes, const void* B, float* D,
+                                   uint32_t M, uint32_t N, uint32_t K, uint32_t stride_b, uint32_t stride_d,
+                                   uint32_t* status, cudaStream_t s, uint64_t* launches) {
+    EncodeFn enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    const uint32_t bn = N <= 32 ? 32u : 128u;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {K, N};
+    const cuuint64_t strides[1] = {(cuuint64_t)stride_b * 2};
+    const cuuint32_t box[2] = {kBK, bn};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(B), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    MoeGemmArgs g{A, A + a_bytes, 0, D, nullptr, nullptr, nullptr, M, K, 1u, stride_d, (M + kBM - 1) / kBM, status, N};
+    const uint64_t items64 = (uint64_t)((N + bn - 1) / bn) * g.row_tiles;
+    const uint32_t items = items64 > 0xFFFFFFFFull ? 0xFFFFFFFFu : (uint32_t)items64;
+    cudaError_t e;
+    if (type == T_Q4_K)
+        e = bn == 32 ? launch_gemm<T_Q4_K, 32>(map, g, items, s) : launch_gemm<T_Q4_K, 128>(map, g, items, s);
+    else if (type == T_MXFP4)
+        e = bn == 32 ? launch_gemm<T_MXFP4, 32>(map, g, items, s) : launch_gemm<T_MXFP4, 128>(map, g, items, s);
+    else
+        e = bn == 32 ? launch_gemm<T_Q6_K, 32>(map, g, items, s) : launch_gemm<T_Q6_K, 128>(map, g, items, s);
+    if (e == cudaSuccess && launches) ++*launches;
     return e;
 }
 
