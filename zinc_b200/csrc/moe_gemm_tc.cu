@@ -15,7 +15,7 @@
 // ring as deep as shared memory allows (3 to 8 blocks); each copy reports to the slot's mbarrier itself. Types: Q4_K, Q6_K (K % 256 == 0) and MXFP4 (K % 64 == 0; dequantised exactly to bf16).
 // Warp roles (23 warps): 0 tensor-memory owner + MMA issuer, 1 TMA loader of the activations, 2 idle,
 // 3-18 dequant (set j = 4 warps = group j of every 256-column block = weight stage j), 19-22 epilogue.
-// Rings: 4 bf16 weight stages (one per set), 16 (BN = 32) or 5 (BN = 128) activation slots, 3 to 8 raw blocks.
+// Rings: 4 bf16 weight stages (one per set) each with its activation slot, 4 to 8 raw blocks.
 // Two accumulators in tensor memory let the epilogue of one item overlap the MMAs of the next.
 // Every mbarrier wait is bounded; a wait that gives up records {1, site}, raises the CTA's flag, and
 // every role drains to the common exit where tensor memory is released.
@@ -31,10 +31,11 @@ namespace {
 
 constexpr int kMoeDeqWarp0 = 3, kMoeEpiWarp0 = 19;
 constexpr int kMoeThreads = 23 * 32;
-// Activation slots (BN x 64 bf16 each) are a ring of their own, deep enough to cover the latency of a TMA
-// load from L2 (a few thousand cycles, i.e. several 64-column stages of MMA work).
+// One activation slot (BN x 64 bf16) per weight stage: its TMA load reports to the stage's own barrier, so the
+// issuing thread waits once and commits once per stage (each wait and each commit costs it a few hundred
+// cycles in this kernel; with a separate activation ring and two waits per stage a layer took 7-20 % longer).
 template <int BN>
-constexpr int moe_x_slots() { return BN <= 32 ? 16 : 5; }
+constexpr int moe_x_slots() { return kAStages; }
 constexpr uint32_t kMoeSmemMax = 227u * 1024u;
 
 // The raw-block ring takes what the weight stages and activation slots leave of the 227 KB: its depth is
@@ -55,8 +56,6 @@ struct MoeTile {
 struct MoeBars {
     uint64_t full_a[kAStages];
     uint64_t empty_a[kAStages];
-    uint64_t full_x[16];
-    uint64_t empty_x[16];
     uint64_t accum_full[2];
     uint64_t accum_empty[2];
     uint64_t full_w[8];   // raw ring: 512 copy-completion arrivals per fill
@@ -134,12 +133,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
 
     if (tid == 0) {
         for (int s = 0; s < kAStages; ++s) {
-            mbar_init(&bars->full_a[s], 4);  // one arrival per warp of the owning set
+            mbar_init(&bars->full_a[s], 5);  // one arrival per warp of the owning set + the activation box
             mbar_init(&bars->empty_a[s], 1);
-        }
-        for (int s = 0; s < T::kXSlots; ++s) {
-            mbar_init(&bars->full_x[s], 1);
-            mbar_init(&bars->empty_x[s], 1);
         }
         for (int s = 0; s < T::kRawSlots; ++s) {
             mbar_init(&bars->full_w[s], 512);
@@ -167,7 +162,7 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
     if (warp == 0) {
         if (lane == 0) {  // ---- MMA issuer ----
             constexpr uint32_t idesc = instr_desc<BN>();
-            uint32_t gs = 0, i = 0, sx = 0, px = 0;
+            uint32_t gs = 0, i = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; w < n_items && ok; w += gridDim.x, ++i) {
                 const uint32_t ab = i & 1;
@@ -177,40 +172,31 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
                 for (int s = 0; s < n_stages; ++s, ++gs) {
                     const int st = gs & 3;
                     const uint32_t ph = (gs >> 2) & 1;
-                    ok = moe_wait<false>(&bars->full_a[st], ph, bars, g.status, 122) &&
-                         moe_wait<false>(&bars->full_x[sx], px, bars, g.status, 123);
+                    ok = moe_wait<false>(&bars->full_a[st], ph, bars, g.status, 122);
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t da = smem_desc(smem_u32(smem + st * kABytes));
-                    const uint64_t dx = smem_desc(smem_u32(smem_x + sx * T::kXBytes));
+                    const uint64_t dx = smem_desc(smem_u32(smem_x + st * T::kXBytes));
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k)
                         umma_bf16(tmem + ab * BN, da + 2 * k, dx + 2 * k, idesc, (s | k) ? 1u : 0u);
-                    umma_commit(&bars->empty_x[sx]);
                     umma_commit(&bars->empty_a[st]);
-                    if (++sx == (uint32_t)T::kXSlots) {
-                        sx = 0;
-                        px ^= 1;
-                    }
                 }
                 if (ok) umma_commit(&bars->accum_full[ab]);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {  // ---- TMA loader of the packed activations ----
-            uint32_t sx = 0, px = 1;
+            uint32_t gs = 0;
             bool ok = true;
             for (uint32_t w = blockIdx.x; w < n_items && ok; w += gridDim.x) {
                 const uint4 tile = moe_tile<BN>(g, w / g.row_tiles);
-                for (int s = 0; s < n_stages; ++s) {
-                    ok = moe_wait(&bars->empty_x[sx], px, bars, g.status, 124);
+                for (int s = 0; s < n_stages; ++s, ++gs) {
+                    const int st = gs & 3;
+                    ok = moe_wait(&bars->empty_a[st], ((gs >> 2) & 1) ^ 1, bars, g.status, 124);
                     if (!ok) break;
-                    mbar_expect_tx(&bars->full_x[sx], T::kXBytes);
-                    tma_load_2d(smem_x + sx * T::kXBytes, &tmap_x, s * kBK, (int)tile.y, &bars->full_x[sx]);
-                    if (++sx == (uint32_t)T::kXSlots) {
-                        sx = 0;
-                        px ^= 1;
-                    }
+                    mbar_expect_tx(&bars->full_a[st], T::kXBytes);
+                    tma_load_2d(smem_x + st * T::kXBytes, &tmap_x, s * kBK, (int)tile.y, &bars->full_a[st]);
                 }
             }
         }
