@@ -269,9 +269,8 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
 
     if (tid == 0) {
         for (int s = 0; s < kAStages; ++s) {
-            mbar_init(&bars->full_a[s], 8);   // weight stage: one arrival per warp of the owning half
+            mbar_init(&bars->full_a[s], 9);   // one arrival per warp of the owning half + the activation box (TMA)
             mbar_init(&bars->empty_a[s], 1);
-            mbar_init(&bars->full_b[s], 1);   // activation slot
         }
         mbar_init(&bars->accum, 1);
         bars->failed = 0;
@@ -296,8 +295,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
             for (int it = 0; it < n_it && ok; ++it) {
                 const int st = it & 3;
                 const uint32_t ph = (it >> 2) & 1;
-                ok = wait_or_fail<false>(&bars->full_a[st], ph, bars, g.status, 111) &&
-                     wait_or_fail<false>(&bars->full_b[st], ph, bars, g.status, 112);
+                ok = wait_or_fail<false>(&bars->full_a[st], ph, bars, g.status, 111);  // weights and activations
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t dx = smem_desc(smem_u32(smem_x + st * kSmXBytes));
@@ -313,8 +311,8 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
             for (int it = 0; it < n_it; ++it) {
                 const int st = it & 3;
                 if (!wait_or_fail(&bars->empty_a[st], ((it >> 2) & 1) ^ 1, bars, g.status, 113)) break;
-                mbar_expect_tx(&bars->full_b[st], kSmXBytes);
-                tma_load_2d(smem_x + st * kSmXBytes, &tmap_x, (b_begin * 4 + it) * kBK, (int)n0, &bars->full_b[st]);
+                mbar_expect_tx(&bars->full_a[st], kSmXBytes);
+                tma_load_2d(smem_x + st * kSmXBytes, &tmap_x, (b_begin * 4 + it) * kBK, (int)n0, &bars->full_a[st]);
             }
         }
     } else {
