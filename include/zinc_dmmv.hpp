@@ -116,6 +116,16 @@ public:
                                                       n_tokens, x_token_stride, y_token_stride));
     }
 
+    // Lend the library scratch for the grouped-by-expert prefill form of recordMoeBatchedDispatch (no
+    // counterpart in the reference's DmmvDispatch; its Metal path owns route_ids / route_counts buffers).
+    // An empty Buffer removes it.
+    Error setWorkspace(Buffer workspace) {
+        return static_cast<Error>(zc_set_workspace(ctx_, workspace.ptr, workspace.size));
+    }
+    static uint64_t moeGroupedWorkspaceBytes(uint32_t n_tokens, uint32_t n_experts_used, uint32_t K, uint32_t n_experts) {
+        return zc_moe_grouped_workspace_bytes(n_tokens, n_experts_used, K, n_experts);
+    }
+
     // recordCountExperts (src/compute/dmmv.zig:981-1028)
     Error recordCountExperts(Buffer routing_buf, Buffer counts_buf, uint32_t n_tokens, uint32_t n_layers, uint32_t layer,
                              uint32_t n_experts_used, uint32_t n_experts, uint64_t d_offset_bytes) {

@@ -26,6 +26,8 @@ int main() {
     EXPECT(zc_expert_slice_bytes(ZC_MXFP4, 2880, 2880) == 4406400ull);
     EXPECT(DmmvDispatch::pipelineForType(GGMLType::q5_k));
     EXPECT(!DmmvDispatch::pipelineForType(GGMLType::bf16));
+    // workspace of the grouped MoE prefill path: tile table + pair list + packed bf16 activations
+    EXPECT(DmmvDispatch::moeGroupedWorkspaceBytes(512, 8, 2048, 256) >= 4096ull * 2048ull * 2ull);
 
     DmmvDispatch dd;
     const Error e = DmmvDispatch::init(0, dd);
@@ -43,6 +45,8 @@ int main() {
     EXPECT(zc_memset(dd.context(), A.ptr, 0, 0, A.size) == ZC_OK);
     EXPECT(zc_memset(dd.context(), x.ptr, 0, 0, x.size) == ZC_OK);
     EXPECT(zc_memset(dd.context(), y.ptr, 0, 0xFF, y.size) == ZC_OK);
+    EXPECT(dd.setWorkspace(Buffer{A.ptr, 0}) == Error::InvalidArgument);  // pointer without a size
+    EXPECT(dd.setWorkspace(Buffer{}) == Error::None);
     EXPECT(dd.recordDispatch(GGMLType::bf16, A, x, y, M, K, 0, 0, 0) == Error::UnsupportedQuantType);
     EXPECT(dd.recordDispatch(GGMLType::q4_k, A, x, y, M, 300, 0, 0, 0) == Error::InvalidArgument);
     EXPECT(dd.recordDispatch(GGMLType::q4_k, A, x, y, M, K, 16, 0, 0) == Error::InvalidArgument);  // runs past A

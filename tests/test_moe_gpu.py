@@ -398,6 +398,48 @@ def test_moe_fused_down_acc_streaming_q6k(gpu, oracle, E, M, K, n_used, xs):
         assert rel_l2(y[:M].cpu().numpy() - h0, want - h0) <= TOL
 
 
+def test_moe_dmmv_batched_grouped_edges(gpu, oracle):
+    # with a workspace: fewer than 16 tokens keep the f32 per-pair kernel; expert ids past n_experts are
+    # skipped by the grouped path (their output rows stay untouched)
+    torch, ctx, dd = gpu
+    t, E, M, K, k = zb.Q4_K, 4, 128, 256, 2
+    g = synth.rng(208, 0)
+    w, stride = stacked(g, t, E, M, K)
+    ws = torch.empty(dd.moeGroupedWorkspaceBytes(64, k, K, E), dtype=torch.uint8, device="cuda")
+    dd.setWorkspace(ws)
+    try:
+        T = 9
+        ids = g.integers(0, E, size=(T, k)).astype(np.uint32)
+        X = synth.activations(g, T, K)
+        Y = out_with_canary(torch, T * k * M)
+        dd.recordMoeBatchedDispatch(t, dev(torch, w), dev(torch, X), Y, dev(torch, ids), M, K, stride, E, k, T, K, k * M)
+        ctx.submit_and_wait()
+        got = Y[:T * k * M].cpu().numpy().reshape(T, k, M)
+        want = np.stack([oracle.moe_dmmv_f64(w, t, M, K, stride, ids[i], K, np.repeat(X[i:i + 1], k, axis=0))
+                         for i in range(T)])
+        assert rel_l2(got, want) <= TOL   # f32 precision: the per-pair kernel ran
+
+        T = 32
+        ids = g.integers(0, E, size=(T, k)).astype(np.uint32)
+        ids[3, 1] = E + 5      # not an expert
+        ids[17, 0] = 0xFFFFFFFF
+        X = synth.activations(g, T, K)
+        Y = out_with_canary(torch, T * k * M, init=-7.0)
+        dd.recordMoeBatchedDispatch(t, dev(torch, w), dev(torch, X), Y, dev(torch, ids), M, K, stride, E, k, T, K, k * M)
+        ctx.submit_and_wait()
+        got = Y[:T * k * M].cpu().numpy().reshape(T, k, M)
+        assert np.all(got[3, 1] == -7.0) and np.all(got[17, 0] == -7.0)
+        ok = np.ones((T, k), bool)
+        ok[3, 1] = ok[17, 0] = False
+        safe = np.where(ok, ids, 0)
+        want = np.stack([oracle.moe_dmmv_f64(w, t, M, K, stride, safe[i], K, np.repeat(X[i:i + 1], k, axis=0))
+                         for i in range(T)])
+        assert rel_l2(got[ok], want[ok]) <= TOL_TC
+        assert canary_intact(Y, T * k * M)
+    finally:
+        dd.setWorkspace(None)
+
+
 @pytest.mark.parametrize("cfg", ["mxfp4", "kquant_shared"])
 def test_moe_decode_tensor_parallel_slices(gpu, cfg):
     # the per-rank slices of a two-rank tensor-parallel MoE step, run one after the other on this GPU
