@@ -250,6 +250,19 @@ int32_t zc_moe_fused_gate_up(zc_ctx* ctx, uint32_t type,
                              uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride,
                              uint64_t x_offset, uint64_t y_offset);
 
+/* The same with the activation applied in the kernel's epilogue: y[s][r] = silu(Wg[e].x) * (Wu[e].x)
+ * (oai = 0, src/shaders/swiglu.comp:25-33) or the GPT-OSS form (oai = 1, src/shaders/swiglu_oai.comp:24-34).
+ * One launch instead of the reference's fused gate+up dispatch followed by its activation dispatch
+ * (src/compute/forward.zig:6206-6240); results are those of zc_moe_fused_gate_up + zc_swiglu(_oai).
+ * Measured on B200 the single launch is not faster than the two (the decode benchmark keeps the two). */
+int32_t zc_moe_fused_gate_up_act(zc_ctx* ctx, uint32_t type,
+                                 const void* Wg, uint64_t wg_size, const void* Wu, uint64_t wu_size,
+                                 const void* x, uint64_t x_size, void* y, uint64_t y_size,
+                                 const void* routing, uint64_t routing_size,
+                                 uint32_t M, uint32_t K,
+                                 uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride,
+                                 uint64_t x_offset, uint64_t y_offset, uint32_t oai);
+
 /* hidden[r] += sum_{s<n_used} w_s * (W[id_s][r] . X[s*x_expert_stride ..]);
  * routing = [n_used ids u32][n_used weights f32 bits]. Replaces the fused
  * down + weighted-accumulate dispatch (src/compute/dmmv.zig:68-76;

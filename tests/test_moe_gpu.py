@@ -345,6 +345,33 @@ def test_moe_fused_gate_up_streaming_mxfp4(gpu, oracle, E, M, K, n_used):
         assert rel_l2(yu[:n_used * M].cpu().numpy(), oracle.moe_dmmv_f64(wu, zb.MXFP4, M, K, stride, ids, K, xs)) <= TOL
 
 
+@pytest.mark.parametrize("t,E,M,K,n_used,oai", [
+    (zb.Q4_K, 12, 512, 2048, 8, False),   # streaming kernel
+    (zb.Q4_K, 4, 33, 512, 2, False),      # one warp per row pair
+    (zb.MXFP4, 6, 300, 2880, 4, True),    # streaming MXFP4, GPT-OSS activation
+    (zb.MXFP4, 3, 32, 512, 2, True),
+    (zb.Q6_K, 4, 40, 512, 2, False),
+])
+def test_moe_fused_gate_up_act(gpu, oracle, t, E, M, K, n_used, oai):
+    # gate + up + activation in one launch = zc_moe_fused_gate_up followed by zc_swiglu / zc_swiglu_oai
+    torch, ctx, dd = gpu
+    g = synth.rng(209, t * 100 + M)
+    wg, stride = stacked(g, t, E, M, K)
+    wu, _ = stacked(g, t, E, M, K)
+    x = synth.activations(g, 1, K)
+    ids = np.array([(3 * i + E - 1) % E for i in range(n_used)], np.uint32)
+    y = out_with_canary(torch, n_used * M)
+    dd.dispatchMoeFusedGateUpAct(t, dev(torch, wg), dev(torch, wu), dev(torch, x), y, dev(torch, routing_buf(ids)),
+                                 M, K, stride, n_used, 0, oai=oai)
+    ctx.submit_and_wait()
+    xs = np.repeat(x, n_used, axis=0)
+    gate = oracle.moe_dmmv_f64(wg, t, M, K, stride, ids, K, xs).astype(np.float32).reshape(-1)
+    up = oracle.moe_dmmv_f64(wu, t, M, K, stride, ids, K, xs).astype(np.float32).reshape(-1)
+    want = oracle.swiglu(gate, up, oai=oai)
+    assert canary_intact(y, n_used * M)
+    assert rel_l2(y[:n_used * M].cpu().numpy(), want) <= TOL
+
+
 @pytest.mark.parametrize("E,M,K,n_used,xs", [(6, 300, 2880, 4, 2880), (4, 64, 512, 3, 520), (3, 2880, 2880, 4, 2880)])
 def test_moe_fused_down_acc_streaming_mxfp4(gpu, oracle, E, M, K, n_used, xs):
     """y += sum_s w_s W[id_s] x_s through the streaming MXFP4 kernel (slots side by side along K), with a

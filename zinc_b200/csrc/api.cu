@@ -643,24 +643,24 @@ int32_t zc_moe_dmmv(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, 
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 
-int32_t zc_moe_fused_gate_up(zc_ctx* ctx, uint32_t type, const void* Wg, uint64_t wg_size, const void* Wu,
-                             uint64_t wu_size, const void* x, uint64_t x_size, void* y_gate, uint64_t yg_size,
-                             void* y_up, uint64_t yu_size, const void* routing, uint64_t routing_size, uint32_t M,
-                             uint32_t K, uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride,
-                             uint64_t x_offset, uint64_t y_offset) {
-    ZC_ENTER(ctx);
-    const char* fn = "zc_moe_fused_gate_up";
+static int32_t moe_gate_up_common(zc_ctx* ctx, const char* fn, uint32_t type, const void* Wg, uint64_t wg_size,
+                                  const void* Wu, uint64_t wu_size, const void* x, uint64_t x_size, void* y_gate,
+                                  uint64_t yg_size, void* y_up, uint64_t yu_size, const void* routing,
+                                  uint64_t routing_size, uint32_t M, uint32_t K, uint64_t expert_stride,
+                                  uint32_t n_used, uint32_t x_expert_stride, uint64_t x_offset, uint64_t y_offset,
+                                  uint32_t act) {
     ZC_TRY(check_moe(ctx, fn, type, Wg, wg_size, x, x_size, routing, routing_size, M, K, expert_stride, n_used,
                      x_expert_stride, x_offset, n_used));
     ZC_TRY(check_mat(ctx, fn, type, Wu, wu_size, 0, (uint64_t)M * row_bytes_of(type, K), M, K));
-    ZC_TRY(check_vec(ctx, fn, "y_gate", y_gate, yg_size, y_offset, (uint64_t)n_used * M * 4, 4));
-    ZC_TRY(check_vec(ctx, fn, "y_up", y_up, yu_size, y_offset, (uint64_t)n_used * M * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, act ? "y" : "y_gate", y_gate, yg_size, y_offset, (uint64_t)n_used * M * 4, 4));
+    if (!act) ZC_TRY(check_vec(ctx, fn, "y_up", y_up, yu_size, y_offset, (uint64_t)n_used * M * 4, 4));
     DmmvArgs a;
     a.A = u8(Wg, 0);
     a.A2 = u8(Wu, 0);
     a.x = f32p(x, x_offset);
     a.y = f32m(y_gate, y_offset);
-    a.y2 = f32m(y_up, y_offset);
+    a.y2 = act ? nullptr : f32m(y_up, y_offset);
+    a.act = act;
     a.routing = static_cast<const uint32_t*>(routing);
     a.M = M;
     a.K = K;
@@ -678,6 +678,29 @@ int32_t zc_moe_fused_gate_up(zc_ctx* ctx, uint32_t type, const void* Wg, uint64_
     else
         e = launch_dmmv(type, MODE_MOE_GATE_UP, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_moe_fused_gate_up(zc_ctx* ctx, uint32_t type, const void* Wg, uint64_t wg_size, const void* Wu,
+                             uint64_t wu_size, const void* x, uint64_t x_size, void* y_gate, uint64_t yg_size,
+                             void* y_up, uint64_t yu_size, const void* routing, uint64_t routing_size, uint32_t M,
+                             uint32_t K, uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride,
+                             uint64_t x_offset, uint64_t y_offset) {
+    ZC_ENTER(ctx);
+    return moe_gate_up_common(ctx, "zc_moe_fused_gate_up", type, Wg, wg_size, Wu, wu_size, x, x_size, y_gate, yg_size,
+                              y_up, yu_size, routing, routing_size, M, K, expert_stride, n_used, x_expert_stride,
+                              x_offset, y_offset, 0);
+}
+
+int32_t zc_moe_fused_gate_up_act(zc_ctx* ctx, uint32_t type, const void* Wg, uint64_t wg_size, const void* Wu,
+                                 uint64_t wu_size, const void* x, uint64_t x_size, void* y, uint64_t y_size,
+                                 const void* routing, uint64_t routing_size, uint32_t M, uint32_t K,
+                                 uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride, uint64_t x_offset,
+                                 uint64_t y_offset, uint32_t oai) {
+    ZC_ENTER(ctx);
+    if (oai > 1) return fail(ctx, ZC_ERR_INVALID_ARG, "zc_moe_fused_gate_up_act: oai must be 0 or 1");
+    return moe_gate_up_common(ctx, "zc_moe_fused_gate_up_act", type, Wg, wg_size, Wu, wu_size, x, x_size, y, y_size,
+                              nullptr, 0, routing, routing_size, M, K, expert_stride, n_used, x_expert_stride,
+                              x_offset, y_offset, 1 + oai);
 }
 
 int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* x,

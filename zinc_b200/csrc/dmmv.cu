@@ -16,6 +16,16 @@ namespace {
 
 constexpr int kWarps = 8;
 
+// src/shaders/swiglu.comp:25-33 (act = 1), src/shaders/swiglu_oai.comp:24-34 (act = 2)
+__device__ __forceinline__ float gate_up_act_v1(uint32_t act, float gate, float up) {
+    if (act == 2) {
+        const float g = fminf(gate, 7.0f);
+        const float u = fmaxf(-7.0f, fminf(up, 7.0f));
+        return (g / (1.0f + expf(1.702f * (-g)))) * (u + 1.0f);
+    }
+    return (gate / (1.0f + expf(-gate))) * up;
+}
+
 template <uint32_t TYPE, int MODE, int NR, bool ALIGNED>
 __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
     const int lane = threadIdx.x & 31;
@@ -98,8 +108,12 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
 #pragma unroll
             for (int r = 0; r < NR; ++r)
                 if (row0 + r < a.M) {
-                    a.y[(size_t)slot * a.M + row0 + r] = acc[2 * r];
-                    a.y2[(size_t)slot * a.M + row0 + r] = acc[2 * r + 1];
+                    if (a.act) {
+                        a.y[(size_t)slot * a.M + row0 + r] = gate_up_act_v1(a.act, acc[2 * r], acc[2 * r + 1]);
+                    } else {
+                        a.y[(size_t)slot * a.M + row0 + r] = acc[2 * r];
+                        a.y2[(size_t)slot * a.M + row0 + r] = acc[2 * r + 1];
+                    }
                 }
         }
     } else if constexpr (MODE == MODE_BATCH) {

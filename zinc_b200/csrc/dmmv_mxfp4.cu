@@ -466,6 +466,7 @@ static void fill_common(WarpArgs& wa, const DmmvArgs& a) {
     wa.x = a.x;
     wa.y = a.y;
     wa.y2 = a.y2;
+    wa.act = a.act;
     wa.gate = nullptr;
     wa.M = a.M;
     wa.K = a.K;

@@ -512,6 +512,7 @@ cudaError_t launch_warp_moe_gate_up(const DmmvArgs& a, cudaStream_t st, uint64_t
     wa.x = a.x;
     wa.y = a.y;
     wa.y2 = a.y2;
+    wa.act = a.act;
     wa.gate = nullptr;
     wa.M = a.M;
     wa.K = a.K;

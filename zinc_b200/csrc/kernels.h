@@ -30,6 +30,7 @@ struct DmmvArgs {
     uint32_t M = 0, K = 0;
     uint32_t acc_mode = 0;
     uint32_t n_used = 1;
+    uint32_t act = 0;             // MoE gate/up: 0 write both, 1 y = silu(gate) * up, 2 the GPT-OSS (swiglu_oai) form
     uint32_t x_expert_stride = 0;
     uint64_t expert_stride = 0;
     uint32_t n_tokens = 1;        // MODE_MOE_BATCHED

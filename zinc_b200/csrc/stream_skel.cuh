@@ -40,7 +40,18 @@ struct WarpArgs {
     uint32_t tiles_per_expert;
     float* y2;
     uint32_t x_slot_stride;  // MoE down projection: elements between the slots' activation vectors
+    uint32_t act = 0;        // EPI_PAIR only: 0 write both streams, 1 y = silu(gate) * up, 2 the GPT-OSS form
 };
+
+// The activation a fused gate + up launch applies (src/shaders/swiglu.comp:25-33, swiglu_oai.comp:24-34).
+__device__ __forceinline__ float gate_up_act(uint32_t act, float gate, float up) {
+    if (act == 2) {
+        const float g = fminf(gate, 7.0f);
+        const float u = fmaxf(-7.0f, fminf(up, 7.0f));
+        return (g / (1.0f + expf(1.702f * (-g)))) * (u + 1.0f);
+    }
+    return (gate / (1.0f + expf(-gate))) * up;
+}
 
 
 __device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
@@ -100,9 +111,13 @@ __device__ __forceinline__ void write_row(const WarpArgs& a, uint32_t row, const
         a.y[row] = (v[0] / (1.0f + expf(-v[0]))) * v[1];
     } else if constexpr (EPI == EPI_ACC) {  // y += result, whatever acc_mode says
         a.y[row] += v[0];
-    } else if constexpr (EPI == EPI_PAIR) {  // two streams, two outputs (MoE gate and up rows)
-        a.y[row] = v[0];
-        a.y2[row] = v[NS - 1];
+    } else if constexpr (EPI == EPI_PAIR) {  // two streams (MoE gate and up rows): both outputs, or their activation
+        if (a.act) {
+            a.y[row] = gate_up_act(a.act, v[0], v[NS - 1]);
+        } else {
+            a.y[row] = v[0];
+            a.y2[row] = v[NS - 1];
+        }
     } else if constexpr (EPI == EPI_SIGMOID_ACC) {
         a.y[row] += (1.0f / (1.0f + expf(-__ldg(a.gate)))) * v[0];
     } else {

@@ -336,6 +336,15 @@ class DmmvDispatch:
                       y_gate.ptr, y_gate.size, y_up.ptr, y_up.size, routing.ptr, routing.size, M, K,
                       expert_stride, n_used, x_expert_stride, x_offset, y_offset)
 
+    # the same with SwiGLU (or the GPT-OSS form) applied in the epilogue: one launch for the reference's
+    # fused gate+up dispatch and its activation dispatch (forward.zig:6206-6240)
+    def dispatchMoeFusedGateUpAct(self, quant_type, Wg, Wu, x, y, routing, M, K, expert_stride, n_used,
+                                  x_expert_stride, oai=False, x_offset=0, y_offset=0):
+        Wg, Wu, x, y, routing = map(_buf, (Wg, Wu, x, y, routing))
+        self.ctx.call("zc_moe_fused_gate_up_act", quant_type, Wg.ptr, Wg.size, Wu.ptr, Wu.size, x.ptr, x.size,
+                      y.ptr, y.size, routing.ptr, routing.size, M, K, expert_stride, n_used, x_expert_stride,
+                      x_offset, y_offset, 1 if oai else 0)
+
     # fused down + weighted accumulate (forward.zig:6362-6389)
     def dispatchMoeFusedDownAcc(self, quant_type, A, x, y, routing, M, K, expert_stride, n_used, x_expert_stride,
                                 x_offset=0, y_offset=0):
