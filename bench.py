@@ -386,8 +386,7 @@ def moe_prefill_bench(torch, zb, args, local_rank):
             flops = 2.0 * T * k * 3 * F * H
 
             def layer():
-                dd.recordMoeBatchedDispatch(S.t_gate_up, Wg, X, gate, ids, F, H, sg, E, k, T, H, k * F)
-                dd.recordMoeBatchedDispatch(S.t_gate_up, Wu, X, up, ids, F, H, sg, E, k, T, H, k * F)
+                dd.recordMoeBatchedDispatchPair(S.t_gate_up, Wg, Wu, X, gate, up, ids, F, H, sg, E, k, T, H, k * F)
                 dd.dispatchSwiglu(gate, up, act, T * k * F, oai=S.oai)
                 dd.recordMoeBatchedDispatch(S.t_down, Wd, act, down, ids, H, F, sd, E, 1, T * k, F, H)
                 dd.dispatchMoeRouteScatter(routing, down, hidden, T, H, k, 2 * k)

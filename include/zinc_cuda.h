@@ -292,6 +292,18 @@ int32_t zc_moe_dmmv_batched(zc_ctx* ctx, uint32_t type,
                             uint32_t n_experts, uint32_t n_experts_used, uint32_t n_tokens,
                             uint32_t x_token_stride, uint32_t y_token_stride);
 
+/* Gate and up of a prefill batch in one call: Yg = Wg[...] X, Yu = Wu[...] X with the arguments of
+ * zc_moe_dmmv_batched. On the grouped path the pairs are grouped and the activations packed once for both
+ * matrices; otherwise it is the two single calls. The prefill counterpart of zc_moe_fused_gate_up
+ * (src/compute/forward.zig:6206-6222). */
+int32_t zc_moe_dmmv_batched_pair(zc_ctx* ctx, uint32_t type,
+                                 const void* Wg, uint64_t wg_size, const void* Wu, uint64_t wu_size,
+                                 const void* X, uint64_t x_size, void* Yg, uint64_t yg_size, void* Yu, uint64_t yu_size,
+                                 const void* routing, uint64_t routing_size,
+                                 uint32_t M, uint32_t K, uint64_t expert_stride,
+                                 uint32_t n_experts, uint32_t n_experts_used, uint32_t n_tokens,
+                                 uint32_t x_token_stride, uint32_t y_token_stride);
+
 /* Caller-owned device scratch for the grouped MoE prefill path; NULL / 0 removes it. The library never
  * allocates on the hot path, so the engine lends the bytes (its prefill scratch arena). 256-byte aligned.
  * The contents are only meaningful during one zc_moe_dmmv_batched call (in stream order). No counterpart

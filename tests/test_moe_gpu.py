@@ -425,6 +425,34 @@ def test_moe_fused_down_acc_streaming_q6k(gpu, oracle, E, M, K, n_used, xs):
         assert rel_l2(y[:M].cpu().numpy() - h0, want - h0) <= TOL
 
 
+@pytest.mark.parametrize("use_ws", [True, False], ids=["grouped", "per_pair"])
+def test_moe_dmmv_batched_pair(gpu, oracle, use_ws):
+    # gate and up in one call: equal to the two single calls on either path
+    torch, ctx, dd = gpu
+    t, E, M, K, k, T = zb.Q4_K, 6, 128, 512, 2, 40
+    g = synth.rng(210, int(use_ws))
+    wg, stride = stacked(g, t, E, M, K)
+    wu, _ = stacked(g, t, E, M, K)
+    ids = g.integers(0, E, size=(T, k)).astype(np.uint32)
+    X = synth.activations(g, T, K)
+    Yg, Yu = out_with_canary(torch, T * k * M), out_with_canary(torch, T * k * M)
+    if use_ws:
+        dd.setWorkspace(torch.empty(dd.moeGroupedWorkspaceBytes(T, k, K, E), dtype=torch.uint8, device="cuda"))
+    try:
+        n0 = ctx.launch_count
+        dd.recordMoeBatchedDispatchPair(t, dev(torch, wg), dev(torch, wu), dev(torch, X), Yg, Yu, dev(torch, ids),
+                                        M, K, stride, E, k, T, K, k * M)
+        ctx.submit_and_wait()
+        assert ctx.launch_count - n0 == (4 if use_ws else 2)   # group, gather, two tile kernels / two per-pair kernels
+    finally:
+        dd.setWorkspace(None)
+    for Y, w in ((Yg, wg), (Yu, wu)):
+        want = np.stack([oracle.moe_dmmv_f64(w, t, M, K, stride, ids[i], K, np.repeat(X[i:i + 1], k, axis=0))
+                         for i in range(T)])
+        assert rel_l2(Y[:T * k * M].cpu().numpy().reshape(T, k, M), want) <= (TOL_TC if use_ws else TOL)
+        assert canary_intact(Y, T * k * M)
+
+
 def test_moe_dmmv_batched_grouped_edges(gpu, oracle):
     # with a workspace: fewer than 16 tokens keep the f32 per-pair kernel; expert ids past n_experts are
     # skipped by the grouped path (their output rows stay untouched)

@@ -41,6 +41,8 @@ _OPS = {
                               _u64, _u64],
     "zc_moe_fused_gate_up_act": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u32,
                                  _u32, _u64, _u64, _u32],
+    "zc_moe_dmmv_batched_pair": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32,
+                                 _u64, _u32, _u32, _u32, _u32, _u32],
     "zc_moe_dmmv_batched": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u32, _u32, _u32,
                             _u32, _u32],
     "zc_softmax_topk": [_vp, _u64, _vp, _vp, _u64, _u32, _u32, _u32, _u32, _u32, _u32],

@@ -734,13 +734,11 @@ int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type, const void* A, uint64_
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 
-int32_t zc_moe_dmmv_batched(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* X,
-                            uint64_t x_size, void* Y, uint64_t y_size, const void* routing, uint64_t routing_size,
-                            uint32_t M, uint32_t K, uint64_t expert_stride, uint32_t n_experts,
-                            uint32_t n_experts_used, uint32_t n_tokens, uint32_t x_token_stride,
-                            uint32_t y_token_stride) {
-    ZC_ENTER(ctx);
-    const char* fn = "zc_moe_dmmv_batched";
+static int32_t check_moe_batched(zc_ctx* ctx, const char* fn, uint32_t type, const void* A, uint64_t a_size,
+                                 const void* X, uint64_t x_size, void* Y, uint64_t y_size, const void* routing,
+                                 uint64_t routing_size, uint32_t M, uint32_t K, uint64_t expert_stride,
+                                 uint32_t n_experts, uint32_t n_experts_used, uint32_t n_tokens,
+                                 uint32_t x_token_stride, uint32_t y_token_stride) {
     if (n_tokens == 0 || n_experts_used == 0 || n_experts == 0)
         return fail(ctx, ZC_ERR_INVALID_ARG, "%s: zero token, expert or slot count", fn);
     ZC_TRY(check_mat(ctx, fn, type, A, a_size, 0, (uint64_t)n_experts * expert_stride, M, K));
@@ -752,6 +750,18 @@ int32_t zc_moe_dmmv_batched(zc_ctx* ctx, uint32_t type, const void* A, uint64_t 
     ZC_TRY(check_vec(ctx, fn, "Y", Y, y_size, 0,
                      ((uint64_t)(n_tokens - 1) * y_token_stride + (uint64_t)n_experts_used * M) * 4, 4));
     ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0, (uint64_t)n_tokens * n_experts_used * 4, 4));
+    return ZC_OK;
+}
+
+int32_t zc_moe_dmmv_batched(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* X,
+                            uint64_t x_size, void* Y, uint64_t y_size, const void* routing, uint64_t routing_size,
+                            uint32_t M, uint32_t K, uint64_t expert_stride, uint32_t n_experts,
+                            uint32_t n_experts_used, uint32_t n_tokens, uint32_t x_token_stride,
+                            uint32_t y_token_stride) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_dmmv_batched";
+    ZC_TRY(check_moe_batched(ctx, fn, type, A, a_size, X, x_size, Y, y_size, routing, routing_size, M, K, expert_stride,
+                             n_experts, n_experts_used, n_tokens, x_token_stride, y_token_stride));
     // With a workspace and a prefill-sized batch: group the pairs by expert and run the tensor-core tiles.
     if (ctx->workspace && n_tokens >= 16 &&
         moe_grouped_eligible(type, u8(A, 0), K, expert_stride, n_experts, (uint64_t)n_tokens * n_experts_used,
@@ -766,6 +776,34 @@ int32_t zc_moe_dmmv_batched(zc_ctx* ctx, uint32_t type, const void* A, uint64_t 
                                             static_cast<const uint32_t*>(routing), M, K, expert_stride,
                                             n_experts_used, n_tokens, x_token_stride, y_token_stride, ctx->stream,
                                             &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_moe_dmmv_batched_pair(zc_ctx* ctx, uint32_t type, const void* Wg, uint64_t wg_size, const void* Wu,
+                                 uint64_t wu_size, const void* X, uint64_t x_size, void* Yg, uint64_t yg_size, void* Yu,
+                                 uint64_t yu_size, const void* routing, uint64_t routing_size, uint32_t M, uint32_t K,
+                                 uint64_t expert_stride, uint32_t n_experts, uint32_t n_experts_used,
+                                 uint32_t n_tokens, uint32_t x_token_stride, uint32_t y_token_stride) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_dmmv_batched_pair";
+    ZC_TRY(check_moe_batched(ctx, fn, type, Wg, wg_size, X, x_size, Yg, yg_size, routing, routing_size, M, K,
+                             expert_stride, n_experts, n_experts_used, n_tokens, x_token_stride, y_token_stride));
+    ZC_TRY(check_moe_batched(ctx, fn, type, Wu, wu_size, X, x_size, Yu, yu_size, routing, routing_size, M, K,
+                             expert_stride, n_experts, n_experts_used, n_tokens, x_token_stride, y_token_stride));
+    const bool grouped = ctx->workspace && n_tokens >= 16 && !(reinterpret_cast<uintptr_t>(Wu) & 15u) &&
+                         moe_grouped_eligible(type, u8(Wg, 0), K, expert_stride, n_experts,
+                                              (uint64_t)n_tokens * n_experts_used, f32p(X, 0), x_token_stride,
+                                              ctx->workspace_size);
+    if (!grouped) {  // the two single calls run whichever path fits
+        ZC_TRY(zc_moe_dmmv_batched(ctx, type, Wg, wg_size, X, x_size, Yg, yg_size, routing, routing_size, M, K,
+                                   expert_stride, n_experts, n_experts_used, n_tokens, x_token_stride, y_token_stride));
+        return zc_moe_dmmv_batched(ctx, type, Wu, wu_size, X, x_size, Yu, yu_size, routing, routing_size, M, K,
+                                   expert_stride, n_experts, n_experts_used, n_tokens, x_token_stride, y_token_stride);
+    }
+    cudaError_t e = launch_moe_grouped(type, u8(Wg, 0), wg_size, f32p(X, 0), f32m(Yg, 0),
+                                       static_cast<const uint32_t*>(routing), M, K, expert_stride, n_experts,
+                                       n_experts_used, n_tokens, x_token_stride, y_token_stride, ctx->workspace,
+                                       ctx->status_dev, ctx->stream, &ctx->launches, u8(Wu, 0), wu_size, f32m(Yu, 0));
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 

@@ -102,7 +102,8 @@ cudaError_t launch_moe_grouped(uint32_t type, const uint8_t* A, uint64_t a_bytes
                                const uint32_t* routing, uint32_t M, uint32_t K, uint64_t expert_stride,
                                uint32_t n_experts, uint32_t n_used, uint32_t n_tokens, uint32_t x_token_stride,
                                uint32_t y_token_stride, void* ws, uint32_t* status, cudaStream_t s,
-                               uint64_t* launches);
+                               uint64_t* launches, const uint8_t* A2 = nullptr, uint64_t a2_bytes = 0,
+                               float* Y2 = nullptr);  // A2 / Y2: a second matrix on the same grouping (gate + up)
 
 // Prefill GEMM for the weight layouts without a 16-byte row pitch (MXFP4, Q6_K with K % 2048 != 0): bf16
 // activations, raw blocks fetched with cp.async, same tile kernel as the grouped MoE path (moe_gemm_tc.cu).

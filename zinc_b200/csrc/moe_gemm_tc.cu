@@ -496,7 +496,7 @@ cudaError_t launch_moe_grouped(uint32_t type, const uint8_t* A, uint64_t a_bytes
                                const uint32_t* routing, uint32_t M, uint32_t K, uint64_t expert_stride,
                                uint32_t n_experts, uint32_t n_used, uint32_t n_tokens, uint32_t x_token_stride,
                                uint32_t y_token_stride, void* ws, uint32_t* status, cudaStream_t s,
-                               uint64_t* launches) {
+                               uint64_t* launches, const uint8_t* A2, uint64_t a2_bytes, float* Y2) {
     EncodeFn enc = encode_fn();
     if (!enc) return cudaErrorNotSupported;
     const uint64_t n_pairs = (uint64_t)n_tokens * n_used;
@@ -529,14 +529,25 @@ cudaError_t launch_moe_grouped(uint32_t type, const uint8_t* A, uint64_t a_bytes
                   (M + kBM - 1) / kBM, status, 0u};
     const uint64_t max_items64 = (uint64_t)l.max_tiles * g.row_tiles;
     const uint32_t max_items = max_items64 > 0xFFFFFFFFull ? 0xFFFFFFFFu : (uint32_t)max_items64;
-    if (type == T_Q4_K)
-        e = bn == 32 ? launch_gemm<T_Q4_K, 32>(map, g, max_items, s) : launch_gemm<T_Q4_K, 128>(map, g, max_items, s);
-    else if (type == T_MXFP4)
-        e = bn == 32 ? launch_gemm<T_MXFP4, 32>(map, g, max_items, s)
-                     : launch_gemm<T_MXFP4, 128>(map, g, max_items, s);
-    else
-        e = bn == 32 ? launch_gemm<T_Q6_K, 32>(map, g, max_items, s) : launch_gemm<T_Q6_K, 128>(map, g, max_items, s);
-    if (e == cudaSuccess && launches) *launches += 3;
+    // one grouping and one packed activation buffer serve both matrices of a pair (gate and up)
+    for (int pass = 0; pass < (A2 ? 2 : 1); ++pass) {
+        if (pass == 1) {
+            g.A = A2;
+            g.a_end = A2 + a2_bytes;
+            g.Y = Y2;
+        }
+        if (type == T_Q4_K)
+            e = bn == 32 ? launch_gemm<T_Q4_K, 32>(map, g, max_items, s)
+                         : launch_gemm<T_Q4_K, 128>(map, g, max_items, s);
+        else if (type == T_MXFP4)
+            e = bn == 32 ? launch_gemm<T_MXFP4, 32>(map, g, max_items, s)
+                         : launch_gemm<T_MXFP4, 128>(map, g, max_items, s);
+        else
+            e = bn == 32 ? launch_gemm<T_Q6_K, 32>(map, g, max_items, s)
+                         : launch_gemm<T_Q6_K, 128>(map, g, max_items, s);
+        if (e != cudaSuccess) return e;
+    }
+    if (launches) *launches += A2 ? 4 : 3;
     return e;
 }
 

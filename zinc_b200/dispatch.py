@@ -281,6 +281,14 @@ class DmmvDispatch:
                       routing.ptr, routing.size, M, K, expert_stride, n_experts, n_experts_used, n_tokens,
                       x_token_stride, y_token_stride)
 
+    # gate and up of a prefill batch on one grouping (the prefill counterpart of dispatchMoeFusedGateUp)
+    def recordMoeBatchedDispatchPair(self, quant_type, Wg, Wu, X, Yg, Yu, routing, M, K, expert_stride, n_experts,
+                                     n_experts_used, n_tokens, x_token_stride, y_token_stride):
+        Wg, Wu, X, Yg, Yu, routing = map(_buf, (Wg, Wu, X, Yg, Yu, routing))
+        self.ctx.call("zc_moe_dmmv_batched_pair", quant_type, Wg.ptr, Wg.size, Wu.ptr, Wu.size, X.ptr, X.size,
+                      Yg.ptr, Yg.size, Yu.ptr, Yu.size, routing.ptr, routing.size, M, K, expert_stride, n_experts,
+                      n_experts_used, n_tokens, x_token_stride, y_token_stride)
+
     # Lend the library scratch for the grouped MoE prefill path (no counterpart in the reference's
     # DmmvDispatch; its Metal path owns route_ids / route_counts buffers). None removes it.
     def setWorkspace(self, workspace=None):
