@@ -116,6 +116,18 @@ public:
                                                       n_tokens, x_token_stride, y_token_stride));
     }
 
+    // Gate and up of a prefill batch on one grouping (no single counterpart in the reference: two
+    // recordMoeBatchedDispatch calls, src/compute/dmmv.zig:746-792)
+    Error recordMoeBatchedDispatchPair(GGMLType quant_type, Buffer wg_buf, Buffer wu_buf, Buffer x_buf, Buffer yg_buf,
+                                       Buffer yu_buf, Buffer routing_buf, uint32_t M, uint32_t K, uint32_t expert_stride,
+                                       uint32_t n_experts, uint32_t n_experts_used, uint32_t n_tokens,
+                                       uint32_t x_token_stride, uint32_t y_token_stride) {
+        return static_cast<Error>(zc_moe_dmmv_batched_pair(
+            ctx_, static_cast<uint32_t>(quant_type), wg_buf.ptr, wg_buf.size, wu_buf.ptr, wu_buf.size, x_buf.ptr,
+            x_buf.size, yg_buf.ptr, yg_buf.size, yu_buf.ptr, yu_buf.size, routing_buf.ptr, routing_buf.size, M, K,
+            expert_stride, n_experts, n_experts_used, n_tokens, x_token_stride, y_token_stride));
+    }
+
     // Lend the library scratch for the grouped-by-expert prefill form of recordMoeBatchedDispatch (no
     // counterpart in the reference's DmmvDispatch; its Metal path owns route_ids / route_counts buffers).
     // An empty Buffer removes it.
