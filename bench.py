@@ -160,7 +160,7 @@ def cpu_reference_arm(args):
     }
 
 
-def cpu_baseline_leg(torch, step, budget_s=12.0):
+def cpu_baseline_leg(torch, step, limit_s=12.0):
     """Oracle (shader-order port) timed on the host cores on layer 0's gate and down matrices."""
     import numpy as np
 
@@ -184,7 +184,7 @@ def cpu_baseline_leg(torch, step, budget_s=12.0):
     t0 = time.perf_counter()
     once()
     one = time.perf_counter() - t0
-    reps = max(1, min(200, int(budget_s / max(one, 1e-4))))
+    reps = max(1, min(200, int(limit_s / max(one, 1e-4))))
     t0 = time.perf_counter()
     for _ in range(reps):
         once()
