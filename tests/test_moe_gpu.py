@@ -235,6 +235,12 @@ def test_weighted_acc_swiglu_count_pack_scatter(gpu, oracle):
         ctx.submit_and_wait()
         assert canary_intact(y, 4099)
         assert rel_l2(y[:4099].cpu().numpy(), oracle.swiglu(gate, up, oai=oai)) <= 1e-6
+        y = out_with_canary(torch, 8192)   # a multiple of four, 16-byte aligned: the four-per-thread kernel
+        g8, u8 = np.tile(gate, 2)[:8192].copy(), np.tile(up, 2)[:8192].copy()
+        dd.dispatchSwiglu(dev(torch, g8), dev(torch, u8), y, 8192, oai=oai)
+        ctx.submit_and_wait()
+        assert canary_intact(y, 8192)
+        assert rel_l2(y[:8192].cpu().numpy(), oracle.swiglu(g8, u8, oai=oai)) <= 1e-6
     # count_experts over a [tokens][layers][2k] capture buffer
     T, L, k, E, layer = 37, 3, 4, 11, 1
     cap = g.integers(0, E, size=(T, L, 2 * k)).astype(np.uint32)

@@ -242,6 +242,27 @@ __global__ void swiglu_kernel(const float* __restrict__ gate, const float* __res
     }
 }
 
+template <bool OAI>
+__device__ __forceinline__ float swiglu_one(float g, float u) {
+    if (OAI) {
+        g = fminf(g, 7.0f);
+        u = fmaxf(-7.0f, fminf(u, 7.0f));
+        return (g / (1.0f + expf(1.702f * (-g)))) * (u + 1.0f);
+    }
+    return (g / (1.0f + expf(-g))) * u;
+}
+
+// the same element by element, four per thread
+template <bool OAI>
+__global__ void swiglu4_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ y,
+                               uint32_t n4) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n4) return;
+    const float4 g = __ldg(reinterpret_cast<const float4*>(gate) + i);
+    const float4 u = __ldg(reinterpret_cast<const float4*>(up) + i);
+    reinterpret_cast<float4*>(y)[i] = make_float4(swiglu_one<OAI>(g.x, u.x), swiglu_one<OAI>(g.y, u.y),
+                                                  swiglu_one<OAI>(g.z, u.z), swiglu_one<OAI>(g.w, u.w));
+}
 
 // ---- fused RMS norm + f32 router matvec -------------------------------------------------
 // src/shaders/rms_norm_dmmv_f32.comp:68-127: every CTA recomputes rms_inv = rsqrt(mean(x^2) + eps) (same
@@ -420,7 +441,14 @@ cudaError_t launch_moe_weighted_acc(float* a, const float* b, const uint32_t* ro
 cudaError_t launch_swiglu(const float* gate, const float* up, float* y, uint32_t n, bool oai, cudaStream_t s,
                           uint64_t* launches) {
     if (n == 0) return cudaSuccess;
-    if (oai) swiglu_kernel<true><<<(n + 255) / 256, 256, 0, s>>>(gate, up, y, n);
+    const bool vec = n >= 4096 && (n & 3u) == 0 &&
+                     ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) |
+                       reinterpret_cast<uintptr_t>(y)) & 15u) == 0;
+    if (vec) {  // prefill-sized vectors: 16 bytes per thread and array
+        const uint32_t n4 = n / 4;
+        if (oai) swiglu4_kernel<true><<<(n4 + 255) / 256, 256, 0, s>>>(gate, up, y, n4);
+        else swiglu4_kernel<false><<<(n4 + 255) / 256, 256, 0, s>>>(gate, up, y, n4);
+    } else if (oai) swiglu_kernel<true><<<(n + 255) / 256, 256, 0, s>>>(gate, up, y, n);
     else swiglu_kernel<false><<<(n + 255) / 256, 256, 0, s>>>(gate, up, y, n);
     if (launches) ++*launches;
     return cudaGetLastError();
