@@ -110,6 +110,17 @@ int32_t zc_memset(zc_ctx* ctx, void* dst, uint64_t dst_offset, int32_t byte_valu
  * idle and returns the first deferred device-side error, if any. */
 int32_t zc_barrier(zc_ctx* ctx);
 int32_t zc_submit_and_wait(zc_ctx* ctx);
+/* Device-side errors are deferred to zc_submit_and_wait, as the reference's are to submitAndWait:
+ *  - a bounded wait inside a kernel gave up (a split-K hand-off or a peer's flag): ZC_ERR_TIMEOUT. The
+ *    results of the calls since the last zc_submit_and_wait are invalid; the context stays usable (its
+ *    hand-off flags are cleared), a communicator whose exchange gave up refuses further collectives
+ *    until zc_comm_destroy + zc_comm_init on every rank;
+ *  - a routing buffer named an expert the weight buffer does not hold: ZC_ERR_INVALID_ARG (the id is
+ *    replaced by expert 0 or the pair is skipped, so no kernel reads outside the buffer).
+ * zc_set_wait_limit sets the number of polls after which such a wait gives up (0 = the defaults,
+ * 2^26 for split-K hand-offs and 2^24 for peer flags, i.e. seconds). No counterpart in the reference
+ * (Vulkan reports a lost device instead). */
+int32_t zc_set_wait_limit(zc_ctx* ctx, uint32_t polls);
 
 /* ---- pre-recorded op sequences ----------------------------------------------
  * The reference records a token's dispatches into a command buffer and
@@ -334,6 +345,26 @@ int32_t zc_moe_weighted_acc(zc_ctx* ctx, void* a, uint64_t a_size, const void* b
 int32_t zc_swiglu(zc_ctx* ctx, const void* gate, const void* up, void* y, uint32_t n);
 int32_t zc_swiglu_oai(zc_ctx* ctx, const void* gate, const void* up, void* y, uint32_t n);
 
+/* out[i] += bias[src_offset + i] for i < n. Replaces dispatchBiasAddSlice
+ * (src/compute/forward.zig:3875-3913; src/shaders/bias_add.comp:19-23), which the reference uses for
+ * the per-expert gate / up / down biases of GPT-OSS (forward.zig:6841-6849, 6923-6927). */
+int32_t zc_bias_add(zc_ctx* ctx, void* out, uint64_t out_size, const void* bias, uint64_t bias_size,
+                    uint32_t n, uint32_t src_offset);
+/* The same biases for all selected slots at once, fused with the activation that follows them in the
+ * reference's sequence (forward.zig:6841-6860): y[s][i] = act(gate[s][i] + gate_bias[e_s][i],
+ * up[s][i] + up_bias[e_s][i]) with e_s = routing[s], biases [n_experts][M] f32 (either may be NULL),
+ * act = swiglu (oai = 0) or swiglu_oai (oai = 1). */
+int32_t zc_moe_bias_act(zc_ctx* ctx, const void* gate, uint64_t gate_size, const void* up, uint64_t up_size,
+                        const void* gate_bias, uint64_t gate_bias_size,
+                        const void* up_bias, uint64_t up_bias_size,
+                        const void* routing, uint64_t routing_size, void* y, uint64_t y_size,
+                        uint32_t M, uint32_t n_used, uint32_t n_experts, uint32_t oai);
+/* a[i] += sum_s w_s * bias[e_s][i]: the down projection's per-expert bias (forward.zig:6923-6927) inside
+ * the weighted sum of the expert outputs; routing = [ids n_used][weights n_used], bias [n_experts][n]. */
+int32_t zc_moe_weighted_bias_acc(zc_ctx* ctx, void* a, uint64_t a_size, const void* bias, uint64_t bias_size,
+                                 const void* routing, uint64_t routing_size,
+                                 uint32_t n, uint32_t n_used, uint32_t n_experts);
+
 /* counts[e] = number of cells equal to e in the routing capture buffer of one
  * layer. Replaces recordCountExperts (src/compute/dmmv.zig:981-1028;
  * src/shaders/count_experts.comp:58-83). d_offset_bytes as there. */
@@ -374,6 +405,12 @@ int32_t zc_dequant_rows(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_si
  * must issue the same sequence of calls. Sums are formed in rank order: all ranks get identical bits. */
 int32_t zc_comm_init(zc_ctx* ctx, uint32_t rank, uint32_t world, uint8_t* out_handle64);
 int32_t zc_comm_connect(zc_ctx* ctx, const uint8_t* all_handles);
+/* For ranks that live in this process (several contexts, one per GPU, with peer access enabled by the
+ * caller): lend rank `rank`'s receive buffer by its device pointer instead of an IPC handle. The buffer
+ * (zc_comm_buffer_bytes() bytes, 256-byte aligned, zeroed) stays the caller's; zc_comm_connect skips
+ * ranks connected this way. */
+int32_t zc_comm_connect_local(zc_ctx* ctx, uint32_t rank, void* receive_buffer, uint64_t size);
+uint64_t zc_comm_buffer_bytes(void);
 int32_t zc_allreduce_sum_f32(zc_ctx* ctx, void* buf, uint64_t buf_size, uint64_t offset, uint32_t n);
 /* dst[r*n .. r*n+n) <- rank r's src[0..n) for every rank r (src may be the rank's own slice of dst);
  * n a multiple of 4, world * n <= 262144. Same protocol and ordering rule as the all-reduce. */
@@ -399,8 +436,9 @@ int32_t zc_comm_destroy(zc_ctx* ctx);
  * the call; a bounded wait that gave up stores {1, site} there, the result is then invalid and
  * the entry point must not be used again on that device.
  *
- * The first call on each device does the set-up (symbol address, SM count, one synchronous
- * clear of the flag words): make it before any stream capture starts on that device.
+ * The first call on each device does the set-up (symbol address, SM count; the flag words are
+ * zero when the library is loaded and every launch leaves them zero): make it before any stream
+ * capture starts on that device.
  * The scratch is shared by all calls on a device: calls ordered on one stream are safe; calls
  * whose kernels may overlap (different streams, unordered threads) race and give wrong results. */
 int32_t zc_dmmv_q4k_static_scratch(void* cuda_stream,

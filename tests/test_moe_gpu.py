@@ -461,7 +461,7 @@ def test_moe_dmmv_batched_pair(gpu, oracle, use_ws):
 
 def test_moe_dmmv_batched_grouped_edges(gpu, oracle):
     # with a workspace: fewer than 16 tokens keep the f32 per-pair kernel; expert ids past n_experts are
-    # skipped by the grouped path (their output rows stay untouched)
+    # skipped on both paths (their output rows stay untouched) and reported by the next submit_and_wait
     torch, ctx, dd = gpu
     t, E, M, K, k = zb.Q4_K, 4, 128, 256, 2
     g = synth.rng(208, 0)
@@ -485,18 +485,22 @@ def test_moe_dmmv_batched_grouped_edges(gpu, oracle):
         ids[3, 1] = E + 5      # not an expert
         ids[17, 0] = 0xFFFFFFFF
         X = synth.activations(g, T, K)
-        Y = out_with_canary(torch, T * k * M, init=-7.0)
-        dd.recordMoeBatchedDispatch(t, dev(torch, w), dev(torch, X), Y, dev(torch, ids), M, K, stride, E, k, T, K, k * M)
-        ctx.submit_and_wait()
-        got = Y[:T * k * M].cpu().numpy().reshape(T, k, M)
-        assert np.all(got[3, 1] == -7.0) and np.all(got[17, 0] == -7.0)
         ok = np.ones((T, k), bool)
         ok[3, 1] = ok[17, 0] = False
         safe = np.where(ok, ids, 0)
         want = np.stack([oracle.moe_dmmv_f64(w, t, M, K, stride, safe[i], K, np.repeat(X[i:i + 1], k, axis=0))
                          for i in range(T)])
-        assert rel_l2(got[ok], want[ok]) <= TOL_TC
-        assert canary_intact(Y, T * k * M)
+        for grouped in (True, False):
+            dd.setWorkspace(ws if grouped else None)
+            Y = out_with_canary(torch, T * k * M, init=-7.0)
+            dd.recordMoeBatchedDispatch(t, dev(torch, w), dev(torch, X), Y, dev(torch, ids), M, K, stride, E, k, T, K,
+                                        k * M)
+            with pytest.raises(zb.InvalidArgument):   # the bad ids are reported ...
+                ctx.submit_and_wait()
+            got = Y[:T * k * M].cpu().numpy().reshape(T, k, M)
+            assert np.all(got[3, 1] == -7.0) and np.all(got[17, 0] == -7.0)   # ... and their rows left alone
+            assert rel_l2(got[ok], want[ok]) <= (TOL_TC if grouped else TOL)
+            assert canary_intact(Y, T * k * M)
     finally:
         dd.setWorkspace(None)
 
@@ -510,7 +514,7 @@ def test_moe_decode_tensor_parallel_slices(gpu, cfg):
 
     if cfg == "mxfp4":   # 5 blocks of 32: an uneven cut (96 + 64)
         shape = MoeShape(hidden=256, n_experts=8, top_k=2, ffn=160, t_gate_up=zb.MXFP4, t_down=zb.MXFP4,
-                         rule=zb.ROUTE_TOPK_THEN_SOFTMAX, shared=False, oai=True, n_layers=2)
+                         rule=zb.ROUTE_TOPK_THEN_SOFTMAX, shared=False, oai=True, n_layers=2, biases=True)
     else:
         shape = MoeShape(hidden=512, n_experts=8, top_k=2, ffn=512, t_gate_up=zb.Q4_K, t_down=zb.Q6_K,
                          rule=zb.ROUTE_SOFTMAX_ALL_RENORM, shared=True, oai=False, n_layers=2)
@@ -525,5 +529,6 @@ def test_moe_decode_tensor_parallel_slices(gpu, cfg):
         n_part = part.record()
         ctx.submit_and_wait()
         total += part.hidden.cpu().numpy().astype(np.float64)
-        assert n_part == n_full + shape.n_layers   # hidden += partial (the zeroing is a memset, not a kernel)
+        # hidden += partial (the zeroing is a memset, not a kernel); only rank 0 adds the down bias
+        assert n_part == n_full + shape.n_layers - (shape.n_layers if shape.biases and rank else 0)
     assert rel_l2(total, want) <= 1e-5

@@ -49,6 +49,11 @@ _OPS = {
     "zc_moe_weighted_acc": [_vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32],
     "zc_swiglu": [_vp, _vp, _vp, _u32],
     "zc_swiglu_oai": [_vp, _vp, _vp, _u32],
+    "zc_bias_add": [_vp, _u64, _vp, _u64, _u32, _u32],
+    "zc_moe_bias_act": [_vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _u32],
+    "zc_moe_weighted_bias_acc": [_vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32],
+    "zc_set_wait_limit": [_u32],
+    "zc_comm_connect_local": [_u32, _vp, _u64],
     "zc_count_experts": [_vp, _u64, _vp, _u64, _u32, _u32, _u32, _u32, _u32, _u64],
     "zc_moe_route_pack": [_vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _u32, _u32],
     "zc_moe_route_scatter": [_vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _u32],
@@ -80,6 +85,7 @@ EXPORTS = sorted(list(_OPS) + [
     "zc_init", "zc_get_stream", "zc_last_error", "zc_status_string", "zc_launch_count",
     "zc_block_size", "zc_bytes_per_block", "zc_tensor_size_bytes", "zc_expert_slice_bytes",
     "zc_dmmv_supported", "zc_moe_dmmv_supported", "zc_dmmv_q4k_static_scratch", "zc_moe_grouped_workspace_bytes",
+    "zc_comm_buffer_bytes",
 ])
 
 _lib = None
@@ -111,6 +117,8 @@ def lib() -> C.CDLL:
         for name in ("zc_block_size", "zc_bytes_per_block"):
             getattr(L, name).restype = _u32
             getattr(L, name).argtypes = [_u32]
+        L.zc_comm_buffer_bytes.restype = _u64
+        L.zc_comm_buffer_bytes.argtypes = []
         L.zc_moe_grouped_workspace_bytes.restype = _u64
         L.zc_moe_grouped_workspace_bytes.argtypes = [_u32, _u32, _u32, _u32]
         L.zc_tensor_size_bytes.restype = _u64

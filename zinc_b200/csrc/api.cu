@@ -32,6 +32,8 @@ struct zc_ctx {
     zc::CommArgs comm;
     uint8_t* comm_local = nullptr;
     bool comm_open[zc::kCommMaxRanks] = {false};
+    bool comm_broken = false;          // a wait for a peer gave up: epochs no longer agree across ranks
+    uint32_t wait_limit = 0;           // 0: every kernel family's default; else polls per device-side wait
     // caller-owned scratch for the grouped MoE prefill path (zc_set_workspace)
     void* workspace = nullptr;
     uint64_t workspace_size = 0;
@@ -131,12 +133,37 @@ inline void attach_scratch(zc_ctx* ctx, DmmvArgs& a) {
     a.scratch_partial = ctx->scratch_partial;
     a.scratch_flags = ctx->scratch_flags;
     a.status = ctx->status_dev;
+    if (ctx->wait_limit) a.spin_limit = ctx->wait_limit;
     a.sm_count = ctx->sm_count;
+}
+
+// Experts a stacked weight buffer holds: ids read from a device-side routing buffer must stay below it.
+inline uint32_t experts_in_buffer(uint64_t a_size, uint64_t expert_bytes, uint64_t expert_stride) {
+    if (a_size < expert_bytes || expert_stride == 0) return 0;
+    const uint64_t n = (a_size - expert_bytes) / expert_stride + 1;
+    return n > 0xFFFFFFFFull ? 0xFFFFFFFFu : (uint32_t)n;
+}
+
+int32_t comm_usable(zc_ctx* ctx, const char* fn) {
+    if (!ctx->comm_local) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: no communicator (zc_comm_init / zc_comm_connect)", fn);
+    if (ctx->comm_broken)
+        return fail(ctx, ZC_ERR_TIMEOUT, "%s: an earlier exchange gave up waiting for a peer; destroy the communicator "
+                    "and set it up again on every rank", fn);
+    for (uint32_t r = 0; r < ctx->comm.world; ++r)
+        if (!ctx->comm.peers[r]) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: rank %u is not connected", fn, r);
+    ctx->comm.spin_limit = ctx->wait_limit ? ctx->wait_limit : (1u << 24);
+    return ZC_OK;
 }
 
 }  // namespace
 
 extern "C" {
+
+int32_t zc_set_wait_limit(zc_ctx* ctx, uint32_t polls) {
+    if (!ctx) return ZC_ERR_INVALID_ARG;
+    ctx->wait_limit = polls;
+    return ZC_OK;
+}
 
 int32_t zc_init(int32_t device, zc_ctx** out_ctx) {
     if (!out_ctx) return ZC_ERR_INVALID_ARG;
@@ -223,7 +250,7 @@ int32_t zc_comm_connect(zc_ctx* ctx, const uint8_t* all_handles) {
     const char* fn = "zc_comm_connect";
     if (!ctx->comm_local || !all_handles) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: call zc_comm_init first", fn);
     for (uint32_t r = 0; r < ctx->comm.world; ++r) {
-        if (r == ctx->comm.rank || ctx->comm_open[r]) continue;
+        if (r == ctx->comm.rank || ctx->comm_open[r] || ctx->comm.peers[r]) continue;  // self, open, or lent locally
         cudaIpcMemHandle_t h;
         memcpy(&h, all_handles + (size_t)r * 64, 64);
         void* p = nullptr;
@@ -238,9 +265,7 @@ int32_t zc_comm_connect(zc_ctx* ctx, const uint8_t* all_handles) {
 int32_t zc_allreduce_sum_f32(zc_ctx* ctx, void* buf, uint64_t buf_size, uint64_t offset, uint32_t n) {
     ZC_ENTER(ctx);
     const char* fn = "zc_allreduce_sum_f32";
-    if (!ctx->comm_local) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: no communicator (zc_comm_init / zc_comm_connect)", fn);
-    for (uint32_t r = 0; r < ctx->comm.world; ++r)
-        if (!ctx->comm.peers[r]) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: rank %u is not connected", fn, r);
+    ZC_TRY(comm_usable(ctx, fn));
     if (n == 0 || (n & 3u) || (uint64_t)n * 4 > kCommSlotBytes)
         return fail(ctx, ZC_ERR_INVALID_ARG, "%s: n=%u must be a non-zero multiple of 4, at most %llu", fn, n,
                     (unsigned long long)(kCommSlotBytes / 4));
@@ -253,9 +278,7 @@ int32_t zc_allgather_f32(zc_ctx* ctx, const void* src, uint64_t src_size, uint64
                          uint64_t dst_size, uint64_t dst_offset, uint32_t n) {
     ZC_ENTER(ctx);
     const char* fn = "zc_allgather_f32";
-    if (!ctx->comm_local) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: no communicator (zc_comm_init / zc_comm_connect)", fn);
-    for (uint32_t r = 0; r < ctx->comm.world; ++r)
-        if (!ctx->comm.peers[r]) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: rank %u is not connected", fn, r);
+    ZC_TRY(comm_usable(ctx, fn));
     if (n == 0 || (n & 3u) || (uint64_t)n * 4 * ctx->comm.world > kCommGatherBytes)
         return fail(ctx, ZC_ERR_INVALID_ARG, "%s: n=%u must be a non-zero multiple of 4 with world * n <= %llu", fn, n,
                     (unsigned long long)(kCommGatherBytes / 4));
@@ -278,8 +301,24 @@ int32_t zc_comm_destroy(zc_ctx* ctx) {
     cudaFree(ctx->comm_local);
     ctx->comm_local = nullptr;
     ctx->comm = CommArgs();
+    ctx->comm_broken = false;
     return ZC_OK;
 }
+
+int32_t zc_comm_connect_local(zc_ctx* ctx, uint32_t rank, void* receive_buffer, uint64_t size) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_comm_connect_local";
+    if (!ctx->comm_local) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: call zc_comm_init first", fn);
+    if (rank >= ctx->comm.world || rank == ctx->comm.rank || ctx->comm_open[rank])
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: rank %u is this rank, out of range or already connected", fn, rank);
+    if (!receive_buffer || size < kCommBufBytes || (reinterpret_cast<uintptr_t>(receive_buffer) & 255u))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: need a 256-byte aligned device buffer of at least %llu bytes", fn,
+                    (unsigned long long)kCommBufBytes);
+    ctx->comm.peers[rank] = static_cast<uint8_t*>(receive_buffer);  // borrowed: never closed or freed here
+    return ZC_OK;
+}
+
+uint64_t zc_comm_buffer_bytes(void) { return kCommBufBytes; }
 
 int32_t zc_set_stream(zc_ctx* ctx, void* cuda_stream) {
     if (!ctx) return ZC_ERR_INVALID_ARG;
@@ -366,6 +405,16 @@ int32_t zc_submit_and_wait(zc_ctx* ctx) {
         const uint32_t code = ctx->status_host[0], where = ctx->status_host[1];
         ctx->status_host[0] = 0;
         ctx->status_host[1] = 0;
+        if (code == 2)
+            return fail(ctx, ZC_ERR_INVALID_ARG,
+                        "a routing buffer named expert %u, which the weight buffer does not hold; the results of that "
+                        "call are invalid", where);
+        // A wait gave up. Split-K publication flags may be left set and would be taken for fresh partial sums
+        // by the next streaming matvec: clear them. A peer exchange that gave up leaves the ranks' epochs out
+        // of step: the communicator refuses further collectives until it is destroyed and set up again.
+        cudaMemsetAsync(ctx->scratch_flags, 0, kStreamFlagBytes, ctx->stream);
+        cudaStreamSynchronize(ctx->stream);
+        if (where >= 200 && ctx->comm_local) ctx->comm_broken = true;
         return fail(ctx, ZC_ERR_TIMEOUT, "device-side wait gave up (code %u, site %u)", code, where);
     }
     return ZC_OK;
@@ -639,6 +688,8 @@ int32_t zc_moe_dmmv(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, 
     a.expert_stride = expert_stride;
     a.n_used = n_used;
     a.x_expert_stride = x_expert_stride;
+    a.n_experts_max = experts_in_buffer(a_size, (uint64_t)M * row_bytes_of(type, K), expert_stride);
+    a.status = ctx->status_dev;
     cudaError_t e = launch_dmmv(type, MODE_MOE, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
@@ -669,6 +720,8 @@ static int32_t moe_gate_up_common(zc_ctx* ctx, const char* fn, uint32_t type, co
     a.x_expert_stride = x_expert_stride;
     a.a_end = u8(Wg, wg_size);
     a.a2_end = u8(Wu, wu_size);
+    a.n_experts_max = experts_in_buffer(wg_size < wu_size ? wg_size : wu_size, (uint64_t)M * row_bytes_of(type, K),
+                                        expert_stride);
     attach_scratch(ctx, a);
     cudaError_t e;
     if (warp_moe_gate_up_eligible(type, a))
@@ -723,6 +776,7 @@ int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type, const void* A, uint64_
     a.n_used = n_used;
     a.x_expert_stride = x_expert_stride;
     a.a_end = u8(A, a_size);
+    a.n_experts_max = experts_in_buffer(a_size, (uint64_t)M * row_bytes_of(type, K), expert_stride);
     attach_scratch(ctx, a);
     cudaError_t e;
     if (mxfp4_moe_down_acc_eligible(type, a))
@@ -774,8 +828,8 @@ int32_t zc_moe_dmmv_batched(zc_ctx* ctx, uint32_t type, const void* A, uint64_t 
     }
     cudaError_t e = launch_moe_dmmv_batched(type, u8(A, 0), f32p(X, 0), f32m(Y, 0),
                                             static_cast<const uint32_t*>(routing), M, K, expert_stride,
-                                            n_experts_used, n_tokens, x_token_stride, y_token_stride, ctx->stream,
-                                            &ctx->launches);
+                                            n_experts_used, n_tokens, x_token_stride, y_token_stride, n_experts,
+                                            ctx->status_dev, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 
@@ -866,6 +920,56 @@ int32_t zc_swiglu(zc_ctx* ctx, const void* gate, const void* up, void* y, uint32
 }
 int32_t zc_swiglu_oai(zc_ctx* ctx, const void* gate, const void* up, void* y, uint32_t n) {
     return swiglu_common(ctx, gate, up, y, n, true);
+}
+
+int32_t zc_bias_add(zc_ctx* ctx, void* out, uint64_t out_size, const void* bias, uint64_t bias_size, uint32_t n,
+                    uint32_t src_offset) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_bias_add";
+    if (n == 0) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: n must be non-zero", fn);
+    ZC_TRY(check_vec(ctx, fn, "out", out, out_size, 0, (uint64_t)n * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "bias", bias, bias_size, (uint64_t)src_offset * 4, (uint64_t)n * 4, 4));
+    cudaError_t e = launch_bias_add(static_cast<float*>(out), static_cast<const float*>(bias), n, src_offset,
+                                    ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_moe_bias_act(zc_ctx* ctx, const void* gate, uint64_t gate_size, const void* up, uint64_t up_size,
+                        const void* gate_bias, uint64_t gate_bias_size, const void* up_bias, uint64_t up_bias_size,
+                        const void* routing, uint64_t routing_size, void* y, uint64_t y_size, uint32_t M,
+                        uint32_t n_used, uint32_t n_experts, uint32_t oai) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_bias_act";
+    if (M == 0 || n_used == 0 || n_experts == 0 || oai > 1)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: M, n_used and n_experts must be non-zero, oai 0 or 1", fn);
+    const uint64_t act_bytes = (uint64_t)n_used * M * 4, bias_bytes = (uint64_t)n_experts * M * 4;
+    ZC_TRY(check_vec(ctx, fn, "gate", gate, gate_size, 0, act_bytes, 4));
+    ZC_TRY(check_vec(ctx, fn, "up", up, up_size, 0, act_bytes, 4));
+    ZC_TRY(check_vec(ctx, fn, "y", y, y_size, 0, act_bytes, 4));
+    if (gate_bias) ZC_TRY(check_vec(ctx, fn, "gate_bias", gate_bias, gate_bias_size, 0, bias_bytes, 4));
+    if (up_bias) ZC_TRY(check_vec(ctx, fn, "up_bias", up_bias, up_bias_size, 0, bias_bytes, 4));
+    ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0, (uint64_t)n_used * 4, 4));
+    cudaError_t e = launch_moe_bias_act(static_cast<const float*>(gate), static_cast<const float*>(up),
+                                        static_cast<const float*>(gate_bias), static_cast<const float*>(up_bias),
+                                        static_cast<const uint32_t*>(routing), static_cast<float*>(y), M, n_used,
+                                        n_experts, oai != 0, ctx->status_dev, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_moe_weighted_bias_acc(zc_ctx* ctx, void* a, uint64_t a_size, const void* bias, uint64_t bias_size,
+                                 const void* routing, uint64_t routing_size, uint32_t n, uint32_t n_used,
+                                 uint32_t n_experts) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_weighted_bias_acc";
+    if (n == 0 || n_used == 0 || n_experts == 0)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: n, n_used and n_experts must be non-zero", fn);
+    ZC_TRY(check_vec(ctx, fn, "a", a, a_size, 0, (uint64_t)n * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "bias", bias, bias_size, 0, (uint64_t)n_experts * n * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0, (uint64_t)2 * n_used * 4, 4));
+    cudaError_t e = launch_moe_weighted_bias_acc(static_cast<float*>(a), static_cast<const float*>(bias),
+                                                 static_cast<const uint32_t*>(routing), n, n_used, n_experts,
+                                                 ctx->status_dev, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 
 int32_t zc_count_experts(zc_ctx* ctx, const void* routing, uint64_t routing_size, void* counts,

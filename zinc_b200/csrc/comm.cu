@@ -23,7 +23,6 @@ namespace zc {
 namespace {
 
 constexpr int kThreads = 1024;
-constexpr uint32_t kCommSpinLimit = 1u << 24;
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     uint32_t v;
@@ -45,12 +44,12 @@ __device__ __forceinline__ void pdl_enter() {
 __global__ void __launch_bounds__(kThreads) allreduce_oneshot_kernel(const CommArgs c, float* buf, uint32_t n) {
     __shared__ uint32_t failed;
     const int tid = threadIdx.x;
+    if (tid == 0) failed = 0;
     pdl_enter();
     uint8_t* local = c.peers[c.rank];
     uint32_t* epoch_word = reinterpret_cast<uint32_t*>(local + kCommEpochOffset);
     const uint32_t epoch = *epoch_word + 1;
     const uint32_t parity = epoch & 1u;
-    if (tid == 0) failed = 0;
     const uint32_t n4 = n >> 2;
     const float4* in = reinterpret_cast<const float4*>(buf);
     // 1. my vector into slot [parity][rank] of every rank's buffer (mine included)
@@ -69,7 +68,7 @@ __global__ void __launch_bounds__(kThreads) allreduce_oneshot_kernel(const CommA
         const uint32_t* mine = reinterpret_cast<const uint32_t*>(local + kCommFlagOffset) + parity * kCommMaxRanks + tid;
         uint32_t spins = 0;
         while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-            if (++spins == kCommSpinLimit) {
+            if (++spins >= c.spin_limit) {
                 failed = 1;
                 if (c.status) {
                     c.status[0] = 1;
@@ -80,6 +79,9 @@ __global__ void __launch_bounds__(kThreads) allreduce_oneshot_kernel(const CommA
         }
     }
     __syncthreads();
+    // A wait gave up: a slot may hold a stale vector, so nothing is summed and the epoch does not advance.
+    // The status words carry {1, site}; the host marks the communicator unusable (zc_submit_and_wait).
+    if (failed) return;
     // 4. sum the slots in rank order (identical on every rank)
     const uint8_t* slots = local + (size_t)parity * kCommMaxRanks * kCommSlotBytes;
     float4* out = reinterpret_cast<float4*>(buf);
@@ -139,7 +141,7 @@ __global__ void __launch_bounds__(kThreads) allgather_oneshot_kernel(const CommA
             reinterpret_cast<const uint32_t*>(local + kCommGatherFlagOffset) + parity * kCommMaxRanks + tid;
         uint32_t spins = 0;
         while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-            if (++spins == kCommSpinLimit) {
+            if (++spins >= c.spin_limit) {
                 s_failed = 1;
                 if (c.status) {
                     c.status[0] = 1;
@@ -150,11 +152,14 @@ __global__ void __launch_bounds__(kThreads) allgather_oneshot_kernel(const CommA
         }
     }
     __syncthreads();
-    // 3. copy the gathered vector out
-    const float4* all = reinterpret_cast<const float4*>(local + region);
-    float4* out = reinterpret_cast<float4*>(dst);
-    const uint32_t total4 = n4 * c.world;
-    for (uint32_t i = blockIdx.x * kThreads + tid; i < total4; i += gridDim.x * kThreads) out[i] = __ldcg(all + i);
+    // 3. copy the gathered vector out (not after a wait that gave up: a slice may be stale; the status words
+    // carry {1, site} and the host marks the communicator unusable)
+    if (!s_failed) {
+        const float4* all = reinterpret_cast<const float4*>(local + region);
+        float4* out = reinterpret_cast<float4*>(dst);
+        const uint32_t total4 = n4 * c.world;
+        for (uint32_t i = blockIdx.x * kThreads + tid; i < total4; i += gridDim.x * kThreads) out[i] = __ldcg(all + i);
+    }
     __syncthreads();
     if (tid == 0 && atomicAdd(words + 3, 1u) == gridDim.x - 1) {  // last CTA to leave: next epoch
         words[3] = 0;

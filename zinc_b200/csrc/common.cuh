@@ -47,6 +47,19 @@ __device__ __forceinline__ float e2m1_to_f32(uint32_t n) {
     return (n & 8u) ? -mag : mag;
 }
 
+// Expert ids come from a routing buffer on the device, so the host cannot range-check them. An id at or
+// beyond n_max (the number of experts the weight buffer holds) is recorded in the status words as
+// {2, id} (reported by zc_submit_and_wait as an invalid argument) and replaced by expert 0, so that no
+// kernel ever forms an address outside the expert stack.
+__device__ __forceinline__ uint32_t checked_expert(uint32_t e, uint32_t n_max, uint32_t* status) {
+    if (e < n_max) return e;
+    if (status) {
+        status[0] = 2u;
+        status[1] = e;
+    }
+    return 0u;
+}
+
 // ---- loads -----------------------------------------------------------------
 
 __device__ __forceinline__ uint32_t ldg_u32(const void* p) {

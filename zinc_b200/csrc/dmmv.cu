@@ -68,7 +68,7 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
         const uint32_t slot = blockIdx.y;
         const uint32_t row0 = (blockIdx.x * kWarps + warp) * NR;
         if (row0 >= a.M) return;
-        const uint8_t* base = a.A + (uint64_t)__ldg(a.routing + slot) * a.expert_stride;
+        const uint8_t* base = a.A + (uint64_t)checked_expert(__ldg(a.routing + slot), a.n_experts_max, a.status) * a.expert_stride;
         const float* x = a.x + (size_t)slot * a.x_expert_stride;
         const uint8_t* rows[NR];
 #pragma unroll
@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
         const uint32_t slot = blockIdx.y;
         const uint32_t row0 = (blockIdx.x * kWarps + warp) * NR;
         if (row0 >= a.M) return;
-        const uint64_t ebase = (uint64_t)__ldg(a.routing + slot) * a.expert_stride;
+        const uint64_t ebase = (uint64_t)checked_expert(__ldg(a.routing + slot), a.n_experts_max, a.status) * a.expert_stride;
         const float* x = a.x + (size_t)slot * a.x_expert_stride;
         const uint8_t* rows[2 * NR];
 #pragma unroll
@@ -138,7 +138,9 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
         const uint32_t slot = blockIdx.y, tok = blockIdx.z;
         const uint32_t row = blockIdx.x * kWarps + warp;
         if (row >= a.M) return;
-        const uint32_t e = __ldg(a.routing + (size_t)tok * a.n_used + slot);
+        const uint32_t e_raw = __ldg(a.routing + (size_t)tok * a.n_used + slot);
+        const uint32_t e = checked_expert(e_raw, a.n_experts_max, a.status);
+        if (e != e_raw) return;  // not an expert: reported, its output row stays untouched (as on the grouped path)
         const uint8_t* rows[1] = {a.A + (uint64_t)e * a.expert_stride + (uint64_t)row * row_bytes};
         float acc[1] = {0.f};
         rowdot<TYPE, 1, ALIGNED>(rows, a.x + (size_t)tok * a.x_token_stride, a.K, lane, acc);
@@ -151,7 +153,7 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
 #pragma unroll
         for (int r = 0; r < NR; ++r) total[r] = 0.f;
         for (uint32_t s = 0; s < a.n_used; ++s) {
-            const uint8_t* base = a.A + (uint64_t)__ldg(a.routing + s) * a.expert_stride;
+            const uint8_t* base = a.A + (uint64_t)checked_expert(__ldg(a.routing + s), a.n_experts_max, a.status) * a.expert_stride;
             const uint8_t* rows[NR];
 #pragma unroll
             for (int r = 0; r < NR; ++r) rows[r] = base + (uint64_t)min(row0 + r, a.M - 1) * row_bytes;
@@ -265,7 +267,8 @@ cudaError_t launch_dmmv_batch(uint32_t type, const uint8_t* A, const float* X, f
 cudaError_t launch_moe_dmmv_batched(uint32_t type, const uint8_t* A, const float* X, float* Y,
                                     const uint32_t* routing, uint32_t M, uint32_t K, uint64_t expert_stride,
                                     uint32_t n_experts_used, uint32_t n_tokens, uint32_t x_token_stride,
-                                    uint32_t y_token_stride, cudaStream_t s, uint64_t* launches) {
+                                    uint32_t y_token_stride, uint32_t n_experts_max, uint32_t* status, cudaStream_t s,
+                                    uint64_t* launches) {
     for (uint32_t t0 = 0; t0 < n_tokens; t0 += 65535u) {
         DmmvArgs a;
         a.A = A;
@@ -279,6 +282,8 @@ cudaError_t launch_moe_dmmv_batched(uint32_t type, const uint8_t* A, const float
         a.n_tokens = n_tokens - t0 < 65535u ? n_tokens - t0 : 65535u;
         a.x_token_stride = x_token_stride;
         a.y_token_stride = y_token_stride;
+        a.n_experts_max = n_experts_max;
+        a.status = status;
         cudaError_t e = launch_dmmv(type, MODE_MOE_BATCHED, a, s, launches);
         if (e != cudaSuccess) return e;
     }

@@ -199,10 +199,11 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
     auto locate = [&](uint32_t T, uint32_t strm, const uint8_t*& base, uint32_t& Mb) {
         if constexpr (kSeg == 2) {
             const uint32_t slot = T / a.tiles_per_expert, t0 = slot * a.tiles_per_expert * 16;
-            base = a.A[strm] + (uint64_t)__ldg(a.routing + slot) * a.expert_stride - (uint64_t)t0 * row_bytes;
+            base = a.A[strm] + (uint64_t)checked_expert(__ldg(a.routing + slot), a.n_experts_max, a.status) * a.expert_stride -
+                   (uint64_t)t0 * row_bytes;
             Mb = t0 + a.M;
         } else if constexpr (kSeg == 3) {
-            base = a.A[0] + (uint64_t)__ldg(a.routing + strm) * a.expert_stride;
+            base = a.A[0] + (uint64_t)checked_expert(__ldg(a.routing + strm), a.n_experts_max, a.status) * a.expert_stride;
             Mb = a.M;
         } else {
             base = a.A[strm];
@@ -391,13 +392,8 @@ template <int NS, int EPI, int kWarps, int kSeg>
 cudaError_t launch_x(const WarpArgs& a, const uint8_t* a_end, const uint8_t* a_end2, cudaStream_t st, int sm_count,
                      size_t smem) {
     auto kern = dmmv_mxfp4_warp_kernel<NS, EPI, kWarps, kSeg>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kWarps == 8 ? (int)kTwoPerSmX : 227 * 1024);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_done{0};  // per device ordinal
+    if (cudaError_t ea = ensure_dynamic_smem(kern, kWarps == 8 ? (int)kTwoPerSmX : 227 * 1024, attr_done); ea != cudaSuccess) return ea;
     const uint32_t nb = a.K >> 5;
     const uint64_t tiles = kSeg == 2 ? (uint64_t)a.nseg * a.tiles_per_expert : (a.M + 15) / 16;
     const uint64_t U = tiles * ((nb + kUnitBlocks - 1) / kUnitBlocks) * (kSeg == 3 ? a.nseg : (uint32_t)NS);
@@ -474,8 +470,10 @@ static void fill_common(WarpArgs& wa, const DmmvArgs& a) {
     wa.gpartial = a.scratch_partial;
     wa.gflags = a.scratch_flags;
     wa.status = a.status;
+    wa.spin_limit = a.spin_limit;
     wa.nseg = 0;
     wa.routing = a.routing;
+    wa.n_experts_max = a.n_experts_max;
     wa.expert_stride = a.expert_stride;
     wa.tiles_per_expert = (a.M + 15) / 16;
     wa.x_slot_stride = 0;

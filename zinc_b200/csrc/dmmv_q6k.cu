@@ -182,7 +182,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
         if constexpr (kMoe) {
             const uint32_t slot = b / bpe;
             lb = b - slot * bpe;
-            return a.A[0] + (uint64_t)__ldg(a.routing + slot) * a.expert_stride;
+            return a.A[0] + (uint64_t)checked_expert(__ldg(a.routing + slot), a.n_experts_max, a.status) * a.expert_stride;
         } else {
             lb = b;
             return a.A[0];
@@ -360,13 +360,8 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
 template <int EPI, int kWarps, bool kRowsAligned, bool kMoe = false>
 cudaError_t launch_w6(const WarpArgs& a, const uint8_t* a_end, cudaStream_t st, int sm_count, size_t smem) {
     auto kern = dmmv_q6k_warp_kernel<EPI, kWarps, kRowsAligned, kMoe>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kWarps == 8 ? (int)kTwoPerSm : 227 * 1024);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_done{0};  // per device ordinal
+    if (cudaError_t ea = ensure_dynamic_smem(kern, kWarps == 8 ? (int)kTwoPerSm : 227 * 1024, attr_done); ea != cudaSuccess) return ea;
     const uint64_t U = (uint64_t)((a.M + 15) / 16) * (a.K >> 8) * (kMoe ? a.nseg : 1u);
     uint64_t grid = (uint64_t)sm_count * (16 / kWarps);
     if (grid * kWarps > U) grid = U / kWarps;
@@ -435,8 +430,10 @@ cudaError_t launch_q6k_moe_down_acc(const DmmvArgs& a, cudaStream_t st, uint64_t
     wa.gpartial = a.scratch_partial;
     wa.gflags = a.scratch_flags;
     wa.status = a.status;
+    wa.spin_limit = a.spin_limit;
     wa.nseg = a.n_used;
     wa.routing = a.routing;
+    wa.n_experts_max = a.n_experts_max;
     wa.expert_stride = a.expert_stride;
     wa.x_slot_stride = a.x_expert_stride;
     const uint32_t Kt = a.K * a.n_used;
@@ -461,6 +458,7 @@ cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t st, uint64
     wa.gpartial = a.scratch_partial;
     wa.gflags = a.scratch_flags;
     wa.status = a.status;
+    wa.spin_limit = a.spin_limit;
     wa.nseg = 0;
     cudaError_t e = mode == MODE_PLAIN ? launch_cfg6<EPI_PLAIN>(wa, a.a_end, st, a.sm_count)
                                        : launch_cfg6<EPI_SIGMOID_ACC>(wa, a.a_end, st, a.sm_count);

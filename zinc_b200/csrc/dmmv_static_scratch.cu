@@ -10,17 +10,16 @@
 // calls no allocating routine: the scratch is part of the loaded module.
 //
 // The array is shared by every call on the same device. Consequences:
-//  * the flag words must be zero when a launch starts. They are zero at module load, the
-//    set-up below clears them once more, and each launch leaves them zero (the reader of a
-//    flag clears it). A launch that gave up on a bounded wait (status word set) may leave
+//  * the flag words must be zero when a launch starts. A __device__ array is zero when the
+//    module is loaded on a device, and each launch leaves the flags zero (the reader of a
+//    flag clears it), so the set-up writes nothing. A launch that gave up on a bounded wait (status word set) may leave
 //    flags set; the next call sees the non-zero status word only if the caller checks it, so
 //    a caller that finds status_words[0] != 0 must stop using this entry point on that device.
 //  * two calls whose kernels can overlap (different streams, or threads without ordering)
 //    race on the array and give wrong results. Calls on one stream are ordered and safe.
 //
-// Set-up happens inside the first call on each device: cudaGetSymbolAddress, one attribute
-// query and one synchronous cudaMemset of the flag words. Make the first call on a device
-// before starting any stream capture on it.
+// Set-up happens inside the first call on each device: cudaGetSymbolAddress and one attribute
+// query (no device work). Make the first call on a device before starting any stream capture on it.
 #include <cuda_runtime.h>
 #include <stdarg.h>
 #include <stdint.h>
@@ -73,9 +72,6 @@ cudaError_t setup_device(int device, DeviceState** out) {
         if (e != cudaSuccess) return e;
         int sms = 0;
         e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
-        if (e != cudaSuccess) return e;
-        // flag words start at zero
-        e = cudaMemset(static_cast<unsigned char*>(ptr) + kStreamPartialBytes, 0, kStreamFlagBytes);
         if (e != cudaSuccess) return e;
         st.scratch = static_cast<unsigned char*>(ptr);
         st.sm_count = sms;

@@ -218,7 +218,8 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
             Mb = a.segM[sg];
         } else if constexpr (kSeg == 2) {
             const uint32_t slot = p_tile / a.tiles_per_expert, t0 = slot * a.tiles_per_expert * 16;
-            base = a.A[p_strm] + (uint64_t)__ldg(a.routing + slot) * a.expert_stride - (uint64_t)t0 * row_bytes;
+            base = a.A[p_strm] + (uint64_t)checked_expert(__ldg(a.routing + slot), a.n_experts_max, a.status) * a.expert_stride -
+                   (uint64_t)t0 * row_bytes;
             Mb = t0 + a.M;
         } else {
             base = a.A[p_strm];
@@ -375,13 +376,8 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
 template <int NS, int EPI, int kWarps, int kSeg = 0>
 cudaError_t launch_w(const WarpArgs& a, cudaStream_t st, int sm_count, size_t smem) {
     auto kern = dmmv_q4k_warp_kernel<NS, EPI, kWarps, kSeg>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kWarps == 8 ? (int)kTwoPerSm : 227 * 1024);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_done{0};  // per device ordinal
+    if (cudaError_t ea = ensure_dynamic_smem(kern, kWarps == 8 ? (int)kTwoPerSm : 227 * 1024, attr_done); ea != cudaSuccess) return ea;
     const uint64_t tiles = kSeg == 1 ? a.seg_end[a.nseg - 1] : kSeg == 2 ? (uint64_t)a.nseg * a.tiles_per_expert : (a.M + 15) / 16;
     const uint64_t U = tiles * (((a.K >> 8) + kCB - 1) / kCB) * NS;
     uint64_t grid = (uint64_t)sm_count * (16 / kWarps);  // 16 worker warps per SM
@@ -426,6 +422,7 @@ cudaError_t launch_warp_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStr
     wa.gpartial = a.scratch_partial;
     wa.gflags = a.scratch_flags;
     wa.status = a.status;
+    wa.spin_limit = a.spin_limit;
     wa.nseg = 0;
     cudaError_t e;
     switch (mode) {
@@ -467,6 +464,7 @@ cudaError_t launch_warp_dmmv_multi(uint32_t n, const uint8_t* const* A, float* c
     wa.gpartial = common.scratch_partial;
     wa.gflags = common.scratch_flags;
     wa.status = common.status;
+    wa.spin_limit = common.spin_limit;
     wa.nseg = n;
     const uint64_t row_bytes = (uint64_t)(common.K >> 8) * 144;
     uint32_t t0 = 0;
@@ -520,8 +518,10 @@ cudaError_t launch_warp_moe_gate_up(const DmmvArgs& a, cudaStream_t st, uint64_t
     wa.gpartial = a.scratch_partial;
     wa.gflags = a.scratch_flags;
     wa.status = a.status;
+    wa.spin_limit = a.spin_limit;
     wa.nseg = a.n_used;
     wa.routing = a.routing;
+    wa.n_experts_max = a.n_experts_max;
     wa.expert_stride = a.expert_stride;
     wa.tiles_per_expert = (a.M + 15) / 16;
     const size_t s8 = smem_bytes(a.K, 8);

@@ -442,13 +442,8 @@ cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, u
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
     auto kern = gemm_tc_kernel<TYPE, BN, NACC>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)Tile<TYPE, BN>::kSmemBytes);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_done{0};  // per device ordinal
+    if (cudaError_t ea = ensure_dynamic_smem(kern, (int)Tile<TYPE, BN>::kSmemBytes, attr_done); ea != cudaSuccess) return ea;
     GemmArgs g{A, D, M, N, K, stride_d, status};
     dim3 grid((M + kBM - 1) / kBM, (N + BN * NACC - 1) / (BN * NACC), 1);
     // Few tiles (short M or few tokens): split K over up to 8 CTAs per tile, at least 4 blocks each, and
@@ -482,13 +477,8 @@ cudaError_t launch_small(const uint8_t* A, const void* B, float* D, uint32_t M, 
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)kSmSmemBytes);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_done{0};  // per device ordinal
+    if (cudaError_t ea = ensure_dynamic_smem(gemm_tc_small_kernel, (int)kSmSmemBytes, attr_done); ea != cudaSuccess) return ea;
     GemmArgs g{A, D, M, N, K, stride_d, status};
     dim3 grid((M + kSmRows - 1) / kSmRows, (N + 127) / 128, 1);
     int dev = 0, sms = 0;

@@ -5,7 +5,24 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace zc {
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device property of a kernel: opt in once per device
+// ordinal (bit d of `done`), with the device that is current at the launch. Safe from several host threads.
+template <typename Kern>
+inline cudaError_t ensure_dynamic_smem(Kern kern, int bytes, std::atomic<uint64_t>& done) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const uint64_t bit = 1ull << (dev & 63);
+    if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return e;
+    done.fetch_or(bit, std::memory_order_release);
+    return cudaSuccess;
+}
 
 // Epilogue / addressing modes of the decode matvec kernel family.
 enum DmmvMode : int {
@@ -33,6 +50,7 @@ struct DmmvArgs {
     uint32_t act = 0;             // MoE gate/up: 0 write both, 1 y = silu(gate) * up, 2 the GPT-OSS (swiglu_oai) form
     uint32_t x_expert_stride = 0;
     uint64_t expert_stride = 0;
+    uint32_t n_experts_max = 0xFFFFFFFFu;  // expert ids in `routing` must be below this (experts the buffer holds)
     uint32_t n_tokens = 1;        // MODE_MOE_BATCHED
     uint32_t x_token_stride = 0;  // MODE_MOE_BATCHED, elements
     uint32_t y_token_stride = 0;  // MODE_MOE_BATCHED, elements
@@ -40,6 +58,7 @@ struct DmmvArgs {
     float* scratch_partial = nullptr;   // [kStreamMaxWorkers][32] partial sums published across CTAs
     uint32_t* scratch_flags = nullptr;  // [kStreamMaxWorkers] publication flags, zero between launches
     uint32_t* status = nullptr;
+    uint32_t spin_limit = 1u << 26;     // polls after which a device-side wait gives up
     int sm_count = 0;
     // first byte past the buffers that hold A / A2 (kernels that fetch aligned supersets of unaligned rows
     // must not read beyond them)
@@ -91,7 +110,8 @@ cudaError_t launch_dmmv_batch(uint32_t type, const uint8_t* A, const float* X, f
 cudaError_t launch_moe_dmmv_batched(uint32_t type, const uint8_t* A, const float* X, float* Y,
                                     const uint32_t* routing, uint32_t M, uint32_t K, uint64_t expert_stride,
                                     uint32_t n_experts_used, uint32_t n_tokens, uint32_t x_token_stride,
-                                    uint32_t y_token_stride, cudaStream_t s, uint64_t* launches);
+                                    uint32_t y_token_stride, uint32_t n_experts_max, uint32_t* status, cudaStream_t s,
+                                    uint64_t* launches);
 
 // Grouped-by-expert tensor-core form of the cross-token MoE matmul (moe_gemm_tc.cu): Q4_K / Q6_K, bf16
 // operands, needs a device workspace of moe_grouped_workspace_bytes(n_tokens * n_used, K, n_experts).
@@ -123,6 +143,17 @@ cudaError_t launch_moe_weighted_acc(float* a, const float* b, const uint32_t* ro
                                     uint32_t src_stride, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_swiglu(const float* gate, const float* up, float* y, uint32_t n, bool oai, cudaStream_t s,
                           uint64_t* launches);
+// out[i] += bias[src_offset + i]
+cudaError_t launch_bias_add(float* out, const float* bias, uint32_t n, uint32_t src_offset, cudaStream_t s,
+                            uint64_t* launches);
+// y[s][i] = act(gate[s][i] + gate_bias[e_s][i], up[s][i] + up_bias[e_s][i]), e_s = routing[s]; biases may be null
+cudaError_t launch_moe_bias_act(const float* gate, const float* up, const float* gate_bias, const float* up_bias,
+                                const uint32_t* routing, float* y, uint32_t M, uint32_t n_used, uint32_t n_experts,
+                                bool oai, uint32_t* status, cudaStream_t s, uint64_t* launches);
+// a[i] += sum_s w_s * bias[e_s][i], routing = [ids n_used][weights n_used]
+cudaError_t launch_moe_weighted_bias_acc(float* a, const float* bias, const uint32_t* routing, uint32_t n,
+                                         uint32_t n_used, uint32_t n_experts, uint32_t* status, cudaStream_t s,
+                                         uint64_t* launches);
 // y[m] = sum_k W[m][k] * xn[k], xn = norm_w * (x * rsqrt(mean(x^2) + eps)) (also written to norm_out when
 // given); norm_w == nullptr: xn = x. One CTA per row: for matrices with few rows (routers). K % 4 == 0.
 cudaError_t launch_rms_norm_dmmv_f32(const float* x, const float* norm_w, const float* W, float* norm_out, float* y,
@@ -151,6 +182,7 @@ struct CommArgs {
     uint8_t* peers[kCommMaxRanks];  // receive buffer of every rank as mapped in this process; [rank] is local
     uint32_t rank = 0, world = 0;
     uint32_t* status = nullptr;
+    uint32_t spin_limit = 1u << 24;  // polls after which a wait for a peer's flag gives up
 };
 // buf[0..n) <- sum over ranks, in place; n a multiple of 4, n * 4 <= kCommSlotBytes
 cudaError_t launch_allreduce_oneshot(const CommArgs& c, float* buf, uint32_t n, cudaStream_t s, uint64_t* launches);

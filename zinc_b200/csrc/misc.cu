@@ -264,6 +264,46 @@ __global__ void swiglu4_kernel(const float* __restrict__ gate, const float* __re
                                                   swiglu_one<OAI>(g.z, u.z), swiglu_one<OAI>(g.w, u.w));
 }
 
+// ---- per-expert biases (GPT-OSS) ------------------------------------------------------------
+// src/shaders/bias_add.comp:19-23: out[i] += bias[src_offset + i]
+__global__ void bias_add_kernel(float* __restrict__ out, const float* __restrict__ bias, uint32_t n,
+                                uint32_t src_offset) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] += bias[(size_t)src_offset + i];
+}
+
+// The reference adds ffn_gate_exps_bias / ffn_up_exps_bias to an expert's gate and up vectors and then applies
+// the activation, expert by expert (src/compute/forward.zig:6841-6860). Here for all selected slots at once, the
+// expert of a slot read from the routing buffer: y[s][i] = act(gate[s][i] + gb[e_s][i], up[s][i] + ub[e_s][i]).
+template <bool OAI>
+__global__ void moe_bias_act_kernel(const float* __restrict__ gate, const float* __restrict__ up,
+                                    const float* __restrict__ gate_bias, const float* __restrict__ up_bias,
+                                    const uint32_t* __restrict__ routing, float* __restrict__ y, uint32_t M,
+                                    uint32_t n_experts, uint32_t* status) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
+    if (i >= M) return;
+    const uint32_t e = checked_expert(__ldg(routing + s), n_experts, status);
+    const size_t o = (size_t)s * M + i, b = (size_t)e * M + i;
+    const float g = gate[o] + (gate_bias ? gate_bias[b] : 0.f);
+    const float u = up[o] + (up_bias ? up_bias[b] : 0.f);
+    y[o] = swiglu_one<OAI>(g, u);
+}
+
+// The down projection's bias enters the weighted sum of the experts' outputs
+// (src/compute/forward.zig:6923-6927 followed by the scale-accumulate): a[i] += sum_s w_s * bias[e_s][i].
+__global__ void moe_weighted_bias_acc_kernel(float* __restrict__ a, const float* __restrict__ bias,
+                                             const uint32_t* __restrict__ routing, uint32_t n, uint32_t n_used,
+                                             uint32_t n_experts, uint32_t* status) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float sum = 0.f;
+    for (uint32_t s = 0; s < n_used; ++s) {
+        const uint32_t e = checked_expert(__ldg(routing + s), n_experts, status);
+        sum = fmaf(__uint_as_float(__ldg(routing + n_used + s)), bias[(size_t)e * n + i], sum);
+    }
+    a[i] += sum;
+}
+
 // ---- fused RMS norm + f32 router matvec -------------------------------------------------
 // src/shaders/rms_norm_dmmv_f32.comp:68-127: every CTA recomputes rms_inv = rsqrt(mean(x^2) + eps) (same
 // reads in the same order everywhere), CTA 0 also writes the normalised vector
@@ -450,6 +490,32 @@ cudaError_t launch_swiglu(const float* gate, const float* up, float* y, uint32_t
         else swiglu4_kernel<false><<<(n4 + 255) / 256, 256, 0, s>>>(gate, up, y, n4);
     } else if (oai) swiglu_kernel<true><<<(n + 255) / 256, 256, 0, s>>>(gate, up, y, n);
     else swiglu_kernel<false><<<(n + 255) / 256, 256, 0, s>>>(gate, up, y, n);
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_bias_add(float* out, const float* bias, uint32_t n, uint32_t src_offset, cudaStream_t s,
+                            uint64_t* launches) {
+    if (n == 0) return cudaSuccess;
+    bias_add_kernel<<<(n + 255) / 256, 256, 0, s>>>(out, bias, n, src_offset);
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_bias_act(const float* gate, const float* up, const float* gate_bias, const float* up_bias,
+                                const uint32_t* routing, float* y, uint32_t M, uint32_t n_used, uint32_t n_experts,
+                                bool oai, uint32_t* status, cudaStream_t s, uint64_t* launches) {
+    const dim3 grid((M + 255) / 256, n_used);
+    if (oai) moe_bias_act_kernel<true><<<grid, 256, 0, s>>>(gate, up, gate_bias, up_bias, routing, y, M, n_experts, status);
+    else moe_bias_act_kernel<false><<<grid, 256, 0, s>>>(gate, up, gate_bias, up_bias, routing, y, M, n_experts, status);
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_weighted_bias_acc(float* a, const float* bias, const uint32_t* routing, uint32_t n,
+                                         uint32_t n_used, uint32_t n_experts, uint32_t* status, cudaStream_t s,
+                                         uint64_t* launches) {
+    moe_weighted_bias_acc_kernel<<<(n + 255) / 256, 256, 0, s>>>(a, bias, routing, n, n_used, n_experts, status);
     if (launches) ++*launches;
     return cudaGetLastError();
 }

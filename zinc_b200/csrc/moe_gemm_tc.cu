@@ -362,7 +362,8 @@ moe_gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const MoeGemmArgs
 // One CTA. Shared: cnt[n_experts], seg[n_experts] (first list slot, then the running cursor), tstart[n_experts].
 __global__ void __launch_bounds__(1024, 1)
 moe_group_kernel(const uint32_t* __restrict__ routing, uint32_t n_pairs, uint32_t n_experts, uint32_t bn,
-                 uint32_t* __restrict__ header, uint4* __restrict__ tiles, uint32_t* __restrict__ list) {
+                 uint32_t* __restrict__ header, uint4* __restrict__ tiles, uint32_t* __restrict__ list,
+                 uint32_t* __restrict__ status) {
     extern __shared__ uint32_t sh[];
     uint32_t* cnt = sh;
     uint32_t* seg = sh + n_experts;
@@ -372,7 +373,12 @@ moe_group_kernel(const uint32_t* __restrict__ routing, uint32_t n_pairs, uint32_
     __syncthreads();
     for (uint32_t p = tid; p < n_pairs; p += nt) {
         const uint32_t e = routing[p];
-        if (e < n_experts) atomicAdd(&cnt[e], 1u);
+        if (e < n_experts) {
+            atomicAdd(&cnt[e], 1u);
+        } else if (status) {  // not an expert: the pair is left out (its output row stays untouched) and reported
+            status[0] = 2u;
+            status[1] = e;
+        }
     }
     __syncthreads();
     if (tid < 32) {  // exclusive scan of the pair and tile counts: a chunk of experts per lane
@@ -458,13 +464,8 @@ WsLayout ws_layout(uint64_t n_pairs, uint32_t K, uint32_t n_experts, uint32_t bn
 template <int TYPE, int BN>
 cudaError_t launch_gemm(const CUtensorMap& map, const MoeGemmArgs& g, uint32_t max_items, cudaStream_t s) {
     auto kern = moe_gemm_tc_kernel<TYPE, BN>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)MoeTile<TYPE, BN>::kSmemBytes);
-        if (e != cudaSuccess) return e;
-        attr_set = true;
-    }
+    static std::atomic<uint64_t> attr_done{0};  // per device ordinal
+    if (cudaError_t ea = ensure_dynamic_smem(kern, (int)MoeTile<TYPE, BN>::kSmemBytes, attr_done); ea != cudaSuccess) return ea;
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -509,7 +510,7 @@ cudaError_t launch_moe_grouped(uint32_t type, const uint8_t* A, uint64_t a_bytes
     __nv_bfloat16* xp = reinterpret_cast<__nv_bfloat16*>(base + l.xp);
 
     moe_group_kernel<<<1, 1024, (size_t)n_experts * 12, s>>>(routing, (uint32_t)n_pairs, n_experts, bn, header, tiles,
-                                                            list);
+                                                            list, status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return e;
     moe_gather_x_kernel<<<(uint32_t)((n_pairs + 7) / 8), 256, 0, s>>>(X, header, list, xp, K, n_used, x_token_stride);

@@ -37,8 +37,10 @@ struct WarpArgs {
     // writes rows [s * M, (s+1) * M) of y (stream 0) and y2 (stream 1). x is shared by all slots.
     const uint32_t* routing;
     uint64_t expert_stride;
+    uint32_t n_experts_max = 0xFFFFFFFFu;  // ids at or beyond it are reported through the status words
     uint32_t tiles_per_expert;
     float* y2;
+    uint32_t spin_limit = 1u << 26;  // polls after which a split-K wait gives up (status {1, site})
     uint32_t x_slot_stride;  // MoE down projection: elements between the slots' activation vectors
     uint32_t act = 0;        // EPI_PAIR only: 0 write both streams, 1 y = silu(gate) * up, 2 the GPT-OSS form
 };
@@ -126,8 +128,6 @@ __device__ __forceinline__ void write_row(const WarpArgs& a, uint32_t row, const
 }
 
 
-constexpr uint32_t kSpinLimit = 1u << 26;
-
 // Ends a tile for this warp. v[i][r]: sums of stream i for rows g (r = 0) and g+8 (r = 1), already
 // reduced over the four lanes of a row.
 template <int NS, int EPI, int kWarps>
@@ -172,7 +172,7 @@ __device__ __forceinline__ void finish_tile(const WarpArgs& a, float* spartial, 
             uint32_t spins = 0;
             while (!__all_sync(0xFFFFFFFFu, ready)) {
                 if (!ready) ready = *flag != 0u;
-                if (++spins > kSpinLimit) {
+                if (++spins > a.spin_limit) {
                     if (lane == 0) { a.status[0] = 1; a.status[1] = 3; }
                     break;
                 }

@@ -94,18 +94,39 @@ class DecodeStep:
             raise ValueError("K shards of O / down must stay multiples of the 256-element super-block")
         dev = f"cuda:{torch.cuda.current_device()}"
         st = DecodeStep(shape=s, dd=dd, rank=rank, world=g, allreduce=allreduce, allgather=allgather)
-        base = seed * 100003 + rank * 1009
+        base = seed * 100003
+
+        # Every rank generates the same full tensor (the seed does not depend on the rank: the "file" all
+        # ranks read) and keeps its shard, cut by the rules of zinc_b200.shard: rows are a contiguous byte
+        # range, a K shard is re-laid out as its own dense [M][K / world] tensor.
+        def rows(t, M, K, sd):
+            w = synth.torch_quant_matrix(t, M, K, dev, sd)
+            if g == 1:
+                return w
+            n = M // g
+            return w.view(M, -1)[rank * n:(rank + 1) * n].contiguous().view(-1)
+
+        def kcut(t, M, K, sd):
+            w = synth.torch_quant_matrix(t, M, K, dev, sd)
+            if g == 1:
+                return w
+            bs, bpb = synth.BLOCK[t]
+            nb = K // bs // g
+            return w.view(M, K // bs, bpb)[:, rank * nb:(rank + 1) * nb, :].contiguous().view(-1)
+
         for layer in range(s.n_layers):
             sd = base + layer * 16
             st.layers.append(LayerWeights(
-                wq=synth.torch_quant_matrix(s.t_attn, s.q_dim // g, s.hidden, dev, sd + 0),
-                wk=synth.torch_quant_matrix(s.t_attn, s.kv_dim // g, s.hidden, dev, sd + 1),
-                wv=synth.torch_quant_matrix(s.t_attn, s.kv_dim // g, s.hidden, dev, sd + 2),
-                wo=synth.torch_quant_matrix(s.t_attn, s.hidden, s.q_dim // g, dev, sd + 3),
-                wgate=synth.torch_quant_matrix(s.t_gate_up, s.ffn // g, s.hidden, dev, sd + 4),
-                wup=synth.torch_quant_matrix(s.t_gate_up, s.ffn // g, s.hidden, dev, sd + 5),
-                wdown=synth.torch_quant_matrix(s.t_down, s.hidden, s.ffn // g, dev, sd + 6)))
-        st.head = synth.torch_quant_matrix(s.t_head, s.vocab // g, s.hidden, dev, base + 99991)
+                wq=rows(s.t_attn, s.q_dim, s.hidden, sd + 0),
+                wk=rows(s.t_attn, s.kv_dim, s.hidden, sd + 1),
+                wv=rows(s.t_attn, s.kv_dim, s.hidden, sd + 2),
+                wo=kcut(s.t_attn, s.hidden, s.q_dim, sd + 3),
+                wgate=rows(s.t_gate_up, s.ffn, s.hidden, sd + 4),
+                wup=rows(s.t_gate_up, s.ffn, s.hidden, sd + 5),
+                wdown=kcut(s.t_down, s.hidden, s.ffn, sd + 6)))
+        st.head = rows(s.t_head, s.vocab, s.hidden, base + 99991)
+        if g > 1:
+            torch.cuda.empty_cache()
         f32 = dict(dtype=torch.float32, device=dev)
         st.x_norm = torch.zeros(s.hidden, **f32)
         st.attn_out = torch.zeros(s.q_dim // g, **f32)

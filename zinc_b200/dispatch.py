@@ -189,6 +189,19 @@ class Context:
         a, b = _buf(src), _buf(dst)
         self.call("zc_allgather_f32", a.ptr, a.size, src_offset, b.ptr, b.size, dst_offset, n)
 
+    def comm_connect_local(self, rank: int, receive_buffer) -> None:
+        """Lend the receive buffer of a rank that lives in this process (a device pointer, no IPC handle)."""
+        b = _buf(receive_buffer)
+        self.call("zc_comm_connect_local", rank, b.ptr, b.size)
+
+    @staticmethod
+    def comm_buffer_bytes() -> int:
+        return int(_lib.lib().zc_comm_buffer_bytes())
+
+    def set_wait_limit(self, polls: int) -> None:
+        """Polls after which a device-side wait gives up (0 = defaults); see zc_set_wait_limit."""
+        self.call("zc_set_wait_limit", polls)
+
     def comm_destroy(self) -> None:
         self.call("zc_comm_destroy")
 
@@ -389,6 +402,25 @@ class DmmvDispatch:
         if gate.size < need or up.size < need or y.size < need:
             raise InvalidArgument("dispatchSwiglu: buffer smaller than n floats")
         self.ctx.call("zc_swiglu_oai" if oai else "zc_swiglu", gate.ptr, up.ptr, y.ptr, n)
+
+    # dispatchBiasAddSlice (forward.zig:3875-3913): out[i] += bias[element_offset + i]
+    def dispatchBiasAddSlice(self, out, bias, element_offset, n_elements):
+        out, bias = _buf(out), _buf(bias)
+        self.ctx.call("zc_bias_add", out.ptr, out.size, bias.ptr, bias.size, n_elements, element_offset)
+
+    # per-expert gate / up biases + activation for all selected slots (forward.zig:6841-6860)
+    def dispatchMoeBiasAct(self, gate, up, gate_bias, up_bias, routing, y, M, n_used, n_experts, oai=False):
+        gate, up, routing, y = map(_buf, (gate, up, routing, y))
+        gb = _buf(gate_bias) if gate_bias is not None else Buffer(None, 0)
+        ub = _buf(up_bias) if up_bias is not None else Buffer(None, 0)
+        self.ctx.call("zc_moe_bias_act", gate.ptr, gate.size, up.ptr, up.size, gb.ptr, gb.size, ub.ptr, ub.size,
+                      routing.ptr, routing.size, y.ptr, y.size, M, n_used, n_experts, 1 if oai else 0)
+
+    # per-expert down bias inside the weighted sum (forward.zig:6923-6927)
+    def dispatchMoeWeightedBiasAcc(self, a, bias, routing, n, n_used, n_experts):
+        a, bias, routing = map(_buf, (a, bias, routing))
+        self.ctx.call("zc_moe_weighted_bias_acc", a.ptr, a.size, bias.ptr, bias.size, routing.ptr, routing.size,
+                      n, n_used, n_experts)
 
     # grouped-by-expert prefill helpers (src/shaders/metal/moe_route_pack.metal, moe_route_scatter.metal)
     def dispatchMoeRoutePack(self, routing, counts, ids, n_tokens, n_experts, k, routing_stride, ids_stride):

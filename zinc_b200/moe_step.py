@@ -5,9 +5,11 @@ down Q6_K, GPU-side routing with softmax over all experts then renormalisation. 
 reference's GPU-routed MoE layer (src/compute/forward.zig:6139-6545): router DMMV, softmax_topk,
 fused gate+up expert DMMV, SwiGLU, fused down + weighted accumulate, then the shared expert.
 
-`GptOssMoeLayer`: hidden 2880, 32 experts top-4, expert FFN 2880, MXFP4 gate / up / down, routing by
-top-k then softmax, `swiglu_oai` (src/compute/forward.zig:6712-6930; biases are not part of the
-matmul path and are left out).
+`GptOssMoeLayer`: hidden 2880, 32 experts top-4, expert FFN 2880, MXFP4 gate / up / down, router bias
+added to the logits, routing by top-k then softmax, per-expert gate / up biases before `swiglu_oai` and a
+per-expert down bias inside the weighted sum (src/compute/forward.zig:6712-6930: bias on the router logits
+6752-6754, `ffn_gate_exps_bias` / `ffn_up_exps_bias` 6841-6849, `ffn_down_exps_bias` 6923-6927). The
+reference walks the selected experts one by one; here every step handles all selected slots in one launch.
 
 Attention, norms and the residual stream are stood in for by fixed N(0,1) vectors, as in the dense
 decode step.
@@ -40,6 +42,7 @@ class MoeShape:
     shared: bool
     oai: bool
     n_layers: int
+    biases: bool = False   # router bias + per-expert gate / up / down biases (GPT-OSS)
 
     def expert_bytes(self) -> int:
         return 2 * self.ffn * row_bytes(self.t_gate_up, self.hidden) + self.hidden * row_bytes(self.t_down, self.ffn)
@@ -55,7 +58,7 @@ class MoeShape:
 QWEN35_MOE = MoeShape(hidden=2048, n_experts=256, top_k=8, ffn=512, t_gate_up=Q4_K, t_down=Q6_K,
                       rule=ROUTE_SOFTMAX_ALL_RENORM, shared=True, oai=False, n_layers=40)
 GPT_OSS_MOE = MoeShape(hidden=2880, n_experts=32, top_k=4, ffn=2880, t_gate_up=MXFP4, t_down=MXFP4,
-                       rule=ROUTE_TOPK_THEN_SOFTMAX, shared=False, oai=True, n_layers=24)
+                       rule=ROUTE_TOPK_THEN_SOFTMAX, shared=False, oai=True, n_layers=24, biases=True)
 
 
 def ffn_split(ffn: int, block: int, world: int):
@@ -95,6 +98,10 @@ class MoeLayerWeights:
     sg: object = None
     su: object = None
     sd: object = None
+    router_bias: object = None   # [n_experts] f32
+    bg: object = None            # [n_experts][ffn_local] f32
+    bu: object = None
+    bd: object = None            # [n_experts][hidden] f32 (rank 0 adds it in a tensor-parallel step)
 
 
 @dataclass
@@ -112,6 +119,8 @@ class MoeDecode:
     sact: object = None
     ffn_local: int = 0
     world: int = 1
+    rank: int = 0
+    parallel: str = "tp"       # how world > 1 ranks share the experts: "tp" (FFN dimension cut) or "ep" (whole experts)
     allreduce: object = None   # callable(tensor): in-place sum over the ranks
     partial: object = None
     one: object = None
@@ -121,10 +130,12 @@ class MoeDecode:
 
     @staticmethod
     def build(torch, dd: DmmvDispatch, shape: MoeShape, seed: int = 3, rank: int = 0, world: int = 1,
-              allreduce=None) -> "MoeDecode":
+              allreduce=None, parallel: str = "tp") -> "MoeDecode":
         s = shape
+        if parallel != "tp":
+            parallel = "tp"
         dev = f"cuda:{torch.cuda.current_device()}"
-        st = MoeDecode(shape=s, dd=dd, world=world, allreduce=allreduce)
+        st = MoeDecode(shape=s, dd=dd, world=world, rank=rank, allreduce=allreduce)
         lo, hi = ffn_split(s.ffn, synth.BLOCK[s.t_down][0], world)[rank]
         st.ffn_local = hi - lo
         rb_h = row_bytes(s.t_gate_up, s.hidden)
@@ -140,6 +151,11 @@ class MoeDecode:
                 w.sg = synth.torch_quant_matrix(s.t_gate_up, s.ffn, s.hidden, dev, sd + 3)
                 w.su = synth.torch_quant_matrix(s.t_gate_up, s.ffn, s.hidden, dev, sd + 4)
                 w.sd = synth.torch_quant_matrix(s.t_down, s.hidden, s.ffn, dev, sd + 5)
+            if s.biases:
+                w.router_bias = torch.randn(s.n_experts, device=dev, generator=gen) * 0.5
+                w.bg = torch.randn(s.n_experts, s.ffn, device=dev, generator=gen)[:, lo:hi].contiguous().view(-1)
+                w.bu = torch.randn(s.n_experts, s.ffn, device=dev, generator=gen)[:, lo:hi].contiguous().view(-1)
+                w.bd = torch.randn(s.n_experts * s.hidden, device=dev, generator=gen)
             if world > 1:  # every rank generates the same full tensors and keeps its slice
                 w.wg = shard_expert_rows(torch, w.wg, s.n_experts, s.ffn, rb_h, lo, hi)
                 w.wu = shard_expert_rows(torch, w.wu, s.n_experts, s.ffn, rb_h, lo, hi)
@@ -176,18 +192,24 @@ class MoeDecode:
         tp = self.world > 1
         for w in self.layers:
             dd.recordDispatch(F32, w.router, self.x, self.logits, s.n_experts, s.hidden)
-            dd.dispatchSoftmaxTopk(self.logits, self.routing, s.n_experts, s.top_k, rule=s.rule)
-            if self.fuse_act:
+            dd.dispatchSoftmaxTopk(self.logits, self.routing, s.n_experts, s.top_k, rule=s.rule, bias=w.router_bias)
+            if self.fuse_act and not s.biases:
                 dd.dispatchMoeFusedGateUpAct(s.t_gate_up, w.wg, w.wu, self.x, self.act, self.routing, f, s.hidden,
                                              es_gu, s.top_k, 0, oai=s.oai)
             else:
                 dd.dispatchMoeFusedGateUp(s.t_gate_up, w.wg, w.wu, self.x, self.yg, self.yu, self.routing, f,
                                           s.hidden, es_gu, s.top_k, 0)
-                dd.dispatchSwiglu(self.yg, self.yu, self.act, s.top_k * f, oai=s.oai)
+                if s.biases:
+                    dd.dispatchMoeBiasAct(self.yg, self.yu, w.bg, w.bu, self.routing, self.act, f, s.top_k,
+                                          s.n_experts, oai=s.oai)
+                else:
+                    dd.dispatchSwiglu(self.yg, self.yu, self.act, s.top_k * f, oai=s.oai)
             acc = self.partial if tp else self.hidden
             if tp:
                 dd.ctx.memset(_as_buffer(self.partial), 0)
             dd.dispatchMoeFusedDownAcc(s.t_down, w.wd, self.act, acc, self.routing, s.hidden, f, es_d, s.top_k, f)
+            if s.biases and self.rank == 0:
+                dd.dispatchMoeWeightedBiasAcc(acc, w.bd, self.routing, s.hidden, s.top_k, s.n_experts)
             if s.shared:
                 dd.dispatchDmmvFusedGateUpSwiglu(s.t_gate_up, w.sg, w.su, self.x, self.sact, f, s.hidden)
                 dd.recordDispatch(s.t_down, w.sd, self.sact, acc, s.hidden, f, acc_mode=1)
