@@ -421,8 +421,8 @@ int32_t zc_comm_destroy(zc_ctx* ctx);
 /* ---- matvec without a context and without any allocation ----------------------------------------
  * No counterpart in the reference (its dispatch layer always owns descriptor pools and buffers).
  * The streaming Q4_K matvec of zc_dmmv, y (+)= W x, with its split-K scratch in a __device__
- * array that is part of the library image (540672 bytes: 4096 worker warps x 32 partial sums
- * plus one flag word each) instead of scratch a context allocated. For hosts that cannot let
+ * array that is part of the library image (1048576 bytes: 4096 worker warps x 32 partial sums,
+ * each stored with a tag word) instead of scratch a context allocated. For hosts that cannot let
  * the library allocate: all device memory already belongs to the host's own arena, or an
  * allocation would synchronise the device in the middle of its decode loop. Neither this call
  * nor its set-up allocates memory of any kind.
@@ -436,8 +436,8 @@ int32_t zc_comm_destroy(zc_ctx* ctx);
  * the call; a bounded wait that gave up stores {1, site} there, the result is then invalid and
  * the entry point must not be used again on that device.
  *
- * The first call on each device does the set-up (symbol address, SM count; the flag words are
- * zero when the library is loaded and every launch leaves them zero): make it before any stream
+ * The first call on each device does the set-up (symbol address, SM count; the array is all
+ * zero when the library is loaded and every launch leaves it zero): make it before any stream
  * capture starts on that device.
  * The scratch is shared by all calls on a device: calls ordered on one stream are safe; calls
  * whose kernels may overlap (different streams, unordered threads) race and give wrong results. */

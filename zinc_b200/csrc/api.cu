@@ -25,8 +25,7 @@ struct zc_ctx {
     uint64_t launches = 0;
     uint32_t* status_host = nullptr;  // pinned, mapped: deferred device-side status words
     uint32_t* status_dev = nullptr;
-    float* scratch_partial = nullptr;     // split-K partial sums of the streaming matvec
-    uint32_t* scratch_flags = nullptr; // publication flags (zero between launches)
+    uint2* scratch_partial = nullptr;  // split-K partial sums of the streaming matvecs, tagged (zero between launches)
     int sm_count = 0;
     // tensor-parallel peer exchange (zc_comm_*)
     zc::CommArgs comm;
@@ -131,7 +130,6 @@ inline float* f32m(void* p, uint64_t off) { return reinterpret_cast<float*>(stat
 
 inline void attach_scratch(zc_ctx* ctx, DmmvArgs& a) {
     a.scratch_partial = ctx->scratch_partial;
-    a.scratch_flags = ctx->scratch_flags;
     a.status = ctx->status_dev;
     if (ctx->wait_limit) a.spin_limit = ctx->wait_limit;
     a.sm_count = ctx->sm_count;
@@ -192,10 +190,8 @@ int32_t zc_init(int32_t device, zc_ctx** out_ctx) {
     memset(ctx->status_host, 0, 256);
     ctx->sm_count = prop.multiProcessorCount;
     if (cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_partial), kStreamPartialBytes) != cudaSuccess ||
-        cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_flags), kStreamFlagBytes) != cudaSuccess ||
-        cudaMemset(ctx->scratch_flags, 0, kStreamFlagBytes) != cudaSuccess) {
+        cudaMemset(ctx->scratch_partial, 0, kStreamPartialBytes) != cudaSuccess) {
         if (ctx->scratch_partial) cudaFree(ctx->scratch_partial);
-        if (ctx->scratch_flags) cudaFree(ctx->scratch_flags);
         cudaFreeHost(ctx->status_host);
         cudaStreamDestroy(ctx->own_stream);
         delete ctx;
@@ -212,7 +208,6 @@ int32_t zc_destroy(zc_ctx* ctx) {
     zc_comm_destroy(ctx);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
     if (ctx->scratch_partial) cudaFree(ctx->scratch_partial);
-    if (ctx->scratch_flags) cudaFree(ctx->scratch_flags);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
     return ZC_OK;
@@ -409,10 +404,10 @@ int32_t zc_submit_and_wait(zc_ctx* ctx) {
             return fail(ctx, ZC_ERR_INVALID_ARG,
                         "a routing buffer named expert %u, which the weight buffer does not hold; the results of that "
                         "call are invalid", where);
-        // A wait gave up. Split-K publication flags may be left set and would be taken for fresh partial sums
-        // by the next streaming matvec: clear them. A peer exchange that gave up leaves the ranks' epochs out
+        // A wait gave up. Tagged partial sums may be left behind and would be taken for fresh ones by the next
+        // streaming matvec: clear them. A peer exchange that gave up leaves the ranks' epochs out
         // of step: the communicator refuses further collectives until it is destroyed and set up again.
-        cudaMemsetAsync(ctx->scratch_flags, 0, kStreamFlagBytes, ctx->stream);
+        cudaMemsetAsync(ctx->scratch_partial, 0, kStreamPartialBytes, ctx->stream);
         cudaStreamSynchronize(ctx->stream);
         if (where >= 200 && ctx->comm_local) ctx->comm_broken = true;
         return fail(ctx, ZC_ERR_TIMEOUT, "device-side wait gave up (code %u, site %u)", code, where);

@@ -424,7 +424,7 @@ cudaError_t launch_cfg_x(const WarpArgs& a, const uint8_t* a_end, const uint8_t*
 }
 
 bool common_ok(const DmmvArgs& a) {
-    if (!a.scratch_partial || !a.scratch_flags || !a.status || !a.a_end) return false;
+    if (!a.scratch_partial || !a.status || !a.a_end) return false;
     // rows are fetched as 16-byte-aligned supersets: the buffers themselves must start on that boundary
     if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (a.A2 && (reinterpret_cast<uintptr_t>(a.A2) & 15u))) return false;
     if ((a.K & 31u) || a.K == 0) return false;
@@ -468,7 +468,6 @@ static void fill_common(WarpArgs& wa, const DmmvArgs& a) {
     wa.K = a.K;
     wa.acc_mode = a.acc_mode;
     wa.gpartial = a.scratch_partial;
-    wa.gflags = a.scratch_flags;
     wa.status = a.status;
     wa.spin_limit = a.spin_limit;
     wa.nseg = 0;

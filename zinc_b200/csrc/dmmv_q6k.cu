@@ -8,18 +8,21 @@
 // 210-byte blocks ql[128] qh[64] scales[16] (int8) d (f16), 16-weight sub-blocks.
 //
 // Arithmetic per super-block of a row:  y += 2^-f * d * sum_s sc_s * P_s,
-//   P_s = sum_{i in s} (v_i - 32) * X_i = D_s - 32 * SX_s,   D_s = sum_i v_i * X_i
-// v_i = 6-bit quant 0..63 fed to the tensor core as u8, X_i = round(x_i * 2^f) the block of x in
-// 21-bit fixed point split into three 7-bit digits (s8), SX_s = sum_i X_i. D_s, SX_s and P_s are
-// exact integers; the only rounding before the f32 scaling is that of x to 21 bits.
+//   P_s = sum_{i in s} (v_i - 32) * X_i = sum_j 2^(14-7j) (D_j,s - 32 * SB_j,s),   D_j,s = sum_i v_i * b_j,i
+// v_i = 6-bit quant 0..63 fed to the tensor core as u8, X_i = round(x_i * 2^f) the block of x in 21-bit fixed
+// point, b_j,i its three digits (s8), SB_j,s = sum_i b_j,i. The MMA accumulators start at -32 * SB_j,s, the
+// int8 scales are applied in integer arithmetic (sum_s sc_s * (..) < 2^31), so one conversion and one f32
+// multiply-add per row, digit and super-block remain; the only rounding before that is x to 21 bits.
 //
-// Blocks are only 2-byte aligned (210 = 13*16 + 2), so a unit is copied as the 16-byte aligned
-// superset of each row's block and read back with aligned 32-bit loads + a funnel shift whose
-// amount is the same for the whole warp. Rows must start 16-byte aligned (K a multiple of 2048).
-//
-// Lane (g = lane/4, t = lane%4) owns, for rows g and g+8, the 32 ql bytes 64h + 32c .. (h = t/2,
-// c = t%2) and the 32 qh bytes of half h: low nibbles are elements 128h + 32c + l, high nibbles
-// 128h + 64 + 32c + l, i.e. four 16-weight sub-blocks. B is block-diagonal as in the Q4_K kernel.
+// Blocks are only 2-byte aligned (210 = 13*16 + 2), so a unit is copied as the 16-byte aligned superset of
+// each row's block into a 240-byte row slot and read back with 32-bit loads: lane (g = lane/4, t = lane%4)
+// reads word t of every 16-byte group of rows g and g+8 (bank = 4 * (15 g mod 8) + t + const: conflict-free),
+// one load when the block starts on a word boundary inside its slot, two and a funnel shift otherwise.
+// That is the native A fragment of mma.sync m16n8k32 (bytes 4t .. 4t+3 and 16 + 4t .. of a 32-byte group):
+// an MMA covers the 32 elements 128h + 32j .. of half h, quarter j, i.e. sub-blocks 8h + 2j (k slots 0..15)
+// and 8h + 2j + 1 (k slots 16..31). B is block-diagonal to match: column 2d + u holds digit d of x in the k
+// slots of sub-block half u and zeros in the other half, so D column 2d + u is digit d's dot product with
+// sub-block u alone; lane t < 3 ends up with digit t of both sub-blocks for rows g and g+8.
 #include "kernels.h"
 #include "stream_skel.cuh"
 
@@ -33,24 +36,25 @@ constexpr int kSlot6 = 16 * kRow6;
 constexpr int kRing6 = kDepth * kSlot6;
 constexpr int kPieces6 = 14;                // 16-byte pieces per row superset
 constexpr int kPiecesLane6 = (16 * kPieces6 + 31) / 32;  // 7
-constexpr int kZeroUnits = 72;
+constexpr int kZeroBytes6 = 128;
 constexpr int kFracBits = 20;
 constexpr int kPrepBlocks = 6;
+constexpr int kBBytes = 1536;               // B operand table per super-block: [h 2][j pair 2][column 6][t 4][16 bytes]
+constexpr int kNsxBytes = 256;              // accumulator start values per super-block: [h 2][digit 4][j 4][u 2] s32
 constexpr size_t kTwoPerSm = 113 * 1024;
 
 struct Smem6 {
-    uint4* xf;       // x digits in B-operand order: unit ((blk*8 + s*4 + i)*2 + p)*4 + t
-    uint4* zeros;
-    int* sx;         // per 16-element sub-block sum of X (exact)
+    uint8_t* zeros;  // kZeroBytes6 of zeros (B operand of the dead columns 6 and 7)
+    uint8_t* bq;     // per super-block kBBytes: {b0, b1} register pairs in B-operand order
+    int* nsx;        // per super-block kNsxBytes / 4: -32 * sum of digit d over sub-block (h, j, u)
     float* xs;       // per super-block 2^-f
     uint8_t* ring;   // [kWarps][kDepth] stages of 16 row slots
-    float* spartial;
-    volatile uint32_t* sflags;
+    float* spartial; // [kWarps][32] partial sums published inside the CTA
+    volatile uint32_t* sflags;  // [kWarps]
 };
 
 __host__ __device__ inline size_t smem_bytes6(uint32_t K, int kWarps) {
-    size_t n = (size_t)K * 4 + (size_t)kZeroUnits * 16;
-    n += (size_t)(K / 16) * 4 + (size_t)(K / 256) * 4;
+    size_t n = (size_t)kZeroBytes6 + (size_t)(K / 256) * (kBBytes + kNsxBytes + 4);
     n = (n + 127) & ~size_t(127);
     n += (size_t)kWarps * kRing6;
     n += (size_t)kWarps * 32 * 4 + (size_t)kWarps * 4 + 16;
@@ -60,12 +64,12 @@ __host__ __device__ inline size_t smem_bytes6(uint32_t K, int kWarps) {
 __device__ inline Smem6 carve6(uint8_t* base, uint32_t K, int kWarps) {
     Smem6 s;
     uintptr_t p = (reinterpret_cast<uintptr_t>(base) + 127) & ~uintptr_t(127);
-    s.xf = reinterpret_cast<uint4*>(p);
-    p += (size_t)K * 4;
-    s.zeros = reinterpret_cast<uint4*>(p);
-    p += (size_t)kZeroUnits * 16;
-    s.sx = reinterpret_cast<int*>(p);
-    p += (size_t)(K / 16) * 4;
+    s.zeros = reinterpret_cast<uint8_t*>(p);
+    p += kZeroBytes6;
+    s.bq = reinterpret_cast<uint8_t*>(p);
+    p += (size_t)(K / 256) * kBBytes;
+    s.nsx = reinterpret_cast<int*>(p);
+    p += (size_t)(K / 256) * kNsxBytes;
     s.xs = reinterpret_cast<float*>(p);
     p += (size_t)(K / 256) * 4;
     p = (p + 127) & ~uintptr_t(127);
@@ -80,11 +84,7 @@ __device__ inline Smem6 carve6(uint8_t* base, uint32_t K, int kWarps) {
 struct XRegs6 {
     float4 lo[kPrepBlocks], hi[kPrepBlocks];
 };
-// lane = i*8 + s*4 + t handles the 8 consecutive elements 128(t/2) + 64s + 32(t%2) + 8i .. +7
-__device__ __forceinline__ uint32_t x_elem6(int lane) {
-    const int i = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
-    return 128 * (t >> 1) + 64 * sh + 32 * (t & 1) + 8 * i;
-}
+// One warp per super-block; lane l handles the 8 consecutive elements 8l .. 8l+7.
 // K: length of the (concatenated) activation. bpe > 0 (MoE down projection): the activation is n_slots
 // vectors of bpe * 256 elements, x + s * x_stride, each scaled by the slot's routing weight wts[s].
 template <int kWarps>
@@ -95,7 +95,7 @@ __device__ __forceinline__ void load_x6(XRegs6& r, const float* __restrict__ x, 
         const uint32_t blk = warp + b * kWarps;
         if (blk < (K >> 8)) {
             const uint32_t slot = bpe ? blk / bpe : 0u, lb = bpe ? blk - slot * bpe : blk;
-            const float* xp = x + (size_t)slot * x_stride + (size_t)lb * 256 + x_elem6(lane);
+            const float* xp = x + (size_t)slot * x_stride + (size_t)lb * 256 + 8 * lane;
             float4 lo = __ldg(reinterpret_cast<const float4*>(xp)), hi = __ldg(reinterpret_cast<const float4*>(xp) + 1);
             if (wts) {
                 const float w = __uint_as_float(__ldg(wts + slot));
@@ -107,9 +107,16 @@ __device__ __forceinline__ void load_x6(XRegs6& r, const float* __restrict__ x, 
         }
     }
 }
+
+__device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+// Lane l's elements 8l .. 8l+7 lie in half h = l/16, quarter j = (l/4)%4, sub-block half u = (l/2)%2, and are
+// the k-slot groups t = 2(l%2) and t+1 of that sub-block half.
 template <int kWarps>
 __device__ __forceinline__ void prep_x6(const Smem6& s, const XRegs6& r, uint32_t K, int warp, int lane) {
-    const int i = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
+    const uint32_t h = lane >> 4, j = (lane >> 2) & 3, u = (lane >> 1) & 1, t0 = 2 * (lane & 1);
 #pragma unroll
     for (int b = 0; b < kPrepBlocks; ++b) {
         const uint32_t blk = warp + b * kWarps;
@@ -124,22 +131,35 @@ __device__ __forceinline__ void prep_x6(const Smem6& s, const XRegs6& r, uint32_
         uint32_t E = (__float_as_uint(mx) >> 23) & 0xFFu;
         E = E < 32u ? 32u : E;
         const float scale = __uint_as_float((127u + 126u + kFracBits - E) << 23);
-        uint32_t d0[2] = {0, 0}, d1[2] = {0, 0}, d2[2] = {0, 0};
-        int sum = 0;
+        int X[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) X[e] = __float2int_rn(v[e] * scale);
+        uint32_t dw[3][2];
+        int ds[3];
+        dw[0][0] = pack4(X[0] >> 14, X[1] >> 14, X[2] >> 14, X[3] >> 14);
+        dw[0][1] = pack4(X[4] >> 14, X[5] >> 14, X[6] >> 14, X[7] >> 14);
+        dw[1][0] = pack4(X[0] >> 7, X[1] >> 7, X[2] >> 7, X[3] >> 7) & 0x7F7F7F7Fu;
+        dw[1][1] = pack4(X[4] >> 7, X[5] >> 7, X[6] >> 7, X[7] >> 7) & 0x7F7F7F7Fu;
+        dw[2][0] = pack4(X[0], X[1], X[2], X[3]) & 0x7F7F7F7Fu;
+        dw[2][1] = pack4(X[4], X[5], X[6], X[7]) & 0x7F7F7F7Fu;
+        ds[0] = ds[1] = ds[2] = 0;
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-            const int X = __float2int_rn(v[e] * scale);
-            sum += X;
-            d0[e >> 2] |= (uint32_t)((X >> 14) & 0xFF) << (8 * (e & 3));
-            d1[e >> 2] |= (uint32_t)((X >> 7) & 0x7F) << (8 * (e & 3));
-            d2[e >> 2] |= (uint32_t)(X & 0x7F) << (8 * (e & 3));
+            ds[0] += X[e] >> 14;
+            ds[1] += (X[e] >> 7) & 0x7F;
+            ds[2] += X[e] & 0x7F;
         }
-        const uint32_t u = (blk * 8 + sh * 4 + i) * 2;
-        s.xf[(u + 0) * 4 + t] = make_uint4(d0[0], d0[1], d2[0], d2[1]);
-        s.xf[(u + 1) * 4 + t] = make_uint4(d1[0], d1[1], 0u, 0u);
-        // 16-element sub-block sums: lanes i and i^1 hold the two halves
-        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 8);
-        if ((i & 1) == 0) s.sx[blk * 16 + (x_elem6(lane) >> 4)] = sum;
+        uint8_t* bq = s.bq + (size_t)blk * kBBytes + h * 768 + (j >> 1) * 384 + (j & 1) * 8;
+#pragma unroll
+        for (int d = 0; d < 3; ++d) {
+            uint8_t* dst = bq + (2 * d + u) * 64 + t0 * 16;
+            // {b0, b1}: the digit word sits in the register that feeds the k slots of sub-block half u
+            *reinterpret_cast<uint2*>(dst) = u ? make_uint2(0u, dw[d][0]) : make_uint2(dw[d][0], 0u);
+            *reinterpret_cast<uint2*>(dst + 16) = u ? make_uint2(0u, dw[d][1]) : make_uint2(dw[d][1], 0u);
+            const int sum = ds[d] + __shfl_xor_sync(0xFFFFFFFFu, ds[d], 1);
+            if ((lane & 1) == 0) s.nsx[blk * 64 + h * 32 + d * 8 + j * 2 + u] = -32 * sum;
+        }
+        if ((lane & 1) == 0) s.nsx[blk * 64 + h * 32 + 24 + j * 2 + u] = 0;  // digit 3 does not exist: lane t = 3
         if (lane == 0) s.xs[blk] = __uint_as_float((E + 1u - kFracBits) << 23);
     }
 }
@@ -149,16 +169,77 @@ __device__ __forceinline__ uint32_t lds_u32s(uint32_t saddr) {
     asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(saddr));
     return v;
 }
+__device__ __forceinline__ uint32_t lds_u16s(uint32_t saddr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(saddr));
+    return v;
+}
 
-// N consecutive 32-bit words starting `sh` bits into the aligned word at shared address saddr (sh = 0 or 16)
-template <int N>
-__device__ __forceinline__ void lds_words(uint32_t saddr, uint32_t sh, uint32_t (&w)[N]) {
-    uint32_t prev = lds_u32s(saddr);
+// The 32-bit word at byte address saddr (2-byte aligned): one load when kFunnel is false (saddr is a multiple
+// of 4), else the two words around it and a funnel shift by sh = 8 * (saddr % 4).
+template <bool kFunnel>
+__device__ __forceinline__ uint32_t lds_word(uint32_t saddr, uint32_t sh) {
+    if constexpr (kFunnel) {
+        const uint32_t base = saddr & ~3u;
+        return __funnelshift_r(lds_u32s(base), lds_u32s(base + 4), sh);
+    } else {
+        return lds_u32s(saddr);
+    }
+}
+
+// sign-extended byte n of w
+template <int n>
+__device__ __forceinline__ int sbyte(uint32_t w) {
+    int r;  // prmt: selector nibble n takes byte n, 8 | n replicates that byte's sign bit
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0u), "n"(n | ((8 | n) << 4) | ((8 | n) << 8) | ((8 | n) << 12)));
+    return r;
+}
+
+// One super-block of rows g (at slot address rA) and g+8 (rB) against the B table at xb / accumulator start
+// values at nb; returns sum_s sc_s * (D_t,s - 32 SB_t,s) for digit t = lane % 4 and both rows.
+template <bool kFunnel>
+__device__ __forceinline__ void block6(uint32_t rA, uint32_t rB, uint32_t shA, uint32_t shB, uint32_t xb, uint32_t xh,
+                                       uint32_t nb, int t, int& IA, int& IB) {
+    constexpr uint32_t kNib = 0x0F0F0F0Fu, kTop = 0x30303030u;
+    IA = IB = 0;
 #pragma unroll
-    for (int i = 0; i < N; ++i) {
-        const uint32_t next = lds_u32s(saddr + 4 * (i + 1));
-        w[i] = __funnelshift_r(prev, next, sh);
-        prev = next;
+    for (int h = 0; h < 2; ++h) {
+        uint32_t vA[4][2], vB[4][2];  // [quarter j][sub-block half m]
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+            const uint32_t o = 16 * m + 4 * t;
+            const uint32_t la0 = lds_word<kFunnel>(rA + 64 * h + o, shA), la1 = lds_word<kFunnel>(rA + 64 * h + 32 + o, shA);
+            const uint32_t ha = lds_word<kFunnel>(rA + 128 + 32 * h + o, shA);
+            const uint32_t lb0 = lds_word<kFunnel>(rB + 64 * h + o, shB), lb1 = lds_word<kFunnel>(rB + 64 * h + 32 + o, shB);
+            const uint32_t hb = lds_word<kFunnel>(rB + 128 + 32 * h + o, shB);
+            vA[0][m] = (la0 & kNib) | ((ha << 4) & kTop);
+            vA[1][m] = (la1 & kNib) | ((ha << 2) & kTop);
+            vA[2][m] = ((la0 >> 4) & kNib) | (ha & kTop);
+            vA[3][m] = ((la1 >> 4) & kNib) | ((ha >> 2) & kTop);
+            vB[0][m] = (lb0 & kNib) | ((hb << 4) & kTop);
+            vB[1][m] = (lb1 & kNib) | ((hb << 2) & kTop);
+            vB[2][m] = ((lb0 >> 4) & kNib) | (hb & kTop);
+            vB[3][m] = ((lb1 >> 4) & kNib) | ((hb >> 2) & kTop);
+        }
+        // int8 scales of the half's eight sub-blocks, rows g and g+8
+        const uint32_t sA0 = lds_word<kFunnel>(rA + 192 + 8 * h, shA), sA1 = lds_word<kFunnel>(rA + 196 + 8 * h, shA);
+        const uint32_t sB0 = lds_word<kFunnel>(rB + 192 + 8 * h, shB), sB1 = lds_word<kFunnel>(rB + 196 + 8 * h, shB);
+        // {b0, b1} of quarters 0, 1 / 2, 3 (xh: 0 for the lanes of the dead columns, which read zeros at xb)
+        const uint4 b01 = lds_v4(xb + (768 * h & xh)), b23 = lds_v4(xb + ((768 * h + 384) & xh));
+        const uint4 n01 = lds_v4(nb + 128 * h), n23 = lds_v4(nb + 128 * h + 16);  // start values: (j, u) pairs
+        int c0[4] = {(int)n01.x, (int)n01.y, (int)n01.x, (int)n01.y};
+        int c1[4] = {(int)n01.z, (int)n01.w, (int)n01.z, (int)n01.w};
+        int c2[4] = {(int)n23.x, (int)n23.y, (int)n23.x, (int)n23.y};
+        int c3[4] = {(int)n23.z, (int)n23.w, (int)n23.z, (int)n23.w};
+        mma_u8s8(c0, vA[0][0], vB[0][0], vA[0][1], vB[0][1], b01.x, b01.y);
+        mma_u8s8(c1, vA[1][0], vB[1][0], vA[1][1], vB[1][1], b01.z, b01.w);
+        mma_u8s8(c2, vA[2][0], vB[2][0], vA[2][1], vB[2][1], b23.x, b23.y);
+        mma_u8s8(c3, vA[3][0], vB[3][0], vA[3][1], vB[3][1], b23.z, b23.w);
+        // D columns 2t, 2t+1 = digit t of sub-blocks 8h + 2j, 8h + 2j + 1: scale bytes 2j, 2j+1 of the half
+        IA += c0[0] * sbyte<0>(sA0) + c0[1] * sbyte<1>(sA0) + c1[0] * sbyte<2>(sA0) + c1[1] * sbyte<3>(sA0) +
+              c2[0] * sbyte<0>(sA1) + c2[1] * sbyte<1>(sA1) + c3[0] * sbyte<2>(sA1) + c3[1] * sbyte<3>(sA1);
+        IB += c0[2] * sbyte<0>(sB0) + c0[3] * sbyte<1>(sB0) + c1[2] * sbyte<2>(sB0) + c1[3] * sbyte<3>(sB0) +
+              c2[2] * sbyte<0>(sB1) + c2[3] * sbyte<1>(sB1) + c3[2] * sbyte<2>(sB1) + c3[3] * sbyte<3>(sB1);
     }
 }
 
@@ -175,7 +256,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
     const uint32_t bpr = kMoe ? bpe * a.nseg : bpe;       // blocks per (concatenated) row = units per tile
     const Smem6 s = carve6(smem_raw, bpr * 256, kWarps);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int g = lane >> 2, t = lane & 3, h = t >> 1, c = t & 1;
+    const int g = lane >> 2, t = lane & 3;
     const uint64_t row_bytes = (uint64_t)bpe * 210;
     // matrix that holds block `b` of the concatenated row, and the block's index inside it
     auto matrix_of = [&](uint32_t b, uint32_t& lb) -> const uint8_t* {
@@ -238,106 +319,63 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
         }
         if (++p_blk == bpr) { p_blk = 0; ++p_tile; }
     };
-    if (n) request(0);
-    cp_async_commit();
+#pragma unroll
+    for (int i = 0; i < kDepth; ++i) {
+        if ((uint32_t)i < n) request(i);
+        cp_async_commit();
+    }
     pdl_wait();
     XRegs6 xr;
     load_x6<kWarps>(xr, a.x, bpr * 256, kMoe ? bpe : 0u, kMoe ? a.x_slot_stride : 0u,
                     kMoe ? a.routing + a.nseg : nullptr, warp, lane);
-#pragma unroll
-    for (int i = 1; i < kDepth; ++i) {
-        if ((uint32_t)i < n) request(i);
-        cp_async_commit();
-    }
 
-    if (tid < kZeroUnits) s.zeros[tid] = make_uint4(0u, 0u, 0u, 0u);
+    if (tid < kZeroBytes6 / 16) reinterpret_cast<uint4*>(s.zeros)[tid] = make_uint4(0u, 0u, 0u, 0u);
     if (tid < kWarps) s.sflags[tid] = 0u;
     prep_x6<kWarps>(s, xr, bpr * 256, warp, lane);
     __syncthreads();
 
     uint32_t tile = u0 / bpr, blk = u0 % bpr;
     float acc[2] = {0.f, 0.f};
-    const bool b_live = (g >> 1) == t;
-    const uint32_t xu_live = smem_u32(s.xf + (g & 1) * 4 + t);
-    const uint32_t xu_dead = smem_u32(s.zeros + (g >> 1) + 1);
-    const uint32_t ring_s = smem_u32(ring), xs_s = smem_u32(s.xs), sx_s = smem_u32(s.sx);
-    const uint32_t shl = 4 - 2 * c, shr = 2 * c;  // qh bit pairs: low nibbles use bits 2c.., high nibbles 4+2c..
-    constexpr uint32_t kNib = 0x0F0F0F0Fu, kTop = 0x30303030u;
+    // B operand: lane (g, t) feeds column g; columns 6 and 7 are dead (zeros, one address for the quarter-warp)
+    const bool b_live = g < 6;
+    const uint32_t xb_base = b_live ? smem_u32(s.bq) + (uint32_t)g * 64u + (uint32_t)t * 16u : smem_u32(s.zeros);
+    const uint32_t xb_step = b_live ? (uint32_t)kBBytes : 0u;
+    const uint32_t xh = b_live ? 0xFFFFFFFFu : 0u;
+    const uint32_t nsx_s = smem_u32(s.nsx) + 32u * t, xs_s = smem_u32(s.xs), ring_s = smem_u32(ring);
+    const float dscale = __uint_as_float((127u + 14u - 7u * t) << 23);  // digit t carries 2^(14 - 7t)
 
     for (uint32_t it = 0; it < n; ++it) {
         const uint32_t slot = it % kDepth;
         cp_async_wait<kDepth - 1>();
         __syncwarp();
-        // byte offset of the block inside each row's aligned superset, and the funnel shift it implies
+        // byte offset of the block inside each row's aligned superset
         uint32_t oA, oB;
         if constexpr (kRowsAligned) {
             oA = oB = (blk * 210u) & 15u;
         } else {
-            const uint32_t rA = min(tile * 16 + g, a.M - 1), rB = min(tile * 16 + g + 8, a.M - 1);
+            const uint32_t rowA = min(tile * 16 + g, a.M - 1), rowB = min(tile * 16 + g + 8, a.M - 1);
             uint32_t lb;
             const uint8_t* mat = matrix_of(blk, lb);
-            oA = (uint32_t)(reinterpret_cast<uintptr_t>(mat + (uint64_t)rA * row_bytes + lb * 210u) & 15u);
-            oB = (uint32_t)(reinterpret_cast<uintptr_t>(mat + (uint64_t)rB * row_bytes + lb * 210u) & 15u);
+            oA = (uint32_t)(reinterpret_cast<uintptr_t>(mat + (uint64_t)rowA * row_bytes + lb * 210u) & 15u);
+            oB = (uint32_t)(reinterpret_cast<uintptr_t>(mat + (uint64_t)rowB * row_bytes + lb * 210u) & 15u);
         }
-        const uint32_t fsA = (oA & 3u) * 8u, fsB = (oB & 3u) * 8u;
         const uint32_t sb = ring_s + slot * kSlot6;
-        const uint32_t xu = b_live ? xu_live + blk * 1024u : xu_dead;  // 64 units of 16 bytes per super-block
-        // both rows share the B operand; accumulators: [row-pair quad] per sub-block (lo k=0,1; hi k=0,1)
-        int d01[4][4], d2[4][4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) d01[q][e] = d2[q][e] = 0;
-        const uint32_t wA = sb + g * kRow6 + (oA & ~3u), wB = sb + (g + 8) * kRow6 + (oB & ~3u);  // byte addresses; word offsets below x 4
-        uint32_t qlA[8], qhA[8], qlB[8], qhB[8];
-        lds_words<8>(wA + 4 * (16 * h + 8 * c), fsA, qlA);
-        lds_words<8>(wA + 4 * (32 + 8 * h), fsA, qhA);
-        lds_words<8>(wB + 4 * (16 * h + 8 * c), fsB, qlB);
-        lds_words<8>(wB + 4 * (32 + 8 * h), fsB, qhB);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint4 bl = lds_v4(xu + i * 128), bh = lds_v4(xu + (4 + i) * 128);
-            uint32_t lo[4], hi[4];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const uint32_t la = qlA[2 * i + e], ha = qhA[2 * i + e], lb = qlB[2 * i + e], hb = qhB[2 * i + e];
-                lo[2 * e] = (la & kNib) | ((ha << shl) & kTop);
-                lo[2 * e + 1] = (lb & kNib) | ((hb << shl) & kTop);
-                hi[2 * e] = ((la >> 4) & kNib) | ((ha >> shr) & kTop);
-                hi[2 * e + 1] = ((lb >> 4) & kNib) | ((hb >> shr) & kTop);
-            }
-            // words 2i, 2i+1 = elements l = 8i .. 8i+7: sub-block half k = i/2
-            mma_u8s8(d01[i >> 1], lo[0], lo[1], lo[2], lo[3], bl.x, bl.y);
-            mma_u8s8(d2[i >> 1], lo[0], lo[1], lo[2], lo[3], bl.z, bl.w);
-            mma_u8s8(d01[2 + (i >> 1)], hi[0], hi[1], hi[2], hi[3], bh.x, bh.y);
-            mma_u8s8(d2[2 + (i >> 1)], hi[0], hi[1], hi[2], hi[3], bh.z, bh.w);
+        const uint32_t rA = sb + g * kRow6 + oA, rB = sb + (g + 8) * kRow6 + oB;
+        const uint32_t xb = xb_base + blk * xb_step, nb = nsx_s + blk * (uint32_t)kNsxBytes;
+        int IA, IB;
+        if (kRowsAligned && (oA & 2u) == 0) {  // the same for the whole warp
+            block6<false>(rA, rB, 0u, 0u, xb, xh, nb, t, IA, IB);
+        } else {
+            block6<true>(rA, rB, (oA & 3u) * 8u, (oB & 3u) * 8u, xb, xh, nb, t, IA, IB);
         }
-        // scales: the 8 int8 of half h; this lane's four are bytes 2c, 2c+1 (low) and 4+2c, 5+2c (high)
-        uint32_t scA[2], scB[2], dA[1], dB[1];
-        lds_words<2>(wA + 4 * (48 + 2 * h), fsA, scA);
-        lds_words<2>(wB + 4 * (48 + 2 * h), fsB, scB);
-        lds_words<1>(wA + 4 * 52, fsA, dA);
-        lds_words<1>(wB + 4 * 52, fsB, dB);
+        const uint32_t dA = lds_u16s(rA + 208), dB = lds_u16s(rB + 208);
         // every lane has read the stage: refill it
         __syncwarp();
         if (it + kDepth < n) request(slot);
         cp_async_commit();
-
-        const uint32_t sx = sx_s + 4 * (blk * 16 + 8 * h + 2 * c);  // sub-blocks 8h+2c+k (low), 8h+4+2c+k (high)
-        const int sx0 = (int)lds_u32s(sx), sx1 = (int)lds_u32s(sx + 4), sx2 = (int)lds_u32s(sx + 16), sx3 = (int)lds_u32s(sx + 20);
-        const int sxs[4] = {sx0, sx1, sx2, sx3};
-        float sumA = 0.f, sumB = 0.f;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int PA = d01[q][0] * 16384 + d01[q][1] * 128 + d2[q][0] - 32 * sxs[q];
-            const int PB = d01[q][2] * 16384 + d01[q][3] * 128 + d2[q][2] - 32 * sxs[q];
-            const uint32_t wa = scA[q >> 1] >> (16 * c + 8 * (q & 1)), wb = scB[q >> 1] >> (16 * c + 8 * (q & 1));
-            sumA += (float)(int8_t)(wa & 0xFFu) * (float)PA;
-            sumB += (float)(int8_t)(wb & 0xFFu) * (float)PB;
-        }
         const float xs = lds_f1(xs_s + blk * 4);
-        acc[0] += h2f(dA[0]) * xs * sumA;
-        acc[1] += h2f(dB[0]) * xs * sumB;
+        acc[0] = fmaf(h2f(dA) * xs, (float)IA, acc[0]);
+        acc[1] = fmaf(h2f(dB) * xs, (float)IB, acc[1]);
 
         const uint32_t T = tile;
         bool tile_done = false;
@@ -346,7 +384,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
             float v[1][2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                float w = acc[r];
+                float w = acc[r] * dscale;
                 w += __shfl_xor_sync(0xFFFFFFFFu, w, 1);
                 w += __shfl_xor_sync(0xFFFFFFFFu, w, 2);
                 v[0][r] = w;
@@ -395,7 +433,7 @@ cudaError_t launch_cfg6(const WarpArgs& a, const uint8_t* a_end, cudaStream_t st
 bool q6k_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a) {
     if (type != T_Q6_K) return false;
     if (mode != MODE_PLAIN && mode != MODE_SIGMOID_ACC) return false;
-    if (!a.scratch_partial || !a.scratch_flags || !a.status) return false;
+    if (!a.scratch_partial || !a.status) return false;
     const uint32_t bpr = a.K >> 8;
     if (reinterpret_cast<uintptr_t>(a.A) & 15u) return false;  // supersets are fetched in 16-byte pieces from the base
     if ((bpr % 8u) != 0 && !a.a_end) return false;          // unaligned rows: the end of the buffer must be known
@@ -408,7 +446,7 @@ bool q6k_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a) {
 // MoE down projection + weighted accumulate (y += sum_s w_s W[routing[s]] x_s) through the streaming kernel.
 bool q6k_moe_down_acc_eligible(uint32_t type, const DmmvArgs& a) {
     if (type != T_Q6_K || !a.routing || a.n_used == 0 || !a.a_end) return false;
-    if (!a.scratch_partial || !a.scratch_flags || !a.status) return false;
+    if (!a.scratch_partial || !a.status) return false;
     if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (a.expert_stride & 15u) || (a.K & 255u)) return false;
     if ((a.x_expert_stride & 3u) || (reinterpret_cast<uintptr_t>(a.x) & 15u)) return false;
     const uint32_t bpr = (a.K >> 8) * a.n_used;
@@ -428,7 +466,6 @@ cudaError_t launch_q6k_moe_down_acc(const DmmvArgs& a, cudaStream_t st, uint64_t
     wa.K = a.K;
     wa.acc_mode = 1;
     wa.gpartial = a.scratch_partial;
-    wa.gflags = a.scratch_flags;
     wa.status = a.status;
     wa.spin_limit = a.spin_limit;
     wa.nseg = a.n_used;
@@ -456,7 +493,6 @@ cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t st, uint64
     wa.K = a.K;
     wa.acc_mode = a.acc_mode;
     wa.gpartial = a.scratch_partial;
-    wa.gflags = a.scratch_flags;
     wa.status = a.status;
     wa.spin_limit = a.spin_limit;
     wa.nseg = 0;

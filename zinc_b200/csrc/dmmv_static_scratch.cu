@@ -2,7 +2,7 @@
 // file-scope __device__ array instead of memory a context allocated.
 //
 // Why: the streaming matvec hands partial row sums between warps of different CTAs through a
-// small global scratch (partials + publication flags). Every other entry point takes that
+// small global scratch (each sum stored together with a tag word). Every other entry point takes that
 // scratch from a context, and creating a context allocates (device scratch, pinned status
 // words, a stream). A host that has already given all device memory to its own arena (weights
 // and KV cache sized to fill HBM), or that runs where an allocation would synchronise the
@@ -10,11 +10,12 @@
 // calls no allocating routine: the scratch is part of the loaded module.
 //
 // The array is shared by every call on the same device. Consequences:
-//  * the flag words must be zero when a launch starts. A __device__ array is zero when the
-//    module is loaded on a device, and each launch leaves the flags zero (the reader of a
-//    flag clears it), so the set-up writes nothing. A launch that gave up on a bounded wait (status word set) may leave
-//    flags set; the next call sees the non-zero status word only if the caller checks it, so
-//    a caller that finds status_words[0] != 0 must stop using this entry point on that device.
+//  * the array must be all zero when a launch starts. A __device__ array is zero when the module
+//    is loaded on a device, and each launch leaves it zero (the reader of a tagged sum clears it),
+//    so the set-up writes nothing. A launch that gave up on a bounded wait (status word set) may
+//    leave tagged sums behind; the next call sees the non-zero status word only if the caller
+//    checks it, so a caller that finds status_words[0] != 0 must stop using this entry point on
+//    that device.
 //  * two calls whose kernels can overlap (different streams, or threads without ordering)
 //    race on the array and give wrong results. Calls on one stream are ordered and safe.
 //
@@ -35,9 +36,9 @@ namespace {
 
 using namespace zc;
 
-// Scratch capacity: kStreamMaxWorkers (4096) worker warps, each 32 partial sums (f32) plus one
-// flag word: 524288 + 16384 = 540672 bytes.
-constexpr size_t kStaticScratchBytes = kStreamPartialBytes + kStreamFlagBytes;
+// Scratch capacity: kStreamMaxWorkers (4096) worker warps, each 32 partial sums as {f32 bits, tag}
+// pairs: 4096 * 32 * 8 = 1048576 bytes.
+constexpr size_t kStaticScratchBytes = kStreamPartialBytes;
 constexpr uint32_t kStaticMaxK = 12288;  // 48 blocks of 256: what the per-warp staging holds
 constexpr int kMaxDevices = 64;
 
@@ -129,8 +130,7 @@ extern "C" int32_t zc_dmmv_q4k_static_scratch(void* cuda_stream, const void* A, 
     a.M = M;
     a.K = K;
     a.acc_mode = acc_mode;
-    a.scratch_partial = reinterpret_cast<float*>(st->scratch);
-    a.scratch_flags = reinterpret_cast<uint32_t*>(st->scratch + kStreamPartialBytes);
+    a.scratch_partial = reinterpret_cast<uint2*>(st->scratch);
     a.status = status_words;
     a.sm_count = st->sm_count;
     if (!warp_dmmv_eligible(T_Q4_K, MODE_PLAIN, a))

@@ -4,12 +4,12 @@
 // kCB 256-weight super-blocks), prefetches them with coalesced 16-byte asynchronous copies
 // (cp.async into the warp's own ring of padded row segments, depth kDepth; bulk TMA copies were
 // measured at ~14 cycles of issue each per SM, too slow for 288-byte row segments), masks the 4-bit
-// quants into int8 lanes (one logic op per four weights) and feeds them to the int8 tensor cores as a 16-row dot-product engine with exact
-// s32 accumulation. There is no block-wide synchronisation after the activation vector has
-// been converted. K is split across workers so that all SMs stream the same number of bytes;
-// a tile that spans several workers is finished by the worker that owns its first unit, which
-// adds the partial sums the later workers have published (shared memory inside a CTA, global
-// memory across CTAs) in worker order, so results do not depend on timing.
+// quants into int8 lanes (one logic op per four weights) and feeds them to the int8 tensor cores as a
+// 16-row dot-product engine with exact s32 accumulation. There is no block-wide synchronisation after
+// the activation vector has been converted. K is split across workers so that all SMs stream the same
+// number of bytes; a tile that spans several workers is finished by the worker that owns its first
+// unit, which adds the partial sums the later workers have published (shared memory inside a CTA,
+// global memory across CTAs) in worker order, so results do not depend on timing.
 //
 // Stands in for the reference's K-parallel decode shaders and their fused epilogues
 // (src/shaders/dmmv_q4k.comp:59-240, dmmv_q4k_wide.comp, dmmv_q4k_fused_gate_up_swiglu.comp:195-218,
@@ -18,16 +18,20 @@
 // Arithmetic per super-block of a row, sub-blocks s = 0..7 of 32 weights:
 //   y += 2^-f * ( d * sum_s sc_s * P_s  -  dmin * sum_s m_s * SX_s ),   P_s = sum_i q_i * X_i
 // X_i = round(x_i * 2^f) is the block of x in 21-bit fixed point (f chosen per 256-element block
-// from its largest magnitude), split into three 7-bit digits X = b0*2^14 + b1*2^7 + b2 that fit
-// int8. The tensor core computes sum_i q_i * b_j,i exactly in s32 for each digit; P_s is
-// reassembled in integer arithmetic, SX_s = sum_i X_i is exact too. Weights are never rounded;
-// the only rounding before the final f32 scaling is that of x to 21 bits.
+// from its largest magnitude), split into three digits X = b0*2^14 + b1*2^7 + b2 that fit int8
+// (b0 signed, b1 and b2 in 0..127). The tensor core computes D_j,s = sum_i q_i * b_j,i exactly in s32
+// for each digit j; the 6-bit scales are applied in integer arithmetic too (sum_s sc_s * D_j,s < 2^31),
+// so one conversion and one f32 multiply-add per row, digit and super-block remain. SX_s = sum_i X_i
+// is exact. Weights are never rounded; the only rounding before the f32 scaling is that of x to 21 bits.
 //
-// Tensor-core mapping (mma.sync m16n8k32, s8 in, s32 out): the 16 A rows are 16 weight rows;
-// lane (g = lane/4, t = lane%4) owns the 32-byte qs group t of rows g and g+8, i.e. sub-blocks
-// 2t (low nibbles) and 2t+1 (high nibbles). B is block-diagonal: columns 2t and 2t+1 are
-// non-zero only in lane t's k slots, so those D columns hold dot products of group t alone and
-// land in lane t's own accumulator registers. Scales are applied per lane afterwards.
+// Tensor-core mapping (mma.sync m16n8k32, u8 x s8 -> s32): the 16 A rows are 16 weight rows. One 128-bit
+// shared-memory read gives lane (g = lane/4, t = lane%4) bytes 16(t%2) .. +15 of the 32-byte qs group
+// 2p + t/2 of row g (p = 0, 1), i.e. sixteen low nibbles (sub-block 4p + 2(t/2)) and sixteen high nibbles
+// (sub-block 4p + 2(t/2) + 1; kept in place as 16 q, the factor is folded into the scale). An MMA thus
+// carries two sub-blocks, k slots of lanes t < 2 one, of lanes t >= 2 the other; B is block-diagonal
+// to match: column 2j + u holds digit j of x for the k slots of sub-block half u and zeros elsewhere, so
+// D column 2j + u is digit j's dot product with sub-block u alone. Lane t < 3 therefore ends up with
+// digit t of both sub-blocks for rows g and g+8 and applies their scales; eight MMAs per 16 x 256 tile.
 #include "kernels.h"
 #include "stream_skel.cuh"
 
@@ -37,18 +41,18 @@ namespace {
 
 constexpr int kDepth = 2;                  // units in flight per warp
 constexpr int kCB = 2;                     // super-blocks per row segment
-constexpr int kRowSeg = kCB * 144 + 16;    // 304: rows land 16 B apart mod 32 B -> conflict-free 128-bit reads
+constexpr int kRowSeg = kCB * 144 + 32;    // 320: rows land 64 B apart mod 128 B -> conflict-free 128-bit reads
 constexpr int kSlotBytes = 16 * kRowSeg;
 constexpr int kWarpRing = kDepth * kSlotBytes;
 constexpr size_t kTwoPerSm = 113 * 1024;   // shared memory per CTA that still lets two CTAs share an SM
-constexpr int kZeroUnits = 72;             // zeros: B operand of the lanes whose columns are dead
+constexpr int kZeroBytes = 256;            // zeros: B operand of the lanes whose column is dead for their k slots
 constexpr int kFracBits = 20;              // |X| <= 2^20
 constexpr int kPiecesPerRow = kCB * 9;     // 16-byte pieces of one row segment
 constexpr int kPiecesPerLane = (16 * kPiecesPerRow + 31) / 32;
 
 struct Smem {
-    uint4* xf;       // x digits in B-operand order: unit ((blk*8 + s*4 + j)*2 + p)*4 + t
-    uint4* zeros;    // kZeroUnits zero units
+    uint8_t* dig;    // three digit planes of K bytes each, elements in natural order
+    uint8_t* zeros;  // kZeroBytes of zeros, 128-byte aligned
     float* sx;       // per 32-element sub-block sum of X
     float* xs;       // per super-block 2^-f
     uint8_t* ring;   // [kWarps][kDepth] stages of 16 padded row segments
@@ -57,7 +61,7 @@ struct Smem {
 };
 
 __host__ __device__ inline size_t smem_bytes(uint32_t K, int kWarps) {
-    size_t n = (size_t)K * 4 + (size_t)kZeroUnits * 16;
+    size_t n = (size_t)K * 3 + (size_t)kZeroBytes;
     n += (size_t)(K / 32) * 4 + (size_t)(K / 256) * 4;
     n = (n + 127) & ~size_t(127);
     n += (size_t)kWarps * kWarpRing;
@@ -68,10 +72,10 @@ __host__ __device__ inline size_t smem_bytes(uint32_t K, int kWarps) {
 __device__ inline Smem carve(uint8_t* base, uint32_t K, int kWarps) {
     Smem s;
     uintptr_t p = (reinterpret_cast<uintptr_t>(base) + 127) & ~uintptr_t(127);
-    s.xf = reinterpret_cast<uint4*>(p);
-    p += (size_t)K * 4;
-    s.zeros = reinterpret_cast<uint4*>(p);
-    p += (size_t)kZeroUnits * 16;
+    s.zeros = reinterpret_cast<uint8_t*>(p);
+    p += (size_t)kZeroBytes;
+    s.dig = reinterpret_cast<uint8_t*>(p);   // K is a multiple of 256: every plane starts 128-byte aligned
+    p += (size_t)K * 3;
     s.sx = reinterpret_cast<float*>(p);
     p += (size_t)(K / 32) * 4;
     s.xs = reinterpret_cast<float*>(p);
@@ -86,11 +90,8 @@ __device__ inline Smem carve(uint8_t* base, uint32_t K, int kWarps) {
 }
 
 
-// Convert x into int8 digits in tensor-core operand order. One warp per super-block;
-// lane = j*8 + s*4 + t handles the 8 consecutive elements 64t + 32s + 8j .. +7 (bytes 8j..8j+7
-// of qs group t; s = 0 low nibbles, 1 high nibbles). Unit p = 0 holds (digit 0 | digit 2) of
-// those 8 elements, unit p = 1 (digit 1 | zeros): the two B register pairs of the lanes that
-// feed columns 2t and 2t+1.
+// Convert x into int8 digit planes. One warp per super-block; lane l handles the 8 consecutive elements
+// 8l .. 8l+7 (a 32-byte coalesced read), so sub-block s is lanes 4s .. 4s+3.
 //
 // The loads are issued before the weight prefetch (so they are not queued behind it) and
 // converted afterwards: kPrepBlocks super-blocks per warp cover K <= kPrepBlocks * kWarps * 256.
@@ -100,20 +101,24 @@ struct XRegs {
 };
 template <int kWarps>
 __device__ __forceinline__ void load_x(XRegs& r, const float* __restrict__ x, uint32_t K, int warp, int lane) {
-    const int j = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
 #pragma unroll
     for (int i = 0; i < kPrepBlocks; ++i) {
         const uint32_t blk = warp + i * kWarps;
         if (blk < (K >> 8)) {
-            const float* xp = x + (size_t)blk * 256 + 64 * t + 32 * sh + 8 * j;
+            const float* xp = x + (size_t)blk * 256 + 8 * lane;
             r.lo[i] = __ldg(reinterpret_cast<const float4*>(xp));
             r.hi[i] = __ldg(reinterpret_cast<const float4*>(xp) + 1);
         }
     }
 }
+
+// Four values' low bytes as one word.
+__device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
 template <int kWarps>
 __device__ __forceinline__ void prep_x(const Smem& s, const XRegs& r, uint32_t K, int warp, int lane) {
-    const int j = lane >> 3, sh = (lane >> 2) & 1, t = lane & 3;
 #pragma unroll
     for (int bi = 0; bi < kPrepBlocks; ++bi) {
         const uint32_t blk = warp + bi * kWarps;
@@ -129,40 +134,31 @@ __device__ __forceinline__ void prep_x(const Smem& s, const XRegs& r, uint32_t K
         uint32_t E = (__float_as_uint(mx) >> 23) & 0xFFu;
         E = E < 32u ? 32u : E;
         const float scale = __uint_as_float((127u + 126u + kFracBits - E) << 23);
-        uint32_t d0[2] = {0, 0}, d1[2] = {0, 0}, d2[2] = {0, 0};
+        int X[8];
         int sum = 0;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const int X = __float2int_rn(v[i] * scale);
-            sum += X;
-            d0[i >> 2] |= (uint32_t)((X >> 14) & 0xFF) << (8 * (i & 3));
-            d1[i >> 2] |= (uint32_t)((X >> 7) & 0x7F) << (8 * (i & 3));
-            d2[i >> 2] |= (uint32_t)(X & 0x7F) << (8 * (i & 3));
+            X[i] = __float2int_rn(v[i] * scale);
+            sum += X[i];
         }
-        const uint32_t u = (blk * 8 + sh * 4 + j) * 2;
-        s.xf[(u + 0) * 4 + t] = make_uint4(d0[0], d0[1], d2[0], d2[1]);
-        s.xf[(u + 1) * 4 + t] = make_uint4(d1[0], d1[1], 0u, 0u);
-        // sub-block sums: reduce over j (lane bits 3 and 4)
-        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 8);
-        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 16);
-        if (j == 0) s.sx[blk * 8 + 2 * t + sh] = (float)sum;
+        uint2 d0, d1, d2;
+        d0.x = pack4(X[0] >> 14, X[1] >> 14, X[2] >> 14, X[3] >> 14);
+        d0.y = pack4(X[4] >> 14, X[5] >> 14, X[6] >> 14, X[7] >> 14);
+        d1.x = pack4(X[0] >> 7, X[1] >> 7, X[2] >> 7, X[3] >> 7) & 0x7F7F7F7Fu;
+        d1.y = pack4(X[4] >> 7, X[5] >> 7, X[6] >> 7, X[7] >> 7) & 0x7F7F7F7Fu;
+        d2.x = pack4(X[0], X[1], X[2], X[3]) & 0x7F7F7F7Fu;
+        d2.y = pack4(X[4], X[5], X[6], X[7]) & 0x7F7F7F7Fu;
+        uint8_t* dst = s.dig + (size_t)blk * 256 + 8 * lane;
+        *reinterpret_cast<uint2*>(dst) = d0;
+        *reinterpret_cast<uint2*>(dst + K) = d1;
+        *reinterpret_cast<uint2*>(dst + 2 * (size_t)K) = d2;
+        // sub-block sums: four lanes per sub-block
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+        if ((lane & 3) == 0) s.sx[blk * 8 + (lane >> 2)] = (float)sum;
         if (lane == 0) s.xs[blk] = __uint_as_float((E + 1u - kFracBits) << 23);  // 2^-f = 2^(E-146)
     }
 }
-
-// Two 6-bit scales and two 6-bit mins of sub-blocks 2t and 2t+1, each pair packed in the low
-// 16 bits (getScaleMinK4, src/compute/forward.zig:229-238, evaluated for two indices at once).
-__device__ __forceinline__ void scales_mins_pair(uint32_t s0, uint32_t s1, uint32_t s2, int t, uint32_t& sc,
-                                                 uint32_t& mn) {
-    const uint32_t sh = 16u * (t & 1);
-    const uint32_t p0 = s0 >> sh, p1 = s1 >> sh, p2 = s2 >> sh;
-    const uint32_t lo_sc = p0 & 0x3F3Fu, lo_mn = p1 & 0x3F3Fu;
-    const uint32_t hi_sc = (p2 & 0x0F0Fu) | ((p0 >> 2) & 0x3030u);
-    const uint32_t hi_mn = ((p2 >> 4) & 0x0F0Fu) | ((p1 >> 2) & 0x3030u);
-    sc = t < 2 ? lo_sc : hi_sc;
-    mn = t < 2 ? lo_mn : hi_mn;
-}
-
 
 // Segment of a grouped launch that holds tile T.
 __device__ __forceinline__ int seg_of(const WarpArgs& a, uint32_t T) {
@@ -246,32 +242,41 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
             if (++p_strm == NS) { p_strm = 0; ++p_tile; }
         }
     };
-    // weights never depend on the previous kernel: start streaming them, then wait for it, then
-    // fetch x (ahead of the rest of the prefetch in the memory queues)
-    if (n) request(0);
-    cp_async_commit();
-    pdl_wait();
-    XRegs xr;
-    load_x<kWarps>(xr, a.x, a.K, warp, lane);
+    // weights never depend on the previous kernel: fill the whole ring, then wait for that kernel, then
+    // fetch x
 #pragma unroll
-    for (int i = 1; i < kDepth; ++i) {
+    for (int i = 0; i < kDepth; ++i) {
         if ((uint32_t)i < n) request(i);
         cp_async_commit();
     }
+    pdl_wait();
+    XRegs xr;
+    load_x<kWarps>(xr, a.x, a.K, warp, lane);
 
-    // ---- activation vector -> B operand layout (all warps), zero region, flags ----
-    if (tid < kZeroUnits) s.zeros[tid] = make_uint4(0u, 0u, 0u, 0u);
+    // ---- activation vector -> digit planes (all warps), zero region, flags ----
+    if (tid < kZeroBytes / 16) reinterpret_cast<uint4*>(s.zeros)[tid] = make_uint4(0u, 0u, 0u, 0u);
     if (tid < kWarps) s.sflags[tid] = 0u;
     prep_x<kWarps>(s, xr, a.K, warp, lane);
     __syncthreads();
 
     // ---- consume ----
     uint32_t tile = u0 / upt_all, strm = (u0 % upt_all) / upt, kc = (u0 % upt_all) % upt;
-    float acc0[2] = {0.f, 0.f}, acc1[2] = {0.f, 0.f};  // stream 0 / stream 1, rows g and g+8
-    const bool b_live = (g >> 1) == t;  // lane (g, t) feeds B column g, live only for g in {2t, 2t+1}
-    const uint32_t xu_live = smem_u32(s.xf + (g & 1) * 4 + t);
-    const uint32_t xu_dead = smem_u32(s.zeros + (g >> 1) + 1);  // a bank group no live lane of the same quarter-warp uses
-    const uint32_t ring_s = smem_u32(ring), xs_s = smem_u32(s.xs), sx_s = smem_u32(s.sx);
+    // per stream, rows g and g+8: digit t's share of d * sum_s sc_s P_s (to be scaled by 2^(10 - 7t)) and this
+    // lane's share of dmin * sum_s m_s SX_s
+    float accM0[2] = {0.f, 0.f}, accM1[2] = {0.f, 0.f}, accm0[2] = {0.f, 0.f}, accm1[2] = {0.f, 0.f};
+    // B operand: lane (g, t) feeds column g for its k slots (elements 64(t/2) + 16(t%2) .. +15 of a 128-element
+    // pair of qs groups, +32 for the high nibbles). Column g = 2j + u is live for the lanes with t/2 == u and
+    // reads digit plane j; the other lanes read zeros, at a bank offset the live lanes of their quarter-warp
+    // do not touch (live: 32h + {0..31, 64..95} mod 128 for nibble half h; zeros at 32 + 32h).
+    const bool b_live = g < 6 && (g & 1) == (t >> 1);
+    const uint32_t xb_base = b_live ? smem_u32(s.dig) + (uint32_t)(g >> 1) * a.K + 64u * (t >> 1) + 16u * (t & 1)
+                                    : smem_u32(s.zeros) + 32u;
+    const uint32_t xb_step = b_live ? 256u : 0u;
+    const uint32_t ring_s = smem_u32(ring), xs_s = smem_u32(s.xs), sx_s = smem_u32(s.sx) + 8u * t;
+    const uint32_t msel = (2u * t) | ((2u * t + 1u) << 4) | 0x7700u;  // bytes 2t, 2t+1 of {mins 0..3, mins 4..7}
+    // digit t's sum carries 2^(14 - 7t) and the 1/16 of the in-place high nibbles; lane t = 3 holds zeros
+    const float dscale = __uint_as_float((127u + 10u - 7u * t) << 23);
+    constexpr uint32_t kLo = 0x0F0F0F0Fu, kHi = 0xF0F0F0F0u;
 
     for (uint32_t it = 0; it < n; ++it) {
         const uint32_t slot = it % kDepth;
@@ -286,44 +291,49 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
             const uint32_t rA = sb + g * kRowSeg;
             const uint32_t rB = sb + (g + 8) * kRowSeg;
             const uint4 hA = lds_v4(rA), hB = lds_v4(rB);
-            const uint4 qa0 = lds_v4(rA + 16 + 32 * t), qa1 = lds_v4(rA + 32 + 32 * t);
-            const uint4 qb0 = lds_v4(rB + 16 + 32 * t), qb1 = lds_v4(rB + 32 + 32 * t);
-            const uint32_t qa[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
-            const uint32_t qb[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
-            const uint32_t xu = b_live ? xu_live + blk * 1024u : xu_dead;  // 64 units of 16 bytes per super-block
-            // D01: digits 0 and 1 in this lane's columns 2t, 2t+1; D2: digit 2 in column 2t
-            int lo01[4] = {0, 0, 0, 0}, lo2[4] = {0, 0, 0, 0}, hi01[4] = {0, 0, 0, 0}, hi2[4] = {0, 0, 0, 0};
-            constexpr uint32_t kNib = 0x0F0F0F0Fu;
+            const uint32_t xb = xb_base + blk * xb_step;
+            // 6-bit scales of sub-blocks 0..3 and 4..7, one per byte (getScaleMinK4, src/compute/forward.zig:229-238)
+            const uint32_t scA[2] = {hA.y & 0x3F3F3F3Fu, (hA.w & 0x0F0F0F0Fu) | ((hA.y >> 2) & 0x30303030u)};
+            const uint32_t scB[2] = {hB.y & 0x3F3F3F3Fu, (hB.w & 0x0F0F0F0Fu) | ((hB.y >> 2) & 0x30303030u)};
+            int IloA = 0, IhiA = 0, IloB = 0, IhiB = 0;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const uint4 bl = lds_v4(xu + j * 128), bh = lds_v4(xu + (4 + j) * 128);
-                const uint32_t a0 = qa[2 * j], a1 = qb[2 * j], a2 = qa[2 * j + 1], a3 = qb[2 * j + 1];
-                const uint32_t l0 = a0 & kNib, l1 = a1 & kNib, l2 = a2 & kNib, l3 = a3 & kNib;
-                mma_s8(lo01, l0, l1, l2, l3, bl.x, bl.y);
-                mma_s8(lo2, l0, l1, l2, l3, bl.z, bl.w);
-                const uint32_t h0 = (a0 >> 4) & kNib, h1 = (a1 >> 4) & kNib, h2 = (a2 >> 4) & kNib,
-                               h3 = (a3 >> 4) & kNib;
-                mma_s8(hi01, h0, h1, h2, h3, bh.x, bh.y);
-                mma_s8(hi2, h0, h1, h2, h3, bh.z, bh.w);
+            for (int p = 0; p < 2; ++p) {
+                const uint4 qa = lds_v4(rA + 16 + 64 * p + 16 * t), qb = lds_v4(rB + 16 + 64 * p + 16 * t);
+                const uint4 bl = lds_v4(xb + 128 * p), bh = lds_v4(xb + 128 * p + 32);
+                int lo[4] = {0, 0, 0, 0}, hi[4] = {0, 0, 0, 0};
+                mma_u8s8(lo, qa.x & kLo, qb.x & kLo, qa.y & kLo, qb.y & kLo, bl.x, bl.y);
+                mma_u8s8(lo, qa.z & kLo, qb.z & kLo, qa.w & kLo, qb.w & kLo, bl.z, bl.w);
+                mma_u8s8(hi, qa.x & kHi, qb.x & kHi, qa.y & kHi, qb.y & kHi, bh.x, bh.y);
+                mma_u8s8(hi, qa.z & kHi, qb.z & kHi, qa.w & kHi, qb.w & kHi, bh.z, bh.w);
+                // D columns 2t, 2t+1 = digit t of sub-blocks 4p (+1 for the high nibbles) and 4p + 2 (+1)
+                const uint32_t sa = scA[p], sb2 = scB[p];
+                IloA += lo[0] * (int)(sa & 0xFFu) + lo[1] * (int)((sa >> 16) & 0xFFu);
+                IhiA += hi[0] * (int)((sa >> 8) & 0xFFu) + hi[1] * (int)(sa >> 24);
+                IloB += lo[2] * (int)(sb2 & 0xFFu) + lo[3] * (int)((sb2 >> 16) & 0xFFu);
+                IhiB += hi[2] * (int)((sb2 >> 8) & 0xFFu) + hi[3] * (int)(sb2 >> 24);
             }
-            // P = D0 * 2^14 + D1 * 2^7 + D2, exact in s32 (|P| < 2^31 for 5-bit quants and below)
-            const float PloA = (float)(lo01[0] * 16384 + lo01[1] * 128 + lo2[0]);
-            const float PloB = (float)(lo01[2] * 16384 + lo01[3] * 128 + lo2[2]);
-            const float PhiA = (float)(hi01[0] * 16384 + hi01[1] * 128 + hi2[0]);
-            const float PhiB = (float)(hi01[2] * 16384 + hi01[3] * 128 + hi2[2]);
-            uint32_t scA, mnA, scB, mnB;
-            scales_mins_pair(hA.y, hA.z, hA.w, t, scA, mnA);
-            scales_mins_pair(hB.y, hB.z, hB.w, t, scB, mnB);
+            // the high nibbles were multiplied as 16 q: sum = (16 * lo + hi) / 16, the 1/16 sits in dscale
+            const float PA = (float)(IloA * 16 + IhiA), PB = (float)(IloB * 16 + IhiB);
+            // mins of sub-blocks 2t, 2t+1
+            const uint32_t mnA = __byte_perm(hA.z & 0x3F3F3F3Fu, ((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u), msel);
+            const uint32_t mnB = __byte_perm(hB.z & 0x3F3F3F3Fu, ((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u), msel);
             const float xs = lds_f1(xs_s + blk * 4);
-            const float2 sxv = lds_f2(sx_s + (blk * 8 + 2 * t) * 4);
+            const float2 sxv = lds_f2(sx_s + blk * 32);
             const float dA = h2f(hA.x) * xs, dmA = h2f(hA.x >> 16) * xs;
             const float dB = h2f(hB.x) * xs, dmB = h2f(hB.x >> 16) * xs;
-            const float vA = dA * ((float)(scA & 0xFFu) * PloA + (float)(scA >> 8) * PhiA) -
-                             dmA * ((float)(mnA & 0xFFu) * sxv.x + (float)(mnA >> 8) * sxv.y);
-            const float vB = dB * ((float)(scB & 0xFFu) * PloB + (float)(scB >> 8) * PhiB) -
-                             dmB * ((float)(mnB & 0xFFu) * sxv.x + (float)(mnB >> 8) * sxv.y);
-            if (NS == 1 || strm == 0) { acc0[0] += vA; acc0[1] += vB; }
-            else { acc1[0] += vA; acc1[1] += vB; }
+            const float mA = (float)(mnA & 0xFFu) * sxv.x + (float)((mnA >> 8) & 0xFFu) * sxv.y;
+            const float mB = (float)(mnB & 0xFFu) * sxv.x + (float)((mnB >> 8) & 0xFFu) * sxv.y;
+            if (NS == 1 || strm == 0) {
+                accM0[0] = fmaf(dA, PA, accM0[0]);
+                accM0[1] = fmaf(dB, PB, accM0[1]);
+                accm0[0] = fmaf(dmA, mA, accm0[0]);
+                accm0[1] = fmaf(dmB, mB, accm0[1]);
+            } else {
+                accM1[0] = fmaf(dA, PA, accM1[0]);
+                accM1[1] = fmaf(dB, PB, accM1[1]);
+                accm1[0] = fmaf(dmA, mA, accm1[0]);
+                accm1[1] = fmaf(dmB, mB, accm1[1]);
+            }
         }
         // every lane has consumed the stage: request the unit kDepth ahead into it
         __syncwarp();
@@ -340,17 +350,17 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
             float v[NS][2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                float w = acc0[r];
+                float w = fmaf(accM0[r], dscale, -accm0[r]);
                 w += __shfl_xor_sync(0xFFFFFFFFu, w, 1);
                 w += __shfl_xor_sync(0xFFFFFFFFu, w, 2);
                 v[0][r] = w;
-                acc0[r] = 0.f;
+                accM0[r] = accm0[r] = 0.f;
                 if (NS == 2) {
-                    float w1 = acc1[r];
+                    float w1 = fmaf(accM1[r], dscale, -accm1[r]);
                     w1 += __shfl_xor_sync(0xFFFFFFFFu, w1, 1);
                     w1 += __shfl_xor_sync(0xFFFFFFFFu, w1, 2);
                     v[NS - 1][r] = w1;
-                    acc1[r] = 0.f;
+                    accM1[r] = accm1[r] = 0.f;
                 }
             }
             if constexpr (kSeg == 2) {
@@ -399,7 +409,7 @@ cudaError_t launch_cfg(const WarpArgs& a, cudaStream_t st, int sm_count) {
 bool warp_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a) {
     if (type != T_Q4_K) return false;
     if (mode != MODE_PLAIN && mode != MODE_GATE_UP_SWIGLU && mode != MODE_SIGMOID_ACC) return false;
-    if (!a.scratch_partial || !a.scratch_flags || !a.status) return false;
+    if (!a.scratch_partial || !a.status) return false;
     if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (a.A2 && (reinterpret_cast<uintptr_t>(a.A2) & 15u))) return false;
     if (smem_bytes(a.K, 16) > 227 * 1024 || (a.K >> 8) > (uint32_t)(kPrepBlocks * 8)) return false;
     const int ns = mode == MODE_GATE_UP_SWIGLU ? 2 : 1;
@@ -420,7 +430,6 @@ cudaError_t launch_warp_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStr
     wa.K = a.K;
     wa.acc_mode = a.acc_mode;
     wa.gpartial = a.scratch_partial;
-    wa.gflags = a.scratch_flags;
     wa.status = a.status;
     wa.spin_limit = a.spin_limit;
     wa.nseg = 0;
@@ -439,7 +448,7 @@ cudaError_t launch_warp_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStr
 bool warp_dmmv_multi_eligible(uint32_t type, uint32_t n, const uint8_t* const* A, const uint32_t* M, uint32_t K,
                               const DmmvArgs& common) {
     if (type != T_Q4_K || n < 2 || n > 3) return false;
-    if (!common.scratch_partial || !common.scratch_flags || !common.status) return false;
+    if (!common.scratch_partial || !common.status) return false;
     if (smem_bytes(K, 16) > 227 * 1024 || (K >> 8) > (uint32_t)(kPrepBlocks * 8) || (K & 255u)) return false;
     uint64_t tiles = 0;
     for (uint32_t i = 0; i < n; ++i) {
@@ -462,7 +471,6 @@ cudaError_t launch_warp_dmmv_multi(uint32_t n, const uint8_t* const* A, float* c
     wa.K = common.K;
     wa.acc_mode = common.acc_mode;
     wa.gpartial = common.scratch_partial;
-    wa.gflags = common.scratch_flags;
     wa.status = common.status;
     wa.spin_limit = common.spin_limit;
     wa.nseg = n;
@@ -495,7 +503,7 @@ cudaError_t launch_warp_dmmv_multi(uint32_t n, const uint8_t* const* A, float* c
 // MoE fused gate + up: y_gate[s][M], y_up[s][M] = Wg[routing[s]] x, Wu[routing[s]] x for the n_used slots, x shared.
 bool warp_moe_gate_up_eligible(uint32_t type, const DmmvArgs& a) {
     if (type != T_Q4_K || a.x_expert_stride != 0 || !a.routing || !a.A2 || !a.y2) return false;
-    if (!a.scratch_partial || !a.scratch_flags || !a.status) return false;
+    if (!a.scratch_partial || !a.status) return false;
     if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (reinterpret_cast<uintptr_t>(a.A2) & 15u) || (a.expert_stride & 15u))
         return false;
     if ((a.K & 255u) || smem_bytes(a.K, 16) > 227 * 1024 || (a.K >> 8) > (uint32_t)(kPrepBlocks * 8)) return false;
@@ -516,7 +524,6 @@ cudaError_t launch_warp_moe_gate_up(const DmmvArgs& a, cudaStream_t st, uint64_t
     wa.K = a.K;
     wa.acc_mode = 0;
     wa.gpartial = a.scratch_partial;
-    wa.gflags = a.scratch_flags;
     wa.status = a.status;
     wa.spin_limit = a.spin_limit;
     wa.nseg = a.n_used;

@@ -55,8 +55,8 @@ struct DmmvArgs {
     uint32_t x_token_stride = 0;  // MODE_MOE_BATCHED, elements
     uint32_t y_token_stride = 0;  // MODE_MOE_BATCHED, elements
     // context scratch of the split-K streaming kernels (null: streaming path not used)
-    float* scratch_partial = nullptr;   // [kStreamMaxWorkers][32] partial sums published across CTAs
-    uint32_t* scratch_flags = nullptr;  // [kStreamMaxWorkers] publication flags, zero between launches
+    uint2* scratch_partial = nullptr;   // [kStreamMaxWorkers][32] {f32 bits, tag} partial sums handed across CTAs;
+                                        // all zero between launches (the reader of a value clears it)
     uint32_t* status = nullptr;
     uint32_t spin_limit = 1u << 26;     // polls after which a device-side wait gives up
     int sm_count = 0;
@@ -70,8 +70,7 @@ struct DmmvArgs {
 // Below this many weight bytes a matvec is latency-bound and the one-warp-per-row kernels (more CTAs) win.
 constexpr uint64_t kStreamMinBytes = 2u << 20;
 constexpr uint32_t kStreamMaxWorkers = 4096;  // warps that may publish a partial tile
-constexpr size_t kStreamPartialBytes = (size_t)kStreamMaxWorkers * 32 * sizeof(float);
-constexpr size_t kStreamFlagBytes = (size_t)kStreamMaxWorkers * sizeof(uint32_t);
+constexpr size_t kStreamPartialBytes = (size_t)kStreamMaxWorkers * 32 * sizeof(uint2);
 
 // Warp-autonomous streaming (cp.async + tensor-core) matvec: eligibility and launch.
 bool warp_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a);

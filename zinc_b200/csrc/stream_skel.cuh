@@ -21,8 +21,8 @@ struct WarpArgs {
     float* y;
     const float* gate;
     uint32_t M, K, acc_mode;
-    float* gpartial;     // [workers][32] partial sums published across CTAs
-    uint32_t* gflags;    // [workers] 0 = empty, 1 = published; the reader clears it
+    uint2* gpartial;     // [workers][32] partial sums published across CTAs as {f32 bits, 1}; {0, 0} = empty,
+                         // the reader puts that back. A 64-bit store is one transaction: no flag, no fence.
     uint32_t* status;    // [0] error code, [1] site
     // Grouped launch (several matrices that share x and K, e.g. Q, K and V): segment i covers the
     // 16-row tiles [seg_end[i-1], seg_end[i]). Its pointers and row bound are pre-shifted by the
@@ -128,6 +128,12 @@ __device__ __forceinline__ void write_row(const WarpArgs& a, uint32_t row, const
 }
 
 
+__device__ __forceinline__ uint2 ld_volatile_u2(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+
 // Ends a tile for this warp. v[i][r]: sums of stream i for rows g (r = 0) and g+8 (r = 1), already
 // reduced over the four lanes of a row.
 template <int NS, int EPI, int kWarps>
@@ -139,58 +145,73 @@ __device__ __forceinline__ void finish_tile(const WarpArgs& a, float* spartial, 
     if (u0 > first) {
         // not the first contributor: publish the partial sums for the worker that owns `first`
         const uint32_t fin = part_owner(first, U, G);
-        const bool same_cta = fin / kWarps == blockIdx.x;
-        float* dst = same_cta ? spartial + warp * 32 : a.gpartial + (size_t)me * 32;
-        if (t == 0) {
+        if (fin / kWarps == blockIdx.x) {  // same CTA: shared memory and a flag
+            float* dst = spartial + warp * 32;
+            if (t == 0) {
+#pragma unroll
+                for (int i = 0; i < NS; ++i) {
+                    dst[i * 16 + g] = v[i][0];
+                    dst[i * 16 + g + 8] = v[i][1];
+                }
+                __threadfence_block();
+            }
+            __syncwarp();
+            if (lane == 0) sflags[warp] = 1u;
+        } else if (t == 0) {  // another CTA: value and tag travel together
+            uint2* dst = a.gpartial + (size_t)me * 32;
 #pragma unroll
             for (int i = 0; i < NS; ++i) {
-                dst[i * 16 + g] = v[i][0];
-                dst[i * 16 + g + 8] = v[i][1];
+                dst[i * 16 + g] = make_uint2(__float_as_uint(v[i][0]), 1u);
+                dst[i * 16 + g + 8] = make_uint2(__float_as_uint(v[i][1]), 1u);
             }
-            if (same_cta) __threadfence_block(); else __threadfence();
-        }
-        __syncwarp();
-        if (lane == 0) {
-            if (same_cta) sflags[warp] = 1u;
-            else *reinterpret_cast<volatile uint32_t*>(a.gflags + me) = 1u;
         }
         return;
     }
     if (last >= u1) {
         // first contributor of a tile that continues in later workers. They published early (the
-        // tile is the first thing they work on); wait for all flags at once, then let lane t of each
-        // row add parts t, t+4, ... so that the remote reads overlap. The order is fixed by lane
-        // index, not by timing.
+        // tile is the first thing they work on). Lane t of each row adds parts t, t+4, ... (the order is
+        // fixed by lane index, not by timing): parts from this CTA after their flag is up, parts from
+        // other CTAs by polling the tagged values themselves, every wait bounded.
         const uint32_t cl = part_owner(last, U, G);
-        const uint32_t cnt = cl - me;  // contributors me+1 .. cl
-        for (uint32_t base = 0; base < cnt; base += 32) {
-            const uint32_t c = me + 1 + base + lane;
-            bool ready = c > cl;
-            const bool same_cta = c / kWarps == blockIdx.x;
-            volatile uint32_t* flag =
-                same_cta ? sflags + (c % kWarps) : reinterpret_cast<volatile uint32_t*>(a.gflags + min(c, cl));
-            uint32_t spins = 0;
-            while (!__all_sync(0xFFFFFFFFu, ready)) {
-                if (!ready) ready = *flag != 0u;
-                if (++spins > a.spin_limit) {
-                    if (lane == 0) { a.status[0] = 1; a.status[1] = 3; }
-                    break;
-                }
-            }
-        }
-        __threadfence();
         float w[NS][2];
 #pragma unroll
         for (int i = 0; i < NS; ++i) w[i][0] = w[i][1] = 0.f;
+        bool gave_up = false;
         for (uint32_t c = me + 1 + t; c <= cl; c += 4) {
-            const bool same_cta = c / kWarps == blockIdx.x;
-            const float* src = same_cta ? spartial + (c % kWarps) * 32 : a.gpartial + (size_t)c * 32;
+            if (c / kWarps == blockIdx.x) {
+                volatile uint32_t* flag = sflags + (c % kWarps);
+                uint32_t spins = 0;
+                while (*flag == 0u) {
+                    if (++spins > a.spin_limit) { gave_up = true; break; }
+                }
+                __threadfence_block();
+                const float* src = spartial + (c % kWarps) * 32;
 #pragma unroll
-            for (int i = 0; i < NS; ++i) {
-                w[i][0] += same_cta ? src[i * 16 + g] : ld_cg_f32(src + i * 16 + g);
-                w[i][1] += same_cta ? src[i * 16 + g + 8] : ld_cg_f32(src + i * 16 + g + 8);
+                for (int i = 0; i < NS; ++i) {
+                    w[i][0] += *reinterpret_cast<const volatile float*>(src + i * 16 + g);
+                    w[i][1] += *reinterpret_cast<const volatile float*>(src + i * 16 + g + 8);
+                }
+            } else {
+                uint2* src = a.gpartial + (size_t)c * 32;
+#pragma unroll
+                for (int i = 0; i < NS; ++i) {
+#pragma unroll
+                    for (int r = 0; r < 2; ++r) {
+                        uint2* p = src + i * 16 + g + 8 * r;
+                        uint2 q = ld_volatile_u2(p);
+                        uint32_t spins = 0;
+                        while (q.y == 0u) {
+                            if (++spins > a.spin_limit) { gave_up = true; break; }
+                            q = ld_volatile_u2(p);
+                        }
+                        w[i][r] += __uint_as_float(q.x);
+                        *p = make_uint2(0u, 0u);  // empty again for the next launch
+                    }
+                }
             }
         }
+        if (gave_up) { a.status[0] = 1; a.status[1] = 3; }
+        __syncwarp();
 #pragma unroll
         for (int i = 0; i < NS; ++i) {
 #pragma unroll
@@ -201,10 +222,6 @@ __device__ __forceinline__ void finish_tile(const WarpArgs& a, float* spartial, 
                 v[i][r] += q;
             }
         }
-        __syncwarp();
-        // every part has been read: clear the global flags for the next launch
-        for (uint32_t c = me + 1 + lane; c <= cl; c += 32)
-            if (c / kWarps != blockIdx.x) *reinterpret_cast<volatile uint32_t*>(a.gflags + c) = 0u;
     }
     if (t == 0) {
         float r0[NS], r1[NS];
