@@ -579,8 +579,10 @@ def main():
                          "prefill_gemm: the batched-prefill dequant-GEMM cases; dmmv_single: one Q4_K 4096x4096 matvec; "
                          "moe_decode: the two MoE configurations at batch 1; moe_prefill: one MoE layer's routed experts "
                          "over a prefill batch")
-    ap.add_argument("--collective", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: the library's peer exchange (default) or NCCL for the hidden-state sums")
+    ap.add_argument("--collective", default="fused", choices=["fused", "peer", "nccl"],
+                    help="N > 1, hidden-state sums: fused = partial rows pushed to every rank from the matvec's epilogue "
+                         "and summed in the next matvec's prologue (default); peer = the library's one-kernel all-reduce; "
+                         "nccl = NCCL all-reduce (the baseline)")
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debug; invalidates the number)")
     ap.add_argument("--tokens", type=int, default=0, help="moe_prefill: override the prefill batch (default 512 / 1024)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -663,6 +665,8 @@ def main():
                 dist.barrier()
             torch.cuda.synchronize()
 
+        if args.collective == "fused":
+            allreduce = None
         check = None
         if world > 1:
             check = tp_check(torch, zb, dd, dist, rank, world, allreduce, allgather)
@@ -799,7 +803,7 @@ def main():
                 "workload": "qwen3-8b-shaped decode step, batch 1, Q4_K_M mix (Q4_K attn/gate/up, Q6_K down + LM head)",
                 "layers": shape.n_layers, "hidden": shape.hidden, "ffn": shape.ffn, "vocab": shape.vocab,
                 "weight_bytes_per_token": total_bytes,
-                "parallelism": "single GPU" if world == 1 else f"tp{world} (rows: QKV/gate/up/head, K: O/down; collectives: {'peer exchange kernels over NVLink' if args.collective == 'peer' else 'NCCL'})",
+                "parallelism": "single GPU" if world == 1 else f"tp{world} (rows: QKV/gate/up/head, K: O/down; hidden-state sums: {dict(fused='rows pushed to every rank from the matvec epilogue, summed in the next matvec prologue, over NVLink peer memory', peer='one-kernel peer all-reduce over NVLink', nccl='NCCL all-reduce')[args.collective]})",
                 "l2": "inputs larger than L2: 4.88 GB of distinct weights per step, no flush needed",
                 "launch": "CUDA graph replay of the recorded op sequence",
                 "timing": f"{n_blocks} blocks of {args.steps} replays, CUDA events per block, median block reported",

@@ -417,6 +417,21 @@ int32_t zc_allreduce_sum_f32(zc_ctx* ctx, void* buf, uint64_t buf_size, uint64_t
 int32_t zc_allgather_f32(zc_ctx* ctx, const void* src, uint64_t src_size, uint64_t src_offset,
                          void* dst, uint64_t dst_size, uint64_t dst_offset, uint32_t n);
 int32_t zc_comm_destroy(zc_ctx* ctx);
+/* The exchange fused into the matvecs: a K-sharded projection whose partial result is summed over the ranks.
+ * Arguments as zc_dmmv; instead of writing y, the kernel's epilogue stores every finished row into the
+ * row's slot of every rank's receive buffer (plain peer stores over NVLink, value and tag in one 8-byte
+ * store: no flag, no fence, no multicast). The sum dst[i] (+)= sum over ranks (acc_mode 1: added to what dst
+ * holds, which must be the same on every rank) is formed, in rank order, by the *next* call on this context:
+ * zc_dmmv, zc_dmmv_multi, zc_dmmv_fused_gate_up_swiglu and zc_dmmv_push carry it in their own kernel (their
+ * threads wait, bounded, for all ranks' rows after the kernel's dependency wait; a call that reads or writes
+ * dst completes it first), any other call completes it with a small kernel of its own first. dst is valid
+ * once that next call has completed; zc_submit_and_wait and zc_end_record count as such a call. M <= 16384;
+ * every rank must issue the same sequence of pushes, an even number of them per recorded sequence. A wait
+ * that gives up reports ZC_ERR_TIMEOUT as the collectives above do. */
+int32_t zc_dmmv_push(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size,
+                     const void* x, uint64_t x_size, void* dst, uint64_t dst_size,
+                     uint32_t M, uint32_t K, uint64_t a_offset, uint64_t x_offset, uint64_t dst_offset,
+                     uint32_t acc_mode);
 
 /* ---- matvec without a context and without any allocation ----------------------------------------
  * No counterpart in the reference (its dispatch layer always owns descriptor pools and buffers).

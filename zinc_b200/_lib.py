@@ -26,6 +26,7 @@ _u32, _u64, _i32, _vp = C.c_uint32, C.c_uint64, C.c_int32, C.c_void_p
 # name -> argument types after the leading zc_ctx* (all return int32 status)
 _OPS = {
     "zc_dmmv": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u64, _u64, _u32],
+    "zc_dmmv_push": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u64, _u64, _u32],
     "zc_dmmv_fused_gate_up_swiglu": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32,
                                      _u64, _u64, _u64, _u64],
     "zc_dmmv_sigmoid_acc": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u64, _u64, _u32],

@@ -32,6 +32,8 @@ struct zc_ctx {
     uint8_t* comm_local = nullptr;
     bool comm_open[zc::kCommMaxRanks] = {false};
     bool comm_broken = false;          // a wait for a peer gave up: epochs no longer agree across ranks
+    zc::ConsumeArgs pending;           // pushed vectors not yet reduced (n != 0): the next call completes it
+    uint32_t push_parity = 0;          // receive-buffer half the next push uses
     uint32_t wait_limit = 0;           // 0: every kernel family's default; else polls per device-side wait
     // caller-owned scratch for the grouped MoE prefill path (zc_set_workspace)
     void* workspace = nullptr;
@@ -79,12 +81,44 @@ inline bool aligned(const void* p, uint64_t off, uint64_t a) {
     return ((reinterpret_cast<uintptr_t>(p) + off) % a) == 0;
 }
 
-#define ZC_ENTER(ctx)                                                              \
+// Entry of a call that may carry a pending reduction of pushed vectors in its own kernel.
+#define ZC_ENTER_CARRY(ctx)                                                        \
     do {                                                                           \
         if (!(ctx)) return ZC_ERR_INVALID_ARG;                                     \
         cudaError_t e_ = cudaSetDevice((ctx)->device);                             \
         if (e_ != cudaSuccess) return cuda_fail((ctx), e_, "cudaSetDevice");       \
     } while (0)
+// Entry of every other call: a pending reduction is completed by a small kernel first, so that whatever
+// the call does comes after it in stream order.
+#define ZC_ENTER(ctx)                                                              \
+    do {                                                                           \
+        ZC_ENTER_CARRY(ctx);                                                       \
+        const int32_t f_ = flush_pending(ctx);                                     \
+        if (f_ != ZC_OK) return f_;                                                \
+    } while (0)
+
+int32_t flush_pending(zc_ctx* ctx) {
+    if (ctx->pending.n == 0) return ZC_OK;
+    const zc::ConsumeArgs c = ctx->pending;
+    ctx->pending = zc::ConsumeArgs();
+    const cudaError_t e = zc::launch_consume(c, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "completing a pushed reduction");
+}
+
+// Hands a pending reduction to the launch described by `a` (which completes it in its own kernel, or in a small
+// kernel in front of it), unless that launch reads or writes the vector being reduced.
+inline int32_t take_pending(zc_ctx* ctx, DmmvArgs& a) {
+    if (ctx->pending.n == 0) return ZC_OK;
+    const uintptr_t lo = reinterpret_cast<uintptr_t>(ctx->pending.dst), hi = lo + (uintptr_t)ctx->pending.n * 4;
+    auto overlaps = [&](const void* p, uint64_t bytes) {
+        const uintptr_t q = reinterpret_cast<uintptr_t>(p);
+        return p != nullptr && q < hi && lo < q + bytes;
+    };
+    if (overlaps(a.x, (uint64_t)a.K * 4) || overlaps(a.y, (uint64_t)a.M * 4)) return flush_pending(ctx);
+    a.consume = ctx->pending;
+    ctx->pending = zc::ConsumeArgs();
+    return ZC_OK;
+}
 
 // Common checks of one matvec-shaped call.
 int32_t check_mat(zc_ctx* ctx, const char* fn, uint32_t type, const void* A, uint64_t a_size, uint64_t a_offset,
@@ -297,6 +331,7 @@ int32_t zc_comm_destroy(zc_ctx* ctx) {
     ctx->comm_local = nullptr;
     ctx->comm = CommArgs();
     ctx->comm_broken = false;
+    ctx->push_parity = 0;
     return ZC_OK;
 }
 
@@ -468,7 +503,7 @@ int32_t zc_moe_dmmv_supported(uint32_t type) { return dmmv_type_ok(type) ? 1 : 0
 int32_t zc_dmmv(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* x, uint64_t x_size, void* y,
                 uint64_t y_size, uint32_t M, uint32_t K, uint64_t a_offset, uint64_t x_offset, uint64_t y_offset,
                 uint32_t acc_mode) {
-    ZC_ENTER(ctx);
+    ZC_ENTER_CARRY(ctx);
     ZC_TRY(check_mat(ctx, "zc_dmmv", type, A, a_size, a_offset, (uint64_t)M * row_bytes_of(type, K), M, K));
     ZC_TRY(check_vec(ctx, "zc_dmmv", "x", x, x_size, x_offset, (uint64_t)K * 4, 16));
     ZC_TRY(check_vec(ctx, "zc_dmmv", "y", y, y_size, y_offset, (uint64_t)M * 4, 4));
@@ -482,13 +517,55 @@ int32_t zc_dmmv(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, cons
     a.a_end = u8(A, a_size);
     attach_scratch(ctx, a);
     cudaError_t e;
-    if (type == T_F32 && M <= 2048 && (K & 3u) == 0 && acc_mode == 0 && aligned(A, a_offset, 16))
+    const bool router = type == T_F32 && M <= 2048 && (K & 3u) == 0 && acc_mode == 0 && aligned(A, a_offset, 16);
+    if (router) ZC_TRY(flush_pending(ctx));
+    else ZC_TRY(take_pending(ctx, a));
+    if (router)
         // few f32 rows (a router): one CTA per row instead of one warp per row
         e = launch_rms_norm_dmmv_f32(a.x, nullptr, reinterpret_cast<const float*>(a.A), nullptr, a.y, M, K, 0.f,
                                      ctx->stream, &ctx->launches);
     else
         e = launch_dmmv(type, MODE_PLAIN, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_dmmv");
+}
+
+int32_t zc_dmmv_push(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* x, uint64_t x_size,
+                     void* dst, uint64_t dst_size, uint32_t M, uint32_t K, uint64_t a_offset, uint64_t x_offset,
+                     uint64_t dst_offset, uint32_t acc_mode) {
+    ZC_ENTER_CARRY(ctx);
+    const char* fn = "zc_dmmv_push";
+    ZC_TRY(comm_usable(ctx, fn));
+    ZC_TRY(check_mat(ctx, fn, type, A, a_size, a_offset, (uint64_t)M * row_bytes_of(type, K), M, K));
+    ZC_TRY(check_vec(ctx, fn, "x", x, x_size, x_offset, (uint64_t)K * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "dst", dst, dst_size, dst_offset, (uint64_t)M * 4, 4));
+    if (M > kPushMaxFloats)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: M=%u is beyond the %u rows the fused exchange carries", fn, M,
+                    kPushMaxFloats);
+    DmmvArgs a;
+    a.A = u8(A, a_offset);
+    a.x = f32p(x, x_offset);
+    a.y = f32m(dst, dst_offset);
+    a.M = M;
+    a.K = K;
+    a.a_end = u8(A, a_size);
+    attach_scratch(ctx, a);
+    ZC_TRY(take_pending(ctx, a));  // an earlier push into another vector rides along; into this one: completed first
+    const uint32_t parity = ctx->push_parity;
+    ctx->push_parity ^= 1u;
+    a.push.world = ctx->comm.world;
+    for (uint32_t r = 0; r < ctx->comm.world; ++r)
+        a.push.peers[r] = reinterpret_cast<uint2*>(ctx->comm.peers[r] + kCommPushOffset + parity * kCommPushParityBytes) +
+                          (size_t)ctx->comm.rank * kPushMaxFloats;
+    const cudaError_t e = launch_dmmv(type, MODE_PLAIN, a, ctx->stream, &ctx->launches);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, fn);
+    ctx->pending.slots = reinterpret_cast<uint2*>(ctx->comm_local + kCommPushOffset + parity * kCommPushParityBytes);
+    ctx->pending.dst = f32m(dst, dst_offset);
+    ctx->pending.n = M;
+    ctx->pending.world = ctx->comm.world;
+    ctx->pending.acc = acc_mode ? 1u : 0u;
+    ctx->pending.spin_limit = ctx->wait_limit ? ctx->wait_limit : (1u << 24);
+    ctx->pending.status = ctx->status_dev;
+    return ZC_OK;
 }
 
 int32_t zc_rms_norm_dmmv_f32(zc_ctx* ctx, const void* hidden, uint64_t hidden_size, const void* norm_weights,
@@ -518,7 +595,7 @@ int32_t zc_dmmv_multi(zc_ctx* ctx, uint32_t type, uint32_t n, const void* const*
                       const uint64_t* a_offset, const void* x, uint64_t x_size, uint64_t x_offset, void* const* y,
                       const uint64_t* y_size, const uint64_t* y_offset, const uint32_t* M, uint32_t K,
                       uint32_t acc_mode) {
-    ZC_ENTER(ctx);
+    ZC_ENTER_CARRY(ctx);
     const char* fn = "zc_dmmv_multi";
     if (n == 0 || n > 3) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: n must be 1, 2 or 3", fn);
     if (!A || !a_size || !a_offset || !y || !y_size || !y_offset || !M)
@@ -537,6 +614,17 @@ int32_t zc_dmmv_multi(zc_ctx* ctx, uint32_t type, uint32_t n, const void* const*
     a.K = K;
     a.acc_mode = acc_mode;
     attach_scratch(ctx, a);
+    a.M = 0;  // no single output vector: only x can collide with a pending reduction
+    ZC_TRY(take_pending(ctx, a));
+    for (uint32_t i = 0; i < n; ++i) {  // an output that is the vector being reduced: complete the reduction first
+        const uintptr_t lo = reinterpret_cast<uintptr_t>(a.consume.dst), hi = lo + (uintptr_t)a.consume.n * 4;
+        const uintptr_t q = reinterpret_cast<uintptr_t>(yp[i]);
+        if (a.consume.n && q < hi && lo < q + (uintptr_t)M[i] * 4) {
+            ctx->pending = a.consume;
+            a.consume = ConsumeArgs();
+            ZC_TRY(flush_pending(ctx));
+        }
+    }
     cudaError_t e = cudaSuccess;
     if (warp_dmmv_multi_eligible(type, n, Ap, M, K, a)) {
         e = launch_warp_dmmv_multi(n, Ap, yp, M, a, ctx->stream, &ctx->launches);
@@ -546,6 +634,7 @@ int32_t zc_dmmv_multi(zc_ctx* ctx, uint32_t type, uint32_t n, const void* const*
             ai.A = Ap[i];
             ai.y = yp[i];
             ai.M = M[i];
+            if (i) ai.consume = ConsumeArgs();  // the first launch completes a pending reduction
             e = launch_dmmv(type, MODE_PLAIN, ai, ctx->stream, &ctx->launches);
         }
     }
@@ -556,7 +645,7 @@ int32_t zc_dmmv_fused_gate_up_swiglu(zc_ctx* ctx, uint32_t type, const void* Wg,
                                      uint64_t wu_size, const void* x, uint64_t x_size, void* out, uint64_t out_size,
                                      uint32_t M, uint32_t K, uint64_t gate_offset, uint64_t up_offset,
                                      uint64_t x_offset, uint64_t out_offset) {
-    ZC_ENTER(ctx);
+    ZC_ENTER_CARRY(ctx);
     const char* fn = "zc_dmmv_fused_gate_up_swiglu";
     ZC_TRY(check_mat(ctx, fn, type, Wg, wg_size, gate_offset, (uint64_t)M * row_bytes_of(type, K), M, K));
     ZC_TRY(check_mat(ctx, fn, type, Wu, wu_size, up_offset, (uint64_t)M * row_bytes_of(type, K), M, K));
@@ -570,6 +659,7 @@ int32_t zc_dmmv_fused_gate_up_swiglu(zc_ctx* ctx, uint32_t type, const void* Wg,
     a.M = M;
     a.K = K;
     attach_scratch(ctx, a);
+    ZC_TRY(take_pending(ctx, a));
     cudaError_t e = launch_dmmv(type, MODE_GATE_UP_SWIGLU, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }

@@ -167,7 +167,54 @@ __global__ void __launch_bounds__(kThreads) allgather_oneshot_kernel(const CommA
     }
 }
 
+__device__ __forceinline__ uint2 ld_volatile_pair(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+
+// The consumer half of the fused exchange as a kernel of its own, for the call sites where the next launch on
+// the stream cannot carry it (same loop as consume_pushed in the streaming kernels).
+__global__ void __launch_bounds__(256) consume_kernel(const ConsumeArgs c) {
+    pdl_enter();
+    for (uint32_t i = threadIdx.x * gridDim.x + blockIdx.x; i < c.n; i += blockDim.x * gridDim.x) {
+        float s = c.acc ? c.dst[i] : 0.f;
+        for (uint32_t r = 0; r < c.world; ++r) {
+            uint2* p = c.slots + (size_t)r * kPushMaxFloats + i;
+            uint2 q = ld_volatile_pair(p);
+            uint32_t spins = 0;
+            while (q.y == 0u) {
+                if (++spins > c.spin_limit) {
+                    c.status[0] = 1;
+                    c.status[1] = 400u + r;
+                    break;
+                }
+                q = ld_volatile_pair(p);
+            }
+            s += __uint_as_float(q.x);
+            *p = make_uint2(0u, 0u);
+        }
+        c.dst[i] = s;
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_consume(const ConsumeArgs& c, cudaStream_t s, uint64_t* launches) {
+    if (c.n == 0) return cudaSuccess;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((c.n + 255) / 256, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, consume_kernel, c);
+    if (e == cudaSuccess && launches) ++*launches;
+    return e;
+}
 
 cudaError_t launch_allgather_oneshot(const CommArgs& c, const float* src, float* dst, uint32_t n, cudaStream_t s,
                                      uint64_t* launches) {

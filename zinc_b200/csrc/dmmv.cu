@@ -51,8 +51,14 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
             for (int r = 0; r < NR; ++r) {
                 if (row0 + r < a.M) {
                     float* yp = a.y + row0 + r;
-                    if constexpr (MODE == MODE_SIGMOID_ACC) *yp += g * acc[r];
-                    else *yp = a.acc_mode ? *yp + acc[r] : acc[r];
+                    if constexpr (MODE == MODE_SIGMOID_ACC) {
+                        *yp += g * acc[r];
+                    } else if (a.push.world) {  // fused exchange: the row goes to every rank's receive buffer
+                        const uint2 pv = make_uint2(__float_as_uint(acc[r]), 1u);
+                        for (uint32_t pr = 0; pr < a.push.world; ++pr) a.push.peers[pr][row0 + r] = pv;
+                    } else {
+                        *yp = a.acc_mode ? *yp + acc[r] : acc[r];
+                    }
                 }
             }
         }
@@ -223,8 +229,13 @@ cudaError_t launch_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t
     if (wbytes >= kStreamMinBytes) {
         if (warp_dmmv_eligible(type, mode, a)) return launch_warp_dmmv(type, mode, a, s, launches);
         if (q6k_dmmv_eligible(type, mode, a)) return launch_q6k_dmmv(mode, a, s, launches);
-        if (mxfp4_dmmv_eligible(type, mode, a)) return launch_mxfp4_dmmv(a, s, launches);
     }
+    // the kernels below do not carry a pending reduction: complete it first
+    if (a.consume.n) {
+        const cudaError_t ec = launch_consume(a.consume, s, launches);
+        if (ec != cudaSuccess) return ec;
+    }
+    if (wbytes >= kStreamMinBytes && mxfp4_dmmv_eligible(type, mode, a)) return launch_mxfp4_dmmv(a, s, launches);
     cudaError_t e;
     // 128-bit weight loads need every block start 16-byte aligned: true for the
     // 144/176-byte K-quant blocks when the base, the second base and the expert

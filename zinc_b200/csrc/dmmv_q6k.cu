@@ -328,6 +328,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
     XRegs6 xr;
     load_x6<kWarps>(xr, a.x, bpr * 256, kMoe ? bpe : 0u, kMoe ? a.x_slot_stride : 0u,
                     kMoe ? a.routing + a.nseg : nullptr, warp, lane);
+    if (a.consume.n) consume_pushed(a.consume, blockIdx.x, gridDim.x, tid, kWarps * 32);
 
     if (tid < kZeroBytes6 / 16) reinterpret_cast<uint4*>(s.zeros)[tid] = make_uint4(0u, 0u, 0u, 0u);
     if (tid < kWarps) s.sflags[tid] = 0u;
@@ -496,6 +497,8 @@ cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t st, uint64
     wa.status = a.status;
     wa.spin_limit = a.spin_limit;
     wa.nseg = 0;
+    wa.push = a.push;
+    wa.consume = a.consume;
     cudaError_t e = mode == MODE_PLAIN ? launch_cfg6<EPI_PLAIN>(wa, a.a_end, st, a.sm_count)
                                        : launch_cfg6<EPI_SIGMOID_ACC>(wa, a.a_end, st, a.sm_count);
     if (e == cudaSuccess && launches) ++*launches;

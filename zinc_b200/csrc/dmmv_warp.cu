@@ -252,6 +252,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
     pdl_wait();
     XRegs xr;
     load_x<kWarps>(xr, a.x, a.K, warp, lane);
+    if (a.consume.n) consume_pushed(a.consume, blockIdx.x, gridDim.x, tid, kWarps * 32);
 
     // ---- activation vector -> digit planes (all warps), zero region, flags ----
     if (tid < kZeroBytes / 16) reinterpret_cast<uint4*>(s.zeros)[tid] = make_uint4(0u, 0u, 0u, 0u);
@@ -433,6 +434,8 @@ cudaError_t launch_warp_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStr
     wa.status = a.status;
     wa.spin_limit = a.spin_limit;
     wa.nseg = 0;
+    wa.push = a.push;
+    wa.consume = a.consume;
     cudaError_t e;
     switch (mode) {
         case MODE_PLAIN: e = launch_cfg<1, EPI_PLAIN>(wa, st, a.sm_count); break;
@@ -473,6 +476,7 @@ cudaError_t launch_warp_dmmv_multi(uint32_t n, const uint8_t* const* A, float* c
     wa.gpartial = common.scratch_partial;
     wa.status = common.status;
     wa.spin_limit = common.spin_limit;
+    wa.consume = common.consume;
     wa.nseg = n;
     const uint64_t row_bytes = (uint64_t)(common.K >> 8) * 144;
     uint32_t t0 = 0;

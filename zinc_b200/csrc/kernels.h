@@ -36,6 +36,27 @@ enum DmmvMode : int {
     MODE_MOE_BATCHED = 7,    // per (token t, slot s): Y[t][s] = W[routing[t*n_used+s]] X[t]
 };
 
+// ---- tensor-parallel exchange fused into the matvecs (peer memory over NVLink, no multicast) -------------
+// A K-sharded projection produces a partial output vector on every rank. Its epilogue stores every finished
+// row, as {f32 bits, 1}, into the row's slot of *every* rank's receive buffer (plain peer stores; an 8-byte
+// store is one transaction, so value and tag arrive together: no flag, no fence). The next matvec on the
+// stream carries the other half: its threads wait, bounded, for the tagged values of all ranks in the local
+// buffer, add them in rank order (bit-identical sums everywhere), write the reduced vector and clear the tags.
+constexpr uint32_t kCommMaxRanks = 8;
+constexpr uint32_t kPushMaxFloats = 16384;  // longest vector the fused exchange carries
+struct PushArgs {
+    uint2* peers[kCommMaxRanks] = {};  // [r]: this rank's slot (current parity) in rank r's receive buffer
+    uint32_t world = 0;                // 0: no push, the kernel writes y
+};
+struct ConsumeArgs {
+    uint2* slots = nullptr;   // local receive buffer, current parity: [world][kPushMaxFloats]
+    float* dst = nullptr;     // dst[i] (+)= sum over ranks
+    uint32_t n = 0;           // 0: nothing to consume
+    uint32_t world = 0, acc = 0;
+    uint32_t spin_limit = 1u << 24;
+    uint32_t* status = nullptr;
+};
+
 struct DmmvArgs {
     const uint8_t* A = nullptr;   // weights (gate weights for the gate/up modes)
     const uint8_t* A2 = nullptr;  // up weights for the gate/up modes
@@ -60,6 +81,8 @@ struct DmmvArgs {
     uint32_t* status = nullptr;
     uint32_t spin_limit = 1u << 26;     // polls after which a device-side wait gives up
     int sm_count = 0;
+    PushArgs push;        // MODE_PLAIN: store the result rows into every rank's receive buffer instead of y
+    ConsumeArgs consume;  // a pending reduction of pushed vectors that this launch (or a small kernel before it) completes
     // first byte past the buffers that hold A / A2 (kernels that fetch aligned supersets of unaligned rows
     // must not read beyond them)
     const uint8_t* a_end = nullptr;
@@ -168,7 +191,6 @@ cudaError_t launch_moe_route_scatter(const uint32_t* routing, const float* src, 
                                      uint64_t* launches);
 
 // ---- one-shot all-reduce over peer memory (comm.cu) -------------------------------------------
-constexpr uint32_t kCommMaxRanks = 8;
 constexpr size_t kCommSlotBytes = 64 * 1024;  // largest vector: 16384 floats
 constexpr size_t kCommGatherBytes = 1024 * 1024;  // largest gathered vector: 262144 floats over all ranks
 constexpr size_t kCommGatherOffset = 2 * kCommMaxRanks * kCommSlotBytes;       // [2 parities][kCommGatherBytes]
@@ -176,7 +198,11 @@ constexpr size_t kCommFlagOffset = kCommGatherOffset + 2 * kCommGatherBytes;   /
 constexpr size_t kCommGatherFlagOffset = kCommFlagOffset + 2 * kCommMaxRanks * sizeof(uint32_t);
 constexpr size_t kCommEpochOffset = kCommGatherFlagOffset + 2 * kCommMaxRanks * sizeof(uint32_t);
 // words at kCommEpochOffset: [0] reduce epoch, [1] gather epoch, [2] gather arrivals, [3] gather departures
-constexpr size_t kCommBufBytes = kCommEpochOffset + 256;
+constexpr size_t kCommPushOffset = kCommEpochOffset + 256;  // fused exchange: [2 parities][ranks][kPushMaxFloats] uint2
+constexpr size_t kCommPushParityBytes = (size_t)kCommMaxRanks * kPushMaxFloats * sizeof(uint2);
+constexpr size_t kCommBufBytes = kCommPushOffset + 2 * kCommPushParityBytes;
+// Completes a pending reduction on its own (when the next call on the stream cannot carry it).
+cudaError_t launch_consume(const ConsumeArgs& c, cudaStream_t s, uint64_t* launches);
 struct CommArgs {
     uint8_t* peers[kCommMaxRanks];  // receive buffer of every rank as mapped in this process; [rank] is local
     uint32_t rank = 0, world = 0;

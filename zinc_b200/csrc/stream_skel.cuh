@@ -42,6 +42,8 @@ struct WarpArgs {
     float* y2;
     uint32_t spin_limit = 1u << 26;  // polls after which a split-K wait gives up (status {1, site})
     uint32_t x_slot_stride;  // MoE down projection: elements between the slots' activation vectors
+    PushArgs push;           // EPI_PLAIN: rows go to every rank's receive buffer instead of y
+    ConsumeArgs consume;     // pending reduction completed by this launch's threads after the dependency wait
     uint32_t act = 0;        // EPI_PAIR only: 0 write both streams, 1 y = silu(gate) * up, 2 the GPT-OSS form
 };
 
@@ -104,6 +106,37 @@ __device__ __forceinline__ void mma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1, 
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ uint2 ld_volatile_u2(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+
+// The consumer half of the fused exchange, spread over the grid: element i belongs to thread i / n_ctas of CTA
+// i % n_ctas. Waits (bounded) for the tagged value of every rank, adds them in rank order and clears the tags.
+__device__ __forceinline__ void consume_pushed(const ConsumeArgs& c, uint32_t cta, uint32_t n_ctas, uint32_t tid,
+                                               uint32_t n_threads) {
+    for (uint32_t i = tid * n_ctas + cta; i < c.n; i += n_threads * n_ctas) {
+        float s = c.acc ? c.dst[i] : 0.f;
+        for (uint32_t r = 0; r < c.world; ++r) {
+            uint2* p = c.slots + (size_t)r * kPushMaxFloats + i;
+            uint2 q = ld_volatile_u2(p);
+            uint32_t spins = 0;
+            while (q.y == 0u) {
+                if (++spins > c.spin_limit) {
+                    c.status[0] = 1;
+                    c.status[1] = 400u + r;
+                    break;
+                }
+                q = ld_volatile_u2(p);
+            }
+            s += __uint_as_float(q.x);
+            *p = make_uint2(0u, 0u);
+        }
+        c.dst[i] = s;
+    }
+}
+
 enum { EPI_PLAIN = 0, EPI_GATE_UP = 1, EPI_SIGMOID_ACC = 2, EPI_PAIR = 3, EPI_ACC = 4 };
 
 template <int NS, int EPI>
@@ -123,16 +156,16 @@ __device__ __forceinline__ void write_row(const WarpArgs& a, uint32_t row, const
     } else if constexpr (EPI == EPI_SIGMOID_ACC) {
         a.y[row] += (1.0f / (1.0f + expf(-__ldg(a.gate)))) * v[0];
     } else {
-        a.y[row] = a.acc_mode ? a.y[row] + v[0] : v[0];
+        if (a.push.world) {
+            const uint2 pv = make_uint2(__float_as_uint(v[0]), 1u);
+            for (uint32_t r = 0; r < a.push.world; ++r) a.push.peers[r][row] = pv;
+        } else {
+            a.y[row] = a.acc_mode ? a.y[row] + v[0] : v[0];
+        }
     }
 }
 
 
-__device__ __forceinline__ uint2 ld_volatile_u2(const uint2* p) {
-    uint2 v;
-    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
-}
 
 // Ends a tile for this warp. v[i][r]: sums of stream i for rows g (r = 0) and g+8 (r = 1), already
 // reduced over the four lanes of a row.

@@ -80,7 +80,7 @@ class DecodeStep:
     act: object = None
     hidden: object = None
     logits: object = None
-    allreduce: Optional[Callable] = None
+    allreduce: Optional[Callable] = None   # None with world > 1: the exchange fused into the matvecs (zc_dmmv_push)
     allgather: Optional[Callable] = None
 
     @staticmethod
@@ -160,7 +160,10 @@ class DecodeStep:
                                    [s.q_dim // g, s.kv_dim // g, s.kv_dim // g], s.hidden)
             if g == 1:
                 dd.recordDispatch(s.t_attn, lw.wo, self.attn_out, self.hidden, s.hidden, s.q_dim, acc_mode=1)
+            elif self.allreduce is None:  # K-sharded, rows pushed to every rank, summed by the next launch
+                dd.recordDispatchPush(s.t_attn, lw.wo, self.attn_out, self.hidden, s.hidden, s.q_dim // g, acc_mode=1)
             else:  # K-sharded: partial sums, then all-reduce into the replicated hidden vector
+                # rank 0 adds to the residual, the others overwrite it: the residual enters the sum once
                 dd.recordDispatch(s.t_attn, lw.wo, self.attn_out, self.hidden, s.hidden, s.q_dim // g,
                                   acc_mode=1 if self.rank == 0 else 0)
                 self.allreduce(self.hidden)
@@ -168,6 +171,8 @@ class DecodeStep:
                                              s.hidden)
             if g == 1:
                 dd.recordDispatch(s.t_down, lw.wdown, self.ffn_act_in, self.hidden, s.hidden, s.ffn, acc_mode=1)
+            elif self.allreduce is None:
+                dd.recordDispatchPush(s.t_down, lw.wdown, self.ffn_act_in, self.hidden, s.hidden, s.ffn // g, acc_mode=1)
             else:
                 dd.recordDispatch(s.t_down, lw.wdown, self.ffn_act_in, self.hidden, s.hidden, s.ffn // g,
                                   acc_mode=1 if self.rank == 0 else 0)

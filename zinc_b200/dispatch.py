@@ -257,6 +257,13 @@ class DmmvDispatch:
         self.ctx.call("zc_dmmv", quant_type, A.ptr, A.size, x.ptr, x.size, y.ptr, y.size, M, K,
                       a_offset, x_offset, y_offset, acc_mode)
 
+    # recordDispatch for a K-sharded projection on N GPUs: the partial result is pushed to every rank and
+    # summed into dst by the next call on the context (no counterpart in the single-GPU reference)
+    def recordDispatchPush(self, quant_type, A, x, dst, M, K, a_offset=0, x_offset=0, dst_offset=0, acc_mode=0):
+        A, x, dst = _buf(A), _buf(x), _buf(dst)
+        self.ctx.call("zc_dmmv_push", quant_type, A.ptr, A.size, x.ptr, x.size, dst.ptr, dst.size, M, K,
+                      a_offset, x_offset, dst_offset, acc_mode)
+
     # recordBatchDispatchPush (src/compute/dmmv.zig:880-926) + dispatchProjectionBatched chunk loop
     def recordDispatchMulti(self, quant_type, As, x, ys, Ms, K, a_offsets=None, x_offset=0, y_offsets=None,
                             acc_mode=0):
