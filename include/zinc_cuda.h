@@ -365,6 +365,15 @@ int32_t zc_moe_weighted_bias_acc(zc_ctx* ctx, void* a, uint64_t a_size, const vo
                                  const void* routing, uint64_t routing_size,
                                  uint32_t n, uint32_t n_used, uint32_t n_experts);
 
+/* Expert parallelism (no counterpart in the single-GPU reference): out = routing with the ids of the experts
+ * [expert_lo, expert_hi) renumbered from 0 and every other id replaced by 0xFFFFFFFF ("no expert in this slot on
+ * this rank"); the k weights of a row are copied. Every MoE entry point reads no weights for such a slot and
+ * contributes zeros for it, so a rank that holds a contiguous range of whole experts runs the same calls on its
+ * own stack with the filtered routing, and the ranks' partial hidden vectors are then summed. Rows of 2k words. */
+int32_t zc_moe_ep_filter(zc_ctx* ctx, const void* routing, uint64_t routing_size, void* out, uint64_t out_size,
+                         uint32_t k, uint32_t n_tokens, uint32_t routing_stride, uint32_t out_stride,
+                         uint32_t expert_lo, uint32_t expert_hi);
+
 /* counts[e] = number of cells equal to e in the routing capture buffer of one
  * layer. Replaces recordCountExperts (src/compute/dmmv.zig:981-1028;
  * src/shaders/count_experts.comp:58-83). d_offset_bytes as there. */

@@ -532,3 +532,85 @@ def test_moe_decode_tensor_parallel_slices(gpu, cfg):
         # hidden += partial (the zeroing is a memset, not a kernel); only rank 0 adds the down bias
         assert n_part == n_full + shape.n_layers - (shape.n_layers if shape.biases and rank else 0)
     assert rel_l2(total, want) <= 1e-5
+
+
+def test_moe_ep_filter_and_skipped_slots(gpu, oracle):
+    """zc_moe_ep_filter against numpy, and every MoE kernel path with a slot that holds no expert: the slot
+    reads nothing and contributes zeros (streaming Q4_K gate+up, generic paths, streaming Q6_K down)."""
+    torch, ctx, dd = gpu
+    g = synth.rng(211, 0)
+    SKIP = 0xFFFFFFFF
+    T, k = 5, 4
+    ids = g.integers(0, 16, size=(T, k)).astype(np.uint32)
+    wts = g.random((T, k)).astype(np.float32)
+    rt = np.concatenate([ids, wts.view(np.uint32)], axis=1)
+    out = torch.zeros(T * 2 * k, dtype=torch.int32, device="cuda")
+    dd.dispatchMoeEpFilter(dev(torch, rt), out, k, 4, 8, n_tokens=T)
+    ctx.submit_and_wait()
+    got = out.cpu().numpy().view(np.uint32).reshape(T, 2 * k)
+    want = np.where((ids >= 4) & (ids < 8), ids - 4, SKIP).astype(np.uint32)
+    assert np.array_equal(got[:, :k], want) and np.array_equal(got[:, k:], wts.view(np.uint32))
+
+    for E, M, K, n_used in ((12, 512, 2048, 8), (4, 33, 512, 3)):   # streaming kernel / one warp per row pair
+        wg, stride = stacked(g, zb.Q4_K, E, M, K)
+        wu, _ = stacked(g, zb.Q4_K, E, M, K)
+        x = synth.activations(g, 1, K)
+        sel = np.array([(5 * i + 1) % E for i in range(n_used)], np.uint32)
+        sel[1] = SKIP
+        if n_used > 4:
+            sel[6] = SKIP
+        yg, yu = out_with_canary(torch, n_used * M, init=5.0), out_with_canary(torch, n_used * M, init=5.0)
+        dd.dispatchMoeFusedGateUp(zb.Q4_K, dev(torch, wg), dev(torch, wu), dev(torch, x), yg, yu,
+                                  dev(torch, routing_buf(sel)), M, K, stride, n_used, 0)
+        ctx.submit_and_wait()
+        safe = np.where(sel == SKIP, 0, sel).astype(np.uint32)
+        live = (sel != SKIP)
+        xs = np.repeat(x, n_used, axis=0)
+        for y, w in ((yg, wg), (yu, wu)):
+            ref = oracle.moe_dmmv_f64(w, zb.Q4_K, M, K, stride, safe, K, xs)
+            have = y[:n_used * M].cpu().numpy().reshape(n_used, M)
+            assert canary_intact(y, n_used * M)
+            assert np.all(have[~live] == 0.0)
+            assert rel_l2(have[live], ref[live]) <= TOL
+
+    for t, E, M, K, n_used in ((zb.Q6_K, 3, 4100, 1024, 3), (zb.Q4_K, 6, 203, 512, 4)):   # streaming Q6_K / generic
+        w, stride = stacked(g, t, E, M, K)
+        sel = np.array([(3 * i + E - 1) % E for i in range(n_used)], np.uint32)
+        sel[1] = SKIP
+        wv = (g.random(n_used).astype(np.float32) + np.float32(0.1))
+        x = synth.activations(g, n_used, K)
+        h0 = synth.activations(g, M)
+        y = out_with_canary(torch, M)
+        y[:M] = dev(torch, h0)
+        dd.dispatchMoeFusedDownAcc(t, dev(torch, w), dev(torch, x.reshape(-1)), y, dev(torch, routing_buf(sel, wv)), M, K,
+                                   stride, n_used, K)
+        ctx.submit_and_wait()
+        safe = np.where(sel == SKIP, 0, sel).astype(np.uint32)
+        per = oracle.moe_dmmv_f64(w, t, M, K, stride, safe, K, x)
+        wl = np.where(sel == SKIP, 0.0, wv.astype(np.float64))
+        want = h0 + (wl[:, None] * per).sum(0)
+        assert canary_intact(y, M)
+        assert rel_l2(y[:M].cpu().numpy() - h0, want - h0) <= TOL
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_moe_decode_expert_parallel_ranks(gpu, world):
+    # the per-rank parts of an expert-parallel MoE step (whole experts per rank, shared expert on rank 0), run
+    # one after the other on this GPU without the collective: they must add up to the single-rank result
+    torch, ctx, dd = gpu
+    from zinc_b200.moe_step import MoeDecode, MoeShape
+
+    shape = MoeShape(hidden=512, n_experts=16, top_k=4, ffn=512, t_gate_up=zb.Q4_K, t_down=zb.Q6_K,
+                     rule=zb.ROUTE_SOFTMAX_ALL_RENORM, shared=True, oai=False, n_layers=2)
+    full = MoeDecode.build(torch, dd, shape, seed=5)
+    full.record()
+    ctx.submit_and_wait()
+    want = full.hidden.cpu().numpy().astype(np.float64)
+    total = np.zeros_like(want)
+    for rank in range(world):
+        part = MoeDecode.build(torch, dd, shape, seed=5, rank=rank, world=world, allreduce=None, parallel="ep")
+        assert (part.e_lo, part.e_hi) == (rank * 16 // world, (rank + 1) * 16 // world) and part.ffn_local == 512
+        part.record()
+        ctx.submit_and_wait()
+        total += part.hidden.cpu().numpy().astype(np.float64)
+    assert rel_l2(total, want) <= 1e-5

@@ -90,6 +90,25 @@ def _worker(rank: int, world: int, port: int, q):
         dist.all_reduce(tm)
         res["moe_tp"] = float(np.abs(tm.numpy() - full).max() / np.abs(full).max())
 
+        # MoE experts, expert parallel: rank r holds the whole experts [r E / N, (r+1) E / N); the routing filter
+        # renumbers the selected ids in that range and skips the others; partial hidden vectors are summed
+        e_lo, e_hi = rank * E // world, (rank + 1) * E // world
+        keep = (ids >= e_lo) & (ids < e_hi)
+        if keep.any():
+            lids = (ids[keep] - e_lo).astype(np.uint32)
+            kk = int(keep.sum())
+            xl = np.repeat(x[None, :H], kk, axis=0)
+            wg_p, wu_p, wd_p = wg_e[e_lo * sg:e_hi * sg], wu_e[e_lo * sg:e_hi * sg], wd_e[e_lo * sdn:e_hi * sdn]
+            gate = zo.moe_dmmv_f64(wg_p, zb.MXFP4, F, H, sg, lids, H, xl).astype(np.float32)
+            up = zo.moe_dmmv_f64(wu_p, zb.MXFP4, F, H, sg, lids, H, xl).astype(np.float32)
+            act = zo.swiglu(gate.reshape(-1), up.reshape(-1)).reshape(kk, F)
+            mine = (wts[keep][:, None] * zo.moe_dmmv_f64(wd_p, zb.MXFP4, H, F, sdn, lids, F, act)).sum(0)
+        else:
+            mine = np.zeros(H)
+        te = torch.from_numpy(np.ascontiguousarray(mine))
+        dist.all_reduce(te)
+        res["moe_ep"] = float(np.abs(te.numpy() - full).max() / np.abs(full).max())
+
         # refusals
         for fn, args in ((shard.row_range, (5, rank, world)), (shard.k_range, (zb.Q6_K, 768, rank, world))):
             try:
@@ -120,6 +139,7 @@ def test_two_rank_tensor_parallel_ffn():
         assert out[r]["row_gather"] == 0.0
         assert out[r]["ffn_pair"] <= 1e-12
         assert out[r]["moe_tp"] <= 1e-6   # f32 SwiGLU outputs feed the down projection
+        assert out[r]["moe_ep"] <= 1e-12  # whole experts: the same numbers, summed in another order
         assert out[r]["refusal"] is True
 
 

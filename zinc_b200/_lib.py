@@ -55,6 +55,7 @@ _OPS = {
     "zc_moe_weighted_bias_acc": [_vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32],
     "zc_set_wait_limit": [_u32],
     "zc_comm_connect_local": [_u32, _vp, _u64],
+    "zc_moe_ep_filter": [_vp, _u64, _vp, _u64, _u32, _u32, _u32, _u32, _u32, _u32],
     "zc_count_experts": [_vp, _u64, _vp, _u64, _u32, _u32, _u32, _u32, _u32, _u64],
     "zc_moe_route_pack": [_vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _u32, _u32],
     "zc_moe_route_scatter": [_vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _u32],

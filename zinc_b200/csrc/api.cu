@@ -1057,6 +1057,21 @@ int32_t zc_moe_weighted_bias_acc(zc_ctx* ctx, void* a, uint64_t a_size, const vo
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 
+int32_t zc_moe_ep_filter(zc_ctx* ctx, const void* routing, uint64_t routing_size, void* out, uint64_t out_size,
+                         uint32_t k, uint32_t n_tokens, uint32_t routing_stride, uint32_t out_stride,
+                         uint32_t expert_lo, uint32_t expert_hi) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_ep_filter";
+    if (k == 0 || n_tokens == 0 || routing_stride < 2 * k || out_stride < 2 * k || expert_lo >= expert_hi)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: zero count, stride < 2k or empty expert range", fn);
+    ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0, ((uint64_t)(n_tokens - 1) * routing_stride + 2 * k) * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "out", out, out_size, 0, ((uint64_t)(n_tokens - 1) * out_stride + 2 * k) * 4, 4));
+    const cudaError_t e = launch_moe_ep_filter(static_cast<const uint32_t*>(routing), static_cast<uint32_t*>(out), k,
+                                               n_tokens, routing_stride, out_stride, expert_lo, expert_hi, ctx->stream,
+                                               &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
 int32_t zc_count_experts(zc_ctx* ctx, const void* routing, uint64_t routing_size, void* counts,
                          uint64_t counts_size, uint32_t n_tokens, uint32_t n_layers, uint32_t layer,
                          uint32_t n_experts_used, uint32_t n_experts, uint64_t d_offset_bytes) {

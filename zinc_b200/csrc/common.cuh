@@ -51,6 +51,10 @@ __device__ __forceinline__ float e2m1_to_f32(uint32_t n) {
 // beyond n_max (the number of experts the weight buffer holds) is recorded in the status words as
 // {2, id} (reported by zc_submit_and_wait as an invalid argument) and replaced by expert 0, so that no
 // kernel ever forms an address outside the expert stack.
+// A routing slot that holds kSkipExpert names no expert: under expert parallelism the slots whose expert lives
+// on another rank are rewritten to it (zc_moe_ep_filter). Such a slot reads no weights and contributes zeros.
+constexpr uint32_t kSkipExpert = 0xFFFFFFFFu;
+
 __device__ __forceinline__ uint32_t checked_expert(uint32_t e, uint32_t n_max, uint32_t* status) {
     if (e < n_max) return e;
     if (status) {

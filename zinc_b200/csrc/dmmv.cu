@@ -74,7 +74,14 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
         const uint32_t slot = blockIdx.y;
         const uint32_t row0 = (blockIdx.x * kWarps + warp) * NR;
         if (row0 >= a.M) return;
-        const uint8_t* base = a.A + (uint64_t)checked_expert(__ldg(a.routing + slot), a.n_experts_max, a.status) * a.expert_stride;
+        const uint32_t e_raw = __ldg(a.routing + slot);
+        if (e_raw == kSkipExpert) {  // no expert in this slot on this rank: zeros
+            if (lane == 0)
+                for (int r = 0; r < NR; ++r)
+                    if (row0 + r < a.M) a.y[(size_t)slot * a.M + row0 + r] = 0.f;
+            return;
+        }
+        const uint8_t* base = a.A + (uint64_t)checked_expert(e_raw, a.n_experts_max, a.status) * a.expert_stride;
         const float* x = a.x + (size_t)slot * a.x_expert_stride;
         const uint8_t* rows[NR];
 #pragma unroll
@@ -95,7 +102,17 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
         const uint32_t slot = blockIdx.y;
         const uint32_t row0 = (blockIdx.x * kWarps + warp) * NR;
         if (row0 >= a.M) return;
-        const uint64_t ebase = (uint64_t)checked_expert(__ldg(a.routing + slot), a.n_experts_max, a.status) * a.expert_stride;
+        const uint32_t e_raw = __ldg(a.routing + slot);
+        if (e_raw == kSkipExpert) {  // no expert in this slot on this rank: zeros
+            if (lane == 0)
+                for (int r = 0; r < NR; ++r)
+                    if (row0 + r < a.M) {
+                        a.y[(size_t)slot * a.M + row0 + r] = 0.f;
+                        if (!a.act) a.y2[(size_t)slot * a.M + row0 + r] = 0.f;
+                    }
+            return;
+        }
+        const uint64_t ebase = (uint64_t)checked_expert(e_raw, a.n_experts_max, a.status) * a.expert_stride;
         const float* x = a.x + (size_t)slot * a.x_expert_stride;
         const uint8_t* rows[2 * NR];
 #pragma unroll
@@ -145,6 +162,7 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
         const uint32_t row = blockIdx.x * kWarps + warp;
         if (row >= a.M) return;
         const uint32_t e_raw = __ldg(a.routing + (size_t)tok * a.n_used + slot);
+        if (e_raw == kSkipExpert) return;
         const uint32_t e = checked_expert(e_raw, a.n_experts_max, a.status);
         if (e != e_raw) return;  // not an expert: reported, its output row stays untouched (as on the grouped path)
         const uint8_t* rows[1] = {a.A + (uint64_t)e * a.expert_stride + (uint64_t)row * row_bytes};
@@ -159,7 +177,9 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
 #pragma unroll
         for (int r = 0; r < NR; ++r) total[r] = 0.f;
         for (uint32_t s = 0; s < a.n_used; ++s) {
-            const uint8_t* base = a.A + (uint64_t)checked_expert(__ldg(a.routing + s), a.n_experts_max, a.status) * a.expert_stride;
+            const uint32_t e_raw = __ldg(a.routing + s);
+            if (e_raw == kSkipExpert) continue;
+            const uint8_t* base = a.A + (uint64_t)checked_expert(e_raw, a.n_experts_max, a.status) * a.expert_stride;
             const uint8_t* rows[NR];
 #pragma unroll
             for (int r = 0; r < NR; ++r) rows[r] = base + (uint64_t)min(row0 + r, a.M - 1) * row_bytes;

@@ -263,7 +263,9 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
         if constexpr (kMoe) {
             const uint32_t slot = b / bpe;
             lb = b - slot * bpe;
-            return a.A[0] + (uint64_t)checked_expert(__ldg(a.routing + slot), a.n_experts_max, a.status) * a.expert_stride;
+            const uint32_t e_raw = __ldg(a.routing + slot);
+            if (e_raw == kSkipExpert) return nullptr;  // no expert in this slot on this rank
+            return a.A[0] + (uint64_t)checked_expert(e_raw, a.n_experts_max, a.status) * a.expert_stride;
         } else {
             lb = b;
             return a.A[0];
@@ -302,6 +304,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
             const uint8_t* mat = matrix_of(p_blk, lb);
 #pragma unroll
             for (int i = 0; i < kPiecesLane6; ++i) {
+                if (kMoe && mat == nullptr) break;  // nothing to fetch
                 const uint32_t r = piece[i] & 0xFFu, col = piece[i] >> 8;
                 const uint32_t row = min(row0 + r, a.M - 1);
                 const uint8_t* start = mat + (uint64_t)row * row_bytes + lb * 210u;
@@ -351,25 +354,32 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
         __syncwarp();
         // byte offset of the block inside each row's aligned superset
         uint32_t oA, oB;
+        bool skip = false;  // MoE: the block belongs to a slot without an expert on this rank
         if constexpr (kRowsAligned) {
             oA = oB = (blk * 210u) & 15u;
         } else {
             const uint32_t rowA = min(tile * 16 + g, a.M - 1), rowB = min(tile * 16 + g + 8, a.M - 1);
             uint32_t lb;
             const uint8_t* mat = matrix_of(blk, lb);
+            skip = kMoe && mat == nullptr;
             oA = (uint32_t)(reinterpret_cast<uintptr_t>(mat + (uint64_t)rowA * row_bytes + lb * 210u) & 15u);
             oB = (uint32_t)(reinterpret_cast<uintptr_t>(mat + (uint64_t)rowB * row_bytes + lb * 210u) & 15u);
         }
         const uint32_t sb = ring_s + slot * kSlot6;
         const uint32_t rA = sb + g * kRow6 + oA, rB = sb + (g + 8) * kRow6 + oB;
         const uint32_t xb = xb_base + blk * xb_step, nb = nsx_s + blk * (uint32_t)kNsxBytes;
-        int IA, IB;
-        if (kRowsAligned && (oA & 2u) == 0) {  // the same for the whole warp
+        int IA = 0, IB = 0;
+        uint32_t dA = 0, dB = 0;
+        if (skip) {
+        } else if (kRowsAligned && (oA & 2u) == 0) {  // the same for the whole warp
             block6<false>(rA, rB, 0u, 0u, xb, xh, nb, t, IA, IB);
         } else {
             block6<true>(rA, rB, (oA & 3u) * 8u, (oB & 3u) * 8u, xb, xh, nb, t, IA, IB);
         }
-        const uint32_t dA = lds_u16s(rA + 208), dB = lds_u16s(rB + 208);
+        if (!skip) {
+            dA = lds_u16s(rA + 208);
+            dB = lds_u16s(rB + 208);
+        }
         // every lane has read the stage: refill it
         __syncwarp();
         if (it + kDepth < n) request(slot);

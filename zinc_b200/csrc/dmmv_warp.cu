@@ -214,7 +214,15 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
             Mb = a.segM[sg];
         } else if constexpr (kSeg == 2) {
             const uint32_t slot = p_tile / a.tiles_per_expert, t0 = slot * a.tiles_per_expert * 16;
-            base = a.A[p_strm] + (uint64_t)checked_expert(__ldg(a.routing + slot), a.n_experts_max, a.status) * a.expert_stride -
+            const uint32_t e_raw = __ldg(a.routing + slot);
+            if (e_raw == kSkipExpert) {  // no expert in this slot on this rank: nothing to fetch
+                if (++p_kc == upt) {
+                    p_kc = 0;
+                    if (++p_strm == NS) { p_strm = 0; ++p_tile; }
+                }
+                return;
+            }
+            base = a.A[p_strm] + (uint64_t)checked_expert(e_raw, a.n_experts_max, a.status) * a.expert_stride -
                    (uint64_t)t0 * row_bytes;
             Mb = t0 + a.M;
         } else {
@@ -283,7 +291,10 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
         const uint32_t slot = it % kDepth;
         cp_async_wait<kDepth - 1>();  // this lane's copies of unit `it` have landed
         __syncwarp();                 // ... and so have the other lanes'
-        const uint32_t nblk = min((uint32_t)kCB, bpr - kc * kCB);
+        uint32_t nblk = min((uint32_t)kCB, bpr - kc * kCB);
+        if constexpr (kSeg == 2) {  // a slot without an expert contributes zeros
+            if (__ldg(a.routing + tile / a.tiles_per_expert) == kSkipExpert) nblk = 0;
+        }
 #pragma unroll
         for (uint32_t bi = 0; bi < (uint32_t)kCB; ++bi) {
             if (bi >= nblk) break;

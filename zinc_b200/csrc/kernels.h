@@ -180,6 +180,10 @@ cudaError_t launch_moe_weighted_bias_acc(float* a, const float* bias, const uint
 // given); norm_w == nullptr: xn = x. One CTA per row: for matrices with few rows (routers). K % 4 == 0.
 cudaError_t launch_rms_norm_dmmv_f32(const float* x, const float* norm_w, const float* W, float* norm_out, float* y,
                                      uint32_t M, uint32_t K, float eps, cudaStream_t s, uint64_t* launches);
+// Expert parallelism: routing rows [k ids][k weights] -> ids of the experts [lo, hi) renumbered from 0, the others
+// replaced by the "no expert" mark (kernels read no weights for such a slot and contribute zeros).
+cudaError_t launch_moe_ep_filter(const uint32_t* in, uint32_t* out, uint32_t k, uint32_t n_tokens, uint32_t stride_in,
+                                 uint32_t stride_out, uint32_t lo, uint32_t hi, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_count_experts(const uint32_t* a, uint32_t* counts, uint32_t n_experts, uint32_t ne00,
                                  uint32_t ne01, uint32_t nb00, uint32_t nb01, uint32_t a_offset, cudaStream_t s,
                                  uint64_t* launches);

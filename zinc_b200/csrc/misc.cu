@@ -282,7 +282,12 @@ __global__ void moe_bias_act_kernel(const float* __restrict__ gate, const float*
                                     uint32_t n_experts, uint32_t* status) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
     if (i >= M) return;
-    const uint32_t e = checked_expert(__ldg(routing + s), n_experts, status);
+    const uint32_t e_raw = __ldg(routing + s);
+    if (e_raw == kSkipExpert) {  // no expert in this slot on this rank
+        y[(size_t)s * M + i] = 0.f;
+        return;
+    }
+    const uint32_t e = checked_expert(e_raw, n_experts, status);
     const size_t o = (size_t)s * M + i, b = (size_t)e * M + i;
     const float g = gate[o] + (gate_bias ? gate_bias[b] : 0.f);
     const float u = up[o] + (up_bias ? up_bias[b] : 0.f);
@@ -298,10 +303,25 @@ __global__ void moe_weighted_bias_acc_kernel(float* __restrict__ a, const float*
     if (i >= n) return;
     float sum = 0.f;
     for (uint32_t s = 0; s < n_used; ++s) {
-        const uint32_t e = checked_expert(__ldg(routing + s), n_experts, status);
+        const uint32_t e_raw = __ldg(routing + s);
+        if (e_raw == kSkipExpert) continue;
+        const uint32_t e = checked_expert(e_raw, n_experts, status);
         sum = fmaf(__uint_as_float(__ldg(routing + n_used + s)), bias[(size_t)e * n + i], sum);
     }
     a[i] += sum;
+}
+
+// ---- expert parallelism: keep the slots whose expert this rank holds ---------------------------------
+// out[s] = in[s] - lo when lo <= in[s] < hi, else the "no expert" mark; the k weights are copied. Rows of 2k
+// words, one per token.
+__global__ void moe_ep_filter_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, uint32_t k,
+                                     uint32_t n_tokens, uint32_t stride_in, uint32_t stride_out, uint32_t lo,
+                                     uint32_t hi) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tokens * 2 * k) return;
+    const uint32_t tok = i / (2 * k), j = i - tok * 2 * k;
+    const uint32_t v = in[(size_t)tok * stride_in + j];
+    out[(size_t)tok * stride_out + j] = j >= k ? v : (v >= lo && v < hi) ? v - lo : 0xFFFFFFFFu;
 }
 
 // ---- fused RMS norm + f32 router matvec -------------------------------------------------
@@ -516,6 +536,14 @@ cudaError_t launch_moe_weighted_bias_acc(float* a, const float* bias, const uint
                                          uint32_t n_used, uint32_t n_experts, uint32_t* status, cudaStream_t s,
                                          uint64_t* launches) {
     moe_weighted_bias_acc_kernel<<<(n + 255) / 256, 256, 0, s>>>(a, bias, routing, n, n_used, n_experts, status);
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_moe_ep_filter(const uint32_t* in, uint32_t* out, uint32_t k, uint32_t n_tokens, uint32_t stride_in,
+                                 uint32_t stride_out, uint32_t lo, uint32_t hi, cudaStream_t s, uint64_t* launches) {
+    const uint32_t n = n_tokens * 2 * k;
+    moe_ep_filter_kernel<<<(n + 255) / 256, 256, 0, s>>>(in, out, k, n_tokens, stride_in, stride_out, lo, hi);
     if (launches) ++*launches;
     return cudaGetLastError();
 }

@@ -375,7 +375,7 @@ moe_group_kernel(const uint32_t* __restrict__ routing, uint32_t n_pairs, uint32_
         const uint32_t e = routing[p];
         if (e < n_experts) {
             atomicAdd(&cnt[e], 1u);
-        } else if (status) {  // not an expert: the pair is left out (its output row stays untouched) and reported
+        } else if (status && e != 0xFFFFFFFFu) {  // not an expert (and not the "no expert here" mark): left out and reported
             status[0] = 2u;
             status[1] = e;
         }

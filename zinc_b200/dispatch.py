@@ -429,6 +429,13 @@ class DmmvDispatch:
         self.ctx.call("zc_moe_weighted_bias_acc", a.ptr, a.size, bias.ptr, bias.size, routing.ptr, routing.size,
                       n, n_used, n_experts)
 
+    # expert parallelism: keep (and renumber) the slots whose expert lies in [expert_lo, expert_hi)
+    def dispatchMoeEpFilter(self, routing, out, k, expert_lo, expert_hi, n_tokens=1, routing_stride=None, out_stride=None):
+        routing, out = _buf(routing), _buf(out)
+        self.ctx.call("zc_moe_ep_filter", routing.ptr, routing.size, out.ptr, out.size, k, n_tokens,
+                      2 * k if routing_stride is None else routing_stride, 2 * k if out_stride is None else out_stride,
+                      expert_lo, expert_hi)
+
     # grouped-by-expert prefill helpers (src/shaders/metal/moe_route_pack.metal, moe_route_scatter.metal)
     def dispatchMoeRoutePack(self, routing, counts, ids, n_tokens, n_experts, k, routing_stride, ids_stride):
         routing, counts, ids = map(_buf, (routing, counts, ids))

@@ -14,11 +14,16 @@ reference walks the selected experts one by one; here every step handles all sel
 Attention, norms and the residual stream are stood in for by fixed N(0,1) vectors, as in the dense
 decode step.
 
-Tensor parallelism (world > 1): every expert's FFN dimension is cut into per-rank slices on block
-boundaries of the down projection's type (`ffn_split`): a rank holds rows [lo, hi) of every expert's
+Tensor parallelism (world > 1, parallel="tp"): every expert's FFN dimension is cut into per-rank slices on
+block boundaries of the down projection's type (`ffn_split`): a rank holds rows [lo, hi) of every expert's
 gate and up matrices and the matching K slice of every expert's down matrix, computes a partial hidden
 vector per layer, and the ranks sum it (one all-reduce of the hidden vector per layer). The router is
 replicated.
+
+Expert parallelism (world > 1, parallel="ep"): rank r holds the whole experts [r E / N, (r+1) E / N). The router
+and the top-k run on every rank; `zc_moe_ep_filter` renumbers the selected ids that fall into the rank's range
+and marks the other slots "no expert here", which every MoE kernel skips (no weight bytes read, zeros
+contributed). The shared expert runs on rank 0. The partial hidden vectors are summed as above.
 """
 from __future__ import annotations
 
@@ -124,6 +129,9 @@ class MoeDecode:
     allreduce: object = None   # callable(tensor): in-place sum over the ranks
     partial: object = None
     one: object = None
+    routing_local: object = None   # expert parallelism: the routing with this rank's experts renumbered, the rest skipped
+    e_lo: int = 0
+    e_hi: int = 0
     # gate + up + activation in one launch instead of the reference's two dispatches. Off: measured slower
     # (config 4: 1.387 vs 1.349 ms per token, config 5: 1.329 vs 1.120 ms) although it saves a launch per layer.
     fuse_act: bool = False
@@ -132,11 +140,18 @@ class MoeDecode:
     def build(torch, dd: DmmvDispatch, shape: MoeShape, seed: int = 3, rank: int = 0, world: int = 1,
               allreduce=None, parallel: str = "tp") -> "MoeDecode":
         s = shape
-        if parallel != "tp":
+        if parallel not in ("tp", "ep"):
+            raise ValueError("parallel must be 'tp' or 'ep'")
+        if world == 1:
             parallel = "tp"
+        if parallel == "ep" and s.n_experts % world:
+            raise ValueError(f"{s.n_experts} experts do not divide over {world} ranks")
         dev = f"cuda:{torch.cuda.current_device()}"
-        st = MoeDecode(shape=s, dd=dd, world=world, rank=rank, allreduce=allreduce)
-        lo, hi = ffn_split(s.ffn, synth.BLOCK[s.t_down][0], world)[rank]
+        st = MoeDecode(shape=s, dd=dd, world=world, rank=rank, allreduce=allreduce, parallel=parallel)
+        ep = parallel == "ep"
+        lo, hi = (0, s.ffn) if ep else ffn_split(s.ffn, synth.BLOCK[s.t_down][0], world)[rank]
+        st.e_lo = rank * (s.n_experts // world) if ep else 0
+        st.e_hi = (rank + 1) * (s.n_experts // world) if ep else s.n_experts
         st.ffn_local = hi - lo
         rb_h = row_bytes(s.t_gate_up, s.hidden)
         gen = torch.Generator(device=dev).manual_seed(seed)
@@ -156,7 +171,19 @@ class MoeDecode:
                 w.bg = torch.randn(s.n_experts, s.ffn, device=dev, generator=gen)[:, lo:hi].contiguous().view(-1)
                 w.bu = torch.randn(s.n_experts, s.ffn, device=dev, generator=gen)[:, lo:hi].contiguous().view(-1)
                 w.bd = torch.randn(s.n_experts * s.hidden, device=dev, generator=gen)
-            if world > 1:  # every rank generates the same full tensors and keeps its slice
+            if ep:  # every rank generates the same full tensors and keeps its experts
+                eg, ed = s.ffn * rb_h, s.hidden * row_bytes(s.t_down, s.ffn)
+                w.wg = w.wg[st.e_lo * eg:st.e_hi * eg].clone()
+                w.wu = w.wu[st.e_lo * eg:st.e_hi * eg].clone()
+                w.wd = w.wd[st.e_lo * ed:st.e_hi * ed].clone()
+                if s.biases:
+                    w.bg = w.bg.view(s.n_experts, -1)[st.e_lo:st.e_hi].contiguous().view(-1)
+                    w.bu = w.bu.view(s.n_experts, -1)[st.e_lo:st.e_hi].contiguous().view(-1)
+                    w.bd = w.bd.view(s.n_experts, -1)[st.e_lo:st.e_hi].contiguous().view(-1)
+                if s.shared and rank != 0:
+                    w.sg = w.su = w.sd = None
+                torch.cuda.empty_cache()
+            elif world > 1:  # every rank generates the same full tensors and keeps its slice
                 w.wg = shard_expert_rows(torch, w.wg, s.n_experts, s.ffn, rb_h, lo, hi)
                 w.wu = shard_expert_rows(torch, w.wu, s.n_experts, s.ffn, rb_h, lo, hi)
                 w.wd = shard_expert_k(torch, w.wd, s.n_experts, s.hidden, s.t_down, s.ffn, lo, hi)
@@ -171,6 +198,7 @@ class MoeDecode:
         st.hidden = torch.zeros(s.hidden, **f32)
         st.logits = torch.zeros(s.n_experts, **f32)
         st.routing = torch.zeros(2 * s.top_k, dtype=torch.int32, device=dev)
+        st.routing_local = torch.zeros(2 * s.top_k, dtype=torch.int32, device=dev) if ep else st.routing
         st.yg = torch.zeros(s.top_k * st.ffn_local, **f32)
         st.yu = torch.zeros(s.top_k * st.ffn_local, **f32)
         st.act = torch.zeros(s.top_k * st.ffn_local, **f32)
@@ -190,27 +218,32 @@ class MoeDecode:
         es_gu = f * row_bytes(s.t_gate_up, s.hidden)
         es_d = s.hidden * row_bytes(s.t_down, f)
         tp = self.world > 1
+        ep = self.parallel == "ep" and tp
+        n_local = self.e_hi - self.e_lo
+        r = self.routing_local
         for w in self.layers:
             dd.recordDispatch(F32, w.router, self.x, self.logits, s.n_experts, s.hidden)
             dd.dispatchSoftmaxTopk(self.logits, self.routing, s.n_experts, s.top_k, rule=s.rule, bias=w.router_bias)
+            if ep:
+                dd.dispatchMoeEpFilter(self.routing, r, s.top_k, self.e_lo, self.e_hi)
             if self.fuse_act and not s.biases:
-                dd.dispatchMoeFusedGateUpAct(s.t_gate_up, w.wg, w.wu, self.x, self.act, self.routing, f, s.hidden,
+                dd.dispatchMoeFusedGateUpAct(s.t_gate_up, w.wg, w.wu, self.x, self.act, r, f, s.hidden,
                                              es_gu, s.top_k, 0, oai=s.oai)
             else:
-                dd.dispatchMoeFusedGateUp(s.t_gate_up, w.wg, w.wu, self.x, self.yg, self.yu, self.routing, f,
+                dd.dispatchMoeFusedGateUp(s.t_gate_up, w.wg, w.wu, self.x, self.yg, self.yu, r, f,
                                           s.hidden, es_gu, s.top_k, 0)
                 if s.biases:
-                    dd.dispatchMoeBiasAct(self.yg, self.yu, w.bg, w.bu, self.routing, self.act, f, s.top_k,
-                                          s.n_experts, oai=s.oai)
+                    dd.dispatchMoeBiasAct(self.yg, self.yu, w.bg, w.bu, r, self.act, f, s.top_k,
+                                          n_local, oai=s.oai)
                 else:
                     dd.dispatchSwiglu(self.yg, self.yu, self.act, s.top_k * f, oai=s.oai)
             acc = self.partial if tp else self.hidden
             if tp:
                 dd.ctx.memset(_as_buffer(self.partial), 0)
-            dd.dispatchMoeFusedDownAcc(s.t_down, w.wd, self.act, acc, self.routing, s.hidden, f, es_d, s.top_k, f)
-            if s.biases and self.rank == 0:
-                dd.dispatchMoeWeightedBiasAcc(acc, w.bd, self.routing, s.hidden, s.top_k, s.n_experts)
-            if s.shared:
+            dd.dispatchMoeFusedDownAcc(s.t_down, w.wd, self.act, acc, r, s.hidden, f, es_d, s.top_k, f)
+            if s.biases and (ep or self.rank == 0):  # tp: the bias enters once; ep: with the rank's own experts
+                dd.dispatchMoeWeightedBiasAcc(acc, w.bd, r, s.hidden, s.top_k, n_local)
+            if s.shared and w.sg is not None:
                 dd.dispatchDmmvFusedGateUpSwiglu(s.t_gate_up, w.sg, w.su, self.x, self.sact, f, s.hidden)
                 dd.recordDispatch(s.t_down, w.sd, self.sact, acc, s.hidden, f, acc_mode=1)
             if tp:
