@@ -399,7 +399,7 @@ def moe_decode_results(torch, zb, ctx, dd, stream, sampler, args, rank=0, world=
             shape = dataclasses.replace(shape, n_layers=args.layers)
         try:
             step = MoeDecode.build(torch, dd, shape, rank=rank, world=world, allreduce=allreduce if world > 1 else None,
-                                   parallel=mode)
+                                   parallel=mode, fused=args.moe_dispatch == "fused")
         except ValueError as e:
             if rank == 0:
                 out.append({"metric": METRIC, "n_gpus": world, "config": {"workload": name + ", decode batch 1"},
@@ -431,6 +431,8 @@ def moe_decode_results(torch, zb, ctx, dd, stream, sampler, args, rank=0, world=
                 "dtype": "f32", "data": "synthetic",
                 "config": {"workload": name + ", decode batch 1", "layers": shape.n_layers,
                            "weight_bytes_per_token": shape.weight_bytes(), "parallelism": par,
+                           "dispatch": "router + selection / gate + up + activation / down + sum: three launches per layer"
+                           if step.fused else "one launch per dispatch of the reference's sequence",
                            "l2": "weights touched per token (all layers) are larger than L2"},
                 "gpu_launches": launches * len(per) * 20, "gpu_launches_per_step": launches,
                 "gpu_launches_per_layer": launches / shape.n_layers,
@@ -579,6 +581,9 @@ def main():
                          "prefill_gemm: the batched-prefill dequant-GEMM cases; dmmv_single: one Q4_K 4096x4096 matvec; "
                          "moe_decode: the two MoE configurations at batch 1; moe_prefill: one MoE layer's routed experts "
                          "over a prefill batch")
+    ap.add_argument("--moe-dispatch", default="fused", choices=["fused", "reference"],
+                    help="moe_decode: fused = three launches per layer (default); reference = one launch per dispatch of "
+                         "the reference's sequence")
     ap.add_argument("--collective", default="fused", choices=["fused", "peer", "nccl"],
                     help="N > 1, hidden-state sums: fused = partial rows pushed to every rank from the matvec's epilogue "
                          "and summed in the next matvec's prologue (default); peer = the library's one-kernel all-reduce; "

@@ -172,6 +172,19 @@ int32_t zc_rms_norm_dmmv_f32(zc_ctx* ctx, const void* hidden, uint64_t hidden_si
                              void* logits, uint64_t logits_size,
                              uint32_t M, uint32_t K, float eps);
 
+/* The same with two M x K f32 matrices on one normalised vector, one launch: alpha_out = W_alpha xn,
+ * beta_out = W_beta xn, xn also written to norm_out when given. Replaces the fused RMS norm + alpha / beta
+ * SSM projection dispatch (src/shaders/rms_norm_dmmv_q4k_alpha_beta.comp:64-133; f32 weights, as its callers
+ * ship them). */
+int32_t zc_rms_norm_dmmv_alpha_beta(zc_ctx* ctx, const void* hidden, uint64_t hidden_size,
+                                    const void* norm_weights, uint64_t norm_size,
+                                    const void* alpha_weights, uint64_t alpha_size,
+                                    const void* beta_weights, uint64_t beta_size,
+                                    void* norm_out, uint64_t norm_out_size,
+                                    void* alpha_out, uint64_t alpha_out_size,
+                                    void* beta_out, uint64_t beta_out_size,
+                                    uint32_t M, uint32_t K, float eps);
+
 /* Grouped matvec: y_i (+)= W_i x for n = 1..3 matrices of one type that share x and K, e.g. the Q, K
  * and V projections the reference records as three dispatches on the same input
  * (src/compute/forward.zig:4530-4564). One kernel launch when the matrices are Q4_K (16-byte aligned);
@@ -284,6 +297,61 @@ int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type,
                               uint32_t M, uint32_t K,
                               uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride,
                               uint64_t x_offset, uint64_t y_offset);
+
+/* Routing id that selects the shared expert: a matrix outside the expert stack, passed beside it to the two
+ * calls below. It lets the always-on expert of a layer (src/compute/forward.zig:6455-6545 runs it as separate
+ * dispatches after the routed ones) ride in the routed launches as one more slot with weight 1. */
+#define ZC_SHARED_EXPERT 0xFFFFFFFEu
+
+/* zc_moe_fused_gate_up_act with, all optional (NULL / 0): the shared expert's gate and up matrices [M][K] of the
+ * same type, selected by a slot whose id is ZC_SHARED_EXPERT; and per-expert f32 biases [n_experts][M] added to
+ * the gate and up rows before the activation (src/compute/forward.zig:6841-6849, ffn_gate_exps_bias /
+ * ffn_up_exps_bias), never to the shared slot. x is shared by the slots. One launch replaces the routed
+ * gate + up dispatch, the shared expert's gate + up dispatch, the bias adds and the activation. */
+int32_t zc_moe_gate_up_act_ex(zc_ctx* ctx, uint32_t type,
+                              const void* Wg, uint64_t wg_size, const void* Wu, uint64_t wu_size,
+                              const void* shared_gate, uint64_t shared_gate_size,
+                              const void* shared_up, uint64_t shared_up_size,
+                              const void* gate_bias, uint64_t gate_bias_size,
+                              const void* up_bias, uint64_t up_bias_size,
+                              const void* x, uint64_t x_size, void* y, uint64_t y_size,
+                              const void* routing, uint64_t routing_size,
+                              uint32_t M, uint32_t K, uint64_t expert_stride, uint32_t n_used,
+                              uint64_t x_offset, uint64_t y_offset, uint32_t oai);
+
+/* zc_moe_fused_down_acc with, both optional: the shared expert's down matrix [M][K] (slot id ZC_SHARED_EXPERT,
+ * weighted by the slot's routing weight like any other) and a per-expert f32 bias [n_experts][M] that joins the
+ * weighted sum, hidden[r] += sum_s w_s * (W[id_s][r] . x_s + bias[id_s][r])
+ * (src/compute/forward.zig:6923-6927, ffn_down_exps_bias), never for the shared slot. */
+int32_t zc_moe_down_acc_ex(zc_ctx* ctx, uint32_t type,
+                           const void* A, uint64_t a_size,
+                           const void* shared_down, uint64_t shared_down_size,
+                           const void* down_bias, uint64_t down_bias_size,
+                           const void* x, uint64_t x_size, void* y, uint64_t y_size,
+                           const void* routing, uint64_t routing_size,
+                           uint32_t M, uint32_t K, uint64_t expert_stride, uint32_t n_used,
+                           uint32_t x_expert_stride, uint64_t x_offset, uint64_t y_offset);
+
+/* Router and expert selection of one token in one launch: logits = W_router . xn with xn = hidden, or
+ * xn = norm_weights * hidden * rsqrt(mean(hidden^2) + eps) when norm_weights is given (then also written to
+ * norm_out if non-NULL); then the selection of zc_softmax_topk (same rules, optional bias on the logits) into
+ * routing = [k + shared_slot ids][k + shared_slot weights]. With shared_slot = 1 the last slot is
+ * {ZC_SHARED_EXPERT, 1.0f}. routing_local (optional, same layout) receives the selection as the expert-parallel
+ * rank that owns experts [e_lo, e_hi) sees it: those ids renumbered from 0, the others 0xFFFFFFFF, the shared
+ * slot kept if local_shared != 0 and 0xFFFFFFFF otherwise. At most 1024 experts; K a multiple of 4.
+ * Replaces the router DMMV / fused norm + router dispatch followed by the softmax_topk dispatch
+ * (src/compute/forward.zig:6139-6190; src/shaders/rms_norm_dmmv_f32.comp, softmax_topk.comp), and
+ * zc_moe_ep_filter behind them. */
+int32_t zc_moe_router_topk(zc_ctx* ctx, const void* hidden, uint64_t hidden_size,
+                           const void* norm_weights, uint64_t norm_size,
+                           const void* router_weights, uint64_t router_size,
+                           const void* bias, uint64_t bias_size,
+                           void* norm_out, uint64_t norm_out_size,
+                           void* logits, uint64_t logits_size,
+                           void* routing, uint64_t routing_size,
+                           void* routing_local, uint64_t routing_local_size,
+                           uint32_t n_experts, uint32_t K, uint32_t k, uint32_t rule, float eps,
+                           uint32_t shared_slot, uint32_t e_lo, uint32_t e_hi, uint32_t local_shared);
 
 /* Cross-token MoE matvec: Y[t][s][M] = W[routing[t*n_experts_used + s]] . X[t][K];
  * routing is the flattened [n_tokens][n_experts_used] id table; strides in

@@ -311,6 +311,25 @@ def test_rms_norm_dmmv_f32(gpu, oracle, M, K):
         dd.dispatchRmsNormDmmvF32(xd, wd, Wd, xd, out_l, M, K, eps)  # in-place normalisation races
 
 
+@pytest.mark.parametrize("M,K", [(32, 2048), (5, 64)])
+def test_rms_norm_dmmv_alpha_beta(gpu, oracle, M, K):
+    """Fused RMS norm + the two small f32 SSM projections (src/shaders/rms_norm_dmmv_q4k_alpha_beta.comp)."""
+    torch, ctx, dd = gpu
+    g = synth.rng(411, M + K)
+    x = synth.activations(g, K) * np.float32(2.0)
+    w = (synth.activations(g, K) * np.float32(0.1) + np.float32(1.0)).astype(np.float32)
+    Wa, Wb = synth.activations(g, M, K) * np.float32(0.05), synth.activations(g, M, K) * np.float32(0.05)
+    xn, la = oracle.rms_norm_dmmv_f32(x, w, Wa, M, K, 1e-6)
+    _, lb = oracle.rms_norm_dmmv_f32(x, w, Wb, M, K, 1e-6)
+    on, oa, ob = out_with_canary(torch, K), out_with_canary(torch, M), out_with_canary(torch, M)
+    dd.dispatchRmsNormDmmvAlphaBeta(dev(torch, x), dev(torch, w), dev(torch, Wa.reshape(-1)), dev(torch, Wb.reshape(-1)),
+                                    on, oa, ob, M, K, 1e-6)
+    ctx.submit_and_wait()
+    assert canary_intact(on, K) and canary_intact(oa, M) and canary_intact(ob, M)
+    assert rel_l2(on[:K].cpu().numpy(), xn) <= 1e-6
+    assert rel_l2(oa[:M].cpu().numpy(), la) <= 1e-5 and rel_l2(ob[:M].cpu().numpy(), lb) <= 1e-5
+
+
 @pytest.mark.parametrize("E,M,K,n_used", [(12, 512, 2048, 8), (5, 100, 1024, 3), (3, 16, 512, 2)])
 def test_moe_fused_gate_up_streaming(gpu, oracle, E, M, K, n_used):
     """Shapes that take the streaming kernel with device-side expert selection (Q4_K, shared x), run
@@ -614,3 +633,157 @@ def test_moe_decode_expert_parallel_ranks(gpu, world):
         ctx.submit_and_wait()
         total += part.hidden.cpu().numpy().astype(np.float64)
     assert rel_l2(total, want) <= 1e-5
+
+
+@pytest.mark.parametrize("rule", [zb.ROUTE_SOFTMAX_ALL_RENORM, zb.ROUTE_TOPK_THEN_SOFTMAX])
+@pytest.mark.parametrize("n,K,k,norm,bias,shared", [(256, 2048, 8, False, False, True), (32, 2880, 4, False, True, False),
+                                                    (129, 4096 + 512, 8, True, True, True), (8, 64, 3, True, False, False)])
+def test_moe_router_topk(gpu, oracle, rule, n, K, k, norm, bias, shared):
+    """Router matvec (+ RMS norm) and expert selection in one launch, twice in a row (the arrival counter must
+    come back to zero): logits against the oracle's router, the selection against the oracle's selection run on
+    the logits the GPU produced, the shared slot, and the expert-parallel view of the selection."""
+    torch, ctx, dd = gpu
+    g = synth.rng(420, n * 7 + rule)
+    W = synth.activations(g, n, K) * np.float32(0.05)
+    nw = (synth.activations(g, K) * np.float32(0.1) + np.float32(1.0)).astype(np.float32)
+    b = (synth.activations(g, n) * np.float32(0.5)).astype(np.float32) if bias else None
+    slots = k + (1 if shared else 0)
+    e_lo, e_hi = n // 4, n // 2
+    Wd, nwd = dev(torch, W.reshape(-1)), dev(torch, nw)
+    for rep in range(2):
+        x = synth.activations(g, K) * np.float32(2.0)
+        if norm:
+            xn, want_logits = oracle.rms_norm_dmmv_f32(x, nw, W, n, K, 1e-6)
+        else:
+            xn, want_logits = x, (W.astype(np.float64) @ x.astype(np.float64)).astype(np.float32)
+        lg, no = out_with_canary(torch, n), out_with_canary(torch, K)
+        rt = torch.full((2 * slots + 8,), 0x7ABCDEF0, dtype=torch.int32, device="cuda")
+        rl = torch.full((2 * slots + 8,), 0x7ABCDEF0, dtype=torch.int32, device="cuda")
+        dd.dispatchMoeRouterTopk(dev(torch, x), Wd, lg, rt, n, K, k, rule=rule, bias=None if b is None else dev(torch, b),
+                                 norm_weights=nwd if norm else None, norm_out=no if norm else None, eps=1e-6,
+                                 shared_slot=shared, routing_local=rl, e_lo=e_lo, e_hi=e_hi, local_shared=(rep == 0))
+        ctx.submit_and_wait()
+        assert canary_intact(lg, n)
+        assert bool((rt[2 * slots:] == 0x7ABCDEF0).all().item()) and bool((rl[2 * slots:] == 0x7ABCDEF0).all().item())
+        got_logits = lg[:n].cpu().numpy()
+        assert rel_l2(got_logits, want_logits) <= 1e-5
+        if norm:
+            assert canary_intact(no, K) and rel_l2(no[:K].cpu().numpy(), xn) <= 1e-6
+        fn = oracle.topk_softmax if rule == zb.ROUTE_SOFTMAX_ALL_RENORM else oracle.topk_softmax_weight
+        ids, w = fn(got_logits + b if b is not None else got_logits, k)
+        r = rt[:2 * slots].cpu().numpy().view(np.uint32)
+        assert np.array_equal(r[:k], ids)
+        assert np.max(np.abs(r[slots:slots + k].view(np.float32) - w)) <= 1e-6
+        if shared:
+            assert r[k] == zb.SHARED_EXPERT and r[slots + k] == np.float32(1.0).view(np.uint32)
+        loc = rl[:2 * slots].cpu().numpy().view(np.uint32)
+        want_loc = np.where((ids >= e_lo) & (ids < e_hi), ids - e_lo, zb.SKIP_EXPERT).astype(np.uint32)
+        assert np.array_equal(loc[:k], want_loc) and np.array_equal(loc[slots:], r[slots:])
+        if shared:
+            assert loc[k] == (zb.SHARED_EXPERT if rep == 0 else zb.SKIP_EXPERT)
+    with pytest.raises(zb.InvalidArgument):
+        dd.dispatchMoeRouterTopk(dev(torch, x), Wd, lg, rt, 2000, K, k)
+
+
+@pytest.mark.parametrize("t,E,M,K,n_used,oai,shared,biases", [
+    (zb.Q4_K, 12, 512, 2048, 8, False, True, False),    # streaming Q4_K, shared expert as the ninth slot
+    (zb.Q4_K, 12, 512, 2048, 8, False, True, True),
+    (zb.MXFP4, 6, 300, 2880, 4, True, False, True),     # streaming MXFP4, GPT-OSS biases and activation
+    (zb.MXFP4, 6, 300, 2880, 4, True, True, True),
+    (zb.Q4_K, 4, 33, 512, 2, False, True, True),        # one warp per row pair
+    (zb.Q6_K, 4, 40, 512, 2, True, True, False),
+])
+def test_moe_gate_up_act_ex(gpu, oracle, t, E, M, K, n_used, oai, shared, biases):
+    """Routed gate + up, the shared expert as one more slot, the per-expert biases and the activation in one
+    launch, against the oracle's per-slot matvecs, bias adds and activation; one slot holds no expert."""
+    torch, ctx, dd = gpu
+    g = synth.rng(421, t * 100 + M + int(shared) + 2 * int(biases))
+    wg, stride = stacked(g, t, E, M, K)
+    wu, _ = stacked(g, t, E, M, K)
+    sg, su = synth.quant_matrix(g, t, M, K), synth.quant_matrix(g, t, M, K)
+    bg, bu = synth.activations(g, E, M), synth.activations(g, E, M)
+    x = synth.activations(g, 1, K)
+    ids = np.array([(3 * i + E - 1) % E for i in range(n_used)], np.uint32)
+    slots = n_used + (1 if shared else 0)
+    sel = np.concatenate([ids, [zb.SHARED_EXPERT]]).astype(np.uint32) if shared else ids.copy()
+    sel[1] = zb.SKIP_EXPERT
+    y = out_with_canary(torch, slots * M, init=3.0)
+    dd.dispatchMoeGateUpActEx(t, dev(torch, wg), dev(torch, wu), dev(torch, x), y, dev(torch, routing_buf(sel)), M, K, stride,
+                              slots, shared=(dev(torch, sg), dev(torch, su)) if shared else None,
+                              biases=(dev(torch, bg.reshape(-1)), dev(torch, bu.reshape(-1))) if biases else None, oai=oai)
+    ctx.submit_and_wait()
+    xs = np.repeat(x, n_used, axis=0)
+    gate = oracle.moe_dmmv_f64(wg, t, M, K, stride, ids, K, xs).astype(np.float32)
+    up = oracle.moe_dmmv_f64(wu, t, M, K, stride, ids, K, xs).astype(np.float32)
+    if biases:
+        gate, up = gate + bg[ids], up + bu[ids]
+    if shared:
+        gate = np.concatenate([gate, oracle.dmmv_f64(sg, t, M, K, x[0]).astype(np.float32)[None]])
+        up = np.concatenate([up, oracle.dmmv_f64(su, t, M, K, x[0]).astype(np.float32)[None]])
+    want = oracle.swiglu(gate.reshape(-1), up.reshape(-1), oai=oai).reshape(slots, M)
+    have = y[:slots * M].cpu().numpy().reshape(slots, M)
+    live = np.ones(slots, bool)
+    live[1] = False
+    assert canary_intact(y, slots * M)
+    assert np.all(have[1] == 0.0)
+    assert rel_l2(have[live], want[live]) <= TOL
+
+
+@pytest.mark.parametrize("t,E,M,K,n_used,shared,bias", [
+    (zb.Q6_K, 12, 2048, 512, 8, True, False),    # streaming Q6_K, shared expert as the ninth slot
+    (zb.Q6_K, 5, 2100, 768, 3, True, True),      # rows that are not 16-byte aligned
+    (zb.MXFP4, 6, 2880, 2880, 4, False, True),   # streaming MXFP4 with the down bias
+    (zb.MXFP4, 3, 300, 2880, 3, True, True),
+    (zb.Q4_K, 6, 203, 512, 4, True, True),       # generic kernel
+])
+def test_moe_down_acc_ex(gpu, oracle, t, E, M, K, n_used, shared, bias):
+    """y += sum_s w_s (W[id_s] x_s + bias[id_s]) with the shared expert as one more slot (its own matrix, no
+    bias), against the oracle; one slot holds no expert."""
+    torch, ctx, dd = gpu
+    g = synth.rng(422, t * 100 + M + int(shared) + 2 * int(bias))
+    w, stride = stacked(g, t, E, M, K)
+    sd = synth.quant_matrix(g, t, M, K)
+    bd = synth.activations(g, E, M)
+    slots = n_used + (1 if shared else 0)
+    ids = np.array([(3 * i + E - 1) % E for i in range(n_used)], np.uint32)
+    sel = np.concatenate([ids, [zb.SHARED_EXPERT]]).astype(np.uint32) if shared else ids.copy()
+    sel[1] = zb.SKIP_EXPERT
+    wts = (g.random(slots).astype(np.float32) + np.float32(0.1))
+    x = synth.activations(g, slots, K)
+    h0 = synth.activations(g, M)
+    y = out_with_canary(torch, M)
+    y[:M] = dev(torch, h0)
+    dd.dispatchMoeDownAccEx(t, dev(torch, w), dev(torch, x.reshape(-1)), y, dev(torch, routing_buf(sel, wts)), M, K, stride,
+                            slots, K, shared=dev(torch, sd) if shared else None,
+                            bias=dev(torch, bd.reshape(-1)) if bias else None)
+    ctx.submit_and_wait()
+    per = oracle.moe_dmmv_f64(w, t, M, K, stride, ids, K, x[:n_used])
+    if bias:
+        per = per + bd[ids].astype(np.float64)
+    if shared:
+        per = np.concatenate([per, oracle.dmmv_f64(sd, t, M, K, x[n_used])[None]])
+    wl = wts.astype(np.float64).copy()
+    wl[1] = 0.0
+    want = h0 + (wl[:, None] * per).sum(0)
+    assert canary_intact(y, M)
+    assert rel_l2(y[:M].cpu().numpy() - h0, want - h0) <= TOL
+
+
+def test_moe_decode_fused_equals_dispatch_sequence(gpu):
+    """The three-launch layer (router + selection, gate + up + activation, down + sum) against the one launch per
+    dispatch sequence on the same weights: a Qwen-shaped layer with a shared expert and a GPT-OSS-shaped one with
+    biases."""
+    torch, ctx, dd = gpu
+    from zinc_b200.moe_step import MoeDecode, MoeShape
+    shapes = (MoeShape(hidden=2048, n_experts=32, top_k=8, ffn=512, t_gate_up=zb.Q4_K, t_down=zb.Q6_K,
+                       rule=zb.ROUTE_SOFTMAX_ALL_RENORM, shared=True, oai=False, n_layers=2),
+              MoeShape(hidden=2880, n_experts=8, top_k=4, ffn=2880, t_gate_up=zb.MXFP4, t_down=zb.MXFP4,
+                       rule=zb.ROUTE_TOPK_THEN_SOFTMAX, shared=False, oai=True, n_layers=2, biases=True))
+    for shape in shapes:
+        a = MoeDecode.build(torch, dd, shape, seed=9, fused=False)
+        b = MoeDecode.build(torch, dd, shape, seed=9, fused=True)
+        na, nb = a.record(), b.record()
+        ctx.submit_and_wait()
+        assert nb == 3 * shape.n_layers and na > nb
+        ha, hb = a.hidden.double(), b.hidden.double()
+        assert float(((ha - hb).norm() / ha.norm()).item()) <= 1e-5

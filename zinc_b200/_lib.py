@@ -20,6 +20,8 @@ TYPE_NAMES = {F32: "f32", F16: "f16", Q5_0: "q5_0", Q5_1: "q5_1", Q8_0: "q8_0", 
               Q5_K: "q5_k", Q6_K: "q6_k", BF16: "bf16", MXFP4: "mxfp4"}
 
 ROUTE_SOFTMAX_ALL_RENORM, ROUTE_TOPK_THEN_SOFTMAX = 0, 1
+# routing ids with a meaning of their own: no expert in this slot on this rank / the shared expert
+SKIP_EXPERT, SHARED_EXPERT = 0xFFFFFFFF, 0xFFFFFFFE
 
 _u32, _u64, _i32, _vp = C.c_uint32, C.c_uint64, C.c_int32, C.c_void_p
 
@@ -31,6 +33,14 @@ _OPS = {
                                      _u64, _u64, _u64, _u64],
     "zc_dmmv_sigmoid_acc": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u64, _u64, _u32],
     "zc_rms_norm_dmmv_f32": [_vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, C.c_float],
+    "zc_moe_gate_up_act_ex": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64,
+                              _vp, _u64, _u32, _u32, _u64, _u32, _u64, _u64, _u32],
+    "zc_moe_down_acc_ex": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u32,
+                           _u32, _u64, _u64],
+    "zc_moe_router_topk": [_vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32,
+                           _u32, _u32, C.c_float, _u32, _u32, _u32, _u32],
+    "zc_rms_norm_dmmv_alpha_beta": [_vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32,
+                                    C.c_float],
     "zc_dmmv_multi": [_u32, _u32, C.POINTER(_vp), C.POINTER(_u64), C.POINTER(_u64), _vp, _u64, _u64,
                       C.POINTER(_vp), C.POINTER(_u64), C.POINTER(_u64), C.POINTER(_u32), _u32, _u32],
     "zc_dmmv_batch": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u64, _u64, _u32],

@@ -26,6 +26,8 @@ struct zc_ctx {
     uint32_t* status_host = nullptr;  // pinned, mapped: deferred device-side status words
     uint32_t* status_dev = nullptr;
     uint2* scratch_partial = nullptr;  // split-K partial sums of the streaming matvecs, tagged (zero between launches)
+    uint32_t* router_counter = nullptr;  // arrival counter of the fused router + selection kernel (zero between launches)
+    uint64_t router_mark = 0;            // value of `launches` right after that kernel's last launch (0: never)
     int sm_count = 0;
     // tensor-parallel peer exchange (zc_comm_*)
     zc::CommArgs comm;
@@ -167,6 +169,9 @@ inline void attach_scratch(zc_ctx* ctx, DmmvArgs& a) {
     a.status = ctx->status_dev;
     if (ctx->wait_limit) a.spin_limit = ctx->wait_limit;
     a.sm_count = ctx->sm_count;
+    // nothing was launched since the fused router + selection kernel, which lets its successor start early:
+    // that successor must order itself behind it before it trusts the routing buffer
+    a.late = ctx->router_mark != 0 && ctx->router_mark == ctx->launches;
 }
 
 // Experts a stacked weight buffer holds: ids read from a device-side routing buffer must stay below it.
@@ -223,14 +228,15 @@ int32_t zc_init(int32_t device, zc_ctx** out_ctx) {
     }
     memset(ctx->status_host, 0, 256);
     ctx->sm_count = prop.multiProcessorCount;
-    if (cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_partial), kStreamPartialBytes) != cudaSuccess ||
-        cudaMemset(ctx->scratch_partial, 0, kStreamPartialBytes) != cudaSuccess) {
+    if (cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_partial), kStreamPartialBytes + 256) != cudaSuccess ||
+        cudaMemset(ctx->scratch_partial, 0, kStreamPartialBytes + 256) != cudaSuccess) {
         if (ctx->scratch_partial) cudaFree(ctx->scratch_partial);
         cudaFreeHost(ctx->status_host);
         cudaStreamDestroy(ctx->own_stream);
         delete ctx;
         return ZC_ERR_OOM;
     }
+    ctx->router_counter = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(ctx->scratch_partial) + kStreamPartialBytes);
     *out_ctx = ctx;
     return ZC_OK;
 }
@@ -442,7 +448,7 @@ int32_t zc_submit_and_wait(zc_ctx* ctx) {
         // A wait gave up. Tagged partial sums may be left behind and would be taken for fresh ones by the next
         // streaming matvec: clear them. A peer exchange that gave up leaves the ranks' epochs out
         // of step: the communicator refuses further collectives until it is destroyed and set up again.
-        cudaMemsetAsync(ctx->scratch_partial, 0, kStreamPartialBytes, ctx->stream);
+        cudaMemsetAsync(ctx->scratch_partial, 0, kStreamPartialBytes + 256, ctx->stream);
         cudaStreamSynchronize(ctx->stream);
         if (where >= 200 && ctx->comm_local) ctx->comm_broken = true;
         return fail(ctx, ZC_ERR_TIMEOUT, "device-side wait gave up (code %u, site %u)", code, where);
@@ -588,6 +594,31 @@ int32_t zc_rms_norm_dmmv_f32(zc_ctx* ctx, const void* hidden, uint64_t hidden_si
     const cudaError_t e = launch_rms_norm_dmmv_f32(f32p(hidden, 0), f32p(norm_weights, 0), f32p(router_weights, 0),
                                                    norm_out ? f32m(norm_out, 0) : nullptr, f32m(logits, 0), M, K, eps,
                                                    ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_rms_norm_dmmv_alpha_beta(zc_ctx* ctx, const void* hidden, uint64_t hidden_size, const void* norm_weights,
+                                    uint64_t norm_size, const void* alpha_weights, uint64_t alpha_size,
+                                    const void* beta_weights, uint64_t beta_size, void* norm_out,
+                                    uint64_t norm_out_size, void* alpha_out, uint64_t alpha_out_size, void* beta_out,
+                                    uint64_t beta_out_size, uint32_t M, uint32_t K, float eps) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_rms_norm_dmmv_alpha_beta";
+    if (M == 0 || K == 0 || (K & 3u))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: M and K must be non-zero and K a multiple of 4", fn);
+    ZC_TRY(check_vec(ctx, fn, "hidden", hidden, hidden_size, 0, (uint64_t)K * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "norm_weights", norm_weights, norm_size, 0, (uint64_t)K * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "alpha_weights", alpha_weights, alpha_size, 0, (uint64_t)M * K * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "beta_weights", beta_weights, beta_size, 0, (uint64_t)M * K * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "alpha_out", alpha_out, alpha_out_size, 0, (uint64_t)M * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "beta_out", beta_out, beta_out_size, 0, (uint64_t)M * 4, 4));
+    if (norm_out) {
+        ZC_TRY(check_vec(ctx, fn, "norm_out", norm_out, norm_out_size, 0, (uint64_t)K * 4, 16));
+        if (norm_out == hidden) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: norm_out must not alias hidden", fn);
+    }
+    const cudaError_t e = launch_rms_norm_dmmv_f32(f32p(hidden, 0), f32p(norm_weights, 0), f32p(alpha_weights, 0),
+                                                   norm_out ? f32m(norm_out, 0) : nullptr, f32m(alpha_out, 0), M, K, eps,
+                                                   ctx->stream, &ctx->launches, f32p(beta_weights, 0), f32m(beta_out, 0));
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 
@@ -779,15 +810,42 @@ int32_t zc_moe_dmmv(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, 
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 
+// What the extended MoE calls add: the shared expert's matrices (a slot whose id is ZC_SHARED_EXPERT selects them)
+// and per-expert f32 bias tables [n_experts][M]. All optional.
+struct MoeExtras {
+    const void* sh = nullptr;
+    uint64_t sh_size = 0;
+    const void* sh2 = nullptr;
+    uint64_t sh2_size = 0;
+    const void* bias = nullptr;
+    uint64_t bias_size = 0;
+    const void* bias2 = nullptr;
+    uint64_t bias2_size = 0;
+};
+
 static int32_t moe_gate_up_common(zc_ctx* ctx, const char* fn, uint32_t type, const void* Wg, uint64_t wg_size,
                                   const void* Wu, uint64_t wu_size, const void* x, uint64_t x_size, void* y_gate,
                                   uint64_t yg_size, void* y_up, uint64_t yu_size, const void* routing,
                                   uint64_t routing_size, uint32_t M, uint32_t K, uint64_t expert_stride,
                                   uint32_t n_used, uint32_t x_expert_stride, uint64_t x_offset, uint64_t y_offset,
-                                  uint32_t act) {
+                                  uint32_t act, const MoeExtras& ex = MoeExtras()) {
     ZC_TRY(check_moe(ctx, fn, type, Wg, wg_size, x, x_size, routing, routing_size, M, K, expert_stride, n_used,
                      x_expert_stride, x_offset, n_used));
     ZC_TRY(check_mat(ctx, fn, type, Wu, wu_size, 0, (uint64_t)M * row_bytes_of(type, K), M, K));
+    if ((ex.sh == nullptr) != (ex.sh2 == nullptr))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: the shared expert needs both its gate and its up matrix", fn);
+    if (ex.sh) {
+        ZC_TRY(check_mat(ctx, fn, type, ex.sh, ex.sh_size, 0, (uint64_t)M * row_bytes_of(type, K), M, K));
+        ZC_TRY(check_mat(ctx, fn, type, ex.sh2, ex.sh2_size, 0, (uint64_t)M * row_bytes_of(type, K), M, K));
+    }
+    const uint32_t n_stack = experts_in_buffer(wg_size < wu_size ? wg_size : wu_size,
+                                               (uint64_t)M * row_bytes_of(type, K), expert_stride);
+    if ((ex.bias == nullptr) != (ex.bias2 == nullptr))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: gate and up biases come together", fn);
+    if (ex.bias) {
+        ZC_TRY(check_vec(ctx, fn, "gate_bias", ex.bias, ex.bias_size, 0, (uint64_t)n_stack * M * 4, 4));
+        ZC_TRY(check_vec(ctx, fn, "up_bias", ex.bias2, ex.bias2_size, 0, (uint64_t)n_stack * M * 4, 4));
+    }
     ZC_TRY(check_vec(ctx, fn, act ? "y" : "y_gate", y_gate, yg_size, y_offset, (uint64_t)n_used * M * 4, 4));
     if (!act) ZC_TRY(check_vec(ctx, fn, "y_up", y_up, yu_size, y_offset, (uint64_t)n_used * M * 4, 4));
     DmmvArgs a;
@@ -805,8 +863,15 @@ static int32_t moe_gate_up_common(zc_ctx* ctx, const char* fn, uint32_t type, co
     a.x_expert_stride = x_expert_stride;
     a.a_end = u8(Wg, wg_size);
     a.a2_end = u8(Wu, wu_size);
-    a.n_experts_max = experts_in_buffer(wg_size < wu_size ? wg_size : wu_size, (uint64_t)M * row_bytes_of(type, K),
-                                        expert_stride);
+    a.n_experts_max = n_stack;
+    if (ex.sh) {
+        a.A_sh = u8(ex.sh, 0);
+        a.A2_sh = u8(ex.sh2, 0);
+        a.a_sh_end = u8(ex.sh, ex.sh_size);
+        a.a2_sh_end = u8(ex.sh2, ex.sh2_size);
+    }
+    a.bias = static_cast<const float*>(ex.bias);
+    a.bias2 = static_cast<const float*>(ex.bias2);
     attach_scratch(ctx, a);
     cudaError_t e;
     if (warp_moe_gate_up_eligible(type, a))
@@ -841,16 +906,24 @@ int32_t zc_moe_fused_gate_up_act(zc_ctx* ctx, uint32_t type, const void* Wg, uin
                               x_offset, y_offset, 1 + oai);
 }
 
-int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* x,
-                              uint64_t x_size, void* y, uint64_t y_size, const void* routing, uint64_t routing_size,
-                              uint32_t M, uint32_t K, uint64_t expert_stride, uint32_t n_used,
-                              uint32_t x_expert_stride, uint64_t x_offset, uint64_t y_offset) {
-    ZC_ENTER(ctx);
-    const char* fn = "zc_moe_fused_down_acc";
+static int32_t moe_down_acc_common(zc_ctx* ctx, const char* fn, uint32_t type, const void* A, uint64_t a_size,
+                                   const void* x, uint64_t x_size, void* y, uint64_t y_size, const void* routing,
+                                   uint64_t routing_size, uint32_t M, uint32_t K, uint64_t expert_stride,
+                                   uint32_t n_used, uint32_t x_expert_stride, uint64_t x_offset, uint64_t y_offset,
+                                   const MoeExtras& ex = MoeExtras()) {
     ZC_TRY(check_moe(ctx, fn, type, A, a_size, x, x_size, routing, routing_size, M, K, expert_stride, n_used,
                      x_expert_stride, x_offset, 2 * n_used));
     ZC_TRY(check_vec(ctx, fn, "y", y, y_size, y_offset, (uint64_t)M * 4, 4));
+    if (ex.sh) ZC_TRY(check_mat(ctx, fn, type, ex.sh, ex.sh_size, 0, (uint64_t)M * row_bytes_of(type, K), M, K));
+    if (ex.bias)
+        ZC_TRY(check_vec(ctx, fn, "down_bias", ex.bias, ex.bias_size, 0,
+                         (uint64_t)experts_in_buffer(a_size, (uint64_t)M * row_bytes_of(type, K), expert_stride) * M * 4, 4));
     DmmvArgs a;
+    if (ex.sh) {
+        a.A_sh = u8(ex.sh, 0);
+        a.a_sh_end = u8(ex.sh, ex.sh_size);
+    }
+    a.bias = static_cast<const float*>(ex.bias);
     a.A = u8(A, 0);
     a.x = f32p(x, x_offset);
     a.y = f32m(y, y_offset);
@@ -871,6 +944,92 @@ int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type, const void* A, uint64_
     else
         e = launch_dmmv(type, MODE_MOE_DOWN_ACC, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
+}
+
+int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* x,
+                              uint64_t x_size, void* y, uint64_t y_size, const void* routing, uint64_t routing_size,
+                              uint32_t M, uint32_t K, uint64_t expert_stride, uint32_t n_used,
+                              uint32_t x_expert_stride, uint64_t x_offset, uint64_t y_offset) {
+    ZC_ENTER(ctx);
+    return moe_down_acc_common(ctx, "zc_moe_fused_down_acc", type, A, a_size, x, x_size, y, y_size, routing,
+                               routing_size, M, K, expert_stride, n_used, x_expert_stride, x_offset, y_offset);
+}
+
+int32_t zc_moe_gate_up_act_ex(zc_ctx* ctx, uint32_t type, const void* Wg, uint64_t wg_size, const void* Wu,
+                              uint64_t wu_size, const void* shared_gate, uint64_t shared_gate_size,
+                              const void* shared_up, uint64_t shared_up_size, const void* gate_bias,
+                              uint64_t gate_bias_size, const void* up_bias, uint64_t up_bias_size, const void* x,
+                              uint64_t x_size, void* y, uint64_t y_size, const void* routing, uint64_t routing_size,
+                              uint32_t M, uint32_t K, uint64_t expert_stride, uint32_t n_used, uint64_t x_offset,
+                              uint64_t y_offset, uint32_t oai) {
+    ZC_ENTER(ctx);
+    if (oai > 1) return fail(ctx, ZC_ERR_INVALID_ARG, "zc_moe_gate_up_act_ex: oai must be 0 or 1");
+    MoeExtras ex;
+    ex.sh = shared_gate;
+    ex.sh_size = shared_gate_size;
+    ex.sh2 = shared_up;
+    ex.sh2_size = shared_up_size;
+    ex.bias = gate_bias;
+    ex.bias_size = gate_bias_size;
+    ex.bias2 = up_bias;
+    ex.bias2_size = up_bias_size;
+    return moe_gate_up_common(ctx, "zc_moe_gate_up_act_ex", type, Wg, wg_size, Wu, wu_size, x, x_size, y, y_size,
+                              nullptr, 0, routing, routing_size, M, K, expert_stride, n_used, 0, x_offset, y_offset,
+                              1 + oai, ex);
+}
+
+int32_t zc_moe_down_acc_ex(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* shared_down,
+                           uint64_t shared_down_size, const void* down_bias, uint64_t down_bias_size, const void* x,
+                           uint64_t x_size, void* y, uint64_t y_size, const void* routing, uint64_t routing_size,
+                           uint32_t M, uint32_t K, uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride,
+                           uint64_t x_offset, uint64_t y_offset) {
+    ZC_ENTER(ctx);
+    MoeExtras ex;
+    ex.sh = shared_down;
+    ex.sh_size = shared_down_size;
+    ex.bias = down_bias;
+    ex.bias_size = down_bias_size;
+    return moe_down_acc_common(ctx, "zc_moe_down_acc_ex", type, A, a_size, x, x_size, y, y_size, routing,
+                               routing_size, M, K, expert_stride, n_used, x_expert_stride, x_offset, y_offset, ex);
+}
+
+int32_t zc_moe_router_topk(zc_ctx* ctx, const void* hidden, uint64_t hidden_size, const void* norm_weights,
+                           uint64_t norm_size, const void* router_weights, uint64_t router_size, const void* bias,
+                           uint64_t bias_size, void* norm_out, uint64_t norm_out_size, void* logits,
+                           uint64_t logits_size, void* routing, uint64_t routing_size, void* routing_local,
+                           uint64_t routing_local_size, uint32_t n_experts, uint32_t K, uint32_t k, uint32_t rule,
+                           float eps, uint32_t shared_slot, uint32_t e_lo, uint32_t e_hi, uint32_t local_shared) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_moe_router_topk";
+    if (n_experts == 0 || k == 0 || k > n_experts || rule > 1 || shared_slot > 1 || K == 0 || (K & 3u))
+        return fail(ctx, ZC_ERR_INVALID_ARG,
+                    "%s: need 0 < k <= n_experts, rule in {0,1}, shared_slot in {0,1}, K a non-zero multiple of 4", fn);
+    if (n_experts > 1024)
+        return fail(ctx, ZC_ERR_INVALID_ARG,
+                    "%s: at most 1024 experts (beyond: zc_rms_norm_dmmv_f32 / zc_dmmv, then zc_softmax_topk)", fn);
+    if (routing_local && (e_lo > e_hi || e_hi > n_experts))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: need e_lo <= e_hi <= n_experts", fn);
+    const uint64_t words = 2ull * (k + shared_slot);
+    ZC_TRY(check_vec(ctx, fn, "hidden", hidden, hidden_size, 0, (uint64_t)K * 4, 16));
+    if (norm_weights) ZC_TRY(check_vec(ctx, fn, "norm_weights", norm_weights, norm_size, 0, (uint64_t)K * 4, 16));
+    ZC_TRY(check_vec(ctx, fn, "router_weights", router_weights, router_size, 0, (uint64_t)n_experts * K * 4, 16));
+    if (bias) ZC_TRY(check_vec(ctx, fn, "bias", bias, bias_size, 0, (uint64_t)n_experts * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "logits", logits, logits_size, 0, (uint64_t)n_experts * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0, words * 4, 4));
+    if (routing_local) ZC_TRY(check_vec(ctx, fn, "routing_local", routing_local, routing_local_size, 0, words * 4, 4));
+    if (norm_out) {
+        if (!norm_weights) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: norm_out without norm_weights", fn);
+        ZC_TRY(check_vec(ctx, fn, "norm_out", norm_out, norm_out_size, 0, (uint64_t)K * 4, 16));
+        if (norm_out == hidden) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: norm_out must not alias hidden", fn);
+    }
+    const cudaError_t e = launch_moe_router_topk(
+        f32p(hidden, 0), norm_weights ? f32p(norm_weights, 0) : nullptr, f32p(router_weights, 0),
+        static_cast<const float*>(bias), norm_out ? f32m(norm_out, 0) : nullptr, f32m(logits, 0),
+        static_cast<uint32_t*>(routing), static_cast<uint32_t*>(routing_local), ctx->router_counter, n_experts, K, k,
+        rule, shared_slot, e_lo, e_hi, local_shared, eps, ctx->stream, &ctx->launches);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, fn);
+    ctx->router_mark = ctx->launches;
+    return ZC_OK;
 }
 
 static int32_t check_moe_batched(zc_ctx* ctx, const char* fn, uint32_t type, const void* A, uint64_t a_size,

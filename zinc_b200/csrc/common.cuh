@@ -55,6 +55,11 @@ __device__ __forceinline__ float e2m1_to_f32(uint32_t n) {
 // on another rank are rewritten to it (zc_moe_ep_filter). Such a slot reads no weights and contributes zeros.
 constexpr uint32_t kSkipExpert = 0xFFFFFFFFu;
 
+// A routing slot that holds kSharedExpert names the shared expert: a matrix outside the expert stack that the
+// launch passes beside it (the always-on expert of a Qwen MoE layer, folded into the routed launch as one more
+// slot). Without such a matrix the id is reported like any other id past the stack.
+constexpr uint32_t kSharedExpert = 0xFFFFFFFEu;
+
 __device__ __forceinline__ uint32_t checked_expert(uint32_t e, uint32_t n_max, uint32_t* status) {
     if (e < n_max) return e;
     if (status) {
@@ -62,6 +67,13 @@ __device__ __forceinline__ uint32_t checked_expert(uint32_t e, uint32_t n_max, u
         status[1] = e;
     }
     return 0u;
+}
+
+// Matrix of the expert a (non-skipped) routing slot names.
+__device__ __forceinline__ const uint8_t* expert_matrix(const uint8_t* stack, const uint8_t* shared, uint32_t e_raw,
+                                                        uint64_t stride, uint32_t n_max, uint32_t* status) {
+    if (e_raw == kSharedExpert && shared) return shared;
+    return stack + (uint64_t)checked_expert(e_raw, n_max, status) * stride;
 }
 
 // ---- loads -----------------------------------------------------------------

@@ -112,14 +112,15 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
                     }
             return;
         }
-        const uint64_t ebase = (uint64_t)checked_expert(e_raw, a.n_experts_max, a.status) * a.expert_stride;
+        const uint8_t* mg = expert_matrix(a.A, a.A_sh, e_raw, a.expert_stride, a.n_experts_max, a.status);
+        const uint8_t* mu = expert_matrix(a.A2, a.A2_sh, e_raw, a.expert_stride, a.n_experts_max, a.status);
         const float* x = a.x + (size_t)slot * a.x_expert_stride;
         const uint8_t* rows[2 * NR];
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
-            const uint64_t off = ebase + (uint64_t)min(row0 + r, a.M - 1) * row_bytes;
-            rows[2 * r] = a.A + off;
-            rows[2 * r + 1] = a.A2 + off;
+            const uint64_t off = (uint64_t)min(row0 + r, a.M - 1) * row_bytes;
+            rows[2 * r] = mg + off;
+            rows[2 * r + 1] = mu + off;
         }
         float acc[2 * NR];
 #pragma unroll
@@ -131,11 +132,16 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
 #pragma unroll
             for (int r = 0; r < NR; ++r)
                 if (row0 + r < a.M) {
+                    float vg = acc[2 * r], vu = acc[2 * r + 1];
+                    if (e_raw < a.n_experts_max) {  // per-expert biases (not for the shared expert's slot)
+                        if (a.bias) vg += __ldg(a.bias + (size_t)e_raw * a.M + row0 + r);
+                        if (a.bias2) vu += __ldg(a.bias2 + (size_t)e_raw * a.M + row0 + r);
+                    }
                     if (a.act) {
-                        a.y[(size_t)slot * a.M + row0 + r] = gate_up_act_v1(a.act, acc[2 * r], acc[2 * r + 1]);
+                        a.y[(size_t)slot * a.M + row0 + r] = gate_up_act_v1(a.act, vg, vu);
                     } else {
-                        a.y[(size_t)slot * a.M + row0 + r] = acc[2 * r];
-                        a.y2[(size_t)slot * a.M + row0 + r] = acc[2 * r + 1];
+                        a.y[(size_t)slot * a.M + row0 + r] = vg;
+                        a.y2[(size_t)slot * a.M + row0 + r] = vu;
                     }
                 }
         }
@@ -179,7 +185,7 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
         for (uint32_t s = 0; s < a.n_used; ++s) {
             const uint32_t e_raw = __ldg(a.routing + s);
             if (e_raw == kSkipExpert) continue;
-            const uint8_t* base = a.A + (uint64_t)checked_expert(e_raw, a.n_experts_max, a.status) * a.expert_stride;
+            const uint8_t* base = expert_matrix(a.A, a.A_sh, e_raw, a.expert_stride, a.n_experts_max, a.status);
             const uint8_t* rows[NR];
 #pragma unroll
             for (int r = 0; r < NR; ++r) rows[r] = base + (uint64_t)min(row0 + r, a.M - 1) * row_bytes;
@@ -190,6 +196,11 @@ __global__ void __launch_bounds__(kWarps * 32) dmmv_kernel(const DmmvArgs a) {
             rowdot<TYPE, NR, ALIGNED>(rows, a.x + (size_t)s * a.x_expert_stride, a.K, lane, acc);
 #pragma unroll
             for (int r = 0; r < NR; ++r) total[r] = fmaf(w, acc[r], total[r]);
+            if (a.bias && lane == 0 && e_raw < a.n_experts_max) {  // the expert's bias, weighted like its product
+#pragma unroll
+                for (int r = 0; r < NR; ++r)
+                    total[r] = fmaf(w, __ldg(a.bias + (size_t)e_raw * a.M + min(row0 + r, a.M - 1)), total[r]);
+            }
         }
 #pragma unroll
         for (int r = 0; r < NR; ++r) total[r] = warp_sum(total[r]);
@@ -260,7 +271,8 @@ cudaError_t launch_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStream_t
     // 128-bit weight loads need every block start 16-byte aligned: true for the
     // 144/176-byte K-quant blocks when the base, the second base and the expert
     // stride are.
-    const bool al = aligned16(a.A) && (a.A2 == nullptr || aligned16(a.A2)) && (a.expert_stride % 16 == 0);
+    const bool al = aligned16(a.A) && (a.A2 == nullptr || aligned16(a.A2)) && (a.expert_stride % 16 == 0) &&
+                    aligned16(a.A_sh) && aligned16(a.A2_sh);
     switch (type) {
         case T_Q4_K: e = al ? launch_type<T_Q4_K, true>(mode, a, s) : launch_type<T_Q4_K, false>(mode, a, s); break;
         case T_Q5_K: e = al ? launch_type<T_Q5_K, true>(mode, a, s) : launch_type<T_Q5_K, false>(mode, a, s); break;

@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
                                                                                    const uint8_t* a_end0,
                                                                                    const uint8_t* a_end1) {
     extern __shared__ uint8_t smem_raw[];
-    pdl_launch_dependents();
+    pdl_prologue(a);
     const uint32_t n_str = kSeg == 3 ? a.nseg : (uint32_t)NS;      // (matrix, activation range) streams per tile
     const uint32_t Kp_total = k_padded(a.K) * (kSeg == 3 ? a.nseg : 1u);
     const SmemX s = carve_x(smem_raw, Kp_total, kWarps);
@@ -195,19 +195,28 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
     const uint32_t n = u1 - u0;
     uint8_t* ring = s.ring + (size_t)warp * kRingX;
 
-    // Matrix base and row bound for tile T in the indexing "row = T * 16 + r".
-    auto locate = [&](uint32_t T, uint32_t strm, const uint8_t*& base, uint32_t& Mb) {
+    // Matrix base, row bound for tile T in the indexing "row = T * 16 + r", and the first byte past the buffer
+    // that holds the matrix. False: the slot names no expert on this rank (nothing to read, zeros contributed).
+    auto locate = [&](uint32_t T, uint32_t strm, const uint8_t*& base, uint32_t& Mb, const uint8_t*& end) -> bool {
         if constexpr (kSeg == 2) {
             const uint32_t slot = T / a.tiles_per_expert, t0 = slot * a.tiles_per_expert * 16;
-            base = a.A[strm] + (uint64_t)checked_expert(__ldg(a.routing + slot), a.n_experts_max, a.status) * a.expert_stride -
-                   (uint64_t)t0 * row_bytes;
+            const uint32_t e_raw = __ldg(a.routing + slot);
+            const uint8_t* m = expert_matrix(a.A[strm], a.A_sh[strm], e_raw, a.expert_stride, a.n_experts_max, a.status);
+            end = m == a.A_sh[strm] ? a.A_sh_end[strm] : (strm == 0 ? a_end0 : a_end1);
+            base = m - (uint64_t)t0 * row_bytes;
             Mb = t0 + a.M;
+            return e_raw != kSkipExpert;
         } else if constexpr (kSeg == 3) {
-            base = a.A[0] + (uint64_t)checked_expert(__ldg(a.routing + strm), a.n_experts_max, a.status) * a.expert_stride;
+            const uint32_t e_raw = __ldg(a.routing + strm);
+            base = expert_matrix(a.A[0], a.A_sh[0], e_raw, a.expert_stride, a.n_experts_max, a.status);
+            end = base == a.A_sh[0] ? a.A_sh_end[0] : a_end0;
             Mb = a.M;
+            return e_raw != kSkipExpert;
         } else {
             base = a.A[strm];
+            end = strm == 0 ? a_end0 : a_end1;
             Mb = a.M;
+            return true;
         }
     };
 
@@ -225,11 +234,17 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
     }
     auto request = [&](uint32_t slot) {
         const uint8_t* base;
+        const uint8_t* a_end;  // first byte past this stream's weight buffer
         uint32_t Mb;
-        locate(p_tile, p_strm, base, Mb);
+        if (!locate(p_tile, p_strm, base, Mb, a_end)) {
+            if (++p_kc == upt) {
+                p_kc = 0;
+                if (++p_strm == n_str) { p_strm = 0; ++p_tile; }
+            }
+            return;
+        }
         const uint32_t seg = min((uint32_t)kUnitBlocks, nb - p_kc * kUnitBlocks) * 17u;  // bytes of this segment
         const uint32_t row0 = p_tile * 16;
-        const uint8_t* a_end = (kSeg == 3 || p_strm == 0) ? a_end0 : a_end1;  // first byte past this stream's weight buffer
         uint8_t* dst = ring + slot * kSlotBytesX;
         const uint8_t* ubase = base + (uint64_t)row0 * row_bytes + (uint64_t)p_kc * kSegBytes;  // row 0 of the unit
         if (row0 + 16 <= Mb && ubase + 16 * row_bytes + 32 <= a_end) {
@@ -295,15 +310,16 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
         __syncwarp();
         // byte offsets of this lane's two rows inside their row slots
         const uint8_t* base;
+        const uint8_t* unused_end;
         uint32_t Mb;
-        locate(tile, strm, base, Mb);
+        const bool live = locate(tile, strm, base, Mb, unused_end);
         const uint32_t rA = min(tile * 16 + g, Mb - 1), rB = min(tile * 16 + g + 8, Mb - 1);
         const uint32_t oA = (uint32_t)(reinterpret_cast<uintptr_t>(base + (uint64_t)rA * row_bytes + (uint64_t)kc * kSegBytes) & 15u);
         const uint32_t oB = (uint32_t)(reinterpret_cast<uintptr_t>(base + (uint64_t)rB * row_bytes + (uint64_t)kc * kSegBytes) & 15u);
         // shared-window byte addresses of the two rows' segments
         const uint32_t sA = ring_s + slot * kSlotBytesX + g * kRowSlot + oA;
         const uint32_t sB = ring_s + slot * kSlotBytesX + (g + 8) * kRowSlot + oB;
-        const uint32_t nblk = min((uint32_t)kUnitBlocks, nb - kc * kUnitBlocks);
+        const uint32_t nblk = live ? min((uint32_t)kUnitBlocks, nb - kc * kUnitBlocks) : 0u;
 #pragma unroll 1
         for (uint32_t gq = 0; gq * 4 < nblk; ++gq) {
             const uint32_t bl = gq * 4 + t;              // this lane's block inside the unit
@@ -375,14 +391,18 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
                 }
             }
             if constexpr (kSeg == 2) {
-                WarpArgs am = a;
                 const uint32_t slot_e = T / a.tiles_per_expert, t0 = slot_e * a.tiles_per_expert * 16;
-                am.y = a.y + (size_t)slot_e * a.M - t0;
-                am.y2 = a.y2 + (size_t)slot_e * a.M - t0;
-                am.M = t0 + a.M;
-                finish_tile<NS, EPI, kWarps>(am, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
+                RowOut o{a.y + (size_t)slot_e * a.M - t0, a.y2 + (size_t)slot_e * a.M - t0, t0 + a.M, nullptr, nullptr};
+                if (a.bias[0]) {  // the slot's expert's rows of the bias tables (none for a shared or absent expert)
+                    const uint32_t e = __ldg(a.routing + slot_e);
+                    if (e < a.n_experts_max) {
+                        o.b0 = a.bias[0] + (size_t)e * a.M - t0;
+                        o.b1 = a.bias[1] ? a.bias[1] + (size_t)e * a.M - t0 : nullptr;
+                    }
+                }
+                finish_tile<NS, EPI, kWarps>(a, o, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
             } else {
-                finish_tile<NS, EPI, kWarps>(a, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
+                finish_tile<NS, EPI, kWarps>(a, row_out(a), s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
             }
         }
     }
@@ -428,6 +448,9 @@ bool common_ok(const DmmvArgs& a) {
     // rows are fetched as 16-byte-aligned supersets: the buffers themselves must start on that boundary
     if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (a.A2 && (reinterpret_cast<uintptr_t>(a.A2) & 15u))) return false;
     if ((a.K & 31u) || a.K == 0) return false;
+    if ((a.A_sh && ((reinterpret_cast<uintptr_t>(a.A_sh) & 15u) || !a.a_sh_end)) ||
+        (a.A2_sh && ((reinterpret_cast<uintptr_t>(a.A2_sh) & 15u) || !a.a2_sh_end)))
+        return false;
     if (smem_bytes_x(k_padded(a.K), 16) > 227 * 1024 || k_padded(a.K) / 256 > (uint32_t)(kPrepX * 8)) return false;
     return true;
 }
@@ -441,7 +464,7 @@ bool mxfp4_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a) {
 }
 
 bool mxfp4_moe_gate_up_eligible(uint32_t type, const DmmvArgs& a) {
-    if (type != T_MXFP4 || a.x_expert_stride != 0 || !a.routing || !a.A2 || !a.y2 || !a.a2_end || !common_ok(a))
+    if (type != T_MXFP4 || a.x_expert_stride != 0 || !a.routing || !a.A2 || (!a.y2 && !a.act) || !a.a2_end || !common_ok(a))
         return false;
     const uint64_t U = (uint64_t)a.n_used * ((a.M + 15) / 16) * (((a.K >> 5) + kUnitBlocks - 1) / kUnitBlocks) * 2;
     return a.n_used >= 1 && U >= 16 && U <= 0xFFFFFFFFull;
@@ -476,6 +499,13 @@ static void fill_common(WarpArgs& wa, const DmmvArgs& a) {
     wa.expert_stride = a.expert_stride;
     wa.tiles_per_expert = (a.M + 15) / 16;
     wa.x_slot_stride = 0;
+    wa.A_sh[0] = a.A_sh;
+    wa.A_sh[1] = a.A2_sh ? a.A2_sh : a.A_sh;
+    wa.A_sh_end[0] = a.a_sh_end;
+    wa.A_sh_end[1] = a.A2_sh ? a.a2_sh_end : a.a_sh_end;
+    wa.bias[0] = a.bias;
+    wa.bias[1] = a.bias2;
+    wa.late = a.late;
 }
 
 cudaError_t launch_mxfp4_dmmv(const DmmvArgs& a, cudaStream_t st, uint64_t* launches) {

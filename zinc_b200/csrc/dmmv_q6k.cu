@@ -251,7 +251,7 @@ template <int EPI, int kWarps, bool kRowsAligned, bool kMoe = false>
 __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel(const WarpArgs a,
                                                                                  const uint8_t* a_end) {
     extern __shared__ uint8_t smem_raw[];
-    pdl_launch_dependents();
+    pdl_prologue(a);
     const uint32_t bpe = a.K >> 8;                        // blocks per row of one matrix
     const uint32_t bpr = kMoe ? bpe * a.nseg : bpe;       // blocks per (concatenated) row = units per tile
     const Smem6 s = carve6(smem_raw, bpr * 256, kWarps);
@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
             lb = b - slot * bpe;
             const uint32_t e_raw = __ldg(a.routing + slot);
             if (e_raw == kSkipExpert) return nullptr;  // no expert in this slot on this rank
-            return a.A[0] + (uint64_t)checked_expert(e_raw, a.n_experts_max, a.status) * a.expert_stride;
+            return expert_matrix(a.A[0], a.A_sh[0], e_raw, a.expert_stride, a.n_experts_max, a.status);
         } else {
             lb = b;
             return a.A[0];
@@ -302,6 +302,8 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
         } else {
             uint32_t lb;
             const uint8_t* mat = matrix_of(p_blk, lb);
+            // first byte past the buffer that holds `mat` (the shared expert lives in a buffer of its own)
+            const uint8_t* m_end = kMoe && mat == a.A_sh[0] ? a.A_sh_end[0] : a_end;
 #pragma unroll
             for (int i = 0; i < kPiecesLane6; ++i) {
                 if (kMoe && mat == nullptr) break;  // nothing to fetch
@@ -312,10 +314,10 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
                 if (col * 16 < o + 210u) {  // the piece holds bytes of the block
                     const uint8_t* src = start - o + col * 16;
                     uint8_t* d = dst + r * kRow6 + col * 16;
-                    if (src + 16 <= a_end) {
+                    if (src + 16 <= m_end) {
                         cp_async16(d, src);
                     } else {  // the very end of the tensor: copy only the bytes that exist
-                        for (const uint8_t* q = src; q < a_end; ++q) d[q - src] = __ldg(q);
+                        for (const uint8_t* q = src; q < m_end; ++q) d[q - src] = __ldg(q);
                     }
                 }
             }
@@ -401,7 +403,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
                 v[0][r] = w;
                 acc[r] = 0.f;
             }
-            finish_tile<1, EPI, kWarps>(a, s.spartial, s.sflags, v, T, bpr, u0, u1, U, G, me, warp, lane);
+            finish_tile<1, EPI, kWarps>(a, row_out(a), s.spartial, s.sflags, v, T, bpr, u0, u1, U, G, me, warp, lane);
         }
     }
 }
@@ -460,6 +462,7 @@ bool q6k_moe_down_acc_eligible(uint32_t type, const DmmvArgs& a) {
     if (!a.scratch_partial || !a.status) return false;
     if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (a.expert_stride & 15u) || (a.K & 255u)) return false;
     if ((a.x_expert_stride & 3u) || (reinterpret_cast<uintptr_t>(a.x) & 15u)) return false;
+    if (a.A_sh && ((reinterpret_cast<uintptr_t>(a.A_sh) & 15u) || !a.a_sh_end)) return false;
     const uint32_t bpr = (a.K >> 8) * a.n_used;
     if (smem_bytes6(bpr * 256, 16) > 227 * 1024 || bpr > (uint32_t)(kPrepBlocks * 8)) return false;
     const uint64_t U = (uint64_t)((a.M + 15) / 16) * bpr;
@@ -484,6 +487,10 @@ cudaError_t launch_q6k_moe_down_acc(const DmmvArgs& a, cudaStream_t st, uint64_t
     wa.n_experts_max = a.n_experts_max;
     wa.expert_stride = a.expert_stride;
     wa.x_slot_stride = a.x_expert_stride;
+    wa.A_sh[0] = wa.A_sh[1] = a.A_sh;
+    wa.A_sh_end[0] = wa.A_sh_end[1] = a.a_sh_end;
+    wa.bias[0] = a.bias;
+    wa.late = a.late;
     const uint32_t Kt = a.K * a.n_used;
     const size_t s8 = smem_bytes6(Kt, 8);
     const cudaError_t e = s8 <= kTwoPerSm ? launch_w6<EPI_ACC, 8, false, true>(wa, a.a_end, st, a.sm_count, s8)
@@ -509,6 +516,7 @@ cudaError_t launch_q6k_dmmv(int mode, const DmmvArgs& a, cudaStream_t st, uint64
     wa.nseg = 0;
     wa.push = a.push;
     wa.consume = a.consume;
+    wa.late = a.late;
     cudaError_t e = mode == MODE_PLAIN ? launch_cfg6<EPI_PLAIN>(wa, a.a_end, st, a.sm_count)
                                        : launch_cfg6<EPI_SIGMOID_ACC>(wa, a.a_end, st, a.sm_count);
     if (e == cudaSuccess && launches) ++*launches;

@@ -169,7 +169,7 @@ __device__ __forceinline__ int seg_of(const WarpArgs& a, uint32_t T) {
 template <int NS, int EPI, int kWarps, int kSeg = 0>
 __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel(const WarpArgs a) {
     extern __shared__ uint8_t smem_raw[];
-    pdl_launch_dependents();
+    pdl_prologue(a);
     const Smem s = carve(smem_raw, a.K, kWarps);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
                 }
                 return;
             }
-            base = a.A[p_strm] + (uint64_t)checked_expert(e_raw, a.n_experts_max, a.status) * a.expert_stride -
+            base = expert_matrix(a.A[p_strm], a.A_sh[p_strm], e_raw, a.expert_stride, a.n_experts_max, a.status) -
                    (uint64_t)t0 * row_bytes;
             Mb = t0 + a.M;
         } else {
@@ -376,20 +376,23 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
                 }
             }
             if constexpr (kSeg == 2) {
-                WarpArgs am = a;
                 const uint32_t slot = T / a.tiles_per_expert, t0 = slot * a.tiles_per_expert * 16;
-                am.y = a.y + (size_t)slot * a.M - t0;
-                am.y2 = a.y2 + (size_t)slot * a.M - t0;
-                am.M = t0 + a.M;
-                finish_tile<NS, EPI, kWarps>(am, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
+                RowOut o{a.y + (size_t)slot * a.M - t0, a.y2 + (size_t)slot * a.M - t0, t0 + a.M, nullptr, nullptr};
+                if (a.bias[0]) {  // the slot's expert's rows of the bias tables (none for a shared or absent expert)
+                    const uint32_t e = __ldg(a.routing + slot);
+                    if (e < a.n_experts_max) {
+                        o.b0 = a.bias[0] + (size_t)e * a.M - t0;
+                        o.b1 = a.bias[1] ? a.bias[1] + (size_t)e * a.M - t0 : nullptr;
+                    }
+                }
+                finish_tile<NS, EPI, kWarps>(a, o, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
             } else if constexpr (kSeg == 1) {
-                WarpArgs am = a;
                 const int sg = seg_of(a, T);
-                am.y = a.segY[sg];
-                am.M = a.segM[sg];
-                finish_tile<NS, EPI, kWarps>(am, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
+                const RowOut o{sg == 0 ? a.segY[0] : sg == 1 ? a.segY[1] : a.segY[2], nullptr,
+                               sg == 0 ? a.segM[0] : sg == 1 ? a.segM[1] : a.segM[2], nullptr, nullptr};
+                finish_tile<NS, EPI, kWarps>(a, o, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
             } else {
-                finish_tile<NS, EPI, kWarps>(a, s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
+                finish_tile<NS, EPI, kWarps>(a, row_out(a), s.spartial, s.sflags, v, T, upt_all, u0, u1, U, G, me, warp, lane);
             }
         }
     }
@@ -447,6 +450,7 @@ cudaError_t launch_warp_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStr
     wa.nseg = 0;
     wa.push = a.push;
     wa.consume = a.consume;
+    wa.late = a.late;
     cudaError_t e;
     switch (mode) {
         case MODE_PLAIN: e = launch_cfg<1, EPI_PLAIN>(wa, st, a.sm_count); break;
@@ -488,6 +492,7 @@ cudaError_t launch_warp_dmmv_multi(uint32_t n, const uint8_t* const* A, float* c
     wa.status = common.status;
     wa.spin_limit = common.spin_limit;
     wa.consume = common.consume;
+    wa.late = common.late;
     wa.nseg = n;
     const uint64_t row_bytes = (uint64_t)(common.K >> 8) * 144;
     uint32_t t0 = 0;
@@ -517,10 +522,11 @@ cudaError_t launch_warp_dmmv_multi(uint32_t n, const uint8_t* const* A, float* c
 
 // MoE fused gate + up: y_gate[s][M], y_up[s][M] = Wg[routing[s]] x, Wu[routing[s]] x for the n_used slots, x shared.
 bool warp_moe_gate_up_eligible(uint32_t type, const DmmvArgs& a) {
-    if (type != T_Q4_K || a.x_expert_stride != 0 || !a.routing || !a.A2 || !a.y2) return false;
+    if (type != T_Q4_K || a.x_expert_stride != 0 || !a.routing || !a.A2 || (!a.y2 && !a.act)) return false;
     if (!a.scratch_partial || !a.status) return false;
     if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (reinterpret_cast<uintptr_t>(a.A2) & 15u) || (a.expert_stride & 15u))
         return false;
+    if ((reinterpret_cast<uintptr_t>(a.A_sh) & 15u) || (reinterpret_cast<uintptr_t>(a.A2_sh) & 15u)) return false;
     if ((a.K & 255u) || smem_bytes(a.K, 16) > 227 * 1024 || (a.K >> 8) > (uint32_t)(kPrepBlocks * 8)) return false;
     const uint64_t U = (uint64_t)a.n_used * ((a.M + 15) / 16) * (((a.K >> 8) + kCB - 1) / kCB) * 2;
     return a.n_used >= 1 && U >= 16 && U <= 0xFFFFFFFFull;
@@ -546,6 +552,11 @@ cudaError_t launch_warp_moe_gate_up(const DmmvArgs& a, cudaStream_t st, uint64_t
     wa.n_experts_max = a.n_experts_max;
     wa.expert_stride = a.expert_stride;
     wa.tiles_per_expert = (a.M + 15) / 16;
+    wa.A_sh[0] = a.A_sh;
+    wa.A_sh[1] = a.A2_sh;
+    wa.bias[0] = a.bias;
+    wa.bias[1] = a.bias2;
+    wa.late = a.late;
     const size_t s8 = smem_bytes(a.K, 8);
     cudaError_t e = s8 <= kTwoPerSm ? launch_w<2, EPI_PAIR, 8, 2>(wa, st, a.sm_count, s8)
                                     : launch_w<2, EPI_PAIR, 16, 2>(wa, st, a.sm_count, smem_bytes(a.K, 16));

@@ -87,6 +87,20 @@ struct DmmvArgs {
     // must not read beyond them)
     const uint8_t* a_end = nullptr;
     const uint8_t* a2_end = nullptr;
+    // MoE launches: the matrices a routing slot with the id kSharedExpert selects (null: there is none)
+    const uint8_t* A_sh = nullptr;
+    const uint8_t* A2_sh = nullptr;
+    const uint8_t* a_sh_end = nullptr;   // first byte past their buffers
+    const uint8_t* a2_sh_end = nullptr;
+    // MoE launches: per-expert f32 biases [n_experts][M]. Gate / up: added to the gate and up rows before the
+    // activation. Down + accumulate: sum_s w_s bias[e_s][row] joins the weighted sum. Never applied to the
+    // shared expert's slot.
+    const float* bias = nullptr;
+    const float* bias2 = nullptr;
+    // The kernel right before this one in the stream releases its dependents early and may still be producing
+    // the routing buffer: read the routing only after the dependency wait, and release this launch's own
+    // dependents only after it (so that a successor's prologue may trust everything older).
+    bool late = false;
 };
 
 // Capacity of the split-K scratch a context owns.
@@ -178,10 +192,19 @@ cudaError_t launch_moe_weighted_bias_acc(float* a, const float* bias, const uint
                                          uint64_t* launches);
 // y[m] = sum_k W[m][k] * xn[k], xn = norm_w * (x * rsqrt(mean(x^2) + eps)) (also written to norm_out when
 // given); norm_w == nullptr: xn = x. One CTA per row: for matrices with few rows (routers). K % 4 == 0.
+// With W2 / y2: a second M x K matrix on the same normalised vector in the same launch (y2 = W2 xn).
 cudaError_t launch_rms_norm_dmmv_f32(const float* x, const float* norm_w, const float* W, float* norm_out, float* y,
-                                     uint32_t M, uint32_t K, float eps, cudaStream_t s, uint64_t* launches);
+                                     uint32_t M, uint32_t K, float eps, cudaStream_t s, uint64_t* launches,
+                                     const float* W2 = nullptr, float* y2 = nullptr);
 // Expert parallelism: routing rows [k ids][k weights] -> ids of the experts [lo, hi) renumbered from 0, the others
 // replaced by the "no expert" mark (kernels read no weights for such a slot and contribute zeros).
+// Router matvec (optionally behind the RMS norm) + expert selection in one launch, for up to 1024 experts
+// (cudaErrorNotSupported beyond, or when K is not a multiple of 4). `counter`: one zeroed word of context scratch.
+cudaError_t launch_moe_router_topk(const float* x, const float* norm_w, const float* W, const float* bias,
+                                   float* norm_out, float* logits, uint32_t* routing, uint32_t* routing_local,
+                                   uint32_t* counter, uint32_t n_experts, uint32_t K, uint32_t k, uint32_t rule,
+                                   uint32_t shared, uint32_t e_lo, uint32_t e_hi, uint32_t local_shared, float eps,
+                                   cudaStream_t s, uint64_t* launches);
 cudaError_t launch_moe_ep_filter(const uint32_t* in, uint32_t* out, uint32_t k, uint32_t n_tokens, uint32_t stride_in,
                                  uint32_t stride_out, uint32_t lo, uint32_t hi, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_count_experts(const uint32_t* a, uint32_t* counts, uint32_t n_experts, uint32_t ne00,

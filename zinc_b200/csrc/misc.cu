@@ -133,18 +133,12 @@ __global__ void __launch_bounds__(kTopkThreads) softmax_topk_kernel(
     }
 }
 
-// The same selection for up to 32 * VPL experts with one warp per token and no block-wide barrier: lane l
-// holds experts l, l + 32, ... in registers. A router has at most a few hundred experts, and the k rounds
-// of block-wide barriers of the kernel above cost more than the arithmetic.
+// One warp selects for one token: lane l holds experts l, l + 32, ... in registers. Ids go to o[0..k), weights (f32 bits) to o[wofs .. wofs + k): wofs = k is the
+// reference's layout, a larger wofs leaves room for slots behind the selected ones. The logits are read past
+// L1 (they may have been written by other CTAs of the same launch).
 template <int VPL>
-__global__ void __launch_bounds__(128) softmax_topk_warp_kernel(
-    const float* __restrict__ logits, const float* __restrict__ bias, uint32_t* __restrict__ out,
-    uint32_t n, uint32_t k, uint32_t rule, uint32_t n_tokens, uint32_t logits_stride, uint32_t out_stride) {
-    const int lane = threadIdx.x & 31;
-    const uint32_t tok = blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (tok >= n_tokens) return;
-    const float* lg = logits + (size_t)tok * logits_stride;
-    uint32_t* o = out + (size_t)tok * out_stride;
+__device__ __forceinline__ void softmax_topk_warp(const float* lg, const float* __restrict__ bias, uint32_t* o,
+                                                  uint32_t n, uint32_t k, uint32_t rule, uint32_t wofs, int lane) {
     const float floor_v = rule == 0u ? -1.0f : -INFINITY;
     const float gone = rule == 0u ? -2.0f : -INFINITY;  // never selected (again)
 
@@ -153,7 +147,7 @@ __global__ void __launch_bounds__(128) softmax_topk_warp_kernel(
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
         const uint32_t i = lane + 32 * j;
-        v[j] = i < n ? lg[i] + (bias ? bias[i] : 0.0f) : -INFINITY;
+        v[j] = i < n ? __ldcg(lg + i) + (bias ? bias[i] : 0.0f) : -INFINITY;
         lmax = fmaxf(lmax, v[j]);
     }
     if (rule == 0u) {  // softmax over all experts first
@@ -186,7 +180,7 @@ __global__ void __launch_bounds__(128) softmax_topk_warp_kernel(
         if (!(best.v > floor_v)) best = ValIdx{rule == 0u ? floor_v : v0, 0u};
         if (lane == 0) {
             o[ki] = best.i;
-            o[k + ki] = __float_as_uint(best.v);
+            o[wofs + ki] = __float_as_uint(best.v);
         }
 #pragma unroll
         for (int j = 0; j < VPL; ++j)
@@ -195,22 +189,36 @@ __global__ void __launch_bounds__(128) softmax_topk_warp_kernel(
     if (lane == 0) {
         if (rule == 0u) {
             float ws = 0.f;
-            for (uint32_t i = 0; i < k; ++i) ws += __uint_as_float(o[k + i]);
+            for (uint32_t i = 0; i < k; ++i) ws += __uint_as_float(o[wofs + i]);
             if (ws > 0.f)
-                for (uint32_t i = 0; i < k; ++i) o[k + i] = __float_as_uint(__uint_as_float(o[k + i]) / ws);
+                for (uint32_t i = 0; i < k; ++i) o[wofs + i] = __float_as_uint(__uint_as_float(o[wofs + i]) / ws);
         } else {
             float mx = -INFINITY;
-            for (uint32_t i = 0; i < k; ++i) mx = fmaxf(mx, __uint_as_float(o[k + i]));
+            for (uint32_t i = 0; i < k; ++i) mx = fmaxf(mx, __uint_as_float(o[wofs + i]));
             float sum = 0.f;
             for (uint32_t i = 0; i < k; ++i) {
-                const float w = expf(__uint_as_float(o[k + i]) - mx);
-                o[k + i] = __float_as_uint(w);
+                const float w = expf(__uint_as_float(o[wofs + i]) - mx);
+                o[wofs + i] = __float_as_uint(w);
                 sum += w;
             }
             if (sum > 0.f)
-                for (uint32_t i = 0; i < k; ++i) o[k + i] = __float_as_uint(__uint_as_float(o[k + i]) / sum);
+                for (uint32_t i = 0; i < k; ++i) o[wofs + i] = __float_as_uint(__uint_as_float(o[wofs + i]) / sum);
         }
     }
+}
+
+// The same selection for up to 32 * VPL experts with one warp per token and no block-wide barrier: lane l
+// holds experts l, l + 32, ... in registers. A router has at most a few hundred experts, and the k rounds
+// of block-wide barriers of the kernel above cost more than the arithmetic.
+template <int VPL>
+__global__ void __launch_bounds__(128) softmax_topk_warp_kernel(
+    const float* __restrict__ logits, const float* __restrict__ bias, uint32_t* __restrict__ out,
+    uint32_t n, uint32_t k, uint32_t rule, uint32_t n_tokens, uint32_t logits_stride, uint32_t out_stride) {
+    const int lane = threadIdx.x & 31;
+    const uint32_t tok = blockIdx.x * 4 + (threadIdx.x >> 5);
+    if (tok >= n_tokens) return;
+    softmax_topk_warp<VPL>(logits + (size_t)tok * logits_stride, bias, out + (size_t)tok * out_stride, n, k, rule, k,
+                           lane);
 }
 
 // ---- combine / activation ------------------------------------------------------------
@@ -346,9 +354,18 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 __global__ void __launch_bounds__(kRouterThreads) rms_norm_dmmv_f32_kernel(
     const float* __restrict__ x, const float* __restrict__ norm_w, const float* __restrict__ W,
-    float* __restrict__ norm_out, float* __restrict__ y, uint32_t M, uint32_t K, float eps) {
+    float* __restrict__ norm_out, float* __restrict__ y, uint32_t M, uint32_t K, float eps,
+    const float* __restrict__ W2, float* __restrict__ y2) {
     __shared__ float scratch[kRouterThreads / 32];
-    const uint32_t row = blockIdx.x, tid = threadIdx.x;
+    // CTAs [0, M) take the rows of W, CTAs [M, 2M) those of a second matrix on the same normalised vector
+    // (src/shaders/rms_norm_dmmv_q4k_alpha_beta.comp:64-133: the alpha and beta projections of an SSM layer)
+    const uint32_t tid = threadIdx.x;
+    const bool second = blockIdx.x >= M;
+    const uint32_t row = second ? blockIdx.x - M : blockIdx.x;
+    if (second) {
+        W = W2;
+        y = y2;
+    }
     const uint32_t K4 = K >> 2;
     const float4* x4 = reinterpret_cast<const float4*>(x);
     float rms_inv = 1.f;
@@ -369,13 +386,113 @@ __global__ void __launch_bounds__(kRouterThreads) rms_norm_dmmv_f32_kernel(
         if (norm_w) {
             const float4 w = __ldg(w4 + i);
             v = make_float4(w.x * (v.x * rms_inv), w.y * (v.y * rms_inv), w.z * (v.z * rms_inv), w.w * (v.w * rms_inv));
-            if (row == 0 && norm_out) reinterpret_cast<float4*>(norm_out)[i] = v;
+            if (blockIdx.x == 0 && norm_out) reinterpret_cast<float4*>(norm_out)[i] = v;
         }
         const float4 r = __ldg(r4 + i);
         sum += v.x * r.x + v.y * r.y + v.z * r.z + v.w * r.w;
     }
     sum = block_sum(sum, scratch);
     if (tid == 0) y[row] = sum;
+}
+
+// ---- router matvec + expert selection in one launch ----------------------------------------------
+// The f32 router of one token (optionally behind the RMS norm, as above) and the selection that follows it
+// (src/compute/forward.zig:6139-6190: router DMMV, then softmax_topk): one CTA per router row; the CTA that
+// finishes last (a ticket from an atomic counter, which it puts back to zero) runs the one-warp selection over
+// the logits all CTAs wrote. Behind the k selected slots the routing buffer can carry one more slot for the
+// shared expert (id kSharedExpert, weight 1), and a second routing buffer can receive the same selection as an
+// expert-parallel rank sees it: ids in [e_lo, e_hi) renumbered from zero, every other slot marked "no expert
+// here", the shared slot kept only where `local_shared` says so.
+// Launched as a programmatic dependent: the row of router weights is in registers before the wait for the
+// previous kernel, and the next kernel of the stream is released at once.
+struct RouterArgs {
+    const float* x;
+    const float* norm_w;
+    const float* W;
+    const float* bias;
+    float* norm_out;
+    float* logits;
+    uint32_t* routing;
+    uint32_t* routing_local;
+    uint32_t* counter;
+    uint32_t n_experts, K, k, rule, shared, e_lo, e_hi, local_shared;
+    float eps;
+};
+constexpr int kRouterPrefetch = 4;  // float4 per thread held across the dependency wait (K <= 4096)
+
+__global__ void __launch_bounds__(kRouterThreads) moe_router_topk_kernel(const RouterArgs a) {
+    __shared__ float scratch[kRouterThreads / 32];
+    __shared__ uint32_t s_last;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const uint32_t tid = threadIdx.x, row = blockIdx.x;
+    const uint32_t K4 = a.K >> 2;
+    const float4* r4 = reinterpret_cast<const float4*>(a.W + (size_t)row * a.K);
+    float4 wreg[kRouterPrefetch];
+#pragma unroll
+    for (int j = 0; j < kRouterPrefetch; ++j) {
+        const uint32_t i = tid + j * kRouterThreads;
+        wreg[j] = i < K4 ? __ldg(r4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const float4* x4 = reinterpret_cast<const float4*>(a.x);
+    float rms_inv = 1.f;
+    if (a.norm_w) {
+        float ss = 0.f;
+        for (uint32_t i = tid; i < K4; i += kRouterThreads) {
+            const float4 v = __ldg(x4 + i);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        ss = block_sum(ss, scratch);
+        rms_inv = rsqrtf(ss / (float)a.K + a.eps);
+    }
+    const float4* w4 = reinterpret_cast<const float4*>(a.norm_w);
+    float sum = 0.f;
+    auto term = [&](uint32_t i, const float4 r) {
+        float4 v = __ldg(x4 + i);
+        if (a.norm_w) {
+            const float4 w = __ldg(w4 + i);
+            v = make_float4(w.x * (v.x * rms_inv), w.y * (v.y * rms_inv), w.z * (v.z * rms_inv), w.w * (v.w * rms_inv));
+            if (row == 0 && a.norm_out) reinterpret_cast<float4*>(a.norm_out)[i] = v;
+        }
+        sum += v.x * r.x + v.y * r.y + v.z * r.z + v.w * r.w;
+    };
+#pragma unroll
+    for (int j = 0; j < kRouterPrefetch; ++j) {
+        const uint32_t i = tid + j * kRouterThreads;
+        if (i < K4) term(i, wreg[j]);
+    }
+    for (uint32_t i = tid + kRouterPrefetch * kRouterThreads; i < K4; i += kRouterThreads) term(i, __ldg(r4 + i));
+    sum = block_sum(sum, scratch);
+    if (tid == 0) {
+        a.logits[row] = sum;
+        __threadfence();
+        s_last = atomicAdd(a.counter, 1u) == gridDim.x - 1 ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!s_last || tid >= 32) return;
+    // ---- the last CTA's first warp: every logit is in global memory ----
+    __threadfence();
+    if (tid == 0) *a.counter = 0u;
+    const uint32_t n = a.n_experts, k = a.k, slots = k + a.shared;
+    uint32_t* o = a.routing;
+    if (n <= 32) softmax_topk_warp<1>(a.logits, a.bias, o, n, k, a.rule, slots, (int)tid);
+    else if (n <= 256) softmax_topk_warp<8>(a.logits, a.bias, o, n, k, a.rule, slots, (int)tid);
+    else softmax_topk_warp<32>(a.logits, a.bias, o, n, k, a.rule, slots, (int)tid);
+    if (tid == 0 && a.shared) {
+        o[k] = kSharedExpert;
+        o[slots + k] = 0x3F800000u;
+    }
+    __syncwarp();
+    if (a.routing_local) {
+        for (uint32_t j = tid; j < slots; j += 32) {
+            const uint32_t id = o[j];
+            uint32_t lid;
+            if (j >= k) lid = a.local_shared ? kSharedExpert : kSkipExpert;
+            else lid = (id >= a.e_lo && id < a.e_hi) ? id - a.e_lo : kSkipExpert;
+            a.routing_local[j] = lid;
+            a.routing_local[slots + j] = o[slots + j];
+        }
+    }
 }
 
 // src/shaders/count_experts.comp:58-83: one CTA per expert.
@@ -490,6 +607,28 @@ cudaError_t launch_softmax_topk(const float* logits, const float* bias, uint32_t
     return cudaGetLastError();
 }
 
+cudaError_t launch_moe_router_topk(const float* x, const float* norm_w, const float* W, const float* bias,
+                                   float* norm_out, float* logits, uint32_t* routing, uint32_t* routing_local,
+                                   uint32_t* counter, uint32_t n_experts, uint32_t K, uint32_t k, uint32_t rule,
+                                   uint32_t shared, uint32_t e_lo, uint32_t e_hi, uint32_t local_shared, float eps,
+                                   cudaStream_t s, uint64_t* launches) {
+    if (n_experts == 0 || n_experts > 1024 || (K & 3u)) return cudaErrorNotSupported;
+    RouterArgs a{x, norm_w, W, bias, norm_out, logits, routing, routing_local, counter,
+                 n_experts, K, k, rule, shared, e_lo, e_hi, local_shared, eps};
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_experts, 1, 1);
+    cfg.blockDim = dim3(kRouterThreads, 1, 1);
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, moe_router_topk_kernel, a);
+    if (e == cudaSuccess && launches) ++*launches;
+    return e;
+}
+
 cudaError_t launch_moe_weighted_acc(float* a, const float* b, const uint32_t* routing, uint32_t n, uint32_t n_used,
                                     uint32_t src_stride, cudaStream_t s, uint64_t* launches) {
     if (n == 0) return cudaSuccess;
@@ -579,8 +718,9 @@ cudaError_t launch_moe_route_scatter(const uint32_t* routing, const float* src, 
 }
 
 cudaError_t launch_rms_norm_dmmv_f32(const float* x, const float* norm_w, const float* W, float* norm_out, float* y,
-                                     uint32_t M, uint32_t K, float eps, cudaStream_t s, uint64_t* launches) {
-    rms_norm_dmmv_f32_kernel<<<M, kRouterThreads, 0, s>>>(x, norm_w, W, norm_out, y, M, K, eps);
+                                     uint32_t M, uint32_t K, float eps, cudaStream_t s, uint64_t* launches,
+                                     const float* W2, float* y2) {
+    rms_norm_dmmv_f32_kernel<<<W2 ? 2 * M : M, kRouterThreads, 0, s>>>(x, norm_w, W, norm_out, y, M, K, eps, W2, y2);
     if (launches) ++*launches;
     return cudaGetLastError();
 }

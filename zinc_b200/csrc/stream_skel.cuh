@@ -45,7 +45,21 @@ struct WarpArgs {
     PushArgs push;           // EPI_PLAIN: rows go to every rank's receive buffer instead of y
     ConsumeArgs consume;     // pending reduction completed by this launch's threads after the dependency wait
     uint32_t act = 0;        // EPI_PAIR only: 0 write both streams, 1 y = silu(gate) * up, 2 the GPT-OSS form
+    const uint8_t* A_sh[2] = {nullptr, nullptr};  // MoE: matrices of the slot whose id is kSharedExpert
+    const uint8_t* A_sh_end[2] = {nullptr, nullptr};  // first byte past the buffers that hold them
+    // MoE per-expert biases [n_experts][M]: EPI_PAIR adds the slot's expert's rows of bias[0] / bias[1] to the
+    // gate / up row; EPI_ACC adds sum_s w_s bias[0][e_s][row]
+    const float* bias[2] = {nullptr, nullptr};
+    uint32_t late = 0;       // release the dependents after the dependency wait, and read the routing after it
 };
+
+// Start of a streaming kernel: release the next kernel of the stream at once, unless this launch was told that
+// its predecessor did the same while the routing buffer was still being written. Then the dependency wait comes
+// first, so that whatever starts behind this kernel finds every older kernel complete.
+__device__ __forceinline__ void pdl_prologue(const WarpArgs& a) {
+    if (a.late) pdl_wait();
+    pdl_launch_dependents();
+}
 
 // The activation a fused gate + up launch applies (src/shaders/swiglu.comp:25-33, swiglu_oai.comp:24-34).
 __device__ __forceinline__ float gate_up_act(uint32_t act, float gate, float up) {
@@ -139,28 +153,49 @@ __device__ __forceinline__ void consume_pushed(const ConsumeArgs& c, uint32_t ct
 
 enum { EPI_PLAIN = 0, EPI_GATE_UP = 1, EPI_SIGMOID_ACC = 2, EPI_PAIR = 3, EPI_ACC = 4 };
 
+// Where the rows of one tile go: the launch's own outputs, or those of the segment / expert slot the tile
+// belongs to, moved back by the segment's first row so that the global row number indexes them.
+struct RowOut {
+    float* y;
+    float* y2;
+    uint32_t M;       // row bound in that indexing
+    const float* b0;  // EPI_PAIR: the slot's expert's gate / up bias rows (null: none); EPI_ACC: the bias table
+    const float* b1;
+};
+__device__ __forceinline__ RowOut row_out(const WarpArgs& a) { return RowOut{a.y, a.y2, a.M, a.bias[0], a.bias[1]}; }
+
 template <int NS, int EPI>
-__device__ __forceinline__ void write_row(const WarpArgs& a, uint32_t row, const float (&v)[NS]) {
-    if (row >= a.M) return;
+__device__ __forceinline__ void write_row(const WarpArgs& a, const RowOut& o, uint32_t row, const float (&v)[NS]) {
+    if (row >= o.M) return;
     if constexpr (EPI == EPI_GATE_UP) {
-        a.y[row] = (v[0] / (1.0f + expf(-v[0]))) * v[1];
+        o.y[row] = (v[0] / (1.0f + expf(-v[0]))) * v[1];
     } else if constexpr (EPI == EPI_ACC) {  // y += result, whatever acc_mode says
-        a.y[row] += v[0];
+        float b = 0.f;
+        if (o.b0) {  // MoE down projection: the selected experts' biases, weighted like their products
+            for (uint32_t s = 0; s < a.nseg; ++s) {
+                const uint32_t e = __ldg(a.routing + s);
+                if (e < a.n_experts_max)
+                    b = fmaf(__uint_as_float(__ldg(a.routing + a.nseg + s)), __ldg(o.b0 + (size_t)e * a.M + row), b);
+            }
+        }
+        o.y[row] += v[0] + b;
     } else if constexpr (EPI == EPI_PAIR) {  // two streams (MoE gate and up rows): both outputs, or their activation
+        const float vg = o.b0 ? v[0] + __ldg(o.b0 + row) : v[0];
+        const float vu = o.b1 ? v[NS - 1] + __ldg(o.b1 + row) : v[NS - 1];
         if (a.act) {
-            a.y[row] = gate_up_act(a.act, v[0], v[NS - 1]);
+            o.y[row] = gate_up_act(a.act, vg, vu);
         } else {
-            a.y[row] = v[0];
-            a.y2[row] = v[NS - 1];
+            o.y[row] = vg;
+            o.y2[row] = vu;
         }
     } else if constexpr (EPI == EPI_SIGMOID_ACC) {
-        a.y[row] += (1.0f / (1.0f + expf(-__ldg(a.gate)))) * v[0];
+        o.y[row] += (1.0f / (1.0f + expf(-__ldg(a.gate)))) * v[0];
     } else {
         if (a.push.world) {
             const uint2 pv = make_uint2(__float_as_uint(v[0]), 1u);
             for (uint32_t r = 0; r < a.push.world; ++r) a.push.peers[r][row] = pv;
         } else {
-            a.y[row] = a.acc_mode ? a.y[row] + v[0] : v[0];
+            o.y[row] = a.acc_mode ? o.y[row] + v[0] : v[0];
         }
     }
 }
@@ -170,7 +205,7 @@ __device__ __forceinline__ void write_row(const WarpArgs& a, uint32_t row, const
 // Ends a tile for this warp. v[i][r]: sums of stream i for rows g (r = 0) and g+8 (r = 1), already
 // reduced over the four lanes of a row.
 template <int NS, int EPI, int kWarps>
-__device__ __forceinline__ void finish_tile(const WarpArgs& a, float* spartial, volatile uint32_t* sflags, float (&v)[NS][2], uint32_t T,
+__device__ __forceinline__ void finish_tile(const WarpArgs& a, const RowOut& o, float* spartial, volatile uint32_t* sflags, float (&v)[NS][2], uint32_t T,
                                             uint32_t upt_all, uint32_t u0, uint32_t u1, uint32_t U, uint32_t G,
                                             uint32_t me, int warp, int lane) {
     const int g = lane >> 2, t = lane & 3;
@@ -260,8 +295,8 @@ __device__ __forceinline__ void finish_tile(const WarpArgs& a, float* spartial, 
         float r0[NS], r1[NS];
 #pragma unroll
         for (int i = 0; i < NS; ++i) { r0[i] = v[i][0]; r1[i] = v[i][1]; }
-        write_row<NS, EPI>(a, T * 16 + g, r0);
-        write_row<NS, EPI>(a, T * 16 + g + 8, r1);
+        write_row<NS, EPI>(a, o, T * 16 + g, r0);
+        write_row<NS, EPI>(a, o, T * 16 + g + 8, r1);
     }
 }
 

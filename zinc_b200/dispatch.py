@@ -373,6 +373,47 @@ class DmmvDispatch:
                       y.ptr, y.size, routing.ptr, routing.size, M, K, expert_stride, n_used, x_expert_stride,
                       x_offset, y_offset, 1 if oai else 0)
 
+    # One launch for the routed gate + up dispatch, the shared expert's gate + up (a slot with the id
+    # SHARED_EXPERT), the per-expert gate / up biases and the activation (forward.zig:6206-6240, 6455-6500,
+    # 6841-6849). shared = (gate, up) matrices or None; biases = (gate_bias, up_bias) [n_experts][M] or None.
+    def dispatchMoeGateUpActEx(self, quant_type, Wg, Wu, x, y, routing, M, K, expert_stride, n_used, shared=None,
+                               biases=None, oai=False, x_offset=0, y_offset=0):
+        Wg, Wu, x, y, routing = map(_buf, (Wg, Wu, x, y, routing))
+        none = Buffer(None, 0)
+        sg, su = map(_buf, shared) if shared is not None else (none, none)
+        bg, bu = map(_buf, biases) if biases is not None else (none, none)
+        self.ctx.call("zc_moe_gate_up_act_ex", quant_type, Wg.ptr, Wg.size, Wu.ptr, Wu.size, sg.ptr, sg.size,
+                      su.ptr, su.size, bg.ptr, bg.size, bu.ptr, bu.size, x.ptr, x.size, y.ptr, y.size,
+                      routing.ptr, routing.size, M, K, expert_stride, n_used, x_offset, y_offset, 1 if oai else 0)
+
+    # fused down + weighted accumulate with the shared expert's down matrix as one more slot and the per-expert
+    # down bias inside the weighted sum (forward.zig:6362-6389, 6501-6545, 6923-6927)
+    def dispatchMoeDownAccEx(self, quant_type, A, x, y, routing, M, K, expert_stride, n_used, x_expert_stride,
+                             shared=None, bias=None, x_offset=0, y_offset=0):
+        A, x, y, routing = map(_buf, (A, x, y, routing))
+        none = Buffer(None, 0)
+        sd = _buf(shared) if shared is not None else none
+        bd = _buf(bias) if bias is not None else none
+        self.ctx.call("zc_moe_down_acc_ex", quant_type, A.ptr, A.size, sd.ptr, sd.size, bd.ptr, bd.size, x.ptr,
+                      x.size, y.ptr, y.size, routing.ptr, routing.size, M, K, expert_stride, n_used,
+                      x_expert_stride, x_offset, y_offset)
+
+    # router DMMV (optionally behind the RMS norm) + softmax_topk (+ the expert-parallel filter) in one launch
+    # (forward.zig:6139-6190). routing = [k + shared_slot ids][k + shared_slot weights].
+    def dispatchMoeRouterTopk(self, hidden, router_weights, logits, routing, n_experts, K, k,
+                              rule=ROUTE_TOPK_THEN_SOFTMAX, bias=None, norm_weights=None, norm_out=None, eps=0.0,
+                              shared_slot=False, routing_local=None, e_lo=0, e_hi=0, local_shared=False):
+        h, w, lg, rt = map(_buf, (hidden, router_weights, logits, routing))
+        none = Buffer(None, 0)
+        b = _buf(bias) if bias is not None else none
+        nw = _buf(norm_weights) if norm_weights is not None else none
+        no = _buf(norm_out) if norm_out is not None else none
+        rl = _buf(routing_local) if routing_local is not None else none
+        self.ctx.call("zc_moe_router_topk", h.ptr, h.size, nw.ptr, nw.size, w.ptr, w.size, b.ptr, b.size, no.ptr,
+                      no.size, lg.ptr, lg.size, rt.ptr, rt.size, rl.ptr, rl.size, n_experts, K, k, rule,
+                      C.c_float(eps), 1 if shared_slot else 0, e_lo, e_hi if routing_local is not None else 0,
+                      1 if local_shared else 0)
+
     # fused down + weighted accumulate (forward.zig:6362-6389)
     def dispatchMoeFusedDownAcc(self, quant_type, A, x, y, routing, M, K, expert_stride, n_used, x_expert_stride,
                                 x_offset=0, y_offset=0):
@@ -395,6 +436,14 @@ class DmmvDispatch:
         no = _buf(norm_out) if norm_out is not None else Buffer(None, 0)
         self.ctx.call("zc_rms_norm_dmmv_f32", h.ptr, h.size, w.ptr, w.size, r.ptr, r.size, no.ptr, no.size,
                       lg.ptr, lg.size, M, K, C.c_float(eps))
+
+    # fused RMS norm + alpha / beta SSM projections (src/shaders/rms_norm_dmmv_q4k_alpha_beta.comp)
+    def dispatchRmsNormDmmvAlphaBeta(self, hidden, norm_weights, alpha_weights, beta_weights, norm_out, alpha_out,
+                                     beta_out, M, K, eps):
+        h, w, a, b, ao, bo = map(_buf, (hidden, norm_weights, alpha_weights, beta_weights, alpha_out, beta_out))
+        no = _buf(norm_out) if norm_out is not None else Buffer(None, 0)
+        self.ctx.call("zc_rms_norm_dmmv_alpha_beta", h.ptr, h.size, w.ptr, w.size, a.ptr, a.size, b.ptr, b.size,
+                      no.ptr, no.size, ao.ptr, ao.size, bo.ptr, bo.size, M, K, C.c_float(eps))
 
     # dispatchMoeWeightedAcc (src/shaders/moe_weighted_acc.comp:23-33)
     def dispatchMoeWeightedAcc(self, a, b, routing, n, n_used, src_stride):

@@ -132,13 +132,14 @@ class MoeDecode:
     routing_local: object = None   # expert parallelism: the routing with this rank's experts renumbered, the rest skipped
     e_lo: int = 0
     e_hi: int = 0
-    # gate + up + activation in one launch instead of the reference's two dispatches. Off: measured slower
-    # (config 4: 1.387 vs 1.349 ms per token, config 5: 1.329 vs 1.120 ms) although it saves a launch per layer.
-    fuse_act: bool = False
+    # fused: three launches per layer (router + selection; gate + up + biases + activation with the shared expert as
+    # one more slot; down + biases + weighted sum with the shared expert). Off: the reference's dispatch sequence,
+    # one launch per dispatch (seven per layer with a shared expert).
+    fused: bool = True
 
     @staticmethod
     def build(torch, dd: DmmvDispatch, shape: MoeShape, seed: int = 3, rank: int = 0, world: int = 1,
-              allreduce=None, parallel: str = "tp") -> "MoeDecode":
+              allreduce=None, parallel: str = "tp", fused: bool = True) -> "MoeDecode":
         s = shape
         if parallel not in ("tp", "ep"):
             raise ValueError("parallel must be 'tp' or 'ep'")
@@ -147,7 +148,7 @@ class MoeDecode:
         if parallel == "ep" and s.n_experts % world:
             raise ValueError(f"{s.n_experts} experts do not divide over {world} ranks")
         dev = f"cuda:{torch.cuda.current_device()}"
-        st = MoeDecode(shape=s, dd=dd, world=world, rank=rank, allreduce=allreduce, parallel=parallel)
+        st = MoeDecode(shape=s, dd=dd, world=world, rank=rank, allreduce=allreduce, parallel=parallel, fused=fused)
         ep = parallel == "ep"
         lo, hi = (0, s.ffn) if ep else ffn_split(s.ffn, synth.BLOCK[s.t_down][0], world)[rank]
         st.e_lo = rank * (s.n_experts // world) if ep else 0
@@ -197,11 +198,12 @@ class MoeDecode:
         st.x = torch.randn(s.hidden, device=dev, generator=gen)
         st.hidden = torch.zeros(s.hidden, **f32)
         st.logits = torch.zeros(s.n_experts, **f32)
-        st.routing = torch.zeros(2 * s.top_k, dtype=torch.int32, device=dev)
-        st.routing_local = torch.zeros(2 * s.top_k, dtype=torch.int32, device=dev) if ep else st.routing
+        slots = s.top_k + (1 if s.shared and fused else 0)   # fused: the shared expert rides as one more slot
+        st.routing = torch.zeros(2 * slots, dtype=torch.int32, device=dev)
+        st.routing_local = torch.zeros(2 * slots, dtype=torch.int32, device=dev) if ep else st.routing
         st.yg = torch.zeros(s.top_k * st.ffn_local, **f32)
         st.yu = torch.zeros(s.top_k * st.ffn_local, **f32)
-        st.act = torch.zeros(s.top_k * st.ffn_local, **f32)
+        st.act = torch.zeros(slots * st.ffn_local, **f32)
         st.sact = torch.zeros(st.ffn_local, **f32)
         if world > 1:
             st.partial = torch.zeros(s.hidden, **f32)
@@ -221,22 +223,20 @@ class MoeDecode:
         ep = self.parallel == "ep" and tp
         n_local = self.e_hi - self.e_lo
         r = self.routing_local
+        if self.fused:
+            return self._record_fused(es_gu, es_d)
         for w in self.layers:
             dd.recordDispatch(F32, w.router, self.x, self.logits, s.n_experts, s.hidden)
             dd.dispatchSoftmaxTopk(self.logits, self.routing, s.n_experts, s.top_k, rule=s.rule, bias=w.router_bias)
             if ep:
                 dd.dispatchMoeEpFilter(self.routing, r, s.top_k, self.e_lo, self.e_hi)
-            if self.fuse_act and not s.biases:
-                dd.dispatchMoeFusedGateUpAct(s.t_gate_up, w.wg, w.wu, self.x, self.act, r, f, s.hidden,
-                                             es_gu, s.top_k, 0, oai=s.oai)
+            dd.dispatchMoeFusedGateUp(s.t_gate_up, w.wg, w.wu, self.x, self.yg, self.yu, r, f,
+                                      s.hidden, es_gu, s.top_k, 0)
+            if s.biases:
+                dd.dispatchMoeBiasAct(self.yg, self.yu, w.bg, w.bu, r, self.act, f, s.top_k,
+                                      n_local, oai=s.oai)
             else:
-                dd.dispatchMoeFusedGateUp(s.t_gate_up, w.wg, w.wu, self.x, self.yg, self.yu, r, f,
-                                          s.hidden, es_gu, s.top_k, 0)
-                if s.biases:
-                    dd.dispatchMoeBiasAct(self.yg, self.yu, w.bg, w.bu, r, self.act, f, s.top_k,
-                                          n_local, oai=s.oai)
-                else:
-                    dd.dispatchSwiglu(self.yg, self.yu, self.act, s.top_k * f, oai=s.oai)
+                dd.dispatchSwiglu(self.yg, self.yu, self.act, s.top_k * f, oai=s.oai)
             acc = self.partial if tp else self.hidden
             if tp:
                 dd.ctx.memset(_as_buffer(self.partial), 0)
@@ -246,6 +246,35 @@ class MoeDecode:
             if s.shared and w.sg is not None:
                 dd.dispatchDmmvFusedGateUpSwiglu(s.t_gate_up, w.sg, w.su, self.x, self.sact, f, s.hidden)
                 dd.recordDispatch(s.t_down, w.sd, self.sact, acc, s.hidden, f, acc_mode=1)
+            if tp:
+                if self.allreduce is not None:
+                    self.allreduce(self.partial)
+                dd.dispatchMoeWeightedAcc(self.hidden, self.partial, self.one, s.hidden, 1, s.hidden)
+        return dd.ctx.launch_count - n0
+
+    def _record_fused(self, es_gu: int, es_d: int) -> int:
+        s, dd, f = self.shape, self.dd, self.ffn_local
+        n0 = dd.ctx.launch_count
+        tp = self.world > 1
+        ep = self.parallel == "ep" and tp
+        slots = s.top_k + (1 if s.shared else 0)
+        r = self.routing_local
+        for w in self.layers:
+            acc = self.partial if tp else self.hidden
+            if tp:
+                dd.ctx.memset(_as_buffer(self.partial), 0)
+            # router + selection (+ the rank's view of it under expert parallelism; the shared expert on rank 0)
+            dd.dispatchMoeRouterTopk(self.x, w.router, self.logits, self.routing, s.n_experts, s.hidden, s.top_k,
+                                     rule=s.rule, bias=w.router_bias, shared_slot=s.shared,
+                                     routing_local=r if ep else None, e_lo=self.e_lo, e_hi=self.e_hi,
+                                     local_shared=w.sg is not None)
+            shared_gu = (w.sg, w.su) if s.shared and w.sg is not None else None
+            dd.dispatchMoeGateUpActEx(s.t_gate_up, w.wg, w.wu, self.x, self.act, r, f, s.hidden, es_gu, slots,
+                                      shared=shared_gu, biases=(w.bg, w.bu) if s.biases else None, oai=s.oai)
+            # tensor parallelism: the down bias enters once (rank 0); expert parallelism: with the rank's own experts
+            bias_d = w.bd if s.biases and (ep or not tp or self.rank == 0) else None
+            dd.dispatchMoeDownAccEx(s.t_down, w.wd, self.act, acc, r, s.hidden, f, es_d, slots, f,
+                                    shared=w.sd if s.shared and w.sg is not None else None, bias=bias_d)
             if tp:
                 if self.allreduce is not None:
                     self.allreduce(self.partial)
