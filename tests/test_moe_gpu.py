@@ -548,8 +548,8 @@ def test_moe_decode_tensor_parallel_slices(gpu, cfg):
         n_part = part.record()
         ctx.submit_and_wait()
         total += part.hidden.cpu().numpy().astype(np.float64)
-        # hidden += partial (the zeroing is a memset, not a kernel); only rank 0 adds the down bias
-        assert n_part == n_full + shape.n_layers - (shape.n_layers if shape.biases and rank else 0)
+        # hidden += partial (the zeroing is a memset, not a kernel)
+        assert n_part == n_full + shape.n_layers
     assert rel_l2(total, want) <= 1e-5
 
 

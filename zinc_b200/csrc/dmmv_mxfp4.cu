@@ -177,7 +177,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
                                                                                    const uint8_t* a_end0,
                                                                                    const uint8_t* a_end1) {
     extern __shared__ uint8_t smem_raw[];
-    pdl_prologue(a);
+    pdl_begin(a);
     const uint32_t n_str = kSeg == 3 ? a.nseg : (uint32_t)NS;      // (matrix, activation range) streams per tile
     const uint32_t Kp_total = k_padded(a.K) * (kSeg == 3 ? a.nseg : 1u);
     const SmemX s = carve_x(smem_raw, Kp_total, kWarps);
@@ -201,17 +201,19 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
         if constexpr (kSeg == 2) {
             const uint32_t slot = T / a.tiles_per_expert, t0 = slot * a.tiles_per_expert * 16;
             const uint32_t e_raw = __ldg(a.routing + slot);
+            if (e_raw == kSkipExpert) return false;
             const uint8_t* m = expert_matrix(a.A[strm], a.A_sh[strm], e_raw, a.expert_stride, a.n_experts_max, a.status);
             end = m == a.A_sh[strm] ? a.A_sh_end[strm] : (strm == 0 ? a_end0 : a_end1);
             base = m - (uint64_t)t0 * row_bytes;
             Mb = t0 + a.M;
-            return e_raw != kSkipExpert;
+            return true;
         } else if constexpr (kSeg == 3) {
             const uint32_t e_raw = __ldg(a.routing + strm);
+            if (e_raw == kSkipExpert) return false;
             base = expert_matrix(a.A[0], a.A_sh[0], e_raw, a.expert_stride, a.n_experts_max, a.status);
             end = base == a.A_sh[0] ? a.A_sh_end[0] : a_end0;
             Mb = a.M;
-            return e_raw != kSkipExpert;
+            return true;
         } else {
             base = a.A[strm];
             end = strm == 0 ? a_end0 : a_end1;
@@ -233,9 +235,9 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
         pc_off[i] = r * row_bytes + c * 16;
     }
     auto request = [&](uint32_t slot) {
-        const uint8_t* base;
-        const uint8_t* a_end;  // first byte past this stream's weight buffer
-        uint32_t Mb;
+        const uint8_t* base = nullptr;
+        const uint8_t* a_end = nullptr;  // first byte past this stream's weight buffer
+        uint32_t Mb = 0;
         if (!locate(p_tile, p_strm, base, Mb, a_end)) {
             if (++p_kc == upt) {
                 p_kc = 0;
@@ -281,6 +283,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
             if (++p_strm == n_str) { p_strm = 0; ++p_tile; }
         }
     };
+    pdl_late(a);
     if (n) request(0);
     cp_async_commit();
     pdl_wait();
@@ -309,9 +312,9 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
         cp_async_wait<kDepthX - 1>();
         __syncwarp();
         // byte offsets of this lane's two rows inside their row slots
-        const uint8_t* base;
+        const uint8_t* base = a.A[0];  // (a slot without an expert: addresses formed below are never used)
         const uint8_t* unused_end;
-        uint32_t Mb;
+        uint32_t Mb = 1;
         const bool live = locate(tile, strm, base, Mb, unused_end);
         const uint32_t rA = min(tile * 16 + g, Mb - 1), rB = min(tile * 16 + g + 8, Mb - 1);
         const uint32_t oA = (uint32_t)(reinterpret_cast<uintptr_t>(base + (uint64_t)rA * row_bytes + (uint64_t)kc * kSegBytes) & 15u);

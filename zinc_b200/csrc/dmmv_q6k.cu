@@ -87,13 +87,21 @@ struct XRegs6 {
 // One warp per super-block; lane l handles the 8 consecutive elements 8l .. 8l+7.
 // K: length of the (concatenated) activation. bpe > 0 (MoE down projection): the activation is n_slots
 // vectors of bpe * 256 elements, x + s * x_stride, each scaled by the slot's routing weight wts[s].
+// Only the n_need super-blocks from b_first on (wrapping at the end of the row) are converted: a CTA whose
+// units cover less than a row does not need the rest.
+__device__ __forceinline__ uint32_t prep_block(uint32_t i, uint32_t b_first, uint32_t nblk) {
+    const uint32_t b = b_first + i;
+    return b >= nblk ? b - nblk : b;
+}
 template <int kWarps>
 __device__ __forceinline__ void load_x6(XRegs6& r, const float* __restrict__ x, uint32_t K, uint32_t bpe,
-                                        uint32_t x_stride, const uint32_t* __restrict__ wts, int warp, int lane) {
+                                        uint32_t x_stride, const uint32_t* __restrict__ wts, int warp, int lane,
+                                        uint32_t b_first, uint32_t n_need) {
 #pragma unroll
     for (int b = 0; b < kPrepBlocks; ++b) {
-        const uint32_t blk = warp + b * kWarps;
-        if (blk < (K >> 8)) {
+        const uint32_t bi = warp + b * kWarps;
+        if (bi < n_need) {
+            const uint32_t blk = prep_block(bi, b_first, K >> 8);
             const uint32_t slot = bpe ? blk / bpe : 0u, lb = bpe ? blk - slot * bpe : blk;
             const float* xp = x + (size_t)slot * x_stride + (size_t)lb * 256 + 8 * lane;
             float4 lo = __ldg(reinterpret_cast<const float4*>(xp)), hi = __ldg(reinterpret_cast<const float4*>(xp) + 1);
@@ -115,12 +123,14 @@ __device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, ui
 // Lane l's elements 8l .. 8l+7 lie in half h = l/16, quarter j = (l/4)%4, sub-block half u = (l/2)%2, and are
 // the k-slot groups t = 2(l%2) and t+1 of that sub-block half.
 template <int kWarps>
-__device__ __forceinline__ void prep_x6(const Smem6& s, const XRegs6& r, uint32_t K, int warp, int lane) {
+__device__ __forceinline__ void prep_x6(const Smem6& s, const XRegs6& r, uint32_t K, int warp, int lane,
+                                        uint32_t b_first, uint32_t n_need) {
     const uint32_t h = lane >> 4, j = (lane >> 2) & 3, u = (lane >> 1) & 1, t0 = 2 * (lane & 1);
 #pragma unroll
     for (int b = 0; b < kPrepBlocks; ++b) {
-        const uint32_t blk = warp + b * kWarps;
-        if (blk >= (K >> 8)) break;
+        const uint32_t bi = warp + b * kWarps;
+        if (bi >= n_need) break;
+        const uint32_t blk = prep_block(bi, b_first, K >> 8);
         const float4 lo = r.lo[b], hi = r.hi[b];
         const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
         float mx = 0.f;
@@ -251,7 +261,7 @@ template <int EPI, int kWarps, bool kRowsAligned, bool kMoe = false>
 __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel(const WarpArgs a,
                                                                                  const uint8_t* a_end) {
     extern __shared__ uint8_t smem_raw[];
-    pdl_prologue(a);
+    pdl_begin(a);
     const uint32_t bpe = a.K >> 8;                        // blocks per row of one matrix
     const uint32_t bpr = kMoe ? bpe * a.nseg : bpe;       // blocks per (concatenated) row = units per tile
     const Smem6 s = carve6(smem_raw, bpr * 256, kWarps);
@@ -324,20 +334,29 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
         }
         if (++p_blk == bpr) { p_blk = 0; ++p_tile; }
     };
+    // super-blocks of the activation this CTA's units touch
+    const uint32_t cu0 = (uint32_t)part_begin((uint64_t)blockIdx.x * kWarps, U, G);
+    const uint32_t cu1 = (uint32_t)part_begin((uint64_t)(blockIdx.x + 1) * kWarps, U, G);
+    const uint32_t x_first = cu1 - cu0 >= bpr ? 0u : cu0 % bpr, x_need = min(bpr, cu1 - cu0);
+    pdl_late(a);
+    XRegs6 xr;
+    if (a.late)
+        load_x6<kWarps>(xr, a.x, bpr * 256, kMoe ? bpe : 0u, kMoe ? a.x_slot_stride : 0u,
+                        kMoe ? a.routing + a.nseg : nullptr, warp, lane, x_first, x_need);
 #pragma unroll
     for (int i = 0; i < kDepth; ++i) {
         if ((uint32_t)i < n) request(i);
         cp_async_commit();
     }
     pdl_wait();
-    XRegs6 xr;
-    load_x6<kWarps>(xr, a.x, bpr * 256, kMoe ? bpe : 0u, kMoe ? a.x_slot_stride : 0u,
-                    kMoe ? a.routing + a.nseg : nullptr, warp, lane);
+    if (!a.late)
+        load_x6<kWarps>(xr, a.x, bpr * 256, kMoe ? bpe : 0u, kMoe ? a.x_slot_stride : 0u,
+                        kMoe ? a.routing + a.nseg : nullptr, warp, lane, x_first, x_need);
     if (a.consume.n) consume_pushed(a.consume, blockIdx.x, gridDim.x, tid, kWarps * 32);
 
     if (tid < kZeroBytes6 / 16) reinterpret_cast<uint4*>(s.zeros)[tid] = make_uint4(0u, 0u, 0u, 0u);
     if (tid < kWarps) s.sflags[tid] = 0u;
-    prep_x6<kWarps>(s, xr, bpr * 256, warp, lane);
+    prep_x6<kWarps>(s, xr, bpr * 256, warp, lane, x_first, x_need);
     __syncthreads();
 
     uint32_t tile = u0 / bpr, blk = u0 % bpr;
@@ -466,7 +485,7 @@ bool q6k_moe_down_acc_eligible(uint32_t type, const DmmvArgs& a) {
     const uint32_t bpr = (a.K >> 8) * a.n_used;
     if (smem_bytes6(bpr * 256, 16) > 227 * 1024 || bpr > (uint32_t)(kPrepBlocks * 8)) return false;
     const uint64_t U = (uint64_t)((a.M + 15) / 16) * bpr;
-    if ((uint64_t)a.M * bpr * 210u < 4 * kStreamMinBytes) return false;  // small expert sets: latency-bound either way
+    if ((uint64_t)a.M * bpr * 210u < kStreamMinBytes) return false;  // small expert sets: latency-bound either way
     return U >= 16 && U <= 0xFFFFFFFFull;
 }
 

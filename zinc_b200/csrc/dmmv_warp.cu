@@ -169,7 +169,7 @@ __device__ __forceinline__ int seg_of(const WarpArgs& a, uint32_t T) {
 template <int NS, int EPI, int kWarps, int kSeg = 0>
 __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel(const WarpArgs a) {
     extern __shared__ uint8_t smem_raw[];
-    pdl_prologue(a);
+    pdl_begin(a);
     const Smem s = carve(smem_raw, a.K, kWarps);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -251,15 +251,18 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
         }
     };
     // weights never depend on the previous kernel: fill the whole ring, then wait for that kernel, then
-    // fetch x
+    // fetch x. (Behind a kernel that may still be writing the routing buffer the wait comes first, and x is
+    // requested before the routing is read, so that the two round trips overlap.)
+    pdl_late(a);
+    XRegs xr;
+    if (a.late) load_x<kWarps>(xr, a.x, a.K, warp, lane);
 #pragma unroll
     for (int i = 0; i < kDepth; ++i) {
         if ((uint32_t)i < n) request(i);
         cp_async_commit();
     }
     pdl_wait();
-    XRegs xr;
-    load_x<kWarps>(xr, a.x, a.K, warp, lane);
+    if (!a.late) load_x<kWarps>(xr, a.x, a.K, warp, lane);
     if (a.consume.n) consume_pushed(a.consume, blockIdx.x, gridDim.x, tid, kWarps * 32);
 
     // ---- activation vector -> digit planes (all warps), zero region, flags ----

@@ -34,6 +34,15 @@ __device__ __forceinline__ ValIdx better(ValIdx a, ValIdx b) {
     return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
 }
 
+// Order-preserving map of (non-NaN) floats to unsigned integers and back; -0 and +0 share a key.
+__device__ __forceinline__ uint32_t float_key(float v) {
+    const uint32_t b = __float_as_uint(v + 0.0f);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float key_float(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
+
 constexpr int kTopkThreads = 256;
 
 __global__ void __launch_bounds__(kTopkThreads) softmax_topk_kernel(
@@ -138,7 +147,8 @@ __global__ void __launch_bounds__(kTopkThreads) softmax_topk_kernel(
 // L1 (they may have been written by other CTAs of the same launch).
 template <int VPL>
 __device__ __forceinline__ void softmax_topk_warp(const float* lg, const float* __restrict__ bias, uint32_t* o,
-                                                  uint32_t n, uint32_t k, uint32_t rule, uint32_t wofs, int lane) {
+                                                  uint32_t n, uint32_t k, uint32_t rule, uint32_t wofs, int lane,
+                                                  uint32_t* my_id = nullptr, uint32_t* my_w = nullptr) {
     const float floor_v = rule == 0u ? -1.0f : -INFINITY;
     const float gone = rule == 0u ? -2.0f : -INFINITY;  // never selected (again)
 
@@ -168,23 +178,59 @@ __device__ __forceinline__ void softmax_topk_warp(const float* lg, const float* 
         }
     }
     const float v0 = __shfl_sync(0xFFFFFFFFu, v[0], 0);  // expert 0, for the "nothing above the floor" case
+    // Up to 32 selections stay in registers (selection ki in lane ki) and reach memory once, at the end: a
+    // round trip through global memory per selection and per weight costs more than the whole selection.
+    const bool in_regs = k <= 32;
+    float sel_v = 0.f;
+    uint32_t sel_i = 0u;
     for (uint32_t ki = 0; ki < k; ++ki) {
         ValIdx best{floor_v, 0u};
 #pragma unroll
         for (int j = 0; j < VPL; ++j)
             if (v[j] > best.v) best = ValIdx{v[j], (uint32_t)(lane + 32 * j)};
-        for (int o2 = 16; o2 > 0; o2 >>= 1) {
-            ValIdx other{__shfl_xor_sync(0xFFFFFFFFu, best.v, o2), __shfl_xor_sync(0xFFFFFFFFu, best.i, o2)};
-            best = better(best, other);
-        }
+        // arg-max over the warp with two integer reductions: the largest value (as an order-preserving key, -0
+        // folded into +0), then the lowest index among the lanes that hold it
+        const uint32_t kmax = __reduce_max_sync(0xFFFFFFFFu, float_key(best.v));
+        const uint32_t imin = __reduce_min_sync(0xFFFFFFFFu, float_key(best.v) == kmax ? best.i : 0xFFFFFFFFu);
+        best = ValIdx{key_float(kmax), imin};
         if (!(best.v > floor_v)) best = ValIdx{rule == 0u ? floor_v : v0, 0u};
-        if (lane == 0) {
+        if (in_regs) {
+            if ((uint32_t)lane == ki) {
+                sel_v = best.v;
+                sel_i = best.i;
+            }
+        } else if (lane == 0) {
             o[ki] = best.i;
             o[wofs + ki] = __float_as_uint(best.v);
         }
 #pragma unroll
         for (int j = 0; j < VPL; ++j)
             if (best.i == (uint32_t)(lane + 32 * j)) v[j] = gone;
+    }
+    if (in_regs) {
+        // the sums run over the selections in order, as the sequential loops of the reference do
+        float w;
+        if (rule == 0u) {
+            float ws = 0.f;
+            for (uint32_t i = 0; i < k; ++i) ws += __shfl_sync(0xFFFFFFFFu, sel_v, (int)i);
+            w = ws > 0.f ? sel_v / ws : sel_v;
+        } else {
+            float mx = (uint32_t)lane < k ? sel_v : -INFINITY;
+            for (int o2 = 16; o2 > 0; o2 >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o2));
+            const float e = expf(sel_v - mx);
+            float sum = 0.f;
+            for (uint32_t i = 0; i < k; ++i) sum += __shfl_sync(0xFFFFFFFFu, e, (int)i);
+            w = sum > 0.f ? e / sum : e;
+        }
+        if ((uint32_t)lane < k) {
+            o[lane] = sel_i;
+            o[wofs + lane] = __float_as_uint(w);
+        }
+        if (my_id) {  // lane ki's selection, for a caller that goes on with it
+            *my_id = sel_i;
+            *my_w = __float_as_uint(w);
+        }
+        return;
     }
     if (lane == 0) {
         if (rule == 0u) {
@@ -475,22 +521,30 @@ __global__ void __launch_bounds__(kRouterThreads) moe_router_topk_kernel(const R
     if (tid == 0) *a.counter = 0u;
     const uint32_t n = a.n_experts, k = a.k, slots = k + a.shared;
     uint32_t* o = a.routing;
-    if (n <= 32) softmax_topk_warp<1>(a.logits, a.bias, o, n, k, a.rule, slots, (int)tid);
-    else if (n <= 256) softmax_topk_warp<8>(a.logits, a.bias, o, n, k, a.rule, slots, (int)tid);
-    else softmax_topk_warp<32>(a.logits, a.bias, o, n, k, a.rule, slots, (int)tid);
+    uint32_t id = 0u, wt = 0u;  // lane j's selection (k <= 32)
+    if (n <= 32) softmax_topk_warp<1>(a.logits, a.bias, o, n, k, a.rule, slots, (int)tid, &id, &wt);
+    else if (n <= 256) softmax_topk_warp<8>(a.logits, a.bias, o, n, k, a.rule, slots, (int)tid, &id, &wt);
+    else softmax_topk_warp<32>(a.logits, a.bias, o, n, k, a.rule, slots, (int)tid, &id, &wt);
     if (tid == 0 && a.shared) {
         o[k] = kSharedExpert;
         o[slots + k] = 0x3F800000u;
     }
-    __syncwarp();
     if (a.routing_local) {
+        if (k > 32) __syncwarp();  // the selections went through memory, written by lane 0
         for (uint32_t j = tid; j < slots; j += 32) {
-            const uint32_t id = o[j];
+            if (k > 32 && j < k) {
+                id = o[j];
+                wt = o[slots + j];
+            }
             uint32_t lid;
-            if (j >= k) lid = a.local_shared ? kSharedExpert : kSkipExpert;
-            else lid = (id >= a.e_lo && id < a.e_hi) ? id - a.e_lo : kSkipExpert;
+            if (j >= k) {
+                lid = a.local_shared ? kSharedExpert : kSkipExpert;
+                wt = 0x3F800000u;
+            } else {
+                lid = (id >= a.e_lo && id < a.e_hi) ? id - a.e_lo : kSkipExpert;
+            }
             a.routing_local[j] = lid;
-            a.routing_local[slots + j] = o[slots + j];
+            a.routing_local[slots + j] = wt;
         }
     }
 }

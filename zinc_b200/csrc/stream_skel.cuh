@@ -60,6 +60,17 @@ __device__ __forceinline__ void pdl_prologue(const WarpArgs& a) {
     if (a.late) pdl_wait();
     pdl_launch_dependents();
 }
+// The same in two steps, for kernels with set-up work that touches nothing another kernel writes: pdl_begin at
+// the start, pdl_late before the first read of the routing buffer (or of anything else a predecessor writes).
+__device__ __forceinline__ void pdl_begin(const WarpArgs& a) {
+    if (!a.late) pdl_launch_dependents();
+}
+__device__ __forceinline__ void pdl_late(const WarpArgs& a) {
+    if (a.late) {
+        pdl_wait();
+        pdl_launch_dependents();
+    }
+}
 
 // The activation a fused gate + up launch applies (src/shaders/swiglu.comp:25-33, swiglu_oai.comp:24-34).
 __device__ __forceinline__ float gate_up_act(uint32_t act, float gate, float up) {
@@ -164,8 +175,19 @@ struct RowOut {
 };
 __device__ __forceinline__ RowOut row_out(const WarpArgs& a) { return RowOut{a.y, a.y2, a.M, a.bias[0], a.bias[1]}; }
 
+// Does this launch add to y (and so needs its old value)?
+template <int EPI>
+__device__ __forceinline__ bool epi_accumulates(const WarpArgs& a) {
+    if constexpr (EPI == EPI_ACC || EPI == EPI_SIGMOID_ACC) return true;
+    if constexpr (EPI == EPI_PLAIN) return a.acc_mode != 0 && a.push.world == 0;
+    return false;
+}
+
+// yold: the value of y[row] before this launch, for the accumulating forms (read by the caller ahead of time,
+// so that the round trip overlaps the wait for the other workers' partial sums; one warp owns a row's result)
 template <int NS, int EPI>
-__device__ __forceinline__ void write_row(const WarpArgs& a, const RowOut& o, uint32_t row, const float (&v)[NS]) {
+__device__ __forceinline__ void write_row(const WarpArgs& a, const RowOut& o, uint32_t row, const float (&v)[NS],
+                                          float yold) {
     if (row >= o.M) return;
     if constexpr (EPI == EPI_GATE_UP) {
         o.y[row] = (v[0] / (1.0f + expf(-v[0]))) * v[1];
@@ -178,7 +200,7 @@ __device__ __forceinline__ void write_row(const WarpArgs& a, const RowOut& o, ui
                     b = fmaf(__uint_as_float(__ldg(a.routing + a.nseg + s)), __ldg(o.b0 + (size_t)e * a.M + row), b);
             }
         }
-        o.y[row] += v[0] + b;
+        o.y[row] = yold + (v[0] + b);
     } else if constexpr (EPI == EPI_PAIR) {  // two streams (MoE gate and up rows): both outputs, or their activation
         const float vg = o.b0 ? v[0] + __ldg(o.b0 + row) : v[0];
         const float vu = o.b1 ? v[NS - 1] + __ldg(o.b1 + row) : v[NS - 1];
@@ -189,13 +211,13 @@ __device__ __forceinline__ void write_row(const WarpArgs& a, const RowOut& o, ui
             o.y2[row] = vu;
         }
     } else if constexpr (EPI == EPI_SIGMOID_ACC) {
-        o.y[row] += (1.0f / (1.0f + expf(-__ldg(a.gate)))) * v[0];
+        o.y[row] = yold + (1.0f / (1.0f + expf(-__ldg(a.gate)))) * v[0];
     } else {
         if (a.push.world) {
             const uint2 pv = make_uint2(__float_as_uint(v[0]), 1u);
             for (uint32_t r = 0; r < a.push.world; ++r) a.push.peers[r][row] = pv;
         } else {
-            o.y[row] = a.acc_mode ? o.y[row] + v[0] : v[0];
+            o.y[row] = a.acc_mode ? yold + v[0] : v[0];
         }
     }
 }
@@ -235,6 +257,12 @@ __device__ __forceinline__ void finish_tile(const WarpArgs& a, const RowOut& o, 
         }
         return;
     }
+    // the old values of the rows this warp completes, requested before any waiting
+    float yold0 = 0.f, yold1 = 0.f;
+    if (t == 0 && epi_accumulates<EPI>(a)) {
+        if (T * 16 + g < o.M) yold0 = o.y[T * 16 + g];
+        if (T * 16 + g + 8 < o.M) yold1 = o.y[T * 16 + g + 8];
+    }
     if (last >= u1) {
         // first contributor of a tile that continues in later workers. They published early (the
         // tile is the first thing they work on). Lane t of each row adds parts t, t+4, ... (the order is
@@ -245,35 +273,57 @@ __device__ __forceinline__ void finish_tile(const WarpArgs& a, const RowOut& o, 
 #pragma unroll
         for (int i = 0; i < NS; ++i) w[i][0] = w[i][1] = 0.f;
         bool gave_up = false;
-        for (uint32_t c = me + 1 + t; c <= cl; c += 4) {
-            if (c / kWarps == blockIdx.x) {
-                volatile uint32_t* flag = sflags + (c % kWarps);
-                uint32_t spins = 0;
-                while (*flag == 0u) {
-                    if (++spins > a.spin_limit) { gave_up = true; break; }
+        // kGroup parts of this lane at a time: the first read of every value a group needs from other CTAs is
+        // issued before any of them is waited for (a tile with many parts would otherwise pay one round trip
+        // through L2 per part and row)
+        constexpr int kGroup = NS == 1 ? 6 : 2;
+        for (uint32_t c0 = me + 1 + t; c0 <= cl; c0 += 4 * kGroup) {
+            uint2 q[kGroup][NS][2];
+#pragma unroll
+            for (int p = 0; p < kGroup; ++p) {
+                const uint32_t c = c0 + 4 * p;
+                if (c <= cl && c / kWarps != blockIdx.x) {
+                    const uint2* src = a.gpartial + (size_t)c * 32;
+#pragma unroll
+                    for (int i = 0; i < NS; ++i) {
+                        q[p][i][0] = ld_volatile_u2(src + i * 16 + g);
+                        q[p][i][1] = ld_volatile_u2(src + i * 16 + g + 8);
+                    }
                 }
-                __threadfence_block();
-                const float* src = spartial + (c % kWarps) * 32;
+            }
 #pragma unroll
-                for (int i = 0; i < NS; ++i) {
-                    w[i][0] += *reinterpret_cast<const volatile float*>(src + i * 16 + g);
-                    w[i][1] += *reinterpret_cast<const volatile float*>(src + i * 16 + g + 8);
-                }
-            } else {
-                uint2* src = a.gpartial + (size_t)c * 32;
+            for (int p = 0; p < kGroup; ++p) {
+                const uint32_t c = c0 + 4 * p;
+                if (c > cl) break;
+                if (c / kWarps == blockIdx.x) {
+                    volatile uint32_t* flag = sflags + (c % kWarps);
+                    uint32_t spins = 0;
+                    while (*flag == 0u) {
+                        if (++spins > a.spin_limit) { gave_up = true; break; }
+                    }
+                    __threadfence_block();
+                    const float* src = spartial + (c % kWarps) * 32;
 #pragma unroll
-                for (int i = 0; i < NS; ++i) {
+                    for (int i = 0; i < NS; ++i) {
+                        w[i][0] += *reinterpret_cast<const volatile float*>(src + i * 16 + g);
+                        w[i][1] += *reinterpret_cast<const volatile float*>(src + i * 16 + g + 8);
+                    }
+                } else {
+                    uint2* src = a.gpartial + (size_t)c * 32;
 #pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        uint2* p = src + i * 16 + g + 8 * r;
-                        uint2 q = ld_volatile_u2(p);
-                        uint32_t spins = 0;
-                        while (q.y == 0u) {
-                            if (++spins > a.spin_limit) { gave_up = true; break; }
-                            q = ld_volatile_u2(p);
+                    for (int i = 0; i < NS; ++i) {
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            uint2* ptr = src + i * 16 + g + 8 * r;
+                            uint2 v2 = q[p][i][r];
+                            uint32_t spins = 0;
+                            while (v2.y == 0u) {
+                                if (++spins > a.spin_limit) { gave_up = true; break; }
+                                v2 = ld_volatile_u2(ptr);
+                            }
+                            w[i][r] += __uint_as_float(v2.x);
+                            *ptr = make_uint2(0u, 0u);  // empty again for the next launch
                         }
-                        w[i][r] += __uint_as_float(q.x);
-                        *p = make_uint2(0u, 0u);  // empty again for the next launch
                     }
                 }
             }
@@ -295,8 +345,8 @@ __device__ __forceinline__ void finish_tile(const WarpArgs& a, const RowOut& o, 
         float r0[NS], r1[NS];
 #pragma unroll
         for (int i = 0; i < NS; ++i) { r0[i] = v[i][0]; r1[i] = v[i][1]; }
-        write_row<NS, EPI>(a, o, T * 16 + g, r0);
-        write_row<NS, EPI>(a, o, T * 16 + g + 8, r1);
+        write_row<NS, EPI>(a, o, T * 16 + g, r0, yold0);
+        write_row<NS, EPI>(a, o, T * 16 + g + 8, r1, yold1);
     }
 }
 
