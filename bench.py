@@ -521,6 +521,90 @@ def moe_prefill_results(torch, zb, ctx, dd, stream, sampler, args, per_pair=True
     return out
 
 
+def moe_prefill_ep_results(torch, zb, ctx, dd, stream, sampler, args, rank, world, dist):
+    """N > 1: the Qwen3.5-like layer's routed experts over a prefill batch, expert-parallel: tokens and routing
+    replicated, each rank groups and computes only the pairs of its own experts, one NCCL all-reduce of the
+    [T][hidden] partial outputs per layer (a bandwidth-bound sum). Before the timed region a small layer cut from
+    the same seeded tensors on every rank is compared with the unsharded layer (`ep_check`)."""
+    from zinc_b200.moe_step import QWEN35_MOE, MoePrefill, MoeShape
+
+    peak, peak_burst, _, kind = measured_peaks()
+
+    def allreduce(t):
+        dist.all_reduce(t)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    # correctness of the partition and the sum, on a layer small enough to build unsharded everywhere
+    small = MoeShape(hidden=512, n_experts=max(16, 2 * world), top_k=4, ffn=512, t_gate_up=zb.Q4_K, t_down=zb.Q6_K,
+                     rule=zb.ROUTE_SOFTMAX_ALL_RENORM, shared=False, oai=False, n_layers=1)
+    full = MoePrefill.build(torch, dd, small, 96, seed=13)
+    dd.setWorkspace(full.workspace)
+    full.record()
+    ctx.submit_and_wait()
+    part = MoePrefill.build(torch, dd, small, 96, seed=13, rank=rank, world=world, allreduce=allreduce)
+    dd.setWorkspace(part.workspace)
+    dist.barrier()
+    part.record()
+    ctx.submit_and_wait()
+    err = float(((part.hidden.double() - full.hidden.double()).norm() / full.hidden.double().norm()).item())
+    tt = torch.tensor([err], device="cuda", dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    ep_check = float(tt.item())
+    dd.setWorkspace(None)
+    del full, part
+    torch.cuda.empty_cache()
+    if ep_check > 1e-4:
+        raise SystemExit(f"expert-parallel prefill check failed: rel_l2 {ep_check:.3e}")
+
+    S, T = QWEN35_MOE, args.tokens or 512
+    copies = 4
+    layers = [MoePrefill.build(torch, dd, S, T, seed=21 + c, rank=rank, world=world, allreduce=allreduce, local_only=True)
+              for c in range(copies)]
+    dd.setWorkspace(layers[0].workspace)   # same size for every copy
+    launches = 0
+
+    def run():
+        nonlocal launches
+        launches = sum(l.record() for l in layers) // copies
+
+    run()
+    stream.synchronize()
+    g = graph_of(torch, stream, run)
+    per, t0, t1 = timed_blocks(torch, stream, g.replay, 4, barrier=barrier, fixed_blocks=10)
+    ms = statistics.median(per) / copies
+    tt = torch.tensor([ms], device="cuda")
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    ms = float(tt.item())
+    ids = layers[0].routing.view(T, 2 * S.top_k)[:, :S.top_k]
+    touched = int(torch.unique(ids).numel())
+    sg, sd = zb.expert_slice_bytes(S.t_gate_up, S.ffn, S.hidden), zb.expert_slice_bytes(S.t_down, S.hidden, S.ffn)
+    wbytes = touched * (2 * sg + sd)
+    flops = 2.0 * T * S.top_k * 3 * S.ffn * S.hidden
+    tf = flops / (ms * 1e-3) / 1e12
+    out = []
+    if rank == 0:
+        out.append({
+            "metric": METRIC, "value": wbytes / (ms * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world, "steps": len(per) * copies,
+            "warmup": 4, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"qwen3.5-35b-a3b-like MoE layer (256 experts top-8, Q4_K gate/up, Q6_K down), prefill T={T}, "
+                                   "routed experts only", "path": "grouped",
+                       "parallelism": f"ep{world}: whole experts per rank, tokens and routing replicated, one NCCL "
+                                      "all-reduce of the [T][hidden] partial outputs per layer",
+                       "experts_touched": touched, "weight_bytes_touched": wbytes, "tokens_per_s": T / (ms * 1e-3),
+                       "tflops": tf, "l2": f"{copies} layers' expert weights in rotation"},
+            "ep_check": {"rel_l2": ep_check, "ranks": world},
+            "gpu_launches": launches * len(per) * copies, "gpu_launches_per_step": launches,
+            "roofline": hbm_roofline(wbytes, ms * 1e3, peak * world, kind, tensor_frac_of_burst=tf / (peak_burst * world)),
+            "clocks": sampler.window(t0, t1),
+        })
+    g.reset()
+    dd.setWorkspace(None)
+    return out
+
+
 # ---- tensor-parallel correctness check (N > 1) -------------------------------------------------------------
 def tp_check(torch, zb, dd, dist, rank, world, allreduce, allgather):
     """A small layer stack cut from the same seeded tensors on every rank, run through the exchange the
@@ -634,6 +718,8 @@ def main():
         if args.workload != "decode":
             if args.workload == "moe_decode":
                 res = moe_decode_results(torch, zb, ctx, dd, stream, sampler, args, rank, world, dist)
+            elif world > 1 and args.workload == "moe_prefill":
+                res = moe_prefill_ep_results(torch, zb, ctx, dd, stream, sampler, args, rank, world, dist)
             elif world > 1:
                 raise SystemExit(f"--workload {args.workload} runs on one GPU")
             elif args.workload == "prefill_gemm":

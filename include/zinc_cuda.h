@@ -298,6 +298,24 @@ int32_t zc_moe_fused_down_acc(zc_ctx* ctx, uint32_t type,
                               uint64_t expert_stride, uint32_t n_used, uint32_t x_expert_stride,
                               uint64_t x_offset, uint64_t y_offset);
 
+/* The O projection fed directly from split-K flash-attention partials: x[head * head_dim + d] =
+ * (sum_c w_c * partial[(head * n_i_chunks + c) * head_dim + d]) / L with w_c = exp(M_c - M) for chunks whose sum
+ * L_c is positive, M the maximum over the chunks' maxima and the head's sink (sinks[sink_offset + head]; NaN or a
+ * NULL sinks pointer: none), L = sum_c w_c L_c (+ exp(sink - M)); the pairs {M_c, L_c} follow the partials at
+ * float index n_heads * n_i_chunks * head_dim. Then y = A x (+ y when acc_mode != 0). K = n_heads * head_dim,
+ * n_i_chunks <= 16. Replaces the fused merge + O projection dispatch and its push block
+ * (src/compute/dmmv.zig:76-93 OprojMergePushConstants; src/compute/forward.zig:8360-8411;
+ * src/shaders/dmmv_q4k_o_proj_merge.comp:96-250). One launch for Q4_K matrices of at least 2 MB with at most four
+ * chunks and head_dim a multiple of 8 (the vector is merged while the matvec loads it); otherwise a small merge
+ * kernel runs first. Any DMMV type. */
+int32_t zc_dmmv_o_proj_merge(zc_ctx* ctx, uint32_t type,
+                             const void* A, uint64_t a_size,
+                             const void* partial, uint64_t partial_size,
+                             void* y, uint64_t y_size,
+                             const void* sinks, uint64_t sinks_size,
+                             uint32_t M, uint32_t K, uint64_t a_offset, uint64_t y_offset, uint32_t acc_mode,
+                             uint32_t n_heads, uint32_t n_i_chunks, uint32_t sink_offset, uint32_t head_dim);
+
 /* Routing id that selects the shared expert: a matrix outside the expert stack, passed beside it to the two
  * calls below. It lets the always-on expert of a layer (src/compute/forward.zig:6455-6545 runs it as separate
  * dispatches after the routed ones) ride in the routed launches as one more slot with weight 1. */
@@ -437,7 +455,9 @@ int32_t zc_moe_weighted_bias_acc(zc_ctx* ctx, void* a, uint64_t a_size, const vo
  * [expert_lo, expert_hi) renumbered from 0 and every other id replaced by 0xFFFFFFFF ("no expert in this slot on
  * this rank"); the k weights of a row are copied. Every MoE entry point reads no weights for such a slot and
  * contributes zeros for it, so a rank that holds a contiguous range of whole experts runs the same calls on its
- * own stack with the filtered routing, and the ranks' partial hidden vectors are then summed. Rows of 2k words. */
+ * own stack with the filtered routing, and the ranks' partial hidden vectors are then summed. Rows of
+ * routing_stride / out_stride words; with k <= out_stride < 2k only the k ids of a row are written (the flattened
+ * id table zc_moe_dmmv_batched takes). zc_moe_route_scatter leaves out the slots marked 0xFFFFFFFF. */
 int32_t zc_moe_ep_filter(zc_ctx* ctx, const void* routing, uint64_t routing_size, void* out, uint64_t out_size,
                          uint32_t k, uint32_t n_tokens, uint32_t routing_stride, uint32_t out_stride,
                          uint32_t expert_lo, uint32_t expert_hi);

@@ -59,6 +59,7 @@ def lib() -> C.CDLL:
         L.zo_topk_softmax_weight.argtypes = [f32p, C.c_uint32, C.c_uint32, u32p, f32p]
         L.zo_rms_norm_dmmv_f32.argtypes = [f32p, f32p, f32p, f32p, C.POINTER(C.c_double), C.c_uint32, C.c_uint32,
                                            C.c_float]
+        L.zo_attn_merge.argtypes = [f32p, f32p, f32p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]
         L.zo_swiglu.argtypes = [f32p, f32p, f32p, C.c_uint32]
         L.zo_swiglu_oai.argtypes = [f32p, f32p, f32p, C.c_uint32]
         L.zo_moe_weighted_acc.argtypes = [f32p, f32p, u32p, C.c_uint32, C.c_uint32, C.c_uint32]
@@ -196,6 +197,17 @@ def rms_norm_dmmv_f32(x, norm_w, W, M: int, K: int, eps: float):
     lib().zo_rms_norm_dmmv_f32(_p(x, C.c_float), _p(w, C.c_float), _p(Wm, C.c_float), _p(xn, C.c_float),
                                _p(logits, C.c_double), M, K, eps)
     return xn, logits
+
+
+def attn_merge(partial, sinks, n_heads: int, n_chunks: int, head_dim: int, sink_offset: int = 0) -> np.ndarray:
+    """Attention output [n_heads * head_dim] merged from split-K partials + their LSE region (sinks: f32 array,
+    NaN = none, or None)."""
+    p = np.ascontiguousarray(partial, dtype=np.float32)
+    out = np.empty(n_heads * head_dim, dtype=np.float32)
+    s = None if sinks is None else np.ascontiguousarray(sinks, dtype=np.float32)
+    lib().zo_attn_merge(_p(p, C.c_float), None if s is None else _p(s, C.c_float), _p(out, C.c_float), n_heads,
+                        n_chunks, head_dim, sink_offset)
+    return out
 
 
 def swiglu(gate, up, oai: bool = False) -> np.ndarray:

@@ -660,6 +660,37 @@ void zo_rms_norm_dmmv_f32(const float* x, const float* w, const float* W, float*
     }
 }
 
+// Merge of split-K flash-attention partials into the attention output vector,
+// src/shaders/dmmv_q4k_o_proj_merge.comp:104-148: per head M_full = max over the chunks' maxima (and the sink, a
+// NaN sink meaning none), w_c = exp(M_c - M_full) for chunks with L_c > 0, L_full = sum_c w_c L_c (+ the sink's
+// exp), out[head*hd + d] = (sum_c fma(w_c, partial[(head*nc + c)*hd + d], acc)) / L_full (0 when L_full is 0).
+// The LSE region {M_c, L_c} follows the partials at float index n_heads * nc * hd.
+void zo_attn_merge(const float* partial, const float* sinks, float* out, uint32_t n_heads, uint32_t nc, uint32_t hd,
+                   uint32_t sink_offset) {
+    const size_t lse_base = (size_t)n_heads * nc * hd;
+    for (uint32_t head = 0; head < n_heads; ++head) {
+        const float* lse = partial + lse_base + (size_t)head * nc * 2;
+        float Mg = lse[0];
+        for (uint32_t c = 1; c < nc; ++c) Mg = std::max(Mg, lse[2 * c]);
+        const float sink = sinks ? sinks[sink_offset + head] : NAN;
+        const bool has_sink = !std::isnan(sink);
+        const float Mf = has_sink ? std::max(Mg, sink) : Mg;
+        std::vector<float> w(nc);
+        float Lf = 0.0f;
+        for (uint32_t c = 0; c < nc; ++c) {
+            w[c] = lse[2 * c + 1] > 0.0f ? std::exp(lse[2 * c] - Mf) : 0.0f;
+            Lf += w[c] * lse[2 * c + 1];
+        }
+        if (has_sink) Lf += std::exp(sink - Mf);
+        const float inv = Lf > 0.0f ? 1.0f / Lf : 0.0f;
+        for (uint32_t d = 0; d < hd; ++d) {
+            float acc = 0.0f;
+            for (uint32_t c = 0; c < nc; ++c) acc = std::fmaf(w[c], partial[((size_t)head * nc + c) * hd + d], acc);
+            out[(size_t)head * hd + d] = acc * inv;
+        }
+    }
+}
+
 // src/shaders/swiglu.comp:25-33
 void zo_swiglu(const float* gate, const float* up, float* out, uint32_t n) {
     for (uint32_t i = 0; i < n; ++i) {

@@ -26,6 +26,13 @@ def test_header_symbols_exported():
     assert set(names) == set(_lib.EXPORTS)
 
 
+def test_integration_binding_lists_every_export():
+    """The reference-side binding written out in INTEGRATION.md has one extern per exported function."""
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    bound = set(re.findall(r'pub extern "zinc_b200" fn (zc_[a-z0-9_]+)\(', text))
+    assert bound == set(declared_symbols())
+
+
 def test_layout_helpers_match_reference_constants():
     # src/model/gguf.zig:545-576, src/compute/forward.zig:11409-11423, 11737-11756
     assert (zb.block_size(zb.Q4_K), zb.bytes_per_block(zb.Q4_K)) == (256, 144)

@@ -372,3 +372,45 @@ def test_streaming_mxfp4(gpu, oracle, M, K):
     dd.recordDispatch(zb.MXFP4, wpad, xd, y2, M, K, a_offset=off)
     ctx.submit_and_wait()
     assert rel_l2(y2[:M].cpu().numpy(), want) <= TOL
+
+
+@pytest.mark.parametrize("t,M,K,n_heads,nc,sink", [
+    (zb.Q4_K, 4096, 4096, 32, 4, "some"),    # streaming kernel: merged while the activation is loaded
+    (zb.Q4_K, 4096, 4096, 32, 1, None),
+    (zb.Q4_K, 2048, 2048, 16, 3, "all"),
+    (zb.Q4_K, 200, 1024, 8, 4, "some"),      # small matrix: merge kernel, then one warp per row
+    (zb.Q6_K, 512, 1024, 4, 6, "none"),      # another type, more chunks than the fused path takes
+])
+def test_o_proj_merge(gpu, oracle, t, M, K, n_heads, nc, sink):
+    """Split-K flash-attention merge fused with the O projection (src/shaders/dmmv_q4k_o_proj_merge.comp): chunks
+    with zero weight, heads with and without a sink (NaN = none), accumulate into the hidden vector."""
+    torch, ctx, dd = gpu
+    hd = K // n_heads
+    g = synth.rng(330, M + nc)
+    w = synth.quant_matrix(g, t, M, K)
+    part = synth.activations(g, n_heads * nc * hd)
+    mx = (synth.activations(g, n_heads, nc) * np.float32(3.0)).astype(np.float32)
+    ls = (g.random((n_heads, nc)).astype(np.float32) * np.float32(50.0) + np.float32(0.5))
+    if nc > 1:
+        ls[1, nc - 1] = 0.0   # a chunk that saw no keys
+    lse = np.stack([mx, ls], axis=-1).reshape(-1)
+    buf = np.concatenate([part, lse]).astype(np.float32)
+    sinks = None
+    if sink is not None:
+        sinks = np.full(n_heads + 5, np.nan, np.float32)
+        if sink in ("some", "all"):
+            sinks[5:] = synth.activations(g, n_heads) * np.float32(2.0)
+        if sink == "some":
+            sinks[5 + 1::2] = np.nan
+    x = oracle.attn_merge(buf, sinks, n_heads, nc, hd, 5 if sinks is not None else 0)
+    h0 = synth.activations(g, M)
+    y = out_with_canary(torch, M)
+    y[:M] = dev(torch, h0)
+    dd.dispatchDmmvOprojMerge(t, dev(torch, w), dev(torch, buf), None if sinks is None else dev(torch, sinks), y, M, K,
+                              n_heads, nc, 5 if sinks is not None else 0, hd)
+    ctx.submit_and_wait()
+    want = oracle.dmmv_f64(w, t, M, K, x)
+    assert canary_intact(y, M)
+    assert rel_l2(y[:M].cpu().numpy() - h0, want) <= 1e-4
+    with pytest.raises(zb.InvalidArgument):
+        dd.dispatchDmmvOprojMerge(t, dev(torch, w), dev(torch, buf), None, y, M, K, n_heads + 1, nc, 0, hd)

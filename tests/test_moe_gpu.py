@@ -787,3 +787,37 @@ def test_moe_decode_fused_equals_dispatch_sequence(gpu):
         assert nb == 3 * shape.n_layers and na > nb
         ha, hb = a.hidden.double(), b.hidden.double()
         assert float(((ha - hb).norm() / ha.norm()).item()) <= 1e-5
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_moe_prefill_expert_parallel_ranks(gpu, world):
+    """The per-rank parts of an expert-parallel MoE prefill layer (whole experts per rank, routing filtered to
+    them, absent pairs neither grouped nor summed), run one after the other on this GPU, add up to the layer on
+    one rank; and zc_moe_ep_filter's ids-only rows against numpy."""
+    torch, ctx, dd = gpu
+    from zinc_b200.moe_step import MoePrefill, MoeShape
+    shape = MoeShape(hidden=512, n_experts=16, top_k=4, ffn=512, t_gate_up=zb.Q4_K, t_down=zb.Q6_K,
+                     rule=zb.ROUTE_SOFTMAX_ALL_RENORM, shared=False, oai=False, n_layers=1)
+    T = 96
+    full = MoePrefill.build(torch, dd, shape, T, seed=13)
+    dd.setWorkspace(full.workspace)
+    try:
+        full.record()
+        ctx.submit_and_wait()
+        want = full.hidden.double().cpu()
+        total = torch.zeros_like(want)
+        ids = full.routing.view(T, 2 * shape.top_k)[:, :shape.top_k].cpu().numpy().view(np.uint32)
+        for rank in range(world):
+            part = MoePrefill.build(torch, dd, shape, T, seed=13, rank=rank, world=world)
+            assert torch.equal(part.routing, full.routing) and torch.equal(part.X, full.X)
+            dd.setWorkspace(part.workspace)
+            part.record()
+            ctx.submit_and_wait()
+            total += part.hidden.double().cpu()
+            lo, hi = part.e_lo, part.e_hi
+            want_ids = np.where((ids >= lo) & (ids < hi), ids - lo, zb.SKIP_EXPERT).astype(np.uint32)
+            assert np.array_equal(part.ids_local.cpu().numpy().view(np.uint32).reshape(T, -1), want_ids)
+            assert np.array_equal(part.routing_local.view(T, -1)[:, :shape.top_k].cpu().numpy().view(np.uint32), want_ids)
+    finally:
+        dd.setWorkspace(None)
+    assert float(((total - want).norm() / want.norm()).item()) <= 1e-5

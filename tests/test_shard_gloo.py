@@ -109,6 +109,35 @@ def _worker(rank: int, world: int, port: int, q):
         dist.all_reduce(te)
         res["moe_ep"] = float(np.abs(te.numpy() - full).max() / np.abs(full).max())
 
+        # the same over a prefill batch: tokens and routing replicated, a rank computes the pairs of its own experts
+        # only, the [T][H] partial outputs are summed
+        T = 5
+        ids_t = np.stack([g.choice(E, size=k, replace=False) for _ in range(T)]).astype(np.uint32)
+        wts_t = g.random((T, k))
+        X_t = synth.activations(g, T, H)
+
+        def pair_out(wg_, wu_, wd_, e, xrow):
+            one = np.array([e], np.uint32)
+            gate = zo.moe_dmmv_f64(wg_, zb.MXFP4, F, H, sg, one, H, xrow[None]).astype(np.float32)
+            up = zo.moe_dmmv_f64(wu_, zb.MXFP4, F, H, sg, one, H, xrow[None]).astype(np.float32)
+            act = zo.swiglu(gate.reshape(-1), up.reshape(-1)).reshape(1, F)
+            return zo.moe_dmmv_f64(wd_, zb.MXFP4, H, F, sdn, one, F, act)[0]
+
+        full_t = np.zeros((T, H))
+        for t in range(T):
+            for s in range(k):
+                full_t[t] += wts_t[t, s] * pair_out(wg_e, wu_e, wd_e, ids_t[t, s], X_t[t])
+        local = moe_step.ep_local_ids(ids_t, e_lo, e_hi)
+        wg_p, wu_p, wd_p = wg_e[e_lo * sg:e_hi * sg], wu_e[e_lo * sg:e_hi * sg], wd_e[e_lo * sdn:e_hi * sdn]
+        mine_t = np.zeros((T, H))
+        for t in range(T):
+            for s in range(k):
+                if local[t, s] != 0xFFFFFFFF:
+                    mine_t[t] += wts_t[t, s] * pair_out(wg_p, wu_p, wd_p, local[t, s], X_t[t])
+        tp_ = torch.from_numpy(mine_t)
+        dist.all_reduce(tp_)
+        res["moe_ep_prefill"] = float(np.abs(tp_.numpy() - full_t).max() / np.abs(full_t).max())
+
         # refusals
         for fn, args in ((shard.row_range, (5, rank, world)), (shard.k_range, (zb.Q6_K, 768, rank, world))):
             try:
@@ -140,6 +169,7 @@ def test_two_rank_tensor_parallel_ffn():
         assert out[r]["ffn_pair"] <= 1e-12
         assert out[r]["moe_tp"] <= 1e-6   # f32 SwiGLU outputs feed the down projection
         assert out[r]["moe_ep"] <= 1e-12  # whole experts: the same numbers, summed in another order
+        assert out[r]["moe_ep_prefill"] <= 1e-12
         assert out[r]["refusal"] is True
 
 

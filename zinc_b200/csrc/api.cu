@@ -28,6 +28,7 @@ struct zc_ctx {
     uint2* scratch_partial = nullptr;  // split-K partial sums of the streaming matvecs, tagged (zero between launches)
     uint32_t* router_counter = nullptr;  // arrival counter of the fused router + selection kernel (zero between launches)
     uint64_t router_mark = 0;            // value of `launches` right after that kernel's last launch (0: never)
+    float* merge_scratch = nullptr;      // kMergeScratchFloats f32: a merged attention vector on its way to a matvec
     int sm_count = 0;
     // tensor-parallel peer exchange (zc_comm_*)
     zc::CommArgs comm;
@@ -46,6 +47,8 @@ struct zc_ctx {
 namespace {
 
 using namespace zc;
+
+constexpr uint32_t kMergeScratchFloats = 16384;
 
 int32_t fail(zc_ctx* ctx, int32_t code, const char* fmt, ...) {
     if (ctx) {
@@ -228,7 +231,8 @@ int32_t zc_init(int32_t device, zc_ctx** out_ctx) {
     }
     memset(ctx->status_host, 0, 256);
     ctx->sm_count = prop.multiProcessorCount;
-    if (cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_partial), kStreamPartialBytes + 256) != cudaSuccess ||
+    if (cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_partial),
+                   kStreamPartialBytes + 256 + kMergeScratchFloats * sizeof(float)) != cudaSuccess ||
         cudaMemset(ctx->scratch_partial, 0, kStreamPartialBytes + 256) != cudaSuccess) {
         if (ctx->scratch_partial) cudaFree(ctx->scratch_partial);
         cudaFreeHost(ctx->status_host);
@@ -237,6 +241,7 @@ int32_t zc_init(int32_t device, zc_ctx** out_ctx) {
         return ZC_ERR_OOM;
     }
     ctx->router_counter = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(ctx->scratch_partial) + kStreamPartialBytes);
+    ctx->merge_scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ctx->scratch_partial) + kStreamPartialBytes + 256);
     *out_ctx = ctx;
     return ZC_OK;
 }
@@ -533,6 +538,54 @@ int32_t zc_dmmv(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, cons
     else
         e = launch_dmmv(type, MODE_PLAIN, a, ctx->stream, &ctx->launches);
     return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, "zc_dmmv");
+}
+
+int32_t zc_dmmv_o_proj_merge(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* partial,
+                             uint64_t partial_size, void* y, uint64_t y_size, const void* sinks, uint64_t sinks_size,
+                             uint32_t M, uint32_t K, uint64_t a_offset, uint64_t y_offset, uint32_t acc_mode,
+                             uint32_t n_heads, uint32_t n_i_chunks, uint32_t sink_offset, uint32_t head_dim) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_dmmv_o_proj_merge";
+    if (!dmmv_type_ok(type)) return fail(ctx, ZC_ERR_UNSUPPORTED_TYPE, "%s: unsupported quant type %u", fn, type);
+    if (n_heads == 0 || head_dim == 0 || n_i_chunks == 0 || n_i_chunks > 16 || (uint64_t)n_heads * head_dim != K)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: need K = n_heads * head_dim and 1 <= n_i_chunks <= 16", fn);
+    if (K > kMergeScratchFloats && !(type == T_Q4_K))
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: K beyond %u", fn, kMergeScratchFloats);
+    ZC_TRY(check_mat(ctx, fn, type, A, a_size, a_offset, (uint64_t)M * row_bytes_of(type, K), M, K));
+    const uint64_t pfloats = (uint64_t)n_heads * n_i_chunks * head_dim + (uint64_t)n_heads * n_i_chunks * 2;
+    ZC_TRY(check_vec(ctx, fn, "partial", partial, partial_size, 0, pfloats * 4, 8));
+    ZC_TRY(check_vec(ctx, fn, "y", y, y_size, y_offset, (uint64_t)M * 4, 4));
+    if (sinks) ZC_TRY(check_vec(ctx, fn, "sinks", sinks, sinks_size, 0, ((uint64_t)sink_offset + n_heads) * 4, 4));
+    DmmvArgs a;
+    a.A = u8(A, a_offset);
+    a.y = f32m(y, y_offset);
+    a.M = M;
+    a.K = K;
+    a.acc_mode = acc_mode;
+    a.a_end = u8(A, a_size);
+    a.merge.partial = f32p(partial, 0);
+    a.merge.sinks = sinks ? f32p(sinks, 0) : nullptr;
+    a.merge.n_heads = n_heads;
+    a.merge.n_chunks = n_i_chunks;
+    a.merge.head_dim = head_dim;
+    a.merge.sink_offset = sink_offset;
+    attach_scratch(ctx, a);
+    const uint64_t wbytes = (uint64_t)M * row_bytes_of(type, K);
+    cudaError_t e;
+    if (wbytes >= kStreamMinBytes && warp_dmmv_eligible(type, MODE_PLAIN, a)) {
+        // the streaming kernel merges the partials while it loads its activation
+        e = launch_warp_dmmv(type, MODE_PLAIN, a, ctx->stream, &ctx->launches);
+    } else {
+        if (K > kMergeScratchFloats) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: K beyond %u", fn, kMergeScratchFloats);
+        e = launch_attn_merge(a.merge, ctx->merge_scratch, ctx->stream, &ctx->launches);
+        if (e == cudaSuccess) {
+            a.merge = MergeArgs();
+            a.x = ctx->merge_scratch;
+            a.late = false;
+            e = launch_dmmv(type, MODE_PLAIN, a, ctx->stream, &ctx->launches);
+        }
+    }
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 
 int32_t zc_dmmv_push(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* x, uint64_t x_size,
@@ -1221,10 +1274,13 @@ int32_t zc_moe_ep_filter(zc_ctx* ctx, const void* routing, uint64_t routing_size
                          uint32_t expert_lo, uint32_t expert_hi) {
     ZC_ENTER(ctx);
     const char* fn = "zc_moe_ep_filter";
-    if (k == 0 || n_tokens == 0 || routing_stride < 2 * k || out_stride < 2 * k || expert_lo >= expert_hi)
-        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: zero count, stride < 2k or empty expert range", fn);
-    ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0, ((uint64_t)(n_tokens - 1) * routing_stride + 2 * k) * 4, 4));
-    ZC_TRY(check_vec(ctx, fn, "out", out, out_size, 0, ((uint64_t)(n_tokens - 1) * out_stride + 2 * k) * 4, 4));
+    if (k == 0 || n_tokens == 0 || routing_stride < k || out_stride < k || expert_lo >= expert_hi)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: zero count, stride < k or empty expert range", fn);
+    const uint32_t per = out_stride < 2 * k ? k : 2 * k;  // ids alone, or ids and weights
+    if (routing_stride < per)
+        return fail(ctx, ZC_ERR_INVALID_ARG, "%s: routing rows hold no weights to copy", fn);
+    ZC_TRY(check_vec(ctx, fn, "routing", routing, routing_size, 0, ((uint64_t)(n_tokens - 1) * routing_stride + per) * 4, 4));
+    ZC_TRY(check_vec(ctx, fn, "out", out, out_size, 0, ((uint64_t)(n_tokens - 1) * out_stride + per) * 4, 4));
     const cudaError_t e = launch_moe_ep_filter(static_cast<const uint32_t*>(routing), static_cast<uint32_t*>(out), k,
                                                n_tokens, routing_stride, out_stride, expert_lo, expert_hi, ctx->stream,
                                                &ctx->launches);

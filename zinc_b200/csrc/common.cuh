@@ -69,6 +69,35 @@ __device__ __forceinline__ uint32_t checked_expert(uint32_t e, uint32_t n_max, u
     return 0u;
 }
 
+// Merge weights of one head's split-K attention chunks (src/shaders/dmmv_q4k_o_proj_merge.comp:104-134):
+// w[c] = exp(M_c - M_full) for chunks with L_c > 0, and 1 / L_full (0 when nothing contributed).
+template <int kMaxChunks>
+__device__ __forceinline__ float attn_merge_weights(const float* __restrict__ lse, const float* __restrict__ sinks,
+                                                    uint32_t sink_index, uint32_t nc, float (&w)[kMaxChunks]) {
+    float Mc[kMaxChunks], Lc[kMaxChunks];
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) {
+        const float2 ml = (uint32_t)c < nc ? __ldg(reinterpret_cast<const float2*>(lse) + c) : make_float2(-INFINITY, 0.f);
+        Mc[c] = ml.x;
+        Lc[c] = ml.y;
+    }
+    float Mg = Mc[0];
+#pragma unroll
+    for (int c = 1; c < kMaxChunks; ++c)
+        if ((uint32_t)c < nc) Mg = fmaxf(Mg, Mc[c]);
+    const float sink = sinks ? __ldg(sinks + sink_index) : __int_as_float(0x7FC00000);
+    const bool has_sink = !isnan(sink);
+    const float Mf = has_sink ? fmaxf(Mg, sink) : Mg;
+    float Lf = 0.f;
+#pragma unroll
+    for (int c = 0; c < kMaxChunks; ++c) {
+        w[c] = ((uint32_t)c < nc && Lc[c] > 0.f) ? expf(Mc[c] - Mf) : 0.f;
+        Lf += w[c] * Lc[c];
+    }
+    if (has_sink) Lf += expf(sink - Mf);
+    return Lf > 0.f ? 1.0f / Lf : 0.f;
+}
+
 // Matrix of the expert a (non-skipped) routing slot names.
 __device__ __forceinline__ const uint8_t* expert_matrix(const uint8_t* stack, const uint8_t* shared, uint32_t e_raw,
                                                         uint64_t stride, uint32_t n_max, uint32_t* status) {

@@ -112,6 +112,46 @@ __device__ __forceinline__ void load_x(XRegs& r, const float* __restrict__ x, ui
     }
 }
 
+// The same eight elements per lane, merged from split-K attention partials (up to four chunks; head_dim a
+// multiple of 8, so a lane's elements share a head).
+constexpr int kMergeChunks = 4;
+template <int kWarps>
+__device__ __forceinline__ void load_x_merge(XRegs& r, const MergeArgs& m, uint32_t K, int warp, int lane) {
+#pragma unroll
+    for (int i = 0; i < kPrepBlocks; ++i) {
+        const uint32_t blk = warp + i * kWarps;
+        if (blk < (K >> 8)) {
+            const uint32_t k0 = blk * 256 + 8 * lane, head = k0 / m.head_dim, d = k0 - head * m.head_dim;
+            float4 pl[kMergeChunks], ph[kMergeChunks];
+#pragma unroll
+            for (int c = 0; c < kMergeChunks; ++c) {
+                if ((uint32_t)c < m.n_chunks) {
+                    const float4* p = reinterpret_cast<const float4*>(
+                        m.partial + ((size_t)head * m.n_chunks + c) * m.head_dim + d);
+                    pl[c] = __ldg(p);
+                    ph[c] = __ldg(p + 1);
+                } else {
+                    pl[c] = ph[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+            float w[kMergeChunks];
+            const float inv = attn_merge_weights<kMergeChunks>(
+                m.partial + (size_t)m.n_heads * m.n_chunks * m.head_dim + (size_t)head * m.n_chunks * 2, m.sinks,
+                m.sink_offset + head, m.n_chunks, w);
+            float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+#pragma unroll
+            for (int c = 0; c < kMergeChunks; ++c) {
+                lo = make_float4(fmaf(w[c], pl[c].x, lo.x), fmaf(w[c], pl[c].y, lo.y), fmaf(w[c], pl[c].z, lo.z),
+                                 fmaf(w[c], pl[c].w, lo.w));
+                hi = make_float4(fmaf(w[c], ph[c].x, hi.x), fmaf(w[c], ph[c].y, hi.y), fmaf(w[c], ph[c].z, hi.z),
+                                 fmaf(w[c], ph[c].w, hi.w));
+            }
+            r.lo[i] = make_float4(lo.x * inv, lo.y * inv, lo.z * inv, lo.w * inv);
+            r.hi[i] = make_float4(hi.x * inv, hi.y * inv, hi.z * inv, hi.w * inv);
+        }
+    }
+}
+
 // Four values' low bytes as one word.
 __device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
@@ -255,14 +295,23 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
     // requested before the routing is read, so that the two round trips overlap.)
     pdl_late(a);
     XRegs xr;
-    if (a.late) load_x<kWarps>(xr, a.x, a.K, warp, lane);
+    auto fetch_x = [&]() {
+        if constexpr (kSeg == 0 && NS == 1 && EPI == EPI_PLAIN) {
+            if (a.merge.partial) {
+                load_x_merge<kWarps>(xr, a.merge, a.K, warp, lane);
+                return;
+            }
+        }
+        load_x<kWarps>(xr, a.x, a.K, warp, lane);
+    };
+    if (a.late) fetch_x();
 #pragma unroll
     for (int i = 0; i < kDepth; ++i) {
         if ((uint32_t)i < n) request(i);
         cp_async_commit();
     }
     pdl_wait();
-    if (!a.late) load_x<kWarps>(xr, a.x, a.K, warp, lane);
+    if (!a.late) fetch_x();
     if (a.consume.n) consume_pushed(a.consume, blockIdx.x, gridDim.x, tid, kWarps * 32);
 
     // ---- activation vector -> digit planes (all warps), zero region, flags ----
@@ -426,6 +475,9 @@ cudaError_t launch_cfg(const WarpArgs& a, cudaStream_t st, int sm_count) {
 
 bool warp_dmmv_eligible(uint32_t type, int mode, const DmmvArgs& a) {
     if (type != T_Q4_K) return false;
+    if (a.merge.partial && (mode != MODE_PLAIN || a.merge.n_chunks > (uint32_t)kMergeChunks || (a.merge.head_dim & 7u) ||
+                            (reinterpret_cast<uintptr_t>(a.merge.partial) & 15u)))
+        return false;
     if (mode != MODE_PLAIN && mode != MODE_GATE_UP_SWIGLU && mode != MODE_SIGMOID_ACC) return false;
     if (!a.scratch_partial || !a.status) return false;
     if ((reinterpret_cast<uintptr_t>(a.A) & 15u) || (a.A2 && (reinterpret_cast<uintptr_t>(a.A2) & 15u))) return false;
@@ -454,6 +506,7 @@ cudaError_t launch_warp_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStr
     wa.push = a.push;
     wa.consume = a.consume;
     wa.late = a.late;
+    if (mode == MODE_PLAIN) wa.merge = a.merge;
     cudaError_t e;
     switch (mode) {
         case MODE_PLAIN: e = launch_cfg<1, EPI_PLAIN>(wa, st, a.sm_count); break;

@@ -57,6 +57,15 @@ struct ConsumeArgs {
     uint32_t* status = nullptr;
 };
 
+// Activation built from split-K flash-attention partials while it is loaded (the fused merge + O projection,
+// src/shaders/dmmv_q4k_o_proj_merge.comp): x[head * head_dim + d] = sum_c w_c partial[(head * n_chunks + c) *
+// head_dim + d] / L, with the chunks' {max, sum} pairs behind the partials. partial == nullptr: plain x.
+struct MergeArgs {
+    const float* partial = nullptr;
+    const float* sinks = nullptr;  // nullptr: none
+    uint32_t n_heads = 0, n_chunks = 0, head_dim = 0, sink_offset = 0;
+};
+
 struct DmmvArgs {
     const uint8_t* A = nullptr;   // weights (gate weights for the gate/up modes)
     const uint8_t* A2 = nullptr;  // up weights for the gate/up modes
@@ -101,6 +110,7 @@ struct DmmvArgs {
     // the routing buffer: read the routing only after the dependency wait, and release this launch's own
     // dependents only after it (so that a successor's prologue may trust everything older).
     bool late = false;
+    MergeArgs merge;  // MODE_PLAIN on the Q4_K streaming kernel: x comes from attention partials
 };
 
 // Capacity of the split-K scratch a context owns.
@@ -205,6 +215,8 @@ cudaError_t launch_moe_router_topk(const float* x, const float* norm_w, const fl
                                    uint32_t* counter, uint32_t n_experts, uint32_t K, uint32_t k, uint32_t rule,
                                    uint32_t shared, uint32_t e_lo, uint32_t e_hi, uint32_t local_shared, float eps,
                                    cudaStream_t s, uint64_t* launches);
+// x[n_heads * head_dim] merged from split-K attention partials (the stand-alone form of MergeArgs).
+cudaError_t launch_attn_merge(const MergeArgs& m, float* out, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_moe_ep_filter(const uint32_t* in, uint32_t* out, uint32_t k, uint32_t n_tokens, uint32_t stride_in,
                                  uint32_t stride_out, uint32_t lo, uint32_t hi, cudaStream_t s, uint64_t* launches);
 cudaError_t launch_count_experts(const uint32_t* a, uint32_t* counts, uint32_t n_experts, uint32_t ne00,

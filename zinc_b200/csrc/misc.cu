@@ -371,11 +371,36 @@ __global__ void moe_weighted_bias_acc_kernel(float* __restrict__ a, const float*
 __global__ void moe_ep_filter_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, uint32_t k,
                                      uint32_t n_tokens, uint32_t stride_in, uint32_t stride_out, uint32_t lo,
                                      uint32_t hi) {
+    // rows of out hold the ids and the weights, or (stride_out < 2k) the ids alone: the flattened id table the
+    // cross-token calls take
+    const uint32_t per = stride_out < 2 * k ? k : 2 * k;
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_tokens * 2 * k) return;
-    const uint32_t tok = i / (2 * k), j = i - tok * 2 * k;
+    if (i >= n_tokens * per) return;
+    const uint32_t tok = i / per, j = i - tok * per;
     const uint32_t v = in[(size_t)tok * stride_in + j];
     out[(size_t)tok * stride_out + j] = j >= k ? v : (v >= lo && v < hi) ? v - lo : 0xFFFFFFFFu;
+}
+
+// ---- merge of split-K attention partials ----------------------------------------------------
+// One thread per output element (src/shaders/dmmv_q4k_o_proj_merge.comp:104-148, without the matvec: the form
+// used when the streaming kernel cannot build the vector while loading it).
+__global__ void attn_merge_kernel(const MergeArgs m, float* __restrict__ out) {
+    const uint32_t k = blockIdx.x * blockDim.x + threadIdx.x;
+    if (k >= m.n_heads * m.head_dim) return;
+    const uint32_t head = k / m.head_dim, d = k - head * m.head_dim;
+    const float* lse = m.partial + (size_t)m.n_heads * m.n_chunks * m.head_dim + (size_t)head * m.n_chunks * 2;
+    float acc = 0.f, inv;
+    if (m.n_chunks <= 16) {
+        float w[16];
+        inv = attn_merge_weights<16>(lse, m.sinks, m.sink_offset + head, m.n_chunks, w);
+#pragma unroll
+        for (int c = 0; c < 16; ++c)
+            if ((uint32_t)c < m.n_chunks)
+                acc = fmaf(w[c], __ldg(m.partial + ((size_t)head * m.n_chunks + c) * m.head_dim + d), acc);
+    } else {
+        inv = 0.f;  // refused on the host
+    }
+    out[k] = acc * inv;
 }
 
 // ---- fused RMS norm + f32 router matvec -------------------------------------------------
@@ -605,8 +630,10 @@ __global__ void moe_route_scatter_kernel(const uint32_t* __restrict__ routing, c
     const uint32_t t = (uint32_t)(id / hidden), d = (uint32_t)(id - (uint64_t)t * hidden);
     const uint32_t* row = routing + (size_t)t * routing_stride;
     float sum = 0.f;
-    for (uint32_t s = 0; s < k; ++s)
+    for (uint32_t s = 0; s < k; ++s) {
+        if (__ldg(row + s) == kSkipExpert) continue;  // no expert in this slot on this rank: its src row was never written
         sum = fmaf(__uint_as_float(__ldg(row + k + s)), src[((size_t)t * k + s) * hidden + d], sum);
+    }
     dst[id] += sum;
 }
 
@@ -729,6 +756,13 @@ cudaError_t launch_moe_weighted_bias_acc(float* a, const float* bias, const uint
                                          uint32_t n_used, uint32_t n_experts, uint32_t* status, cudaStream_t s,
                                          uint64_t* launches) {
     moe_weighted_bias_acc_kernel<<<(n + 255) / 256, 256, 0, s>>>(a, bias, routing, n, n_used, n_experts, status);
+    if (launches) ++*launches;
+    return cudaGetLastError();
+}
+
+cudaError_t launch_attn_merge(const MergeArgs& m, float* out, cudaStream_t s, uint64_t* launches) {
+    const uint32_t n = m.n_heads * m.head_dim;
+    attn_merge_kernel<<<(n + 255) / 256, 256, 0, s>>>(m, out);
     if (launches) ++*launches;
     return cudaGetLastError();
 }

@@ -437,6 +437,14 @@ class DmmvDispatch:
         self.ctx.call("zc_rms_norm_dmmv_f32", h.ptr, h.size, w.ptr, w.size, r.ptr, r.size, no.ptr, no.size,
                       lg.ptr, lg.size, M, K, C.c_float(eps))
 
+    # dispatchDmmvOprojMerge (src/compute/forward.zig:8360-8411): split-K attention merge + O projection
+    def dispatchDmmvOprojMerge(self, quant_type, o_tensor, partial_buf, sinks_buf, hidden_buf, M, K, n_heads,
+                               n_i_chunks, sink_offset, head_dim, acc_mode=1, a_offset=0, y_offset=0):
+        A, p, y = map(_buf, (o_tensor, partial_buf, hidden_buf))
+        s = _buf(sinks_buf) if sinks_buf is not None else Buffer(None, 0)
+        self.ctx.call("zc_dmmv_o_proj_merge", quant_type, A.ptr, A.size, p.ptr, p.size, y.ptr, y.size, s.ptr, s.size,
+                      M, K, a_offset, y_offset, acc_mode, n_heads, n_i_chunks, sink_offset, head_dim)
+
     # fused RMS norm + alpha / beta SSM projections (src/shaders/rms_norm_dmmv_q4k_alpha_beta.comp)
     def dispatchRmsNormDmmvAlphaBeta(self, hidden, norm_weights, alpha_weights, beta_weights, norm_out, alpha_out,
                                      beta_out, M, K, eps):

@@ -83,6 +83,15 @@ def ffn_split(ffn: int, block: int, world: int):
     return out
 
 
+def ep_local_ids(ids, e_lo: int, e_hi: int):
+    """Host restatement of the expert-parallel routing filter (`zc_moe_ep_filter`): a numpy array of expert ids
+    as the rank that owns [e_lo, e_hi) sees them, renumbered from zero, every other id 0xFFFFFFFF."""
+    import numpy as np
+
+    ids = np.asarray(ids, dtype=np.uint32)
+    return np.where((ids >= e_lo) & (ids < e_hi), ids - np.uint32(e_lo), np.uint32(0xFFFFFFFF)).astype(np.uint32)
+
+
 def shard_expert_rows(torch, w, n_experts: int, rows: int, row_nbytes: int, lo: int, hi: int):
     """Rows [lo, hi) of every expert of a stacked [n_experts][rows][row bytes] tensor, stacked again."""
     return w.view(n_experts, rows, row_nbytes)[:, lo:hi, :].contiguous().view(-1)
@@ -280,6 +289,113 @@ class MoeDecode:
                     self.allreduce(self.partial)
                 dd.dispatchMoeWeightedAcc(self.hidden, self.partial, self.one, s.hidden, 1, s.hidden)
         return dd.ctx.launch_count - n0
+
+
+@dataclass
+class MoePrefill:
+    """The routed experts of one MoE layer over a prefill batch of T tokens: gate and up of every (token, slot)
+    pair grouped by expert on the tensor cores, activation, down, and the weighted sum of a token's slots back
+    into its hidden row (the grouped path of src/shaders/metal/moe_route_pack.metal, dmmv_q4k_moe_cols.metal,
+    moe_route_scatter.metal). The routing ids are the selection of N(0,1) logits.
+
+    Expert parallelism (world > 1): tokens and routing are replicated; rank r holds the whole experts
+    [r E / N, (r+1) E / N), filters the routing to them (`zc_moe_ep_filter`: local ids, the other slots marked
+    absent), runs the same calls on its own stack (pairs of absent slots are neither grouped nor computed, and the
+    weighted sum leaves them out), and the ranks' partial [T][hidden] outputs are summed by `allreduce` (a
+    bandwidth-bound sum of T * hidden floats: NCCL)."""
+    shape: MoeShape
+    dd: DmmvDispatch
+    T: int
+    rank: int = 0
+    world: int = 1
+    e_lo: int = 0
+    e_hi: int = 0
+    wg: object = None
+    wu: object = None
+    wd: object = None
+    X: object = None
+    routing: object = None        # [T][2k] ids + weights of the global selection
+    routing_local: object = None  # the same as this rank sees it
+    ids_local: object = None      # [T][k] flattened id table of the cross-token calls
+    gate: object = None
+    up: object = None
+    act: object = None
+    down: object = None
+    hidden: object = None
+    workspace: object = None
+    allreduce: object = None
+
+    @staticmethod
+    def build(torch, dd: DmmvDispatch, shape: MoeShape, T: int, seed: int = 5, rank: int = 0, world: int = 1,
+              allreduce=None, local_only: bool = False) -> "MoePrefill":
+        s = shape
+        if s.n_experts % world:
+            raise ValueError(f"{s.n_experts} experts do not divide over {world} ranks")
+        dev = f"cuda:{torch.cuda.current_device()}"
+        n_local = s.n_experts // world
+        st = MoePrefill(shape=s, dd=dd, T=T, rank=rank, world=world, allreduce=allreduce,
+                        e_lo=rank * n_local, e_hi=(rank + 1) * n_local)
+        eg = s.ffn * row_bytes(s.t_gate_up, s.hidden)
+        ed = s.hidden * row_bytes(s.t_down, s.ffn)
+        if local_only and world > 1:   # benchmark: only this rank's experts are ever generated
+            st.wg = synth.torch_quant_matrix(s.t_gate_up, n_local * s.ffn, s.hidden, dev, seed * 31 + 3 * rank)
+            st.wu = synth.torch_quant_matrix(s.t_gate_up, n_local * s.ffn, s.hidden, dev, seed * 31 + 3 * rank + 1)
+            st.wd = synth.torch_quant_matrix(s.t_down, n_local * s.hidden, s.ffn, dev, seed * 31 + 3 * rank + 2)
+        else:                           # every rank cuts its experts out of the same seeded full tensors
+            wg = synth.torch_quant_matrix(s.t_gate_up, s.n_experts * s.ffn, s.hidden, dev, seed * 31)
+            wu = synth.torch_quant_matrix(s.t_gate_up, s.n_experts * s.ffn, s.hidden, dev, seed * 31 + 1)
+            wd = synth.torch_quant_matrix(s.t_down, s.n_experts * s.hidden, s.ffn, dev, seed * 31 + 2)
+            st.wg = wg[st.e_lo * eg:st.e_hi * eg].clone()
+            st.wu = wu[st.e_lo * eg:st.e_hi * eg].clone()
+            st.wd = wd[st.e_lo * ed:st.e_hi * ed].clone()
+            del wg, wu, wd
+            torch.cuda.empty_cache()
+        gen = torch.Generator(device=dev).manual_seed(seed)   # the same tokens and routing on every rank
+        k = s.top_k
+        st.X = torch.randn(T, s.hidden, device=dev, generator=gen)
+        logits = torch.randn(T, s.n_experts, device=dev, generator=gen)
+        st.routing = torch.zeros(T * 2 * k, dtype=torch.int32, device=dev)
+        dd.dispatchSoftmaxTopk(logits, st.routing, s.n_experts, k, s.rule, T)
+        if world > 1:
+            st.routing_local = torch.zeros(T * 2 * k, dtype=torch.int32, device=dev)
+            st.ids_local = torch.zeros(T * k, dtype=torch.int32, device=dev)
+        else:
+            dd.ctx.submit_and_wait()
+            st.routing_local = st.routing
+            st.ids_local = st.routing.view(T, 2 * k)[:, :k].contiguous().view(-1)
+        f32 = dict(dtype=torch.float32, device=dev)
+        st.gate = torch.zeros(T * k * s.ffn, **f32)
+        st.up = torch.zeros(T * k * s.ffn, **f32)
+        st.act = torch.zeros(T * k * s.ffn, **f32)
+        st.down = torch.zeros(T * k * s.hidden, **f32)
+        st.hidden = torch.zeros(T * s.hidden, **f32)
+        st.workspace = torch.empty(max(dd.moeGroupedWorkspaceBytes(T, k, s.hidden, n_local),
+                                       dd.moeGroupedWorkspaceBytes(T * k, 1, s.ffn, n_local)),
+                                   dtype=torch.uint8, device=dev)
+        return st
+
+    def record(self) -> int:
+        """Enqueue the layer (the workspace must be set: `dd.setWorkspace(self.workspace)`); hidden += result.
+        Returns the number of the library's kernels launched."""
+        s, dd, T, k = self.shape, self.dd, self.T, self.shape.top_k
+        n0 = dd.ctx.launch_count
+        n_local = self.e_hi - self.e_lo
+        eg = s.ffn * row_bytes(s.t_gate_up, s.hidden)
+        ed = s.hidden * row_bytes(s.t_down, s.ffn)
+        if self.world > 1:
+            dd.ctx.memset(_as_buffer(self.hidden), 0)
+            dd.dispatchMoeEpFilter(self.routing, self.routing_local, k, self.e_lo, self.e_hi, n_tokens=T)
+            dd.dispatchMoeEpFilter(self.routing, self.ids_local, k, self.e_lo, self.e_hi, n_tokens=T, out_stride=k)
+        dd.recordMoeBatchedDispatchPair(s.t_gate_up, self.wg, self.wu, self.X, self.gate, self.up, self.ids_local,
+                                        s.ffn, s.hidden, eg, n_local, k, T, s.hidden, k * s.ffn)
+        dd.dispatchSwiglu(self.gate, self.up, self.act, T * k * s.ffn, oai=s.oai)
+        dd.recordMoeBatchedDispatch(s.t_down, self.wd, self.act, self.down, self.ids_local, s.hidden, s.ffn, ed,
+                                    n_local, 1, T * k, s.ffn, s.hidden)
+        dd.dispatchMoeRouteScatter(self.routing_local, self.down, self.hidden, T, s.hidden, k, 2 * k)
+        n = dd.ctx.launch_count - n0
+        if self.world > 1 and self.allreduce is not None:
+            self.allreduce(self.hidden)
+        return n
 
 
 def _as_buffer(t):
