@@ -53,6 +53,9 @@ struct MoeDmmvPushConstants {  // src/compute/dmmv.zig:42-49
 struct MoeBatchedDmmvPushConstants {  // src/compute/dmmv.zig:55-62
     uint32_t M, K, expert_stride, n_experts_used, x_token_stride, y_token_stride;
 };
+struct OprojMergePushConstants {  // src/compute/dmmv.zig:76-93
+    uint32_t M, K, a_offset = 0, x_offset = 0, y_offset = 0, acc_mode = 1, n_heads, n_i_chunks, sink_offset, head_dim;
+};
 
 class DmmvDispatch {
 public:
@@ -86,6 +89,16 @@ public:
     }
     Error recordDispatch(GGMLType quant_type, Buffer A, Buffer x, Buffer y, const DmmvPushConstants& pc) {
         return recordDispatch(quant_type, A, x, y, pc.M, pc.K, pc.a_offset, pc.x_offset, pc.y_offset, pc.acc_mode);
+    }
+
+    // The fused split-K attention merge + O projection dispatch (src/compute/forward.zig:8360-8411): bindings
+    // W_o, partials (+ LSE region), hidden, sinks (an empty Buffer: no sinks)
+    Error recordOprojMerge(GGMLType quant_type, Buffer o_tensor, Buffer partial_buf, Buffer hidden_buf, Buffer sinks_buf,
+                           const OprojMergePushConstants& pc) {
+        return static_cast<Error>(zc_dmmv_o_proj_merge(
+            ctx_, static_cast<uint32_t>(quant_type), o_tensor.ptr, o_tensor.size, partial_buf.ptr, partial_buf.size,
+            hidden_buf.ptr, hidden_buf.size, sinks_buf.ptr, sinks_buf.size, pc.M, pc.K, pc.a_offset, pc.y_offset,
+            pc.acc_mode, pc.n_heads, pc.n_i_chunks, pc.sink_offset, pc.head_dim));
     }
 
     // recordBatchDispatchPush (src/compute/dmmv.zig:880-926)

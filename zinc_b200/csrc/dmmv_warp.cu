@@ -206,8 +206,10 @@ __device__ __forceinline__ int seg_of(const WarpArgs& a, uint32_t T) {
 }
 
 // kSeg: 0 one matrix (pair), 1 grouped matrices (host-side segment table), 2 MoE slots (device-side routing)
-template <int NS, int EPI, int kWarps, int kSeg = 0>
-__global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel(const WarpArgs a) {
+// kMerge: the activation is merged from split-K attention partials while it is loaded (a kernel of its own, so
+// that the plain matvec carries neither the code nor the arguments)
+template <int NS, int EPI, int kWarps, int kSeg, bool kMerge>
+__device__ __forceinline__ void dmmv_q4k_body(const WarpArgs& a, const MergeArgs& merge) {
     extern __shared__ uint8_t smem_raw[];
     pdl_begin(a);
     const Smem s = carve(smem_raw, a.K, kWarps);
@@ -296,13 +298,8 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
     pdl_late(a);
     XRegs xr;
     auto fetch_x = [&]() {
-        if constexpr (kSeg == 0 && NS == 1 && EPI == EPI_PLAIN) {
-            if (a.merge.partial) {
-                load_x_merge<kWarps>(xr, a.merge, a.K, warp, lane);
-                return;
-            }
-        }
-        load_x<kWarps>(xr, a.x, a.K, warp, lane);
+        if constexpr (kMerge) load_x_merge<kWarps>(xr, merge, a.K, warp, lane);
+        else load_x<kWarps>(xr, a.x, a.K, warp, lane);
     };
     if (a.late) fetch_x();
 #pragma unroll
@@ -451,6 +448,15 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel
 }
 
 template <int NS, int EPI, int kWarps, int kSeg = 0>
+__global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_warp_kernel(const WarpArgs a) {
+    dmmv_q4k_body<NS, EPI, kWarps, kSeg, false>(a, MergeArgs());
+}
+template <int kWarps>
+__global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q4k_merge_kernel(const WarpArgs a, const MergeArgs m) {
+    dmmv_q4k_body<1, EPI_PLAIN, kWarps, 0, true>(a, m);
+}
+
+template <int NS, int EPI, int kWarps, int kSeg = 0>
 cudaError_t launch_w(const WarpArgs& a, cudaStream_t st, int sm_count, size_t smem) {
     auto kern = dmmv_q4k_warp_kernel<NS, EPI, kWarps, kSeg>;
     static std::atomic<uint64_t> attr_done{0};  // per device ordinal
@@ -462,6 +468,29 @@ cudaError_t launch_w(const WarpArgs& a, cudaStream_t st, int sm_count, size_t sm
     if (grid * kWarps > kStreamMaxWorkers) grid = kStreamMaxWorkers / kWarps;
     if (grid == 0) return cudaErrorInvalidConfiguration;
     return launch_pdl(kern, (uint32_t)grid, kWarps * 32, smem, st, a);
+}
+
+template <int kWarps>
+cudaError_t launch_w_merge(const WarpArgs& a, const MergeArgs& m, cudaStream_t st, int sm_count, size_t smem) {
+    auto kern = dmmv_q4k_merge_kernel<kWarps>;
+    static std::atomic<uint64_t> attr_done{0};  // per device ordinal
+    if (cudaError_t ea = ensure_dynamic_smem(kern, kWarps == 8 ? (int)kTwoPerSm : 227 * 1024, attr_done); ea != cudaSuccess) return ea;
+    const uint64_t U = (uint64_t)((a.M + 15) / 16) * (((a.K >> 8) + kCB - 1) / kCB);
+    uint64_t grid = (uint64_t)sm_count * (16 / kWarps);
+    if (grid * kWarps > U) grid = U / kWarps;
+    if (grid * kWarps > kStreamMaxWorkers) grid = kStreamMaxWorkers / kWarps;
+    if (grid == 0) return cudaErrorInvalidConfiguration;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((uint32_t)grid, 1, 1);
+    cfg.blockDim = dim3(kWarps * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, a, m);
 }
 
 template <int NS, int EPI>
@@ -506,10 +535,17 @@ cudaError_t launch_warp_dmmv(uint32_t type, int mode, const DmmvArgs& a, cudaStr
     wa.push = a.push;
     wa.consume = a.consume;
     wa.late = a.late;
-    if (mode == MODE_PLAIN) wa.merge = a.merge;
     cudaError_t e;
     switch (mode) {
-        case MODE_PLAIN: e = launch_cfg<1, EPI_PLAIN>(wa, st, a.sm_count); break;
+        case MODE_PLAIN:
+            if (a.merge.partial) {
+                const size_t s8 = smem_bytes(a.K, 8);
+                e = s8 <= kTwoPerSm ? launch_w_merge<8>(wa, a.merge, st, a.sm_count, s8)
+                                    : launch_w_merge<16>(wa, a.merge, st, a.sm_count, smem_bytes(a.K, 16));
+            } else {
+                e = launch_cfg<1, EPI_PLAIN>(wa, st, a.sm_count);
+            }
+            break;
         case MODE_GATE_UP_SWIGLU: e = launch_cfg<2, EPI_GATE_UP>(wa, st, a.sm_count); break;
         case MODE_SIGMOID_ACC: e = launch_cfg<1, EPI_SIGMOID_ACC>(wa, st, a.sm_count); break;
         default: return cudaErrorInvalidValue;

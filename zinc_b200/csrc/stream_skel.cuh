@@ -51,7 +51,6 @@ struct WarpArgs {
     // gate / up row; EPI_ACC adds sum_s w_s bias[0][e_s][row]
     const float* bias[2] = {nullptr, nullptr};
     uint32_t late = 0;       // release the dependents after the dependency wait, and read the routing after it
-    MergeArgs merge;         // Q4_K: the activation is merged from attention partials while it is loaded
 };
 
 // Start of a streaming kernel: release the next kernel of the stream at once, unless this launch was told that
