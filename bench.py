@@ -334,9 +334,15 @@ def prefill_gemm_results(torch, zb, ctx, dd, stream, sampler, quick):
     for qt, name, M, K in ((zb.Q4_K, "q4_k", 12288, 4096), (zb.Q6_K, "q6_k", 4096, 12288),
                            (zb.MXFP4, "mxfp4", 5760, 2880)):
         ws = [synth.torch_quant_matrix(qt, M, K, dev, 100 + i) for i in range(copies)]
-        for T in (128, 512, 2048):
+        # MXFP4 twice: weights dequantised to bf16 tiles, and (a workspace lent) as stored on the block-scaled path
+        cases = [(T, path) for T in (128, 512, 2048) for path in (("bf16 tiles", "block-scaled") if qt == zb.MXFP4 else ("",))]
+        for T, path in cases:
             X = torch.randn(T, K, device=dev).to(torch.bfloat16)
             D = torch.zeros(T * M, dtype=torch.float32, device=dev)
+            wsp = None
+            if path == "block-scaled":
+                wsp = torch.empty(dd.mulMmWorkspaceBytes(qt, T, K), dtype=torch.uint8, device=dev)
+                dd.setWorkspace(wsp)
             n0 = ctx.launch_count
             for i in range(copies):
                 dd.recordMulMm(qt, ws[i], X, D, M, T, K, K, M, 0, 0, 0, zb.BF16)
@@ -360,6 +366,9 @@ def prefill_gemm_results(torch, zb, ctx, dd, stream, sampler, quick):
                 "warmup": copies, "ms_per_step": us / 1e3, "best_ms_per_step": min(per), "higher_is_better": True,
                 "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": f"prefill dequant-GEMM {name} {M}x{K}, T={T}, bf16 activations, f32 out",
+                           **({"path": path + (" (tcgen05 kind::mxf8f6f4 with E8M0 block scales, weights as stored, two FP8 "
+                                               "activation terms; the activation split kernel is inside the timed call)"
+                                               if path == "block-scaled" else "")} if path else {}),
                            "l2": f"{copies} weight copies in rotation ({copies * ws[0].numel() / 1e6:.0f} MB)",
                            "bytes_per_launch": wbytes + T * K * 2 + T * M * 4},
                 "gpu_launches": per_call * len(per) * 24,
@@ -369,7 +378,9 @@ def prefill_gemm_results(torch, zb, ctx, dd, stream, sampler, quick):
                              "us_per_launch": us, "traffic": None},
                 "clocks": sampler.window(t0, t1),
             })
-            del X, D
+            if wsp is not None:
+                dd.setWorkspace(None)
+            del X, D, wsp
         del ws
         torch.cuda.empty_cache()
     return out

@@ -408,6 +408,14 @@ int32_t zc_moe_dmmv_batched_pair(zc_ctx* ctx, uint32_t type,
 int32_t zc_set_workspace(zc_ctx* ctx, void* workspace, uint64_t size);
 uint64_t zc_moe_grouped_workspace_bytes(uint32_t n_tokens, uint32_t n_experts_used, uint32_t K, uint32_t n_experts);
 
+/* Workspace with which zc_mul_mm runs MXFP4 weights (bf16 activations, N >= 64 tokens, K % 32 == 0) on the
+ * block-scaled tensor-core path: the weights stay as stored (E2M1 nibbles + E8M0 block scales are the tensor
+ * core's own operand format), the activations are split into two FP8 terms whose sum is the bf16 value, written
+ * with their block scales into this workspace by a small kernel before the GEMM. 0 for types without such a path.
+ * Without a workspace of that size the weights are dequantised to bf16 tiles instead (same results to rounding
+ * of the f32 accumulation). */
+uint64_t zc_mul_mm_workspace_bytes(uint32_t type, uint32_t N, uint32_t K);
+
 /* ---- routing, combine, activation -----------------------------------------------------------
  * zc_softmax_topk: per token t, out[t*out_stride ..] = [k ids u32][k weights f32 bits].
  * Replaces dispatchSoftmaxTopk (src/compute/forward.zig:4135-4210;

@@ -99,7 +99,7 @@ EXPORTS = sorted(list(_OPS) + [
     "zc_init", "zc_get_stream", "zc_last_error", "zc_status_string", "zc_launch_count",
     "zc_block_size", "zc_bytes_per_block", "zc_tensor_size_bytes", "zc_expert_slice_bytes",
     "zc_dmmv_supported", "zc_moe_dmmv_supported", "zc_dmmv_q4k_static_scratch", "zc_moe_grouped_workspace_bytes",
-    "zc_comm_buffer_bytes",
+    "zc_comm_buffer_bytes", "zc_mul_mm_workspace_bytes",
 ])
 
 _lib = None
@@ -133,6 +133,8 @@ def lib() -> C.CDLL:
             getattr(L, name).argtypes = [_u32]
         L.zc_comm_buffer_bytes.restype = _u64
         L.zc_comm_buffer_bytes.argtypes = []
+        L.zc_mul_mm_workspace_bytes.restype = _u64
+        L.zc_mul_mm_workspace_bytes.argtypes = [_u32, _u32, _u32]
         L.zc_moe_grouped_workspace_bytes.restype = _u64
         L.zc_moe_grouped_workspace_bytes.argtypes = [_u32, _u32, _u32, _u32]
         L.zc_tensor_size_bytes.restype = _u64

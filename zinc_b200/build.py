@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 SO = os.path.join(HERE, "libzinc_b200.so")
 SOURCES = ["api.cu", "dmmv.cu", "dmmv_warp.cu", "dmmv_q6k.cu", "misc.cu", "gemm_simple.cu", "gemm_tc.cu",
-           "dmmv_static_scratch.cu", "comm.cu", "dmmv_mxfp4.cu", "moe_gemm_tc.cu"]
+           "dmmv_static_scratch.cu", "comm.cu", "dmmv_mxfp4.cu", "moe_gemm_tc.cu", "gemm_mx.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--use_fast_math=false", "-Xptxas", "-v",

@@ -809,6 +809,11 @@ int32_t zc_mul_mm(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, co
     const void* Bp = static_cast<const uint8_t*>(B) + b_offset * esz;
     cudaError_t e = launch_mul_mm(type, u8(A, a_offset), Bp, f32m(D, d_offset * 4), M, N, K, stride_b, stride_d,
                                   act_type == ZC_BF16, ctx->status_dev, ctx->stream, &ctx->launches);
+    // MXFP4 with a lent workspace: the block-scaled tensor-core path (weights as stored, two FP8 activation terms)
+    if (e == cudaErrorNotSupported && act_type == ZC_BF16 &&
+        mul_mm_mx_eligible(type, u8(A, a_offset), Bp, N, K, stride_b, ctx->workspace, ctx->workspace_size))
+        e = launch_mul_mm_mx(u8(A, a_offset), a_size - a_offset, Bp, f32m(D, d_offset * 4), M, N, K, stride_b, stride_d,
+                             ctx->workspace, ctx->status_dev, ctx->sm_count, ctx->stream, &ctx->launches);
     // layouts a tensor map cannot describe (MXFP4; Q6_K rows without a 16-byte pitch): still tensor cores
     if (e == cudaErrorNotSupported && act_type == ZC_BF16 &&
         mul_mm_cp_async_eligible(type, u8(A, a_offset), Bp, N, K, stride_b))
@@ -1160,6 +1165,10 @@ int32_t zc_moe_dmmv_batched_pair(zc_ctx* ctx, uint32_t type, const void* Wg, uin
 
 uint64_t zc_moe_grouped_workspace_bytes(uint32_t n_tokens, uint32_t n_experts_used, uint32_t K, uint32_t n_experts) {
     return moe_grouped_workspace_bytes((uint64_t)n_tokens * n_experts_used, K, n_experts);
+}
+
+uint64_t zc_mul_mm_workspace_bytes(uint32_t type, uint32_t N, uint32_t K) {
+    return type == T_MXFP4 ? mul_mm_mx_workspace_bytes(N, K) : 0;
 }
 
 int32_t zc_set_workspace(zc_ctx* ctx, void* workspace, uint64_t size) {

@@ -173,6 +173,14 @@ cudaError_t launch_moe_grouped(uint32_t type, const uint8_t* A, uint64_t a_bytes
 
 // Prefill GEMM for the weight layouts without a 16-byte row pitch (MXFP4, Q6_K with K % 2048 != 0): bf16
 // activations, raw blocks fetched with cp.async, same tile kernel as the grouped MoE path (moe_gemm_tc.cu).
+// MXFP4 weights on the block-scaled tensor-core path (gemm_mx.cu): weights as stored, bf16 activations split into
+// two FP8 terms in a caller-lent workspace.
+uint64_t mul_mm_mx_workspace_bytes(uint32_t N, uint32_t K);
+bool mul_mm_mx_eligible(uint32_t type, const uint8_t* A, const void* B, uint32_t N, uint32_t K, uint32_t stride_b,
+                        const void* workspace, uint64_t workspace_size);
+cudaError_t launch_mul_mm_mx(const uint8_t* A, uint64_t a_bytes, const void* B, float* D, uint32_t M, uint32_t N,
+                             uint32_t K, uint32_t stride_b, uint32_t stride_d, void* workspace, uint32_t* status,
+                             int sm_count, cudaStream_t s, uint64_t* launches);
 bool mul_mm_cp_async_eligible(uint32_t type, const uint8_t* A, const void* B, uint32_t N, uint32_t K,
                               uint32_t stride_b);
 cudaError_t launch_mul_mm_cp_async(uint32_t type, const uint8_t* A, uint64_t a_bytes, const void* B, float* D,

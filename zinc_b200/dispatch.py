@@ -320,6 +320,11 @@ class DmmvDispatch:
         self._workspace = workspace  # keep the tensor alive while the library may use it
 
     @staticmethod
+    def mulMmWorkspaceBytes(quant_type, N, K) -> int:
+        from ._lib import lib
+        return int(lib().zc_mul_mm_workspace_bytes(quant_type, N, K))
+
+    @staticmethod
     def moeGroupedWorkspaceBytes(n_tokens, n_experts_used, K, n_experts) -> int:
         from ._lib import lib
         return int(lib().zc_moe_grouped_workspace_bytes(n_tokens, n_experts_used, K, n_experts))
