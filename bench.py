@@ -342,16 +342,22 @@ def prefill_gemm_results(torch, zb, ctx, dd, stream, sampler, quick):
             wsp = None
             if path == "block-scaled":
                 wsp = torch.empty(dd.mulMmWorkspaceBytes(qt, T, K), dtype=torch.uint8, device=dev)
-                dd.setWorkspace(wsp)
+
+            def call(wmat, wsp=wsp, X=X, D=D, T=T):
+                if wsp is not None:
+                    dd.recordMulMmBlockScaled(qt, wmat, X, D, M, T, K, K, M, wsp)
+                else:
+                    dd.recordMulMm(qt, wmat, X, D, M, T, K, K, M, 0, 0, 0, zb.BF16)
+
             n0 = ctx.launch_count
             for i in range(copies):
-                dd.recordMulMm(qt, ws[i], X, D, M, T, K, K, M, 0, 0, 0, zb.BF16)
+                call(ws[i])
             per_call = (ctx.launch_count - n0) // copies
             stream.synchronize()
             it = [0]
 
             def one():
-                dd.recordMulMm(qt, ws[it[0] % copies], X, D, M, T, K, K, M, 0, 0, 0, zb.BF16)
+                call(ws[it[0] % copies])
                 it[0] += 1
 
             per, t0, t1 = timed_blocks(torch, stream, one, 24, min_total_s=0.15 if quick else 0.4, max_blocks=400)
@@ -378,8 +384,6 @@ def prefill_gemm_results(torch, zb, ctx, dd, stream, sampler, quick):
                              "us_per_launch": us, "traffic": None},
                 "clocks": sampler.window(t0, t1),
             })
-            if wsp is not None:
-                dd.setWorkspace(None)
             del X, D, wsp
         del ws
         torch.cuda.empty_cache()

@@ -408,13 +408,22 @@ int32_t zc_moe_dmmv_batched_pair(zc_ctx* ctx, uint32_t type,
 int32_t zc_set_workspace(zc_ctx* ctx, void* workspace, uint64_t size);
 uint64_t zc_moe_grouped_workspace_bytes(uint32_t n_tokens, uint32_t n_experts_used, uint32_t K, uint32_t n_experts);
 
-/* Workspace with which zc_mul_mm runs MXFP4 weights (bf16 activations, N >= 64 tokens, K % 32 == 0) on the
- * block-scaled tensor-core path: the weights stay as stored (E2M1 nibbles + E8M0 block scales are the tensor
- * core's own operand format), the activations are split into two FP8 terms whose sum is the bf16 value, written
- * with their block scales into this workspace by a small kernel before the GEMM. 0 for types without such a path.
- * Without a workspace of that size the weights are dequantised to bf16 tiles instead (same results to rounding
- * of the f32 accumulation). */
+/* zc_mul_mm for MXFP4 weights and bf16 activations on the block-scaled tensor-core path
+ * (tcgen05.mma kind::mxf8f6f4 with E8M0 block scales): the weights stay as stored (E2M1 nibbles + one E8M0 scale
+ * byte per 32 elements are the tensor core's own operand format; src/compute/forward.zig:441-459 gives the
+ * element order), the activations are split into two FP8 (E4M3) terms with power-of-two block scales whose sum
+ * is the bf16 value exactly, written into `workspace` (zc_mul_mm_workspace_bytes(type, N, K) bytes, 256-byte
+ * aligned, caller-owned) by a small kernel before the GEMM. N >= 64 tokens, K >= 128 and a multiple of 32; A and
+ * B 16-byte aligned, stride_b a multiple of 8; offsets in elements of B and D as in zc_mul_mm. Results equal
+ * zc_mul_mm's to the rounding of the f32 accumulation. As measured it is not yet faster than zc_mul_mm's route
+ * (weights dequantised to bf16 tiles), which therefore stays the default. */
 uint64_t zc_mul_mm_workspace_bytes(uint32_t type, uint32_t N, uint32_t K);
+int32_t zc_mul_mm_block_scaled(zc_ctx* ctx, uint32_t type,
+                               const void* A, uint64_t a_size, const void* B, uint64_t b_size,
+                               void* D, uint64_t d_size,
+                               uint32_t M, uint32_t N, uint32_t K, uint32_t stride_b, uint32_t stride_d,
+                               uint64_t a_offset, uint64_t b_offset, uint64_t d_offset,
+                               void* workspace, uint64_t workspace_size);
 
 /* ---- routing, combine, activation -----------------------------------------------------------
  * zc_softmax_topk: per token t, out[t*out_stride ..] = [k ids u32][k weights f32 bits].

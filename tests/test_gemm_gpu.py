@@ -94,7 +94,7 @@ def test_mul_mm_mxfp4_bf16(gpu, oracle, M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (256, 128, 512), (300, 200, 2880), (1024, 600, 2880), (130, 64, 160)])
 def test_mul_mm_mxfp4_block_scaled(gpu, oracle, M, N, K):
-    """MXFP4 weights as stored on the block-scaled tensor-core path (a workspace is lent): the two FP8 terms add
+    """MXFP4 weights as stored on the block-scaled tensor-core path (zc_mul_mm_block_scaled): the two FP8 terms add
     up to the bf16 activation exactly, so the product differs from the exact one by the f32 accumulation only.
     Row, token and K counts that are not multiples of the tile, a wide activation range inside a block, and the
     launch count (split + GEMM) that shows this path ran."""
@@ -111,14 +111,14 @@ def test_mul_mm_mxfp4_block_scaled(gpu, oracle, M, N, K):
     D = out_with_canary(torch, N * M)
     ws = torch.empty(dd.mulMmWorkspaceBytes(t, N, K), dtype=torch.uint8, device="cuda")
     assert ws.numel() > 0 and dd.mulMmWorkspaceBytes(zb.Q4_K, N, K) == 0
-    dd.setWorkspace(ws)
-    try:
-        n0 = ctx.launch_count
-        dd.recordMulMm(t, dev(torch, w), dev(torch, bits.view(np.int16)), D, M, N, K, K, M, 0, 0, 0, zb.BF16)
-        ctx.submit_and_wait()
-        assert ctx.launch_count - n0 == 2
-    finally:
-        dd.setWorkspace(None)
+    n0 = ctx.launch_count
+    dd.recordMulMmBlockScaled(t, dev(torch, w), dev(torch, bits.view(np.int16)), D, M, N, K, K, M, ws)
+    ctx.submit_and_wait()
+    assert ctx.launch_count - n0 == 2
+    with pytest.raises(zb.InvalidArgument):   # a workspace that is too small
+        dd.recordMulMmBlockScaled(t, dev(torch, w), dev(torch, bits.view(np.int16)), D, M, N, K, K, M, ws[:1024])
+    with pytest.raises(zb.UnsupportedQuantType):
+        dd.recordMulMmBlockScaled(zb.Q4_K, dev(torch, w), dev(torch, bits.view(np.int16)), D, M, N, K, K, M, ws)
     got = D[:N * M].cpu().numpy().reshape(N, M)
     assert canary_intact(D, N * M)
     assert rel_l2(got, oracle.gemm_f64(w, t, M, K, Bexact)) <= 1e-5

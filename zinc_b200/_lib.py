@@ -33,6 +33,8 @@ _OPS = {
                                      _u64, _u64, _u64, _u64],
     "zc_dmmv_sigmoid_acc": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u64, _u64, _u32],
     "zc_rms_norm_dmmv_f32": [_vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, C.c_float],
+    "zc_mul_mm_block_scaled": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u32, _u32, _u32, _u64, _u64, _u64, _vp,
+                               _u64],
     "zc_dmmv_o_proj_merge": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _u32, _u32, _u64, _u64, _u32, _u32, _u32, _u32,
                              _u32],
     "zc_moe_gate_up_act_ex": [_u32, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64, _vp, _u64,

@@ -809,11 +809,6 @@ int32_t zc_mul_mm(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, co
     const void* Bp = static_cast<const uint8_t*>(B) + b_offset * esz;
     cudaError_t e = launch_mul_mm(type, u8(A, a_offset), Bp, f32m(D, d_offset * 4), M, N, K, stride_b, stride_d,
                                   act_type == ZC_BF16, ctx->status_dev, ctx->stream, &ctx->launches);
-    // MXFP4 with a lent workspace: the block-scaled tensor-core path (weights as stored, two FP8 activation terms)
-    if (e == cudaErrorNotSupported && act_type == ZC_BF16 &&
-        mul_mm_mx_eligible(type, u8(A, a_offset), Bp, N, K, stride_b, ctx->workspace, ctx->workspace_size))
-        e = launch_mul_mm_mx(u8(A, a_offset), a_size - a_offset, Bp, f32m(D, d_offset * 4), M, N, K, stride_b, stride_d,
-                             ctx->workspace, ctx->status_dev, ctx->sm_count, ctx->stream, &ctx->launches);
     // layouts a tensor map cannot describe (MXFP4; Q6_K rows without a 16-byte pitch): still tensor cores
     if (e == cudaErrorNotSupported && act_type == ZC_BF16 &&
         mul_mm_cp_async_eligible(type, u8(A, a_offset), Bp, N, K, stride_b))
@@ -1169,6 +1164,28 @@ uint64_t zc_moe_grouped_workspace_bytes(uint32_t n_tokens, uint32_t n_experts_us
 
 uint64_t zc_mul_mm_workspace_bytes(uint32_t type, uint32_t N, uint32_t K) {
     return type == T_MXFP4 ? mul_mm_mx_workspace_bytes(N, K) : 0;
+}
+
+int32_t zc_mul_mm_block_scaled(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, const void* B, uint64_t b_size,
+                               void* D, uint64_t d_size, uint32_t M, uint32_t N, uint32_t K, uint32_t stride_b,
+                               uint32_t stride_d, uint64_t a_offset, uint64_t b_offset, uint64_t d_offset,
+                               void* workspace, uint64_t workspace_size) {
+    ZC_ENTER(ctx);
+    const char* fn = "zc_mul_mm_block_scaled";
+    if (type != T_MXFP4) return fail(ctx, ZC_ERR_UNSUPPORTED_TYPE, "%s: MXFP4 weights only", fn);
+    if (N < 64 || K < 128) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: needs at least 64 tokens and K >= 128", fn);
+    ZC_TRY(check_mat(ctx, fn, type, A, a_size, a_offset, (uint64_t)M * row_bytes_of(type, K), M, K));
+    if (stride_b < K || stride_d < M) return fail(ctx, ZC_ERR_INVALID_ARG, "%s: stride smaller than extent", fn);
+    ZC_TRY(check_vec(ctx, fn, "B", B, b_size, b_offset * 2, ((uint64_t)(N - 1) * stride_b + K) * 2, 2));
+    ZC_TRY(check_vec(ctx, fn, "D", D, d_size, d_offset * 4, ((uint64_t)(N - 1) * stride_d + M) * 4, 4));
+    const void* Bp = static_cast<const uint8_t*>(B) + b_offset * 2;
+    if (!mul_mm_mx_eligible(type, u8(A, a_offset), Bp, N, K, stride_b, workspace, workspace_size))
+        return fail(ctx, ZC_ERR_INVALID_ARG,
+                    "%s: needs 16-byte aligned A and B, stride_b a multiple of 8 and a 256-byte aligned workspace of "
+                    "zc_mul_mm_workspace_bytes(type, N, K) bytes", fn);
+    const cudaError_t e = launch_mul_mm_mx(u8(A, a_offset), a_size - a_offset, Bp, f32m(D, d_offset * 4), M, N, K, stride_b,
+                                           stride_d, workspace, ctx->status_dev, ctx->sm_count, ctx->stream, &ctx->launches);
+    return e == cudaSuccess ? ZC_OK : cuda_fail(ctx, e, fn);
 }
 
 int32_t zc_set_workspace(zc_ctx* ctx, void* workspace, uint64_t size) {

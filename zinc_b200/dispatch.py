@@ -319,6 +319,14 @@ class DmmvDispatch:
             self.ctx.call("zc_set_workspace", w.ptr, w.size)
         self._workspace = workspace  # keep the tensor alive while the library may use it
 
+    # recordMulMm for MXFP4 weights on the block-scaled FP4 tensor-core path (weights as stored, bf16 activations
+    # as two exact FP8 terms in `workspace`)
+    def recordMulMmBlockScaled(self, quant_type, a_buf, b_buf, d_buf, M, N, K, stride_b, stride_d, workspace,
+                               a_offset=0, b_offset=0, d_offset=0):
+        a, b, d, w = map(_buf, (a_buf, b_buf, d_buf, workspace))
+        self.ctx.call("zc_mul_mm_block_scaled", quant_type, a.ptr, a.size, b.ptr, b.size, d.ptr, d.size, M, N, K,
+                      stride_b, stride_d, a_offset, b_offset, d_offset, w.ptr, w.size)
+
     @staticmethod
     def mulMmWorkspaceBytes(quant_type, N, K) -> int:
         from ._lib import lib
