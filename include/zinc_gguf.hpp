@@ -144,7 +144,7 @@ struct Reader {
                 const uint64_t n = read<uint64_t>();
                 if (n > size - pos) throw GGUFError("UnexpectedEof");  // every element takes at least one byte
                 MetadataArray arr;
-                arr.reserve((size_t)n);
+                arr.reserve((size_t)(n < (1u << 20) ? n : (1u << 20)));  // a count is a claim: grow beyond this as read
                 for (uint64_t i = 0; i < n; ++i) arr.push_back(readValue(et, depth + 1));
                 m.v = std::move(arr);
                 break;
@@ -178,6 +178,11 @@ inline GGUFFile parse(const void* data, uint64_t size) {
         t.n_dims = r.read<uint32_t>();
         if (t.n_dims > 4) throw GGUFError("InvalidTensor: more than 4 dimensions");
         for (uint32_t d = 0; d < t.n_dims; ++d) t.dims[d] = r.read<uint64_t>();
+        {  // the element count must fit 64 bits (a wrapped product would pass the byte-range check further down)
+            uint64_t n = 1;
+            for (uint32_t d = 0; d < t.n_dims; ++d)
+                if (__builtin_mul_overflow(n, t.dims[d], &n)) throw GGUFError("InvalidTensor: element count overflows");
+        }
         t.type_ = r.read<uint32_t>();
         t.offset = r.read<uint64_t>();
         f.tensors.push_back(std::move(t));
