@@ -26,7 +26,7 @@ struct zc_ctx {
     uint32_t* status_host = nullptr;  // pinned, mapped: deferred device-side status words
     uint32_t* status_dev = nullptr;
     uint2* scratch_partial = nullptr;  // split-K partial sums of the streaming matvecs, tagged (zero between launches)
-    uint32_t* router_counter = nullptr;  // arrival counter of the fused router + selection kernel (zero between launches)
+    uint2* router_tagged = nullptr;      // 1024 tagged logits of the fused router + selection kernel (zero between launches)
     uint64_t router_mark = 0;            // value of `launches` right after that kernel's last launch (0: never)
     float* merge_scratch = nullptr;      // kMergeScratchFloats f32: a merged attention vector on its way to a matvec
     int sm_count = 0;
@@ -49,6 +49,8 @@ namespace {
 using namespace zc;
 
 constexpr uint32_t kMergeScratchFloats = 16384;
+constexpr size_t kRouterTaggedBytes = 1024 * sizeof(uint2);
+constexpr size_t kScratchBytes = kStreamPartialBytes + kRouterTaggedBytes + kMergeScratchFloats * sizeof(float);
 
 int32_t fail(zc_ctx* ctx, int32_t code, const char* fmt, ...) {
     if (ctx) {
@@ -231,17 +233,17 @@ int32_t zc_init(int32_t device, zc_ctx** out_ctx) {
     }
     memset(ctx->status_host, 0, 256);
     ctx->sm_count = prop.multiProcessorCount;
-    if (cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_partial),
-                   kStreamPartialBytes + 256 + kMergeScratchFloats * sizeof(float)) != cudaSuccess ||
-        cudaMemset(ctx->scratch_partial, 0, kStreamPartialBytes + 256) != cudaSuccess) {
+    if (cudaMalloc(reinterpret_cast<void**>(&ctx->scratch_partial), kScratchBytes) != cudaSuccess ||
+        cudaMemset(ctx->scratch_partial, 0, kScratchBytes) != cudaSuccess) {
         if (ctx->scratch_partial) cudaFree(ctx->scratch_partial);
         cudaFreeHost(ctx->status_host);
         cudaStreamDestroy(ctx->own_stream);
         delete ctx;
         return ZC_ERR_OOM;
     }
-    ctx->router_counter = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(ctx->scratch_partial) + kStreamPartialBytes);
-    ctx->merge_scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ctx->scratch_partial) + kStreamPartialBytes + 256);
+    ctx->router_tagged = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(ctx->scratch_partial) + kStreamPartialBytes);
+    ctx->merge_scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ctx->scratch_partial) + kStreamPartialBytes +
+                                                  kRouterTaggedBytes);
     *out_ctx = ctx;
     return ZC_OK;
 }
@@ -453,7 +455,7 @@ int32_t zc_submit_and_wait(zc_ctx* ctx) {
         // A wait gave up. Tagged partial sums may be left behind and would be taken for fresh ones by the next
         // streaming matvec: clear them. A peer exchange that gave up leaves the ranks' epochs out
         // of step: the communicator refuses further collectives until it is destroyed and set up again.
-        cudaMemsetAsync(ctx->scratch_partial, 0, kStreamPartialBytes + 256, ctx->stream);
+        cudaMemsetAsync(ctx->scratch_partial, 0, kStreamPartialBytes + kRouterTaggedBytes, ctx->stream);
         cudaStreamSynchronize(ctx->stream);
         if (where >= 200 && ctx->comm_local) ctx->comm_broken = true;
         return fail(ctx, ZC_ERR_TIMEOUT, "device-side wait gave up (code %u, site %u)", code, where);
@@ -1078,7 +1080,8 @@ int32_t zc_moe_router_topk(zc_ctx* ctx, const void* hidden, uint64_t hidden_size
     const cudaError_t e = launch_moe_router_topk(
         f32p(hidden, 0), norm_weights ? f32p(norm_weights, 0) : nullptr, f32p(router_weights, 0),
         static_cast<const float*>(bias), norm_out ? f32m(norm_out, 0) : nullptr, f32m(logits, 0),
-        static_cast<uint32_t*>(routing), static_cast<uint32_t*>(routing_local), ctx->router_counter, n_experts, K, k,
+        static_cast<uint32_t*>(routing), static_cast<uint32_t*>(routing_local), ctx->router_tagged, ctx->status_dev,
+        ctx->wait_limit ? ctx->wait_limit : (1u << 26), n_experts, K, k,
         rule, shared_slot, e_lo, e_hi, local_shared, eps, ctx->stream, &ctx->launches);
     if (e != cudaSuccess) return cuda_fail(ctx, e, fn);
     ctx->router_mark = ctx->launches;

@@ -217,10 +217,11 @@ cudaError_t launch_rms_norm_dmmv_f32(const float* x, const float* norm_w, const 
 // Expert parallelism: routing rows [k ids][k weights] -> ids of the experts [lo, hi) renumbered from 0, the others
 // replaced by the "no expert" mark (kernels read no weights for such a slot and contribute zeros).
 // Router matvec (optionally behind the RMS norm) + expert selection in one launch, for up to 1024 experts
-// (cudaErrorNotSupported beyond, or when K is not a multiple of 4). `counter`: one zeroed word of context scratch.
+// (cudaErrorNotSupported beyond, or when K is not a multiple of 4). `tagged`: 1024 zeroed uint2 of context scratch
+// (zero again when the kernel ends); `status` / `spin_limit`: where and after how many polls a wait gives up.
 cudaError_t launch_moe_router_topk(const float* x, const float* norm_w, const float* W, const float* bias,
                                    float* norm_out, float* logits, uint32_t* routing, uint32_t* routing_local,
-                                   uint32_t* counter, uint32_t n_experts, uint32_t K, uint32_t k, uint32_t rule,
+                                   uint2* tagged, uint32_t* status, uint32_t spin_limit, uint32_t n_experts, uint32_t K, uint32_t k, uint32_t rule,
                                    uint32_t shared, uint32_t e_lo, uint32_t e_hi, uint32_t local_shared, float eps,
                                    cudaStream_t s, uint64_t* launches);
 // x[n_heads * head_dim] merged from split-K attention partials (the stand-alone form of MergeArgs).

@@ -145,19 +145,38 @@ __global__ void __launch_bounds__(kTopkThreads) softmax_topk_kernel(
 // One warp selects for one token: lane l holds experts l, l + 32, ... in registers. Ids go to o[0..k), weights (f32 bits) to o[wofs .. wofs + k): wofs = k is the
 // reference's layout, a larger wofs leaves room for slots behind the selected ones. The logits are read past
 // L1 (they may have been written by other CTAs of the same launch).
-template <int VPL>
-__device__ __forceinline__ void softmax_topk_warp(const float* lg, const float* __restrict__ bias, uint32_t* o,
+// Where the selection takes its logits from, in two steps so that all of a lane's reads are in flight before any
+// of them is waited for: first(i) issues the read, value(i, q) completes it.
+struct LogitsPlain {  // logits in global memory, read past L1
+    const float* lg;
+    __device__ __forceinline__ uint2 first(uint32_t i) const { return make_uint2(__float_as_uint(__ldcg(lg + i)), 1u); }
+    __device__ __forceinline__ float value(uint32_t, uint2 q) const { return __uint_as_float(q.x); }
+};
+
+template <int VPL, typename Load>
+__device__ __forceinline__ void softmax_topk_warp(const Load& load, const float* __restrict__ bias, uint32_t* o,
                                                   uint32_t n, uint32_t k, uint32_t rule, uint32_t wofs, int lane,
                                                   uint32_t* my_id = nullptr, uint32_t* my_w = nullptr) {
     const float floor_v = rule == 0u ? -1.0f : -INFINITY;
     const float gone = rule == 0u ? -2.0f : -INFINITY;  // never selected (again)
 
     float v[VPL];
+    uint2 raw[VPL];
     float lmax = -INFINITY;
 #pragma unroll
     for (int j = 0; j < VPL; ++j) {
         const uint32_t i = lane + 32 * j;
-        v[j] = i < n ? __ldcg(lg + i) + (bias ? bias[i] : 0.0f) : -INFINITY;
+        raw[j] = i < n ? load.first(i) : make_uint2(0xFF800000u, 1u);
+    }
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        const uint32_t i = lane + 32 * j;
+        v[j] = i < n ? load.value(i, raw[j]) : -INFINITY;
+    }
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+        const uint32_t i = lane + 32 * j;
+        if (bias && i < n) v[j] += bias[i];
         lmax = fmaxf(lmax, v[j]);
     }
     if (rule == 0u) {  // softmax over all experts first
@@ -263,8 +282,8 @@ __global__ void __launch_bounds__(128) softmax_topk_warp_kernel(
     const int lane = threadIdx.x & 31;
     const uint32_t tok = blockIdx.x * 4 + (threadIdx.x >> 5);
     if (tok >= n_tokens) return;
-    softmax_topk_warp<VPL>(logits + (size_t)tok * logits_stride, bias, out + (size_t)tok * out_stride, n, k, rule, k,
-                           lane);
+    softmax_topk_warp<VPL>(LogitsPlain{logits + (size_t)tok * logits_stride}, bias, out + (size_t)tok * out_stride, n, k,
+                           rule, k, lane);
 }
 
 // ---- combine / activation ------------------------------------------------------------
@@ -468,9 +487,9 @@ __global__ void __launch_bounds__(kRouterThreads) rms_norm_dmmv_f32_kernel(
 
 // ---- router matvec + expert selection in one launch ----------------------------------------------
 // The f32 router of one token (optionally behind the RMS norm, as above) and the selection that follows it
-// (src/compute/forward.zig:6139-6190: router DMMV, then softmax_topk): one CTA per router row; the CTA that
-// finishes last (a ticket from an atomic counter, which it puts back to zero) runs the one-warp selection over
-// the logits all CTAs wrote. Behind the k selected slots the routing buffer can carry one more slot for the
+// (src/compute/forward.zig:6139-6190: router DMMV, then softmax_topk): one CTA per router row; every CTA hands
+// its logit to CTA 0 as a tagged 64-bit value, and CTA 0's first warp, once its own row is done, collects them
+// (bounded polls) and runs the one-warp selection. Behind the k selected slots the routing buffer can carry one more slot for the
 // shared expert (id kSharedExpert, weight 1), and a second routing buffer can receive the same selection as an
 // expert-parallel rank sees it: ids in [e_lo, e_hi) renumbered from zero, every other slot marked "no expert
 // here", the shared slot kept only where `local_shared` says so.
@@ -485,7 +504,9 @@ struct RouterArgs {
     float* logits;
     uint32_t* routing;
     uint32_t* routing_local;
-    uint32_t* counter;
+    uint2* tagged;    // [n_experts] {logit bits, 1}: how the rows' CTAs hand their logits to CTA 0 ({0, 0} between launches)
+    uint32_t* status;
+    uint32_t spin_limit;
     uint32_t n_experts, K, k, rule, shared, e_lo, e_hi, local_shared;
     float eps;
 };
@@ -493,7 +514,6 @@ constexpr int kRouterPrefetch = 4;  // float4 per thread held across the depende
 
 __global__ void __launch_bounds__(kRouterThreads) moe_router_topk_kernel(const RouterArgs a) {
     __shared__ float scratch[kRouterThreads / 32];
-    __shared__ uint32_t s_last;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const uint32_t tid = threadIdx.x, row = blockIdx.x;
     const uint32_t K4 = a.K >> 2;
@@ -536,20 +556,40 @@ __global__ void __launch_bounds__(kRouterThreads) moe_router_topk_kernel(const R
     sum = block_sum(sum, scratch);
     if (tid == 0) {
         a.logits[row] = sum;
-        __threadfence();
-        s_last = atomicAdd(a.counter, 1u) == gridDim.x - 1 ? 1u : 0u;
+        a.tagged[row] = make_uint2(__float_as_uint(sum), 1u);  // value and tag in one 64-bit store: no fence, no flag
     }
-    __syncthreads();
-    if (!s_last || tid >= 32) return;
-    // ---- the last CTA's first warp: every logit is in global memory ----
-    __threadfence();
-    if (tid == 0) *a.counter = 0u;
+    if (row != 0 || tid >= 32) return;
+    // ---- CTA 0's first warp collects every row's logit (bounded polls; the tags are cleared for the next launch)
+    // and runs the selection ----
     const uint32_t n = a.n_experts, k = a.k, slots = k + a.shared;
     uint32_t* o = a.routing;
     uint32_t id = 0u, wt = 0u;  // lane j's selection (k <= 32)
-    if (n <= 32) softmax_topk_warp<1>(a.logits, a.bias, o, n, k, a.rule, slots, (int)tid, &id, &wt);
-    else if (n <= 256) softmax_topk_warp<8>(a.logits, a.bias, o, n, k, a.rule, slots, (int)tid, &id, &wt);
-    else softmax_topk_warp<32>(a.logits, a.bias, o, n, k, a.rule, slots, (int)tid, &id, &wt);
+    struct LogitsTagged {
+        const RouterArgs& a;
+        __device__ __forceinline__ uint2 first(uint32_t i) const {
+            uint2 q;
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(q.x), "=r"(q.y) : "l"(a.tagged + i) : "memory");
+            return q;
+        }
+        __device__ __forceinline__ float value(uint32_t i, uint2 q) const {
+            uint2* p = a.tagged + i;
+            uint32_t spins = 0;
+            while (q.y == 0u) {
+                if (++spins > a.spin_limit) {
+                    a.status[0] = 1;
+                    a.status[1] = 500u;
+                    break;
+                }
+                asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(q.x), "=r"(q.y) : "l"(p) : "memory");
+            }
+            *p = make_uint2(0u, 0u);
+            return __uint_as_float(q.x);
+        }
+    };
+    const LogitsTagged load{a};
+    if (n <= 32) softmax_topk_warp<1>(load, a.bias, o, n, k, a.rule, slots, (int)tid, &id, &wt);
+    else if (n <= 256) softmax_topk_warp<8>(load, a.bias, o, n, k, a.rule, slots, (int)tid, &id, &wt);
+    else softmax_topk_warp<32>(load, a.bias, o, n, k, a.rule, slots, (int)tid, &id, &wt);
     if (tid == 0 && a.shared) {
         o[k] = kSharedExpert;
         o[slots + k] = 0x3F800000u;
@@ -690,11 +730,11 @@ cudaError_t launch_softmax_topk(const float* logits, const float* bias, uint32_t
 
 cudaError_t launch_moe_router_topk(const float* x, const float* norm_w, const float* W, const float* bias,
                                    float* norm_out, float* logits, uint32_t* routing, uint32_t* routing_local,
-                                   uint32_t* counter, uint32_t n_experts, uint32_t K, uint32_t k, uint32_t rule,
+                                   uint2* tagged, uint32_t* status, uint32_t spin_limit, uint32_t n_experts, uint32_t K, uint32_t k, uint32_t rule,
                                    uint32_t shared, uint32_t e_lo, uint32_t e_hi, uint32_t local_shared, float eps,
                                    cudaStream_t s, uint64_t* launches) {
     if (n_experts == 0 || n_experts > 1024 || (K & 3u)) return cudaErrorNotSupported;
-    RouterArgs a{x, norm_w, W, bias, norm_out, logits, routing, routing_local, counter,
+    RouterArgs a{x, norm_w, W, bias, norm_out, logits, routing, routing_local, tagged, status, spin_limit,
                  n_experts, K, k, rule, shared, e_lo, e_hi, local_shared, eps};
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_experts, 1, 1);
