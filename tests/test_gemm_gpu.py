@@ -73,6 +73,37 @@ def test_mul_mm(gpu, oracle, t, act, M, N, K):
         assert rel_l2(got[:, :M], oracle.gemm_f64(w, t, M, K, Bexact, round_bf16=True)) <= TOL_BF16_OPERANDS
 
 
+@pytest.mark.parametrize("t", [zb.Q4_K, zb.Q6_K], ids=["q4_k", "q6_k"])
+@pytest.mark.parametrize("M,N,K", [(2043, 2600, 1024), (1280, 4100, 512)])
+def test_mul_mm_cta_pairs(gpu, oracle, t, M, N, K):
+    """Shapes with enough tiles that K is not split and an even number of 128-row tiles: the large-tile kernel runs
+    as CTA pairs (one MMA of 256 rows per pair, each CTA fetching half of every activation box). Ragged last row
+    tile, a last token tile that fills one accumulator only, strided B and D."""
+    torch, ctx, dd = gpu
+    g = synth.rng(304, t * 100 + M)
+    w = synth.quant_matrix(g, t, M, K)
+    Bm = synth.activations(g, N, K)
+    stride_b, stride_d = K + 8, M + 5
+    Bpad = np.zeros((N, stride_b), np.float32)
+    Bpad[:, :K] = Bm
+    bits = synth.to_bf16_bits(Bpad.reshape(-1))
+    Bexact = synth.bf16_bits_to_f32(synth.to_bf16_bits(Bm.reshape(-1))).reshape(N, K)
+    D = out_with_canary(torch, N * stride_d)
+    dd.recordMulMm(t, dev(torch, w), dev(torch, bits.view(np.int16)), D, M, N, K, stride_b, stride_d, 0, 0, 0, zb.BF16)
+    ctx.submit_and_wait()
+    got = D[:N * stride_d].cpu().numpy().reshape(N, stride_d)
+    assert canary_intact(D, N * stride_d)
+    assert np.all(got[:, M:] == 0.0), "padding between columns must stay untouched"
+    exact = oracle.gemm_f64(w, t, M, K, Bexact)
+    assert rel_l2(got[:, :M], exact) <= TOL_BF16
+    assert rel_l2(got[:, :M], oracle.gemm_f64(w, t, M, K, Bexact, round_bf16=True)) <= TOL_BF16_OPERANDS
+    # every row tile against its own rows: a pair that swapped or dropped a half would pass no global norm
+    for r0 in range(0, M, 128):
+        assert rel_l2(got[:, r0:min(r0 + 128, M)], exact[:, r0:r0 + 128]) <= TOL_BF16
+    for c0 in range(0, N, 128):
+        assert rel_l2(got[c0:c0 + 128, :M], exact[c0:c0 + 128]) <= TOL_BF16
+
+
 @pytest.mark.parametrize("M,N,K", [(64, 16, 64), (300, 77, 320), (200, 32, 2880), (256, 300, 2880)])
 def test_mul_mm_mxfp4_bf16(gpu, oracle, M, N, K):
     # MXFP4 weights dequantise exactly to bf16, so with bf16 activations the tensor-core product differs

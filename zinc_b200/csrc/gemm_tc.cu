@@ -26,6 +26,13 @@
 namespace zc {
 namespace {
 
+// CTA pairs for the large-tile kernel: on by default; ZC_GEMM_PAIRS=0 in the environment keeps single CTAs (for
+// comparisons).
+const bool g_pair_mode = [] {
+    const char* e = getenv("ZC_GEMM_PAIRS");
+    return !(e && e[0] == '0');
+}();
+
 struct GemmArgs {
     const uint8_t* A;
     float* D;
@@ -34,7 +41,10 @@ struct GemmArgs {
     uint32_t* status;
 };
 
-template <int TYPE, int BN, int NACC>
+// kPair: clusters of two CTAs (consecutive row tiles) share every MMA (cta_group::2, M = 256): each CTA
+// dequantises its own 128 rows and fetches half of every activation box (tmap_b then has boxes of BN / 2 tokens),
+// so an activation byte crosses from L2 to an SM once per 256 weight rows instead of once per 128.
+template <int TYPE, int BN, int NACC, bool kPair = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_w,
                    const GemmArgs g) {
@@ -42,12 +52,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // swizzle atoms: 1024-byte aligned
     uint8_t* smem_b = smem + Tile<TYPE, BN>::kBOffset;
     uint8_t* smem_w = smem + Tile<TYPE, BN>::kWOffset;
-    constexpr int kBSlots = Tile<TYPE, BN>::kBSlots;
+    // a pair's CTA holds half of every activation box: twice the slots in the same room
+    constexpr int kBSlots = Tile<TYPE, BN>::kBSlots * (kPair ? 2 : 1);
+    constexpr uint32_t kBSlotBytes = Tile<TYPE, BN>::kBBytes / (kPair ? 2 : 1);
+    // With an odd number of slots two issuers take the fills of a slot in turn, and a parity wait only tells the
+    // current phase from the one before it: a thread that waited on a barrier it visits every other phase could
+    // not tell "not filled yet" from "filled twice since". Such a slot has two "full" barriers, used by its even
+    // and odd fills: each is then waited on by one thread only, phase after phase. With an even number of slots
+    // every slot belongs to one issuer.
+    constexpr int kFullSets = (NACC == 2 && kBSlots % 2 == 1) ? 2 : 1;
+    static_assert(kBSlots * kFullSets <= 6, "full_b / empty_b hold six barriers");
     constexpr int kWSlots = Tile<TYPE, BN>::kWSlots;
     constexpr uint32_t kWBytes = Tile<TYPE, BN>::kWBytes;
     Bars* bars = reinterpret_cast<Bars*>(smem + Tile<TYPE, BN>::kBarOffset);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t m0 = blockIdx.x * kBM, n0 = blockIdx.y * (BN * NACC);
+    const uint32_t rank = kPair ? cluster_ctarank() : 0u;  // 0: issues the pair's MMAs and owns the full barriers
     // split-K: CTA z handles blocks [b_begin, b_end) of every row and adds its partial tile into D
     const int nblk_all = g.K >> 8;
     const int b_begin = (int)((long long)blockIdx.z * nblk_all / gridDim.z);
@@ -56,84 +76,145 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     const int it0 = b_begin * 4;
     // accumulators of this tile that hold at least one real token
     const int nacc = min(NACC, (int)((g.N - n0 + BN - 1) / BN));
+    const int n_iss = NACC == 1 ? 1 : nacc;  // issuing threads at work: one per accumulator in use
 
     if (tid == 0) {
         for (int s = 0; s < kAStages; ++s) {
-            mbar_init(&bars->full_a[s], 4);  // one arrival per producer warp of the owning set
-            mbar_init(&bars->empty_a[s], 1);
+            mbar_init(&bars->full_a[s], kPair ? 8 : 4);  // one arrival per producer warp of the owning set (of both CTAs)
+            mbar_init(&bars->empty_a[s], n_iss);  // one commit per issuing thread
         }
-        for (int s = 0; s < kBSlots; ++s) {
-            mbar_init(&bars->full_b[s], 1);
-            mbar_init(&bars->empty_b[s], 1);
-        }
+        for (int s = 0; s < kBSlots; ++s) mbar_init(&bars->empty_b[s], 1);
+        for (int s = 0; s < kBSlots * kFullSets; ++s) mbar_init(&bars->full_b[s], kPair ? 2 : 1);  // one loader per CTA
         for (int s = 0; s < kWSlots; ++s) {
             mbar_init(&bars->full_w[s], 1);
             mbar_init(&bars->empty_w[s], 16);  // one arrival per producer warp
         }
-        mbar_init(&bars->accum, 1);
+        mbar_init(&bars->accum, n_iss);
         bars->failed = 0;
         mbar_fence_init();
     }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                         smem_u32(&bars->tmem_base)),
-                     "r"((uint32_t)(BN * NACC))
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (kPair) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(&bars->tmem_base)),
+                         "r"((uint32_t)(BN * NACC))
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                             smem_u32(&bars->tmem_base)),
+                         "r"((uint32_t)(BN * NACC))
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();  // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
 
-    if (warp == 0) {
-        if (lane == 0) {  // ---- MMA issuer ----
-            constexpr uint32_t idesc = instr_desc<BN>();
-            int sb = 0;
-            uint32_t pb = 0;
+    if (warp == 0 || (NACC == 2 && warp == 2)) {
+        // ---- MMA issuers: one thread per accumulator (an issue costs the thread about as many cycles as the
+        // tensor core needs for half the instruction, waits and commits not counted, so one thread alone
+        // cannot keep two accumulators fed); both read every weight stage, each its own activation slots ----
+        const int w = warp == 0 ? 0 : 1;
+        if (lane == 0 && rank == 0 && w < n_iss) {
+            constexpr uint32_t idesc = kPair ? instr_desc_pair<BN>() : instr_desc<BN>();
+            int sb = w;  // slots are used in the order (iteration, accumulator)
+            uint32_t fill = 0;  // how often the ring has wrapped = the number of this slot's fill
             bool ok = true;
             for (int it = 0; it < n_it && ok; ++it) {
                 const int sa = it & 3;
                 ok = wait_or_fail<false>(&bars->full_a[sa], (it >> 2) & 1, bars, g.status, 101);
                 const uint64_t da = smem_desc(smem_u32(smem + sa * kABytes));
-                for (int acc = 0; acc < nacc && ok; ++acc) {
-                    ok = wait_or_fail<false>(&bars->full_b[sb], pb, bars, g.status, 102);
+                for (int acc = w; acc < nacc && ok; acc += n_iss) {
+                    ok = wait_or_fail<false>(&bars->full_b[sb + kBSlots * (fill & kFullSets - 1)], (fill / kFullSets) & 1, bars,
+                                             g.status, 102);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint64_t db = smem_desc(smem_u32(smem_b + sb * Tile<TYPE, BN>::kBBytes));
+                    const uint64_t db = smem_desc(smem_u32(smem_b + sb * kBSlotBytes));
 #pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k)  // 16 columns = 32 bytes per instruction
-                        umma_bf16(tmem + acc * BN, da + 2 * k, db + 2 * k, idesc, (it | k) ? 1u : 0u);
-                    umma_commit(&bars->empty_b[sb]);
-                    if (++sb == kBSlots) {
-                        sb = 0;
-                        pb ^= 1;
+                    for (int k = 0; k < kBK / 16; ++k) {  // 16 columns = 32 bytes per instruction
+                        if constexpr (kPair) umma_bf16_pair(tmem + acc * BN, da + 2 * k, db + 2 * k, idesc, (it | k) ? 1u : 0u);
+                        else umma_bf16(tmem + acc * BN, da + 2 * k, db + 2 * k, idesc, (it | k) ? 1u : 0u);
+                    }
+                    if constexpr (kPair) umma_commit_pair(&bars->empty_b[sb]);
+                    else umma_commit(&bars->empty_b[sb]);
+                    sb += n_iss;
+                    if (sb >= kBSlots) {
+                        sb -= kBSlots;
+                        ++fill;
                     }
                 }
-                umma_commit(&bars->empty_a[sa]);
+                if (!ok) break;
+                if constexpr (kPair) umma_commit_pair(&bars->empty_a[sa]);
+                else umma_commit(&bars->empty_a[sa]);
             }
-            umma_commit(&bars->accum);
+            if constexpr (kPair) umma_commit_pair(&bars->accum);
+            else umma_commit(&bars->accum);
         }
     } else if (warp == 1) {
-        if (lane == 0) {  // ---- TMA loader of X ----
-            int sb = 0;
-            uint32_t pb = 1;
-            bool ok = true;
-            for (int it = 0; it < n_it && ok; ++it) {
-                for (int acc = 0; acc < nacc; ++acc) {
-                    ok = wait_or_fail(&bars->empty_b[sb], pb, bars, g.status, 103);
-                    if (!ok) break;
-                    mbar_expect_tx(&bars->full_b[sb], Tile<TYPE, BN>::kBBytes);
-                    tma_load_2d(smem_b + sb * Tile<TYPE, BN>::kBBytes, &tmap_b, (it0 + it) * kBK, (int)(n0 + acc * BN),
-                                &bars->full_b[sb]);
+        if (lane == 0) {
+            // ---- TMA loader of X and, with two accumulators (whose second issuer has the third control warp),
+            // of the raw weight blocks too: polls both rings without suspending on either ----
+            int sb = 0, it = 0, acc = 0;
+            uint32_t pb = 1, fill = 0;
+            int sw = 0, b = NACC == 2 ? b_begin : b_end;
+            uint32_t pw = 1, idle = 0;
+            while (it < n_it || b < b_end) {
+                bool moved = false;
+                if (it < n_it && mbar_test_wait(&bars->empty_b[sb], pb)) {
+                    uint64_t* full = &bars->full_b[sb + kBSlots * (fill & kFullSets - 1)];
+                    if constexpr (kPair) {  // this CTA's half of the box, counted on the even CTA's barrier
+                        const uint32_t fb = leader_addr(full);
+                        mbar_expect_tx_cluster(fb, kBSlotBytes);
+                        tma_load_2d_pair(smem_b + sb * kBSlotBytes, &tmap_b, (it0 + it) * kBK,
+                                         (int)(n0 + acc * BN + rank * (BN / 2)), fb);
+                    } else {
+                        mbar_expect_tx(full, kBSlotBytes);
+                        tma_load_2d(smem_b + sb * kBSlotBytes, &tmap_b, (it0 + it) * kBK, (int)(n0 + acc * BN), full);
+                    }
                     if (++sb == kBSlots) {
                         sb = 0;
                         pb ^= 1;
+                        ++fill;
+                    }
+                    if (++acc == nacc) {
+                        acc = 0;
+                        ++it;
+                    }
+                    moved = true;
+                }
+                if (NACC == 2 && b < b_end && mbar_test_wait(&bars->empty_w[sw], pw)) {
+                    mbar_expect_tx(&bars->full_w[sw], kWBytes);
+                    tma_load_2d(smem_w + sw * kWBytes, &tmap_w, (int)((b * Raw<TYPE>::kBlock) & ~15u), (int)m0,
+                                &bars->full_w[sw]);
+                    if (++sw == kWSlots) {
+                        sw = 0;
+                        pw ^= 1;
+                    }
+                    ++b;
+                    moved = true;
+                }
+                if (moved) {
+                    idle = 0;
+                } else {  // bounded like every other wait
+                    __nanosleep(32);
+                    ++idle;
+                    if ((idle & 63u) == 63u && bars->failed) break;
+                    if (idle >= kWaitLimit) {
+                        bars->failed = 1;
+                        if (g.status) {
+                            g.status[0] = 1;
+                            g.status[1] = 103;
+                        }
+                        break;
                     }
                 }
             }
         }
-    } else if (warp == 2) {
+    } else if (NACC == 1 && warp == 2) {
         if (lane == 0) {  // ---- TMA loader of the raw weight blocks ----
             int sw = 0;
             uint32_t pw = 1;
@@ -150,7 +231,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
         }
     } else {
         // ---- dequant producers: thread = one row; set j owns group j of every block = weight stage j ----
-        const int p = tid - kCtlWarps * 32;
+        const int p = tid - kCtlWarps * 32;  // with three control warps the quarters come in the order 3, 0, 1, 2
         const int row = p & 127, j = p >> 7;
         uint8_t* a_stage = smem + j * kABytes;
         int sw = 0;
@@ -187,10 +268,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->full_a[j]);
+            if (lane == 0) {
+                if constexpr (kPair) mbar_arrive_cluster(leader_addr(&bars->full_a[j]));
+                else mbar_arrive(&bars->full_a[j]);
+            }
         }
-        // ---- epilogue: warps 3..6, TMEM lane quarter = warp % 4 ----
-        if (warp < 7) {
+        // ---- epilogue: the first four producer warps, TMEM lane quarter = warp % 4 ----
+        if (warp < kCtlWarps + 4) {
             if (wait_or_fail(&bars->accum, 0, bars, g.status, 105)) {
                 __syncwarp();
                 tc_fence_after();
@@ -231,10 +315,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     }
     tc_fence_before();
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();  // the peer's MMAs read this CTA's stages, its commits arrive here
     if (warp == 0) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(BN * NACC))
-                     : "memory");
+        if constexpr (kPair)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(BN * NACC))
+                         : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(BN * NACC))
+                         : "memory");
     }
 }
 
@@ -417,7 +506,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
     }
 }
 
-template <int TYPE, int BN, int NACC>
+template <int TYPE, int BN, int NACC, bool kPair = false>
 cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N, uint32_t K,
                         uint32_t stride_b, uint32_t stride_d, uint32_t* status, cudaStream_t s) {
     EncodeFn enc = encode_fn();
@@ -425,7 +514,7 @@ cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, u
     CUtensorMap map;
     const cuuint64_t dims[2] = {K, N};
     const cuuint64_t strides[1] = {(cuuint64_t)stride_b * 2};
-    const cuuint32_t box[2] = {kBK, BN};
+    const cuuint32_t box[2] = {kBK, kPair ? BN / 2 : BN};  // a pair's CTAs fetch half a box each
     const cuuint32_t estr[2] = {1, 1};
     if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(B), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -441,7 +530,7 @@ cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, u
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    auto kern = gemm_tc_kernel<TYPE, BN, NACC>;
+    auto kern = gemm_tc_kernel<TYPE, BN, NACC, kPair>;
     static std::atomic<uint64_t> attr_done{0};  // per device ordinal
     if (cudaError_t ea = ensure_dynamic_smem(kern, (int)Tile<TYPE, BN>::kSmemBytes, attr_done); ea != cudaSuccess) return ea;
     GemmArgs g{A, D, M, N, K, stride_d, status};
@@ -455,10 +544,28 @@ cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, u
     uint32_t splits = tiles ? (uint32_t)sms / tiles : 1;
     splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
     while (splits > 1 && (K >> 8) / splits < 4) --splits;
+    // pairs: an even number of row tiles (nothing has been launched or written yet); the CTAs of a pair have
+    // the same K range
+    if (kPair && (grid.x & 1u)) return cudaErrorNotSupported;
     if (splits > 1) {
         cudaError_t e = cudaMemset2DAsync(D, (size_t)stride_d * 4, 0, (size_t)M * 4, N, s);
         if (e != cudaSuccess) return e;
         grid.z = splits;
+    }
+    if constexpr (kPair) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kThreads, 1, 1);
+        cfg.dynamicSmemBytes = Tile<TYPE, BN>::kSmemBytes;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        return cudaLaunchKernelEx(&cfg, kern, map, wmap, g);
     }
     kern<<<grid, kThreads, Tile<TYPE, BN>::kSmemBytes, s>>>(map, wmap, g);
     return cudaGetLastError();
@@ -505,6 +612,11 @@ cudaError_t launch_typed(const uint8_t* A, const void* B, float* D, uint32_t M, 
         return launch_tile<TYPE, 128, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
     }
     if (N <= 256) return launch_tile<TYPE, 256, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
+    // CTA pairs (half the activation traffic per SM) where the row tiles pair up
+    if (g_pair_mode && (((M + kBM - 1) / kBM) & 1u) == 0) {
+        const cudaError_t e = launch_tile<TYPE, 256, 2, true>(A, B, D, M, N, K, stride_b, stride_d, status, s);
+        if (e != cudaErrorNotSupported) return e;
+    }
     return launch_tile<TYPE, 256, 2>(A, B, D, M, N, K, stride_b, stride_d, status, s);
 }
 

@@ -36,6 +36,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
+// one poll that never suspends the thread: for a thread that serves several rings
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Iteration limit of every mbarrier wait: a waiter that reaches it records an error status and leaves
 // its loop instead of spinning forever (each failed try_wait already suspends for a while).
 constexpr uint32_t kWaitLimit = 1u << 22;

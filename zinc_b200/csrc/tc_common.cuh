@@ -17,6 +17,8 @@ namespace {
 constexpr int kBM = 128;      // weight rows per tile (= TMEM lanes)
 constexpr int kBK = 64;       // columns per stage: 128 bytes of bf16, one swizzle row
 constexpr int kAStages = 4;   // one per 64-column group of a 256-column block
+// control warps ahead of the 16 dequant warps. One accumulator: MMA issuer, activation loader, raw-weight loader.
+// Two: the first accumulator's issuer, one loader for both rings, the second accumulator's issuer.
 constexpr int kCtlWarps = 3;
 constexpr int kThreads = kCtlWarps * 32 + 4 * 128;
 constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB
@@ -90,6 +92,61 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
+}
+
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster share one MMA of M = 256 --------------------------------
+// Each CTA holds its own 128 weight rows (A) and half of the activation tile's tokens (B); the even CTA of the
+// pair issues the MMAs and owns the "full" barriers, on which the odd CTA's producers and copies arrive through
+// the cluster's shared window; a commit arrives on the barrier at the same offset in both CTAs. No copy is
+// multicast: every CTA fetches what it holds itself.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address of `p` in the pair's even CTA, in the cluster's shared window
+__device__ __forceinline__ uint32_t leader_addr(const void* p) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(r) : "r"(smem_u32(p)));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t cluster_bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_bar), "r"(bytes)
+                 : "memory");
+}
+// TMA tile into this CTA's shared memory, completion counted on a barrier of the pair's even CTA
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, int x, int y, uint32_t cluster_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(cluster_bar)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// arrives on the barrier at this offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                     smem_u32(bar)),
+                 "h"((uint16_t)3)
+                 : "memory");
+}
+// Instruction descriptor of the pair's MMA: as instr_desc, M = 256.
+template <int BN>
+__host__ __device__ constexpr uint32_t instr_desc_pair() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
 // Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
