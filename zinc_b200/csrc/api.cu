@@ -29,6 +29,7 @@ struct zc_ctx {
     uint2* router_tagged = nullptr;      // 1024 tagged logits of the fused router + selection kernel (zero between launches)
     uint64_t router_mark = 0;            // value of `launches` right after that kernel's last launch (0: never)
     float* merge_scratch = nullptr;      // kMergeScratchFloats f32: a merged attention vector on its way to a matvec
+    uint32_t* gemm_flags = nullptr;      // kGemmTileFlags words: tiles of a prefill GEMM that are summed through memory
     int sm_count = 0;
     // tensor-parallel peer exchange (zc_comm_*)
     zc::CommArgs comm;
@@ -50,7 +51,9 @@ using namespace zc;
 
 constexpr uint32_t kMergeScratchFloats = 16384;
 constexpr size_t kRouterTaggedBytes = 1024 * sizeof(uint2);
-constexpr size_t kScratchBytes = kStreamPartialBytes + kRouterTaggedBytes + kMergeScratchFloats * sizeof(float);
+constexpr uint32_t kGemmTileFlags = 32768;  // two per 256 x 512 tile of a prefill GEMM split over CTA pairs
+constexpr size_t kScratchBytes =
+    kStreamPartialBytes + kRouterTaggedBytes + kMergeScratchFloats * sizeof(float) + kGemmTileFlags * sizeof(uint32_t);
 
 int32_t fail(zc_ctx* ctx, int32_t code, const char* fmt, ...) {
     if (ctx) {
@@ -244,6 +247,7 @@ int32_t zc_init(int32_t device, zc_ctx** out_ctx) {
     ctx->router_tagged = reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(ctx->scratch_partial) + kStreamPartialBytes);
     ctx->merge_scratch = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ctx->scratch_partial) + kStreamPartialBytes +
                                                   kRouterTaggedBytes);
+    ctx->gemm_flags = reinterpret_cast<uint32_t*>(ctx->merge_scratch + kMergeScratchFloats);
     *out_ctx = ctx;
     return ZC_OK;
 }
@@ -786,7 +790,7 @@ int32_t zc_dmmv_batch(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size
     // (Y[c][M] is D column-major with stride M, X[c][K] is B with stride K).
     if (num_cols >= 16)
         e = launch_mul_mm(type, u8(A, a_offset), f32p(X, x_offset), f32m(Y, y_offset), M, num_cols, K, K, M, false,
-                          ctx->status_dev, ctx->stream, &ctx->launches);
+                          ctx->status_dev, ctx->gemm_flags, kGemmTileFlags, ctx->stream, &ctx->launches);
     else
         e = cudaErrorNotSupported;
     if (e == cudaErrorNotSupported)
@@ -810,7 +814,8 @@ int32_t zc_mul_mm(zc_ctx* ctx, uint32_t type, const void* A, uint64_t a_size, co
     ZC_TRY(check_vec(ctx, fn, "D", D, d_size, d_offset * 4, ((uint64_t)(N - 1) * stride_d + M) * 4, 4));
     const void* Bp = static_cast<const uint8_t*>(B) + b_offset * esz;
     cudaError_t e = launch_mul_mm(type, u8(A, a_offset), Bp, f32m(D, d_offset * 4), M, N, K, stride_b, stride_d,
-                                  act_type == ZC_BF16, ctx->status_dev, ctx->stream, &ctx->launches);
+                                  act_type == ZC_BF16, ctx->status_dev, ctx->gemm_flags, kGemmTileFlags, ctx->stream,
+                                  &ctx->launches);
     // layouts a tensor map cannot describe (MXFP4; Q6_K rows without a 16-byte pitch): still tensor cores
     if (e == cudaErrorNotSupported && act_type == ZC_BF16 &&
         mul_mm_cp_async_eligible(type, u8(A, a_offset), Bp, N, K, stride_b))

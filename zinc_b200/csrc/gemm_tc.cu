@@ -5,14 +5,18 @@
 //   X  bf16 activations [N][stride_b], fetched by TMA (cp.async.bulk.tensor, 128-byte swizzle)
 //   D  f32 [N][stride_d]; accumulators live in tensor memory and are read back with tcgen05.ld
 //
-// One CTA computes a 128-row x (NACC x BN)-token tile: a dequantised weight stage is used for
-// NACC accumulators of BN tokens each, so with 512 tokens per tile every weight is unpacked once
-// per 512 tokens and tensor memory is fully used. Warp roles (19 warps):
-//   warp 0       allocates tensor memory; lane 0 issues tcgen05.mma and the commits
-//   warp 1       lane 0 issues the TMA loads of X
-//   warp 2       lane 0 issues the TMA loads of the raw weight blocks (one 256-column block of 128 rows per box)
+// Three kernels. More than 256 tokens: gemm_tc_pair_kernel, persistent CTA pairs (cta_group::2, one MMA of 256
+// rows x 256 tokens per pair and accumulator, K streamed over the pairs). Up to 256 tokens (and the few shapes the
+// pair kernel leaves): gemm_tc_kernel, one CTA per 128-row x (NACC x BN)-token tile. At most 128 tokens of Q4_K:
+// gemm_tc_small_kernel, tokens on the MMA's M side. In all of them a dequantised weight stage is used for every
+// accumulator of the tile, so with 512 tokens per tile every weight is unpacked once per 512 tokens and tensor
+// memory is fully used. Warp roles of the first two (19 warps):
+//   warp 0       allocates tensor memory; lane 0 issues the tcgen05.mma and commits of accumulator 0
+//   warp 1       lane 0 issues the TMA loads of X; with two accumulators also those of the raw weight blocks
+//   warp 2       one accumulator: lane 0 issues the TMA loads of the raw weight blocks (one 256-column block of
+//                128 rows per box); two accumulators: lane 0 issues the MMAs and commits of accumulator 1
 //   warps 3-18   dequantise: set j (4 warps, one thread per row) owns 64-column group j of every
-//                256-column block, i.e. stage j of the bf16 weight ring; warps 3-6 also run the epilogue
+//                256-column block, i.e. stage j of the bf16 weight ring; all of them also run the epilogue
 // Rings: 3 raw-block slots of 18 KB (Q4_K) or 2 of 30 KB (Q6_K), 4 bf16 weight stages of 16 KB, 3 (BN = 256) or 6 (BN = 128)
 // activation slots of BN x 64 bf16. Every wait on an mbarrier
 // is bounded; a wait that gives up records {1, site} in the status words, raises a CTA-wide flag
@@ -26,8 +30,8 @@
 namespace zc {
 namespace {
 
-// CTA pairs for the large-tile kernel: on by default; ZC_GEMM_PAIRS=0 in the environment keeps single CTAs (for
-// comparisons).
+// The persistent CTA-pair kernel takes launches of more than 256 tokens; ZC_GEMM_PAIRS=0 in the environment keeps
+// them on the one-CTA-per-tile kernel (for comparisons).
 const bool g_pair_mode = [] {
     const char* e = getenv("ZC_GEMM_PAIRS");
     return !(e && e[0] == '0');
@@ -41,10 +45,7 @@ struct GemmArgs {
     uint32_t* status;
 };
 
-// kPair: clusters of two CTAs (consecutive row tiles) share every MMA (cta_group::2, M = 256): each CTA
-// dequantises its own 128 rows and fetches half of every activation box (tmap_b then has boxes of BN / 2 tokens),
-// so an activation byte crosses from L2 to an SM once per 256 weight rows instead of once per 128.
-template <int TYPE, int BN, int NACC, bool kPair = false>
+template <int TYPE, int BN, int NACC>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_w,
                    const GemmArgs g) {
@@ -52,9 +53,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // swizzle atoms: 1024-byte aligned
     uint8_t* smem_b = smem + Tile<TYPE, BN>::kBOffset;
     uint8_t* smem_w = smem + Tile<TYPE, BN>::kWOffset;
-    // a pair's CTA holds half of every activation box: twice the slots in the same room
-    constexpr int kBSlots = Tile<TYPE, BN>::kBSlots * (kPair ? 2 : 1);
-    constexpr uint32_t kBSlotBytes = Tile<TYPE, BN>::kBBytes / (kPair ? 2 : 1);
+    constexpr int kBSlots = Tile<TYPE, BN>::kBSlots;
+    constexpr uint32_t kBSlotBytes = Tile<TYPE, BN>::kBBytes;
     // With an odd number of slots two issuers take the fills of a slot in turn, and a parity wait only tells the
     // current phase from the one before it: a thread that waited on a barrier it visits every other phase could
     // not tell "not filled yet" from "filled twice since". Such a slot has two "full" barriers, used by its even
@@ -67,7 +67,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     Bars* bars = reinterpret_cast<Bars*>(smem + Tile<TYPE, BN>::kBarOffset);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t m0 = blockIdx.x * kBM, n0 = blockIdx.y * (BN * NACC);
-    const uint32_t rank = kPair ? cluster_ctarank() : 0u;  // 0: issues the pair's MMAs and owns the full barriers
     // split-K: CTA z handles blocks [b_begin, b_end) of every row and adds its partial tile into D
     const int nblk_all = g.K >> 8;
     const int b_begin = (int)((long long)blockIdx.z * nblk_all / gridDim.z);
@@ -80,11 +79,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
 
     if (tid == 0) {
         for (int s = 0; s < kAStages; ++s) {
-            mbar_init(&bars->full_a[s], kPair ? 8 : 4);  // one arrival per producer warp of the owning set (of both CTAs)
+            mbar_init(&bars->full_a[s], 4);  // one arrival per producer warp of the owning set
             mbar_init(&bars->empty_a[s], n_iss);  // one commit per issuing thread
         }
         for (int s = 0; s < kBSlots; ++s) mbar_init(&bars->empty_b[s], 1);
-        for (int s = 0; s < kBSlots * kFullSets; ++s) mbar_init(&bars->full_b[s], kPair ? 2 : 1);  // one loader per CTA
+        for (int s = 0; s < kBSlots * kFullSets; ++s) mbar_init(&bars->full_b[s], 1);
         for (int s = 0; s < kWSlots; ++s) {
             mbar_init(&bars->full_w[s], 1);
             mbar_init(&bars->empty_w[s], 16);  // one arrival per producer warp
@@ -94,23 +93,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
         mbar_fence_init();
     }
     if (warp == 0) {
-        if constexpr (kPair) {
-            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                             smem_u32(&bars->tmem_base)),
-                         "r"((uint32_t)(BN * NACC))
-                         : "memory");
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-        } else {
-            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
-                             smem_u32(&bars->tmem_base)),
-                         "r"((uint32_t)(BN * NACC))
-                         : "memory");
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-        }
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         smem_u32(&bars->tmem_base)),
+                     "r"((uint32_t)(BN * NACC))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
-    if constexpr (kPair) cluster_sync_all();  // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem = bars->tmem_base;
 
@@ -119,8 +109,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
         // tensor core needs for half the instruction, waits and commits not counted, so one thread alone
         // cannot keep two accumulators fed); both read every weight stage, each its own activation slots ----
         const int w = warp == 0 ? 0 : 1;
-        if (lane == 0 && rank == 0 && w < n_iss) {
-            constexpr uint32_t idesc = kPair ? instr_desc_pair<BN>() : instr_desc<BN>();
+        if (lane == 0 && w < n_iss) {
+            constexpr uint32_t idesc = instr_desc<BN>();
             int sb = w;  // slots are used in the order (iteration, accumulator)
             uint32_t fill = 0;  // how often the ring has wrapped = the number of this slot's fill
             bool ok = true;
@@ -135,12 +125,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                     tc_fence_after();
                     const uint64_t db = smem_desc(smem_u32(smem_b + sb * kBSlotBytes));
 #pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k) {  // 16 columns = 32 bytes per instruction
-                        if constexpr (kPair) umma_bf16_pair(tmem + acc * BN, da + 2 * k, db + 2 * k, idesc, (it | k) ? 1u : 0u);
-                        else umma_bf16(tmem + acc * BN, da + 2 * k, db + 2 * k, idesc, (it | k) ? 1u : 0u);
-                    }
-                    if constexpr (kPair) umma_commit_pair(&bars->empty_b[sb]);
-                    else umma_commit(&bars->empty_b[sb]);
+                    for (int k = 0; k < kBK / 16; ++k)  // 16 columns = 32 bytes per instruction
+                        umma_bf16(tmem + acc * BN, da + 2 * k, db + 2 * k, idesc, (it | k) ? 1u : 0u);
+                    umma_commit(&bars->empty_b[sb]);
                     sb += n_iss;
                     if (sb >= kBSlots) {
                         sb -= kBSlots;
@@ -148,11 +135,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                     }
                 }
                 if (!ok) break;
-                if constexpr (kPair) umma_commit_pair(&bars->empty_a[sa]);
-                else umma_commit(&bars->empty_a[sa]);
+                umma_commit(&bars->empty_a[sa]);
             }
-            if constexpr (kPair) umma_commit_pair(&bars->accum);
-            else umma_commit(&bars->accum);
+            umma_commit(&bars->accum);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -166,15 +151,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
                 bool moved = false;
                 if (it < n_it && mbar_test_wait(&bars->empty_b[sb], pb)) {
                     uint64_t* full = &bars->full_b[sb + kBSlots * (fill & kFullSets - 1)];
-                    if constexpr (kPair) {  // this CTA's half of the box, counted on the even CTA's barrier
-                        const uint32_t fb = leader_addr(full);
-                        mbar_expect_tx_cluster(fb, kBSlotBytes);
-                        tma_load_2d_pair(smem_b + sb * kBSlotBytes, &tmap_b, (it0 + it) * kBK,
-                                         (int)(n0 + acc * BN + rank * (BN / 2)), fb);
-                    } else {
-                        mbar_expect_tx(full, kBSlotBytes);
-                        tma_load_2d(smem_b + sb * kBSlotBytes, &tmap_b, (it0 + it) * kBK, (int)(n0 + acc * BN), full);
-                    }
+                    mbar_expect_tx(full, kBSlotBytes);
+                    tma_load_2d(smem_b + sb * kBSlotBytes, &tmap_b, (it0 + it) * kBK, (int)(n0 + acc * BN), full);
                     if (++sb == kBSlots) {
                         sb = 0;
                         pb ^= 1;
@@ -268,20 +246,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
             }
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0) {
-                if constexpr (kPair) mbar_arrive_cluster(leader_addr(&bars->full_a[j]));
-                else mbar_arrive(&bars->full_a[j]);
-            }
+            if (lane == 0) mbar_arrive(&bars->full_a[j]);
         }
-        // ---- epilogue: the first four producer warps, TMEM lane quarter = warp % 4 ----
-        if (warp < kCtlWarps + 4) {
+        // ---- epilogue: all sixteen producer warps (the stores take the time: the more in flight the better);
+        // TMEM lane quarter = warp % 4, set j takes the column chunks c = j mod 4 ----
+        {
             if (wait_or_fail(&bars->accum, 0, bars, g.status, 105)) {
                 __syncwarp();
                 tc_fence_after();
                 const uint32_t q = warp & 3;
                 const uint32_t m = m0 + q * 32 + lane;
 #pragma unroll 1
-                for (int c = 0; c < nacc * (BN / 32); ++c) {
+                for (int c = j; c < nacc * (BN / 32); c += 4) {
                     uint32_t v[32];
                     const uint32_t taddr = tmem + ((q * 32u) << 16) + c * 32;
                     asm volatile(
@@ -315,15 +291,343 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant
     }
     tc_fence_before();
     __syncthreads();
-    if constexpr (kPair) cluster_sync_all();  // the peer's MMAs read this CTA's stages, its commits arrive here
     if (warp == 0) {
         tc_fence_after();
-        if constexpr (kPair)
-            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(BN * NACC))
-                         : "memory");
-        else
-            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(BN * NACC))
-                         : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(BN * NACC))
+                     : "memory");
+    }
+}
+
+// ---- CTA pairs, persistent, K streamed over the pairs ------------------------------------------------------
+// Tiles of 256 weight rows (128 per CTA of a pair) x 512 tokens (two accumulators). Their (tile, 256-column
+// block) units, tile-major, are dealt in contiguous ranges to as many pairs as the GPU holds at once, so every
+// pair has the same amount of work whatever the tile count: a pair works through a list of segments (tile, block
+// range), all rings running on across segment boundaries. A tile whose blocks are split over pairs is finished
+// through memory: the pair with the tile's last blocks (always the first segment of its range, so nobody waits
+// long for it) stores its partial sums and raises the tile's flag; the others add theirs once the flag is up.
+struct PairArgs {
+    GemmArgs g;
+    uint32_t* flags;  // [tile][CTA rank]: number of epilogue warps (of 16) of the storing CTA that are done; zero at launch
+    uint32_t n_row_pairs, n_tiles;
+};
+
+struct Segment {
+    uint32_t tile, b0, b1;
+};
+__device__ __forceinline__ bool next_segment(uint32_t& u, uint32_t u1, uint32_t nblk, Segment& sg) {
+    if (u >= u1) return false;
+    sg.tile = u / nblk;
+    sg.b0 = u - sg.tile * nblk;
+    sg.b1 = min(nblk, sg.b0 + (u1 - u));
+    u += sg.b1 - sg.b0;
+    return true;
+}
+
+constexpr uint32_t kFlagSpinLimit = 1u << 21;
+
+template <int TYPE>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_w,
+                    const PairArgs p) {
+    constexpr int BN = 256, NACC = 2;
+    using T = Tile<TYPE, BN>;
+    // A CTA's activation slot holds 256 consecutive tokens, n0 + 256 * rank ..: its first 128 are this CTA's half
+    // of accumulator 0's operand, the other 128 of accumulator 1's, so one copy per 64-column step feeds both.
+    // Accumulator a therefore holds the tokens n0 + 128 a .. (columns 0..127) and n0 + 256 + 128 a .. (128..255).
+    constexpr int kRing = T::kBSlots;
+    constexpr uint32_t kBSlotBytes = T::kBBytes;
+    constexpr int kWSlots = T::kWSlots;
+    constexpr uint32_t kWBytes = T::kWBytes;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* smem_b = smem + T::kBOffset;
+    uint8_t* smem_w = smem + T::kWOffset;
+    Bars* bars = reinterpret_cast<Bars*>(smem + T::kBarOffset);
+    const GemmArgs& g = p.g;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t nblk = g.K >> 8;
+    const uint32_t U = p.n_tiles * nblk, G = gridDim.x >> 1, slot = blockIdx.x >> 1;
+    const uint32_t u_begin = (uint32_t)part_begin(slot, U, G), u_end = (uint32_t)part_begin(slot + 1, U, G);
+    auto tile_m0 = [&](uint32_t tile) { return ((tile % p.n_row_pairs) * 2 + rank) * (uint32_t)kBM; };
+    auto tile_n0 = [&](uint32_t tile) { return (tile / p.n_row_pairs) * (uint32_t)(BN * NACC); };
+    // accumulators with at least one real token
+    auto tile_nacc = [&](uint32_t tile) { return g.N - tile_n0(tile) > (uint32_t)(BN / 2) ? 2 : 1; };
+
+    if (tid == 0) {
+        for (int s = 0; s < kAStages; ++s) {
+            mbar_init(&bars->full_a[s], 8);   // one arrival per producer warp of the owning set, both CTAs
+            mbar_init(&bars->empty_a[s], NACC);  // one commit per issuing thread
+        }
+        for (int s = 0; s < kRing; ++s) {
+            mbar_init(&bars->full_b[s], 2);      // one loader per CTA
+            mbar_init(&bars->empty_b[s], NACC);  // one commit per issuing thread
+        }
+        for (int s = 0; s < kWSlots; ++s) {
+            mbar_init(&bars->full_w[s], 1);
+            mbar_init(&bars->empty_w[s], 16);  // one arrival per producer warp
+        }
+        mbar_init(&bars->accum, NACC);
+        mbar_init(&bars->tmem_free, 32);     // the sixteen epilogue warps of both CTAs
+        bars->failed = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars->tmem_base)),
+                     "r"((uint32_t)(BN * NACC))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers exist before anything arrives on them
+    tc_fence_after();
+    const uint32_t tmem = bars->tmem_base;
+
+    if (warp == 0 || warp == 2) {
+        // ---- MMA issuers (even CTA): one thread per accumulator. A thread whose accumulator lies past the last
+        // token of a tile still takes part in every hand-off (its commits follow no MMA and arrive at once). ----
+        const int w = warp == 0 ? 0 : 1;
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = instr_desc_pair<BN>();
+            uint32_t git = 0, fill = 0, seg_i = 0, u = u_begin;
+            int sb = 0;
+            bool ok = true;
+            Segment sg;
+            while (ok && next_segment(u, u_end, nblk, sg)) {
+                const bool live = w < tile_nacc(sg.tile);
+                if (seg_i > 0) {  // the epilogue has read the previous segment's sums out of tensor memory
+                    ok = wait_or_fail<false>(&bars->tmem_free, (seg_i - 1) & 1, bars, g.status, 109);
+                    if (!ok) break;
+                    tc_fence_after();
+                }
+                const int n_it = (int)(sg.b1 - sg.b0) * 4;
+                for (int it = 0; it < n_it; ++it, ++git) {
+                    const int sa = git & 3;
+                    ok = wait_or_fail<false>(&bars->full_a[sa], (git >> 2) & 1, bars, g.status, 101);
+                    if (!ok) break;
+                    ok = wait_or_fail<false>(&bars->full_b[sb], fill & 1, bars, g.status, 102);
+                    if (!ok) break;
+                    if (live) {
+                        tc_fence_after();
+                        const uint64_t da = smem_desc(smem_u32(smem + sa * kABytes));
+                        const uint64_t db = smem_desc(smem_u32(smem_b + sb * kBSlotBytes + w * (kBSlotBytes / 2)));
+#pragma unroll
+                        for (int k = 0; k < kBK / 16; ++k)
+                            umma_bf16_pair(tmem + w * BN, da + 2 * k, db + 2 * k, idesc, (it | k) ? 1u : 0u);
+                    }
+                    umma_commit_pair(&bars->empty_b[sb]);
+                    if (++sb == kRing) {
+                        sb = 0;
+                        ++fill;
+                    }
+                    umma_commit_pair(&bars->empty_a[sa]);
+                }
+                if (!ok) break;
+                umma_commit_pair(&bars->accum);
+                ++seg_i;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- loader of both rings (each CTA its own half of the activation boxes and its own weight rows):
+            // polls without suspending on either ----
+            uint32_t ub = u_begin, uw = u_begin;
+            Segment sb_seg, sw_seg;
+            bool b_live = next_segment(ub, u_end, nblk, sb_seg), w_live = next_segment(uw, u_end, nblk, sw_seg);
+            uint32_t b_it = 0;                   // 64-column step inside the activation segment
+            uint32_t w_b = w_live ? sw_seg.b0 : 0;
+            // per segment (the divisions stay out of the per-copy path)
+            uint32_t b_n0 = 0, b_k0 = 0, b_nit = 0, w_m0 = 0;
+            auto b_enter = [&]() {
+                b_n0 = tile_n0(sb_seg.tile) + rank * BN;
+                b_k0 = sb_seg.b0 * 4;
+                b_nit = (sb_seg.b1 - sb_seg.b0) * 4;
+            };
+            if (b_live) b_enter();
+            if (w_live) w_m0 = tile_m0(sw_seg.tile);
+            int sbl = 0, sw = 0;
+            uint32_t pbl = 1, pw = 1, idle = 0;
+            while (b_live || w_live) {
+                bool moved = false;
+                if (b_live && mbar_test_wait(&bars->empty_b[sbl], pbl)) {
+                    const uint32_t fb = leader_addr(&bars->full_b[sbl]);
+                    mbar_expect_tx_cluster(fb, kBSlotBytes);
+                    tma_load_2d_pair(smem_b + sbl * kBSlotBytes, &tmap_b, (int)((b_k0 + b_it) * kBK), (int)b_n0, fb);
+                    if (++sbl == kRing) {
+                        sbl = 0;
+                        pbl ^= 1;
+                    }
+                    if (++b_it == b_nit) {
+                        b_it = 0;
+                        b_live = next_segment(ub, u_end, nblk, sb_seg);
+                        if (b_live) b_enter();
+                    }
+                    moved = true;
+                }
+                if (w_live && mbar_test_wait(&bars->empty_w[sw], pw)) {
+                    mbar_expect_tx(&bars->full_w[sw], kWBytes);
+                    tma_load_2d(smem_w + sw * kWBytes, &tmap_w, (int)((w_b * Raw<TYPE>::kBlock) & ~15u),
+                                (int)w_m0, &bars->full_w[sw]);
+                    if (++sw == kWSlots) {
+                        sw = 0;
+                        pw ^= 1;
+                    }
+                    if (++w_b == sw_seg.b1) {
+                        w_live = next_segment(uw, u_end, nblk, sw_seg);
+                        w_b = sw_seg.b0;
+                        if (w_live) w_m0 = tile_m0(sw_seg.tile);
+                    }
+                    moved = true;
+                }
+                if (moved) {
+                    idle = 0;
+                } else {  // bounded like every other wait
+                    __nanosleep(32);
+                    ++idle;
+                    if ((idle & 63u) == 63u && bars->failed) break;
+                    if (idle >= kWaitLimit) {
+                        bars->failed = 1;
+                        if (g.status) {
+                            g.status[0] = 1;
+                            g.status[1] = 103;
+                        }
+                        break;
+                    }
+                }
+            }
+        }
+    } else {
+        // ---- dequant producers: thread = one row; set j owns group j of every block = weight stage j ----
+        const int pi = tid - kCtlWarps * 32;
+        const int row = pi & 127, j = pi >> 7;
+        uint8_t* a_stage = smem + j * kABytes;
+        const uint32_t full_a_leader = leader_addr(&bars->full_a[j]);
+        const uint32_t free_leader = leader_addr(&bars->tmem_free);
+        int sw = 0;
+        uint32_t pw = 0, gb = 0, seg_i = 0, u = u_begin;
+        bool ok = true;
+        Segment sg;
+        while (ok && next_segment(u, u_end, nblk, sg)) {
+            for (uint32_t b = sg.b0; b < sg.b1; ++b, ++gb) {
+                if (!wait_or_fail(&bars->full_w[sw], pw, bars, g.status, 107)) { ok = false; break; }
+                if constexpr (TYPE == T_Q4_K) {
+                    const uint8_t* wp = smem_w + sw * kWBytes + row * 144;  // rows past M arrive as zeros
+                    const uint4 chdr = *reinterpret_cast<const uint4*>(wp);
+                    const uint4 c0 = *reinterpret_cast<const uint4*>(wp + 16 + j * 32);
+                    const uint4 c1 = *reinterpret_cast<const uint4*>(wp + 32 + j * 32);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->empty_w[sw]);
+                    const __half2 dd = *reinterpret_cast<const __half2*>(&chdr.x);
+                    const float d = __low2float(dd), dmin = __high2float(dd);
+                    uint32_t s0, mn0, s1, mn1;
+                    scale_min_k4(2 * j, chdr.y, chdr.z, chdr.w, s0, mn0);
+                    scale_min_k4(2 * j + 1, chdr.y, chdr.z, chdr.w, s1, mn1);
+                    if (!wait_or_fail(&bars->empty_a[j], (gb & 1) ^ 1, bars, g.status, 104)) { ok = false; break; }
+                    dequant_group_q4k(c0, c1, d * (float)s0, dmin * (float)mn0, d * (float)s1, dmin * (float)mn1, a_stage,
+                                      row);
+                } else {
+                    // the block starts (b * 210) & 15 bytes into the box; that offset is even
+                    const uint32_t off = (b * 210u) & 15u;
+                    const uint8_t* wp = smem_w + sw * kWBytes + row * 240 + (off & ~3u);
+                    if (!wait_or_fail(&bars->empty_a[j], (gb & 1) ^ 1, bars, g.status, 104)) { ok = false; break; }
+                    dequant_group_q6k(reinterpret_cast<const uint32_t*>(wp), (off & 2u) * 8u, j, a_stage, row);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->empty_w[sw]);
+                }
+                if (++sw == kWSlots) {
+                    sw = 0;
+                    pw ^= 1;
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(full_a_leader);
+            }
+            if (!ok) break;
+            // ---- epilogue of the segment: all sixteen producer warps (the stores, not the tensor memory reads, take
+            // the time: the more in flight the better). TMEM lane quarter = warp % 4; set j takes the column chunks
+            // c = j mod 4. ----
+            {
+                if (!wait_or_fail(&bars->accum, seg_i & 1, bars, g.status, 105)) { ok = false; break; }
+                __syncwarp();
+                tc_fence_after();
+                const bool store = sg.b1 == nblk;  // the tile's last blocks: plain stores, the others add to them
+                uint32_t* flag = p.flags + 2 * sg.tile + rank;
+                bool go = true;
+                if (!store) {
+                    if (lane == 0) {
+                        uint32_t n = 0;
+                        while (ld_acquire_u32(flag) < 16u) {
+                            __nanosleep(64);
+                            if (++n >= kFlagSpinLimit || ((n & 63u) == 63u && bars->failed)) {
+                                bars->failed = 1;
+                                if (g.status) {
+                                    g.status[0] = 1;
+                                    g.status[1] = 110;
+                                }
+                                go = false;
+                                break;
+                            }
+                        }
+                    }
+                    go = __shfl_sync(0xFFFFFFFFu, go ? 1 : 0, 0) != 0;
+                }
+                const uint32_t q = warp & 3;
+                const uint32_t m = tile_m0(sg.tile) + q * 32 + lane, n0 = tile_n0(sg.tile);
+#pragma unroll 1
+                for (int c = j; c < NACC * (BN / 32); c += 4) {
+                    // columns 32 c .. of tensor memory: accumulator c / 8, its columns 32 (c % 8) ..
+                    const uint32_t col = (uint32_t)(c & 7) * 32u;
+                    const uint32_t nc = n0 + (uint32_t)(c >> 3) * (BN / 2) + col + (col >= (uint32_t)(BN / 2) ? BN / 2 : 0);
+                    if (nc >= g.N) continue;  // no real token (an accumulator nobody fed holds stale sums)
+                    uint32_t v[32];
+                    const uint32_t taddr = tmem + ((q * 32u) << 16) + c * 32;
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+                          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+                          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+                          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+                          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                        : "r"(taddr)
+                        : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (m < g.M && go) {
+#pragma unroll
+                        for (int jj = 0; jj < 32; ++jj) {
+                            const uint32_t n = nc + jj;
+                            if (n < g.N) {
+                                float* dst = g.D + (uint64_t)n * g.stride_d + m;
+                                if (store)
+                                    *dst = __uint_as_float(v[jj]);
+                                else
+                                    atomicAdd(dst, __uint_as_float(v[jj]));
+                            }
+                        }
+                    }
+                }
+                // tensor memory is free for the next segment
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(free_leader);
+                if (store && sg.b0 > 0) {  // others add to this tile: publish the stores
+                    __threadfence();
+                    __syncwarp();
+                    if (lane == 0) atomicAdd(flag, 1u);
+                }
+            }
+            ++seg_i;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's MMAs read this CTA's stages, its commits arrive here
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)(BN * NACC)) : "memory");
     }
 }
 
@@ -445,15 +749,16 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
                 if (lane == 0) mbar_arrive(&bars->full_a[grp]);
             }
         }
-        // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4; a lane is a token, columns are rows ----
-        if (warp < 6) {
+        // ---- epilogue: all sixteen producer warps, TMEM lane quarter = warp % 4, each group of four warps its own
+        // column chunks; a lane is a token, columns are rows ----
+        {
             if (wait_or_fail(&bars->accum, 0, bars, g.status, 115)) {
                 __syncwarp();
                 tc_fence_after();
                 const uint32_t q = warp & 3;
                 const uint32_t n = n0 + q * 32 + lane;
 #pragma unroll 1
-                for (int c = 0; c < kSmRows / 32; ++c) {
+                for (int c = (warp - 2) >> 2; c < kSmRows / 32; c += 4) {
                     uint32_t v[32];
                     const uint32_t taddr = tmem + ((q * 32u) << 16) + c * 32;
                     asm volatile(
@@ -506,7 +811,7 @@ gemm_tc_small_kernel(const __grid_constant__ CUtensorMap tmap_x, const GemmArgs 
     }
 }
 
-template <int TYPE, int BN, int NACC, bool kPair = false>
+template <int TYPE, int BN, int NACC>
 cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N, uint32_t K,
                         uint32_t stride_b, uint32_t stride_d, uint32_t* status, cudaStream_t s) {
     EncodeFn enc = encode_fn();
@@ -514,7 +819,7 @@ cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, u
     CUtensorMap map;
     const cuuint64_t dims[2] = {K, N};
     const cuuint64_t strides[1] = {(cuuint64_t)stride_b * 2};
-    const cuuint32_t box[2] = {kBK, kPair ? BN / 2 : BN};  // a pair's CTAs fetch half a box each
+    const cuuint32_t box[2] = {kBK, BN};
     const cuuint32_t estr[2] = {1, 1};
     if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(B), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -530,7 +835,7 @@ cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, u
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    auto kern = gemm_tc_kernel<TYPE, BN, NACC, kPair>;
+    auto kern = gemm_tc_kernel<TYPE, BN, NACC>;
     static std::atomic<uint64_t> attr_done{0};  // per device ordinal
     if (cudaError_t ea = ensure_dynamic_smem(kern, (int)Tile<TYPE, BN>::kSmemBytes, attr_done); ea != cudaSuccess) return ea;
     GemmArgs g{A, D, M, N, K, stride_d, status};
@@ -544,28 +849,10 @@ cudaError_t launch_tile(const uint8_t* A, const void* B, float* D, uint32_t M, u
     uint32_t splits = tiles ? (uint32_t)sms / tiles : 1;
     splits = splits < 1 ? 1 : (splits > 8 ? 8 : splits);
     while (splits > 1 && (K >> 8) / splits < 4) --splits;
-    // pairs: an even number of row tiles (nothing has been launched or written yet); the CTAs of a pair have
-    // the same K range
-    if (kPair && (grid.x & 1u)) return cudaErrorNotSupported;
     if (splits > 1) {
         cudaError_t e = cudaMemset2DAsync(D, (size_t)stride_d * 4, 0, (size_t)M * 4, N, s);
         if (e != cudaSuccess) return e;
         grid.z = splits;
-    }
-    if constexpr (kPair) {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = grid;
-        cfg.blockDim = dim3(kThreads, 1, 1);
-        cfg.dynamicSmemBytes = Tile<TYPE, BN>::kSmemBytes;
-        cfg.stream = s;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        return cudaLaunchKernelEx(&cfg, kern, map, wmap, g);
     }
     kern<<<grid, kThreads, Tile<TYPE, BN>::kSmemBytes, s>>>(map, wmap, g);
     return cudaGetLastError();
@@ -604,17 +891,89 @@ cudaError_t launch_small(const uint8_t* A, const void* B, float* D, uint32_t M, 
     return cudaGetLastError();
 }
 
+// The persistent pair kernel. cudaErrorNotSupported: the caller takes another path (nothing launched or written).
+template <int TYPE>
+cudaError_t launch_pair(const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N, uint32_t K, uint32_t stride_b,
+                        uint32_t stride_d, uint32_t* status, uint32_t* flags, uint32_t n_flags, cudaStream_t s) {
+    using T = Tile<TYPE, 256>;
+    EncodeFn enc = encode_fn();
+    if (!enc) return cudaErrorNotSupported;
+    PairArgs p{};
+    p.g = GemmArgs{A, D, M, N, K, stride_d, status};
+    p.flags = flags;
+    p.n_row_pairs = (M + 2 * kBM - 1) / (2 * kBM);
+    p.n_tiles = p.n_row_pairs * ((N + 511) / 512);
+    if (!flags || (uint64_t)p.n_tiles * 2 > n_flags) return cudaErrorNotSupported;
+    auto kern = gemm_tc_pair_kernel<TYPE>;
+    static std::atomic<uint64_t> attr_done{0};  // per device ordinal
+    if (cudaError_t ea = ensure_dynamic_smem(kern, (int)T::kSmemBytes, attr_done); ea != cudaSuccess) return ea;
+    cudaLaunchConfig_t cfg = {};
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = T::kSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    // pairs the device holds at once (every pair of the grid must be resident: pairs wait for each other's tiles)
+    static std::atomic<int> max_pairs[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int pairs = dev < 64 ? max_pairs[dev].load(std::memory_order_relaxed) : 0;
+    if (pairs == 0) {
+        cfg.gridDim = dim3(2, 1, 1);
+        if (cudaOccupancyMaxActiveClusters(&pairs, kern, &cfg) != cudaSuccess || pairs < 1) {
+            cudaGetLastError();
+            return cudaErrorNotSupported;
+        }
+        if (dev < 64) max_pairs[dev].store(pairs, std::memory_order_relaxed);
+    }
+    const uint32_t units = p.n_tiles * (K >> 8);
+    uint32_t G = units / 4;  // at least four blocks per pair
+    G = G < 1 ? 1 : (G > (uint32_t)pairs ? (uint32_t)pairs : G);
+    // Nearly as many tiles as pairs: one whole tile per pair (a split tile costs two epilogues and a pass of
+    // atomic adds, more than the idle pairs would win)
+    if (p.n_tiles <= (uint32_t)pairs && p.n_tiles * 5 >= (uint32_t)pairs * 3) G = p.n_tiles;
+    cfg.gridDim = dim3(2 * G, 1, 1);
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {K, N};
+    const cuuint64_t strides[1] = {(cuuint64_t)stride_b * 2};
+    const cuuint32_t box[2] = {kBK, 256};  // a CTA's 256 tokens: half of either accumulator's operand
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(B), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    CUtensorMap wmap;
+    const cuuint64_t row_bytes = (cuuint64_t)(K >> 8) * Raw<TYPE>::kBlock;
+    const cuuint64_t wdims[2] = {row_bytes, M};
+    const cuuint64_t wstrides[1] = {row_bytes};
+    const cuuint32_t wbox[2] = {Raw<TYPE>::kBox, kBM};
+    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(A), wdims, wstrides, wbox, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    if (cudaError_t e = cudaMemsetAsync(flags, 0, (size_t)p.n_tiles * 2 * sizeof(uint32_t), s); e != cudaSuccess) return e;
+    return cudaLaunchKernelEx(&cfg, kern, map, wmap, p);
+}
+
 template <int TYPE>
 cudaError_t launch_typed(const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N, uint32_t K,
-                         uint32_t stride_b, uint32_t stride_d, uint32_t* status, cudaStream_t s) {
+                         uint32_t stride_b, uint32_t stride_d, uint32_t* status, uint32_t* flags, uint32_t n_flags,
+                         cudaStream_t s) {
     if (N <= 128) {
         if constexpr (TYPE == T_Q4_K) return launch_small(A, B, D, M, N, K, stride_b, stride_d, status, s);
         return launch_tile<TYPE, 128, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
     }
     if (N <= 256) return launch_tile<TYPE, 256, 1>(A, B, D, M, N, K, stride_b, stride_d, status, s);
-    // CTA pairs (half the activation traffic per SM) where the row tiles pair up
-    if (g_pair_mode && (((M + kBM - 1) / kBM) & 1u) == 0) {
-        const cudaError_t e = launch_tile<TYPE, 256, 2, true>(A, B, D, M, N, K, stride_b, stride_d, status, s);
+    // CTA pairs (half the activation traffic per SM, K streamed over the pairs) unless the half-empty pair of an
+    // odd number of row tiles would waste more than a seventh of the work
+    const uint32_t row_tiles = (M + kBM - 1) / kBM;
+    if (g_pair_mode && ((row_tiles & 1u) == 0 || row_tiles >= 7)) {
+        const cudaError_t e = launch_pair<TYPE>(A, B, D, M, N, K, stride_b, stride_d, status, flags, n_flags, s);
         if (e != cudaErrorNotSupported) return e;
     }
     return launch_tile<TYPE, 256, 2>(A, B, D, M, N, K, stride_b, stride_d, status, s);
@@ -624,7 +983,7 @@ cudaError_t launch_typed(const uint8_t* A, const void* B, float* D, uint32_t M, 
 
 cudaError_t launch_mul_mm(uint32_t type, const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N,
                           uint32_t K, uint32_t stride_b, uint32_t stride_d, bool act_bf16, uint32_t* status,
-                          cudaStream_t s, uint64_t* launches) {
+                          uint32_t* tile_flags, uint32_t n_tile_flags, cudaStream_t s, uint64_t* launches) {
     if ((type != T_Q4_K && type != T_Q6_K) || !act_bf16 || !status) return cudaErrorNotSupported;
     if ((K & 255u) || (stride_b & 7u) || (reinterpret_cast<uintptr_t>(B) & 15u) ||
         (reinterpret_cast<uintptr_t>(A) & 15u))
@@ -632,8 +991,9 @@ cudaError_t launch_mul_mm(uint32_t type, const uint8_t* A, const void* B, float*
     // Q6_K rows are 210 bytes per block: the TMA row pitch is a multiple of 16 only for K % 2048 == 0
     if (type == T_Q6_K && (K & 2047u)) return cudaErrorNotSupported;
     if (N < 16) return cudaErrorNotSupported;  // a handful of tokens: the matvec-style kernels are the better fit
-    cudaError_t e = type == T_Q4_K ? launch_typed<T_Q4_K>(A, B, D, M, N, K, stride_b, stride_d, status, s)
-                                   : launch_typed<T_Q6_K>(A, B, D, M, N, K, stride_b, stride_d, status, s);
+    cudaError_t e = type == T_Q4_K
+                        ? launch_typed<T_Q4_K>(A, B, D, M, N, K, stride_b, stride_d, status, tile_flags, n_tile_flags, s)
+                        : launch_typed<T_Q6_K>(A, B, D, M, N, K, stride_b, stride_d, status, tile_flags, n_tile_flags, s);
     if (e == cudaSuccess && launches) ++*launches;
     return e;
 }

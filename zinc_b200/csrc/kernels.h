@@ -265,9 +265,10 @@ cudaError_t launch_allgather_oneshot(const CommArgs& c, const float* src, float*
 
 // Tensor-core dequant-GEMM: D[col][row] = sum_k A[row][k] B[col][k].
 // act_bf16: B holds bf16 (else f32). Returns cudaErrorNotSupported for types
-// without a tile dequantiser.
+// without a tile dequantiser. tile_flags: n_tile_flags words of device scratch for the kernel that splits tiles
+// over CTA pairs (two per tile of 256 rows x 512 tokens; shapes that need more take the other kernels).
 cudaError_t launch_mul_mm(uint32_t type, const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N,
                           uint32_t K, uint32_t stride_b, uint32_t stride_d, bool act_bf16, uint32_t* status,
-                          cudaStream_t s, uint64_t* launches);
+                          uint32_t* tile_flags, uint32_t n_tile_flags, cudaStream_t s, uint64_t* launches);
 
 }  // namespace zc

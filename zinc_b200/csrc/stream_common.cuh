@@ -53,6 +53,11 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 // its loop instead of spinning forever (each failed try_wait already suspends for a while).
 constexpr uint32_t kWaitLimit = 1u << 22;
 
+__device__ __forceinline__ uint32_t ld_acquire_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ float ld_cg_f32(const float* p) {
     float v;
     asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p));

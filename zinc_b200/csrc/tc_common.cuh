@@ -66,7 +66,9 @@ struct Bars {
     uint64_t accum;
     uint32_t tmem_base;
     volatile uint32_t failed;
+    uint64_t tmem_free;  // persistent kernel: the epilogue has emptied the accumulators
 };
+static_assert(sizeof(Bars) <= 256, "the tiles reserve 256 bytes for the barrier block");
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
