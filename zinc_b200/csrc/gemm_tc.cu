@@ -575,27 +575,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                 }
                 const uint32_t q = warp & 3;
                 const uint32_t m = tile_m0(sg.tile) + q * 32 + lane, n0 = tile_n0(sg.tile);
-#pragma unroll 1
-                for (int c = j; c < NACC * (BN / 32); c += 4) {
-                    // columns 32 c .. of tensor memory: accumulator c / 8, its columns 32 (c % 8) ..
+                // this warp's chunks j, j + 4 (accumulator 0) and j + 8, j + 12 (accumulator 1), two reads in flight;
+                // columns 32 c .. of tensor memory are accumulator c / 8, its columns 32 (c % 8) ..
+                auto first_token = [&](int c) {
                     const uint32_t col = (uint32_t)(c & 7) * 32u;
-                    const uint32_t nc = n0 + (uint32_t)(c >> 3) * (BN / 2) + col + (col >= (uint32_t)(BN / 2) ? BN / 2 : 0);
-                    if (nc >= g.N) continue;  // no real token (an accumulator nobody fed holds stale sums)
-                    uint32_t v[32];
-                    const uint32_t taddr = tmem + ((q * 32u) << 16) + c * 32;
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
-                          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
-                          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
-                          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
-                          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                        : "r"(taddr)
-                        : "memory");
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (m < g.M && go) {
+                    return n0 + (uint32_t)(c >> 3) * (BN / 2) + col + (col >= (uint32_t)(BN / 2) ? BN / 2 : 0);
+                };
+                auto put = [&](uint32_t nc, const uint32_t (&v)[32]) {
+                    if (m < g.M && go && nc < g.N) {
 #pragma unroll
                         for (int jj = 0; jj < 32; ++jj) {
                             const uint32_t n = nc + jj;
@@ -608,6 +595,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                             }
                         }
                     }
+                };
+#pragma unroll 1
+                for (int c = j; c < NACC * (BN / 32); c += 8) {
+                    const uint32_t na = first_token(c), nb = first_token(c + 4);
+                    if (na >= g.N && nb >= g.N) continue;  // no real token (an accumulator nobody fed holds stale sums)
+                    uint32_t va[32], vb[32];
+                    tmem_ld32(tmem + ((q * 32u) << 16) + c * 32, va);
+                    tmem_ld32(tmem + ((q * 32u) << 16) + (c + 4) * 32, vb);
+                    tmem_ld_wait();
+                    put(na, va);
+                    put(nb, vb);
                 }
                 // tensor memory is free for the next segment
                 tc_fence_before();
