@@ -296,17 +296,40 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_q6k_warp_kernel
         piece[i] = r | ((p - r * kPieces6) << 8);
     }
     uint32_t p_tile = u0 / bpr, p_blk = u0 % bpr;
+    // Rows aligned and a whole number of tiles: a piece's place in the slot and its offset from the tile's first
+    // row are fixed per lane
+    const bool whole_tiles = kRowsAligned && (a.M & 15u) == 0;
+    uint32_t pdst[kPiecesLane6], psrc[kPiecesLane6];
+    if constexpr (kRowsAligned) {
+#pragma unroll
+        for (int i = 0; i < kPiecesLane6; ++i) {
+            const uint32_t r = piece[i] & 0xFFu, col = piece[i] >> 8;
+            pdst[i] = r * kRow6 + col * 16;
+            psrc[i] = r * (uint32_t)row_bytes + col * 16;
+        }
+    }
+    const uint32_t ring_addr = smem_u32(ring);
     auto request = [&](uint32_t slot) {
         uint8_t* dst = ring + slot * kSlot6;
         const uint32_t row0 = p_tile * 16;
         if constexpr (kRowsAligned) {
             const uint32_t al = (p_blk * 210u) & ~15u;  // aligned start of the block's superset within the row
+            if (whole_tiles) {
+                const uint8_t* base = a.A[0] + (uint64_t)row0 * row_bytes + al;
+                const uint32_t room = (uint32_t)row_bytes - al, ds = ring_addr + slot * kSlot6;
 #pragma unroll
-            for (int i = 0; i < kPiecesLane6; ++i) {
-                const uint32_t r = piece[i] & 0xFFu, col = piece[i] >> 8;
-                if (al + col * 16 < (uint32_t)row_bytes) {  // rows are 16-byte aligned: a piece never crosses the row end
-                    const uint32_t row = min(row0 + r, a.M - 1);
-                    cp_async16(dst + r * kRow6 + col * 16, a.A[0] + (uint64_t)row * row_bytes + al + col * 16);
+                for (int i = 0; i < kPiecesLane6; ++i)
+                    if ((piece[i] >> 8) * 16 < room)  // rows are 16-byte aligned: a piece never crosses the row end
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ds + pdst[i]), "l"(base + psrc[i])
+                                     : "memory");
+            } else {
+#pragma unroll
+                for (int i = 0; i < kPiecesLane6; ++i) {
+                    const uint32_t r = piece[i] & 0xFFu, col = piece[i] >> 8;
+                    if (al + col * 16 < (uint32_t)row_bytes) {
+                        const uint32_t row = min(row0 + r, a.M - 1);
+                        cp_async16(dst + r * kRow6 + col * 16, a.A[0] + (uint64_t)row * row_bytes + al + col * 16);
+                    }
                 }
             }
         } else {
