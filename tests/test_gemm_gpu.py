@@ -104,6 +104,40 @@ def test_mul_mm_cta_pairs(gpu, oracle, t, M, N, K):
         assert rel_l2(got[c0:c0 + 128, :M], exact[c0:c0 + 128]) <= TOL_BF16
 
 
+def test_mul_mm_cta_pairs_recorded(gpu, oracle):
+    """The pair kernel inside a recording, replayed: tiles split over pairs are summed behind flags that a memset node
+    of the recording clears, so every replay has to give the product again (a flag left up would let an adder run
+    ahead of the stores it adds to, a flag left down would time out)."""
+    torch, _, _ = gpu
+    t, M, N, K = zb.Q4_K, 512, 700, 2048   # 4 tiles x 8 blocks over 8 pairs: every tile is split
+    g = synth.rng(305, 1)
+    w = synth.quant_matrix(g, t, M, K)
+    Bm = synth.activations(g, N, K)
+    bits = synth.to_bf16_bits(Bm.reshape(-1))
+    Bexact = synth.bf16_bits_to_f32(bits).reshape(N, K)
+    exact = oracle.gemm_f64(w, t, M, K, Bexact)
+    stream = torch.cuda.Stream()   # a stream of its own: the default stream cannot be captured
+    with torch.cuda.stream(stream):
+        ctx = zb.Context(0, stream=stream.cuda_stream)
+        dd = zb.DmmvDispatch(ctx)
+        wd, bd = dev(torch, w), dev(torch, bits.view(np.int16))
+        D = out_with_canary(torch, N * M)
+        stream.synchronize()
+        ctx.begin_record()
+        dd.recordMulMm(t, wd, bd, D, M, N, K, K, M, 0, 0, 0, zb.BF16)
+        rec = ctx.end_record()
+        try:
+            for _ in range(3):
+                D[:N * M] = float("nan")
+                ctx.replay(rec)
+                ctx.submit_and_wait()
+                got = D[:N * M].cpu().numpy().reshape(N, M)
+                assert canary_intact(D, N * M)
+                assert rel_l2(got, exact) <= TOL_BF16
+        finally:
+            ctx.free_recording(rec)
+
+
 @pytest.mark.parametrize("M,N,K", [(64, 16, 64), (300, 77, 320), (200, 32, 2880), (256, 300, 2880)])
 def test_mul_mm_mxfp4_bf16(gpu, oracle, M, N, K):
     # MXFP4 weights dequantise exactly to bf16, so with bf16 activations the tensor-core product differs
