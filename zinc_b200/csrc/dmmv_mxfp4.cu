@@ -155,18 +155,21 @@ __device__ __forceinline__ uint4 lds_u128(uint32_t saddr) {
     return v;
 }
 
-// Four nibbles (bits 0..15 of h) -> four signed bytes 2 * E2M1, in nibble order.
-__device__ __forceinline__ uint32_t e2m1x4_to_s8(uint32_t h) {
-    const uint32_t sel = h & 0x7777u;
-    const uint32_t pos = __byte_perm(0x03020100u, 0x0C080604u, sel);
-    const uint32_t neg = __byte_perm(0xFDFEFF00u, 0xF4F8FAFCu, sel);
-    // byte i = 0xFF when nibble i has bit 3 set: prmt's selector bit 3 replicates the top bit of the byte
-    // it selects (__byte_perm ignores that bit, hence the PTX form)
-    uint32_t mask;
-    asm("prmt.b32 %0, %1, %2, 0xD9C8;" : "=r"(mask) : "r"(h << 4), "r"(h));
-    uint32_t r;
-    asm("lop3.b32 %0, %1, %2, %3, 0xCA;" : "=r"(r) : "r"(mask), "r"(neg), "r"(pos));
-    return r;
+// Eight nibbles of q -> signed bytes 2 * E2M1: lo from nibbles 0..3, hi from nibbles 4..7 (eleven operations for
+// eight weights; the selector of a byte permute is its low 16 bits, so the low half needs no extraction).
+__device__ __forceinline__ void e2m1x8_to_s8(uint32_t q, uint32_t& lo, uint32_t& hi) {
+    const uint32_t sel = q & 0x77777777u, sel_hi = sel >> 16;
+    const uint32_t pos_lo = __byte_perm(0x03020100u, 0x0C080604u, sel);
+    const uint32_t neg_lo = __byte_perm(0xFDFEFF00u, 0xF4F8FAFCu, sel);
+    const uint32_t pos_hi = __byte_perm(0x03020100u, 0x0C080604u, sel_hi);
+    const uint32_t neg_hi = __byte_perm(0xFDFEFF00u, 0xF4F8FAFCu, sel_hi);
+    // byte i = 0xFF when nibble i (i + 4) has bit 3 set: selector bit 3 replicates the top bit of the selected byte
+    const uint32_t q4 = q << 4;
+    uint32_t m_lo, m_hi;
+    asm("prmt.b32 %0, %1, %2, 0xD9C8;" : "=r"(m_lo) : "r"(q4), "r"(q));
+    asm("prmt.b32 %0, %1, %2, 0xFBEA;" : "=r"(m_hi) : "r"(q4), "r"(q));
+    asm("lop3.b32 %0, %1, %2, %3, 0xCA;" : "=r"(lo) : "r"(m_lo), "r"(neg_lo), "r"(pos_lo));
+    asm("lop3.b32 %0, %1, %2, %3, 0xCA;" : "=r"(hi) : "r"(m_hi), "r"(neg_hi), "r"(pos_hi));
 }
 
 // kSeg: 0 one matrix (pair); 2 MoE slots resolved through the routing buffer, one output block per slot, x shared;
@@ -328,30 +331,25 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
             const uint32_t bl = gq * 4 + t;              // this lane's block inside the unit
             // group of four blocks along the (concatenated) activation
             const uint32_t q = (kSeg == 3 ? strm * (k_padded(a.K) / 128) : 0u) + kc * (kUnitBlocks / 4) + gq;
-            // 17 bytes per row at an arbitrary byte offset: six aligned words, funnel-shifted
+            // 17 bytes per row at an arbitrary byte offset o (0..3) inside five aligned words: the scale is byte o,
+            // nibble word i is bytes o + 1 + 4 i .. of them: one funnel shift by 8 (o + 1) bits (a shift of 32
+            // hands back the upper word)
             uint32_t wa[5], wb[5];
-            {
-                const uint32_t pa = sA + bl * 17, pb = sB + bl * 17;
-                const uint32_t ba = pa & ~3u, bb = pb & ~3u;
-                const uint32_t sa = (pa & 3u) * 8u, sb2 = (pb & 3u) * 8u;
-                uint32_t pva = lds_u32(ba), pvb = lds_u32(bb);
+            const uint32_t pa = sA + bl * 17, pb = sB + bl * 17;
+            const uint32_t sha = (pa & 3u) * 8u + 8u, shb = (pb & 3u) * 8u + 8u;
 #pragma unroll
-                for (int i = 0; i < 5; ++i) {
-                    const uint32_t na = lds_u32(ba + 4 * (i + 1)), nbw = lds_u32(bb + 4 * (i + 1));
-                    wa[i] = __funnelshift_r(pva, na, sa);
-                    wb[i] = __funnelshift_r(pvb, nbw, sb2);
-                    pva = na;
-                    pvb = nbw;
-                }
+            for (int i = 0; i < 5; ++i) {
+                wa[i] = lds_u32((pa & ~3u) + 4 * i);
+                wb[i] = lds_u32((pb & ~3u) + 4 * i);
             }
-            // wa[0] byte 0 = scale, bytes 1.. = nibbles: nibble word i = bytes 1+4i .. 4+4i
             const uint32_t xu = b_live ? xu_live + q * 512u : xu_dead;  // 32 units of 16 bytes per group
             int d01[4] = {0, 0, 0, 0}, d2[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint32_t qa = __funnelshift_r(wa[j], wa[j + 1], 8), qb = __funnelshift_r(wb[j], wb[j + 1], 8);
-                const uint32_t a0 = e2m1x4_to_s8(qa & 0xFFFFu), a2 = e2m1x4_to_s8(qa >> 16);
-                const uint32_t a1 = e2m1x4_to_s8(qb & 0xFFFFu), a3 = e2m1x4_to_s8(qb >> 16);
+                const uint32_t qa = __funnelshift_rc(wa[j], wa[j + 1], sha), qb = __funnelshift_rc(wb[j], wb[j + 1], shb);
+                uint32_t a0, a1, a2, a3;
+                e2m1x8_to_s8(qa, a0, a2);
+                e2m1x8_to_s8(qb, a1, a3);
                 const uint4 bx = lds_u128(xu + j * 128);
                 mma_s8(d01, a0, a1, a2, a3, bx.x, bx.y);
                 mma_s8(d2, a0, a1, a2, a3, bx.z, bx.w);
@@ -360,7 +358,7 @@ __global__ void __launch_bounds__(kWarps * 32, 16 / kWarps) dmmv_mxfp4_warp_kern
                 const float PA = (float)(d01[0] * 16384 + d01[1] * 128 + d2[0]);
                 const float PB = (float)(d01[2] * 16384 + d01[3] * 128 + d2[2]);
                 const float xs = s.xs[q >> 1];
-                const uint32_t ea = wa[0] & 0xFFu, eb = wb[0] & 0xFFu;
+                const uint32_t ea = (wa[0] >> (sha - 8u)) & 0xFFu, eb = (wb[0] >> (shb - 8u)) & 0xFFu;
                 const float da = __uint_as_float(ea ? ea << 23 : 0x00400000u) * xs;
                 const float db = __uint_as_float(eb ? eb << 23 : 0x00400000u) * xs;
                 if (NS == 1 || strm == 0) { acc0[0] = fmaf(da, PA, acc0[0]); acc0[1] = fmaf(db, PB, acc0[1]); }  // NS == 1: every stream sums into acc0
