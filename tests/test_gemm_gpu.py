@@ -104,12 +104,15 @@ def test_mul_mm_cta_pairs(gpu, oracle, t, M, N, K):
         assert rel_l2(got[c0:c0 + 128, :M], exact[c0:c0 + 128]) <= TOL_BF16
 
 
-def test_mul_mm_cta_pairs_recorded(gpu, oracle):
-    """The pair kernel inside a recording, replayed: tiles split over pairs are summed behind flags that a memset node
-    of the recording clears, so every replay has to give the product again (a flag left up would let an adder run
-    ahead of the stores it adds to, a flag left down would time out)."""
+@pytest.mark.parametrize("M,N,K", [(2048, 1100, 6144), (512, 700, 2048)], ids=["flags", "zeroed"])
+def test_mul_mm_cta_pairs_recorded(gpu, oracle, M, N, K):
+    """The pair kernel inside a recording, replayed. Tiles split over pairs are summed through memory: with long
+    ranges (24 tiles x 24 blocks over 74 pairs) behind per-tile flags that a memset node of the recording clears (a
+    flag left up would let an adder run ahead of the stores it adds to, a flag left down would time out), with
+    short ranges (4 tiles x 8 blocks over 8 pairs) by adding into D, which a memset node zeroes. Either way every
+    replay has to give the product again."""
     torch, _, _ = gpu
-    t, M, N, K = zb.Q4_K, 512, 700, 2048   # 4 tiles x 8 blocks over 8 pairs: every tile is split
+    t = zb.Q4_K
     g = synth.rng(305, 1)
     w = synth.quant_matrix(g, t, M, K)
     Bm = synth.activations(g, N, K)
@@ -138,7 +141,8 @@ def test_mul_mm_cta_pairs_recorded(gpu, oracle):
             ctx.free_recording(rec)
 
 
-@pytest.mark.parametrize("M,N,K", [(64, 16, 64), (300, 77, 320), (200, 32, 2880), (256, 300, 2880)])
+@pytest.mark.parametrize("M,N,K", [(64, 16, 64), (300, 77, 320), (200, 32, 2880), (256, 300, 2880),
+                                   (1000, 700, 2880), (1152, 520, 448)])
 def test_mul_mm_mxfp4_bf16(gpu, oracle, M, N, K):
     # MXFP4 weights dequantise exactly to bf16, so with bf16 activations the tensor-core product differs
     # from the exact one only by the f32 accumulation order (rows of 17-byte blocks: no alignment at all)

@@ -309,6 +309,8 @@ struct PairArgs {
     GemmArgs g;
     uint32_t* flags;  // [tile][CTA rank]: number of epilogue warps (of 16) of the storing CTA that are done; zero at launch
     uint32_t n_row_pairs, n_tiles;
+    const uint8_t* a_end;  // MXFP4: first byte past the matrix (its rows are fetched as 16-byte aligned supersets)
+    uint32_t zeroed;       // D was zeroed before the launch: the parts of a split tile all add, without an order
 };
 
 struct Segment {
@@ -347,7 +349,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t rank = cluster_ctarank();
-    const uint32_t nblk = g.K >> 8;
+    // MXFP4: K is a multiple of 64 only; the columns past K of the last 256-column block are zeros on both sides
+    // (the dequant warps write zero rows, the activation boxes past K are filled with zeros by the copy engine)
+    const uint32_t nblk = TYPE == T_MXFP4 ? (g.K + 255) >> 8 : g.K >> 8;
     const uint32_t U = p.n_tiles * nblk, G = gridDim.x >> 1, slot = blockIdx.x >> 1;
     const uint32_t u_begin = (uint32_t)part_begin(slot, U, G), u_end = (uint32_t)part_begin(slot + 1, U, G);
     auto tile_m0 = [&](uint32_t tile) { return ((tile % p.n_row_pairs) * 2 + rank) * (uint32_t)kBM; };
@@ -365,7 +369,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
             mbar_init(&bars->empty_b[s], NACC);  // one commit per issuing thread
         }
         for (int s = 0; s < kWSlots; ++s) {
-            mbar_init(&bars->full_w[s], 1);
+            // filled by one TMA box, or (MXFP4) by the 512 dequant threads, whose copies report by themselves
+            mbar_init(&bars->full_w[s], TYPE == T_MXFP4 ? 512 : 1);
             mbar_init(&bars->empty_w[s], 16);  // one arrival per producer warp
         }
         mbar_init(&bars->accum, NACC);
@@ -435,7 +440,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
             // polls without suspending on either ----
             uint32_t ub = u_begin, uw = u_begin;
             Segment sb_seg, sw_seg;
-            bool b_live = next_segment(ub, u_end, nblk, sb_seg), w_live = next_segment(uw, u_end, nblk, sw_seg);
+            bool b_live = next_segment(ub, u_end, nblk, sb_seg);
+            bool w_live = TYPE != T_MXFP4 && next_segment(uw, u_end, nblk, sw_seg);  // MXFP4 rows: no tensor map
             uint32_t b_it = 0;                   // 64-column step inside the activation segment
             uint32_t w_b = w_live ? sw_seg.b0 : 0;
             // per segment (the divisions stay out of the per-copy path)
@@ -509,10 +515,69 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
         uint32_t pw = 0, gb = 0, seg_i = 0, u = u_begin;
         bool ok = true;
         Segment sg;
+        // MXFP4: the dequant threads fetch the raw blocks themselves, one ring slot (a block) ahead: thread (row, j)
+        // copies the 16-byte pieces j, j + 4, j + 8 of the aligned superset of its row's 136 bytes
+        const uint64_t mx_row_bytes = (uint64_t)(g.K >> 5) * 17u;
+        uint32_t uf = u_begin, f_b = 0, f_pw = 1;
+        int f_sw = 0;
+        Segment f_seg{0, 0, 0};
+        bool f_live = false;
+        uint64_t f_row_off = 0, c_row_off = 0;
+        auto mx_row_off = [&](uint32_t tile) {
+            return (uint64_t)min(tile_m0(tile) + (uint32_t)row, g.M - 1) * mx_row_bytes;  // rows past M: computed, dropped
+        };
+        auto mx_fetch = [&]() -> bool {
+            if (!f_live) return true;
+            if (!wait_or_fail(&bars->empty_w[f_sw], f_pw, bars, g.status, 111)) return false;
+            const uint64_t o = f_row_off + (uint64_t)f_b * 136u;
+            const uint8_t* src = g.A + (o & ~(uint64_t)15);
+            uint8_t* dst = smem_w + f_sw * kWBytes + row * 176;
+#pragma unroll
+            for (int pc = 0; pc < 12; pc += 4) {
+                const int piece = pc + j;
+                if (piece < 10) {
+                    const uint8_t* sp = src + piece * 16;
+                    const uint32_t nbytes = sp + 16 <= p.a_end ? 16u : (sp < p.a_end ? (uint32_t)(p.a_end - sp) : 0u);
+                    cp_async16_zfill(dst + piece * 16, nbytes ? sp : g.A, nbytes);
+                }
+            }
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&bars->full_w[f_sw])) : "memory");
+            if (++f_sw == kWSlots) {
+                f_sw = 0;
+                f_pw ^= 1;
+            }
+            if (++f_b == f_seg.b1) {
+                f_live = next_segment(uf, u_end, nblk, f_seg);
+                f_b = f_seg.b0;
+                if (f_live) f_row_off = mx_row_off(f_seg.tile);
+            }
+            return true;
+        };
+        if constexpr (TYPE == T_MXFP4) {
+            f_live = next_segment(uf, u_end, nblk, f_seg);
+            f_b = f_seg.b0;
+            if (f_live) f_row_off = mx_row_off(f_seg.tile);
+            for (int d = 0; d < kWSlots - 1 && ok; ++d) ok = mx_fetch();
+        }
         while (ok && next_segment(u, u_end, nblk, sg)) {
+            if constexpr (TYPE == T_MXFP4) c_row_off = mx_row_off(sg.tile);
             for (uint32_t b = sg.b0; b < sg.b1; ++b, ++gb) {
                 if (!wait_or_fail(&bars->full_w[sw], pw, bars, g.status, 107)) { ok = false; break; }
-                if constexpr (TYPE == T_Q4_K) {
+                if constexpr (TYPE == T_MXFP4) {
+                    if (!mx_fetch()) { ok = false; break; }  // the next block, into the slot the previous one left
+                    if (!wait_or_fail(&bars->empty_a[j], (gb & 1) ^ 1, bars, g.status, 104)) { ok = false; break; }
+                    if (4 * b + (uint32_t)j < (g.K >> 6)) {
+                        const uint32_t off = (uint32_t)((c_row_off + (uint64_t)b * 136u) & 15u) + 34u * (uint32_t)j;
+                        const uint8_t* wp = smem_w + sw * kWBytes + row * 176;
+                        dequant_group_mxfp4(reinterpret_cast<const uint32_t*>(wp + (off & ~3u)), (off & 3u) * 8u, a_stage, row);
+                    } else {  // past K: a zero row (the swizzle permutes 16-byte chunks of zeros)
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<uint4*>(a_stage + row * 128 + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&bars->empty_w[sw]);
+                } else if constexpr (TYPE == T_Q4_K) {
                     const uint8_t* wp = smem_w + sw * kWBytes + row * 144;  // rows past M arrive as zeros
                     const uint4 chdr = *reinterpret_cast<const uint4*>(wp);
                     const uint4 c0 = *reinterpret_cast<const uint4*>(wp + 16 + j * 32);
@@ -552,10 +617,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                 if (!wait_or_fail(&bars->accum, seg_i & 1, bars, g.status, 105)) { ok = false; break; }
                 __syncwarp();
                 tc_fence_after();
-                const bool store = sg.b1 == nblk;  // the tile's last blocks: plain stores, the others add to them
+                // A tile split over pairs. Long ranges (flags): the pair with the tile's last blocks stores, the others add
+                // once its flag is up. Short ranges (D zeroed before the launch): every part adds, nobody waits.
+                const bool whole = sg.b0 == 0 && sg.b1 == nblk;
+                const bool store = p.zeroed ? whole : sg.b1 == nblk;
                 uint32_t* flag = p.flags + 2 * sg.tile + rank;
                 bool go = true;
-                if (!store) {
+                if (!store && !p.zeroed) {
                     if (lane == 0) {
                         uint32_t n = 0;
                         while (ld_acquire_u32(flag) < 16u) {
@@ -611,7 +679,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(free_leader);
-                if (store && sg.b0 > 0) {  // others add to this tile: publish the stores
+                if (store && sg.b0 > 0 && !p.zeroed) {  // others add to this tile: publish the stores
                     __threadfence();
                     __syncwarp();
                     if (lane == 0) atomicAdd(flag, 1u);
@@ -899,6 +967,7 @@ cudaError_t launch_pair(const uint8_t* A, const void* B, float* D, uint32_t M, u
     PairArgs p{};
     p.g = GemmArgs{A, D, M, N, K, stride_d, status};
     p.flags = flags;
+    p.a_end = A + (uint64_t)M * ((uint64_t)(K >> 5) * 17u);  // used by the MXFP4 fetch only
     p.n_row_pairs = (M + 2 * kBM - 1) / (2 * kBM);
     p.n_tiles = p.n_row_pairs * ((N + 511) / 512);
     if (!flags || (uint64_t)p.n_tiles * 2 > n_flags) return cudaErrorNotSupported;
@@ -929,13 +998,19 @@ cudaError_t launch_pair(const uint8_t* A, const void* B, float* D, uint32_t M, u
         }
         if (dev < 64) max_pairs[dev].store(pairs, std::memory_order_relaxed);
     }
-    const uint32_t units = p.n_tiles * (K >> 8);
+    const uint32_t units = p.n_tiles * (TYPE == T_MXFP4 ? (K + 255) >> 8 : K >> 8);
     uint32_t G = units / 4;  // at least four blocks per pair
     G = G < 1 ? 1 : (G > (uint32_t)pairs ? (uint32_t)pairs : G);
     // Nearly as many tiles as pairs: one whole tile per pair (a split tile costs two epilogues and a pass of
     // atomic adds, more than the idle pairs would win)
     if (p.n_tiles <= (uint32_t)pairs && p.n_tiles * 5 >= (uint32_t)pairs * 3) G = p.n_tiles;
     cfg.gridDim = dim3(2 * G, 1, 1);
+    // Ranges of a few blocks, shorter than a tile: every pair has one or two partial segments that all end at about
+    // the same time, so an ordered hand-over (store, flag, add) would put two epilogues in a row; zero D and let
+    // every part add (measured: 5760 x 2880 MXFP4 at 512 tokens 41.9 -> 35.2 us; with ten blocks per pair the
+    // flags are ahead again).
+    const uint32_t per_pair = units / G;
+    p.zeroed = G > 1 && per_pair <= 6 && per_pair < (TYPE == T_MXFP4 ? (K + 255) >> 8 : K >> 8) ? 1u : 0u;
     CUtensorMap map;
     const cuuint64_t dims[2] = {K, N};
     const cuuint64_t strides[1] = {(cuuint64_t)stride_b * 2};
@@ -945,16 +1020,22 @@ cudaError_t launch_pair(const uint8_t* A, const void* B, float* D, uint32_t M, u
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    CUtensorMap wmap;
-    const cuuint64_t row_bytes = (cuuint64_t)(K >> 8) * Raw<TYPE>::kBlock;
-    const cuuint64_t wdims[2] = {row_bytes, M};
-    const cuuint64_t wstrides[1] = {row_bytes};
-    const cuuint32_t wbox[2] = {Raw<TYPE>::kBox, kBM};
-    if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(A), wdims, wstrides, wbox, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return cudaErrorInvalidValue;
-    if (cudaError_t e = cudaMemsetAsync(flags, 0, (size_t)p.n_tiles * 2 * sizeof(uint32_t), s); e != cudaSuccess) return e;
+    CUtensorMap wmap = map;  // MXFP4: not used (rows of 17-byte blocks have no 16-byte pitch)
+    if constexpr (TYPE != T_MXFP4) {
+        const cuuint64_t row_bytes = (cuuint64_t)(K >> 8) * Raw<TYPE>::kBlock;
+        const cuuint64_t wdims[2] = {row_bytes, M};
+        const cuuint64_t wstrides[1] = {row_bytes};
+        const cuuint32_t wbox[2] = {Raw<TYPE>::kBox, kBM};
+        if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(A), wdims, wstrides, wbox, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    if (p.zeroed) {
+        if (cudaError_t e = cudaMemset2DAsync(D, (size_t)stride_d * 4, 0, (size_t)M * 4, N, s); e != cudaSuccess) return e;
+    } else {
+        if (cudaError_t e = cudaMemsetAsync(flags, 0, (size_t)p.n_tiles * 2 * sizeof(uint32_t), s); e != cudaSuccess) return e;
+    }
     return cudaLaunchKernelEx(&cfg, kern, map, wmap, p);
 }
 
@@ -982,10 +1063,19 @@ cudaError_t launch_typed(const uint8_t* A, const void* B, float* D, uint32_t M, 
 cudaError_t launch_mul_mm(uint32_t type, const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N,
                           uint32_t K, uint32_t stride_b, uint32_t stride_d, bool act_bf16, uint32_t* status,
                           uint32_t* tile_flags, uint32_t n_tile_flags, cudaStream_t s, uint64_t* launches) {
-    if ((type != T_Q4_K && type != T_Q6_K) || !act_bf16 || !status) return cudaErrorNotSupported;
-    if ((K & 255u) || (stride_b & 7u) || (reinterpret_cast<uintptr_t>(B) & 15u) ||
-        (reinterpret_cast<uintptr_t>(A) & 15u))
+    if ((type != T_Q4_K && type != T_Q6_K && type != T_MXFP4) || !act_bf16 || !status) return cudaErrorNotSupported;
+    if ((stride_b & 7u) || (reinterpret_cast<uintptr_t>(B) & 15u) || (reinterpret_cast<uintptr_t>(A) & 15u))
         return cudaErrorNotSupported;
+    if (type == T_MXFP4) {
+        // 512-token tiles on the pair kernel (every weight unpacked once per 512 tokens); fewer tokens, or shapes it
+        // leaves, go to the caller's other route (128-token tiles)
+        const uint32_t row_tiles = (M + kBM - 1) / kBM;
+        if (N <= 256 || (K & 63u) || !g_pair_mode || ((row_tiles & 1u) && row_tiles < 7)) return cudaErrorNotSupported;
+        cudaError_t e = launch_pair<T_MXFP4>(A, B, D, M, N, K, stride_b, stride_d, status, tile_flags, n_tile_flags, s);
+        if (e == cudaSuccess && launches) ++*launches;
+        return e;
+    }
+    if (K & 255u) return cudaErrorNotSupported;
     // Q6_K rows are 210 bytes per block: the TMA row pitch is a multiple of 16 only for K % 2048 == 0
     if (type == T_Q6_K && (K & 2047u)) return cudaErrorNotSupported;
     if (N < 16) return cudaErrorNotSupported;  // a handful of tokens: the matvec-style kernels are the better fit

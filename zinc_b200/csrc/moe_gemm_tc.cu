@@ -100,12 +100,6 @@ __device__ __forceinline__ bool moe_wait(uint64_t* bar, uint32_t parity, MoeBars
     return false;
 }
 
-// 16 bytes global -> shared; bytes past `n` (0..16) are written as zeros and not read.
-__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gmem_src, uint32_t n) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(n)
-                 : "memory");
-}
-
 // Position of the dequant warps in the flat sequence of (work item, 256-column block).
 struct BlockCursor {
     uint32_t w;             // work item

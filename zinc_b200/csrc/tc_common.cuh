@@ -151,6 +151,12 @@ __host__ __device__ constexpr uint32_t instr_desc_pair() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
+// 16 bytes global -> shared; bytes past `n` (0..16) are written as zeros and not read.
+__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gmem_src, uint32_t n) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(n)
+                 : "memory");
+}
+
 // 32 consecutive columns of this thread's tensor-memory lane (issued, not waited for)
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
     asm volatile(
