@@ -74,7 +74,7 @@ def test_mul_mm(gpu, oracle, t, act, M, N, K):
 
 
 @pytest.mark.parametrize("t", [zb.Q4_K, zb.Q6_K], ids=["q4_k", "q6_k"])
-@pytest.mark.parametrize("M,N,K", [(2043, 2600, 1024), (1280, 4100, 512)])
+@pytest.mark.parametrize("M,N,K", [(2043, 2600, 1024), (1280, 4100, 512), (1026, 600, 2816)])
 def test_mul_mm_cta_pairs(gpu, oracle, t, M, N, K):
     """Shapes with enough tiles that K is not split and an even number of 128-row tiles: the large-tile kernel runs
     as CTA pairs (one MMA of 256 rows per pair, each CTA fetching half of every activation box). Ragged last row

@@ -327,10 +327,14 @@ __device__ __forceinline__ bool next_segment(uint32_t& u, uint32_t u1, uint32_t 
 
 constexpr uint32_t kFlagSpinLimit = 1u << 21;
 
-template <int TYPE>
+// kFetch: the dequant threads copy the raw blocks themselves (rows a tensor map cannot describe: MXFP4 always, Q6_K
+// when the row pitch is not a multiple of 16 bytes); else one thread fetches them as TMA boxes.
+template <int TYPE, bool kFetch = TYPE == T_MXFP4>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_w,
                     const PairArgs p) {
+    static_assert(TYPE != T_MXFP4 || kFetch, "MXFP4 rows have no tensor map");
+    static_assert(TYPE != T_Q4_K || !kFetch, "Q4_K rows always have a 16-byte pitch");
     constexpr int BN = 256, NACC = 2;
     using T = Tile<TYPE, BN>;
     // A CTA's activation slot holds 256 consecutive tokens, n0 + 256 * rank ..: its first 128 are this CTA's half
@@ -370,7 +374,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
         }
         for (int s = 0; s < kWSlots; ++s) {
             // filled by one TMA box, or (MXFP4) by the 512 dequant threads, whose copies report by themselves
-            mbar_init(&bars->full_w[s], TYPE == T_MXFP4 ? 512 : 1);
+            mbar_init(&bars->full_w[s], kFetch ? 512 : 1);
             mbar_init(&bars->empty_w[s], 16);  // one arrival per producer warp
         }
         mbar_init(&bars->accum, NACC);
@@ -441,7 +445,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
             uint32_t ub = u_begin, uw = u_begin;
             Segment sb_seg, sw_seg;
             bool b_live = next_segment(ub, u_end, nblk, sb_seg);
-            bool w_live = TYPE != T_MXFP4 && next_segment(uw, u_end, nblk, sw_seg);  // MXFP4 rows: no tensor map
+            bool w_live = !kFetch && next_segment(uw, u_end, nblk, sw_seg);
             uint32_t b_it = 0;                   // 64-column step inside the activation segment
             uint32_t w_b = w_live ? sw_seg.b0 : 0;
             // per segment (the divisions stay out of the per-copy path)
@@ -515,9 +519,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
         uint32_t pw = 0, gb = 0, seg_i = 0, u = u_begin;
         bool ok = true;
         Segment sg;
-        // MXFP4: the dequant threads fetch the raw blocks themselves, one ring slot (a block) ahead: thread (row, j)
-        // copies the 16-byte pieces j, j + 4, j + 8 of the aligned superset of its row's 136 bytes
-        const uint64_t mx_row_bytes = (uint64_t)(g.K >> 5) * 17u;
+        // kFetch: the dequant threads fetch the raw blocks themselves, one ring slot (a block) ahead: thread (row, j)
+        // copies the 16-byte pieces j, j + 4, ... of the aligned superset of its row's block (136 or 210 bytes)
+        constexpr uint32_t kRawBlock = Raw<TYPE>::kBlock, kRawRow = Raw<TYPE>::kBox;
+        constexpr int kRawPieces = TYPE == T_MXFP4 ? 10 : 15;  // (15 + block bytes) / 16 rounded up
+        const uint64_t mx_row_bytes = TYPE == T_MXFP4 ? (uint64_t)(g.K >> 5) * 17u : (uint64_t)(g.K >> 8) * kRawBlock;
         uint32_t uf = u_begin, f_b = 0, f_pw = 1;
         int f_sw = 0;
         Segment f_seg{0, 0, 0};
@@ -529,13 +535,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
         auto mx_fetch = [&]() -> bool {
             if (!f_live) return true;
             if (!wait_or_fail(&bars->empty_w[f_sw], f_pw, bars, g.status, 111)) return false;
-            const uint64_t o = f_row_off + (uint64_t)f_b * 136u;
+            const uint64_t o = f_row_off + (uint64_t)f_b * kRawBlock;
             const uint8_t* src = g.A + (o & ~(uint64_t)15);
-            uint8_t* dst = smem_w + f_sw * kWBytes + row * 176;
+            uint8_t* dst = smem_w + f_sw * kWBytes + row * kRawRow;
 #pragma unroll
-            for (int pc = 0; pc < 12; pc += 4) {
+            for (int pc = 0; pc < 16; pc += 4) {
                 const int piece = pc + j;
-                if (piece < 10) {
+                if (piece < kRawPieces) {
                     const uint8_t* sp = src + piece * 16;
                     const uint32_t nbytes = sp + 16 <= p.a_end ? 16u : (sp < p.a_end ? (uint32_t)(p.a_end - sp) : 0u);
                     cp_async16_zfill(dst + piece * 16, nbytes ? sp : g.A, nbytes);
@@ -553,18 +559,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
             }
             return true;
         };
-        if constexpr (TYPE == T_MXFP4) {
+        if constexpr (kFetch) {
             f_live = next_segment(uf, u_end, nblk, f_seg);
             f_b = f_seg.b0;
             if (f_live) f_row_off = mx_row_off(f_seg.tile);
             for (int d = 0; d < kWSlots - 1 && ok; ++d) ok = mx_fetch();
         }
         while (ok && next_segment(u, u_end, nblk, sg)) {
-            if constexpr (TYPE == T_MXFP4) c_row_off = mx_row_off(sg.tile);
+            if constexpr (kFetch) c_row_off = mx_row_off(sg.tile);
             for (uint32_t b = sg.b0; b < sg.b1; ++b, ++gb) {
                 if (!wait_or_fail(&bars->full_w[sw], pw, bars, g.status, 107)) { ok = false; break; }
-                if constexpr (TYPE == T_MXFP4) {
+                if constexpr (kFetch) {
                     if (!mx_fetch()) { ok = false; break; }  // the next block, into the slot the previous one left
+                }
+                if constexpr (TYPE == T_MXFP4) {
                     if (!wait_or_fail(&bars->empty_a[j], (gb & 1) ^ 1, bars, g.status, 104)) { ok = false; break; }
                     if (4 * b + (uint32_t)j < (g.K >> 6)) {
                         const uint32_t off = (uint32_t)((c_row_off + (uint64_t)b * 136u) & 15u) + 34u * (uint32_t)j;
@@ -593,8 +601,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_con
                     dequant_group_q4k(c0, c1, d * (float)s0, dmin * (float)mn0, d * (float)s1, dmin * (float)mn1, a_stage,
                                       row);
                 } else {
-                    // the block starts (b * 210) & 15 bytes into the box; that offset is even
-                    const uint32_t off = (b * 210u) & 15u;
+                    // the block starts `off` bytes into the box or (fetched by the threads) into the row's aligned
+                    // superset; that offset is even
+                    const uint32_t off = kFetch ? (uint32_t)((c_row_off + (uint64_t)b * 210u) & 15u) : (b * 210u) & 15u;
                     const uint8_t* wp = smem_w + sw * kWBytes + row * 240 + (off & ~3u);
                     if (!wait_or_fail(&bars->empty_a[j], (gb & 1) ^ 1, bars, g.status, 104)) { ok = false; break; }
                     dequant_group_q6k(reinterpret_cast<const uint32_t*>(wp), (off & 2u) * 8u, j, a_stage, row);
@@ -958,7 +967,7 @@ cudaError_t launch_small(const uint8_t* A, const void* B, float* D, uint32_t M, 
 }
 
 // The persistent pair kernel. cudaErrorNotSupported: the caller takes another path (nothing launched or written).
-template <int TYPE>
+template <int TYPE, bool kFetch = TYPE == T_MXFP4>
 cudaError_t launch_pair(const uint8_t* A, const void* B, float* D, uint32_t M, uint32_t N, uint32_t K, uint32_t stride_b,
                         uint32_t stride_d, uint32_t* status, uint32_t* flags, uint32_t n_flags, cudaStream_t s) {
     using T = Tile<TYPE, 256>;
@@ -967,11 +976,12 @@ cudaError_t launch_pair(const uint8_t* A, const void* B, float* D, uint32_t M, u
     PairArgs p{};
     p.g = GemmArgs{A, D, M, N, K, stride_d, status};
     p.flags = flags;
-    p.a_end = A + (uint64_t)M * ((uint64_t)(K >> 5) * 17u);  // used by the MXFP4 fetch only
+    // first byte past the matrix: used where the dequant threads fetch their rows as aligned supersets
+    p.a_end = A + (uint64_t)M * (TYPE == T_MXFP4 ? (uint64_t)(K >> 5) * 17u : (uint64_t)(K >> 8) * Raw<TYPE>::kBlock);
     p.n_row_pairs = (M + 2 * kBM - 1) / (2 * kBM);
     p.n_tiles = p.n_row_pairs * ((N + 511) / 512);
     if (!flags || (uint64_t)p.n_tiles * 2 > n_flags) return cudaErrorNotSupported;
-    auto kern = gemm_tc_pair_kernel<TYPE>;
+    auto kern = gemm_tc_pair_kernel<TYPE, kFetch>;
     static std::atomic<uint64_t> attr_done{0};  // per device ordinal
     if (cudaError_t ea = ensure_dynamic_smem(kern, (int)T::kSmemBytes, attr_done); ea != cudaSuccess) return ea;
     cudaLaunchConfig_t cfg = {};
@@ -1020,8 +1030,8 @@ cudaError_t launch_pair(const uint8_t* A, const void* B, float* D, uint32_t M, u
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
-    CUtensorMap wmap = map;  // MXFP4: not used (rows of 17-byte blocks have no 16-byte pitch)
-    if constexpr (TYPE != T_MXFP4) {
+    CUtensorMap wmap = map;  // not used where the rows have no 16-byte pitch
+    if constexpr (!kFetch) {
         const cuuint64_t row_bytes = (cuuint64_t)(K >> 8) * Raw<TYPE>::kBlock;
         const cuuint64_t wdims[2] = {row_bytes, M};
         const cuuint64_t wstrides[1] = {row_bytes};
@@ -1076,8 +1086,16 @@ cudaError_t launch_mul_mm(uint32_t type, const uint8_t* A, const void* B, float*
         return e;
     }
     if (K & 255u) return cudaErrorNotSupported;
-    // Q6_K rows are 210 bytes per block: the TMA row pitch is a multiple of 16 only for K % 2048 == 0
-    if (type == T_Q6_K && (K & 2047u)) return cudaErrorNotSupported;
+    // Q6_K rows are 210 bytes per block: the TMA row pitch is a multiple of 16 only for K % 2048 == 0. Other K:
+    // the pair kernel with the dequant threads fetching their rows (more than 256 tokens), else the caller's
+    // 128-token-tile route.
+    if (type == T_Q6_K && (K & 2047u)) {
+        const uint32_t row_tiles = (M + kBM - 1) / kBM;
+        if (N <= 256 || !g_pair_mode || ((row_tiles & 1u) && row_tiles < 7)) return cudaErrorNotSupported;
+        cudaError_t e = launch_pair<T_Q6_K, true>(A, B, D, M, N, K, stride_b, stride_d, status, tile_flags, n_tile_flags, s);
+        if (e == cudaSuccess && launches) ++*launches;
+        return e;
+    }
     if (N < 16) return cudaErrorNotSupported;  // a handful of tokens: the matvec-style kernels are the better fit
     cudaError_t e = type == T_Q4_K
                         ? launch_typed<T_Q4_K>(A, B, D, M, N, K, stride_b, stride_d, status, tile_flags, n_tile_flags, s)
