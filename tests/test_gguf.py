@@ -105,7 +105,7 @@ def test_errors(tmp_path):
     with open(short, "r+b") as f:  # drop the last tensor's bytes: the table then points outside the file
         f.truncate(data_offset + offsets[-1] + 100)
     assert any(l.startswith("tensor output_norm.weight error InvalidTensor") for l in _parse(short))
-    # dimensions whose product wraps around 64 bits: refused while the table is read
+    # dimensions whose product overflows 64 bits: refused while the table is read
     wrap = str(tmp_path / "wrap.gguf")
     write_gguf(wrap, [("w", [1 << 33, 1 << 33], 12, b"\0" * 144)] + ts)
     assert _parse(wrap)[0].startswith("error InvalidTensor")
